@@ -1,0 +1,1073 @@
+/*
+ * geist_b200_abi.cu — the C ABI declared in include/geist_b200.h: argument
+ * checks, launch planning, the sampler.h host-pointer surface, sessions and
+ * the multi-session batcher. All numeric work happens in the kernels of
+ * sampler_kernels.cu; nothing here computes a token on the CPU.
+ */
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/geist_b200.h"
+#include "sampler_params.h"
+
+namespace gb {
+size_t      sample_rows_fixed_smem();
+cudaError_t launch_sample_rows(const SampleParams &p, int cluster, size_t smem_bytes, cudaStream_t stream);
+int         sample_rows_max_clusters(int cluster, size_t smem_bytes);
+cudaError_t launch_merge_sample(const MergeParams &p, cudaStream_t stream);
+cudaError_t launch_accept(const AcceptParams &p, cudaStream_t stream);
+cudaError_t launch_scatter_kept(const int *kept_n, const int *kept_idx, const float *kept_val, int kept_cap, int n_rows, int V, int vocab_offset, float *dense, cudaStream_t stream);
+cudaError_t launch_softmax_rows(const float *logits, long long row_stride, int n_rows, int V, const float *temperature, float *probs, double *sums, cudaStream_t stream);
+cudaError_t launch_post_step(const int *slot, int n_seq, int per_seq, int first, const int *tokens, const int *counts, int *hist, int hist_cap, int *hist_len, long long *hist_total, const unsigned long long *rng_tmp, unsigned long long *rng, cudaStream_t stream);
+} /* namespace gb */
+
+/* ------------------------------------------------------------- errors -- */
+
+static thread_local std::string g_err;
+
+static enum geist_status fail(enum geist_status s, const char *fmt, ...) {
+    char    buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return s;
+}
+
+#define CUDA_TRY(expr)                                                                                   \
+    do {                                                                                                 \
+        cudaError_t e_ = (expr);                                                                         \
+        if (e_ != cudaSuccess) {                                                                         \
+            return fail(e_ == cudaErrorMemoryAllocation ? GEIST_E_OOM : GEIST_E_BACKEND, "%s: %s", #expr, \
+                        cudaGetErrorString(e_));                                                         \
+        }                                                                                                \
+    } while (0)
+
+extern "C" const char *geist_b200_errmsg(void) { return g_err.c_str(); }
+
+/* ------------------------------------------------------- launch planning -- */
+
+namespace {
+
+constexpr size_t kSmemMax      = 227 * 1024; /* opt-in shared memory per CTA on sm_100 */
+constexpr int    kSliceTarget  = 16384;      /* floats per CTA the planner aims for (64 KiB) */
+
+struct Plan {
+    int    cluster      = 0;
+    int    slice        = 0;
+    int    slice_bytes  = 0;
+    int    bitmap_words = 0;
+    int    hist_cap     = 0;
+    size_t smem         = 0;
+};
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+/* hist_max = 0: no history pointer will be given. */
+bool shape_for(size_t V, size_t hist_max, int cluster, Plan &pl) {
+    size_t slice = round_up((V + cluster - 1) / cluster, 4);
+    if ((size_t) (cluster - 1) * slice >= V && cluster > 1) {
+        return false; /* a CTA would own nothing */
+    }
+    pl.cluster      = cluster;
+    pl.slice        = (int) slice;
+    pl.slice_bytes  = (int) round_up(std::max(slice * 4, (size_t) 20 * cluster * gb::kLocalCand), 128);
+    pl.bitmap_words = hist_max ? (int) ((slice + 31) / 32) : 0;
+    pl.hist_cap     = hist_max ? (int) std::min(hist_max, slice) : 0;
+    pl.smem         = (size_t) pl.slice_bytes + gb::sample_rows_fixed_smem() + (size_t) pl.bitmap_words * 4 + (size_t) pl.hist_cap * 8;
+    return pl.smem <= kSmemMax;
+}
+
+bool make_plan(size_t V, size_t hist_max, Plan &pl) {
+    int want = (int) std::min<size_t>((V + kSliceTarget - 1) / kSliceTarget, gb::kMaxCluster);
+    want     = std::max(want, 1);
+    /* first choice: ~64 KiB slices; then any cluster size that fits and that the device can place */
+    for (int c = want; c <= gb::kMaxCluster; c++) {
+        if (shape_for(V, hist_max, c, pl) && gb::sample_rows_max_clusters(c, pl.smem) > 0) {
+            return true;
+        }
+    }
+    for (int c = want - 1; c >= 1; c--) {
+        if (shape_for(V, hist_max, c, pl) && gb::sample_rows_max_clusters(c, pl.smem) > 0) {
+            return true;
+        }
+    }
+    return false;
+}
+
+struct PlanCache {
+    std::mutex mu;
+    struct Key {
+        int    dev;
+        size_t V, H;
+    };
+    std::vector<std::pair<Key, Plan>> items;
+
+    bool get(size_t V, size_t H, Plan &pl) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        std::lock_guard<std::mutex> lk(mu);
+        for (auto &it : items) {
+            if (it.first.dev == dev && it.first.V == V && it.first.H == H) {
+                pl = it.second;
+                return pl.cluster > 0;
+            }
+        }
+        Plan p;
+        bool ok = make_plan(V, H, p);
+        if (!ok) {
+            p = Plan();
+        }
+        items.push_back({{dev, V, H}, p});
+        pl = p;
+        return ok;
+    }
+} g_plans;
+
+cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+} /* namespace */
+
+/* ------------------------------------------------------------- context -- */
+
+struct geist_b200_ctx {
+    int          device = 0;
+    cudaStream_t stream = nullptr;
+    /* scratch of the host-pointer surface: one row + a handful of words */
+    float *d_row     = nullptr;
+    size_t d_row_cap = 0;
+    struct Small {
+        float              T;
+        int                top_k;
+        float              top_p;
+        int                token;
+        int                status;
+        int                pad;
+        unsigned long long rng_in;
+        unsigned long long rng_out;
+    };
+    Small *d_small = nullptr;
+    Small *h_small = nullptr; /* pinned */
+};
+
+extern "C" enum geist_status geist_b200_ctx_create(int device, struct geist_b200_ctx **out) {
+    if (out == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "ctx_create: out is NULL");
+    }
+    *out = nullptr;
+    int n = 0;
+    CUDA_TRY(cudaGetDeviceCount(&n));
+    if (device < 0 || device >= n) {
+        return fail(GEIST_E_INVALID_ARG, "ctx_create: device %d of %d", device, n);
+    }
+    CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        return fail(GEIST_E_UNSUPPORTED, "ctx_create: device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+    }
+    geist_b200_ctx *c = new (std::nothrow) geist_b200_ctx();
+    if (c == nullptr) {
+        return fail(GEIST_E_OOM, "ctx_create: host allocation");
+    }
+    c->device = device;
+    cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) {
+        e = cudaMalloc(&c->d_small, sizeof(geist_b200_ctx::Small));
+    }
+    if (e == cudaSuccess) {
+        e = cudaHostAlloc(&c->h_small, sizeof(geist_b200_ctx::Small), cudaHostAllocDefault);
+    }
+    if (e != cudaSuccess) {
+        geist_b200_ctx_destroy(c);
+        return fail(GEIST_E_BACKEND, "ctx_create: %s", cudaGetErrorString(e));
+    }
+    *out = c;
+    return GEIST_OK;
+}
+
+extern "C" void geist_b200_ctx_destroy(struct geist_b200_ctx *c) {
+    if (c == nullptr) {
+        return;
+    }
+    cudaSetDevice(c->device);
+    if (c->stream) {
+        cudaStreamSynchronize(c->stream);
+    }
+    cudaFree(c->d_row);
+    cudaFree(c->d_small);
+    cudaFreeHost(c->h_small);
+    if (c->stream) {
+        cudaStreamDestroy(c->stream);
+    }
+    delete c;
+}
+
+/* ------------------------------------------------------- batched entries -- */
+
+static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct geist_b200_batch *b, void *stream, unsigned flags) {
+    if (ctx == nullptr || b == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: NULL context or batch");
+    }
+    if (b->logits == nullptr || b->tokens == nullptr || b->row_status == nullptr || b->temperature == nullptr || b->top_k == nullptr || b->top_p == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: logits, tokens, row_status, temperature, top_k, top_p are required");
+    }
+    if (b->n_seq == 0 || b->rows_per_seq == 0 || b->n_vocab == 0) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: n_seq, rows_per_seq and n_vocab must be positive");
+    }
+    if (b->n_vocab > 0x7fffffffu || b->n_seq * b->rows_per_seq > (size_t) 0x7fffffff / gb::kMaxCluster) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: sizes exceed int32 ids / grid limits");
+    }
+    if (b->row_stride < b->n_vocab) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: row_stride %zu < n_vocab %zu", b->row_stride, b->n_vocab);
+    }
+    if (b->rows_per_seq > 1 && b->rng_out != nullptr && (const void *) b->rng_out == (const void *) b->rng_in) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: rng_out may alias rng_in only when rows_per_seq == 1");
+    }
+    if (b->history != nullptr && (b->history_len == nullptr || b->history_stride == 0)) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: history needs history_len and history_stride");
+    }
+    if (b->fed_tokens != nullptr && b->fed_stride < b->rows_per_seq) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: fed_stride %zu < rows_per_seq %zu", b->fed_stride, b->rows_per_seq);
+    }
+    if (b->kept_cap < 0 || (b->kept_cap > 0 && (b->kept_n == nullptr || b->kept_idx == nullptr || b->kept_prob == nullptr))) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: kept_cap > 0 needs kept_n, kept_idx and kept_prob");
+    }
+    if ((flags & gb::F_SELECT_ONLY) && b->kept_cap <= 0) {
+        return fail(GEIST_E_INVALID_ARG, "shard_select: kept_cap must hold the shard's candidates");
+    }
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    const size_t hist_max = (b->history || b->fed_tokens) ? (b->history ? b->history_stride : 0) + (b->fed_tokens ? b->rows_per_seq : 0) : 0;
+    Plan         pl;
+    if (!g_plans.get(b->n_vocab, hist_max, pl)) {
+        return fail(GEIST_E_UNSUPPORTED, "sample_batch: no launch shape for n_vocab=%zu with %zu history ids per row (shared memory)", b->n_vocab, hist_max);
+    }
+    gb::SampleParams p{};
+    p.logits       = b->logits;
+    p.row_stride   = (long long) b->row_stride;
+    p.V            = (int) b->n_vocab;
+    p.n_rows       = (int) (b->n_seq * b->rows_per_seq);
+    p.rows_per_seq = (int) b->rows_per_seq;
+    p.vocab_offset = b->vocab_offset;
+    p.slot         = b->slot;
+    p.temperature  = b->temperature;
+    p.top_k        = b->top_k;
+    p.top_p        = b->top_p;
+    p.rep          = b->repetition_penalty;
+    p.freq         = b->frequency_penalty;
+    p.pres         = b->presence_penalty;
+    p.hist         = b->history;
+    p.hist_stride  = (long long) b->history_stride;
+    p.hist_len     = b->history_len;
+    p.extra        = b->fed_tokens;
+    p.extra_stride = (long long) b->fed_stride;
+    p.rng_in       = reinterpret_cast<const unsigned long long *>(b->rng_in);
+    p.rng_out      = reinterpret_cast<unsigned long long *>(b->rng_out);
+    p.tokens       = b->tokens;
+    p.status       = b->row_status;
+    p.out_logits   = b->out_logits;
+    p.kept_cap     = b->kept_cap;
+    p.kept_n       = b->kept_n;
+    p.kept_idx     = b->kept_idx;
+    p.kept_val     = b->kept_prob;
+    p.slice        = pl.slice;
+    p.slice_bytes  = pl.slice_bytes;
+    p.bitmap_words = pl.bitmap_words;
+    p.hist_cap     = pl.hist_cap;
+    p.aligned      = ((reinterpret_cast<uintptr_t>(b->logits) & 15u) == 0 && (b->row_stride & 3u) == 0) ? 1 : 0;
+    p.flags        = flags;
+    cudaStream_t st = stream ? as_stream(stream) : ctx->stream;
+    CUDA_TRY(gb::launch_sample_rows(p, pl.cluster, pl.smem, st));
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_sample_batch(struct geist_b200_ctx *ctx, const struct geist_b200_batch *b, void *stream) {
+    if (b != nullptr && (b->rng_in == nullptr || b->rng_out == nullptr)) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: rng_in and rng_out are required");
+    }
+    return launch_batch(ctx, b, stream, 0u);
+}
+
+extern "C" enum geist_status geist_b200_shard_select(struct geist_b200_ctx *ctx, const struct geist_b200_batch *b, void *stream) {
+    if (b != nullptr && b->rows_per_seq != 1) {
+        return fail(GEIST_E_INVALID_ARG, "shard_select: rows_per_seq must be 1");
+    }
+    return launch_batch(ctx, b, stream, gb::F_SELECT_ONLY);
+}
+
+extern "C" enum geist_status geist_b200_shard_merge_sample(struct geist_b200_ctx *ctx, const struct geist_b200_merge *m, void *stream) {
+    if (ctx == nullptr || m == nullptr || m->cand_val == nullptr || m->cand_gid == nullptr || m->cand_n == nullptr || m->temperature == nullptr || m->top_k == nullptr ||
+        m->rng_in == nullptr || m->tokens == nullptr || m->row_status == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "shard_merge_sample: missing pointer");
+    }
+    if (m->n_shards == 0 || m->n_rows == 0 || m->cand_stride == 0 || m->n_shards * m->cand_stride > 8192) {
+        return fail(GEIST_E_INVALID_ARG, "shard_merge_sample: n_shards * cand_stride must be in [1, 8192]");
+    }
+    if (m->kept_cap > 0 && (m->kept_n == nullptr || m->kept_idx == nullptr || m->kept_prob == nullptr)) {
+        return fail(GEIST_E_INVALID_ARG, "shard_merge_sample: kept_cap > 0 needs the kept arrays");
+    }
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    gb::MergeParams p{};
+    p.cand_val    = m->cand_val;
+    p.cand_gid    = m->cand_gid;
+    p.cand_n      = m->cand_n;
+    p.n_shards    = (int) m->n_shards;
+    p.n_rows      = (int) m->n_rows;
+    p.k_stride    = (int) m->cand_stride;
+    p.temperature = m->temperature;
+    p.top_k       = m->top_k;
+    p.rng_in      = reinterpret_cast<const unsigned long long *>(m->rng_in);
+    p.rng_out     = reinterpret_cast<unsigned long long *>(m->rng_out);
+    p.tokens      = m->tokens;
+    p.status      = m->row_status;
+    p.kept_cap    = m->kept_cap;
+    p.kept_n      = m->kept_n;
+    p.kept_idx    = m->kept_idx;
+    p.kept_val    = m->kept_prob;
+    CUDA_TRY(gb::launch_merge_sample(p, stream ? as_stream(stream) : ctx->stream));
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_accept_batch(struct geist_b200_ctx *ctx, size_t n_seq, size_t k, const int32_t *fed, const int32_t *verify_out, int32_t *accepted,
+                                                     int32_t *n_emitted, int32_t *emitted, void *stream) {
+    if (ctx == nullptr || fed == nullptr || verify_out == nullptr || accepted == nullptr || n_emitted == nullptr || emitted == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "accept_batch: missing pointer");
+    }
+    if (n_seq == 0 || k == 0 || k > GEIST_B200_SPEC_KMAX) {
+        return fail(GEIST_E_INVALID_ARG, "accept_batch: need n_seq > 0 and 1 <= k <= %d", GEIST_B200_SPEC_KMAX);
+    }
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    gb::AcceptParams p{fed, verify_out, (int) n_seq, (int) k, accepted, n_emitted, emitted};
+    CUDA_TRY(gb::launch_accept(p, stream ? as_stream(stream) : ctx->stream));
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_softmax(struct geist_b200_ctx *ctx, const float *logits, size_t row_stride, size_t n_rows, size_t n_vocab, const float *temperature,
+                                                float *probs, double *sums, void *stream) {
+    if (ctx == nullptr || logits == nullptr || temperature == nullptr || probs == nullptr || n_rows == 0 || n_vocab == 0 || n_vocab > 0x7fffffffu || row_stride < n_vocab) {
+        return fail(GEIST_E_INVALID_ARG, "softmax: bad argument");
+    }
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    CUDA_TRY(gb::launch_softmax_rows(logits, (long long) row_stride, (int) n_rows, (int) n_vocab, temperature, probs, sums, stream ? as_stream(stream) : ctx->stream));
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_scatter_kept(struct geist_b200_ctx *ctx, size_t n_rows, size_t n_vocab, int32_t kept_cap, const int32_t *kept_n, const int32_t *kept_idx,
+                                                     const float *kept_prob, int32_t vocab_offset, float *dense, void *stream) {
+    if (ctx == nullptr || kept_n == nullptr || kept_idx == nullptr || kept_prob == nullptr || dense == nullptr || n_rows == 0 || n_vocab == 0 || kept_cap <= 0) {
+        return fail(GEIST_E_INVALID_ARG, "scatter_kept: bad argument");
+    }
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    CUDA_TRY(gb::launch_scatter_kept(kept_n, kept_idx, kept_prob, kept_cap, (int) n_rows, (int) n_vocab, vocab_offset, dense, stream ? as_stream(stream) : ctx->stream));
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history, int32_t *cluster, int32_t *slice, int32_t *smem_bytes, int32_t *resident_clusters) {
+    Plan pl;
+    if (n_vocab == 0 || !g_plans.get(n_vocab, max_history, pl)) {
+        if (cluster) {
+            *cluster = 0;
+        }
+        if (resident_clusters) {
+            *resident_clusters = 0;
+        }
+        return fail(GEIST_E_UNSUPPORTED, "plan: no launch shape for n_vocab=%zu, history=%zu", n_vocab, max_history);
+    }
+    if (cluster) {
+        *cluster = pl.cluster;
+    }
+    if (slice) {
+        *slice = pl.slice;
+    }
+    if (smem_bytes) {
+        *smem_bytes = (int32_t) pl.smem;
+    }
+    if (resident_clusters) {
+        *resident_clusters = gb::sample_rows_max_clusters(pl.cluster, pl.smem);
+    }
+    return GEIST_OK;
+}
+
+/* -------------------------------------------- sampler.h host-pointer surface -- */
+
+extern "C" void geist_rng_seed(struct geist_rng *rng, uint64_t seed) {
+    if (rng != nullptr) {
+        rng->state = seed != 0 ? seed : 0x9E3779B97F4A7C15ULL; /* the all-zero state is a fixed point */
+    }
+}
+
+extern "C" uint64_t geist_rng_next_u64(struct geist_rng *rng) {
+    uint64_t s = rng->state;
+    s ^= s >> 12;
+    s ^= s << 25;
+    s ^= s >> 27;
+    rng->state = s;
+    return s * 0x2545F4914F6CDD1DULL;
+}
+
+extern "C" float geist_rng_next_unit(struct geist_rng *rng) { return (float) (uint32_t) (geist_rng_next_u64(rng) >> 40) * (1.0f / 16777216.0f); }
+
+namespace {
+
+std::mutex      g_default_mu;
+geist_b200_ctx *g_default_ctx[64] = {nullptr};
+
+geist_b200_ctx *default_ctx() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        fail(GEIST_E_BACKEND, "no CUDA device is current");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lk(g_default_mu);
+    if (g_default_ctx[dev] == nullptr) {
+        if (geist_b200_ctx_create(dev, &g_default_ctx[dev]) != GEIST_OK) {
+            return nullptr;
+        }
+    }
+    return g_default_ctx[dev];
+}
+
+/* One host row through the batched kernel. staging: optional pinned buffer of n floats. */
+geist_token_t sample_host_row(size_t n, const float *logits, float *staging, float T, int top_k, float top_p, struct geist_rng *rng) {
+    if (n == 0 || logits == nullptr) {
+        fail(GEIST_E_INVALID_ARG, "sampler: empty row");
+        return -1;
+    }
+    geist_b200_ctx *c = default_ctx();
+    if (c == nullptr) {
+        return -1;
+    }
+    static std::mutex           mu; /* the default context's scratch is shared */
+    std::lock_guard<std::mutex> lk(mu);
+    cudaError_t                 e = cudaSetDevice(c->device);
+    if (e == cudaSuccess && c->d_row_cap < n) {
+        cudaFree(c->d_row);
+        c->d_row     = nullptr;
+        c->d_row_cap = 0;
+        e            = cudaMalloc(&c->d_row, n * sizeof(float));
+        if (e == cudaSuccess) {
+            c->d_row_cap = n;
+        }
+    }
+    if (e == cudaSuccess) {
+        const float *src = logits;
+        if (staging != nullptr) {
+            memcpy(staging, logits, n * sizeof(float));
+            src = staging;
+        }
+        e = cudaMemcpyAsync(c->d_row, src, n * sizeof(float), cudaMemcpyHostToDevice, c->stream);
+    }
+    if (e != cudaSuccess) {
+        fail(GEIST_E_BACKEND, "sampler: staging the row: %s", cudaGetErrorString(e));
+        return -1;
+    }
+    geist_b200_ctx::Small *h = c->h_small;
+    h->T                     = T;
+    h->top_k                 = top_k;
+    h->top_p                 = top_p;
+    h->token                 = -1;
+    h->status                = 0;
+    h->rng_in                = rng ? rng->state : 1ull;
+    h->rng_out               = h->rng_in;
+    e                        = cudaMemcpyAsync(c->d_small, h, sizeof *h, cudaMemcpyHostToDevice, c->stream);
+    if (e != cudaSuccess) {
+        fail(GEIST_E_BACKEND, "sampler: %s", cudaGetErrorString(e));
+        return -1;
+    }
+    geist_b200_batch b{};
+    b.logits       = c->d_row;
+    b.row_stride   = n;
+    b.n_seq        = 1;
+    b.rows_per_seq = 1;
+    b.n_vocab      = n;
+    b.temperature  = &c->d_small->T;
+    b.top_k        = &c->d_small->top_k;
+    b.top_p        = &c->d_small->top_p;
+    b.rng_in       = reinterpret_cast<const uint64_t *>(&c->d_small->rng_in);
+    b.rng_out      = reinterpret_cast<uint64_t *>(&c->d_small->rng_out);
+    b.tokens       = &c->d_small->token;
+    b.row_status   = &c->d_small->status;
+    if (geist_b200_sample_batch(c, &b, nullptr) != GEIST_OK) {
+        return -1;
+    }
+    e = cudaMemcpyAsync(h, c->d_small, sizeof *h, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) {
+        e = cudaStreamSynchronize(c->stream);
+    }
+    if (e != cudaSuccess) {
+        fail(GEIST_E_BACKEND, "sampler: %s", cudaGetErrorString(e));
+        return -1;
+    }
+    if (h->status & (GEIST_B200_ROW_LOAD_TIMEOUT | GEIST_B200_ROW_HIST_OVERFLOW | GEIST_B200_ROW_INTERNAL)) {
+        fail(GEIST_E_BACKEND, "sampler: kernel reported row status 0x%x", h->status);
+        return -1;
+    }
+    if (rng != nullptr) {
+        rng->state = h->rng_out;
+    }
+    return h->token;
+}
+
+} /* namespace */
+
+extern "C" geist_token_t geist_sampler_argmax(size_t n_vocab, const float *logits) { return sample_host_row(n_vocab, logits, nullptr, 0.0f, 0, 1.0f, nullptr); }
+
+extern "C" geist_token_t geist_sampler_temperature(size_t n_vocab, const float *logits, float temperature, struct geist_rng *rng) {
+    return sample_host_row(n_vocab, logits, nullptr, temperature, 0, 1.0f, rng); /* T <= 0 -> argmax inside */
+}
+
+extern "C" enum geist_status geist_sampler_workspace_init(struct geist_sampler_workspace *ws, size_t n_vocab) {
+    if (ws == nullptr || n_vocab == 0) {
+        return fail(GEIST_E_INVALID_ARG, "workspace_init: NULL workspace or n_vocab == 0");
+    }
+    ws->probs   = nullptr;
+    ws->n_vocab = 0;
+    if (default_ctx() == nullptr) {
+        return GEIST_E_BACKEND;
+    }
+    cudaError_t e = cudaHostAlloc(reinterpret_cast<void **>(&ws->probs), n_vocab * sizeof(float), cudaHostAllocDefault);
+    if (e != cudaSuccess) {
+        ws->probs = nullptr;
+        return fail(GEIST_E_OOM, "workspace_init: pinned staging: %s", cudaGetErrorString(e));
+    }
+    ws->n_vocab = n_vocab;
+    return GEIST_OK;
+}
+
+extern "C" void geist_sampler_workspace_destroy(struct geist_sampler_workspace *ws) {
+    if (ws == nullptr) {
+        return;
+    }
+    if (ws->probs != nullptr) {
+        cudaFreeHost(ws->probs);
+        ws->probs = nullptr;
+    }
+    ws->n_vocab = 0;
+}
+
+extern "C" geist_token_t geist_sampler_top_k_ws(struct geist_sampler_workspace *ws, const float *logits, int top_k, float temperature, struct geist_rng *rng) {
+    if (ws == nullptr || ws->n_vocab == 0) {
+        fail(GEIST_E_INVALID_ARG, "top_k_ws: workspace not initialised");
+        return -1;
+    }
+    if (top_k <= 1 || !(temperature > 0.0f)) { /* sampler.c:184-186: greedy, no draw */
+        return sample_host_row(ws->n_vocab, logits, ws->probs, 0.0f, 0, 1.0f, nullptr);
+    }
+    return sample_host_row(ws->n_vocab, logits, ws->probs, temperature, top_k, 1.0f, rng);
+}
+
+extern "C" geist_token_t geist_sampler_top_p_ws(struct geist_sampler_workspace *ws, const float *logits, float top_p, float temperature, struct geist_rng *rng) {
+    if (ws == nullptr || ws->n_vocab == 0) {
+        fail(GEIST_E_INVALID_ARG, "top_p_ws: workspace not initialised");
+        return -1;
+    }
+    if (!(top_p > 0.0f) || !(temperature > 0.0f)) { /* sampler.c:238-240: greedy, no draw */
+        return sample_host_row(ws->n_vocab, logits, ws->probs, 0.0f, 0, 1.0f, nullptr);
+    }
+    return sample_host_row(ws->n_vocab, logits, ws->probs, temperature, 0, top_p, rng); /* top_p >= 1 -> temperature inside */
+}
+
+extern "C" int geist_b200_argmax_f32_supported(size_t m, size_t n_vocab) {
+    if (m != 1 || n_vocab == 0 || n_vocab > 0x7fffffffu) {
+        return 0;
+    }
+    Plan pl;
+    return g_plans.get(n_vocab, 0, pl) ? 1 : 0;
+}
+
+extern "C" enum geist_status geist_b200_argmax_f32(struct geist_b200_ctx *ctx, const float *logits_dev, size_t n, int32_t *out_index) {
+    if (ctx == nullptr || logits_dev == nullptr || out_index == nullptr || n == 0) {
+        return fail(GEIST_E_INVALID_ARG, "argmax_f32: bad argument");
+    }
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    geist_b200_ctx::Small *h = ctx->h_small;
+    memset(h, 0, sizeof *h);
+    h->top_p  = 1.0f;
+    h->token  = -1;
+    h->rng_in = 1;
+    CUDA_TRY(cudaMemcpyAsync(ctx->d_small, h, sizeof *h, cudaMemcpyHostToDevice, ctx->stream));
+    geist_b200_batch b{};
+    b.logits       = logits_dev;
+    b.row_stride   = n;
+    b.n_seq        = 1;
+    b.rows_per_seq = 1;
+    b.n_vocab      = n;
+    b.temperature  = &ctx->d_small->T;
+    b.top_k        = &ctx->d_small->top_k;
+    b.top_p        = &ctx->d_small->top_p;
+    b.rng_in       = reinterpret_cast<const uint64_t *>(&ctx->d_small->rng_in);
+    b.rng_out      = reinterpret_cast<uint64_t *>(&ctx->d_small->rng_out);
+    b.tokens       = &ctx->d_small->token;
+    b.row_status   = &ctx->d_small->status;
+    enum geist_status s = geist_b200_sample_batch(ctx, &b, nullptr);
+    if (s != GEIST_OK) {
+        return s;
+    }
+    CUDA_TRY(cudaMemcpyAsync(h, ctx->d_small, sizeof *h, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    if ((h->status & ~(GEIST_B200_ROW_SLOW_PATH | GEIST_B200_ROW_KEPT_PARTIAL)) != 0 || h->token < 0 || (size_t) h->token >= n) {
+        return fail(GEIST_E_BACKEND, "argmax_f32: row status 0x%x, index %d", h->status, h->token);
+    }
+    *out_index = h->token;
+    return GEIST_OK;
+}
+
+/* ------------------------------------------------- sessions and the batcher -- */
+
+struct geist_b200_batcher {
+    geist_b200_ctx *ctx          = nullptr;
+    size_t          V            = 0;
+    size_t          max_sessions = 0;
+    size_t          max_history  = 0;
+    std::mutex      mu; /* open/close/push/get/set are setup-time calls; step/verify take it too */
+
+    /* per-slot device state (what arch_state.h:287-294 keeps per session) */
+    float              *d_T = nullptr, *d_P = nullptr, *d_rep = nullptr, *d_freq = nullptr, *d_pres = nullptr;
+    int                *d_K        = nullptr;
+    unsigned long long *d_rng      = nullptr;
+    unsigned long long *d_rng_tmp  = nullptr;
+    int                *d_hist     = nullptr; /* [max_sessions, max_history] ring */
+    int                *d_hist_len = nullptr;
+    long long          *d_hist_tot = nullptr;
+
+    /* per-call device scratch, sized for max_sessions * GEIST_B200_SPEC_KMAX rows */
+    int   *d_slot = nullptr, *d_tokens = nullptr, *d_status = nullptr, *d_fed = nullptr;
+    int   *d_accepted = nullptr, *d_nemit = nullptr, *d_emitted = nullptr, *d_ones = nullptr;
+    float *d_logits     = nullptr; /* staging for host logits, grown on demand */
+    size_t d_logits_cap = 0;
+    int   *h_pin        = nullptr; /* pinned: slots | fed | tokens | status | accepted | nemit | emitted */
+    size_t h_pin_ints   = 0;
+
+    cudaStream_t copy_stream[2] = {nullptr, nullptr};
+    cudaEvent_t  ev[2]          = {nullptr, nullptr};
+
+    std::vector<char> used;
+    std::vector<char> pen_active;
+    size_t            n_pen_active = 0;
+};
+
+extern "C" void geist_b200_batcher_destroy(struct geist_b200_batcher *b) {
+    if (b == nullptr) {
+        return;
+    }
+    cudaSetDevice(b->ctx->device);
+    cudaDeviceSynchronize();
+    void *dev[] = {b->d_T, b->d_P, b->d_rep, b->d_freq, b->d_pres, b->d_K, b->d_rng, b->d_rng_tmp, b->d_hist, b->d_hist_len, b->d_hist_tot, b->d_slot, b->d_tokens,
+                   b->d_status, b->d_fed, b->d_accepted, b->d_nemit, b->d_emitted, b->d_ones, b->d_logits};
+    for (void *p : dev) {
+        cudaFree(p);
+    }
+    cudaFreeHost(b->h_pin);
+    for (int i = 0; i < 2; i++) {
+        if (b->copy_stream[i]) {
+            cudaStreamDestroy(b->copy_stream[i]);
+        }
+        if (b->ev[i]) {
+            cudaEventDestroy(b->ev[i]);
+        }
+    }
+    delete b;
+}
+
+extern "C" enum geist_status geist_b200_batcher_create(struct geist_b200_ctx *ctx, size_t n_vocab, size_t max_sessions, size_t max_history, struct geist_b200_batcher **out) {
+    if (out == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "batcher_create: out is NULL");
+    }
+    *out = nullptr;
+    if (ctx == nullptr || n_vocab == 0 || n_vocab > 0x7fffffffu || max_sessions == 0 || max_sessions > (1u << 20)) {
+        return fail(GEIST_E_INVALID_ARG, "batcher_create: bad argument");
+    }
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    Plan pl;
+    if (!g_plans.get(n_vocab, max_history ? max_history + GEIST_B200_SPEC_KMAX : 0, pl)) {
+        return fail(GEIST_E_UNSUPPORTED, "batcher_create: no launch shape for n_vocab=%zu with max_history=%zu", n_vocab, max_history);
+    }
+    geist_b200_batcher *b = new (std::nothrow) geist_b200_batcher();
+    if (b == nullptr) {
+        return fail(GEIST_E_OOM, "batcher_create: host allocation");
+    }
+    b->ctx          = ctx;
+    b->V            = n_vocab;
+    b->max_sessions = max_sessions;
+    b->max_history  = max_history;
+    b->used.assign(max_sessions, 0);
+    b->pen_active.assign(max_sessions, 0);
+    const size_t S = max_sessions, R = S * GEIST_B200_SPEC_KMAX;
+    cudaError_t  e = cudaSuccess;
+    auto         A = [&](void **p, size_t bytes) {
+        if (e == cudaSuccess) {
+            e = cudaMalloc(p, std::max<size_t>(bytes, 16));
+            if (e == cudaSuccess) {
+                e = cudaMemset(*p, 0, std::max<size_t>(bytes, 16));
+            }
+        }
+    };
+    A((void **) &b->d_T, S * 4);
+    A((void **) &b->d_P, S * 4);
+    A((void **) &b->d_rep, S * 4);
+    A((void **) &b->d_freq, S * 4);
+    A((void **) &b->d_pres, S * 4);
+    A((void **) &b->d_K, S * 4);
+    A((void **) &b->d_rng, S * 8);
+    A((void **) &b->d_rng_tmp, S * 8);
+    A((void **) &b->d_hist, S * std::max<size_t>(max_history, 1) * 4);
+    A((void **) &b->d_hist_len, S * 4);
+    A((void **) &b->d_hist_tot, S * 8);
+    A((void **) &b->d_slot, S * 4);
+    A((void **) &b->d_tokens, R * 4);
+    A((void **) &b->d_status, R * 4);
+    A((void **) &b->d_fed, R * 4);
+    A((void **) &b->d_accepted, S * 4);
+    A((void **) &b->d_nemit, S * 4);
+    A((void **) &b->d_emitted, S * (GEIST_B200_SPEC_KMAX + 1) * 4);
+    A((void **) &b->d_ones, S * 4);
+    b->h_pin_ints = S * (1 + 2 + 2 * GEIST_B200_SPEC_KMAX + GEIST_B200_SPEC_KMAX + GEIST_B200_SPEC_KMAX + 1) + 64;
+    if (e == cudaSuccess) {
+        e = cudaHostAlloc((void **) &b->h_pin, b->h_pin_ints * 4, cudaHostAllocDefault);
+    }
+    for (int i = 0; i < 2 && e == cudaSuccess; i++) {
+        e = cudaStreamCreateWithFlags(&b->copy_stream[i], cudaStreamNonBlocking);
+        if (e == cudaSuccess) {
+            e = cudaEventCreateWithFlags(&b->ev[i], cudaEventDisableTiming);
+        }
+    }
+    if (e == cudaSuccess) {
+        std::vector<int> ones(S, 1);
+        e = cudaMemcpy(b->d_ones, ones.data(), S * 4, cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) {
+        geist_b200_batcher_destroy(b);
+        return fail(e == cudaErrorMemoryAllocation ? GEIST_E_OOM : GEIST_E_BACKEND, "batcher_create: %s", cudaGetErrorString(e));
+    }
+    *out = b;
+    return GEIST_OK;
+}
+
+static bool slot_ok(const geist_b200_batcher *b, int32_t s) { return b != nullptr && s >= 0 && (size_t) s < b->max_sessions && b->used[(size_t) s]; }
+
+extern "C" enum geist_status geist_b200_session_open(struct geist_b200_batcher *b, const struct geist_session_opts *opts, const struct geist_b200_penalty_opts *pen,
+                                                     int32_t *out_session) {
+    if (b == nullptr || out_session == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "session_open: NULL batcher or out_session");
+    }
+    *out_session = -1;
+    std::lock_guard<std::mutex> lk(b->mu);
+    size_t                      s = 0;
+    while (s < b->max_sessions && b->used[s]) {
+        s++;
+    }
+    if (s == b->max_sessions) {
+        return fail(GEIST_E_OOM, "session_open: all %zu session slots are in use", b->max_sessions);
+    }
+    /* arch_state.c:1168-1173 defaults, then step.c:385-411 */
+    float    T = 0.0f, P = 1.0f;
+    int      K    = 0;
+    uint64_t seed = 0xCAFEBABE1234ULL;
+    if (opts != nullptr) {
+        T = opts->temperature;
+        P = opts->top_p > 0.0f ? opts->top_p : 1.0f;
+        K = opts->top_k;
+        if (opts->random_seed != 0) {
+            seed = opts->random_seed;
+        }
+        if (T != T || P != P) {
+            return fail(GEIST_E_INVALID_ARG, "session_open: NaN sampler option");
+        }
+    }
+    float rep = 1.0f, freq = 0.0f, pres = 0.0f;
+    if (pen != nullptr) {
+        rep  = pen->repetition_penalty > 0.0f ? pen->repetition_penalty : 1.0f;
+        freq = pen->frequency_penalty;
+        pres = pen->presence_penalty;
+        if (rep != rep || freq != freq || pres != pres) {
+            return fail(GEIST_E_INVALID_ARG, "session_open: NaN penalty option");
+        }
+    }
+    const bool active = rep != 1.0f || freq != 0.0f || pres != 0.0f;
+    if (active && b->max_history == 0) {
+        return fail(GEIST_E_INVALID_ARG, "session_open: penalties need a batcher created with max_history > 0");
+    }
+    CUDA_TRY(cudaSetDevice(b->ctx->device));
+    struct geist_rng r;
+    geist_rng_seed(&r, seed);
+    const long long zero64 = 0;
+    const int       zero   = 0;
+    CUDA_TRY(cudaMemcpy(b->d_T + s, &T, 4, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_P + s, &P, 4, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_K + s, &K, 4, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_rep + s, &rep, 4, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_freq + s, &freq, 4, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_pres + s, &pres, 4, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_rng + s, &r.state, 8, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_hist_len + s, &zero, 4, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_hist_tot + s, &zero64, 8, cudaMemcpyHostToDevice));
+    b->used[s]       = 1;
+    b->pen_active[s] = active ? 1 : 0;
+    b->n_pen_active += active ? 1 : 0;
+    *out_session = (int32_t) s;
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_session_close(struct geist_b200_batcher *b, int32_t session) {
+    if (b == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "session_close: NULL batcher");
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    if (!slot_ok(b, session)) {
+        return fail(GEIST_E_INVALID_ARG, "session_close: session %d is not open", session);
+    }
+    b->n_pen_active -= b->pen_active[(size_t) session] ? 1 : 0;
+    b->pen_active[(size_t) session] = 0;
+    b->used[(size_t) session]       = 0;
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_session_reset(struct geist_b200_batcher *b, int32_t session) {
+    if (b == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "session_reset: NULL batcher");
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    if (!slot_ok(b, session)) {
+        return fail(GEIST_E_INVALID_ARG, "session_reset: session %d is not open", session);
+    }
+    CUDA_TRY(cudaSetDevice(b->ctx->device));
+    const long long zero64 = 0;
+    const int       zero   = 0;
+    CUDA_TRY(cudaMemcpy(b->d_hist_len + session, &zero, 4, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_hist_tot + session, &zero64, 8, cudaMemcpyHostToDevice));
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_session_get_rng(struct geist_b200_batcher *b, int32_t session, uint64_t *state) {
+    if (b == nullptr || state == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "session_get_rng: NULL argument");
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    if (!slot_ok(b, session)) {
+        return fail(GEIST_E_INVALID_ARG, "session_get_rng: session %d is not open", session);
+    }
+    CUDA_TRY(cudaSetDevice(b->ctx->device));
+    CUDA_TRY(cudaMemcpy(state, b->d_rng + session, 8, cudaMemcpyDeviceToHost));
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_session_set_rng(struct geist_b200_batcher *b, int32_t session, uint64_t state) {
+    if (b == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "session_set_rng: NULL batcher");
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    if (!slot_ok(b, session)) {
+        return fail(GEIST_E_INVALID_ARG, "session_set_rng: session %d is not open", session);
+    }
+    if (state == 0) {
+        return fail(GEIST_E_INVALID_ARG, "session_set_rng: 0 is not a valid xorshift state");
+    }
+    CUDA_TRY(cudaSetDevice(b->ctx->device));
+    CUDA_TRY(cudaMemcpy(b->d_rng + session, &state, 8, cudaMemcpyHostToDevice));
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_session_push_history(struct geist_b200_batcher *b, int32_t session, size_t n, const geist_token_t *ids) {
+    if (b == nullptr || (n > 0 && ids == nullptr)) {
+        return fail(GEIST_E_INVALID_ARG, "session_push_history: NULL argument");
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    if (!slot_ok(b, session)) {
+        return fail(GEIST_E_INVALID_ARG, "session_push_history: session %d is not open", session);
+    }
+    if (b->max_history == 0 || n == 0) {
+        return GEIST_OK; /* nothing is kept */
+    }
+    CUDA_TRY(cudaSetDevice(b->ctx->device));
+    long long tot = 0;
+    CUDA_TRY(cudaMemcpy(&tot, b->d_hist_tot + session, 8, cudaMemcpyDeviceToHost));
+    /* ring: only the last max_history ids can matter */
+    const size_t H     = b->max_history;
+    const size_t first = n > H ? n - H : 0;
+    int         *row   = b->d_hist + (size_t) session * H;
+    for (size_t i = first; i < n;) {
+        const size_t pos = (size_t) ((tot + (long long) i) % (long long) H);
+        const size_t run = std::min(n - i, H - pos);
+        CUDA_TRY(cudaMemcpy(row + pos, ids + i, run * 4, cudaMemcpyHostToDevice));
+        i += run;
+    }
+    tot += (long long) n;
+    const int len = (int) std::min<long long>(tot, (long long) H);
+    CUDA_TRY(cudaMemcpy(b->d_hist_tot + session, &tot, 8, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_hist_len + session, &len, 4, cudaMemcpyHostToDevice));
+    return GEIST_OK;
+}
+
+namespace {
+
+/* Shared by step and verify: k rows per session, optional accept. */
+enum geist_status batcher_run(geist_b200_batcher *b, size_t n, const int32_t *sessions, size_t k, const geist_token_t *fed, const float *logits, size_t row_stride,
+                              int logits_on_host, int append_history, bool verify, int32_t *accepted, int32_t *n_out, geist_token_t *out_tokens) {
+    if (b == nullptr || sessions == nullptr || logits == nullptr || out_tokens == nullptr || n == 0) {
+        return fail(GEIST_E_INVALID_ARG, "batcher: missing argument");
+    }
+    if (n > b->max_sessions) {
+        return fail(GEIST_E_INVALID_ARG, "batcher: %zu sessions in one call, batcher holds %zu", n, b->max_sessions);
+    }
+    if (k == 0 || k > GEIST_B200_SPEC_KMAX) {
+        return fail(GEIST_E_INVALID_ARG, "batcher: k must be in [1, %d]", GEIST_B200_SPEC_KMAX);
+    }
+    if (verify && (fed == nullptr || accepted == nullptr || n_out == nullptr)) {
+        return fail(GEIST_E_INVALID_ARG, "batcher_verify: fed, accepted and n_out are required");
+    }
+    if (row_stride < b->V) {
+        return fail(GEIST_E_INVALID_ARG, "batcher: row_stride %zu < n_vocab %zu", row_stride, b->V);
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    std::vector<char>           seen(b->max_sessions, 0);
+    for (size_t i = 0; i < n; i++) {
+        if (!slot_ok(b, sessions[i])) {
+            return fail(GEIST_E_INVALID_ARG, "batcher: session %d is not open", sessions[i]);
+        }
+        if (seen[(size_t) sessions[i]]) {
+            return fail(GEIST_E_INVALID_ARG, "batcher: session %d appears twice in one call", sessions[i]);
+        }
+        seen[(size_t) sessions[i]] = 1;
+    }
+    CUDA_TRY(cudaSetDevice(b->ctx->device));
+    cudaStream_t st   = b->ctx->stream;
+    const size_t rows = n * k;
+    /* pinned layout */
+    int *h_slot = b->h_pin;
+    int *h_fed  = h_slot + b->max_sessions;
+    int *h_tok  = h_fed + b->max_sessions * GEIST_B200_SPEC_KMAX;
+    int *h_stat = h_tok + b->max_sessions * GEIST_B200_SPEC_KMAX;
+    int *h_acc  = h_stat + b->max_sessions * GEIST_B200_SPEC_KMAX;
+    int *h_nem  = h_acc + b->max_sessions;
+    int *h_emit = h_nem + b->max_sessions; /* [n, k+1] */
+    memcpy(h_slot, sessions, n * 4);
+    CUDA_TRY(cudaMemcpyAsync(b->d_slot, h_slot, n * 4, cudaMemcpyHostToDevice, st));
+    if (verify) {
+        memcpy(h_fed, fed, rows * 4);
+        CUDA_TRY(cudaMemcpyAsync(b->d_fed, h_fed, rows * 4, cudaMemcpyHostToDevice, st));
+    }
+    const bool pen = b->n_pen_active > 0 && b->max_history > 0;
+
+    geist_b200_batch d{};
+    d.n_vocab            = b->V;
+    d.rows_per_seq       = k;
+    d.temperature        = b->d_T;
+    d.top_k              = b->d_K;
+    d.top_p              = b->d_P;
+    d.repetition_penalty = pen ? b->d_rep : nullptr;
+    d.frequency_penalty  = pen ? b->d_freq : nullptr;
+    d.presence_penalty   = pen ? b->d_pres : nullptr;
+    d.history            = pen ? b->d_hist : nullptr;
+    d.history_stride     = b->max_history;
+    d.history_len        = pen ? b->d_hist_len : nullptr;
+    d.fed_stride         = k;
+    d.rng_in             = reinterpret_cast<const uint64_t *>(b->d_rng);
+    d.rng_out            = reinterpret_cast<uint64_t *>(b->d_rng_tmp);
+
+    if (!logits_on_host) {
+        d.logits     = logits;
+        d.row_stride = row_stride;
+        d.n_seq      = n;
+        d.slot       = b->d_slot;
+        d.fed_tokens = (pen && verify) ? b->d_fed : nullptr;
+        d.tokens     = b->d_tokens;
+        d.row_status = b->d_status;
+        enum geist_status s = geist_b200_sample_batch(b->ctx, &d, st);
+        if (s != GEIST_OK) {
+            return s;
+        }
+    } else {
+        /* host logits: copy in chunks of sequences on two streams so that one chunk's kernel
+         * runs under the next chunk's copy */
+        if (b->d_logits_cap < rows * b->V) {
+            cudaFree(b->d_logits);
+            b->d_logits     = nullptr;
+            b->d_logits_cap = 0;
+            CUDA_TRY(cudaMalloc((void **) &b->d_logits, rows * b->V * sizeof(float)));
+            b->d_logits_cap = rows * b->V;
+        }
+        CUDA_TRY(cudaEventRecord(b->ev[0], st)); /* slots / fed are on the way */
+        const size_t seq_chunk = std::max<size_t>(1, (32 + k - 1) / k);
+        int          which     = 0;
+        for (size_t s0 = 0; s0 < n; s0 += seq_chunk, which ^= 1) {
+            const size_t ns = std::min(seq_chunk, n - s0);
+            cudaStream_t cs = b->copy_stream[which];
+            if (s0 < 2 * seq_chunk) {
+                CUDA_TRY(cudaStreamWaitEvent(cs, b->ev[0], 0));
+            }
+            CUDA_TRY(cudaMemcpy2DAsync(b->d_logits + s0 * k * b->V, b->V * 4, logits + s0 * k * row_stride, row_stride * 4, b->V * 4, ns * k, cudaMemcpyHostToDevice, cs));
+            d.logits     = b->d_logits + s0 * k * b->V;
+            d.row_stride = b->V;
+            d.n_seq      = ns;
+            d.slot       = b->d_slot + s0;
+            d.fed_tokens = (pen && verify) ? b->d_fed + s0 * k : nullptr;
+            d.tokens     = b->d_tokens + s0 * k;
+            d.row_status = b->d_status + s0 * k;
+            enum geist_status s = geist_b200_sample_batch(b->ctx, &d, cs);
+            if (s != GEIST_OK) {
+                return s;
+            }
+        }
+        for (int i = 0; i < 2; i++) {
+            CUDA_TRY(cudaEventRecord(b->ev[1], b->copy_stream[i]));
+            CUDA_TRY(cudaStreamWaitEvent(st, b->ev[1], 0));
+        }
+    }
+    const int *append_tok = b->d_tokens;
+    const int *append_cnt = b->d_ones;
+    int        per_seq    = 1;
+    int        first      = 0;
+    if (verify) {
+        gb::AcceptParams ap{b->d_fed, b->d_tokens, (int) n, (int) k, b->d_accepted, b->d_nemit, b->d_emitted};
+        CUDA_TRY(gb::launch_accept(ap, st));
+        append_tok = b->d_emitted;
+        append_cnt = b->d_nemit;
+        per_seq    = (int) k + 1;
+        first      = 1; /* emitted[0] is the pending token, which joined the history when it was sampled */
+    }
+    CUDA_TRY(gb::launch_post_step(b->d_slot, (int) n, per_seq, first, (append_history && b->max_history) ? append_tok : nullptr, append_cnt, b->d_hist, (int) b->max_history,
+                                  b->d_hist_len, b->d_hist_tot, b->d_rng_tmp, b->d_rng, st));
+    CUDA_TRY(cudaMemcpyAsync(h_stat, b->d_status, rows * 4, cudaMemcpyDeviceToHost, st));
+    if (verify) {
+        CUDA_TRY(cudaMemcpyAsync(h_acc, b->d_accepted, n * 4, cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaMemcpyAsync(h_nem, b->d_nemit, n * 4, cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaMemcpyAsync(h_emit, b->d_emitted, n * (k + 1) * 4, cudaMemcpyDeviceToHost, st));
+    } else {
+        CUDA_TRY(cudaMemcpyAsync(h_tok, b->d_tokens, rows * 4, cudaMemcpyDeviceToHost, st));
+    }
+    CUDA_TRY(cudaStreamSynchronize(st));
+    for (size_t i = 0; i < rows; i++) {
+        if (h_stat[i] & (GEIST_B200_ROW_LOAD_TIMEOUT | GEIST_B200_ROW_HIST_OVERFLOW | GEIST_B200_ROW_INTERNAL)) {
+            return fail(GEIST_E_BACKEND, "batcher: row %zu reported status 0x%x", i, h_stat[i]);
+        }
+    }
+    if (verify) {
+        memcpy(accepted, h_acc, n * 4);
+        memcpy(n_out, h_nem, n * 4);
+        memcpy(out_tokens, h_emit, n * (k + 1) * 4);
+    } else {
+        memcpy(out_tokens, h_tok, rows * 4);
+    }
+    return GEIST_OK;
+}
+
+} /* namespace */
+
+extern "C" enum geist_status geist_b200_batcher_step(struct geist_b200_batcher *b, size_t n, const int32_t *sessions, const float *logits, size_t row_stride, int logits_on_host,
+                                                     int append_history, geist_token_t *out_tokens) {
+    return batcher_run(b, n, sessions, 1, nullptr, logits, row_stride, logits_on_host, append_history, false, nullptr, nullptr, out_tokens);
+}
+
+extern "C" enum geist_status geist_b200_batcher_verify(struct geist_b200_batcher *b, size_t n, const int32_t *sessions, size_t k, const geist_token_t *fed, const float *logits,
+                                                       size_t row_stride, int logits_on_host, int append_history, int32_t *accepted, int32_t *n_out, geist_token_t *out_tokens) {
+    return batcher_run(b, n, sessions, k, fed, logits, row_stride, logits_on_host, append_history, true, accepted, n_out, out_tokens);
+}

@@ -1,0 +1,308 @@
+/*
+ * geist_b200.h — C ABI of the B200 (sm_100a) token-sampling path for geistlib.
+ *
+ * libgeist_b200.so replaces ONE path of the geistlib engine: logits -> token
+ * (sampler, speculative verify/accept, multi-session batching). Three layers,
+ * innermost first; each entry cites the geistlib interface it stands in for
+ * (paths inside the geistlib tree):
+ *
+ *   1. sampler.h surface, host pointers ........ src/engine/sampler.h:27-69
+ *   2. batched device entries + plugin slot ..... include/geist_backend.h:414-421,
+ *                                                 src/archs/transformer/forward/head.c:131-186, :267-306
+ *   3. per-session state, verify/accept, batcher  include/geist.h:209-247,
+ *                                                 src/archs/transformer/arch_state.h:287-294,
+ *                                                 src/archs/transformer/forward/step.c:385-411,
+ *                                                 src/engine/session.c:593-636
+ *
+ * Conventions kept from geistlib: every fallible call returns enum geist_status
+ * (0 = OK); no exceptions or errno cross this boundary; detail text through
+ * geist_b200_errmsg(); per-session calls may run concurrently on different
+ * sessions, never on the same one (include/geist_arch.h:43-51).
+ *
+ * There is no CPU fallback anywhere in this library: a call that cannot reach
+ * the GPU fails with GEIST_E_BACKEND.
+ *
+ * EXTENSIONS (no geistlib counterpart, zero-initialised = off):
+ *   Penalties. For every distinct id t of a row's history (multiplicity c),
+ *   before temperature and before any filter:
+ *       x = logits[t];  x = x > 0 ? x / r : x * r;   (r = repetition_penalty, r <= 0 reads as 1)
+ *       x = x - (float)c * frequency_penalty;  x = x - presence_penalty;
+ *   each step one binary32 operation (no fused multiply-add). Ids outside the
+ *   vocabulary are ignored. In a verify pass the pending token fed[0] is taken
+ *   to be part of the history already (it joined when it was sampled); row i
+ *   additionally counts the proposals fed[1..i].
+ *   Vocabulary shards. A shard emits its best k (value, global id); the union
+ *   over shards, ordered by (value desc, id asc) and cut to k, is the row's
+ *   top-k, which then goes through the ordinary top-k draw.
+ */
+#ifndef GEIST_B200_H
+#define GEIST_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------- status -- */
+/* Same enumerators, same values as include/geist.h:46-67. */
+#ifndef GEIST_H
+enum geist_status {
+    GEIST_OK = 0,
+    GEIST_E_OOM,
+    GEIST_E_INVALID_ARG,
+    GEIST_E_INTERNAL,
+    GEIST_E_FILE_NOT_FOUND,
+    GEIST_E_IO,
+    GEIST_E_FORMAT,
+    GEIST_E_UNSUPPORTED,
+    GEIST_E_NOT_FOUND,
+    GEIST_E_BACKEND,
+    GEIST_E_INVALID_STATE,
+    GEIST_E_TOO_MANY_TOKENS,
+};
+typedef int32_t geist_token_t; /* include/geist.h:190 */
+#endif
+
+/* Text of the last failure on the calling thread ("" when none). Replaces the
+ * per-backend error slot of include/geist_backend.h:599-626 for this path. */
+const char *geist_b200_errmsg(void);
+
+/* ------------------------------------------------- 1. sampler.h surface -- */
+/* Same names, argument meaning and early-outs as src/engine/sampler.h:27-69.
+ * `logits` are HOST pointers: the row is staged to the device, one kernel
+ * runs, four bytes come back. On a device failure the token is -1 and
+ * geist_b200_errmsg() says why (the reference's "degrade to argmax on OOM"
+ * has no equivalent here: nothing is computed on the CPU). */
+
+struct geist_rng {
+    uint64_t state; /* src/engine/sampler.h:28-30 */
+};
+
+void     geist_rng_seed(struct geist_rng *rng, uint64_t seed);      /* sampler.c:27-33 */
+uint64_t geist_rng_next_u64(struct geist_rng *rng);                 /* sampler.c:35-42 */
+float    geist_rng_next_unit(struct geist_rng *rng);                /* sampler.c:44-48 */
+
+geist_token_t geist_sampler_argmax(size_t n_vocab, const float *logits); /* sampler.c:52-62 */
+geist_token_t geist_sampler_temperature(size_t n_vocab, const float *logits, float temperature,
+                                        struct geist_rng *rng);     /* sampler.c:106-132 */
+
+struct geist_sampler_workspace {
+    float *probs;   /* here: pinned host staging for one row (sampler.h:50-53 keeps V floats of scratch) */
+    size_t n_vocab;
+};
+
+enum geist_status geist_sampler_workspace_init(struct geist_sampler_workspace *ws, size_t n_vocab); /* sampler.c:136-149 */
+void              geist_sampler_workspace_destroy(struct geist_sampler_workspace *ws);              /* sampler.c:151-157 */
+
+geist_token_t geist_sampler_top_k_ws(struct geist_sampler_workspace *ws, const float *logits, int top_k,
+                                     float temperature, struct geist_rng *rng); /* sampler.c:178-228 */
+geist_token_t geist_sampler_top_p_ws(struct geist_sampler_workspace *ws, const float *logits, float top_p,
+                                     float temperature, struct geist_rng *rng); /* sampler.c:232-305 */
+
+/* ------------------------------------------ 2. batched device entries -- */
+
+struct geist_b200_ctx; /* one per (device, caller): scratch + default stream */
+
+enum geist_status geist_b200_ctx_create(int device, struct geist_b200_ctx **out);
+void              geist_b200_ctx_destroy(struct geist_b200_ctx *ctx);
+
+/* Row status bits written by the kernels (int32 per row). */
+#define GEIST_B200_ROW_LOAD_TIMEOUT  (1 << 0) /* result invalid */
+#define GEIST_B200_ROW_SLOW_PATH     (1 << 1) /* informational */
+#define GEIST_B200_ROW_HIST_OVERFLOW (1 << 2) /* result invalid */
+#define GEIST_B200_ROW_KEPT_PARTIAL  (1 << 3) /* kept_idx / kept_val not filled, kept_n is */
+#define GEIST_B200_ROW_INTERNAL      (1 << 4) /* result invalid */
+
+/*
+ * One launch over n_seq * rows_per_seq logits rows. All pointers are DEVICE
+ * pointers. A "sequence" is what geistlib calls a session's sampler state
+ * (arch_state.h:287-294): one parameter set, one generator, one history. Its
+ * rows_per_seq rows are sampled "in order with the same generator" exactly as
+ * finalize_logits_batch does (head.c:282-303): row r starts from the state
+ * left by r draws. rows_per_seq == 1 is plain batched decode (head.c:165-186).
+ *
+ * Mode per sequence, head.c:172-183 folded with the early-outs of the three
+ * sampler functions: temperature <= 0 -> argmax, 0 draws; top_k > 1 -> top-k
+ * (top_k >= n_vocab -> temperature; top_k clamps to 8192); 0 < top_p < 1 ->
+ * top-p; else plain temperature. top_p is used as given: callers wanting the
+ * session rule "top_p <= 0 means 1.0" (step.c:391) apply it first, as the
+ * session layer below does.
+ */
+struct geist_b200_batch {
+    const float *logits;    /* [n_seq * rows_per_seq, n_vocab] fp32 */
+    size_t       row_stride; /* floats between rows (>= n_vocab) */
+    size_t       n_seq;
+    size_t       rows_per_seq;
+    size_t       n_vocab;
+
+    const int32_t *slot; /* optional [n_seq]: index of sequence s in every per-sequence array; NULL = s */
+
+    const float   *temperature; /* per sequence */
+    const int32_t *top_k;       /* per sequence */
+    const float   *top_p;       /* per sequence */
+
+    const float   *repetition_penalty; /* per sequence or NULL   (EXTENSION) */
+    const float   *frequency_penalty;  /* per sequence or NULL   (EXTENSION) */
+    const float   *presence_penalty;   /* per sequence or NULL   (EXTENSION) */
+    const int32_t *history;            /* [*, history_stride] or NULL */
+    size_t         history_stride;     /* also the longest history a row can have */
+    const int32_t *history_len;        /* per sequence */
+    const int32_t *fed_tokens;         /* optional [n_seq, fed_stride]: row r also counts fed[1..r] */
+    size_t         fed_stride;
+
+    const uint64_t *rng_in;  /* per sequence: xorshift64* state (sampler.h:28-30) */
+    uint64_t       *rng_out; /* per sequence: state after the sequence's draws; may equal rng_in only if rows_per_seq == 1 */
+
+    int32_t *tokens;     /* [n_seq * rows_per_seq] */
+    int32_t *row_status; /* [n_seq * rows_per_seq] */
+
+    float *out_logits; /* optional [rows, n_vocab]: rows after penalties */
+
+    int32_t  kept_cap; /* 0 = off; else entries per row below */
+    int32_t *kept_n;   /* [rows] size of the kept set (k, nucleus size, 0 for argmax/temperature) */
+    int32_t *kept_idx; /* [rows, kept_cap] ids in walk order */
+    float   *kept_prob; /* [rows, kept_cap] probability renormalised inside the kept set */
+
+    int32_t vocab_offset; /* id of column 0; added to every id written, subtracted from history ids */
+};
+
+/* Replaces the sampler dispatch of finalize_logits_one_row / _batch
+ * (head.c:165-186, :289-303) for any number of sessions at once. `stream` is a
+ * cudaStream_t passed as void* (NULL = the context's own stream). Asynchronous. */
+enum geist_status geist_b200_sample_batch(struct geist_b200_ctx *ctx, const struct geist_b200_batch *b, void *stream);
+
+/* Backend operator slot argmax_f32 (include/geist_backend.h:414-421): greedy
+ * argmax of one [1, n] F32 row that lives on this device; ties -> lowest index.
+ * Synchronous: returns after the 4-byte index is on the host. The glue that
+ * unpacks struct geist_tensor is shown in INTEGRATION.md. */
+enum geist_status geist_b200_argmax_f32(struct geist_b200_ctx *ctx, const float *logits_dev, size_t n, int32_t *out_index);
+/* The matching probe (geist_backend.h:276-326): true for q->op == ARGMAX_F32, m == 1, 1 <= d_model <= supported max. */
+int geist_b200_argmax_f32_supported(size_t m, size_t n_vocab);
+
+/* Speculative accept rule, session.c:599-625, batched: for each sequence,
+ * accepted = longest run of i < k-1 with verify_out[i] == fed[i+1]; emitted =
+ * fed[0..accepted] + verify_out[accepted] (accepted + 2 tokens, the last one is
+ * the bonus token when everything matched). Device pointers; emitted is
+ * [n_seq, k+1], unused tail = -1. */
+enum geist_status geist_b200_accept_batch(struct geist_b200_ctx *ctx, size_t n_seq, size_t k, const int32_t *fed,
+                                          const int32_t *verify_out, int32_t *accepted, int32_t *n_emitted,
+                                          int32_t *emitted, void *stream);
+
+/* Dense inspection outputs (device pointers). */
+/* probs[r, :] = softmax(logits[r, :] / T_r) as the top-p path forms it (sampler.c:68-85, :253-255). */
+enum geist_status geist_b200_softmax(struct geist_b200_ctx *ctx, const float *logits, size_t row_stride, size_t n_rows,
+                                     size_t n_vocab, const float *temperature, float *probs, double *sums, void *stream);
+/* dense[r, :] = 0 except the kept entries: the "post-filter probability vector". */
+enum geist_status geist_b200_scatter_kept(struct geist_b200_ctx *ctx, size_t n_rows, size_t n_vocab, int32_t kept_cap,
+                                          const int32_t *kept_n, const int32_t *kept_idx, const float *kept_prob,
+                                          int32_t vocab_offset, float *dense, void *stream);
+
+/* Vocabulary shards (EXTENSION). Phase 1 on every rank: the shard's best
+ * min(top_k, n_vocab) candidates per row as (raw value, global id) into
+ * kept_prob / kept_idx (any order), kept_n = their number; penalties apply to
+ * the ids of this shard. The caller all-gathers the three arrays (NCCL) into
+ * [n_shards, n_rows, kept_cap] buffers. Phase 2: merge + top-k draw. */
+enum geist_status geist_b200_shard_select(struct geist_b200_ctx *ctx, const struct geist_b200_batch *b, void *stream);
+
+struct geist_b200_merge {
+    const float   *cand_val; /* [n_shards, n_rows, cand_stride] */
+    const int32_t *cand_gid; /* [n_shards, n_rows, cand_stride] */
+    const int32_t *cand_n;   /* [n_shards, n_rows] */
+    size_t         n_shards, n_rows, cand_stride;
+    const float   *temperature; /* [n_rows] */
+    const int32_t *top_k;       /* [n_rows] */
+    const uint64_t *rng_in;     /* [n_rows] */
+    uint64_t       *rng_out;    /* [n_rows] */
+    int32_t        *tokens;     /* [n_rows] */
+    int32_t        *row_status; /* [n_rows] */
+    int32_t         kept_cap;
+    int32_t        *kept_n, *kept_idx;
+    float          *kept_prob;
+};
+enum geist_status geist_b200_shard_merge_sample(struct geist_b200_ctx *ctx, const struct geist_b200_merge *m, void *stream);
+
+/* ----------------------------- 3. sessions, verify/accept, the batcher -- */
+
+#ifndef GEIST_H
+enum geist_kv_mode { GEIST_KV_AUTO = 0, GEIST_KV_FP32, GEIST_KV_INT8, GEIST_KV_KIVI, GEIST_KV_F16, GEIST_KV_INT4 };
+/* Field for field include/geist.h:209-247; only the four sampler fields are read here. */
+struct geist_session_opts {
+    size_t             max_seq_len;
+    float              temperature;
+    float              top_p;
+    int                top_k;
+    uint64_t           random_seed;
+    const char        *awq_scales_path;
+    enum geist_kv_mode kv_mode;
+    size_t             m_max;
+};
+#endif
+
+/* EXTENSION, separate from geist_session_opts so that struct keeps its layout; all zero = off. */
+struct geist_b200_penalty_opts {
+    float repetition_penalty; /* <= 0 reads as 1 */
+    float frequency_penalty;
+    float presence_penalty;
+};
+
+#define GEIST_B200_SPEC_KMAX 16 /* GEIST_SPEC_KMAX_HARDCAP, session.c:515 */
+
+struct geist_b200_batcher; /* N sessions -> one launch */
+
+/* max_history: ids kept per session for the penalties (0 = none kept). */
+enum geist_status geist_b200_batcher_create(struct geist_b200_ctx *ctx, size_t n_vocab, size_t max_sessions,
+                                            size_t max_history, struct geist_b200_batcher **out);
+void              geist_b200_batcher_destroy(struct geist_b200_batcher *b);
+
+/* Sampler half of geist_session_create (geist.h:252-255): defaults T=0, top_p=1,
+ * top_k=0, seed 0xCAFEBABE1234 (arch_state.c:1168-1173); then opts applied as
+ * transformer_session_apply_opts does: top_p <= 0 -> 1.0, random_seed 0 keeps
+ * the default stream (step.c:385-411). opts / pen may be NULL. */
+enum geist_status geist_b200_session_open(struct geist_b200_batcher *b, const struct geist_session_opts *opts,
+                                          const struct geist_b200_penalty_opts *pen, int32_t *out_session);
+enum geist_status geist_b200_session_close(struct geist_b200_batcher *b, int32_t session);
+/* geist_session_reset (geist.h:262): forget the history, keep sampler config and generator. */
+enum geist_status geist_b200_session_reset(struct geist_b200_batcher *b, int32_t session);
+/* Tokens committed to the context (prompt, or tokens emitted elsewhere). */
+enum geist_status geist_b200_session_push_history(struct geist_b200_batcher *b, int32_t session, size_t n,
+                                                  const geist_token_t *ids);
+/* The generator word (checkpoint / resume of a sampled stream). */
+enum geist_status geist_b200_session_get_rng(struct geist_b200_batcher *b, int32_t session, uint64_t *state);
+enum geist_status geist_b200_session_set_rng(struct geist_b200_batcher *b, int32_t session, uint64_t state);
+
+/* Sampler half of one decode step for n sessions at once (finalize_logits_one_row,
+ * head.c:165-186, for each). logits [n, n_vocab] is a DEVICE pointer unless
+ * logits_on_host != 0, in which case it is a host buffer that is copied in
+ * inside the call. out_tokens is a HOST array. Each session's generator
+ * advances and, when append_history != 0, its sampled token joins its history.
+ * Synchronous. */
+enum geist_status geist_b200_batcher_step(struct geist_b200_batcher *b, size_t n, const int32_t *sessions,
+                                          const float *logits, size_t row_stride, int logits_on_host,
+                                          int append_history, geist_token_t *out_tokens);
+
+/* Sampler + accept half of geist_session_decode_speculative (session.c:593-636)
+ * for n sessions: logits [n, k, n_vocab] are the verify pass's rows, fed [n, k]
+ * the tokens pushed through it (fed[.][0] = pending token, the rest proposals;
+ * HOST array). All k rows are sampled in order with the session's generator,
+ * then the prefix-accept rule runs. Outputs (HOST): accepted [n], n_out [n],
+ * out_tokens [n, k+1]. 1 <= k <= GEIST_B200_SPEC_KMAX. The emitted tokens join
+ * the history when append_history != 0. The caller then feeds the last emitted
+ * token back (the "correction prefill" of session.c:627-634) and calls
+ * geist_b200_batcher_step for its logits. */
+enum geist_status geist_b200_batcher_verify(struct geist_b200_batcher *b, size_t n, const int32_t *sessions, size_t k,
+                                            const geist_token_t *fed, const float *logits, size_t row_stride,
+                                            int logits_on_host, int append_history, int32_t *accepted,
+                                            int32_t *n_out, geist_token_t *out_tokens);
+
+/* Launch-shape report for one vocabulary size: cluster size, floats per slice,
+ * shared memory per CTA, resident clusters on the current device (0 = the row
+ * does not fit this path). */
+enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history, int32_t *cluster, int32_t *slice,
+                                  int32_t *smem_bytes, int32_t *resident_clusters);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEIST_B200_H */

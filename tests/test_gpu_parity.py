@@ -1,0 +1,251 @@
+"""GPU parity: the CUDA path through the C ABI against the CPU checker on the
+same seeded inputs. Token ids, kept-set ids and generator states must be
+bit-exact; probabilities within 1e-5 relative (fp32)."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import (gumbel_logits, histories, independent_states, normal_logits, per_seq, rel_err, seq_states,
+                     to_dev, u64_from_dev, u64_to_dev)
+
+pytestmark = pytest.mark.gpu
+PROB_RTOL = 1e-5
+INVALID = 1 | 4 | 16
+
+
+def run_gpu(ctx, logits, T, K, P, states, **kw):
+    n_seq = logits.shape[0] // kw.get("rows_per_seq", 1)
+    dT, dK, dP = per_seq(n_seq, T, K, P)
+    dl = to_dev(logits)
+    extra = {}
+    for name in ("rep", "freq", "pres"):
+        if kw.get(name) is not None:
+            extra[name] = to_dev(np.broadcast_to(np.asarray(kw.pop(name), np.float32), (n_seq,)))
+        else:
+            kw.pop(name, None)
+    if kw.get("history") is not None:
+        h = kw.pop("history")
+        hl = kw.pop("history_len", None)
+        extra["history"] = to_dev(h)
+        extra["history_len"] = to_dev(np.full(n_seq, h.shape[1], np.int32) if hl is None else np.asarray(hl, np.int32))
+    if kw.get("fed") is not None:
+        extra["fed"] = to_dev(kw.pop("fed"))
+    out = ctx.sample_batch(dl, dT, dK, dP, u64_to_dev(states), **extra, **kw)
+    res = {k: (v.cpu().numpy() if v is not None else None) for k, v in out.items()}
+    res["rng_state"] = u64_from_dev(out["rng_state"])
+    assert (res["status"] & INVALID == 0).all(), res["status"]
+    return res
+
+
+def check_tokens(g, o):
+    bad = np.nonzero(g["tokens"] != o["tokens"])[0]
+    assert bad.size == 0, f"{bad.size} of {g['tokens'].size} tokens differ, first rows {bad[:8]}: gpu {g['tokens'][bad[:8]]} cpu {o['tokens'][bad[:8]]}"
+    assert (g["rng_state"] == o["rng_state"]).all()
+
+
+@pytest.mark.parametrize("V", [1, 2, 3, 31, 32, 33, 127, 1023, 1024, 1025, 4099, 16384, 16385, 50257])
+def test_greedy_edge_sizes(ctx, V):
+    x = normal_logits(5, V, 3.0, 100 + V)
+    x[1, :] = 0.25          # all equal: lowest index wins
+    x[2, V // 2:] = x[2].max() + 1.0   # tie of the maximum
+    x[3, :] = -np.inf       # sampler.c:52-62 keeps index 0
+    st = independent_states(oracle.port, 5, 5)
+    g = run_gpu(ctx, x, 0.0, 0, 1.0, st)
+    o = oracle.port.sample_batch(x, 0.0, 0, 1.0, st)
+    check_tokens(g, o)
+
+
+def test_greedy_batched_with_penalties(ctx):
+    """Batched greedy + frequency/presence penalties, 256-token histories (scaled-down rows)."""
+    V, rows, H = 151936, 16, 256
+    x = normal_logits(rows, V, 3.0, 7)
+    h = histories(rows, H, V, 8)
+    h[:, :32] = h[:, 32:64]  # repeated ids so that counts > 1 matter
+    arg = x.argmax(axis=1)
+    h[:, 0] = arg            # the unpenalised winner is in the history
+    st = independent_states(oracle.port, 7, rows)
+    g = run_gpu(ctx, x, 0.0, 0, 1.0, st, freq=0.2, pres=0.3, history=h, want_logits=True)
+    o = oracle.port.sample_batch(x, 0.0, 0, 1.0, st, freq=0.2, pres=0.3, hist=h, want_logits=True)
+    check_tokens(g, o)
+    assert np.array_equal(g["logits"].view(np.uint32), o["logits"].view(np.uint32)), "post-penalty logits must be bit-equal"
+    assert (g["tokens"] != arg).any()
+
+
+@pytest.mark.parametrize("rep,freq,pres", [(1.1, 0.0, 0.0), (1.15, 0.2, 0.3), (0.0, 0.0, 0.0)])
+def test_topk_with_repetition_penalty(ctx, rep, freq, pres):
+    V, rows, H = 128256, 16, 64
+    x = normal_logits(rows, V, 2.5, 1234)
+    rng = np.random.default_rng(5)
+    for r in range(rows):
+        x[r, rng.integers(0, V, 8)] += 12.0
+    h = histories(rows, H, V, 9)
+    h[:, :8] = np.argsort(-x, axis=1)[:, :8]  # penalise the boosted ids
+    hl = rng.integers(0, H + 1, rows).astype(np.int32)
+    st = seq_states(oracle.port, 1234, rows)
+    g = run_gpu(ctx, x, 0.8, 40, 0.95, st, rep=rep, freq=freq, pres=pres, history=h, history_len=hl, kept_cap=40, want_logits=True)
+    o = oracle.port.sample_batch(x, 0.8, 40, 0.95, st, rep=rep, freq=freq, pres=pres, hist=h, hist_len=hl, detail_cap=40, want_logits=True)
+    check_tokens(g, o)
+    assert np.array_equal(g["logits"].view(np.uint32), o["logits"].view(np.uint32))
+    assert np.array_equal(g["kept_n"], o["detail_n"])
+    assert np.array_equal(g["kept_idx"], o["detail_idx"])
+    assert rel_err(g["kept_prob"], o["detail_prob"]) <= PROB_RTOL
+
+
+@pytest.mark.parametrize("V,k", [(128256, 40), (128256, 2), (128256, 50), (128256, 128), (128256, 256), (32000, 40), (5000, 40), (300, 40), (41, 40), (262144, 64)])
+def test_topk_sizes(ctx, V, k):
+    rows = 8
+    x = normal_logits(rows, V, 2.5, 31 + V + k)
+    st = independent_states(oracle.port, 77, rows)
+    g = run_gpu(ctx, x, 0.7, k, 0.9, st, kept_cap=k)
+    o = oracle.port.sample_batch(x, 0.7, k, 0.9, st, detail_cap=k)
+    check_tokens(g, o)
+    assert np.array_equal(g["kept_idx"], o["detail_idx"])
+    assert rel_err(g["kept_prob"], o["detail_prob"]) <= PROB_RTOL
+
+
+def test_topk_ties_and_slow_path(ctx):
+    """Rows made of a few distinct values: the k-th entry sits inside a run of ties, which
+    must resolve by ascending id; also k beyond the fast path."""
+    V, rows = 20000, 6
+    rng = np.random.default_rng(3)
+    x = rng.integers(-3, 4, size=(rows, V)).astype(np.float32)
+    x[0, :] = 0.0
+    st = independent_states(oracle.port, 11, rows)
+    for k in (3, 40, 1000, 9000):
+        g = run_gpu(ctx, x, 1.0, k, 1.0, st)
+        o = oracle.port.sample_batch(x, 1.0, k, 1.0, st)
+        check_tokens(g, o)
+    x2 = normal_logits(4, 128256, 2.5, 4)
+    for k in (1000, 8192, 20000):
+        g = run_gpu(ctx, x2, 0.9, k, 1.0, st[:4])
+        o = oracle.port.sample_batch(x2, 0.9, k, 1.0, st[:4])
+        check_tokens(g, o)
+
+
+def test_topp_heavy_tail(ctx):
+    """Gumbel*4 rows, per-row temperature and top_p: tiny nuclei (fast path)."""
+    V, rows = 262144, 32
+    x = gumbel_logits(rows, V, 4.0, 99)
+    rng = np.random.default_rng(99)
+    T = rng.uniform(0.5, 1.2, rows).astype(np.float32)
+    P = rng.uniform(0.8, 0.98, rows).astype(np.float32)
+    st = seq_states(oracle.port, 99, rows)
+    g = run_gpu(ctx, x, T, 0, P, st, kept_cap=16)
+    o = oracle.port.sample_batch(x, T, 0, P, st, detail_cap=16)
+    check_tokens(g, o)
+    assert np.array_equal(g["kept_n"], o["detail_n"])
+    full = (g["status"] & 8) == 0
+    assert full.any()
+    assert np.array_equal(g["kept_idx"][full], o["detail_idx"][full])
+    assert rel_err(g["kept_prob"][full], o["detail_prob"][full]) <= PROB_RTOL
+
+
+@pytest.mark.parametrize("V,sigma,p", [(128256, 2.5, 0.95), (128256, 2.5, 0.5), (5000, 1.0, 0.9), (1000, 0.0, 0.9), (33, 2.0, 0.3)])
+def test_topp_wide_nucleus(ctx, V, sigma, p):
+    """Gaussian rows give nuclei of thousands of ids: the bisection path."""
+    rows = 6
+    x = normal_logits(rows, V, sigma, 17 + V)
+    st = independent_states(oracle.port, 21, rows)
+    g = run_gpu(ctx, x, 0.8, 0, p, st, kept_cap=8)
+    o = oracle.port.sample_batch(x, 0.8, 0, p, st, detail_cap=8)
+    check_tokens(g, o)
+    assert np.array_equal(g["kept_n"], o["detail_n"])
+
+
+@pytest.mark.parametrize("V", [5, 1000, 32000, 128256, 262144])
+def test_temperature_only(ctx, V):
+    rows = 16
+    x = normal_logits(rows, V, 2.5, 5 + V)
+    x[0, :] = 0.0  # uniform row: every id equally likely
+    st = independent_states(oracle.port, 42, rows)
+    T = np.linspace(0.3, 1.5, rows).astype(np.float32)
+    g = run_gpu(ctx, x, T, 0, 1.0, st)
+    o = oracle.port.sample_batch(x, T, 0, 1.0, st)
+    check_tokens(g, o)
+    # top_k >= V and top_p >= 1 also end in the temperature path (sampler.c:187-189, :241-243)
+    g = run_gpu(ctx, x, T, V + 5, 1.0, st)
+    check_tokens(g, o)
+
+
+def test_softmax_probabilities(ctx):
+    V, rows = 128256, 4
+    x = normal_logits(rows, V, 2.5, 2)
+    T = np.array([0.5, 0.8, 1.0, 1.3], np.float32)
+    probs, sums = ctx.softmax(to_dev(x), to_dev(T))
+    probs = probs.cpu().numpy()
+    for r in range(rows):
+        ref, s = oracle.port.softmax(x[r], float(T[r]))
+        big = ref > 1e-30
+        assert rel_err(probs[r][big], ref[big]) <= PROB_RTOL
+        assert abs(float(sums[r]) - s) / s < 1e-6
+
+
+def test_verify_rows_share_one_generator(ctx):
+    """K+1 rows per sequence sampled in order with one generator, then the prefix-accept rule."""
+    V, S, K = 128256, 6, 6
+    R = K + 1
+    rng = np.random.default_rng(2024)
+    draft = normal_logits(S * K, V, 2.5, 2024).reshape(S, K, V)
+    target = np.empty((S, R, V), np.float32)
+    target[:, :K] = draft + normal_logits(S * K, V, 0.5, 2025).reshape(S, K, V)
+    target[:, K] = normal_logits(S, V, 2.5, 2026)
+    target = target.reshape(S * R, V)
+    for (T, k, p) in [(0.0, 0, 1.0), (1.0, 0, 1.0), (0.8, 40, 1.0)]:
+        st = independent_states(oracle.port, 2024, S)
+        dst = independent_states(oracle.port, 3024, S)
+        drafts = oracle.port.sample_batch(draft.reshape(S * K, V), T, k, p, dst, rows_per_seq=K)["tokens"].reshape(S, K)
+        fed = np.concatenate([rng.integers(0, V, (S, 1)).astype(np.int32), drafts], axis=1)
+        # make some proposals certainly right: replace them by what the target will say
+        o = oracle.port.sample_batch(target, T, k, p, st, rows_per_seq=R)
+        vo = o["tokens"].reshape(S, R)
+        fed[0, 1:] = vo[0, :K]        # everything accepted
+        fed[1, 1:3] = vo[1, :2]       # at least two accepted
+        g = run_gpu(ctx, target, T, k, p, st, rows_per_seq=R)
+        check_tokens(g, o)
+        acc, nem, em = ctx.accept_batch(to_dev(fed), to_dev(g["tokens"].reshape(S, R)))
+        acc, nem, em = acc.cpu().numpy(), nem.cpu().numpy(), em.cpu().numpy()
+        for s in range(S):
+            a, emitted = oracle.port.spec_accept(fed[s], vo[s])
+            assert acc[s] == a and nem[s] == a + 2
+            assert np.array_equal(em[s, :a + 2], emitted)
+        assert acc[0] == K and acc[1] >= 2
+
+
+def test_verify_penalties_count_fed_tokens(ctx):
+    V, S, R, H = 32000, 4, 5, 32
+    x = normal_logits(S * R, V, 2.5, 8)
+    h = histories(S, H, V, 9)
+    fed = np.argsort(-x.reshape(S, R, V)[:, -1], axis=1)[:, :R].astype(np.int32)  # ids that matter in the last row
+    st = independent_states(oracle.port, 1, S)
+    g = run_gpu(ctx, x, 0.0, 0, 1.0, st, rows_per_seq=R, rep=1.3, freq=0.5, pres=0.4, history=h, fed=fed, want_logits=True)
+    o = oracle.port.sample_batch(x, 0.0, 0, 1.0, st, rows_per_seq=R, rep=1.3, freq=0.5, pres=0.4, hist=h, extra=fed, want_logits=True)
+    check_tokens(g, o)
+    assert np.array_equal(g["logits"].view(np.uint32), o["logits"].view(np.uint32))
+
+
+def test_unaligned_rows(ctx):
+    """Rows that do not start on 16-byte boundaries take the plain-load path."""
+    import torch
+    V, rows = 10007, 8
+    x = normal_logits(rows, V, 2.5, 6)
+    buf = torch.zeros(rows * (V + 3) + 1, dtype=torch.float32, device="cuda")
+    view = buf[1:1 + rows * (V + 3)].view(rows, V + 3)[:, :V]
+    view.copy_(torch.from_numpy(x))
+    st = independent_states(oracle.port, 3, rows)
+    dT, dK, dP = per_seq(rows, 0.8, 40, 1.0)
+    out = ctx.sample_batch(view, dT, dK, dP, u64_to_dev(st))
+    o = oracle.port.sample_batch(x, 0.8, 40, 1.0, st)
+    assert np.array_equal(out["tokens"].cpu().numpy(), o["tokens"])
+
+
+def test_mixed_modes_in_one_launch(ctx):
+    V, rows = 128256, 12
+    x = normal_logits(rows, V, 2.5, 12)
+    x[:, :4] += 14.0
+    T = np.array([0.0, 0.8, 0.8, 1.0] * 3, np.float32)
+    K = np.array([0, 40, 0, 0] * 3, np.int32)
+    P = np.array([1.0, 1.0, 0.9, 1.0] * 3, np.float32)
+    st = independent_states(oracle.port, 8, rows)
+    g = run_gpu(ctx, x, T, K, P, st)
+    o = oracle.port.sample_batch(x, T, K, P, st)
+    check_tokens(g, o)
