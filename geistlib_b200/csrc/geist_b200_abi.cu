@@ -67,6 +67,7 @@ struct Plan {
     int    slice_bytes  = 0;
     int    bitmap_words = 0;
     int    hist_cap     = 0;
+    int    cand_cap     = 0;
     size_t smem         = 0;
 };
 
@@ -80,10 +81,12 @@ bool shape_for(size_t V, size_t hist_max, int cluster, Plan &pl) {
     }
     pl.cluster      = cluster;
     pl.slice        = (int) slice;
-    pl.slice_bytes  = (int) round_up(std::max(slice * 4, (size_t) 20 * cluster * gb::kLocalCand), 128);
+    /* short slices reserve room for every element, so that "collect everything" can never overflow */
+    pl.cand_cap     = slice <= 1024 ? (int) std::max<size_t>(slice, gb::kLocalCand) : gb::kLocalCand;
+    pl.slice_bytes  = (int) round_up(std::max(slice * 4, (size_t) 20 * cluster * pl.cand_cap), 128);
     pl.bitmap_words = hist_max ? (int) ((slice + 31) / 32) : 0;
     pl.hist_cap     = hist_max ? (int) std::min(hist_max, slice) : 0;
-    pl.smem         = (size_t) pl.slice_bytes + gb::sample_rows_fixed_smem() + (size_t) pl.bitmap_words * 4 + (size_t) pl.hist_cap * 8;
+    pl.smem         = (size_t) pl.slice_bytes + gb::sample_rows_fixed_smem() + (size_t) pl.cand_cap * 8 + (size_t) pl.bitmap_words * 4 + (size_t) pl.hist_cap * 8;
     return pl.smem <= kSmemMax;
 }
 
@@ -283,6 +286,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.slice_bytes  = pl.slice_bytes;
     p.bitmap_words = pl.bitmap_words;
     p.hist_cap     = pl.hist_cap;
+    p.cand_cap     = pl.cand_cap;
     p.aligned      = ((reinterpret_cast<uintptr_t>(b->logits) & 15u) == 0 && (b->row_stride & 3u) == 0) ? 1 : 0;
     p.flags        = flags;
     cudaStream_t st = stream ? as_stream(stream) : ctx->stream;

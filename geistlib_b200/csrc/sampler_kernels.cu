@@ -66,7 +66,6 @@ struct __align__(16) RowShared {
     long long wred_i[2][kWarps];
     float     wred_f[kWarps];
     int       wred_a[kWarps];
-    Pair      cand[kLocalCand];
     int       n_cand_local;
     int       n_dlist;
     int       decision;
@@ -320,7 +319,8 @@ __global__ void __launch_bounds__(kThreads) sample_rows_kernel(const __grid_cons
     c.par   = 0;
     c.sl    = reinterpret_cast<float *>(smem_raw);
     c.sh    = reinterpret_cast<RowShared *>(smem_raw + p.slice_bytes);
-    unsigned *bitmap = reinterpret_cast<unsigned *>(c.sh + 1);
+    Pair     *cand   = reinterpret_cast<Pair *>(c.sh + 1); /* this CTA's candidates for the row's finisher */
+    unsigned *bitmap = reinterpret_cast<unsigned *>(cand + p.cand_cap);
     PenEntry *dlist  = reinterpret_cast<PenEntry *>(bitmap + p.bitmap_words);
     RowShared *sh    = c.sh;
 
@@ -686,9 +686,9 @@ __global__ void __launch_bounds__(kThreads) sample_rows_kernel(const __grid_cons
                 if (li < c.n) {
                     if (x >= tau) {
                         const int pos = atomicAdd(&sh->n_cand_local, 1);
-                        if (pos < kLocalCand) {
-                            sh->cand[pos].v   = x;
-                            sh->cand[pos].idx = c.s0 + li;
+                        if (pos < p.cand_cap) {
+                            cand[pos].v   = x;
+                            cand[pos].idx = c.s0 + li;
                         }
                     } else if (mode == M_TOPP) {
                         bulk += (double) expf(scaled_arg(x, row_max, inv_t));
@@ -717,7 +717,7 @@ __global__ void __launch_bounds__(kThreads) sample_rows_kernel(const __grid_cons
             int total = 0;
             for (int i = 0; i < c.C; i++) {
                 const int nc = sh->cta_ncand[i];
-                if (nc > kLocalCand) {
+                if (nc > p.cand_cap) {
                     need_generic = true;
                 }
                 total += nc;
@@ -735,7 +735,7 @@ __global__ void __launch_bounds__(kThreads) sample_rows_kernel(const __grid_cons
                  * top-p: scratch in the dead group-maxima area, because a failed probe must leave
                  * the slice intact for the bisection path. */
                 const bool in_slice = mode == M_TOPK;
-                const int  fcap     = c.C * kLocalCand;
+                const int  fcap     = c.C * p.cand_cap;
                 Pair      *ml       = in_slice ? reinterpret_cast<Pair *>(c.sl) : sh->u.fin.ml; /* merged, unsorted */
                 Pair      *sorted   = in_slice ? ml + fcap : sh->u.fin.srt;                     /* walk order */
                 float     *q        = in_slice ? reinterpret_cast<float *>(sorted + fcap) : sh->u.fin.q;
@@ -744,7 +744,7 @@ __global__ void __launch_bounds__(kThreads) sample_rows_kernel(const __grid_cons
                     for (int i = 0; i < c.warp; i++) {
                         off += sh->cta_ncand[i];
                     }
-                    const Pair *src = cg::this_cluster().map_shared_rank(sh->cand, c.warp);
+                    const Pair *src = cg::this_cluster().map_shared_rank(cand, c.warp);
                     const int   nc  = sh->cta_ncand[c.warp];
                     for (int i = c.lane; i < nc; i += 32) {
                         ml[off + i] = src[i];

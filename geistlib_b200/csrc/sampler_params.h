@@ -70,6 +70,7 @@ struct SampleParams {
     int      slice_bytes;  /* bytes reserved for the slice buffer (multiple of 128) */
     int      bitmap_words; /* 0 when no history is given */
     int      hist_cap;     /* distinct-id entries reserved per CTA */
+    int      cand_cap;     /* candidate entries reserved per CTA (>= kLocalCand) */
     int      aligned;      /* rows start on 16-byte boundaries: bulk copies allowed */
     unsigned flags;
 };
