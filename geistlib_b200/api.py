@@ -164,7 +164,7 @@ class Context:
     def sample_batch(self, logits, temperature, top_k, top_p, rng_state, rows_per_seq: int = 1,
                      rep=None, freq=None, pres=None, history=None, history_len=None, fed=None,
                      slot=None, kept_cap: int = 0, want_logits: bool = False, vocab_offset: int = 0,
-                     select_only: bool = False, stream=None, out=None, sync: bool = True):
+                     select_only: bool = False, stream=None, out=None, sync: bool = True, launch: bool = True):
         """logits: CUDA float32 [rows, V] (rows = n_seq * rows_per_seq). Per-sequence
         arguments are CUDA tensors of length n_seq (or of the slot table's size).
         Returns a dict of CUDA tensors; ``out`` lets a caller reuse a previous dict."""
@@ -218,10 +218,16 @@ class Context:
         if stream is None:
             stream = torch.cuda.current_stream(dev).cuda_stream
         fn = lib.geist_b200_shard_select if select_only else lib.geist_b200_sample_batch
-        _check(fn(self.handle, C.byref(b), c_void_p(stream)))
-        if sync:
-            torch.cuda.synchronize(dev)
+        if launch:
+            _check(fn(self.handle, C.byref(b), c_void_p(stream)))
+            if sync:
+                torch.cuda.synchronize(dev)
+        out["_desc"] = b  # the filled struct geist_b200_batch, for callers that relaunch it themselves
         return out
+
+    def relaunch(self, out, stream: int) -> None:
+        """Launch a descriptor prepared by sample_batch(..., launch=False) again (asynchronous)."""
+        _check(lib.geist_b200_sample_batch(self.handle, C.byref(out["_desc"]), c_void_p(stream)))
 
     def argmax_f32(self, row) -> int:
         idx = c_int32(-1)

@@ -289,7 +289,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.cand_cap     = pl.cand_cap;
     p.aligned      = ((reinterpret_cast<uintptr_t>(b->logits) & 15u) == 0 && (b->row_stride & 3u) == 0) ? 1 : 0;
     p.flags        = flags;
-    cudaStream_t st = stream ? as_stream(stream) : ctx->stream;
+    cudaStream_t st = as_stream(stream);
     CUDA_TRY(gb::launch_sample_rows(p, pl.cluster, pl.smem, st));
     return GEIST_OK;
 }
@@ -337,7 +337,7 @@ extern "C" enum geist_status geist_b200_shard_merge_sample(struct geist_b200_ctx
     p.kept_n      = m->kept_n;
     p.kept_idx    = m->kept_idx;
     p.kept_val    = m->kept_prob;
-    CUDA_TRY(gb::launch_merge_sample(p, stream ? as_stream(stream) : ctx->stream));
+    CUDA_TRY(gb::launch_merge_sample(p, as_stream(stream)));
     return GEIST_OK;
 }
 
@@ -351,7 +351,7 @@ extern "C" enum geist_status geist_b200_accept_batch(struct geist_b200_ctx *ctx,
     }
     CUDA_TRY(cudaSetDevice(ctx->device));
     gb::AcceptParams p{fed, verify_out, (int) n_seq, (int) k, accepted, n_emitted, emitted};
-    CUDA_TRY(gb::launch_accept(p, stream ? as_stream(stream) : ctx->stream));
+    CUDA_TRY(gb::launch_accept(p, as_stream(stream)));
     return GEIST_OK;
 }
 
@@ -361,7 +361,7 @@ extern "C" enum geist_status geist_b200_softmax(struct geist_b200_ctx *ctx, cons
         return fail(GEIST_E_INVALID_ARG, "softmax: bad argument");
     }
     CUDA_TRY(cudaSetDevice(ctx->device));
-    CUDA_TRY(gb::launch_softmax_rows(logits, (long long) row_stride, (int) n_rows, (int) n_vocab, temperature, probs, sums, stream ? as_stream(stream) : ctx->stream));
+    CUDA_TRY(gb::launch_softmax_rows(logits, (long long) row_stride, (int) n_rows, (int) n_vocab, temperature, probs, sums, as_stream(stream)));
     return GEIST_OK;
 }
 
@@ -371,7 +371,7 @@ extern "C" enum geist_status geist_b200_scatter_kept(struct geist_b200_ctx *ctx,
         return fail(GEIST_E_INVALID_ARG, "scatter_kept: bad argument");
     }
     CUDA_TRY(cudaSetDevice(ctx->device));
-    CUDA_TRY(gb::launch_scatter_kept(kept_n, kept_idx, kept_prob, kept_cap, (int) n_rows, (int) n_vocab, vocab_offset, dense, stream ? as_stream(stream) : ctx->stream));
+    CUDA_TRY(gb::launch_scatter_kept(kept_n, kept_idx, kept_prob, kept_cap, (int) n_rows, (int) n_vocab, vocab_offset, dense, as_stream(stream)));
     return GEIST_OK;
 }
 
@@ -500,7 +500,7 @@ geist_token_t sample_host_row(size_t n, const float *logits, float *staging, flo
     b.rng_out      = reinterpret_cast<uint64_t *>(&c->d_small->rng_out);
     b.tokens       = &c->d_small->token;
     b.row_status   = &c->d_small->status;
-    if (geist_b200_sample_batch(c, &b, nullptr) != GEIST_OK) {
+    if (geist_b200_sample_batch(c, &b, c->stream) != GEIST_OK) {
         return -1;
     }
     e = cudaMemcpyAsync(h, c->d_small, sizeof *h, cudaMemcpyDeviceToHost, c->stream);
@@ -612,7 +612,7 @@ extern "C" enum geist_status geist_b200_argmax_f32(struct geist_b200_ctx *ctx, c
     b.rng_out      = reinterpret_cast<uint64_t *>(&ctx->d_small->rng_out);
     b.tokens       = &ctx->d_small->token;
     b.row_status   = &ctx->d_small->status;
-    enum geist_status s = geist_b200_sample_batch(ctx, &b, nullptr);
+    enum geist_status s = geist_b200_sample_batch(ctx, &b, ctx->stream);
     if (s != GEIST_OK) {
         return s;
     }

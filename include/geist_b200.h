@@ -170,7 +170,7 @@ struct geist_b200_batch {
 
 /* Replaces the sampler dispatch of finalize_logits_one_row / _batch
  * (head.c:165-186, :289-303) for any number of sessions at once. `stream` is a
- * cudaStream_t passed as void* (NULL = the context's own stream). Asynchronous. */
+ * cudaStream_t passed as void* (NULL = the legacy default stream, as in CUDA). Asynchronous. */
 enum geist_status geist_b200_sample_batch(struct geist_b200_ctx *ctx, const struct geist_b200_batch *b, void *stream);
 
 /* Backend operator slot argmax_f32 (include/geist_backend.h:414-421): greedy

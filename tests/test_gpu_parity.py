@@ -31,7 +31,7 @@ def run_gpu(ctx, logits, T, K, P, states, **kw):
     if kw.get("fed") is not None:
         extra["fed"] = to_dev(kw.pop("fed"))
     out = ctx.sample_batch(dl, dT, dK, dP, u64_to_dev(states), **extra, **kw)
-    res = {k: (v.cpu().numpy() if v is not None else None) for k, v in out.items()}
+    res = {k: (v.cpu().numpy() if v is not None else None) for k, v in out.items() if not k.startswith("_")}
     res["rng_state"] = u64_from_dev(out["rng_state"])
     assert (res["status"] & INVALID == 0).all(), res["status"]
     return res
