@@ -301,7 +301,7 @@ class Context:
 def plan(n_vocab: int, max_history: int = 0):
     c, s, m, r = c_int32(), c_int32(), c_int32(), c_int32()
     _check(lib.geist_b200_plan(n_vocab, max_history, C.byref(c), C.byref(s), C.byref(m), C.byref(r)))
-    return {"cluster": c.value, "slice": s.value, "smem_bytes": m.value, "resident_clusters": r.value}
+    return {"slices_per_row": c.value, "slice": s.value, "smem_bytes": m.value, "ring_stages": r.value}
 
 
 class Batcher:

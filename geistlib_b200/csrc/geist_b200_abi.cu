@@ -19,9 +19,8 @@
 #include "sampler_params.h"
 
 namespace gb {
-size_t      sample_rows_fixed_smem();
-cudaError_t launch_sample_rows(const SampleParams &p, int cluster, size_t smem_bytes, cudaStream_t stream);
-int         sample_rows_max_clusters(int cluster, size_t smem_bytes);
+size_t      sample_stream_fixed_smem();
+cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, cudaStream_t stream);
 cudaError_t launch_merge_sample(const MergeParams &p, cudaStream_t stream);
 cudaError_t launch_accept(const AcceptParams &p, cudaStream_t stream);
 cudaError_t launch_scatter_kept(const int *kept_n, const int *kept_idx, const float *kept_val, int kept_cap, int n_rows, int V, int vocab_offset, float *dense, cudaStream_t stream);
@@ -58,50 +57,63 @@ extern "C" const char *geist_b200_errmsg(void) { return g_err.c_str(); }
 
 namespace {
 
-constexpr size_t kSmemMax      = 227 * 1024; /* opt-in shared memory per CTA on sm_100 */
-constexpr int    kSliceTarget  = 16384;      /* floats per CTA the planner aims for (64 KiB) */
+constexpr size_t kSmemMax = 227 * 1024; /* opt-in shared memory per CTA on sm_100 */
+constexpr int    kLanes   = 4;          /* launches of one context that may overlap on the GPU */
 
 struct Plan {
-    int    cluster      = 0;
+    int    n_slices     = 0;
     int    slice        = 0;
-    int    slice_bytes  = 0;
+    int    stage_bytes  = 0;
+    int    stages       = 0;
     int    bitmap_words = 0;
     int    hist_cap     = 0;
     int    cand_cap     = 0;
+    int    fin_cap      = 0;
     size_t smem         = 0;
+    int    sms          = 0;
 };
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-/* hist_max = 0: no history pointer will be given. */
-bool shape_for(size_t V, size_t hist_max, int cluster, Plan &pl) {
-    size_t slice = round_up((V + cluster - 1) / cluster, 4);
-    if ((size_t) (cluster - 1) * slice >= V && cluster > 1) {
-        return false; /* a CTA would own nothing */
+/* hist_max = 0: no history pointer will be given. Rows are cut into the fewest slices of at
+ * most kSliceMax floats; whatever shared memory the candidate / history / finisher buffers
+ * leave goes to the bulk-copy ring. */
+bool make_plan(size_t V, size_t hist_max, Plan &pl) {
+    int            dev = 0;
+    cudaDeviceProp prop;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+        return false;
     }
-    pl.cluster      = cluster;
+    const size_t n_slices = (V + gb::kSliceMax - 1) / gb::kSliceMax;
+    const size_t slice    = round_up((V + n_slices - 1) / n_slices, 4);
+    if (n_slices > 1 && (n_slices - 1) * slice >= V) {
+        return false;
+    }
+    pl.sms          = prop.multiProcessorCount;
+    pl.n_slices     = (int) n_slices;
     pl.slice        = (int) slice;
-    /* short slices reserve room for every element, so that "collect everything" can never overflow */
-    pl.cand_cap     = slice <= 1024 ? (int) std::max<size_t>(slice, gb::kLocalCand) : gb::kLocalCand;
-    pl.slice_bytes  = (int) round_up(std::max(slice * 4, (size_t) 20 * cluster * pl.cand_cap), 128);
+    pl.stage_bytes  = (int) round_up(slice * 4, 128);
     pl.bitmap_words = hist_max ? (int) ((slice + 31) / 32) : 0;
     pl.hist_cap     = hist_max ? (int) std::min(hist_max, slice) : 0;
-    pl.smem         = (size_t) pl.slice_bytes + gb::sample_rows_fixed_smem() + (size_t) pl.cand_cap * 8 + (size_t) pl.bitmap_words * 4 + (size_t) pl.hist_cap * 8;
-    return pl.smem <= kSmemMax;
-}
-
-bool make_plan(size_t V, size_t hist_max, Plan &pl) {
-    int want = (int) std::min<size_t>((V + kSliceTarget - 1) / kSliceTarget, gb::kMaxCluster);
-    want     = std::max(want, 1);
-    /* first choice: ~64 KiB slices; then any cluster size that fits and that the device can place */
-    for (int c = want; c <= gb::kMaxCluster; c++) {
-        if (shape_for(V, hist_max, c, pl) && gb::sample_rows_max_clusters(c, pl.smem) > 0) {
-            return true;
-        }
-    }
-    for (int c = want - 1; c >= 1; c--) {
-        if (shape_for(V, hist_max, c, pl) && gb::sample_rows_max_clusters(c, pl.smem) > 0) {
-            return true;
+    const int caps[] = {256, 224, 192, 160, 128, 96, 64};
+    for (int want_stages = 3; want_stages >= 1; want_stages--) {
+        for (int cap : caps) {
+            /* short slices reserve room for every element, so that "collect everything" cannot overflow */
+            const int cand_cap = slice <= 1024 ? (int) round_up(slice, 32) : cap;
+            const int fin_cap  = (int) std::max<size_t>(256, std::min<size_t>(n_slices * (size_t) cand_cap, 4096));
+            const size_t fixed = gb::sample_stream_fixed_smem() + (size_t) cand_cap * 8 + (size_t) pl.bitmap_words * 4 + (size_t) pl.hist_cap * 8 + (size_t) fin_cap * 16 +
+                                 (size_t) gb::kFastKMax * 12 + 128;
+            if (fixed + (size_t) pl.stage_bytes > kSmemMax) {
+                continue;
+            }
+            const int stages = (int) std::min<size_t>(gb::kMaxStages, (kSmemMax - fixed) / (size_t) pl.stage_bytes);
+            if (stages >= want_stages) {
+                pl.cand_cap = cand_cap;
+                pl.fin_cap  = fin_cap;
+                pl.stages   = stages;
+                pl.smem     = fixed + (size_t) stages * (size_t) pl.stage_bytes;
+                return true;
+            }
         }
     }
     return false;
@@ -122,7 +134,7 @@ struct PlanCache {
         for (auto &it : items) {
             if (it.first.dev == dev && it.first.V == V && it.first.H == H) {
                 pl = it.second;
-                return pl.cluster > 0;
+                return pl.n_slices > 0;
             }
         }
         Plan p;
@@ -160,6 +172,17 @@ struct geist_b200_ctx {
     };
     Small *d_small = nullptr;
     Small *h_small = nullptr; /* pinned */
+
+    /* kernel scratch: slice records, candidates, row counters, multi-pass row copies. kLanes
+     * independent sets, used round-robin, so that up to kLanes launches may overlap on the GPU. */
+    struct Lane {
+        unsigned char *buf         = nullptr;
+        size_t         bytes       = 0;
+        int           *counters    = nullptr;
+        size_t         counter_cap = 0;
+    } lane[kLanes];
+    unsigned   next_lane = 0;
+    std::mutex lane_mu;
 };
 
 extern "C" enum geist_status geist_b200_ctx_create(int device, struct geist_b200_ctx **out) {
@@ -206,6 +229,10 @@ extern "C" void geist_b200_ctx_destroy(struct geist_b200_ctx *c) {
     if (c->stream) {
         cudaStreamSynchronize(c->stream);
     }
+    for (auto &ln : c->lane) {
+        cudaFree(ln.buf);
+        cudaFree(ln.counters);
+    }
     cudaFree(c->d_row);
     cudaFree(c->d_small);
     cudaFreeHost(c->h_small);
@@ -227,7 +254,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     if (b->n_seq == 0 || b->rows_per_seq == 0 || b->n_vocab == 0) {
         return fail(GEIST_E_INVALID_ARG, "sample_batch: n_seq, rows_per_seq and n_vocab must be positive");
     }
-    if (b->n_vocab > 0x7fffffffu || b->n_seq * b->rows_per_seq > (size_t) 0x7fffffff / gb::kMaxCluster) {
+    if (b->n_vocab > 0x7fffffffu || b->n_seq * b->rows_per_seq > (size_t) 0x7fffffff / gb::kMaxSlices) {
         return fail(GEIST_E_INVALID_ARG, "sample_batch: sizes exceed int32 ids / grid limits");
     }
     if (b->row_stride < b->n_vocab) {
@@ -282,15 +309,62 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.kept_n       = b->kept_n;
     p.kept_idx     = b->kept_idx;
     p.kept_val     = b->kept_prob;
+    p.n_slices     = pl.n_slices;
     p.slice        = pl.slice;
-    p.slice_bytes  = pl.slice_bytes;
+    p.stage_bytes  = pl.stage_bytes;
+    p.stages       = pl.stages;
     p.bitmap_words = pl.bitmap_words;
     p.hist_cap     = pl.hist_cap;
     p.cand_cap     = pl.cand_cap;
+    p.fin_cap      = pl.fin_cap;
     p.aligned      = ((reinterpret_cast<uintptr_t>(b->logits) & 15u) == 0 && (b->row_stride & 3u) == 0) ? 1 : 0;
     p.flags        = flags;
     cudaStream_t st = as_stream(stream);
-    CUDA_TRY(gb::launch_sample_rows(p, pl.cluster, pl.smem, st));
+
+    /* scratch of this launch */
+    const size_t n_rows   = (size_t) p.n_rows;
+    const size_t n_items  = n_rows * (size_t) pl.n_slices;
+    const int    grid     = (int) std::min<size_t>((size_t) pl.sms, n_items);
+    const size_t gen_str  = round_up(b->n_vocab, 4);
+    const size_t gen_bmw  = (b->n_vocab + 31) / 32;
+    const size_t gen_hcap = hist_max ? std::min(hist_max, b->n_vocab) : 0;
+    const size_t off_recs = 0;
+    const size_t off_cand = round_up(off_recs + n_items * sizeof(gb::SliceRec), 256);
+    const size_t off_rows = round_up(off_cand + n_items * (size_t) pl.cand_cap * sizeof(gb::Pair), 256);
+    const size_t off_bm   = round_up(off_rows + (size_t) grid * gen_str * 4, 256);
+    const size_t off_dl   = round_up(off_bm + (size_t) grid * gen_bmw * 4, 256);
+    const size_t need     = round_up(off_dl + (size_t) grid * gen_hcap * sizeof(gb::Pair), 256);
+    geist_b200_ctx::Lane *ln;
+    {
+        std::lock_guard<std::mutex> lk(ctx->lane_mu);
+        ln = &ctx->lane[ctx->next_lane++ % kLanes];
+        if (ln->bytes < need) {
+            cudaFree(ln->buf); /* waits for work that may still use it */
+            ln->buf   = nullptr;
+            ln->bytes = 0;
+            CUDA_TRY(cudaMalloc((void **) &ln->buf, need));
+            ln->bytes = need;
+        }
+        if (ln->counter_cap < n_rows) {
+            cudaFree(ln->counters);
+            ln->counters    = nullptr;
+            ln->counter_cap = 0;
+            const size_t cap = round_up(n_rows, 1024);
+            CUDA_TRY(cudaMalloc((void **) &ln->counters, cap * sizeof(int)));
+            CUDA_TRY(cudaMemset(ln->counters, 0, cap * sizeof(int)));
+            ln->counter_cap = cap;
+        }
+    }
+    p.row_counter      = ln->counters;
+    p.recs             = reinterpret_cast<gb::SliceRec *>(ln->buf + off_recs);
+    p.cands            = reinterpret_cast<gb::Pair *>(ln->buf + off_cand);
+    p.gen_rows         = reinterpret_cast<float *>(ln->buf + off_rows);
+    p.gen_stride       = (long long) gen_str;
+    p.gen_bitmap       = reinterpret_cast<unsigned *>(ln->buf + off_bm);
+    p.gen_bitmap_words = (int) gen_bmw;
+    p.gen_dlist        = reinterpret_cast<gb::Pair *>(ln->buf + off_dl);
+    p.gen_hist_cap     = (int) gen_hcap;
+    CUDA_TRY(gb::launch_sample_stream(p, grid, pl.smem, st));
     return GEIST_OK;
 }
 
@@ -375,19 +449,16 @@ extern "C" enum geist_status geist_b200_scatter_kept(struct geist_b200_ctx *ctx,
     return GEIST_OK;
 }
 
-extern "C" enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history, int32_t *cluster, int32_t *slice, int32_t *smem_bytes, int32_t *resident_clusters) {
+extern "C" enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history, int32_t *slices_per_row, int32_t *slice, int32_t *smem_bytes, int32_t *ring_stages) {
     Plan pl;
     if (n_vocab == 0 || !g_plans.get(n_vocab, max_history, pl)) {
-        if (cluster) {
-            *cluster = 0;
-        }
-        if (resident_clusters) {
-            *resident_clusters = 0;
+        if (slices_per_row) {
+            *slices_per_row = 0;
         }
         return fail(GEIST_E_UNSUPPORTED, "plan: no launch shape for n_vocab=%zu, history=%zu", n_vocab, max_history);
     }
-    if (cluster) {
-        *cluster = pl.cluster;
+    if (slices_per_row) {
+        *slices_per_row = pl.n_slices;
     }
     if (slice) {
         *slice = pl.slice;
@@ -395,8 +466,8 @@ extern "C" enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history,
     if (smem_bytes) {
         *smem_bytes = (int32_t) pl.smem;
     }
-    if (resident_clusters) {
-        *resident_clusters = gb::sample_rows_max_clusters(pl.cluster, pl.smem);
+    if (ring_stages) {
+        *ring_stages = pl.stages;
     }
     return GEIST_OK;
 }

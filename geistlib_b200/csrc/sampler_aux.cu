@@ -1,0 +1,263 @@
+/*
+ * sampler_aux.cu — the small kernels around the streaming sampler: merge of
+ * vocabulary-shard candidates, the speculative prefix-accept rule, batcher
+ * bookkeeping, and the dense inspection outputs.
+ */
+#include "sampler_device.cuh"
+
+namespace gb {
+
+/* ------------------------------------------------- merge of shard candidates -- */
+
+/* One CTA per row: the union of the per-shard lists, ordered by (value desc,
+ * global id asc), cut to k, then the top-k draw of sampler.c:217-222. */
+__global__ void __launch_bounds__(256) merge_sample_kernel(const __grid_constant__ MergeParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int row   = blockIdx.x;
+    const int cap   = p.n_shards * p.k_stride;
+    Pair     *ml    = reinterpret_cast<Pair *>(smem_raw);
+    Pair     *srt   = ml + cap;
+    float    *q     = reinterpret_cast<float *>(srt + cap);
+    __shared__ int    n_total;
+    __shared__ double S_sh;
+    if (threadIdx.x == 0) {
+        n_total = 0;
+    }
+    __syncthreads();
+    for (int s = 0; s < p.n_shards; s++) {
+        const int    nc  = min(p.cand_n[(size_t) s * p.n_rows + row], p.k_stride);
+        const size_t off = ((size_t) s * p.n_rows + row) * (size_t) p.k_stride;
+        __shared__ int base;
+        if (threadIdx.x == 0) {
+            base = n_total;
+            n_total += nc;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nc; i += blockDim.x) {
+            ml[base + i].v   = p.cand_val[off + i];
+            ml[base + i].idx = p.cand_gid[off + i];
+        }
+        __syncthreads();
+    }
+    const int total = n_total;
+    for (int t = threadIdx.x; t < total; t += blockDim.x) {
+        const Pair me   = ml[t];
+        int        rank = 0;
+        for (int j = 0; j < total; j++) {
+            rank += pair_before(ml[j].v, ml[j].idx, me.v, me.idx) ? 1 : 0;
+        }
+        srt[rank] = me;
+    }
+    __syncthreads();
+    const float T     = p.temperature[row];
+    int         k     = min(min(p.top_k[row], kTopKClamp), total);
+    const float inv_t = T > 0.0f ? __fdiv_rn(1.0f, T) : 1.0f;
+    if (!(T > 0.0f) || k <= 1) {
+        /* greedy: best candidate, no draw (sampler.c:184-186) */
+        if (threadIdx.x == 0) {
+            p.tokens[row] = total > 0 ? srt[0].idx : -1;
+            p.status[row] = total > 0 ? ST_OK : ST_INTERNAL;
+            if (p.rng_out) {
+                p.rng_out[row] = p.rng_in[row];
+            }
+            if (p.kept_cap > 0) {
+                p.kept_n[row] = 0;
+            }
+        }
+        return;
+    }
+    const float m = srt[0].v;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) {
+        q[i] = exp_exact(scaled_arg(srt[i].v, m, inv_t));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double S = 0.0;
+        for (int i = 0; i < k; i++) {
+            S += (double) q[i];
+        }
+        unsigned long long rng  = p.rng_in[row];
+        const double       u    = (double) unit_from(xorshift_next(rng)) * S;
+        double             a    = 0.0;
+        int                pick = k - 1;
+        for (int i = 0; i < k; i++) {
+            a += (double) q[i];
+            if (u < a) {
+                pick = i;
+                break;
+            }
+        }
+        p.tokens[row] = srt[pick].idx;
+        p.status[row] = ST_OK;
+        if (p.rng_out) {
+            p.rng_out[row] = rng;
+        }
+        if (p.kept_cap > 0) {
+            p.kept_n[row] = k;
+        }
+        S_sh = S;
+    }
+    __syncthreads();
+    if (p.kept_cap > 0) {
+        for (int i = threadIdx.x; i < min(k, p.kept_cap); i += blockDim.x) {
+            p.kept_idx[(size_t) row * p.kept_cap + i] = srt[i].idx;
+            p.kept_val[(size_t) row * p.kept_cap + i] = __double2float_rn((double) q[i] / S_sh);
+        }
+    }
+}
+
+/* ------------------------------------------------------ speculative accept -- */
+
+/* session.c:599-625, one thread per sequence. */
+__global__ void accept_kernel(const AcceptParams p) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= p.n_seq) {
+        return;
+    }
+    const int *fed = p.fed + (size_t) s * p.k;
+    const int *vo  = p.verify_out + (size_t) s * p.k;
+    int        a   = 0;
+    while (a + 1 < p.k && vo[a] == fed[a + 1]) {
+        a++;
+    }
+    int *em = p.emitted + (size_t) s * (p.k + 1);
+    for (int i = 0; i <= a; i++) {
+        em[i] = fed[i];
+    }
+    em[a + 1] = vo[a];
+    for (int i = a + 2; i <= p.k; i++) {
+        em[i] = -1;
+    }
+    p.accepted[s]  = a;
+    p.n_emitted[s] = a + 2;
+}
+
+/* ------------------------------------------------------ batcher bookkeeping -- */
+
+/* After a batcher call, one thread per participating session: the generator
+ * word computed by the sampling kernel becomes the session's state, and the
+ * tokens that were committed join its history ring. */
+__global__ void post_step_kernel(const int *slot, int n_seq, int per_seq, int first, const int *tokens, const int *counts, int *hist, int hist_cap, int *hist_len,
+                                 long long *hist_total, const unsigned long long *rng_tmp, unsigned long long *rng) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_seq) {
+        return;
+    }
+    const int s = slot[i];
+    rng[s]      = rng_tmp[s];
+    if (tokens != nullptr && hist_cap > 0) {
+        long long tot = hist_total[s];
+        const int cnt = counts[i];
+        for (int j = first; j < cnt; j++) {
+            hist[(size_t) s * hist_cap + (size_t) (tot % hist_cap)] = tokens[(size_t) i * per_seq + j];
+            tot++;
+        }
+        hist_total[s] = tot;
+        hist_len[s]   = (int) (tot < hist_cap ? tot : hist_cap);
+    }
+}
+
+/* ------------------------------------------------------------- dense helpers -- */
+
+/* probs[row, :] = 0, then kept entries scattered: the post-filter probability vector. */
+__global__ void scatter_kept_kernel(const int *kept_n, const int *kept_idx, const float *kept_val, int kept_cap, int V, int vocab_offset, float *dense) {
+    const int row = blockIdx.x;
+    const int n   = min(kept_n[row], kept_cap);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int id = kept_idx[(size_t) row * kept_cap + i] - vocab_offset;
+        if (id >= 0 && id < V) {
+            dense[(size_t) row * V + id] = kept_val[(size_t) row * kept_cap + i];
+        }
+    }
+}
+
+/* Dense softmax with temperature, p_i = (float)((double)expf((x_i - max) * inv_t) / sum)
+ * (sampler.c:68-85 and :253-255). One CTA per row, three passes; an inspection
+ * kernel, not part of the sampling hot path. */
+__global__ void __launch_bounds__(1024) softmax_rows_kernel(const float *logits, long long row_stride, int V, const float *temperature, float *probs, double *sums) {
+    const int    row = blockIdx.x;
+    const float *x   = logits + (size_t) row * (size_t) row_stride;
+    float       *y   = probs + (size_t) row * (size_t) V;
+    const float  T   = temperature[row];
+    const float  inv_t = T > 0.0f ? __fdiv_rn(1.0f, T) : 1.0f;
+    __shared__ float  red_f[32];
+    __shared__ double red_d[32];
+    float m = -CUDART_INF_F;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        m = fmaxf(m, x[i]);
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        red_f[threadIdx.x >> 5] = m;
+    }
+    __syncthreads();
+    m = red_f[0];
+    for (int w = 1; w < (int) (blockDim.x >> 5); w++) {
+        m = fmaxf(m, red_f[w]);
+    }
+    double acc = 0.0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float e = expf(scaled_arg(x[i], m, inv_t));
+        y[i]          = e;
+        acc += (double) e;
+    }
+    acc = warp_sum_d(acc);
+    if ((threadIdx.x & 31) == 0) {
+        red_d[threadIdx.x >> 5] = acc;
+    }
+    __syncthreads();
+    double S = 0.0;
+    for (int w = 0; w < (int) (blockDim.x >> 5); w++) {
+        S += red_d[w];
+    }
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        y[i] = __double2float_rn((double) y[i] / S);
+    }
+    if (threadIdx.x == 0 && sums != nullptr) {
+        sums[row] = S;
+    }
+}
+
+/* ----------------------------------------------------------------- launchers -- */
+
+cudaError_t launch_merge_sample(const MergeParams &p, cudaStream_t stream) {
+    const size_t cap  = (size_t) p.n_shards * (size_t) p.k_stride;
+    const size_t smem = cap * (2 * sizeof(Pair) + sizeof(float));
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(merge_sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        if (e != cudaSuccess) {
+            return e;
+        }
+    }
+    merge_sample_kernel<<<p.n_rows, 256, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_accept(const AcceptParams &p, cudaStream_t stream) {
+    accept_kernel<<<(p.n_seq + 127) / 128, 128, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_post_step(const int *slot, int n_seq, int per_seq, int first, const int *tokens, const int *counts, int *hist, int hist_cap, int *hist_len, long long *hist_total,
+                             const unsigned long long *rng_tmp, unsigned long long *rng, cudaStream_t stream) {
+    post_step_kernel<<<(n_seq + 127) / 128, 128, 0, stream>>>(slot, n_seq, per_seq, first, tokens, counts, hist, hist_cap, hist_len, hist_total, rng_tmp, rng);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_kept(const int *kept_n, const int *kept_idx, const float *kept_val, int kept_cap, int n_rows, int V, int vocab_offset, float *dense, cudaStream_t stream) {
+    cudaError_t e = cudaMemsetAsync(dense, 0, (size_t) n_rows * (size_t) V * sizeof(float), stream);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    scatter_kept_kernel<<<n_rows, 128, 0, stream>>>(kept_n, kept_idx, kept_val, kept_cap, V, vocab_offset, dense);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_softmax_rows(const float *logits, long long row_stride, int n_rows, int V, const float *temperature, float *probs, double *sums, cudaStream_t stream) {
+    softmax_rows_kernel<<<n_rows, 1024, 0, stream>>>(logits, row_stride, V, temperature, probs, sums);
+    return cudaGetLastError();
+}
+
+} /* namespace gb */

@@ -1,0 +1,109 @@
+/*
+ * sampler_device.cuh — small device helpers shared by the sampling kernels:
+ * the reference generator (src/engine/sampler.c:27-48 of geistlib), ordered
+ * keys, exact exponentials for the entries that decide a draw, warp sums and
+ * the mbarrier / bulk-copy wrappers (no cluster multicast anywhere).
+ */
+#pragma once
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "sampler_params.h"
+
+namespace gb {
+
+__device__ __forceinline__ unsigned order_key(float x) {
+    /* monotone map float -> uint32 (larger float, larger key) */
+    unsigned b = __float_as_uint(x);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ unsigned long long xorshift_next(unsigned long long &s) {
+    s ^= s >> 12;
+    s ^= s << 25;
+    s ^= s >> 27;
+    return s * 0x2545F4914F6CDD1DULL;
+}
+
+__device__ __forceinline__ float unit_from(unsigned long long r) {
+    return (float) (unsigned) (r >> 40) * (1.0f / 16777216.0f);
+}
+
+/* expf of the reference, for the few entries that decide a draw: the double
+ * exponential rounded once to binary32 (what a correctly rounded expf gives). */
+__device__ __forceinline__ float exp_exact(float a) { return __double2float_rn(exp((double) a)); }
+
+__device__ __forceinline__ float scaled_arg(float x, float m, float inv_t) {
+    return __fmul_rn(__fsub_rn(x, m), inv_t); /* two roundings, never fused */
+}
+
+__device__ __forceinline__ bool pair_before(float av, int ai, float bv, int bi) {
+    return av > bv || (av == bv && ai < bi);
+}
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    }
+    return v;
+}
+
+__device__ __forceinline__ long long warp_sum_ll(long long v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    }
+    return v;
+}
+
+/* mbarrier + bulk copy (global -> this CTA's shared memory, no multicast) */
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, unsigned bytes, unsigned long long *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+    return ok != 0;
+}
+
+/* Bounded wait. Returns false when the copy never signalled. */
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long *bar, unsigned parity) {
+    for (int i = 0; i < (1 << 20); i++) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+    }
+    return false;
+}
+
+
+/* (key, id) packed so that a larger word comes earlier in (key desc, id asc). */
+__device__ __forceinline__ unsigned long long composite(unsigned key, int gid, int idx_bits) {
+    const unsigned long long mask = (1ull << idx_bits) - 1ull;
+    return ((unsigned long long) key << idx_bits) | (mask - (unsigned long long) gid);
+}
+
+} /* namespace gb */

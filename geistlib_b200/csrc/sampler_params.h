@@ -7,28 +7,45 @@
 
 namespace gb {
 
-constexpr int kThreads      = 512;            /* threads per CTA */
-constexpr int kWarps        = kThreads / 32;  /* 16 */
-constexpr int kMaxCluster   = 16;             /* CTAs that share one row */
-constexpr int kLocalCand    = 128;            /* candidates one CTA may hand to the row's finisher */
-constexpr int kGroupCap     = 512;            /* group maxima per row used for the select threshold */
+constexpr int kThreads      = 1024;           /* threads per CTA of the streaming kernel */
+constexpr int kWarps        = kThreads / 32;  /* 32 */
+constexpr int kSliceMax     = 16 * kThreads;  /* floats of one row slice: 4 float4 per thread */
+constexpr int kGroupCap     = 512;            /* group maxima per slice used for the select threshold */
 constexpr int kTopKClamp    = 8192;           /* sampler.c:212-215 */
 constexpr int kFastKMax     = 256;            /* largest k served by the threshold fast path */
-constexpr int kNucleusProbe = 32;             /* candidates the top-p fast path asks the threshold for */
-constexpr int kNucleusCap   = 64;             /* candidates the top-p fast path can hold */
+constexpr int kNucleusProbe = 32;             /* entries the top-p fast path looks at */
+constexpr int kMaxSlices    = 1024;           /* slices per row the finisher can merge */
+constexpr int kMaxStages    = 4;              /* depth of the bulk-copy ring */
+constexpr int kHistBins     = 256;            /* value histogram of the finisher's select */
 
 /* status word, one per row (bit set) */
 enum : int {
     ST_OK            = 0,
-    ST_LOAD_TIMEOUT  = 1 << 0, /* bulk copy did not signal in time; row result is invalid */
-    ST_SLOW_PATH     = 1 << 1, /* informational: the bisection path served this row */
-    ST_HIST_OVERFLOW = 1 << 2, /* more distinct history ids in a slice than the launch reserved */
+    ST_LOAD_TIMEOUT  = 1 << 0, /* a bulk copy did not signal in time; row result is invalid */
+    ST_SLOW_PATH     = 1 << 1, /* informational: the multi-pass path served this row */
+    ST_HIST_OVERFLOW = 1 << 2, /* more distinct history ids than the launch reserved */
     ST_KEPT_PARTIAL  = 1 << 3, /* kept-set list not materialised (only kept_n is valid) */
     ST_INTERNAL      = 1 << 4, /* an invariant of the select failed; row result is invalid */
 };
 
 enum : unsigned {
     F_SELECT_ONLY = 1u << 0, /* vocabulary shard: emit the row's best k (value, global id), no draw */
+};
+
+struct Pair {
+    float v;
+    int   idx;
+};
+
+/* What one CTA leaves behind for one (row, slice) work item. */
+struct __align__(16) SliceRec {
+    float  max;         /* slice maximum after penalties */
+    int    arg;         /* first global id of that maximum */
+    int    n_cand;      /* candidates this slice found (may exceed the reserved room) */
+    int    st;          /* status bits raised while processing the slice */
+    double bulk;        /* top-p: sum of expf((x - max) * inv_t) over the non-candidates */
+    double pad;
+    double seg[kWarps]; /* temperature: per-warp sums of expf((x - max) * inv_t), id order */
 };
 
 struct SampleParams {
@@ -51,7 +68,7 @@ struct SampleParams {
     const int *hist;          /* [n_seq, hist_stride] or null */
     long long  hist_stride;
     const int *hist_len;      /* [n_seq] */
-    const int *extra;         /* [n_seq, extra_stride] or null: tokens fed before row r (r+1 of them) */
+    const int *extra;         /* [n_seq, extra_stride] or null: tokens fed through a verify pass */
     long long  extra_stride;
 
     const unsigned long long *rng_in;  /* [n_seq] */
@@ -66,13 +83,28 @@ struct SampleParams {
     int   *kept_idx;  /* [n_rows, kept_cap] */
     float *kept_val;  /* [n_rows, kept_cap]: probability inside the kept set (or raw value for F_SELECT_ONLY) */
 
-    int      slice;        /* floats per CTA, multiple of 4 */
-    int      slice_bytes;  /* bytes reserved for the slice buffer (multiple of 128) */
-    int      bitmap_words; /* 0 when no history is given */
-    int      hist_cap;     /* distinct-id entries reserved per CTA */
-    int      cand_cap;     /* candidate entries reserved per CTA (>= kLocalCand) */
+    /* launch shape */
+    int      n_slices;     /* work items per row */
+    int      slice;        /* floats per slice, multiple of 4, <= kSliceMax */
+    int      stage_bytes;  /* bytes of one ring stage (multiple of 128, >= 4 * slice) */
+    int      stages;       /* ring depth, 1..kMaxStages */
+    int      bitmap_words; /* per-slice id bitmap (0 when no history is given) */
+    int      hist_cap;     /* distinct-id entries reserved per slice */
+    int      cand_cap;     /* candidates reserved per slice */
+    int      fin_cap;      /* candidates the finisher can merge per row */
     int      aligned;      /* rows start on 16-byte boundaries: bulk copies allowed */
     unsigned flags;
+
+    /* scratch in global memory (one lane of the context's scratch) */
+    int       *row_counter; /* [n_rows], zero between launches */
+    SliceRec  *recs;        /* [n_rows * n_slices] */
+    Pair      *cands;       /* [n_rows * n_slices, cand_cap] */
+    float     *gen_rows;    /* [grid, gen_stride]: a CTA's private copy of one row for the multi-pass path */
+    long long  gen_stride;  /* floats */
+    unsigned  *gen_bitmap;  /* [grid, gen_bitmap_words] */
+    int        gen_bitmap_words;
+    Pair      *gen_dlist;   /* [grid, gen_hist_cap] (id, original value) */
+    int        gen_hist_cap;
 };
 
 struct MergeParams {

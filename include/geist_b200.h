@@ -103,7 +103,12 @@ geist_token_t geist_sampler_top_p_ws(struct geist_sampler_workspace *ws, const f
 
 /* ------------------------------------------ 2. batched device entries -- */
 
-struct geist_b200_ctx; /* one per (device, caller): scratch + default stream */
+/* One per (device, caller). Owns the kernels' scratch memory (slice records,
+ * candidate lists, row counters), which grows on demand: the first call with a
+ * larger batch allocates. At most four launches of one context may be in
+ * flight on the GPU at a time (they rotate over four scratch sets); callers
+ * that need more overlap create more contexts. */
+struct geist_b200_ctx;
 
 enum geist_status geist_b200_ctx_create(int device, struct geist_b200_ctx **out);
 void              geist_b200_ctx_destroy(struct geist_b200_ctx *ctx);
@@ -296,11 +301,11 @@ enum geist_status geist_b200_batcher_verify(struct geist_b200_batcher *b, size_t
                                             int logits_on_host, int append_history, int32_t *accepted,
                                             int32_t *n_out, geist_token_t *out_tokens);
 
-/* Launch-shape report for one vocabulary size: cluster size, floats per slice,
- * shared memory per CTA, resident clusters on the current device (0 = the row
- * does not fit this path). */
-enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history, int32_t *cluster, int32_t *slice,
-                                  int32_t *smem_bytes, int32_t *resident_clusters);
+/* Launch-shape report for one vocabulary size on the current device: slices a
+ * row is cut into, floats per slice, shared memory per CTA, depth of the
+ * bulk-copy ring. GEIST_E_UNSUPPORTED when the row cannot be served. */
+enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history, int32_t *slices_per_row, int32_t *slice,
+                                  int32_t *smem_bytes, int32_t *ring_stages);
 
 #ifdef __cplusplus
 }
