@@ -7,9 +7,14 @@
 
 namespace gb {
 
-constexpr int kThreads      = 1024;           /* threads per CTA of the streaming kernel */
-constexpr int kWarps        = kThreads / 32;  /* 32 */
-constexpr int kSliceMax     = 16 * kThreads;  /* floats of one row slice: 4 float4 per thread */
+constexpr int kWorkWarps    = 14;             /* warps that stream slices */
+constexpr int kWorkThreads  = kWorkWarps * 32;
+constexpr int kFinWarps     = 4;              /* warps that finish completed rows */
+constexpr int kFinThreads   = kFinWarps * 32;
+constexpr int kQueue        = 32;             /* completed rows waiting for the finisher warps */
+constexpr int kThreads      = kWorkThreads + kFinThreads; /* 576 threads per CTA of the streaming kernel */
+constexpr int kWarps        = 32;             /* room for per-warp values in the slice record */
+constexpr int kSliceMax     = 32 * kWorkThreads; /* floats of one row slice: 8 float4 per worker thread */
 constexpr int kGroupCap     = 512;            /* group maxima per slice used for the select threshold */
 constexpr int kTopKClamp    = 8192;           /* sampler.c:212-215 */
 constexpr int kFastKMax     = 256;            /* largest k served by the threshold fast path */

@@ -2,23 +2,27 @@
  * sampler_stream.cu — the logits -> token kernel (sm_100a).
  *
  * A persistent grid (one CTA per SM) streams every logits row through the chip
- * exactly once. A row is cut into slices of at most 16384 floats; the work
- * item is (row, slice). Each CTA keeps a ring of shared-memory stages that a
- * single thread fills with bulk asynchronous copies (mbarrier-signalled, no
- * cluster multicast) a few items ahead, so HBM stays busy while the CTA
- * computes. A slice is lifted from its stage into registers (4 float4 per
- * thread) and the stage is handed back to the copy engine at once; the passes
- * over the slice (maximum, select threshold, collect / exp-sum) then run on
- * registers.
+ * exactly once. A row is cut into slices of at most 14336 floats; the work
+ * item is (row, slice). Inside a CTA the warps are specialised:
  *
- * What a slice finds goes to a small record in global scratch. The CTA that
- * completes a row (a per-row counter tells it) is the row's finisher: it
- * merges the slice records, orders the few surviving candidates, evaluates
- * their probabilities exactly and makes the draw. Nothing ever waits on
- * another CTA.
+ *   14 WORKER warps own a ring of shared-memory stages that one thread keeps
+ *   full with bulk asynchronous copies (mbarrier-signalled, no cluster
+ *   multicast) a few items ahead, so HBM stays busy while the CTA computes.
+ *   A slice is lifted from its stage into registers (8 float4 per thread),
+ *   the stage goes straight back to the copy engine, and the passes over the
+ *   slice (maximum, select threshold, collect / exp-sum) run on registers.
+ *   What a slice finds is written to a small record in global scratch, and a
+ *   per-row counter is bumped; the workers never look at the result again.
+ *
+ *   4 FINISHER warps serve the rows this CTA completed (the counter told the
+ *   worker it was the last slice): they merge the slice records, order the
+ *   few surviving candidates, evaluate their probabilities exactly and make
+ *   the draw — concurrently with the workers, which are already streaming
+ *   the next slices. Workers hand rows over through a small shared-memory
+ *   queue. Nothing ever waits on another CTA.
  *
  * Rows whose kept set is too large for this (top-k beyond the candidate room,
- * wide top-p nuclei) are served by the finisher alone with a multi-pass
+ * wide top-p nuclei) are served by the finisher warps alone with a multi-pass
  * bisection over a private copy of the row in global scratch.
  *
  * Semantics follow geistlib's CPU sampler:
@@ -40,27 +44,47 @@ struct PenEntry {
     float orig;
 };
 
+/* A set of warps that synchronise on their own named barrier. */
+struct Grp {
+    int tid, lane, warp; /* position inside the group */
+    int n, nw;           /* threads, warps */
+    int bar;             /* hardware barrier id (0 is left to __syncthreads) */
+    __device__ __forceinline__ void sync() const { asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(n) : "memory"); }
+};
+
+/* Reduction scratch, one instance per group. */
+struct __align__(16) GroupShared {
+    float     wred_f[32];
+    int       wred_a[32];
+    double    wred_d[32];
+    long long wred_l[32];
+    int       bins[kHistBins];
+    double    S;
+    float     tau;
+    float     blk_max;
+    int       blk_arg;
+    int       n_cand;
+    int       n_dlist;
+    int       n_sel;
+    int       n_border;
+    int       b_star;
+    int       n_hi;
+    int       flag;
+    int       pick;
+    int       cur_row;
+};
+
 struct __align__(16) StreamShared {
     unsigned long long full[kMaxStages];
     float              gmax[kGroupCap];
-    float              wred_f[kWarps];
-    int                wred_a[kWarps];
-    double             wred_d[kWarps];
-    long long          wred_l[kWarps];
-    int                bins[kHistBins];
-    double             S;
-    float              tau;
-    float              blk_max;
-    int                blk_arg;
-    int                n_cand;
-    int                n_dlist;
-    int                is_last;
-    int                n_sel;
-    int                n_border;
-    int                b_star;
-    int                n_hi;
-    int                flag;
-    int                pick;
+    GroupShared        wk; /* workers */
+    GroupShared        fn; /* finishers */
+    /* completed rows, worker thread 0 -> finisher warps */
+    volatile int q_rows[kQueue];
+    volatile int q_head; /* next slot the worker writes */
+    volatile int q_tail; /* next slot the finishers read */
+    volatile int q_done; /* the worker loop has ended */
+    volatile int q_error;
 };
 
 enum Mode { M_ARGMAX, M_TOPK, M_TOPP, M_TEMP };
@@ -79,15 +103,38 @@ struct RowCfg {
     int                draws_per_row;
 };
 
-__device__ __forceinline__ RowCfg row_config(const SampleParams &p, int row) {
+/* The part of a row's configuration that costs memory round trips; workers
+ * fetch it one item ahead. */
+struct RawCfg {
+    int   seq;
+    float T, top_p;
+    int   top_k, hist_len;
+    float rep, freq, pres;
+};
+
+__device__ __forceinline__ RawCfg raw_config(const SampleParams &p, int row) {
+    RawCfg    c;
+    const int seq0 = p.rows_per_seq == 1 ? row : row / p.rows_per_seq;
+    c.seq          = p.slot ? p.slot[seq0] : seq0;
+    c.T            = p.temperature[c.seq];
+    c.top_k        = p.top_k[c.seq];
+    c.top_p        = p.top_p[c.seq];
+    c.hist_len     = p.hist ? p.hist_len[c.seq] : 0;
+    c.rep          = p.rep ? p.rep[c.seq] : 1.0f;
+    c.freq         = p.freq ? p.freq[c.seq] : 0.0f;
+    c.pres         = p.pres ? p.pres[c.seq] : 0.0f;
+    return c;
+}
+
+__device__ __forceinline__ RowCfg row_config(const SampleParams &p, int row, const RawCfg &c, bool want_rng) {
     RowCfg r;
     r.row   = row;
-    r.seq0  = row / p.rows_per_seq;
+    r.seq0  = p.rows_per_seq == 1 ? row : row / p.rows_per_seq;
     r.rr    = row - r.seq0 * p.rows_per_seq;
-    r.seq   = p.slot ? p.slot[r.seq0] : r.seq0;
-    r.T     = p.temperature[r.seq];
-    r.top_k = p.top_k[r.seq];
-    r.top_p = p.top_p[r.seq];
+    r.seq   = c.seq;
+    r.T     = c.T;
+    r.top_k = c.top_k;
+    r.top_p = c.top_p;
     /* head.c:172-183 folded with the early-outs of the three sampler functions */
     if (!(r.T > 0.0f)) {
         r.mode = M_ARGMAX;
@@ -104,24 +151,24 @@ __device__ __forceinline__ RowCfg row_config(const SampleParams &p, int row) {
         r.mode = M_TOPK;
         r.k    = min(max(r.top_k, 1), min(p.V, kTopKClamp));
     }
-    r.kq = r.mode == M_TOPK ? r.k : (r.mode == M_TOPP ? min(kNucleusProbe, p.V) : 0);
+    r.kq            = r.mode == M_TOPK ? r.k : (r.mode == M_TOPP ? min(kNucleusProbe, p.V) : 0);
     r.inv_t         = r.T > 0.0f ? __fdiv_rn(1.0f, r.T) : 1.0f;
     r.draws_per_row = (r.T > 0.0f && !r.select_only) ? 1 : 0;
-    r.rng           = p.rng_in ? p.rng_in[r.seq] : 1ull;
-    for (int i = 0; i < r.rr * r.draws_per_row; i++) {
-        (void) xorshift_next(r.rng);
+    r.rng           = 1ull;
+    if (want_rng) {
+        r.rng = p.rng_in ? p.rng_in[r.seq] : 1ull;
+        for (int i = 0; i < r.rr * r.draws_per_row; i++) {
+            (void) xorshift_next(r.rng);
+        }
     }
     r.pen_on = p.hist != nullptr || p.extra != nullptr;
-    r.H      = p.hist ? (int) min((long long) max(p.hist_len[r.seq], 0), p.hist_stride) : 0;
+    r.H      = p.hist ? (int) min((long long) max(c.hist_len, 0), p.hist_stride) : 0;
     r.E      = p.extra ? r.rr : 0; /* proposals fed before this row: extra[1..rr] */
-    r.rep    = p.rep ? p.rep[r.seq] : 1.0f;
-    if (!(r.rep > 0.0f)) {
-        r.rep = 1.0f;
-    }
-    r.freq = p.freq ? p.freq[r.seq] : 0.0f;
-    r.pres = p.pres ? p.pres[r.seq] : 0.0f;
-    r.hrow = p.hist ? p.hist + (size_t) r.seq * (size_t) p.hist_stride : nullptr;
-    r.erow = p.extra ? p.extra + (size_t) r.seq0 * (size_t) p.extra_stride : nullptr; /* per call, not per slot */
+    r.rep    = c.rep > 0.0f ? c.rep : 1.0f;
+    r.freq   = c.freq;
+    r.pres   = c.pres;
+    r.hrow   = p.hist ? p.hist + (size_t) r.seq * (size_t) p.hist_stride : nullptr;
+    r.erow   = p.extra ? p.extra + (size_t) r.seq0 * (size_t) p.extra_stride : nullptr; /* per call, not per slot */
     return r;
 }
 
@@ -138,62 +185,80 @@ __device__ __forceinline__ float penalise(float x, int cnt, float rep, float fre
 /*
  * Penalties on a run of n values that hold the global ids [s0, s0 + n). `buf`
  * may be shared or global memory; `bitmap` has (n + 31) / 32 zeroed words;
- * `dlist` has room for `cap` distinct ids. All threads of the CTA call this.
+ * `dlist` has room for `cap` distinct ids; *n_dlist is zero. `first_id` is the
+ * caller's pre-fetched history id for j = g.tid (or any value when the caller
+ * did not prefetch: have_first = false). All threads of the group call this.
  * Returns status bits.
  */
-template <class Entry>
-__device__ int apply_penalties(float *buf, int s0, int n, const RowCfg &r, int V, int vocab_offset, unsigned *bitmap, Entry *dlist, int cap, int *n_dlist) {
-    const int tid = threadIdx.x;
-    int       st  = 0;
+__device__ int apply_penalties(const Grp &g, float *buf, int s0, int n, const RowCfg &r, int V, int vocab_offset, unsigned *bitmap, PenEntry *dlist, int cap, int *n_dlist,
+                               bool have_first, int first_id) {
+    int       st    = 0;
+    const int total = r.H + r.E;
+    auto      id_at = [&](int j) { return (have_first && j == g.tid) ? first_id : hist_id(r, j, vocab_offset); };
+    if (r.freq == 0.0f) {
+        /* multiplicities do not matter: the first thread to mark an id rewrites it, one pass */
+        for (int j = g.tid; j < total; j += g.n) {
+            const int id = id_at(j);
+            const int li = id - s0;
+            if (id >= 0 && id < V && li >= 0 && li < n) {
+                const unsigned bit = 1u << (li & 31);
+                if (!(atomicOr(&bitmap[li >> 5], bit) & bit)) {
+                    buf[li] = penalise(buf[li], 1, r.rep, 0.0f, r.pres);
+                }
+            }
+        }
+        g.sync();
+        return st;
+    }
     /* (a) the first thread to mark an id owns it and saves the original value */
-    for (int j = tid; j < r.H + r.E; j += kThreads) {
-        const int id = hist_id(r, j, vocab_offset);
+    for (int j = g.tid; j < total; j += g.n) {
+        const int id = id_at(j);
         const int li = id - s0;
         if (id >= 0 && id < V && li >= 0 && li < n) {
             const unsigned bit = 1u << (li & 31);
-            const unsigned old = atomicOr(&bitmap[li >> 5], bit);
-            if (!(old & bit)) {
+            if (!(atomicOr(&bitmap[li >> 5], bit) & bit)) {
                 const int pos = atomicAdd(n_dlist, 1);
                 if (pos < cap) {
-                    dlist[pos] = Entry{li, buf[li]};
+                    dlist[pos].li   = li;
+                    dlist[pos].orig = buf[li];
                 }
             }
         }
     }
-    __syncthreads();
+    g.sync();
     int nd = *n_dlist;
     if (nd > cap) { /* cannot happen when the launcher sized the room; keep the run consistent anyway */
         st |= ST_HIST_OVERFLOW;
         nd = 0;
     }
     /* (b) the slot becomes an integer counter */
-    for (int i = tid; i < nd; i += kThreads) {
+    for (int i = g.tid; i < nd; i += g.n) {
         reinterpret_cast<int *>(buf)[dlist[i].li] = 0;
     }
-    __syncthreads();
+    g.sync();
     if (nd > 0) {
-        for (int j = tid; j < r.H + r.E; j += kThreads) {
-            const int id = hist_id(r, j, vocab_offset);
+        for (int j = g.tid; j < total; j += g.n) {
+            const int id = id_at(j);
             const int li = id - s0;
             if (id >= 0 && id < V && li >= 0 && li < n) {
                 atomicAdd(reinterpret_cast<int *>(buf) + li, 1);
             }
         }
     }
-    __syncthreads();
+    g.sync();
     /* (c) one thread per distinct id writes the penalised value */
-    for (int i = tid; i < nd; i += kThreads) {
+    for (int i = g.tid; i < nd; i += g.n) {
         const int li = dlist[i].li;
         buf[li]      = penalise(dlist[i].orig, reinterpret_cast<int *>(buf)[li], r.rep, r.freq, r.pres);
     }
-    __syncthreads();
+    g.sync();
     return st;
 }
 
-/* ------------------------------------------------------- block reductions -- */
+/* ------------------------------------------------------- group reductions -- */
 
-__device__ __forceinline__ void block_argmax(StreamShared *sh, float &v, int &a) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+/* (max, first id) over the group; every thread gets the result. */
+__device__ __forceinline__ void group_argmax(const Grp &g, GroupShared *sh, float &v, int &a) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, v, o);
@@ -203,14 +268,15 @@ __device__ __forceinline__ void block_argmax(StreamShared *sh, float &v, int &a)
             a = oa;
         }
     }
-    if (lane == 0) {
-        sh->wred_f[warp] = v;
-        sh->wred_a[warp] = a;
+    g.sync(); /* earlier readers of the scratch are done */
+    if (g.lane == 0) {
+        sh->wred_f[g.warp] = v;
+        sh->wred_a[g.warp] = a;
     }
-    __syncthreads();
-    if (warp == 0) {
-        v = sh->wred_f[lane];
-        a = sh->wred_a[lane];
+    g.sync();
+    if (g.warp == 0) {
+        v = g.lane < g.nw ? sh->wred_f[g.lane] : -CUDART_INF_F;
+        a = g.lane < g.nw ? sh->wred_a[g.lane] : 0x7fffffff;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, v, o);
@@ -220,44 +286,58 @@ __device__ __forceinline__ void block_argmax(StreamShared *sh, float &v, int &a)
                 a = oa;
             }
         }
-        if (lane == 0) {
+        if (g.lane == 0) {
             sh->blk_max = v;
             sh->blk_arg = a;
         }
     }
-    __syncthreads();
+    g.sync();
     v = sh->blk_max;
     a = sh->blk_arg;
 }
 
-/* Every thread gets the same total (fixed order of additions). */
-__device__ __forceinline__ double block_sum_d(StreamShared *sh, double v) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    v = warp_sum_d(v);
-    __syncthreads(); /* the previous result has been read */
-    if (lane == 0) {
-        sh->wred_d[warp] = v;
-    }
-    __syncthreads();
-    double t = 0.0;
+/* Maximum over the group (values only); one barrier less than group_argmax. */
+__device__ __forceinline__ float group_max(const Grp &g, GroupShared *sh, float v) {
 #pragma unroll
-    for (int w = 0; w < kWarps; w++) {
+    for (int o = 16; o > 0; o >>= 1) {
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    }
+    g.sync();
+    if (g.lane == 0) {
+        sh->wred_f[g.warp] = v;
+    }
+    g.sync();
+    float m = sh->wred_f[0];
+    for (int w = 1; w < g.nw; w++) {
+        m = fmaxf(m, sh->wred_f[w]);
+    }
+    return m;
+}
+
+/* Every thread gets the same total (fixed order of additions). */
+__device__ __forceinline__ double group_sum_d(const Grp &g, GroupShared *sh, double v) {
+    v = warp_sum_d(v);
+    g.sync(); /* the previous result has been read */
+    if (g.lane == 0) {
+        sh->wred_d[g.warp] = v;
+    }
+    g.sync();
+    double t = 0.0;
+    for (int w = 0; w < g.nw; w++) {
         t += sh->wred_d[w];
     }
     return t;
 }
 
-__device__ __forceinline__ long long block_sum_ll(StreamShared *sh, long long v) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__device__ __forceinline__ long long group_sum_ll(const Grp &g, GroupShared *sh, long long v) {
     v = warp_sum_ll(v);
-    __syncthreads();
-    if (lane == 0) {
-        sh->wred_l[warp] = v;
+    g.sync();
+    if (g.lane == 0) {
+        sh->wred_l[g.warp] = v;
     }
-    __syncthreads();
+    g.sync();
     long long t = 0;
-#pragma unroll
-    for (int w = 0; w < kWarps; w++) {
+    for (int w = 0; w < g.nw; w++) {
         t += sh->wred_l[w];
     }
     return t;
@@ -270,65 +350,64 @@ __device__ __forceinline__ long long block_sum_ll(StreamShared *sh, long long v)
  * (value desc, id asc) order to sorted[0..kq). A histogram over the
  * candidates' key range finds the bin that holds the kq-th entry; entries in
  * higher bins are in, only that one bin is ranked exactly. tmp has room for
- * `total` pairs. Called by the whole CTA.
+ * `total` pairs. Called by the whole group.
  */
-__device__ void select_sorted(StreamShared *sh, const Pair *cand, int total, int kq, Pair *tmp, Pair *sorted) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    unsigned  lo = 0xffffffffu, hi = 0u;
-    for (int i = tid; i < total; i += kThreads) {
+__device__ void select_sorted(const Grp &g, GroupShared *sh, const Pair *cand, int total, int kq, Pair *tmp, Pair *sorted) {
+    unsigned lo = 0xffffffffu, hi = 0u;
+    for (int i = g.tid; i < total; i += g.n) {
         const unsigned key = order_key(cand[i].v);
         lo                 = min(lo, key);
         hi                 = max(hi, key);
     }
     lo = __reduce_min_sync(0xffffffffu, lo);
     hi = __reduce_max_sync(0xffffffffu, hi);
-    __syncthreads();
-    if (lane == 0) {
-        sh->wred_a[warp]                               = (int) lo;
-        reinterpret_cast<unsigned *>(sh->wred_f)[warp] = hi;
+    g.sync();
+    if (g.lane == 0) {
+        sh->wred_a[g.warp]                               = (int) lo;
+        reinterpret_cast<unsigned *>(sh->wred_f)[g.warp] = hi;
     }
-    for (int i = tid; i < kHistBins; i += kThreads) {
+    for (int i = g.tid; i < kHistBins; i += g.n) {
         sh->bins[i] = 0;
     }
-    if (tid == 0) {
+    if (g.tid == 0) {
         sh->n_sel    = 0;
         sh->n_border = 0;
         sh->b_star   = 0;
         sh->n_hi     = 0;
     }
-    __syncthreads();
+    g.sync();
     lo = 0xffffffffu;
     hi = 0u;
-    for (int w = 0; w < kWarps; w++) {
+    for (int w = 0; w < g.nw; w++) {
         lo = min(lo, (unsigned) sh->wred_a[w]);
         hi = max(hi, reinterpret_cast<unsigned *>(sh->wred_f)[w]);
     }
     const unsigned range = hi >= lo ? hi - lo : 0u;
     const int      shift = max(0, (32 - __clz(range)) - 8); /* (range >> shift) < 256 */
-    for (int i = tid; i < total; i += kThreads) {
+    for (int i = g.tid; i < total; i += g.n) {
         atomicAdd(&sh->bins[(order_key(cand[i].v) - lo) >> shift], 1);
     }
-    __syncthreads();
-    if (warp == 0) {
+    g.sync();
+    if (g.warp == 0) {
         /* b* = largest bin with count(bins >= b*) >= kq; lane l owns bins [8l, 8l+8) */
         int mine = 0;
 #pragma unroll
         for (int q = 0; q < 8; q++) {
-            mine += sh->bins[8 * lane + q];
+            mine += sh->bins[8 * g.lane + q];
         }
         int above = 0; /* entries owned by higher lanes */
         for (int l = 31; l >= 1; l--) {
             const int c = __shfl_sync(0xffffffffu, mine, l);
-            if (lane < l) {
+            if (g.lane < l) {
                 above += c;
             }
         }
         if (above < kq && above + mine >= kq) {
             int acc = above;
             for (int q = 7; q >= 0; q--) {
-                const int c = sh->bins[8 * lane + q];
+                const int c = sh->bins[8 * g.lane + q];
                 if (acc + c >= kq) {
-                    sh->b_star = 8 * lane + q;
+                    sh->b_star = 8 * g.lane + q;
                     sh->n_hi   = acc;
                     break;
                 }
@@ -336,10 +415,10 @@ __device__ void select_sorted(StreamShared *sh, const Pair *cand, int total, int
             }
         }
     }
-    __syncthreads();
+    g.sync();
     const int b_star = sh->b_star, n_hi = sh->n_hi;
     /* entries above the bin fill tmp from the front, the bin's entries from the back */
-    for (int i = tid; i < total; i += kThreads) {
+    for (int i = g.tid; i < total; i += g.n) {
         const int bin = (int) ((order_key(cand[i].v) - lo) >> shift);
         if (bin > b_star) {
             tmp[atomicAdd(&sh->n_sel, 1)] = cand[i];
@@ -347,10 +426,10 @@ __device__ void select_sorted(StreamShared *sh, const Pair *cand, int total, int
             tmp[total - 1 - atomicAdd(&sh->n_border, 1)] = cand[i];
         }
     }
-    __syncthreads();
+    g.sync();
     const int nb   = sh->n_border;
     const int need = kq - n_hi;
-    for (int i = tid; i < nb; i += kThreads) {
+    for (int i = g.tid; i < nb; i += g.n) {
         const Pair me   = tmp[total - 1 - i];
         int        rank = 0;
         for (int j = 0; j < nb; j++) {
@@ -361,7 +440,7 @@ __device__ void select_sorted(StreamShared *sh, const Pair *cand, int total, int
             sorted[n_hi + rank] = me;
         }
     }
-    for (int i = tid; i < n_hi; i += kThreads) {
+    for (int i = g.tid; i < n_hi; i += g.n) {
         const Pair me   = tmp[i];
         int        rank = 0;
         for (int j = 0; j < n_hi; j++) {
@@ -369,42 +448,42 @@ __device__ void select_sorted(StreamShared *sh, const Pair *cand, int total, int
         }
         sorted[rank] = me;
     }
-    __syncthreads();
+    g.sync();
 }
 
 /* ------------------------------------------------- multi-pass path (finisher) -- */
 
 template <class F>
-__device__ __forceinline__ void row_sweep(const float *row, int V, F &&f) {
+__device__ __forceinline__ void row_sweep(const Grp &g, const float *row, int V, F &&f) {
     const int     V4 = V >> 2;
     const float4 *p4 = reinterpret_cast<const float4 *>(row);
-    for (int j = threadIdx.x; j < V4; j += kThreads) {
+    for (int j = g.tid; j < V4; j += g.n) {
         const float4 x = p4[j];
         f(x.x, 4 * j);
         f(x.y, 4 * j + 1);
         f(x.z, 4 * j + 2);
         f(x.w, 4 * j + 3);
     }
-    for (int i = (V4 << 2) + threadIdx.x; i < V; i += kThreads) {
+    for (int i = (V4 << 2) + g.tid; i < V; i += g.n) {
         f(row[i], i);
     }
 }
 
 template <class F>
-__device__ __forceinline__ void row_rewrite(float *row, int V, F &&f) {
-    for (int i = threadIdx.x; i < V; i += kThreads) {
+__device__ __forceinline__ void row_rewrite(const Grp &g, float *row, int V, F &&f) {
+    for (int i = g.tid; i < V; i += g.n) {
         row[i] = f(row[i], i);
     }
 }
 
 /* Largest composite word t such that at least `want` entries are >= t. */
-__device__ unsigned long long bisect_rank(StreamShared *sh, const float *row, int V, int idx_bits, long long want) {
+__device__ unsigned long long bisect_rank(const Grp &g, GroupShared *sh, const float *row, int V, int idx_bits, long long want) {
     unsigned long long prefix = 0;
     for (int bit = 31 + idx_bits; bit >= 0; bit--) {
         const unsigned long long t   = prefix | (1ull << bit);
         long long                cnt = 0;
-        row_sweep(row, V, [&](float x, int i) { cnt += composite(order_key(x), i, idx_bits) >= t ? 1 : 0; });
-        if (block_sum_ll(sh, cnt) >= want) {
+        row_sweep(g, row, V, [&](float x, int i) { cnt += composite(order_key(x), i, idx_bits) >= t ? 1 : 0; });
+        if (group_sum_ll(g, sh, cnt) >= want) {
             prefix = t;
         }
     }
@@ -413,17 +492,17 @@ __device__ unsigned long long bisect_rank(StreamShared *sh, const float *row, in
 
 /* Largest composite word t with mass{word >= t} >= target (inclusive) or > target. */
 template <class KeyF, class MassF>
-__device__ unsigned long long bisect_mass(StreamShared *sh, const float *row, int V, int idx_bits, double target, bool inclusive, KeyF &&key, MassF &&mass) {
+__device__ unsigned long long bisect_mass(const Grp &g, GroupShared *sh, const float *row, int V, int idx_bits, double target, bool inclusive, KeyF &&key, MassF &&mass) {
     unsigned long long prefix = 0;
     for (int bit = 31 + idx_bits; bit >= 0; bit--) {
         const unsigned long long t = prefix | (1ull << bit);
         double                   m = 0.0;
-        row_sweep(row, V, [&](float x, int i) {
+        row_sweep(g, row, V, [&](float x, int i) {
             if (composite(key(x), i, idx_bits) >= t) {
                 m += mass(x, i);
             }
         });
-        const double tot = block_sum_d(sh, m);
+        const double tot = group_sum_d(g, sh, m);
         if (inclusive ? (tot >= target) : (tot > target)) {
             prefix = t;
         }
@@ -431,43 +510,52 @@ __device__ unsigned long long bisect_mass(StreamShared *sh, const float *row, in
     return prefix;
 }
 
-/* The finisher alone serves a row whose kept set does not fit the fast path. */
-__device__ int multipass_row(const SampleParams &p, StreamShared *sh, RowCfg &r, float row_max, int row_arg) {
-    const int   tid      = threadIdx.x;
-    const int   V        = p.V;
-    const int   idx_bits = 32 - __clz(max(V - 1, 1));
-    int         st       = ST_SLOW_PATH;
-    float      *g        = p.gen_rows + (size_t) blockIdx.x * (size_t) p.gen_stride;
-    const float *src     = p.logits + (size_t) r.row * (size_t) p.row_stride;
-    int        *kept_i   = p.kept_cap > 0 ? p.kept_idx + (size_t) r.row * (size_t) p.kept_cap : nullptr;
-    float      *kept_v   = p.kept_cap > 0 ? p.kept_val + (size_t) r.row * (size_t) p.kept_cap : nullptr;
+/* The finisher warps alone serve a row whose kept set does not fit the fast path. */
+__device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, float row_max, int row_arg) {
+    const int    V        = p.V;
+    const int    idx_bits = 32 - __clz(max(V - 1, 1));
+    int          st       = ST_SLOW_PATH;
+    float       *gr       = p.gen_rows + (size_t) blockIdx.x * (size_t) p.gen_stride;
+    const float *src      = p.logits + (size_t) r.row * (size_t) p.row_stride;
+    int         *kept_i   = p.kept_cap > 0 ? p.kept_idx + (size_t) r.row * (size_t) p.kept_cap : nullptr;
+    float       *kept_v   = p.kept_cap > 0 ? p.kept_val + (size_t) r.row * (size_t) p.kept_cap : nullptr;
     /* private copy of the row, penalties applied once */
-    for (int i = tid; i < V; i += kThreads) {
-        g[i] = src[i];
+    for (int i = g.tid; i < V; i += g.n) {
+        gr[i] = src[i];
     }
     if (r.pen_on) {
         unsigned *bm = p.gen_bitmap + (size_t) blockIdx.x * (size_t) p.gen_bitmap_words;
-        for (int i = tid; i < p.gen_bitmap_words; i += kThreads) {
+        for (int i = g.tid; i < p.gen_bitmap_words; i += g.n) {
             bm[i] = 0u;
         }
-        if (tid == 0) {
+        if (g.tid == 0) {
             sh->n_dlist = 0;
         }
-        __syncthreads();
-        st |= apply_penalties(g, 0, V, r, V, p.vocab_offset, bm, reinterpret_cast<PenEntry *>(p.gen_dlist + (size_t) blockIdx.x * (size_t) p.gen_hist_cap), p.gen_hist_cap,
-                              &sh->n_dlist);
+        g.sync();
+        st |= apply_penalties(g, gr, 0, V, r, V, p.vocab_offset, bm, reinterpret_cast<PenEntry *>(p.gen_dlist + (size_t) blockIdx.x * (size_t) p.gen_hist_cap), p.gen_hist_cap,
+                              &sh->n_dlist, false, 0);
     } else {
-        __syncthreads();
+        g.sync();
     }
+    /* the fast path's slice records need not carry the maximum: take it from the copy */
+    row_max = -CUDART_INF_F;
+    row_arg = 0x7fffffff;
+    row_sweep(g, gr, V, [&](float x, int i) {
+        if (row_arg == 0x7fffffff || pair_before(x, i, row_max, row_arg)) {
+            row_max = x;
+            row_arg = i;
+        }
+    });
+    group_argmax(g, sh, row_max, row_arg);
     if (r.mode == M_TOPK) {
-        const unsigned long long t_set  = bisect_rank(sh, g, V, idx_bits, (long long) r.k);
+        const unsigned long long t_set  = bisect_rank(g, sh, gr, V, idx_bits, (long long) r.k);
         auto                     in_set = [&](float x, int i) { return composite(order_key(x), i, idx_bits) >= t_set; };
         if (r.select_only) {
-            if (tid == 0) {
+            if (g.tid == 0) {
                 sh->n_sel = 0;
             }
-            __syncthreads();
-            row_sweep(g, V, [&](float x, int i) {
+            g.sync();
+            row_sweep(g, gr, V, [&](float x, int i) {
                 if (in_set(x, i)) {
                     const int pos = atomicAdd(&sh->n_sel, 1);
                     if (pos < p.kept_cap) {
@@ -476,33 +564,33 @@ __device__ int multipass_row(const SampleParams &p, StreamShared *sh, RowCfg &r,
                     }
                 }
             });
-            if (tid == 0) {
+            if (g.tid == 0) {
                 p.kept_n[r.row] = r.k;
                 p.tokens[r.row] = row_arg + p.vocab_offset;
             }
         } else {
             auto   qof = [&](float x) { return (double) exp_exact(scaled_arg(x, row_max, r.inv_t)); };
             double m   = 0.0;
-            row_sweep(g, V, [&](float x, int i) {
+            row_sweep(g, gr, V, [&](float x, int i) {
                 if (in_set(x, i)) {
                     m += qof(x);
                 }
             });
-            const double S = block_sum_d(sh, m);
+            const double S = group_sum_d(g, sh, m);
             const double u = (double) unit_from(xorshift_next(r.rng)) * S;
             /* the pick is the earliest walk position whose running sum exceeds u: the largest
              * word t with mass{word >= t} > u */
             unsigned long long t_pick = bisect_mass(
-                    sh, g, V, idx_bits, u, false, [&](float x) { return order_key(x); }, [&](float x, int i) { return in_set(x, i) ? qof(x) : 0.0; });
+                    g, sh, gr, V, idx_bits, u, false, [&](float x) { return order_key(x); }, [&](float x, int i) { return in_set(x, i) ? qof(x) : 0.0; });
             if (t_pick < t_set) {
                 t_pick = t_set;
             }
-            row_sweep(g, V, [&](float x, int i) {
+            row_sweep(g, gr, V, [&](float x, int i) {
                 if (composite(order_key(x), i, idx_bits) == t_pick) {
                     p.tokens[r.row] = i + p.vocab_offset;
                 }
             });
-            if (tid == 0 && p.kept_cap > 0) {
+            if (g.tid == 0 && p.kept_cap > 0) {
                 p.kept_n[r.row] = r.k;
             }
             if (p.kept_cap > 0) {
@@ -512,62 +600,61 @@ __device__ int multipass_row(const SampleParams &p, StreamShared *sh, RowCfg &r,
     } else {
         /* top-p with any nucleus size: the copy becomes e_i, then p_i (sampler.c:245-255) */
         double acc = 0.0;
-        row_rewrite(g, V, [&](float x, int) {
+        row_rewrite(g, gr, V, [&](float x, int) {
             const float e = expf(scaled_arg(x, row_max, r.inv_t));
             acc += (double) e;
             return e;
         });
-        const double S = block_sum_d(sh, acc);
-        row_rewrite(g, V, [&](float e, int) { return __double2float_rn((double) e / S); });
-        __syncthreads();
+        const double S = group_sum_d(g, sh, acc);
+        row_rewrite(g, gr, V, [&](float e, int) { return __double2float_rn((double) e / S); });
+        g.sync();
         auto keyf  = [](float pv) { return __float_as_uint(pv); }; /* p >= 0: the bits are ordered */
         auto massf = [](float pv, int) { return (double) pv; };
         /* cutoff: first walk position whose running sum reaches top_p, inclusive */
-        const unsigned long long t_cut = bisect_mass(sh, g, V, idx_bits, (double) r.top_p, true, keyf, massf);
+        const unsigned long long t_cut = bisect_mass(g, sh, gr, V, idx_bits, (double) r.top_p, true, keyf, massf);
         double                   nm    = 0.0;
         long long                ncnt  = 0;
-        row_sweep(g, V, [&](float pv, int i) {
+        row_sweep(g, gr, V, [&](float pv, int i) {
             if (composite(keyf(pv), i, idx_bits) >= t_cut) {
                 nm += (double) pv;
                 ncnt++;
             }
         });
-        const double       N      = block_sum_d(sh, nm);
-        const long long    cut    = block_sum_ll(sh, ncnt);
+        const double       N      = group_sum_d(g, sh, nm);
+        const long long    cut    = group_sum_ll(g, sh, ncnt);
         const double       u      = (double) unit_from(xorshift_next(r.rng)) * N;
-        unsigned long long t_pick = bisect_mass(sh, g, V, idx_bits, u, false, keyf, massf);
+        unsigned long long t_pick = bisect_mass(g, sh, gr, V, idx_bits, u, false, keyf, massf);
         if (t_pick < t_cut) {
             t_pick = t_cut; /* default: the last nucleus entry (sampler.c:292) */
         }
-        row_sweep(g, V, [&](float pv, int i) {
+        row_sweep(g, gr, V, [&](float pv, int i) {
             if (composite(keyf(pv), i, idx_bits) == t_pick) {
                 p.tokens[r.row] = i + p.vocab_offset;
             }
         });
-        if (tid == 0 && p.kept_cap > 0) {
+        if (g.tid == 0 && p.kept_cap > 0) {
             p.kept_n[r.row] = (int) cut;
         }
         if (p.kept_cap > 0) {
             st |= ST_KEPT_PARTIAL;
         }
     }
-    __syncthreads();
+    g.sync();
     return st;
 }
-
 
 /* ---------------------------------------------------------------- finisher -- */
 
 struct FinBuffers {
     Pair     *fcand, *ftmp, *fsort;
     float    *fq;
-    unsigned *bitmap;
+    unsigned *bitmap; /* 16 words: ids of one walked segment */
     PenEntry *dlist;
+    int       dlist_cap;
 };
 
-/* Runs in the CTA that completed the row. Returns status bits for the row. */
-__device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, const FinBuffers &fb) {
-    const int       tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+/* Runs in the finisher warps of the CTA that completed the row. Returns the row's status bits. */
+__device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, const FinBuffers &fb) {
     const int       row    = r.row;
     const SliceRec *recs   = p.recs + (size_t) row * (size_t) p.n_slices;
     int            *kept_i = p.kept_cap > 0 ? p.kept_idx + (size_t) row * (size_t) p.kept_cap : nullptr;
@@ -578,7 +665,7 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
     float row_max = -CUDART_INF_F;
     int   row_arg = 0x7fffffff;
     int   rst     = 0;
-    for (int cc = tid; cc < p.n_slices; cc += kThreads) {
+    for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
         const float m = __ldcg(&recs[cc].max);
         const int   a = __ldcg(&recs[cc].arg);
         rst |= __ldcg(&recs[cc].st);
@@ -588,17 +675,17 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
         }
     }
     rst = __reduce_or_sync(0xffffffffu, rst);
-    __syncthreads();
-    if (lane == 0) {
-        sh->wred_l[warp] = rst;
+    g.sync();
+    if (g.lane == 0) {
+        sh->wred_l[g.warp] = rst;
     }
-    block_argmax(sh, row_max, row_arg);
-    for (int w = 0; w < kWarps; w++) {
+    group_argmax(g, sh, row_max, row_arg);
+    for (int w = 0; w < g.nw; w++) {
         st |= (int) sh->wred_l[w];
     }
 
     if (r.mode == M_ARGMAX) {
-        if (tid == 0) {
+        if (g.tid == 0) {
             p.tokens[row] = row_arg + p.vocab_offset;
             if (p.kept_cap > 0) {
                 p.kept_n[row] = 0;
@@ -609,59 +696,61 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
 
     if (r.mode == M_TEMP) {
         /* segment sums, rescaled from their slice maximum to the row maximum, in id order */
-        const int nseg   = p.n_slices * kWarps;
+        const int nseg   = p.n_slices * kWorkWarps;
         auto      seg_at = [&](int t) {
-            const int cc = t / kWarps;
-            return exp(((double) __ldcg(&recs[cc].max) - (double) row_max) * (double) r.inv_t) * __ldcg(&recs[cc].seg[t % kWarps]);
+            const int   cc = t / kWorkWarps;
+            const float m  = __ldcg(&recs[cc].max);
+            const double sc = m == -CUDART_INF_F ? 0.0 : exp(((double) m - (double) row_max) * (double) r.inv_t);
+            return sc * __ldcg(&recs[cc].seg[t % kWorkWarps]);
         };
         double part = 0.0;
-        for (int t = tid; t < nseg; t += kThreads) {
+        for (int t = g.tid; t < nseg; t += g.n) {
             part += seg_at(t);
         }
-        const double S     = block_sum_d(sh, part);
+        const double S     = group_sum_d(g, sh, part);
         const double u     = (double) unit_from(xorshift_next(r.rng)) * S;
         double       carry = 0.0;
         int          found = -1;
         double       fbase = -CUDART_INF; /* nothing crosses: the walk ends on its last id */
-        for (int t0 = 0; t0 < nseg; t0 += kThreads) {
-            const int    t    = t0 + tid;
+        for (int t0 = 0; t0 < nseg; t0 += g.n) {
+            const int    t    = t0 + g.tid;
             const double val  = t < nseg ? seg_at(t) : 0.0;
             double       incl = val;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const double up = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) {
+                if (g.lane >= o) {
                     incl += up;
                 }
             }
-            __syncthreads();
-            if (lane == 31) {
-                sh->wred_d[warp] = incl;
+            g.sync();
+            if (g.lane == 31) {
+                sh->wred_d[g.warp] = incl;
             }
-            if (tid == 0) {
+            if (g.tid == 0) {
                 sh->pick = 0x7fffffff;
             }
-            __syncthreads();
+            g.sync();
             double woff = carry;
-            for (int w = 0; w < warp; w++) {
+            for (int w = 0; w < g.warp; w++) {
                 woff += sh->wred_d[w];
             }
             incl += woff;
             if (t < nseg && u < incl) {
                 atomicMin(&sh->pick, t);
             }
-            __syncthreads();
+            g.sync();
             const int pk = sh->pick;
             if (pk != 0x7fffffff) {
                 if (t == pk) {
                     sh->S = incl - val;
                 }
-                __syncthreads();
+                g.sync();
                 found = pk;
                 fbase = sh->S;
                 break;
             }
-            for (int w = 0; w < kWarps; w++) {
+            for (int w = 0; w < g.nw; w++) {
                 carry += sh->wred_d[w];
             }
         }
@@ -669,40 +758,40 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
             found = nseg - 1;
         }
         /* the crossing segment, re-read from the row (L2), penalised, walked with the row maximum */
-        const int    cc     = found / kWarps, w = found % kWarps;
-        const int    s0c    = cc * p.slice;
-        const int    nc     = max(0, min(p.slice, p.V - s0c));
-        const int    nv4c   = (nc + 3) >> 2;
-        const int    Lc     = (nv4c + kWarps - 1) / kWarps;
-        const int    e0     = min(4 * w * Lc, nc);
-        const int    e1     = min(4 * min((w + 1) * Lc, nv4c), nc);
-        const int    seg_n  = max(e1 - e0, 0);
-        float       *wbuf   = reinterpret_cast<float *>(fb.fcand); /* >= 512 floats */
-        const float *src    = p.logits + (size_t) row * (size_t) p.row_stride + s0c + e0;
-        __syncthreads();
-        for (int i = tid; i < seg_n; i += kThreads) {
+        const int    cc    = found / kWorkWarps, w = found % kWorkWarps;
+        const int    s0c   = cc * p.slice;
+        const int    nc    = max(0, min(p.slice, p.V - s0c));
+        const int    nv4c  = (nc + 3) >> 2;
+        const int    Lc    = (nv4c + kWorkWarps - 1) / kWorkWarps;
+        const int    e0    = min(4 * w * Lc, nc);
+        const int    e1    = min(4 * min((w + 1) * Lc, nv4c), nc);
+        const int    seg_n = max(e1 - e0, 0);
+        float       *wbuf  = reinterpret_cast<float *>(fb.fcand); /* >= 512 floats */
+        const float *src   = p.logits + (size_t) row * (size_t) p.row_stride + s0c + e0;
+        g.sync();
+        for (int i = g.tid; i < seg_n; i += g.n) {
             wbuf[i] = src[i];
         }
         if (r.pen_on) {
-            for (int i = tid; i < (seg_n + 31) / 32; i += kThreads) {
+            for (int i = g.tid; i < 16; i += g.n) {
                 fb.bitmap[i] = 0u;
             }
-            if (tid == 0) {
+            if (g.tid == 0) {
                 sh->n_dlist = 0;
             }
         }
-        __syncthreads();
+        g.sync();
         if (r.pen_on && seg_n > 0) {
-            st |= apply_penalties(wbuf, s0c + e0, seg_n, r, p.V, p.vocab_offset, fb.bitmap, fb.dlist, p.hist_cap, &sh->n_dlist);
+            st |= apply_penalties(g, wbuf, s0c + e0, seg_n, r, p.V, p.vocab_offset, fb.bitmap, fb.dlist, fb.dlist_cap, &sh->n_dlist, false, 0);
         }
-        if (warp == 0) {
+        if (g.warp == 0) {
             int    hit  = -1;
             double base = fbase;
             for (int c0 = 0; c0 < seg_n && hit < 0; c0 += 128) {
                 float ev[4];
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    const int i = c0 + 4 * lane + q;
+                    const int i = c0 + 4 * g.lane + q;
                     ev[q]       = i < seg_n ? expf(scaled_arg(wbuf[i], row_max, r.inv_t)) : 0.0f;
                 }
                 const double mine = ((double) ev[0] + (double) ev[1]) + ((double) ev[2] + (double) ev[3]);
@@ -710,7 +799,7 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
                     const double up = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) {
+                    if (g.lane >= o) {
                         incl += up;
                     }
                 }
@@ -718,14 +807,14 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
                 if (ball != 0u) {
                     const int srcl = __ffs(ball) - 1;
                     int       f    = -1;
-                    if (lane == srcl) {
+                    if (g.lane == srcl) {
                         double a = base + (incl - mine);
-                        f        = c0 + 4 * lane + 3;
+                        f        = c0 + 4 * g.lane + 3;
 #pragma unroll
                         for (int q = 0; q < 4; q++) {
                             a += (double) ev[q];
                             if (u < a) {
-                                f = c0 + 4 * lane + q;
+                                f = c0 + 4 * g.lane + q;
                                 break;
                             }
                         }
@@ -737,14 +826,14 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
             if (hit < 0) {
                 hit = max(seg_n - 1, 0); /* regrouped sums can end a hair below the segment's share */
             }
-            if (lane == 0) {
+            if (g.lane == 0) {
                 p.tokens[row] = s0c + e0 + hit + p.vocab_offset;
                 if (p.kept_cap > 0) {
                     p.kept_n[row] = 0;
                 }
             }
         }
-        __syncthreads();
+        g.sync();
         return st;
     }
 
@@ -752,11 +841,11 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
     bool need_multipass = !(r.kq > 0 && r.kq <= kFastKMax) || p.n_slices > kHistBins;
     int  total          = 0;
     if (!need_multipass) {
-        __syncthreads();
-        for (int cc = tid; cc < p.n_slices; cc += kThreads) {
+        g.sync();
+        for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
             sh->bins[cc] = __ldcg(&recs[cc].n_cand);
         }
-        __syncthreads();
+        g.sync();
         for (int cc = 0; cc < p.n_slices; cc++) {
             const int nc = sh->bins[cc];
             if (nc > p.cand_cap) {
@@ -769,42 +858,43 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
         }
     }
     if (!need_multipass) {
-        for (int cc = warp; cc < p.n_slices; cc += kWarps) {
+        for (int cc = g.warp; cc < p.n_slices; cc += g.nw) {
             int off = 0;
             for (int i = 0; i < cc; i++) {
                 off += sh->bins[i];
             }
             const Pair *src = p.cands + ((size_t) row * (size_t) p.n_slices + (size_t) cc) * (size_t) p.cand_cap;
             const int   nc  = sh->bins[cc];
-            for (int i = lane; i < nc; i += 32) {
+            for (int i = g.lane; i < nc; i += 32) {
                 Pair v;
-                v.v              = __ldcg(&src[i].v);
-                v.idx            = __ldcg(&src[i].idx);
+                v.v               = __ldcg(&src[i].v);
+                v.idx             = __ldcg(&src[i].idx);
                 fb.fcand[off + i] = v;
             }
         }
-        __syncthreads();
+        g.sync();
         if (r.mode == M_TOPK) {
             const int k = r.k;
-            select_sorted(sh, fb.fcand, total, k, fb.ftmp, fb.fsort);
+            select_sorted(g, sh, fb.fcand, total, k, fb.ftmp, fb.fsort);
             if (r.select_only) {
-                for (int i = tid; i < min(k, p.kept_cap); i += kThreads) {
+                for (int i = g.tid; i < min(k, p.kept_cap); i += g.n) {
                     kept_i[i] = fb.fsort[i].idx + p.vocab_offset;
                     kept_v[i] = fb.fsort[i].v;
                 }
-                if (tid == 0) {
+                if (g.tid == 0) {
                     p.kept_n[row] = k;
                     p.tokens[row] = fb.fsort[0].idx + p.vocab_offset;
                 }
+                g.sync();
                 return st;
             }
             /* sampler.c:217-222: softmax over the k kept logits (max = the first), one draw */
             const float m = fb.fsort[0].v;
-            for (int i = tid; i < k; i += kThreads) {
+            for (int i = g.tid; i < k; i += g.n) {
                 fb.fq[i] = exp_exact(scaled_arg(fb.fsort[i].v, m, r.inv_t));
             }
-            __syncthreads();
-            if (tid == 0) {
+            g.sync();
+            if (g.tid == 0) {
                 double S = 0.0;
                 for (int i = 0; i < k; i++) {
                     S += (double) fb.fq[i];
@@ -825,15 +915,15 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
                     p.kept_n[row] = k;
                 }
             }
-            __syncthreads();
+            g.sync();
             if (p.kept_cap > 0) {
                 const double S = sh->S;
-                for (int i = tid; i < min(k, p.kept_cap); i += kThreads) {
+                for (int i = g.tid; i < min(k, p.kept_cap); i += g.n) {
                     kept_i[i] = fb.fsort[i].idx + p.vocab_offset;
                     kept_v[i] = __double2float_rn((double) fb.fq[i] / S);
                 }
             }
-            __syncthreads();
+            g.sync();
             return st;
         }
 
@@ -841,23 +931,25 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
          * to the row maximum; the rest of the row was summed per slice with expf relative to the
          * slice maximum and is rescaled here. */
         double part = 0.0;
-        for (int i = tid; i < total; i += kThreads) {
+        for (int i = g.tid; i < total; i += g.n) {
             const float e = exp_exact(scaled_arg(fb.fcand[i].v, row_max, r.inv_t));
             fb.fcand[i].v = e;
             part += (double) e;
         }
-        for (int cc = tid; cc < p.n_slices; cc += kThreads) {
-            part += exp(((double) __ldcg(&recs[cc].max) - (double) row_max) * (double) r.inv_t) * __ldcg(&recs[cc].bulk);
+        for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
+            const float  m  = __ldcg(&recs[cc].max);
+            const double sc = m == -CUDART_INF_F ? 0.0 : exp(((double) m - (double) row_max) * (double) r.inv_t);
+            part += sc * __ldcg(&recs[cc].bulk);
         }
-        const double S = block_sum_d(sh, part);
-        for (int i = tid; i < total; i += kThreads) {
+        const double S = group_sum_d(g, sh, part);
+        for (int i = g.tid; i < total; i += g.n) {
             fb.fcand[i].v = __double2float_rn((double) fb.fcand[i].v / S); /* p_i as the reference normalises it */
         }
-        __syncthreads();
+        g.sync();
         /* the walk order is (p desc, id asc); the row's kq most probable ids are all candidates */
         const int kq = min(r.kq, total);
-        select_sorted(sh, fb.fcand, total, kq, fb.ftmp, fb.fsort);
-        if (tid == 0) {
+        select_sorted(g, sh, fb.fcand, total, kq, fb.ftmp, fb.fsort);
+        if (g.tid == 0) {
             const float p_floor = fb.fsort[kq - 1].v; /* nothing outside fsort has a larger p */
             double      cum     = 0.0;
             int         cut     = -1;
@@ -900,264 +992,53 @@ __device__ int finish_row(const SampleParams &p, StreamShared *sh, RowCfg &r, co
             }
             sh->flag = ok ? 1 : 0;
         }
-        __syncthreads();
+        g.sync();
         if (sh->flag) {
             return st;
         }
-        need_multipass = true;
     }
-    __syncthreads();
-    return st | multipass_row(p, sh, r, row_max, row_arg);
+    g.sync();
+    return st | multipass_row(g, p, sh, r, row_max, row_arg);
 }
 
-/* ------------------------------------------------------------------ kernel -- */
-
-__global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid_constant__ SampleParams p) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-
-    unsigned char *ring   = smem_raw;
-    StreamShared  *sh     = reinterpret_cast<StreamShared *>(smem_raw + (size_t) p.stages * (size_t) p.stage_bytes);
-    Pair          *cstage = reinterpret_cast<Pair *>(sh + 1); /* this slice's candidates */
-    FinBuffers     fb;
-    fb.bitmap = reinterpret_cast<unsigned *>(cstage + p.cand_cap);
-    fb.dlist  = reinterpret_cast<PenEntry *>(fb.bitmap + p.bitmap_words);
-    fb.fcand  = reinterpret_cast<Pair *>(fb.dlist + p.hist_cap); /* finisher: merged candidates */
-    fb.ftmp   = fb.fcand + p.fin_cap;
-    fb.fsort  = fb.ftmp + p.fin_cap;                              /* kFastKMax entries */
-    fb.fq     = reinterpret_cast<float *>(fb.fsort + kFastKMax);  /* kFastKMax entries */
-
-    const int n_items  = p.n_rows * p.n_slices;
-    const int G        = (int) gridDim.x;
-    const int my_count = (int) blockIdx.x < n_items ? (n_items - (int) blockIdx.x + G - 1) / G : 0;
-
-    if (tid == 0) {
-        for (int s = 0; s < p.stages; s++) {
-            mbar_init(&sh->full[s], 1);
+/* The finisher warps' loop: rows arrive through the shared-memory queue. */
+__device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared *sh, const FinBuffers &fb) {
+    GroupShared *fs   = &sh->fn;
+    int          tail = 0;
+    for (;;) {
+        if (g.tid == 0) {
+            int row = -1;
+            /* bounded wait for a row or for the end of the worker loop */
+            for (long long spin = 0; spin < (1ll << 31); spin++) {
+                if (sh->q_head != tail) {
+                    row = sh->q_rows[tail % kQueue];
+                    break;
+                }
+                if (sh->q_done) {
+                    if (sh->q_head != tail) {
+                        continue;
+                    }
+                    row = -2;
+                    break;
+                }
+                __nanosleep(64);
+            }
+            if (row == -1) {
+                sh->q_error = 1; /* gave up waiting: leave */
+                row         = -2;
+            }
+            __threadfence(); /* the row's records, published by other CTAs, are visible from here on */
+            fs->cur_row = row;
         }
-    }
-    __syncthreads();
-
-    /* one thread keeps the ring full: item jj of this CTA goes to stage jj % stages */
-    auto issue = [&](int jj) {
-        const int      item  = (int) blockIdx.x + jj * G;
-        const int      row   = item / p.n_slices;
-        const int      c     = item - row * p.n_slices;
-        const int      s0    = c * p.slice;
-        const int      n     = max(0, min(p.slice, p.V - s0));
-        const unsigned bytes = (unsigned) (n & ~3) * 4u;
-        if (bytes == 0u) {
+        g.sync();
+        const int row = fs->cur_row;
+        if (row < 0) {
             return;
         }
-        const int            stage = jj % p.stages;
-        unsigned char       *dst   = ring + (size_t) stage * (size_t) p.stage_bytes;
-        const unsigned char *src   = reinterpret_cast<const unsigned char *>(p.logits + (size_t) row * (size_t) p.row_stride + s0);
-        mbar_expect_tx(&sh->full[stage], bytes);
-        for (unsigned off = 0; off < bytes; off += 32768u) {
-            bulk_g2s(dst + off, src + off, min(32768u, bytes - off), &sh->full[stage]);
-        }
-    };
-    if (tid == 0 && p.aligned) {
-        for (int jj = 0; jj < min(p.stages, my_count); jj++) {
-            issue(jj);
-        }
-    }
-    unsigned phase_bits = 0u; /* parity of the next wait, one bit per stage */
-
-    for (int j = 0; j < my_count; j++) {
-        const int item  = (int) blockIdx.x + j * G;
-        const int row   = item / p.n_slices;
-        const int c     = item - row * p.n_slices;
-        const int stage = j % p.stages;
-        float    *sl    = reinterpret_cast<float *>(ring + (size_t) stage * (size_t) p.stage_bytes);
-        const int s0    = c * p.slice;
-        const int n     = max(0, min(p.slice, p.V - s0));
-        const int nv4   = (n + 3) >> 2;
-        const int body  = p.aligned ? (n & ~3) : 0;
-        int       st    = ST_OK;
-        RowCfg    r     = row_config(p, row);
-
-        /* ---- 1. the slice arrives in its stage ---- */
-        {
-            const float *grow = p.logits + (size_t) row * (size_t) p.row_stride + s0;
-            for (int i = body + tid; i < nv4 * 4; i += kThreads) {
-                sl[i] = i < n ? grow[i] : -CUDART_INF_F;
-            }
-            if (tid == 0) {
-                sh->n_cand  = 0;
-                sh->n_dlist = 0;
-                sh->tau     = -CUDART_INF_F;
-            }
-            if (r.pen_on) {
-                for (int i = tid; i < p.bitmap_words; i += kThreads) {
-                    fb.bitmap[i] = 0u;
-                }
-            }
-            if (body > 0) {
-                const unsigned parity = (phase_bits >> stage) & 1u;
-                phase_bits ^= 1u << stage;
-                if (!mbar_wait_bounded(&sh->full[stage], parity)) {
-                    st |= ST_LOAD_TIMEOUT;
-                    (void) mbar_wait_bounded(&sh->full[stage], parity); /* a second bounded chance for the copy in flight */
-                }
-            }
-            __syncthreads();
-        }
-
-        /* ---- 2. penalties in shared memory, then the slice moves to registers ---- */
-        if (r.pen_on) {
-            st |= apply_penalties(sl, s0, n, r, p.V, p.vocab_offset, fb.bitmap, fb.dlist, p.hist_cap, &sh->n_dlist);
-        }
-        if (p.out_logits != nullptr) {
-            float *orow = p.out_logits + (size_t) row * (size_t) p.V + s0;
-            for (int i = tid; i < n; i += kThreads) {
-                orow[i] = sl[i];
-            }
-        }
-        /* warp w owns float4 [w*L, (w+1)*L) of the slice, lanes interleave: 128 consecutive ids per step */
-        const int L = (nv4 + kWarps - 1) / kWarps; /* <= 128 */
-        float4    x[4];
-        int       base4[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int  o  = lane + 32 * i;
-            const int  j4 = warp * L + o;
-            const bool ok = o < L && j4 < nv4;
-            base4[i]      = ok ? 4 * j4 : -1;
-            x[i]          = ok ? reinterpret_cast<const float4 *>(sl)[j4] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
-        }
-        __syncthreads(); /* the stage is free again */
-        if (tid == 0 && p.aligned && j + p.stages < my_count) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            issue(j + p.stages);
-        }
-
-        /* ---- 3. pass 1 on registers: maximum, its first id, group maxima ---- */
-        float bv = -CUDART_INF_F;
-        int   bi = 0x7fffffff;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float xs[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const int li = base4[i] + q;
-                if (base4[i] >= 0 && li < n && (bi == 0x7fffffff || xs[q] > bv)) {
-                    bv = xs[q];
-                    bi = s0 + li;
-                }
-            }
-        }
-        /* groups for the select threshold: 128 / 256 / 512 per slice (8 / 4 / 2 lanes each) */
-        const int  lpg      = r.kq <= 64 ? 8 : (r.kq <= 128 ? 4 : 2);
-        const int  Gs       = kThreads / lpg;
-        const bool fast_sel = r.kq > 0 && r.kq <= kFastKMax;
-        if (fast_sel) {
-            float gv = bv;
-            for (int o = 1; o < lpg; o <<= 1) {
-                gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, o));
-            }
-            if ((lane % lpg) == 0) {
-                sh->gmax[tid / lpg] = gv;
-            }
-        }
-        float smax = bv;
-        int   sarg = bi;
-        block_argmax(sh, smax, sarg); /* its barriers also publish gmax */
-
-        SliceRec *rec = p.recs + item;
-        if (r.mode == M_TEMP) {
-            /* per-warp sums of e_i relative to the SLICE maximum; the finisher rescales to the row maximum */
-            double acc = 0.0;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                if (base4[i] >= 0) {
-                    const float e0 = base4[i] + 0 < n ? expf(scaled_arg(x[i].x, smax, r.inv_t)) : 0.0f;
-                    const float e1 = base4[i] + 1 < n ? expf(scaled_arg(x[i].y, smax, r.inv_t)) : 0.0f;
-                    const float e2 = base4[i] + 2 < n ? expf(scaled_arg(x[i].z, smax, r.inv_t)) : 0.0f;
-                    const float e3 = base4[i] + 3 < n ? expf(scaled_arg(x[i].w, smax, r.inv_t)) : 0.0f;
-                    acc += ((double) e0 + (double) e1) + ((double) e2 + (double) e3);
-                }
-            }
-            acc = warp_sum_d(acc);
-            if (lane == 0) {
-                rec->seg[warp] = acc;
-            }
-        } else if (fast_sel) {
-            /* tau = kq-th largest group maximum of this slice: at least kq entries are >= tau, so the
-             * slice's share of the row's kq best is among them */
-            for (int t = tid; t < Gs; t += kThreads) {
-                const float v    = sh->gmax[t];
-                int         rank = 0;
-                for (int g4 = 0; g4 < Gs / 4; g4++) {
-                    const float4 o = reinterpret_cast<const float4 *>(sh->gmax)[g4];
-                    rank += (o.x > v || (o.x == v && 4 * g4 + 0 < t)) ? 1 : 0;
-                    rank += (o.y > v || (o.y == v && 4 * g4 + 1 < t)) ? 1 : 0;
-                    rank += (o.z > v || (o.z == v && 4 * g4 + 2 < t)) ? 1 : 0;
-                    rank += (o.w > v || (o.w == v && 4 * g4 + 3 < t)) ? 1 : 0;
-                }
-                if (rank == min(r.kq, Gs) - 1) {
-                    sh->tau = v;
-                }
-            }
-            __syncthreads();
-            const float tau  = sh->tau;
-            double      bulk = 0.0;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float xs[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
-                float       part  = 0.0f;
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int li = base4[i] + q;
-                    if (base4[i] >= 0 && li < n) {
-                        if (xs[q] >= tau) {
-                            const int pos = atomicAdd(&sh->n_cand, 1);
-                            if (pos < p.cand_cap) {
-                                cstage[pos].v   = xs[q];
-                                cstage[pos].idx = s0 + li;
-                            }
-                        } else if (r.mode == M_TOPP) {
-                            part += expf(scaled_arg(xs[q], smax, r.inv_t));
-                        }
-                    }
-                }
-                bulk += (double) part;
-            }
-            if (r.mode == M_TOPP) {
-                bulk = block_sum_d(sh, bulk);
-            } else {
-                __syncthreads();
-            }
-            const int nc = sh->n_cand;
-            Pair     *gc = p.cands + (size_t) item * (size_t) p.cand_cap;
-            for (int i = tid; i < min(nc, p.cand_cap); i += kThreads) {
-                gc[i] = cstage[i];
-            }
-            if (tid == 0) {
-                rec->n_cand = nc;
-                rec->bulk   = bulk;
-            }
-        }
-        if (tid == 0) {
-            rec->max = smax;
-            rec->arg = sarg;
-            rec->st  = st;
-        }
-
-        /* ---- 4. the CTA that completes the row finishes it ---- */
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const int old = atomicAdd(&p.row_counter[row], 1);
-            sh->is_last   = old == p.n_slices - 1 ? 1 : 0;
-        }
-        __syncthreads();
-        if (!sh->is_last) {
-            continue;
-        }
-        __threadfence();
-        const int fst = finish_row(p, sh, r, fb);
-        if (tid == 0) {
+        const RawCfg rc  = raw_config(p, row);
+        RowCfg       r   = row_config(p, row, rc, true);
+        const int    fst = finish_row(g, p, fs, r, fb);
+        if (g.tid == 0) {
             p.status[row]      = fst;
             p.row_counter[row] = 0; /* ready for the next launch */
             if (p.rng_out != nullptr && r.rr == p.rows_per_seq - 1) {
@@ -1168,8 +1049,373 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                 }
                 p.rng_out[r.seq] = s;
             }
+            tail++;
+            sh->q_tail = tail;
+        } else {
+            tail++;
         }
-        __syncthreads();
+        g.sync();
+    }
+}
+
+/* ------------------------------------------------------------------ kernel -- */
+
+__global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid_constant__ SampleParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+
+    unsigned char *ring   = smem_raw;
+    StreamShared  *sh     = reinterpret_cast<StreamShared *>(smem_raw + (size_t) p.stages * (size_t) p.stage_bytes);
+    unsigned      *bitmap = reinterpret_cast<unsigned *>(sh + 1);             /* workers: ids of the slice */
+    PenEntry      *dlist  = reinterpret_cast<PenEntry *>(bitmap + p.bitmap_words);
+    FinBuffers     fb;
+    fb.dlist_cap = min(p.hist_cap, 512);
+    fb.bitmap    = reinterpret_cast<unsigned *>(dlist + p.hist_cap);
+    fb.dlist     = reinterpret_cast<PenEntry *>(fb.bitmap + 16);
+    fb.fcand     = reinterpret_cast<Pair *>(fb.dlist + fb.dlist_cap); /* merged candidates of one row */
+    fb.ftmp      = fb.fcand + p.fin_cap;
+    fb.fsort     = fb.ftmp + p.fin_cap;                                /* kFastKMax entries */
+    fb.fq        = reinterpret_cast<float *>(fb.fsort + kFastKMax);    /* kFastKMax entries */
+
+    const int n_items  = p.n_rows * p.n_slices;
+    const int G        = (int) gridDim.x;
+    const int my_count = (int) blockIdx.x < n_items ? (n_items - (int) blockIdx.x + G - 1) / G : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; s++) {
+            mbar_init(&sh->full[s], 1);
+        }
+        sh->q_head  = 0;
+        sh->q_tail  = 0;
+        sh->q_done  = 0;
+        sh->q_error = 0;
+    }
+    __syncthreads();
+
+    if (threadIdx.x >= kWorkThreads) {
+        Grp g;
+        g.tid  = (int) threadIdx.x - kWorkThreads;
+        g.lane = g.tid & 31;
+        g.warp = g.tid >> 5;
+        g.n    = kFinThreads;
+        g.nw   = kFinWarps;
+        g.bar  = 2;
+        finisher_loop(g, p, sh, fb);
+        return;
+    }
+
+    /* ================================================================ workers == */
+    Grp g;
+    g.tid  = (int) threadIdx.x;
+    g.lane = g.tid & 31;
+    g.warp = g.tid >> 5;
+    g.n    = kWorkThreads;
+    g.nw   = kWorkWarps;
+    g.bar  = 1;
+    GroupShared *ws = &sh->wk;
+
+    /* this CTA's items are blockIdx.x + j * G; (row, slice) advance without divisions */
+    const int dr = G / p.n_slices, dc = G - dr * p.n_slices;
+    auto      advance = [&](int &row, int &c) {
+        row += dr;
+        c += dc;
+        if (c >= p.n_slices) {
+            c -= p.n_slices;
+            row++;
+        }
+    };
+
+    /* one thread keeps the ring full: the jj-th item of this CTA goes to stage jj % stages */
+    auto issue = [&](int row, int c, int stage) {
+        const int      s0    = c * p.slice;
+        const int      n     = max(0, min(p.slice, p.V - s0));
+        const unsigned bytes = (unsigned) (n & ~3) * 4u;
+        if (bytes == 0u) {
+            return;
+        }
+        unsigned char       *dst = ring + (size_t) stage * (size_t) p.stage_bytes;
+        const unsigned char *src = reinterpret_cast<const unsigned char *>(p.logits + (size_t) row * (size_t) p.row_stride + s0);
+        mbar_expect_tx(&sh->full[stage], bytes);
+        for (unsigned off = 0; off < bytes; off += 32768u) {
+            bulk_g2s(dst + off, src + off, min(32768u, bytes - off), &sh->full[stage]);
+        }
+    };
+    int row = (int) blockIdx.x / p.n_slices, c = (int) blockIdx.x - row * p.n_slices; /* current item */
+    int irow = row, ic = c, istage = 0;                                                /* next item to load (thread 0) */
+    int issued = 0;
+    if (g.tid == 0 && p.aligned) {
+        for (; issued < min(p.stages, my_count); issued++) {
+            issue(irow, ic, istage);
+            advance(irow, ic);
+            istage = istage + 1 == p.stages ? 0 : istage + 1;
+        }
+    }
+    unsigned phase_bits = 0u; /* parity of the next wait, one bit per stage */
+
+    /* worker thread 0 hands completed rows to the finisher warps, one item late, so that nobody
+     * waits for the counter's round trip */
+    int  pend_row = -1, pend_old = 0, head = 0;
+    auto hand_over = [&]() {
+        if (pend_row >= 0 && pend_old == p.n_slices - 1) {
+            for (long long spin = 0; spin < (1ll << 31) && head - sh->q_tail >= kQueue; spin++) {
+                __nanosleep(64);
+            }
+            sh->q_rows[head % kQueue] = pend_row;
+            __threadfence();
+            head++;
+            sh->q_head = head;
+        }
+        pend_row = -1;
+    };
+
+    /* configuration and this thread's history id, fetched one item ahead */
+    RawCfg nxt{};
+    int    nxt_hid = 0;
+    auto   prefetch = [&](int prow) {
+        nxt     = raw_config(p, prow);
+        nxt_hid = 0;
+        if (p.hist != nullptr || p.extra != nullptr) {
+            const int seq0 = p.rows_per_seq == 1 ? prow : prow / p.rows_per_seq;
+            const int rr   = prow - seq0 * p.rows_per_seq;
+            const int H    = p.hist ? (int) min((long long) max(nxt.hist_len, 0), p.hist_stride) : 0;
+            const int E    = p.extra ? rr : 0;
+            if (g.tid < H) {
+                nxt_hid = p.hist[(size_t) nxt.seq * (size_t) p.hist_stride + g.tid] - p.vocab_offset;
+            } else if (g.tid < H + E) {
+                nxt_hid = p.extra[(size_t) seq0 * (size_t) p.extra_stride + 1 + g.tid - H] - p.vocab_offset;
+            }
+        }
+    };
+    if (my_count > 0) {
+        prefetch(row);
+    }
+    int stage = 0;
+
+    for (int j = 0; j < my_count; j++) {
+        float       *sl   = reinterpret_cast<float *>(ring + (size_t) stage * (size_t) p.stage_bytes);
+        const int    s0   = c * p.slice;
+        const int    n    = max(0, min(p.slice, p.V - s0));
+        const int    nv4  = (n + 3) >> 2;
+        const int    body = p.aligned ? (n & ~3) : 0;
+        const int    item = row * p.n_slices + c;
+        int          st   = ST_OK;
+        const RawCfg rc   = nxt;
+        const int    hid  = nxt_hid;
+        const RowCfg r    = row_config(p, row, rc, false);
+        int          nrow = row, ncs = c;
+        advance(nrow, ncs);
+        if (j + 1 < my_count) {
+            prefetch(nrow); /* loads in flight while this item is processed */
+        }
+
+        /* ---- 1. the slice arrives in its stage; its tail is padded with -inf up to a float4 ---- */
+        {
+            const float *grow = p.logits + (size_t) row * (size_t) p.row_stride + s0;
+            for (int i = body + g.tid; i < nv4 * 4; i += g.n) {
+                sl[i] = i < n ? grow[i] : -CUDART_INF_F;
+            }
+            if (g.tid == 0) {
+                ws->n_cand  = 0;
+                ws->n_dlist = 0;
+                ws->tau     = -CUDART_INF_F;
+                ws->pick    = 0x7fffffff;
+            }
+            if (r.pen_on) {
+                for (int i = g.tid; i < p.bitmap_words; i += g.n) {
+                    bitmap[i] = 0u;
+                }
+            }
+            if (body > 0) {
+                const unsigned parity = (phase_bits >> stage) & 1u;
+                phase_bits ^= 1u << stage;
+                if (!mbar_wait_bounded(&sh->full[stage], parity)) {
+                    st |= ST_LOAD_TIMEOUT;
+                    (void) mbar_wait_bounded(&sh->full[stage], parity); /* a second bounded chance for the copy in flight */
+                }
+            }
+            g.sync();
+        }
+
+        /* ---- 2. penalties in shared memory, then the slice moves to registers ---- */
+        if (r.pen_on) {
+            st |= apply_penalties(g, sl, s0, n, r, p.V, p.vocab_offset, bitmap, dlist, p.hist_cap, &ws->n_dlist, true, hid);
+        }
+        if (p.out_logits != nullptr) {
+            float *orow = p.out_logits + (size_t) row * (size_t) p.V + s0;
+            for (int i = g.tid; i < n; i += g.n) {
+                orow[i] = sl[i];
+            }
+        }
+        /* warp w owns float4 [w*L, (w+1)*L) of the slice, lanes interleave: 128 consecutive ids per
+         * step; what a thread does not own reads as -inf, so the passes below need no bounds checks */
+        const int L      = (nv4 + kWorkWarps - 1) / kWorkWarps; /* <= 256 */
+        const int first4 = g.warp * L + g.lane;                  /* this thread's float4 are first4 + 32 i */
+        float4    x[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int  o  = g.lane + 32 * i;
+            const bool ok = o < L && first4 + 32 * i < nv4;
+            x[i]          = ok ? reinterpret_cast<const float4 *>(sl)[first4 + 32 * i] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+        }
+        g.sync(); /* the stage is free again */
+        if (g.tid == 0) {
+            if (p.aligned && issued < my_count) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue(irow, ic, stage);
+                advance(irow, ic);
+                issued++;
+            }
+            hand_over(); /* the previous item's counter has long returned */
+        }
+
+        /* ---- 3. pass 1 on registers: the thread's maximum ---- */
+        float bv = -CUDART_INF_F;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            bv = fmaxf(bv, fmaxf(fmaxf(x[i].x, x[i].y), fmaxf(x[i].z, x[i].w)));
+        }
+        /* local index of element q of float4 i */
+        auto li_of = [&](int i, int q) { return 4 * (first4 + 32 * i) + q; };
+
+        const bool fast_sel = r.kq > 0 && r.kq <= kFastKMax;
+        SliceRec  *rec      = p.recs + item;
+        float      smax     = bv;
+        int        sarg     = 0;
+        double     bulk     = 0.0;
+        bool       wrote    = false; /* this thread stored to global scratch */
+
+        if (r.mode == M_ARGMAX || (r.mode == M_TOPK && !fast_sel)) {
+            /* maximum first, then only the threads that hold it look for its first id */
+            smax = group_max(g, ws, bv);
+            if (bv == smax) {
+                int best = 0x7fffffff;
+#pragma unroll
+                for (int i = 7; i >= 0; i--) {
+                    const float xs[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+#pragma unroll
+                    for (int q = 3; q >= 0; q--) {
+                        if (xs[q] == smax && li_of(i, q) < n) {
+                            best = s0 + li_of(i, q);
+                        }
+                    }
+                }
+                atomicMin(&ws->pick, best);
+            }
+            g.sync();
+            sarg = ws->pick;
+        } else if (r.mode == M_TEMP) {
+            smax = group_max(g, ws, bv);
+            /* per-warp sums of e_i relative to the SLICE maximum; the finisher rescales to the row
+             * maximum. -inf padding gives exp(-inf) = 0. */
+            const float ref = smax == -CUDART_INF_F ? 0.0f : smax;
+            double      acc = 0.0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float e0 = expf(scaled_arg(x[i].x, ref, r.inv_t));
+                const float e1 = expf(scaled_arg(x[i].y, ref, r.inv_t));
+                const float e2 = expf(scaled_arg(x[i].z, ref, r.inv_t));
+                const float e3 = expf(scaled_arg(x[i].w, ref, r.inv_t));
+                acc += (double) ((e0 + e1) + (e2 + e3));
+            }
+            acc = warp_sum_d(acc);
+            if (g.lane == 0) {
+                rec->seg[g.warp] = acc;
+                wrote            = true;
+            }
+        } else {
+            /* top-k / top-p fast path. Groups of 4 / 2 / 1 lanes: 112 / 224 / 448 group maxima per slice.
+             * tau = kq-th largest group maximum: at least kq entries of the slice are >= tau, so the
+             * slice's share of the row's kq best is among the entries it lets through. */
+            const int lpg = r.kq <= 48 ? 4 : (r.kq <= 96 ? 2 : 1);
+            const int Gs  = kWorkThreads / lpg;
+            float     gv  = bv;
+            for (int o = 1; o < lpg; o <<= 1) {
+                gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, o));
+            }
+            if ((g.lane % lpg) == 0) {
+                sh->gmax[g.tid / lpg] = gv;
+            }
+            if (r.mode == M_TOPP) {
+                smax = group_max(g, ws, bv); /* its barriers also publish gmax */
+            } else {
+                g.sync();
+            }
+            /* rank of every group maximum: 4 threads share one value, each scans a quarter */
+            const int kth = min(r.kq, Gs) - 1;
+            for (int idx = g.tid; idx < 4 * Gs; idx += g.n) {
+                const int   t    = idx >> 2, part = idx & 3;
+                const float v    = sh->gmax[t];
+                const int   q0   = part * (Gs / 4), q1 = q0 + Gs / 4;
+                int         rank = 0;
+                for (int jg = q0; jg < q1; jg++) {
+                    const float o = sh->gmax[jg];
+                    rank += (o > v || (o == v && jg < t)) ? 1 : 0;
+                }
+                rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+                rank += __shfl_xor_sync(0xffffffffu, rank, 2);
+                if (part == 0 && rank == kth) {
+                    ws->tau = v;
+                }
+            }
+            g.sync();
+            const float tau = ws->tau;
+            Pair       *gc  = p.cands + (size_t) item * (size_t) p.cand_cap;
+            if (bv >= tau) { /* few threads hold anything that passes */
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float xs[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        if (xs[q] >= tau && li_of(i, q) < n) {
+                            const int pos = atomicAdd(&ws->n_cand, 1);
+                            if (pos < p.cand_cap) {
+                                Pair c2;
+                                c2.v    = xs[q];
+                                c2.idx  = s0 + li_of(i, q);
+                                gc[pos] = c2; /* straight to the row's scratch */
+                                wrote   = true;
+                            }
+                        }
+                    }
+                }
+            }
+            if (r.mode == M_TOPP) {
+                /* everything below tau is summed here; -inf padding adds exp(-inf) = 0 */
+                const float ref = smax == -CUDART_INF_F ? 0.0f : smax;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float e0 = x[i].x >= tau ? 0.0f : expf(scaled_arg(x[i].x, ref, r.inv_t));
+                    const float e1 = x[i].y >= tau ? 0.0f : expf(scaled_arg(x[i].y, ref, r.inv_t));
+                    const float e2 = x[i].z >= tau ? 0.0f : expf(scaled_arg(x[i].z, ref, r.inv_t));
+                    const float e3 = x[i].w >= tau ? 0.0f : expf(scaled_arg(x[i].w, ref, r.inv_t));
+                    bulk += (double) ((e0 + e1) + (e2 + e3));
+                }
+                bulk = group_sum_d(g, ws, bulk);
+            }
+        }
+
+        /* ---- 4. publish the slice; whoever completes the row queues it for its finisher warps ---- */
+        if (wrote) {
+            __threadfence();
+        }
+        g.sync();
+        if (g.tid == 0) {
+            rec->max    = smax;
+            rec->arg    = sarg;
+            rec->n_cand = ws->n_cand;
+            rec->st     = st;
+            rec->bulk   = bulk;
+            __threadfence();
+            pend_old = atomicAdd(&p.row_counter[row], 1);
+            pend_row = row;
+        }
+        row   = nrow;
+        c     = ncs;
+        stage = stage + 1 == p.stages ? 0 : stage + 1;
+    }
+    if (g.tid == 0) {
+        hand_over();
+        __threadfence();
+        sh->q_done = 1;
     }
 }
 
