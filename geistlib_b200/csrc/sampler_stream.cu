@@ -11,15 +11,16 @@
  *   A slice is lifted from its stage into registers (8 float4 per thread),
  *   the stage goes straight back to the copy engine, and the passes over the
  *   slice (maximum, select threshold, collect / exp-sum) run on registers.
- *   What a slice finds is written to a small record in global scratch, and a
- *   per-row counter is bumped; the workers never look at the result again.
+ *   Candidates go straight to global scratch; the slice's summary is handed
+ *   to the finisher warps.
  *
- *   4 FINISHER warps serve the rows this CTA completed (the counter told the
- *   worker it was the last slice): they merge the slice records, order the
- *   few surviving candidates, evaluate their probabilities exactly and make
- *   the draw — concurrently with the workers, which are already streaming
- *   the next slices. Workers hand rows over through a small shared-memory
- *   queue. Nothing ever waits on another CTA.
+ *   4 FINISHER warps take it from there, concurrently with the workers, which
+ *   are already streaming the next slices. They publish each slice's record
+ *   (a small mail queue in shared memory feeds them) and bump the row's
+ *   counter; when the counter says the row is complete they merge its slice
+ *   records, order the few surviving candidates, evaluate their
+ *   probabilities exactly and make the draw. Nothing ever waits on another
+ *   CTA, and the workers never wait on a global round trip.
  *
  * Rows whose kept set is too large for this (top-k beyond the candidate room,
  * wide top-p nuclei) are served by the finisher warps alone with a multi-pass
@@ -71,7 +72,26 @@ struct __align__(16) GroupShared {
     int       n_hi;
     int       flag;
     int       pick;
-    int       cur_row;
+    unsigned  tau_key;       /* ordered key of the select threshold */
+    int       n_done;        /* rows completed by the last batch of mail */
+    int       done_rows[32];
+};
+
+/* A work item's configuration, decoded once by worker thread 0. */
+struct ItemCfg {
+    int   row, c, s0, n;
+    int   mode, kq, pen_on, lpg;
+    int   H, E, seq, seq0;
+    float inv_t, rep, freq, pres;
+};
+
+/* What a finished slice leaves for the finisher warps to publish. */
+struct __align__(8) Mail {
+    int    row, item;
+    float  smax;
+    int    sarg;
+    int    n_cand, st;
+    double bulk;
 };
 
 struct __align__(16) StreamShared {
@@ -79,10 +99,11 @@ struct __align__(16) StreamShared {
     float              gmax[kGroupCap];
     GroupShared        wk; /* workers */
     GroupShared        fn; /* finishers */
-    /* completed rows, worker thread 0 -> finisher warps */
-    volatile int q_rows[kQueue];
-    volatile int q_head; /* next slot the worker writes */
-    volatile int q_tail; /* next slot the finishers read */
+    ItemCfg            cfg[4]; /* ring: items j .. j+2 of this CTA */
+    /* finished slices, worker thread 0 -> finisher warps */
+    Mail         mail[kQueue];
+    volatile int q_head; /* mail written so far */
+    volatile int q_tail; /* mail consumed so far */
     volatile int q_done; /* the worker loop has ended */
     volatile int q_error;
 };
@@ -1001,58 +1022,145 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
     return st | multipass_row(g, p, sh, r, row_max, row_arg);
 }
 
-/* The finisher warps' loop: rows arrive through the shared-memory queue. */
+/* Optional cycle accounting of worker thread 0 (build with -DGB_PROFILE): where one CTA's time goes. */
+#ifdef GB_PROFILE
+__device__ long long g_prof[512][8]; /* [0,256) workers, [256,512) finishers */
+#define PROF_INIT()              \
+    long long prof_acc[8] = {0}; \
+    long long prof_t      = clock64()
+#define PROF(i)                         \
+    if (g.tid == 0) {                   \
+        const long long t_ = clock64(); \
+        prof_acc[i] += t_ - prof_t;     \
+        prof_t = t_;                    \
+    }
+#define PROF_DONE()                                \
+    if (g.tid == 0 && blockIdx.x < 256) {          \
+        for (int i_ = 0; i_ < 8; i_++) {           \
+            g_prof[blockIdx.x][i_] = prof_acc[i_]; \
+        }                                          \
+    }
+#else
+#define PROF_INIT()
+#define PROF(i)
+#define PROF_DONE()
+#endif
+
+/*
+ * The finisher warps' loop. Worker thread 0 leaves one mail entry per finished
+ * slice; the lanes of the first finisher warp publish up to 32 of them at a
+ * time (record to global scratch, fence, row counter) so that the round trips
+ * overlap, and rows whose counter reports the last slice are finished by all
+ * four warps.
+ */
 __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared *sh, const FinBuffers &fb) {
     GroupShared *fs   = &sh->fn;
     int          tail = 0;
+#ifdef GB_PROFILE
+    long long facc[8] = {0};
+    long long ft      = clock64();
+#define FPROF(i)                        \
+    if (g.tid == 0) {                   \
+        const long long t_ = clock64(); \
+        facc[i] += t_ - ft;             \
+        ft = t_;                        \
+    }
+#else
+#define FPROF(i)
+#endif
     for (;;) {
-        if (g.tid == 0) {
-            int row = -1;
-            /* bounded wait for a row or for the end of the worker loop */
-            for (long long spin = 0; spin < (1ll << 31); spin++) {
-                if (sh->q_head != tail) {
-                    row = sh->q_rows[tail % kQueue];
-                    break;
-                }
-                if (sh->q_done) {
-                    if (sh->q_head != tail) {
-                        continue;
+        FPROF(0);
+        if (g.warp == 0) {
+            int avail = 0;
+            if (g.lane == 0) {
+                /* bounded wait for mail or for the end of the worker loop */
+                for (long long spin = 0; spin < (1ll << 31); spin++) {
+                    avail = sh->q_head - tail;
+                    if (avail > 0) {
+                        break;
                     }
-                    row = -2;
-                    break;
+                    if (sh->q_done) {
+                        avail = sh->q_head - tail;
+                        if (avail > 0) {
+                            break;
+                        }
+                        avail = -1;
+                        break;
+                    }
+                    __nanosleep(32);
                 }
-                __nanosleep(64);
+                if (avail == 0) {
+                    sh->q_error = 1; /* gave up waiting: leave */
+                    avail       = -1;
+                }
             }
-            if (row == -1) {
-                sh->q_error = 1; /* gave up waiting: leave */
-                row         = -2;
+            avail        = __shfl_sync(0xffffffffu, avail, 0);
+            __threadfence_block(); /* the mail written before q_head moved is readable */
+            FPROF(1); /* polling */
+            const int nb = min(avail, 32);
+            bool      last = false;
+            int       row  = -1;
+            if (g.lane < nb) {
+                const Mail m   = sh->mail[(tail + g.lane) % kQueue];
+                SliceRec  *rec = p.recs + m.item;
+                rec->max      = m.smax;
+                rec->arg      = m.sarg;
+                rec->n_cand   = m.n_cand;
+                rec->st       = m.st;
+                rec->bulk     = m.bulk;
+                row           = m.row;
+                __threadfence(); /* the slice's record and candidates are visible before the counter moves */
+                last = atomicAdd(&p.row_counter[row], 1) == p.n_slices - 1;
+                __threadfence(); /* and the other slices' records are visible to whoever saw the last count */
             }
-            __threadfence(); /* the row's records, published by other CTAs, are visible from here on */
-            fs->cur_row = row;
+            const unsigned done = __ballot_sync(0xffffffffu, last);
+            if (last) {
+                fs->done_rows[__popc(done & ((1u << g.lane) - 1u))] = row;
+            }
+            if (g.lane == 0) {
+                fs->n_done = avail < 0 ? -1 : __popc(done);
+                if (nb > 0) {
+                    sh->q_tail = tail + nb; /* the mail slots are free again */
+                }
+            }
         }
         g.sync();
-        const int row = fs->cur_row;
-        if (row < 0) {
+        FPROF(2); /* publishing */
+        const int n_done = fs->n_done;
+        if (n_done < 0) {
+#ifdef GB_PROFILE
+            if (g.tid == 0 && blockIdx.x < 256) {
+                for (int i_ = 0; i_ < 8; i_++) {
+                    g_prof[256 + blockIdx.x][i_] = facc[i_];
+                }
+            }
+#endif
             return;
         }
-        const RawCfg rc  = raw_config(p, row);
-        RowCfg       r   = row_config(p, row, rc, true);
-        const int    fst = finish_row(g, p, fs, r, fb);
-        if (g.tid == 0) {
-            p.status[row]      = fst;
-            p.row_counter[row] = 0; /* ready for the next launch */
-            if (p.rng_out != nullptr && r.rr == p.rows_per_seq - 1) {
-                /* the sequence's generator after all of its rows drew */
-                unsigned long long s = p.rng_in ? p.rng_in[r.seq] : 1ull;
-                for (int i = 0; i < p.rows_per_seq * r.draws_per_row; i++) {
-                    (void) xorshift_next(s);
+        tail = sh->q_tail;
+        for (int d = 0; d < n_done; d++) {
+            const int    row = fs->done_rows[d];
+            const RawCfg rc  = raw_config(p, row);
+            RowCfg       r   = row_config(p, row, rc, true);
+            FPROF(3); /* row configuration */
+            const int    fst = finish_row(g, p, fs, r, fb);
+            FPROF(4); /* finishing */
+#ifdef GB_PROFILE
+            facc[5] += 1;
+#endif
+            if (g.tid == 0) {
+                p.status[row]      = fst;
+                p.row_counter[row] = 0; /* ready for the next launch */
+                if (p.rng_out != nullptr && r.rr == p.rows_per_seq - 1) {
+                    /* the sequence's generator after all of its rows drew */
+                    unsigned long long s = p.rng_in ? p.rng_in[r.seq] : 1ull;
+                    for (int i = 0; i < p.rows_per_seq * r.draws_per_row; i++) {
+                        (void) xorshift_next(s);
+                    }
+                    p.rng_out[r.seq] = s;
                 }
-                p.rng_out[r.seq] = s;
             }
-            tail++;
-            sh->q_tail = tail;
-        } else {
-            tail++;
+            g.sync();
         }
         g.sync();
     }
@@ -1065,7 +1173,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
 
     unsigned char *ring   = smem_raw;
     StreamShared  *sh     = reinterpret_cast<StreamShared *>(smem_raw + (size_t) p.stages * (size_t) p.stage_bytes);
-    unsigned      *bitmap = reinterpret_cast<unsigned *>(sh + 1);             /* workers: ids of the slice */
+    unsigned      *bitmap = reinterpret_cast<unsigned *>(sh + 1); /* workers: ids of the slice */
     PenEntry      *dlist  = reinterpret_cast<PenEntry *>(bitmap + p.bitmap_words);
     FinBuffers     fb;
     fb.dlist_cap = min(p.hist_cap, 512);
@@ -1073,8 +1181,8 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     fb.dlist     = reinterpret_cast<PenEntry *>(fb.bitmap + 16);
     fb.fcand     = reinterpret_cast<Pair *>(fb.dlist + fb.dlist_cap); /* merged candidates of one row */
     fb.ftmp      = fb.fcand + p.fin_cap;
-    fb.fsort     = fb.ftmp + p.fin_cap;                                /* kFastKMax entries */
-    fb.fq        = reinterpret_cast<float *>(fb.fsort + kFastKMax);    /* kFastKMax entries */
+    fb.fsort     = fb.ftmp + p.fin_cap;                             /* kFastKMax entries */
+    fb.fq        = reinterpret_cast<float *>(fb.fsort + kFastKMax); /* kFastKMax entries */
 
     const int n_items  = p.n_rows * p.n_slices;
     const int G        = (int) gridDim.x;
@@ -1124,7 +1232,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         }
     };
 
-    /* one thread keeps the ring full: the jj-th item of this CTA goes to stage jj % stages */
+    /* thread 0 keeps the ring full: the jj-th item of this CTA goes to stage jj % stages */
     auto issue = [&](int row, int c, int stage) {
         const int      s0    = c * p.slice;
         const int      n     = max(0, min(p.slice, p.V - s0));
@@ -1139,87 +1247,107 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             bulk_g2s(dst + off, src + off, min(32768u, bytes - off), &sh->full[stage]);
         }
     };
-    int row = (int) blockIdx.x / p.n_slices, c = (int) blockIdx.x - row * p.n_slices; /* current item */
-    int irow = row, ic = c, istage = 0;                                                /* next item to load (thread 0) */
-    int issued = 0;
-    if (g.tid == 0 && p.aligned) {
-        for (; issued < min(p.stages, my_count); issued++) {
-            issue(irow, ic, istage);
-            advance(irow, ic);
-            istage = istage + 1 == p.stages ? 0 : istage + 1;
+    /* thread 0 decodes the configuration of an item into shared memory two items ahead, so that
+     * the other warps spend no instructions and no memory round trips on it */
+    auto decode = [&](int row, int c, const RawCfg &rc, ItemCfg *o) {
+        const RowCfg r = row_config(p, row, rc, false);
+        o->row         = row;
+        o->c           = c;
+        o->s0          = c * p.slice;
+        o->n           = max(0, min(p.slice, p.V - o->s0));
+        o->mode        = (int) r.mode;
+        o->kq          = r.kq;
+        o->pen_on      = r.pen_on ? 1 : 0;
+        o->H           = r.H;
+        o->E           = r.E;
+        o->seq         = r.seq;
+        o->seq0        = r.seq0;
+        o->inv_t       = r.inv_t;
+        o->rep         = r.rep;
+        o->freq        = r.freq;
+        o->pres        = r.pres;
+        o->lpg         = r.kq <= 48 ? 4 : (r.kq <= 96 ? 2 : 1);
+    };
+    /* this thread's history id of an item whose configuration is already decoded */
+    auto hist_fetch = [&](const ItemCfg *o) {
+        int id = 0;
+        if (o->pen_on && g.tid < o->H + o->E) {
+            id = (g.tid < o->H ? p.hist[(size_t) o->seq * (size_t) p.hist_stride + g.tid] : p.extra[(size_t) o->seq0 * (size_t) p.extra_stride + 1 + g.tid - o->H]) -
+                 p.vocab_offset;
+        }
+        return id;
+    };
+
+    int    irow = (int) blockIdx.x / p.n_slices, ic = (int) blockIdx.x - irow * p.n_slices; /* next item to load   (thread 0) */
+    int    drow = irow, dcs = ic;                                                            /* next item to decode (thread 0) */
+    int    issued = 0, decoded = 0, head = 0;
+    RawCfg raw{};
+    if (g.tid == 0) {
+        if (p.aligned) {
+            for (; issued < min(p.stages, my_count); issued++) {
+                issue(irow, ic, issued);
+                advance(irow, ic);
+            }
+        }
+        for (; decoded < min(2, my_count); decoded++) {
+            decode(drow, dcs, raw_config(p, drow), &sh->cfg[decoded & 3]);
+            advance(drow, dcs);
+        }
+        if (decoded < my_count) {
+            raw = raw_config(p, drow); /* in flight; decoded in the first iteration */
         }
     }
+    g.sync();
+    int      hid        = my_count > 0 ? hist_fetch(&sh->cfg[0]) : 0;
     unsigned phase_bits = 0u; /* parity of the next wait, one bit per stage */
+    int      stage      = 0;
 
-    /* worker thread 0 hands completed rows to the finisher warps, one item late, so that nobody
-     * waits for the counter's round trip */
-    int  pend_row = -1, pend_old = 0, head = 0;
-    auto hand_over = [&]() {
-        if (pend_row >= 0 && pend_old == p.n_slices - 1) {
-            for (long long spin = 0; spin < (1ll << 31) && head - sh->q_tail >= kQueue; spin++) {
-                __nanosleep(64);
-            }
-            sh->q_rows[head % kQueue] = pend_row;
-            __threadfence();
-            head++;
-            sh->q_head = head;
-        }
-        pend_row = -1;
-    };
-
-    /* configuration and this thread's history id, fetched one item ahead */
-    RawCfg nxt{};
-    int    nxt_hid = 0;
-    auto   prefetch = [&](int prow) {
-        nxt     = raw_config(p, prow);
-        nxt_hid = 0;
-        if (p.hist != nullptr || p.extra != nullptr) {
-            const int seq0 = p.rows_per_seq == 1 ? prow : prow / p.rows_per_seq;
-            const int rr   = prow - seq0 * p.rows_per_seq;
-            const int H    = p.hist ? (int) min((long long) max(nxt.hist_len, 0), p.hist_stride) : 0;
-            const int E    = p.extra ? rr : 0;
-            if (g.tid < H) {
-                nxt_hid = p.hist[(size_t) nxt.seq * (size_t) p.hist_stride + g.tid] - p.vocab_offset;
-            } else if (g.tid < H + E) {
-                nxt_hid = p.extra[(size_t) seq0 * (size_t) p.extra_stride + 1 + g.tid - H] - p.vocab_offset;
-            }
-        }
-    };
-    if (my_count > 0) {
-        prefetch(row);
-    }
-    int stage = 0;
-
+    PROF_INIT();
     for (int j = 0; j < my_count; j++) {
-        float       *sl   = reinterpret_cast<float *>(ring + (size_t) stage * (size_t) p.stage_bytes);
-        const int    s0   = c * p.slice;
-        const int    n    = max(0, min(p.slice, p.V - s0));
-        const int    nv4  = (n + 3) >> 2;
-        const int    body = p.aligned ? (n & ~3) : 0;
-        const int    item = row * p.n_slices + c;
-        int          st   = ST_OK;
-        const RawCfg rc   = nxt;
-        const int    hid  = nxt_hid;
-        const RowCfg r    = row_config(p, row, rc, false);
-        int          nrow = row, ncs = c;
-        advance(nrow, ncs);
+        PROF(0); /* loop overhead */
+        const ItemCfg *cf   = &sh->cfg[j & 3];
+        const int      row  = cf->row;
+        const int      s0   = cf->s0;
+        const int      n    = cf->n;
+        const int      mode = cf->mode;
+        const int      kq   = cf->kq;
+        const float    inv_t = cf->inv_t;
+        const bool     pen_on = cf->pen_on != 0;
+        float         *sl   = reinterpret_cast<float *>(ring + (size_t) stage * (size_t) p.stage_bytes);
+        const int      nv4  = (n + 3) >> 2;
+        const int      body = p.aligned ? (n & ~3) : 0;
+        const int      item = row * p.n_slices + cf->c;
+        int            st   = ST_OK;
+        const int      my_hid = hid;
+        if (g.tid == 0) {
+            if (decoded < my_count) { /* item j + 2: its raw values were requested one iteration ago */
+                decode(drow, dcs, raw, &sh->cfg[decoded & 3]);
+                advance(drow, dcs);
+                decoded++;
+                if (decoded < my_count) {
+                    raw = raw_config(p, drow);
+                }
+            }
+        }
         if (j + 1 < my_count) {
-            prefetch(nrow); /* loads in flight while this item is processed */
+            hid = hist_fetch(&sh->cfg[(j + 1) & 3]); /* in flight while this item is processed */
         }
 
         /* ---- 1. the slice arrives in its stage; its tail is padded with -inf up to a float4 ---- */
         {
-            const float *grow = p.logits + (size_t) row * (size_t) p.row_stride + s0;
-            for (int i = body + g.tid; i < nv4 * 4; i += g.n) {
-                sl[i] = i < n ? grow[i] : -CUDART_INF_F;
+            if (nv4 * 4 > body) {
+                const float *grow = p.logits + (size_t) row * (size_t) p.row_stride + s0;
+                for (int i = body + g.tid; i < nv4 * 4; i += g.n) {
+                    sl[i] = i < n ? grow[i] : -CUDART_INF_F;
+                }
             }
             if (g.tid == 0) {
                 ws->n_cand  = 0;
                 ws->n_dlist = 0;
-                ws->tau     = -CUDART_INF_F;
+                ws->tau_key = 0xffffffffu;
                 ws->pick    = 0x7fffffff;
             }
-            if (r.pen_on) {
+            if (pen_on) {
                 for (int i = g.tid; i < p.bitmap_words; i += g.n) {
                     bitmap[i] = 0u;
                 }
@@ -1232,12 +1360,21 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                     (void) mbar_wait_bounded(&sh->full[stage], parity); /* a second bounded chance for the copy in flight */
                 }
             }
+            PROF(1); /* waiting for the slice */
             g.sync();
         }
 
         /* ---- 2. penalties in shared memory, then the slice moves to registers ---- */
-        if (r.pen_on) {
-            st |= apply_penalties(g, sl, s0, n, r, p.V, p.vocab_offset, bitmap, dlist, p.hist_cap, &ws->n_dlist, true, hid);
+        if (pen_on) {
+            RowCfg r;
+            r.H    = cf->H;
+            r.E    = cf->E;
+            r.rep  = cf->rep;
+            r.freq = cf->freq;
+            r.pres = cf->pres;
+            r.hrow = p.hist ? p.hist + (size_t) cf->seq * (size_t) p.hist_stride : nullptr;
+            r.erow = p.extra ? p.extra + (size_t) cf->seq0 * (size_t) p.extra_stride : nullptr;
+            st |= apply_penalties(g, sl, s0, n, r, p.V, p.vocab_offset, bitmap, dlist, p.hist_cap, &ws->n_dlist, true, my_hid);
         }
         if (p.out_logits != nullptr) {
             float *orow = p.out_logits + (size_t) row * (size_t) p.V + s0;
@@ -1252,20 +1389,17 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         float4    x[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const int  o  = g.lane + 32 * i;
-            const bool ok = o < L && first4 + 32 * i < nv4;
+            const bool ok = g.lane + 32 * i < L && first4 + 32 * i < nv4;
             x[i]          = ok ? reinterpret_cast<const float4 *>(sl)[first4 + 32 * i] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
         }
         g.sync(); /* the stage is free again */
-        if (g.tid == 0) {
-            if (p.aligned && issued < my_count) {
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                issue(irow, ic, stage);
-                advance(irow, ic);
-                issued++;
-            }
-            hand_over(); /* the previous item's counter has long returned */
+        if (g.tid == 0 && p.aligned && issued < my_count) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue(irow, ic, stage);
+            advance(irow, ic);
+            issued++;
         }
+        PROF(2); /* penalties, registers, release, issue */
 
         /* ---- 3. pass 1 on registers: the thread's maximum ---- */
         float bv = -CUDART_INF_F;
@@ -1276,14 +1410,13 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         /* local index of element q of float4 i */
         auto li_of = [&](int i, int q) { return 4 * (first4 + 32 * i) + q; };
 
-        const bool fast_sel = r.kq > 0 && r.kq <= kFastKMax;
+        const bool fast_sel = kq > 0 && kq <= kFastKMax;
         SliceRec  *rec      = p.recs + item;
         float      smax     = bv;
         int        sarg     = 0;
         double     bulk     = 0.0;
-        bool       wrote    = false; /* this thread stored to global scratch */
 
-        if (r.mode == M_ARGMAX || (r.mode == M_TOPK && !fast_sel)) {
+        if (mode == M_ARGMAX || (mode == M_TOPK && !fast_sel)) {
             /* maximum first, then only the threads that hold it look for its first id */
             smax = group_max(g, ws, bv);
             if (bv == smax) {
@@ -1302,7 +1435,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             }
             g.sync();
             sarg = ws->pick;
-        } else if (r.mode == M_TEMP) {
+        } else if (mode == M_TEMP) {
             smax = group_max(g, ws, bv);
             /* per-warp sums of e_i relative to the SLICE maximum; the finisher rescales to the row
              * maximum. -inf padding gives exp(-inf) = 0. */
@@ -1310,111 +1443,119 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             double      acc = 0.0;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-                const float e0 = expf(scaled_arg(x[i].x, ref, r.inv_t));
-                const float e1 = expf(scaled_arg(x[i].y, ref, r.inv_t));
-                const float e2 = expf(scaled_arg(x[i].z, ref, r.inv_t));
-                const float e3 = expf(scaled_arg(x[i].w, ref, r.inv_t));
+                const float e0 = expf(scaled_arg(x[i].x, ref, inv_t));
+                const float e1 = expf(scaled_arg(x[i].y, ref, inv_t));
+                const float e2 = expf(scaled_arg(x[i].z, ref, inv_t));
+                const float e3 = expf(scaled_arg(x[i].w, ref, inv_t));
                 acc += (double) ((e0 + e1) + (e2 + e3));
             }
             acc = warp_sum_d(acc);
             if (g.lane == 0) {
                 rec->seg[g.warp] = acc;
-                wrote            = true;
             }
         } else {
             /* top-k / top-p fast path. Groups of 4 / 2 / 1 lanes: 112 / 224 / 448 group maxima per slice.
              * tau = kq-th largest group maximum: at least kq entries of the slice are >= tau, so the
              * slice's share of the row's kq best is among the entries it lets through. */
-            const int lpg = r.kq <= 48 ? 4 : (r.kq <= 96 ? 2 : 1);
-            const int Gs  = kWorkThreads / lpg;
+            const int lpg = cf->lpg;
+            const int Gs  = lpg == 4 ? kWorkThreads / 4 : (lpg == 2 ? kWorkThreads / 2 : kWorkThreads);
             float     gv  = bv;
-            for (int o = 1; o < lpg; o <<= 1) {
-                gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, o));
+            if (lpg >= 2) {
+                gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 1));
             }
-            if ((g.lane % lpg) == 0) {
-                sh->gmax[g.tid / lpg] = gv;
+            if (lpg >= 4) {
+                gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 2));
             }
-            if (r.mode == M_TOPP) {
+            if ((g.lane & (lpg - 1)) == 0) {
+                sh->gmax[lpg == 4 ? g.tid >> 2 : (lpg == 2 ? g.tid >> 1 : g.tid)] = gv;
+            }
+            if (mode == M_TOPP) {
                 smax = group_max(g, ws, bv); /* its barriers also publish gmax */
             } else {
                 g.sync();
             }
-            /* rank of every group maximum: 4 threads share one value, each scans a quarter */
-            const int kth = min(r.kq, Gs) - 1;
+            PROF(6);
+            /* tau = the smallest group maximum that fewer than kq group maxima exceed (ties need no
+             * order: only the value matters). Four threads share one value, each counts a quarter. */
+            const int kth = min(kq, Gs);
             for (int idx = g.tid; idx < 4 * Gs; idx += g.n) {
-                const int   t    = idx >> 2, part = idx & 3;
-                const float v    = sh->gmax[t];
-                const int   q0   = part * (Gs / 4), q1 = q0 + Gs / 4;
-                int         rank = 0;
-                for (int jg = q0; jg < q1; jg++) {
-                    const float o = sh->gmax[jg];
-                    rank += (o > v || (o == v && jg < t)) ? 1 : 0;
+                const int     t    = idx >> 2, part = idx & 3;
+                const float   v    = sh->gmax[t];
+                const float4 *q4   = reinterpret_cast<const float4 *>(sh->gmax) + part * (Gs / 16);
+                int           above = 0;
+                for (int jg = 0; jg < Gs / 16; jg++) {
+                    const float4 o = q4[jg];
+                    above += (o.x > v) + (o.y > v) + (o.z > v) + (o.w > v);
                 }
-                rank += __shfl_xor_sync(0xffffffffu, rank, 1);
-                rank += __shfl_xor_sync(0xffffffffu, rank, 2);
-                if (part == 0 && rank == kth) {
-                    ws->tau = v;
+                above += __shfl_xor_sync(0xffffffffu, above, 1);
+                above += __shfl_xor_sync(0xffffffffu, above, 2);
+                if (part == 0 && above < kth) {
+                    atomicMin(&ws->tau_key, order_key(v));
                 }
             }
             g.sync();
-            const float tau = ws->tau;
-            Pair       *gc  = p.cands + (size_t) item * (size_t) p.cand_cap;
-            if (bv >= tau) { /* few threads hold anything that passes */
+            PROF(7);
+            const unsigned tkey = ws->tau_key;
+            Pair          *gc   = p.cands + (size_t) item * (size_t) p.cand_cap;
+            if (order_key(bv) >= tkey) { /* few threads hold anything that passes */
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     const float xs[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
-                        if (xs[q] >= tau && li_of(i, q) < n) {
+                        if (order_key(xs[q]) >= tkey && li_of(i, q) < n) {
                             const int pos = atomicAdd(&ws->n_cand, 1);
                             if (pos < p.cand_cap) {
                                 Pair c2;
                                 c2.v    = xs[q];
                                 c2.idx  = s0 + li_of(i, q);
                                 gc[pos] = c2; /* straight to the row's scratch */
-                                wrote   = true;
                             }
                         }
                     }
                 }
             }
-            if (r.mode == M_TOPP) {
+            if (mode == M_TOPP) {
                 /* everything below tau is summed here; -inf padding adds exp(-inf) = 0 */
                 const float ref = smax == -CUDART_INF_F ? 0.0f : smax;
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    const float e0 = x[i].x >= tau ? 0.0f : expf(scaled_arg(x[i].x, ref, r.inv_t));
-                    const float e1 = x[i].y >= tau ? 0.0f : expf(scaled_arg(x[i].y, ref, r.inv_t));
-                    const float e2 = x[i].z >= tau ? 0.0f : expf(scaled_arg(x[i].z, ref, r.inv_t));
-                    const float e3 = x[i].w >= tau ? 0.0f : expf(scaled_arg(x[i].w, ref, r.inv_t));
+                    const float e0 = order_key(x[i].x) >= tkey ? 0.0f : expf(scaled_arg(x[i].x, ref, inv_t));
+                    const float e1 = order_key(x[i].y) >= tkey ? 0.0f : expf(scaled_arg(x[i].y, ref, inv_t));
+                    const float e2 = order_key(x[i].z) >= tkey ? 0.0f : expf(scaled_arg(x[i].z, ref, inv_t));
+                    const float e3 = order_key(x[i].w) >= tkey ? 0.0f : expf(scaled_arg(x[i].w, ref, inv_t));
                     bulk += (double) ((e0 + e1) + (e2 + e3));
                 }
                 bulk = group_sum_d(g, ws, bulk);
             }
         }
+        PROF(4); /* the passes */
 
-        /* ---- 4. publish the slice; whoever completes the row queues it for its finisher warps ---- */
-        if (wrote) {
-            __threadfence();
-        }
-        g.sync();
+        /* ---- 4. hand the slice's result to the finisher warps; they publish it ---- */
+        g.sync(); /* every candidate / segment store of this slice is ordered before the mail below */
         if (g.tid == 0) {
-            rec->max    = smax;
-            rec->arg    = sarg;
-            rec->n_cand = ws->n_cand;
-            rec->st     = st;
-            rec->bulk   = bulk;
-            __threadfence();
-            pend_old = atomicAdd(&p.row_counter[row], 1);
-            pend_row = row;
+            for (long long spin = 0; spin < (1ll << 31) && head - sh->q_tail >= kQueue; spin++) {
+                __nanosleep(32);
+            }
+            Mail m;
+            m.row    = row;
+            m.item   = item;
+            m.smax   = smax;
+            m.sarg   = sarg;
+            m.n_cand = ws->n_cand;
+            m.st     = st;
+            m.bulk   = bulk;
+            sh->mail[head % kQueue] = m;
+            __threadfence_block();
+            head++;
+            sh->q_head = head;
         }
-        row   = nrow;
-        c     = ncs;
+        PROF(5); /* mail */
         stage = stage + 1 == p.stages ? 0 : stage + 1;
     }
+    PROF_DONE();
     if (g.tid == 0) {
-        hand_over();
-        __threadfence();
+        __threadfence_block();
         sh->q_done = 1;
     }
 }
@@ -1442,6 +1583,10 @@ static cudaError_t ensure_attributes(size_t smem_bytes) {
     }
     return cudaSuccess;
 }
+
+#ifdef GB_PROFILE
+extern "C" int geist_b200_debug_prof(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 512 * 8); }
+#endif
 
 cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, cudaStream_t stream) {
     cudaError_t e = ensure_attributes(smem_bytes);
