@@ -73,8 +73,9 @@ struct __align__(16) GroupShared {
     int       flag;
     int       pick;
     unsigned  tau_key;       /* ordered key of the select threshold */
-    int       n_done;        /* rows completed by the last batch of mail */
-    int       done_rows[32];
+    int       cur_row;
+    float     hmax[kHistBins]; /* finisher: slice maxima of the row */
+    int       harg[kHistBins]; /* finisher: their first ids */
 };
 
 /* A work item's configuration, decoded once by worker thread 0. */
@@ -106,6 +107,11 @@ struct __align__(16) StreamShared {
     volatile int q_tail; /* mail consumed so far */
     volatile int q_done; /* the worker loop has ended */
     volatile int q_error;
+    /* completed rows, publisher warp -> finisher warps */
+    volatile int r_rows[kRowQueue];
+    volatile int r_head;
+    volatile int r_tail;
+    volatile int p_done; /* the publisher has ended */
 };
 
 enum Mode { M_ARGMAX, M_TOPK, M_TOPP, M_TEMP };
@@ -674,36 +680,147 @@ struct FinBuffers {
     int       dlist_cap;
 };
 
+/* What the finisher warps request from global scratch the moment a row is theirs, so that it
+ * travels while the row's configuration is still being read. */
+constexpr int kSpec      = 48; /* candidates per slice fetched before their count is known */
+constexpr int kSpecSlots = 8;  /* per finisher thread */
+struct Prefetch {
+    int4      hdr;              /* slice record header {max, arg, n_cand, st} of slice g.tid */
+    long long c[kSpecSlots];    /* candidate (value, id) pairs, flat index g.tid + kFinThreads * m */
+};
+
+__device__ __forceinline__ Prefetch prefetch_row(const Grp &g, const SampleParams &p, int row) {
+    Prefetch        pf;
+    const SliceRec *recs = p.recs + (size_t) row * (size_t) p.n_slices;
+    pf.hdr               = make_int4(0, 0, 0, 0);
+    if (g.tid < p.n_slices) {
+        pf.hdr = __ldcg(reinterpret_cast<const int4 *>(&recs[g.tid]));
+    }
+    const int   flat = p.n_slices * kSpec;
+    const Pair *base = p.cands + (size_t) row * (size_t) p.n_slices * (size_t) p.cand_cap;
+#pragma unroll
+    for (int m = 0; m < kSpecSlots; m++) {
+        const int f = g.tid + kFinThreads * m;
+        pf.c[m]     = 0;
+        if (f < flat && flat <= kFinThreads * kSpecSlots) {
+            const int cc = f / kSpec, i = f - cc * kSpec;
+            pf.c[m]      = __ldcg(reinterpret_cast<const long long *>(base + (size_t) cc * (size_t) p.cand_cap + i));
+        }
+    }
+    return pf;
+}
+
+/* Warp 0 of the group: S = sum of w[0..n) and the first i with u(S) < w[0] + .. + w[i] (n - 1 if
+ * none), for n <= 256. u01 is the unit draw; the comparison is made against u01 * S like the
+ * reference's inverse CDF (sampler.c:90-102). Sums are formed lane-wise and scanned across the
+ * warp in double precision. Returns through *S_out and the return value (valid in every lane). */
+__device__ __forceinline__ int warp_inverse_cdf(int lane, const float *w, int n, float u01, double *S_out) {
+    const int per = (n + 31) / 32; /* <= 8 consecutive weights per lane */
+    const int b   = lane * per;
+    double    mine = 0.0;
+    for (int i = b; i < min(b + per, n); i++) {
+        mine += (double) w[i];
+    }
+    double incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) {
+            incl += up;
+        }
+    }
+    const double   S    = __shfl_sync(0xffffffffu, incl, 31);
+    const double   u    = (double) u01 * S;
+    const unsigned ball = __ballot_sync(0xffffffffu, b < n && u < incl);
+    int            pick = n - 1;
+    if (ball != 0u) {
+        const int src = __ffs(ball) - 1;
+        int       f   = n - 1;
+        if (lane == src) {
+            double a = incl - mine;
+            f        = min(b + per, n) - 1;
+            for (int i = b; i < min(b + per, n); i++) {
+                a += (double) w[i];
+                if (u < a) {
+                    f = i;
+                    break;
+                }
+            }
+        }
+        pick = __shfl_sync(0xffffffffu, f, src);
+    }
+    *S_out = S;
+    return pick;
+}
+
 /* Runs in the finisher warps of the CTA that completed the row. Returns the row's status bits. */
-__device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, const FinBuffers &fb) {
+__device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, const FinBuffers &fb, const Prefetch &pf) {
     const int       row    = r.row;
     const SliceRec *recs   = p.recs + (size_t) row * (size_t) p.n_slices;
     int            *kept_i = p.kept_cap > 0 ? p.kept_idx + (size_t) row * (size_t) p.kept_cap : nullptr;
     float          *kept_v = p.kept_cap > 0 ? p.kept_val + (size_t) row * (size_t) p.kept_cap : nullptr;
     int             st     = 0;
 
-    /* row maximum, its first id, and the slices' status bits */
-    float row_max = -CUDART_INF_F;
-    int   row_arg = 0x7fffffff;
-    int   rst     = 0;
-    for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
-        const float m = __ldcg(&recs[cc].max);
-        const int   a = __ldcg(&recs[cc].arg);
-        rst |= __ldcg(&recs[cc].st);
-        if (row_arg == 0x7fffffff || pair_before(m, a, row_max, row_arg)) {
-            row_max = m;
-            row_arg = a;
+    /* slice headers into shared memory; every thread then derives the row's maximum, its first id,
+     * the status bits and the candidate totals from them */
+    const bool small_row = p.n_slices <= kHistBins;
+    g.sync();
+    if (small_row) {
+        for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
+            const int4 h = cc == g.tid ? pf.hdr : __ldcg(reinterpret_cast<const int4 *>(&recs[cc]));
+            sh->hmax[cc] = __int_as_float(h.x);
+            sh->harg[cc] = h.y;
+            sh->bins[cc] = h.z;
+            st |= h.w;
         }
     }
-    rst = __reduce_or_sync(0xffffffffu, rst);
-    g.sync();
+    st = __reduce_or_sync(0xffffffffu, st);
     if (g.lane == 0) {
-        sh->wred_l[g.warp] = rst;
+        sh->wred_a[g.warp] = st;
     }
-    group_argmax(g, sh, row_max, row_arg);
+    g.sync();
     for (int w = 0; w < g.nw; w++) {
-        st |= (int) sh->wred_l[w];
+        st |= sh->wred_a[w];
     }
+    float row_max  = -CUDART_INF_F;
+    int   row_arg  = 0x7fffffff;
+    int   total    = 0;
+    bool  overflow = false;
+    if (small_row) {
+        for (int cc = 0; cc < p.n_slices; cc++) {
+            const float m = sh->hmax[cc];
+            const int   a = sh->harg[cc];
+            if (row_arg == 0x7fffffff || pair_before(m, a, row_max, row_arg)) {
+                row_max = m;
+                row_arg = a;
+            }
+            const int nc = sh->bins[cc];
+            overflow |= nc > p.cand_cap;
+            total += nc;
+        }
+    } else {
+        /* very long rows: the records are read straight from global memory */
+        int rst = 0;
+        for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
+            const int4  h = __ldcg(reinterpret_cast<const int4 *>(&recs[cc]));
+            const float m = __int_as_float(h.x);
+            rst |= h.w;
+            if (row_arg == 0x7fffffff || pair_before(m, h.y, row_max, row_arg)) {
+                row_max = m;
+                row_arg = h.y;
+            }
+        }
+        rst = __reduce_or_sync(0xffffffffu, rst);
+        g.sync();
+        if (g.lane == 0) {
+            sh->wred_l[g.warp] = rst;
+        }
+        group_argmax(g, sh, row_max, row_arg);
+        for (int w = 0; w < g.nw; w++) {
+            st |= (int) sh->wred_l[w];
+        }
+    }
+    auto slice_max = [&](int cc) { return small_row ? sh->hmax[cc] : __ldcg(&recs[cc].max); };
 
     if (r.mode == M_ARGMAX) {
         if (g.tid == 0) {
@@ -720,7 +837,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
         const int nseg   = p.n_slices * kWorkWarps;
         auto      seg_at = [&](int t) {
             const int   cc = t / kWorkWarps;
-            const float m  = __ldcg(&recs[cc].max);
+            const float m  = slice_max(cc);
             const double sc = m == -CUDART_INF_F ? 0.0 : exp(((double) m - (double) row_max) * (double) r.inv_t);
             return sc * __ldcg(&recs[cc].seg[t % kWorkWarps]);
         };
@@ -859,38 +976,45 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
     }
 
     /* ---- top-k and top-p: merge the slices' candidates ---- */
-    bool need_multipass = !(r.kq > 0 && r.kq <= kFastKMax) || p.n_slices > kHistBins;
-    int  total          = 0;
+    bool need_multipass = !(r.kq > 0 && r.kq <= kFastKMax) || !small_row || overflow || total > p.fin_cap || total < r.kq;
     if (!need_multipass) {
-        g.sync();
-        for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
-            sh->bins[cc] = __ldcg(&recs[cc].n_cand);
-        }
-        g.sync();
-        for (int cc = 0; cc < p.n_slices; cc++) {
-            const int nc = sh->bins[cc];
-            if (nc > p.cand_cap) {
-                need_multipass = true;
+        /* place the pre-fetched candidates, then fetch what the pre-fetch did not cover */
+        const bool spec = p.n_slices * kSpec <= kFinThreads * kSpecSlots;
+        if (spec) {
+#pragma unroll
+            for (int m = 0; m < kSpecSlots; m++) {
+                const int f = g.tid + kFinThreads * m;
+                if (f < p.n_slices * kSpec) {
+                    const int cc = f / kSpec, i = f - cc * kSpec;
+                    if (i < sh->bins[cc]) {
+                        int off = 0;
+                        for (int q = 0; q < cc; q++) {
+                            off += sh->bins[q];
+                        }
+                        Pair v;
+                        v.v               = __int_as_float((int) (pf.c[m] & 0xffffffffll));
+                        v.idx             = (int) (pf.c[m] >> 32);
+                        fb.fcand[off + i] = v;
+                    }
+                }
             }
-            total += nc;
         }
-        if (total > p.fin_cap || total < r.kq) {
-            need_multipass = true; /* too many ties / clustered maxima, or NaN rows */
-        }
-    }
-    if (!need_multipass) {
+        const int first = spec ? kSpec : 0;
         for (int cc = g.warp; cc < p.n_slices; cc += g.nw) {
-            int off = 0;
-            for (int i = 0; i < cc; i++) {
-                off += sh->bins[i];
-            }
-            const Pair *src = p.cands + ((size_t) row * (size_t) p.n_slices + (size_t) cc) * (size_t) p.cand_cap;
-            const int   nc  = sh->bins[cc];
-            for (int i = g.lane; i < nc; i += 32) {
-                Pair v;
-                v.v               = __ldcg(&src[i].v);
-                v.idx             = __ldcg(&src[i].idx);
-                fb.fcand[off + i] = v;
+            const int nc = sh->bins[cc];
+            if (nc > first) {
+                int off = 0;
+                for (int i = 0; i < cc; i++) {
+                    off += sh->bins[i];
+                }
+                const long long *src = reinterpret_cast<const long long *>(p.cands + ((size_t) row * (size_t) p.n_slices + (size_t) cc) * (size_t) p.cand_cap);
+                for (int i = first + g.lane; i < nc; i += 32) {
+                    const long long w = __ldcg(src + i);
+                    Pair            v;
+                    v.v               = __int_as_float((int) (w & 0xffffffffll));
+                    v.idx             = (int) (w >> 32);
+                    fb.fcand[off + i] = v;
+                }
             }
         }
         g.sync();
@@ -915,29 +1039,19 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
                 fb.fq[i] = exp_exact(scaled_arg(fb.fsort[i].v, m, r.inv_t));
             }
             g.sync();
-            if (g.tid == 0) {
-                double S = 0.0;
-                for (int i = 0; i < k; i++) {
-                    S += (double) fb.fq[i];
-                }
-                const double u    = (double) unit_from(xorshift_next(r.rng)) * S;
-                double       a    = 0.0;
-                int          pick = k - 1;
-                for (int i = 0; i < k; i++) {
-                    a += (double) fb.fq[i];
-                    if (u < a) {
-                        pick = i;
-                        break;
+            if (g.warp == 0) {
+                double    S;
+                const int pick = warp_inverse_cdf(g.lane, fb.fq, k, unit_from(xorshift_next(r.rng)), &S);
+                if (g.lane == 0) {
+                    p.tokens[row] = fb.fsort[pick].idx + p.vocab_offset;
+                    sh->S         = S;
+                    if (p.kept_cap > 0) {
+                        p.kept_n[row] = k;
                     }
                 }
-                p.tokens[row] = fb.fsort[pick].idx + p.vocab_offset;
-                sh->S         = S;
-                if (p.kept_cap > 0) {
-                    p.kept_n[row] = k;
-                }
             }
-            g.sync();
             if (p.kept_cap > 0) {
+                g.sync();
                 const double S = sh->S;
                 for (int i = g.tid; i < min(k, p.kept_cap); i += g.n) {
                     kept_i[i] = fb.fsort[i].idx + p.vocab_offset;
@@ -958,7 +1072,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
             part += (double) e;
         }
         for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
-            const float  m  = __ldcg(&recs[cc].max);
+            const float  m  = slice_max(cc);
             const double sc = m == -CUDART_INF_F ? 0.0 : exp(((double) m - (double) row_max) * (double) r.inv_t);
             part += sc * __ldcg(&recs[cc].bulk);
         }
@@ -1047,87 +1161,127 @@ __device__ long long g_prof[512][8]; /* [0,256) workers, [256,512) finishers */
 #endif
 
 /*
- * The finisher warps' loop. Worker thread 0 leaves one mail entry per finished
- * slice; the lanes of the first finisher warp publish up to 32 of them at a
- * time (record to global scratch, fence, row counter) so that the round trips
- * overlap, and rows whose counter reports the last slice are finished by all
- * four warps.
+ * The publisher warp. Worker thread 0 leaves one mail entry per finished
+ * slice; the lanes publish up to 32 of them at a time (record to global
+ * scratch, fence, row counter) so that the round trips overlap. Rows whose
+ * counter reports the last slice go to the finisher warps' queue.
  */
-__device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared *sh, const FinBuffers &fb) {
-    GroupShared *fs   = &sh->fn;
-    int          tail = 0;
-#ifdef GB_PROFILE
-    long long facc[8] = {0};
-    long long ft      = clock64();
-#define FPROF(i)                        \
-    if (g.tid == 0) {                   \
-        const long long t_ = clock64(); \
-        facc[i] += t_ - ft;             \
-        ft = t_;                        \
-    }
-#else
-#define FPROF(i)
-#endif
+__device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh) {
+    int tail = 0, rhead = 0;
     for (;;) {
-        FPROF(0);
-        if (g.warp == 0) {
-            int avail = 0;
-            if (g.lane == 0) {
-                /* bounded wait for mail or for the end of the worker loop */
-                for (long long spin = 0; spin < (1ll << 31); spin++) {
+        int avail = 0;
+        if (lane == 0) {
+            /* bounded wait for mail or for the end of the worker loop */
+            for (long long spin = 0; spin < (1ll << 31); spin++) {
+                avail = sh->q_head - tail;
+                if (avail > 0) {
+                    break;
+                }
+                if (sh->q_done) {
                     avail = sh->q_head - tail;
-                    if (avail > 0) {
-                        break;
-                    }
-                    if (sh->q_done) {
-                        avail = sh->q_head - tail;
-                        if (avail > 0) {
-                            break;
-                        }
+                    if (avail <= 0) {
                         avail = -1;
-                        break;
                     }
-                    __nanosleep(32);
+                    break;
                 }
-                if (avail == 0) {
-                    sh->q_error = 1; /* gave up waiting: leave */
-                    avail       = -1;
-                }
+                __nanosleep(32);
             }
-            avail        = __shfl_sync(0xffffffffu, avail, 0);
-            __threadfence_block(); /* the mail written before q_head moved is readable */
-            FPROF(1); /* polling */
-            const int nb = min(avail, 32);
-            bool      last = false;
-            int       row  = -1;
-            if (g.lane < nb) {
-                const Mail m   = sh->mail[(tail + g.lane) % kQueue];
-                SliceRec  *rec = p.recs + m.item;
-                rec->max      = m.smax;
-                rec->arg      = m.sarg;
-                rec->n_cand   = m.n_cand;
-                rec->st       = m.st;
-                rec->bulk     = m.bulk;
-                row           = m.row;
-                __threadfence(); /* the slice's record and candidates are visible before the counter moves */
-                last = atomicAdd(&p.row_counter[row], 1) == p.n_slices - 1;
-                __threadfence(); /* and the other slices' records are visible to whoever saw the last count */
-            }
-            const unsigned done = __ballot_sync(0xffffffffu, last);
-            if (last) {
-                fs->done_rows[__popc(done & ((1u << g.lane) - 1u))] = row;
-            }
-            if (g.lane == 0) {
-                fs->n_done = avail < 0 ? -1 : __popc(done);
-                if (nb > 0) {
-                    sh->q_tail = tail + nb; /* the mail slots are free again */
-                }
+            if (avail == 0) {
+                sh->q_error = 1; /* gave up waiting: leave */
+                avail       = -1;
             }
         }
+        avail = __shfl_sync(0xffffffffu, avail, 0);
+        __threadfence_block(); /* the mail written before q_head moved is readable */
+        const int nb   = min(avail, 32);
+        bool      last = false;
+        int       row  = -1;
+        if (lane < nb) {
+            const Mail m   = sh->mail[(tail + lane) % kQueue];
+            SliceRec  *rec = p.recs + m.item;
+            int4       h;
+            h.x                             = __float_as_int(m.smax);
+            h.y                             = m.sarg;
+            h.z                             = m.n_cand;
+            h.w                             = m.st;
+            *reinterpret_cast<int4 *>(rec) = h;
+            rec->bulk                       = m.bulk;
+            row                             = m.row;
+            __threadfence(); /* the slice's record and candidates are visible before the counter moves */
+            last = atomicAdd(&p.row_counter[row], 1) == p.n_slices - 1;
+            if (last) {
+                __threadfence(); /* and the other slices' records are visible to whoever saw the last count */
+            }
+        }
+        const unsigned done = __ballot_sync(0xffffffffu, last);
+        const int      nd   = __popc(done);
+        if (nd > 0) {
+            if (lane == 0) {
+                for (long long spin = 0; spin < (1ll << 31) && rhead + nd - sh->r_tail > kRowQueue; spin++) {
+                    __nanosleep(32);
+                }
+            }
+            __syncwarp();
+            if (last) {
+                sh->r_rows[(rhead + __popc(done & ((1u << lane) - 1u))) % kRowQueue] = row;
+            }
+            __threadfence_block();
+            __syncwarp();
+            rhead += nd;
+        }
+        if (lane == 0) {
+            if (nd > 0) {
+                sh->r_head = rhead;
+            }
+            if (nb > 0) {
+                sh->q_tail = tail + nb; /* the mail slots are free again */
+            }
+            if (avail < 0) {
+                __threadfence_block();
+                sh->p_done = 1;
+            }
+        }
+        if (avail < 0) {
+            return;
+        }
+        tail += nb;
+    }
+}
+
+/* The finisher warps' loop: completed rows arrive through the row queue. */
+__device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared *sh, const FinBuffers &fb) {
+    GroupShared *fs    = &sh->fn;
+    int          rtail = 0;
+#ifdef GB_PROFILE
+    long long facc[8] = {0};
+#endif
+    for (;;) {
+        if (g.tid == 0) {
+            int row = -1;
+            for (long long spin = 0; spin < (1ll << 31); spin++) {
+                if (sh->r_head != rtail) {
+                    row = sh->r_rows[rtail % kRowQueue];
+                    break;
+                }
+                if (sh->p_done) {
+                    if (sh->r_head != rtail) {
+                        continue;
+                    }
+                    row = -2;
+                    break;
+                }
+                __nanosleep(32);
+            }
+            if (row == -1) {
+                sh->q_error = 1;
+                row         = -2;
+            }
+            __threadfence(); /* the row's records, published by other CTAs, are visible from here on */
+            fs->cur_row = row;
+        }
         g.sync();
-        FPROF(2); /* publishing */
-        const int n_done = fs->n_done;
-        if (n_done < 0) {
+        const int row = fs->cur_row;
+        if (row < 0) {
 #ifdef GB_PROFILE
             if (g.tid == 0 && blockIdx.x < 256) {
                 for (int i_ = 0; i_ < 8; i_++) {
@@ -1137,31 +1291,31 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
 #endif
             return;
         }
-        tail = sh->q_tail;
-        for (int d = 0; d < n_done; d++) {
-            const int    row = fs->done_rows[d];
-            const RawCfg rc  = raw_config(p, row);
-            RowCfg       r   = row_config(p, row, rc, true);
-            FPROF(3); /* row configuration */
-            const int    fst = finish_row(g, p, fs, r, fb);
-            FPROF(4); /* finishing */
 #ifdef GB_PROFILE
-            facc[5] += 1;
+        const long long ft0 = clock64();
 #endif
-            if (g.tid == 0) {
-                p.status[row]      = fst;
-                p.row_counter[row] = 0; /* ready for the next launch */
-                if (p.rng_out != nullptr && r.rr == p.rows_per_seq - 1) {
-                    /* the sequence's generator after all of its rows drew */
-                    unsigned long long s = p.rng_in ? p.rng_in[r.seq] : 1ull;
-                    for (int i = 0; i < p.rows_per_seq * r.draws_per_row; i++) {
-                        (void) xorshift_next(s);
-                    }
-                    p.rng_out[r.seq] = s;
+        const RawCfg   rc  = raw_config(p, row);   /* in flight together with ... */
+        const Prefetch pf  = prefetch_row(g, p, row); /* ... the row's slice headers and first candidates */
+        RowCfg         r   = row_config(p, row, rc, true);
+        const int      fst = finish_row(g, p, fs, r, fb, pf);
+#ifdef GB_PROFILE
+        facc[4] += clock64() - ft0;
+        facc[5] += 1;
+#endif
+        if (g.tid == 0) {
+            p.status[row]      = fst;
+            p.row_counter[row] = 0; /* ready for the next launch */
+            if (p.rng_out != nullptr && r.rr == p.rows_per_seq - 1) {
+                /* the sequence's generator after all of its rows drew */
+                unsigned long long s = p.rng_in ? p.rng_in[r.seq] : 1ull;
+                for (int i = 0; i < p.rows_per_seq * r.draws_per_row; i++) {
+                    (void) xorshift_next(s);
                 }
+                p.rng_out[r.seq] = s;
             }
-            g.sync();
+            sh->r_tail = rtail + 1;
         }
+        rtail++;
         g.sync();
     }
 }
@@ -1196,12 +1350,19 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         sh->q_tail  = 0;
         sh->q_done  = 0;
         sh->q_error = 0;
+        sh->r_head  = 0;
+        sh->r_tail  = 0;
+        sh->p_done  = 0;
     }
     __syncthreads();
 
-    if (threadIdx.x >= kWorkThreads) {
+    if (threadIdx.x >= kWorkThreads && threadIdx.x < kWorkThreads + 32) {
+        publisher_loop((int) threadIdx.x - kWorkThreads, p, sh);
+        return;
+    }
+    if (threadIdx.x >= kWorkThreads + 32) {
         Grp g;
-        g.tid  = (int) threadIdx.x - kWorkThreads;
+        g.tid  = (int) threadIdx.x - kWorkThreads - 32;
         g.lane = g.tid & 31;
         g.warp = g.tid >> 5;
         g.n    = kFinThreads;
@@ -1282,13 +1443,13 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     int    drow = irow, dcs = ic;                                                            /* next item to decode (thread 0) */
     int    issued = 0, decoded = 0, head = 0;
     RawCfg raw{};
-    if (g.tid == 0) {
-        if (p.aligned) {
-            for (; issued < min(p.stages, my_count); issued++) {
-                issue(irow, ic, issued);
-                advance(irow, ic);
-            }
+    if (g.tid == 0 && p.aligned) {
+        for (; issued < min(p.stages, my_count); issued++) {
+            issue(irow, ic, issued);
+            advance(irow, ic);
         }
+    }
+    if (g.tid == 32) { /* a thread of another warp than the one that issues the copies */
         for (; decoded < min(2, my_count); decoded++) {
             decode(drow, dcs, raw_config(p, drow), &sh->cfg[decoded & 3]);
             advance(drow, dcs);
@@ -1319,7 +1480,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         const int      item = row * p.n_slices + cf->c;
         int            st   = ST_OK;
         const int      my_hid = hid;
-        if (g.tid == 0) {
+        if (g.tid == 32) {
             if (decoded < my_count) { /* item j + 2: its raw values were requested one iteration ago */
                 decode(drow, dcs, raw, &sh->cfg[decoded & 3]);
                 advance(drow, dcs);
@@ -1489,21 +1650,28 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                 }
                 above += __shfl_xor_sync(0xffffffffu, above, 1);
                 above += __shfl_xor_sync(0xffffffffu, above, 2);
-                if (part == 0 && above < kth) {
-                    atomicMin(&ws->tau_key, order_key(v));
+                unsigned cand_key = (part == 0 && above < kth) ? order_key(v) : 0xffffffffu;
+                cand_key          = __reduce_min_sync(0xffffffffu, cand_key);
+                if (g.lane == 0 && cand_key != 0xffffffffu) {
+                    atomicMin(&ws->tau_key, cand_key);
                 }
             }
             g.sync();
             PROF(7);
             const unsigned tkey = ws->tau_key;
+            /* back from the ordered key to the float (nothing qualified: +NaN pattern, nothing passes) */
+            const float    tau  = __uint_as_float((tkey & 0x80000000u) ? (tkey ^ 0x80000000u) : ~tkey);
             Pair          *gc   = p.cands + (size_t) item * (size_t) p.cand_cap;
-            if (order_key(bv) >= tkey) { /* few threads hold anything that passes */
+            if (bv >= tau) { /* few threads hold anything that passes */
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
+                    if (!(fmaxf(fmaxf(x[i].x, x[i].y), fmaxf(x[i].z, x[i].w)) >= tau)) {
+                        continue;
+                    }
                     const float xs[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
-                        if (order_key(xs[q]) >= tkey && li_of(i, q) < n) {
+                        if (xs[q] >= tau && li_of(i, q) < n) {
                             const int pos = atomicAdd(&ws->n_cand, 1);
                             if (pos < p.cand_cap) {
                                 Pair c2;
@@ -1520,10 +1688,10 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                 const float ref = smax == -CUDART_INF_F ? 0.0f : smax;
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    const float e0 = order_key(x[i].x) >= tkey ? 0.0f : expf(scaled_arg(x[i].x, ref, inv_t));
-                    const float e1 = order_key(x[i].y) >= tkey ? 0.0f : expf(scaled_arg(x[i].y, ref, inv_t));
-                    const float e2 = order_key(x[i].z) >= tkey ? 0.0f : expf(scaled_arg(x[i].z, ref, inv_t));
-                    const float e3 = order_key(x[i].w) >= tkey ? 0.0f : expf(scaled_arg(x[i].w, ref, inv_t));
+                    const float e0 = x[i].x >= tau ? 0.0f : expf(scaled_arg(x[i].x, ref, inv_t));
+                    const float e1 = x[i].y >= tau ? 0.0f : expf(scaled_arg(x[i].y, ref, inv_t));
+                    const float e2 = x[i].z >= tau ? 0.0f : expf(scaled_arg(x[i].z, ref, inv_t));
+                    const float e3 = x[i].w >= tau ? 0.0f : expf(scaled_arg(x[i].w, ref, inv_t));
                     bulk += (double) ((e0 + e1) + (e2 + e3));
                 }
                 bulk = group_sum_d(g, ws, bulk);
@@ -1533,7 +1701,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
 
         /* ---- 4. hand the slice's result to the finisher warps; they publish it ---- */
         g.sync(); /* every candidate / segment store of this slice is ordered before the mail below */
-        if (g.tid == 0) {
+        if (g.tid == 64) {
             for (long long spin = 0; spin < (1ll << 31) && head - sh->q_tail >= kQueue; spin++) {
                 __nanosleep(32);
             }
@@ -1554,7 +1722,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         stage = stage + 1 == p.stages ? 0 : stage + 1;
     }
     PROF_DONE();
-    if (g.tid == 0) {
+    if (g.tid == 64) {
         __threadfence_block();
         sh->q_done = 1;
     }
