@@ -180,8 +180,9 @@ struct geist_b200_ctx {
     struct Lane {
         unsigned char *buf         = nullptr;
         size_t         bytes       = 0;
-        int           *counters    = nullptr;
+        int           *counters    = nullptr; /* row counters | ready-row slots | 2 queue tickets */
         size_t         counter_cap = 0;
+        unsigned       uses        = 0;       /* which of the two copies of the control words is live */
     } lane[kLanes];
     unsigned   next_lane = 0;
     std::mutex lane_mu;
@@ -337,6 +338,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     const size_t off_dl   = round_up(off_bm + (size_t) grid * gen_bmw * 4, 256);
     const size_t need     = round_up(off_dl + (size_t) grid * gen_hcap * sizeof(gb::Pair), 256);
     geist_b200_ctx::Lane *ln;
+    unsigned              use_now = 0;
     {
         std::lock_guard<std::mutex> lk(ctx->lane_mu);
         ln = &ctx->lane[ctx->next_lane++ % kLanes];
@@ -352,12 +354,22 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
             ln->counters    = nullptr;
             ln->counter_cap = 0;
             const size_t cap = round_up(n_rows, 1024);
-            CUDA_TRY(cudaMalloc((void **) &ln->counters, cap * sizeof(int)));
-            CUDA_TRY(cudaMemset(ln->counters, 0, cap * sizeof(int)));
+            /* two copies of {[cap] row counters | [cap] queue slots | 4 ticket words}, all zero: a launch
+             * works on one copy and zeroes the other for the set's next use */
+            CUDA_TRY(cudaMalloc((void **) &ln->counters, 2 * (2 * cap + 4) * sizeof(int)));
+            CUDA_TRY(cudaMemset(ln->counters, 0, 2 * (2 * cap + 4) * sizeof(int)));
             ln->counter_cap = cap;
+            ln->uses        = 0;
         }
+        use_now = ln->uses++;
     }
-    p.row_counter      = ln->counters;
+    const size_t ctl_words = 2 * ln->counter_cap + 4;
+    int         *ctl       = ln->counters + (use_now & 1u) * ctl_words;
+    p.row_counter      = ctl;
+    p.ready_rows       = ctl + ln->counter_cap;
+    p.q_ctr            = reinterpret_cast<unsigned *>(ctl + 2 * ln->counter_cap);
+    p.clear_ptr        = ln->counters + ((use_now + 1u) & 1u) * ctl_words;
+    p.clear_words      = (int) ctl_words;
     p.recs             = reinterpret_cast<gb::SliceRec *>(ln->buf + off_recs);
     p.cands            = reinterpret_cast<gb::Pair *>(ln->buf + off_cand);
     p.gen_rows         = reinterpret_cast<float *>(ln->buf + off_rows);
@@ -1148,3 +1160,4 @@ extern "C" enum geist_status geist_b200_batcher_verify(struct geist_b200_batcher
                                                        size_t row_stride, int logits_on_host, int append_history, int32_t *accepted, int32_t *n_out, geist_token_t *out_tokens) {
     return batcher_run(b, n, sessions, k, fed, logits, row_stride, logits_on_host, append_history, true, accepted, n_out, out_tokens);
 }
+

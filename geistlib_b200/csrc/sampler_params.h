@@ -12,7 +12,6 @@ constexpr int kWorkThreads  = kWorkWarps * 32;
 constexpr int kFinWarps     = 4;              /* warps that finish completed rows */
 constexpr int kFinThreads   = kFinWarps * 32;
 constexpr int kQueue        = 32;             /* finished slices waiting for the publisher warp */
-constexpr int kRowQueue     = 64;             /* completed rows waiting for the finisher warps */
 constexpr int kThreads      = kWorkThreads + 32 + kFinThreads; /* workers, one publisher warp, finishers: 608 */
 constexpr int kWarps        = 32;             /* room for per-warp values in the slice record */
 constexpr int kSliceMax     = 32 * kWorkThreads; /* floats of one row slice: 8 float4 per worker thread */
@@ -102,7 +101,11 @@ struct SampleParams {
     unsigned flags;
 
     /* scratch in global memory (one lane of the context's scratch) */
-    int       *row_counter; /* [n_rows], zero between launches */
+    int       *row_counter; /* [n_rows] slices published per row; zero when the launch starts */
+    int       *ready_rows;  /* [n_rows] grid-wide queue of completed rows: row + 1, 0 = empty */
+    unsigned  *q_ctr;       /* {tickets reserved, tickets claimed}, zero when the launch starts */
+    int       *clear_ptr;   /* the other copy of these control words, zeroed by this launch */
+    int        clear_words;
     SliceRec  *recs;        /* [n_rows * n_slices] */
     Pair      *cands;       /* [n_rows * n_slices, cand_cap] */
     float     *gen_rows;    /* [grid, gen_stride]: a CTA's private copy of one row for the multi-pass path */

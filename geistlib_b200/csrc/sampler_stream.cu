@@ -45,6 +45,23 @@ struct PenEntry {
     float orig;
 };
 
+/* A short, bounded pause between two polls of a flag (the sleep instruction's granularity is far
+ * coarser than the waits here). */
+__device__ __forceinline__ void pause_cycles(int cycles) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < cycles) {
+    }
+}
+
+/* A load that is served by the L2, where the other SMs' atomics and stores land (a cached load can
+ * keep returning an old line of this SM's L1). */
+__device__ __forceinline__ unsigned load_l2(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int load_l2(const int *p) { return (int) load_l2(reinterpret_cast<const unsigned *>(p)); }
+
 /* A set of warps that synchronise on their own named barrier. */
 struct Grp {
     int tid, lane, warp; /* position inside the group */
@@ -107,10 +124,6 @@ struct __align__(16) StreamShared {
     volatile int q_tail; /* mail consumed so far */
     volatile int q_done; /* the worker loop has ended */
     volatile int q_error;
-    /* completed rows, publisher warp -> finisher warps */
-    volatile int r_rows[kRowQueue];
-    volatile int r_head;
-    volatile int r_tail;
     volatile int p_done; /* the publisher has ended */
 };
 
@@ -1139,6 +1152,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
 /* Optional cycle accounting of worker thread 0 (build with -DGB_PROFILE): where one CTA's time goes. */
 #ifdef GB_PROFILE
 __device__ long long g_prof[512][8]; /* [0,256) workers, [256,512) finishers */
+__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #define PROF_INIT()              \
     long long prof_acc[8] = {0}; \
     long long prof_t      = clock64()
@@ -1149,6 +1163,7 @@ __device__ long long g_prof[512][8]; /* [0,256) workers, [256,512) finishers */
         prof_t = t_;                    \
     }
 #define PROF_DONE()                                \
+    prof_acc[7] = gtime();                         \
     if (g.tid == 0 && blockIdx.x < 256) {          \
         for (int i_ = 0; i_ < 8; i_++) {           \
             g_prof[blockIdx.x][i_] = prof_acc[i_]; \
@@ -1167,7 +1182,7 @@ __device__ long long g_prof[512][8]; /* [0,256) workers, [256,512) finishers */
  * counter reports the last slice go to the finisher warps' queue.
  */
 __device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh) {
-    int tail = 0, rhead = 0;
+    int tail = 0;
     for (;;) {
         int avail = 0;
         if (lane == 0) {
@@ -1184,7 +1199,7 @@ __device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh
                     }
                     break;
                 }
-                __nanosleep(32);
+                pause_cycles(60);
             }
             if (avail == 0) {
                 sh->q_error = 1; /* gave up waiting: leave */
@@ -1213,32 +1228,28 @@ __device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh
                 __threadfence(); /* and the other slices' records are visible to whoever saw the last count */
             }
         }
-        const unsigned done = __ballot_sync(0xffffffffu, last);
-        const int      nd   = __popc(done);
-        if (nd > 0) {
-            if (lane == 0) {
-                for (long long spin = 0; spin < (1ll << 31) && rhead + nd - sh->r_tail > kRowQueue; spin++) {
-                    __nanosleep(32);
-                }
+        if (last) {
+            /* the row joins the grid-wide queue of completed rows: reserve a ticket, then fill its
+             * slot; whichever CTA's finisher warps are idle will claim it */
+            const unsigned t = atomicAdd(&p.q_ctr[0], 1u);
+            if (t < (unsigned) p.n_rows) {
+                atomicExch(&p.ready_rows[t], row + 1); /* 0 = empty */
+            } else {
+                sh->q_error = 2; /* the queue tickets do not belong to this launch: never index with them */
             }
-            __syncwarp();
-            if (last) {
-                sh->r_rows[(rhead + __popc(done & ((1u << lane) - 1u))) % kRowQueue] = row;
-            }
-            __threadfence_block();
-            __syncwarp();
-            rhead += nd;
         }
         if (lane == 0) {
-            if (nd > 0) {
-                sh->r_head = rhead;
-            }
             if (nb > 0) {
                 sh->q_tail = tail + nb; /* the mail slots are free again */
             }
             if (avail < 0) {
                 __threadfence_block();
                 sh->p_done = 1;
+#ifdef GB_PROFILE
+                if (blockIdx.x < 256) {
+                    g_prof[256 + blockIdx.x][3] = gtime();
+                }
+#endif
             }
         }
         if (avail < 0) {
@@ -1248,29 +1259,59 @@ __device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh
     }
 }
 
-/* The finisher warps' loop: completed rows arrive through the row queue. */
+/* The finisher warps' loop: they serve completed rows of the whole grid, first come first served. */
 __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared *sh, const FinBuffers &fb) {
-    GroupShared *fs    = &sh->fn;
-    int          rtail = 0;
+    GroupShared *fs = &sh->fn;
 #ifdef GB_PROFILE
     long long facc[8] = {0};
+    facc[6]           = gtime();
 #endif
     for (;;) {
         if (g.tid == 0) {
+            /* Claim the next completed row of the whole grid, if there is one. A ticket is only
+             * claimed once it has been reserved by a publisher that is about to fill the slot, so
+             * the wait below is for a store that is already on its way. This CTA leaves when its
+             * own publisher has ended and nothing is left unclaimed: a row that completes later is
+             * queued by a CTA whose finisher warps are then still here. */
             int row = -1;
-            for (long long spin = 0; spin < (1ll << 31); spin++) {
-                if (sh->r_head != rtail) {
-                    row = sh->r_rows[rtail % kRowQueue];
-                    break;
+            for (long long spin = 0; spin < (1ll << 28); spin++) {
+                const unsigned claimed  = load_l2(&p.q_ctr[1]);
+                const unsigned reserved = load_l2(&p.q_ctr[0]);
+                if ((int) (reserved - claimed) > 0) { /* the two loads are not ordered: never claim past what is reserved */
+                    if (atomicCAS(&p.q_ctr[1], claimed, claimed + 1u) == claimed) {
+                        const unsigned t = claimed;
+                        if (t >= (unsigned) p.n_rows) {
+                            sh->q_error = 2;
+                            row         = -1;
+                            break;
+                        }
+                        for (long long w = 0; w < (1ll << 16) && row < 0; w++) {
+                            row = load_l2(&p.ready_rows[t]) - 1; /* 0 = not filled yet */
+                            if (row < 0) {
+                                pause_cycles(100);
+                            }
+                        }
+                        if (row >= p.n_rows || (row >= 0 && atomicAdd(&p.row_counter[row], 0) != p.n_slices)) {
+                            sh->q_error = 3; /* a queued row must be complete */
+                            row         = -1;
+                        }
+                        if (row < 0) {
+                            row = -1; /* never filled: give up below */
+                            break;
+                        }
+                        break;
+                    }
+                    continue;
                 }
                 if (sh->p_done) {
-                    if (sh->r_head != rtail) {
+                    /* look once more: this CTA's publisher may have queued a row just before it ended */
+                    if ((int) (load_l2(&p.q_ctr[0]) - load_l2(&p.q_ctr[1])) > 0) {
                         continue;
                     }
                     row = -2;
                     break;
                 }
-                __nanosleep(32);
+                pause_cycles(600);
             }
             if (row == -1) {
                 sh->q_error = 1;
@@ -1283,9 +1324,12 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
         const int row = fs->cur_row;
         if (row < 0) {
 #ifdef GB_PROFILE
+            facc[7] = gtime();
             if (g.tid == 0 && blockIdx.x < 256) {
                 for (int i_ = 0; i_ < 8; i_++) {
-                    g_prof[256 + blockIdx.x][i_] = facc[i_];
+                    if (i_ != 3) {
+                        g_prof[256 + blockIdx.x][i_] = facc[i_];
+                    }
                 }
             }
 #endif
@@ -1301,10 +1345,10 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
 #ifdef GB_PROFILE
         facc[4] += clock64() - ft0;
         facc[5] += 1;
+        facc[2] = gtime();
 #endif
         if (g.tid == 0) {
             p.status[row]      = fst;
-            p.row_counter[row] = 0; /* ready for the next launch */
             if (p.rng_out != nullptr && r.rr == p.rows_per_seq - 1) {
                 /* the sequence's generator after all of its rows drew */
                 unsigned long long s = p.rng_in ? p.rng_in[r.seq] : 1ull;
@@ -1313,9 +1357,7 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
                 }
                 p.rng_out[r.seq] = s;
             }
-            sh->r_tail = rtail + 1;
         }
-        rtail++;
         g.sync();
     }
 }
@@ -1342,6 +1384,12 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     const int G        = (int) gridDim.x;
     const int my_count = (int) blockIdx.x < n_items ? (n_items - (int) blockIdx.x + G - 1) / G : 0;
 
+    /* the control words (row counters, queue slots, tickets) of this scratch set exist twice; this
+     * launch uses one copy, which was zeroed during the set's previous use, and zeroes the other */
+    for (int i = (int) blockIdx.x * kThreads + (int) threadIdx.x; i < p.clear_words; i += G * kThreads) {
+        p.clear_ptr[i] = 0;
+    }
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
             mbar_init(&sh->full[s], 1);
@@ -1350,8 +1398,6 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         sh->q_tail  = 0;
         sh->q_done  = 0;
         sh->q_error = 0;
-        sh->r_head  = 0;
-        sh->r_tail  = 0;
         sh->p_done  = 0;
     }
     __syncthreads();
@@ -1464,6 +1510,9 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     int      stage      = 0;
 
     PROF_INIT();
+#ifdef GB_PROFILE
+    prof_acc[3] = gtime();
+#endif
     for (int j = 0; j < my_count; j++) {
         PROF(0); /* loop overhead */
         const ItemCfg *cf   = &sh->cfg[j & 3];
@@ -1657,7 +1706,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                 }
             }
             g.sync();
-            PROF(7);
+            PROF(6);
             const unsigned tkey = ws->tau_key;
             /* back from the ordered key to the float (nothing qualified: +NaN pattern, nothing passes) */
             const float    tau  = __uint_as_float((tkey & 0x80000000u) ? (tkey ^ 0x80000000u) : ~tkey);
@@ -1703,7 +1752,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         g.sync(); /* every candidate / segment store of this slice is ordered before the mail below */
         if (g.tid == 64) {
             for (long long spin = 0; spin < (1ll << 31) && head - sh->q_tail >= kQueue; spin++) {
-                __nanosleep(32);
+                pause_cycles(60);
             }
             Mail m;
             m.row    = row;
