@@ -1259,34 +1259,27 @@ __device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh
     }
 }
 
-/* The finisher warps' loop: they serve completed rows of the whole grid, first come first served. */
+/* The finisher warps' loop: they serve every G-th completed row of the grid. */
 __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared *sh, const FinBuffers &fb) {
-    GroupShared *fs = &sh->fn;
+    GroupShared *fs        = &sh->fn;
+    int          my_ticket = (int) blockIdx.x;
 #ifdef GB_PROFILE
     long long facc[8] = {0};
     facc[6]           = gtime();
 #endif
     for (;;) {
         if (g.tid == 0) {
-            /* Claim the next completed row of the whole grid, if there is one. A ticket is only
-             * claimed once it has been reserved by a publisher that is about to fill the slot, so
-             * the wait below is for a store that is already on its way. This CTA leaves when its
-             * own publisher has ended and nothing is left unclaimed: a row that completes later is
-             * queued by a CTA whose finisher warps are then still here. */
-            int row = -1;
-            for (long long spin = 0; spin < (1ll << 28); spin++) {
-                const unsigned claimed  = load_l2(&p.q_ctr[1]);
-                const unsigned reserved = load_l2(&p.q_ctr[0]);
-                if ((int) (reserved - claimed) > 0) { /* the two loads are not ordered: never claim past what is reserved */
-                    if (atomicCAS(&p.q_ctr[1], claimed, claimed + 1u) == claimed) {
-                        const unsigned t = claimed;
-                        if (t >= (unsigned) p.n_rows) {
-                            sh->q_error = 2;
-                            row         = -1;
-                            break;
-                        }
+            /* Completed rows take tickets in the order they complete; ticket t belongs to the
+             * finisher warps of CTA t % G, so consecutive completions spread over the grid and
+             * nobody contends for a claim. The grid is launched cooperatively (all CTAs are
+             * resident), and the wait for a ticket to be reserved is bounded. */
+            int row = -2;
+            if (my_ticket < p.n_rows) {
+                row = -1;
+                for (long long spin = 0; spin < (1ll << 24); spin++) {
+                    if ((int) load_l2(&p.q_ctr[0]) > my_ticket) {
                         for (long long w = 0; w < (1ll << 16) && row < 0; w++) {
-                            row = load_l2(&p.ready_rows[t]) - 1; /* 0 = not filled yet */
+                            row = load_l2(&p.ready_rows[my_ticket]) - 1; /* 0 = not filled yet */
                             if (row < 0) {
                                 pause_cycles(100);
                             }
@@ -1295,27 +1288,15 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
                             sh->q_error = 3; /* a queued row must be complete */
                             row         = -1;
                         }
-                        if (row < 0) {
-                            row = -1; /* never filled: give up below */
-                            break;
-                        }
                         break;
                     }
-                    continue;
+                    pause_cycles(300);
                 }
-                if (sh->p_done) {
-                    /* look once more: this CTA's publisher may have queued a row just before it ended */
-                    if ((int) (load_l2(&p.q_ctr[0]) - load_l2(&p.q_ctr[1])) > 0) {
-                        continue;
-                    }
-                    row = -2;
-                    break;
+                if (row == -1) {
+                    sh->q_error = 1; /* gave up waiting: leave */
+                    row         = -2;
                 }
-                pause_cycles(600);
-            }
-            if (row == -1) {
-                sh->q_error = 1;
-                row         = -2;
+                my_ticket += (int) gridDim.x;
             }
             __threadfence(); /* the row's records, published by other CTAs, are visible from here on */
             fs->cur_row = row;
@@ -1541,6 +1522,9 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         }
         if (j + 1 < my_count) {
             hid = hist_fetch(&sh->cfg[(j + 1) & 3]); /* in flight while this item is processed */
+        }
+        if (g.tid == 96 && cf->c == 0) {
+            p.status[row] = ST_INTERNAL; /* stands until the row's finisher writes the real status */
         }
 
         /* ---- 1. the slice arrives in its stage; its tail is padded with -inf up to a float4 ---- */
@@ -1810,8 +1794,9 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     if (e != cudaSuccess) {
         return e;
     }
-    sample_stream_kernel<<<grid, kThreads, smem_bytes, stream>>>(p);
-    return cudaGetLastError();
+    /* cooperative: every CTA is resident, which the finisher warps' ticket wait relies on */
+    void *args[] = {const_cast<SampleParams *>(&p)};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(sample_stream_kernel), dim3((unsigned) grid), dim3(kThreads), args, smem_bytes, stream);
 }
 
 } /* namespace gb */
