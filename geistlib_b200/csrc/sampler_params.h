@@ -12,7 +12,7 @@ constexpr int kWorkThreads  = kWorkWarps * 32;
 constexpr int kFinWarps     = 4;              /* warps that finish completed rows */
 constexpr int kFinThreads   = kFinWarps * 32;
 constexpr int kQueue        = 32;             /* finished slices waiting for the publisher warp */
-constexpr int kThreads      = kWorkThreads + 32 + kFinThreads; /* workers, one publisher warp, finishers: 608 */
+constexpr int kThreads      = kWorkThreads + 64 + kFinThreads; /* workers, loader warp, publisher warp, finishers: 640 */
 constexpr int kWarps        = 32;             /* room for per-warp values in the slice record */
 constexpr int kSliceMax     = 32 * kWorkThreads; /* floats of one row slice: 8 float4 per worker thread */
 constexpr int kGroupCap     = 512;            /* group maxima per slice used for the select threshold */

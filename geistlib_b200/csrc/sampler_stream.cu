@@ -125,6 +125,8 @@ struct __align__(16) StreamShared {
     volatile int q_done; /* the worker loop has ended */
     volatile int q_error;
     volatile int p_done; /* the publisher has ended */
+    volatile int l_released; /* items whose stage is free again (workers -> loader) */
+    volatile int l_decoded;  /* items whose configuration is ready (loader -> workers) */
 };
 
 enum Mode { M_ARGMAX, M_TOPK, M_TOPP, M_TEMP };
@@ -1380,16 +1382,116 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         sh->q_done  = 0;
         sh->q_error = 0;
         sh->p_done  = 0;
+        sh->l_released = 0;
+        sh->l_decoded  = 0;
+        sh->wk.n_cand  = 0;
     }
     __syncthreads();
 
+    /* this CTA's items are blockIdx.x + j * G; (row, slice) advance without divisions */
+    const int dr = G / p.n_slices, dc = G - dr * p.n_slices;
+    auto      advance = [&](int &row, int &c) {
+        row += dr;
+        c += dc;
+        if (c >= p.n_slices) {
+            c -= p.n_slices;
+            row++;
+        }
+    };
+
+    /* the loader keeps the ring full: the jj-th item of this CTA goes to stage jj % stages */
+    auto issue = [&](int row, int c, int stage) {
+        const int      s0    = c * p.slice;
+        const int      n     = max(0, min(p.slice, p.V - s0));
+        const unsigned bytes = (unsigned) (n & ~3) * 4u;
+        if (bytes == 0u) {
+            return;
+        }
+        unsigned char       *dst = ring + (size_t) stage * (size_t) p.stage_bytes;
+        const unsigned char *src = reinterpret_cast<const unsigned char *>(p.logits + (size_t) row * (size_t) p.row_stride + s0);
+        mbar_expect_tx(&sh->full[stage], bytes);
+        for (unsigned off = 0; off < bytes; off += 32768u) {
+            bulk_g2s(dst + off, src + off, min(32768u, bytes - off), &sh->full[stage]);
+        }
+    };
+    /* the loader decodes the configuration of an item into shared memory a few items ahead, so that
+     * the worker warps spend no instructions and no memory round trips on it */
+    auto decode = [&](int row, int c, const RawCfg &rc, ItemCfg *o) {
+        const RowCfg r = row_config(p, row, rc, false);
+        o->row         = row;
+        o->c           = c;
+        o->s0          = c * p.slice;
+        o->n           = max(0, min(p.slice, p.V - o->s0));
+        o->mode        = (int) r.mode;
+        o->kq          = r.kq;
+        o->pen_on      = r.pen_on ? 1 : 0;
+        o->H           = r.H;
+        o->E           = r.E;
+        o->seq         = r.seq;
+        o->seq0        = r.seq0;
+        o->inv_t       = r.inv_t;
+        o->rep         = r.rep;
+        o->freq        = r.freq;
+        o->pres        = r.pres;
+        o->lpg         = r.kq <= 40 ? 8 : (r.kq <= 80 ? 4 : (r.kq <= 160 ? 2 : 1)); /* 56 / 112 / 224 / 448 groups */
+    };
+
     if (threadIdx.x >= kWorkThreads && threadIdx.x < kWorkThreads + 32) {
-        publisher_loop((int) threadIdx.x - kWorkThreads, p, sh);
+        /* ============================================================== loader == */
+        /* One lane: bulk copies up to `stages` items ahead of what the workers have released, item
+         * configurations up to three items ahead of it. Every wait is bounded. */
+        if (threadIdx.x != kWorkThreads) {
+            return;
+        }
+        int    irow = (int) blockIdx.x / p.n_slices, ic = (int) blockIdx.x - irow * p.n_slices; /* next item to load */
+        int    drow = irow, dcs = ic;                                                            /* next item to decode */
+        int    issued = 0, decoded = 0, istage = 0;
+        RawCfg raw{};
+        if (my_count > 0) {
+            raw = raw_config(p, drow);
+        }
+        long long idle = 0;
+        while ((p.aligned && issued < my_count) || decoded < my_count) {
+            const int rel  = sh->l_released; /* items whose stage the workers have handed back */
+            bool      work = false;
+            if (p.aligned && issued < my_count && issued < rel + p.stages) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue(irow, ic, istage);
+                advance(irow, ic);
+                istage = istage + 1 == p.stages ? 0 : istage + 1;
+                issued++;
+                work = true;
+            }
+            if (decoded < my_count && decoded < rel + 3) {
+                decode(drow, dcs, raw, &sh->cfg[decoded & 3]);
+                advance(drow, dcs);
+                decoded++;
+                if (decoded < my_count) {
+                    raw = raw_config(p, drow); /* requested now, used on the next turn */
+                }
+                __threadfence_block();
+                sh->l_decoded = decoded;
+                work          = true;
+            }
+            if (!work) {
+                if (++idle > (1ll << 26)) {
+                    sh->q_error = 4; /* the workers stopped releasing stages: leave */
+                    break;
+                }
+                pause_cycles(40);
+            } else {
+                idle = 0;
+            }
+        }
         return;
     }
-    if (threadIdx.x >= kWorkThreads + 32) {
+    if (threadIdx.x >= kWorkThreads + 32 && threadIdx.x < kWorkThreads + 64) {
+        publisher_loop((int) threadIdx.x - kWorkThreads - 32, p, sh);
+        return;
+    }
+    if (threadIdx.x >= kWorkThreads + 64) {
         Grp g;
-        g.tid  = (int) threadIdx.x - kWorkThreads - 32;
+        g.tid  = (int) threadIdx.x - kWorkThreads - 64;
         g.lane = g.tid & 31;
         g.warp = g.tid >> 5;
         g.n    = kFinThreads;
@@ -1409,53 +1511,6 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     g.bar  = 1;
     GroupShared *ws = &sh->wk;
 
-    /* this CTA's items are blockIdx.x + j * G; (row, slice) advance without divisions */
-    const int dr = G / p.n_slices, dc = G - dr * p.n_slices;
-    auto      advance = [&](int &row, int &c) {
-        row += dr;
-        c += dc;
-        if (c >= p.n_slices) {
-            c -= p.n_slices;
-            row++;
-        }
-    };
-
-    /* thread 0 keeps the ring full: the jj-th item of this CTA goes to stage jj % stages */
-    auto issue = [&](int row, int c, int stage) {
-        const int      s0    = c * p.slice;
-        const int      n     = max(0, min(p.slice, p.V - s0));
-        const unsigned bytes = (unsigned) (n & ~3) * 4u;
-        if (bytes == 0u) {
-            return;
-        }
-        unsigned char       *dst = ring + (size_t) stage * (size_t) p.stage_bytes;
-        const unsigned char *src = reinterpret_cast<const unsigned char *>(p.logits + (size_t) row * (size_t) p.row_stride + s0);
-        mbar_expect_tx(&sh->full[stage], bytes);
-        for (unsigned off = 0; off < bytes; off += 32768u) {
-            bulk_g2s(dst + off, src + off, min(32768u, bytes - off), &sh->full[stage]);
-        }
-    };
-    /* thread 0 decodes the configuration of an item into shared memory two items ahead, so that
-     * the other warps spend no instructions and no memory round trips on it */
-    auto decode = [&](int row, int c, const RawCfg &rc, ItemCfg *o) {
-        const RowCfg r = row_config(p, row, rc, false);
-        o->row         = row;
-        o->c           = c;
-        o->s0          = c * p.slice;
-        o->n           = max(0, min(p.slice, p.V - o->s0));
-        o->mode        = (int) r.mode;
-        o->kq          = r.kq;
-        o->pen_on      = r.pen_on ? 1 : 0;
-        o->H           = r.H;
-        o->E           = r.E;
-        o->seq         = r.seq;
-        o->seq0        = r.seq0;
-        o->inv_t       = r.inv_t;
-        o->rep         = r.rep;
-        o->freq        = r.freq;
-        o->pres        = r.pres;
-        o->lpg         = r.kq <= 48 ? 4 : (r.kq <= 96 ? 2 : 1);
-    };
     /* this thread's history id of an item whose configuration is already decoded */
     auto hist_fetch = [&](const ItemCfg *o) {
         int id = 0;
@@ -1466,29 +1521,22 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         return id;
     };
 
-    int    irow = (int) blockIdx.x / p.n_slices, ic = (int) blockIdx.x - irow * p.n_slices; /* next item to load   (thread 0) */
-    int    drow = irow, dcs = ic;                                                            /* next item to decode (thread 0) */
-    int    issued = 0, decoded = 0, head = 0;
-    RawCfg raw{};
-    if (g.tid == 0 && p.aligned) {
-        for (; issued < min(p.stages, my_count); issued++) {
-            issue(irow, ic, issued);
-            advance(irow, ic);
+    /* bounded wait until the loader has decoded item jj */
+    auto wait_decoded = [&](int jj) {
+        for (long long spin = 0; spin < (1ll << 26) && sh->l_decoded <= jj; spin++) {
+            pause_cycles(20);
         }
-    }
-    if (g.tid == 32) { /* a thread of another warp than the one that issues the copies */
-        for (; decoded < min(2, my_count); decoded++) {
-            decode(drow, dcs, raw_config(p, drow), &sh->cfg[decoded & 3]);
-            advance(drow, dcs);
-        }
-        if (decoded < my_count) {
-            raw = raw_config(p, drow); /* in flight; decoded in the first iteration */
-        }
-    }
-    g.sync();
-    int      hid        = my_count > 0 ? hist_fetch(&sh->cfg[0]) : 0;
+        return sh->l_decoded > jj;
+    };
+    int      head       = 0;
+    int      hid        = 0;
+    bool     have_hid   = false;
     unsigned phase_bits = 0u; /* parity of the next wait, one bit per stage */
     int      stage      = 0;
+    if (my_count > 0 && wait_decoded(0)) {
+        hid      = hist_fetch(&sh->cfg[0]);
+        have_hid = true;
+    }
 
     PROF_INIT();
 #ifdef GB_PROFILE
@@ -1496,6 +1544,9 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
 #endif
     for (int j = 0; j < my_count; j++) {
         PROF(0); /* loop overhead */
+        if (!wait_decoded(j)) {
+            break; /* the loader gave up (it has flagged the error) */
+        }
         const ItemCfg *cf   = &sh->cfg[j & 3];
         const int      row  = cf->row;
         const int      s0   = cf->s0;
@@ -1509,19 +1560,12 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         const int      body = p.aligned ? (n & ~3) : 0;
         const int      item = row * p.n_slices + cf->c;
         int            st   = ST_OK;
-        const int      my_hid = hid;
-        if (g.tid == 32) {
-            if (decoded < my_count) { /* item j + 2: its raw values were requested one iteration ago */
-                decode(drow, dcs, raw, &sh->cfg[decoded & 3]);
-                advance(drow, dcs);
-                decoded++;
-                if (decoded < my_count) {
-                    raw = raw_config(p, drow);
-                }
-            }
-        }
-        if (j + 1 < my_count) {
-            hid = hist_fetch(&sh->cfg[(j + 1) & 3]); /* in flight while this item is processed */
+        const int      my_hid      = hid;
+        const bool     my_have_hid = have_hid;
+        have_hid                   = false;
+        if (j + 1 < my_count && sh->l_decoded > j + 1) {
+            hid      = hist_fetch(&sh->cfg[(j + 1) & 3]); /* in flight while this item is processed */
+            have_hid = true;
         }
         if (g.tid == 96 && cf->c == 0) {
             p.status[row] = ST_INTERNAL; /* stands until the row's finisher writes the real status */
@@ -1536,7 +1580,6 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                 }
             }
             if (g.tid == 0) {
-                ws->n_cand  = 0;
                 ws->n_dlist = 0;
                 ws->tau_key = 0xffffffffu;
                 ws->pick    = 0x7fffffff;
@@ -1568,7 +1611,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             r.pres = cf->pres;
             r.hrow = p.hist ? p.hist + (size_t) cf->seq * (size_t) p.hist_stride : nullptr;
             r.erow = p.extra ? p.extra + (size_t) cf->seq0 * (size_t) p.extra_stride : nullptr;
-            st |= apply_penalties(g, sl, s0, n, r, p.V, p.vocab_offset, bitmap, dlist, p.hist_cap, &ws->n_dlist, true, my_hid);
+            st |= apply_penalties(g, sl, s0, n, r, p.V, p.vocab_offset, bitmap, dlist, p.hist_cap, &ws->n_dlist, my_have_hid, my_hid);
         }
         if (p.out_logits != nullptr) {
             float *orow = p.out_logits + (size_t) row * (size_t) p.V + s0;
@@ -1587,11 +1630,8 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             x[i]          = ok ? reinterpret_cast<const float4 *>(sl)[first4 + 32 * i] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
         }
         g.sync(); /* the stage is free again */
-        if (g.tid == 0 && p.aligned && issued < my_count) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            issue(irow, ic, stage);
-            advance(irow, ic);
-            issued++;
+        if (g.tid == 0) {
+            sh->l_released = j + 1; /* the loader may refill this stage */
         }
         PROF(2); /* penalties, registers, release, issue */
 
@@ -1648,11 +1688,11 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                 rec->seg[g.warp] = acc;
             }
         } else {
-            /* top-k / top-p fast path. Groups of 4 / 2 / 1 lanes: 112 / 224 / 448 group maxima per slice.
+            /* top-k / top-p fast path. Groups of 8 / 4 / 2 / 1 lanes: 56 / 112 / 224 / 448 group maxima per slice.
              * tau = kq-th largest group maximum: at least kq entries of the slice are >= tau, so the
              * slice's share of the row's kq best is among the entries it lets through. */
-            const int lpg = cf->lpg;
-            const int Gs  = lpg == 4 ? kWorkThreads / 4 : (lpg == 2 ? kWorkThreads / 2 : kWorkThreads);
+            const int lpg = cf->lpg; /* 8, 4, 2 or 1 lanes per group */
+            const int Gs  = kWorkThreads / lpg;
             float     gv  = bv;
             if (lpg >= 2) {
                 gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 1));
@@ -1660,29 +1700,33 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             if (lpg >= 4) {
                 gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 2));
             }
+            if (lpg >= 8) {
+                gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 4));
+            }
             if ((g.lane & (lpg - 1)) == 0) {
-                sh->gmax[lpg == 4 ? g.tid >> 2 : (lpg == 2 ? g.tid >> 1 : g.tid)] = gv;
+                sh->gmax[g.tid / lpg] = gv;
             }
             if (mode == M_TOPP) {
                 smax = group_max(g, ws, bv); /* its barriers also publish gmax */
             } else {
                 g.sync();
             }
-            PROF(6);
             /* tau = the smallest group maximum that fewer than kq group maxima exceed (ties need no
-             * order: only the value matters). Four threads share one value, each counts a quarter. */
+             * order: only the value matters). Eight threads share one value, each counts an eighth
+             * (Gs / 8 = 7, 14, 28 or 56 values, read as float4 where that divides). */
             const int kth = min(kq, Gs);
-            for (int idx = g.tid; idx < 4 * Gs; idx += g.n) {
-                const int     t    = idx >> 2, part = idx & 3;
-                const float   v    = sh->gmax[t];
-                const float4 *q4   = reinterpret_cast<const float4 *>(sh->gmax) + part * (Gs / 16);
-                int           above = 0;
-                for (int jg = 0; jg < Gs / 16; jg++) {
-                    const float4 o = q4[jg];
-                    above += (o.x > v) + (o.y > v) + (o.z > v) + (o.w > v);
+            const int per = Gs >> 3;
+            for (int idx = g.tid; idx < 8 * Gs; idx += g.n) {
+                const int    t     = idx >> 3, part = idx & 7;
+                const float  v     = sh->gmax[t];
+                const float *q     = sh->gmax + part * per;
+                int          above = 0;
+                for (int jg = 0; jg < per; jg++) {
+                    above += q[jg] > v ? 1 : 0;
                 }
                 above += __shfl_xor_sync(0xffffffffu, above, 1);
                 above += __shfl_xor_sync(0xffffffffu, above, 2);
+                above += __shfl_xor_sync(0xffffffffu, above, 4);
                 unsigned cand_key = (part == 0 && above < kth) ? order_key(v) : 0xffffffffu;
                 cand_key          = __reduce_min_sync(0xffffffffu, cand_key);
                 if (g.lane == 0 && cand_key != 0xffffffffu) {
@@ -1695,23 +1739,49 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             /* back from the ordered key to the float (nothing qualified: +NaN pattern, nothing passes) */
             const float    tau  = __uint_as_float((tkey & 0x80000000u) ? (tkey ^ 0x80000000u) : ~tkey);
             Pair          *gc   = p.cands + (size_t) item * (size_t) p.cand_cap;
-            if (bv >= tau) { /* few threads hold anything that passes */
+            /* which of this thread's 32 entries pass (few threads hold any) */
+            unsigned mask = 0u;
+            if (bv >= tau) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    if (!(fmaxf(fmaxf(x[i].x, x[i].y), fmaxf(x[i].z, x[i].w)) >= tau)) {
-                        continue;
-                    }
+                    mask |= (x[i].x >= tau && li_of(i, 0) < n ? 1u : 0u) << (4 * i);
+                    mask |= (x[i].y >= tau && li_of(i, 1) < n ? 1u : 0u) << (4 * i + 1);
+                    mask |= (x[i].z >= tau && li_of(i, 2) < n ? 1u : 0u) << (4 * i + 2);
+                    mask |= (x[i].w >= tau && li_of(i, 3) < n ? 1u : 0u) << (4 * i + 3);
+                }
+            }
+            PROF(0);
+            /* one shared-memory atomic per warp reserves room for the whole warp's candidates */
+            const int cnt  = __popc(mask);
+            int       incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (g.lane >= o) {
+                    incl += up;
+                }
+            }
+            const int wtot = __shfl_sync(0xffffffffu, incl, 31);
+            int       base = 0;
+            if (g.lane == 0 && wtot > 0) {
+                base = atomicAdd(&ws->n_cand, wtot);
+            }
+            base = __shfl_sync(0xffffffffu, base, 0);
+            if (mask != 0u) {
+                int pos = base + incl - cnt;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
                     const float xs[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
-                        if (xs[q] >= tau && li_of(i, q) < n) {
-                            const int pos = atomicAdd(&ws->n_cand, 1);
+                        if (mask & (1u << (4 * i + q))) {
                             if (pos < p.cand_cap) {
                                 Pair c2;
                                 c2.v    = xs[q];
                                 c2.idx  = s0 + li_of(i, q);
                                 gc[pos] = c2; /* straight to the row's scratch */
                             }
+                            pos++;
                         }
                     }
                 }
@@ -1744,6 +1814,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             m.smax   = smax;
             m.sarg   = sarg;
             m.n_cand = ws->n_cand;
+            ws->n_cand = 0; /* reset by the thread that read it; the next collect is two barriers away */
             m.st     = st;
             m.bulk   = bulk;
             sh->mail[head % kQueue] = m;
