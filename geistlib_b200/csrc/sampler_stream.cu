@@ -1660,7 +1660,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                     const float xs[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
 #pragma unroll
                     for (int q = 3; q >= 0; q--) {
-                        if (xs[q] == smax && li_of(i, q) < n) {
+                        if (xs[q] == smax && li_of(i, q) < n && g.lane + 32 * i < L) {
                             best = s0 + li_of(i, q);
                         }
                     }
@@ -1744,6 +1744,9 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             if (bv >= tau) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
+                    if (!(g.lane + 32 * i < L)) {
+                        continue; /* not this thread's float4: it reads as -inf but must never count */
+                    }
                     mask |= (x[i].x >= tau && li_of(i, 0) < n ? 1u : 0u) << (4 * i);
                     mask |= (x[i].y >= tau && li_of(i, 1) < n ? 1u : 0u) << (4 * i + 1);
                     mask |= (x[i].z >= tau && li_of(i, 2) < n ? 1u : 0u) << (4 * i + 2);
