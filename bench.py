@@ -41,6 +41,9 @@ N_SETS = 8
 SEED = 1234
 # algorithmic bytes per row: logits once + history ids + generator state in/out + token out
 BYTES_PER_ROW = 4 * V + 4 * H + 16 + 4
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload (131.99 MB + 3.91 MB), from the
+# ncu capture summarised under profiles/; a bench run cannot measure it itself.
+NCU_TRAFFIC_BYTES = 135.9e6
 WORKLOAD = ("B=256 rows x V=128256 fp32 logits ~ N(0,2.5^2) with 8 ids/row +12; temperature 0.8, top_k 40, "
             "top_p 0.95 (top_k precedence), repetition penalty 1.1 over 64-token history, 1 draw/row, seed 1234")
 
@@ -323,7 +326,7 @@ def main():
             "config": {"workload": WORKLOAD, "rows_per_gpu": B, "l2": f"inputs rotate over {N_SETS} sets of 131 MB (> 126 MB L2)",
                        "launch": api.plan(V, H), "rows_invalid": bad, "rows_on_slow_path": slow},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "bytes_per_launch": B * BYTES_PER_ROW,
+                         "traffic": NCU_TRAFFIC_BYTES, "traffic_source": "ncu capture of one launch of this workload, see profiles/", "peak_kind": peak_kind, "bytes_per_launch": B * BYTES_PER_ROW,
                          "us_per_launch": per_launch_s * 1e6},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_rows_per_s, "unit": "rows/s", "h2d_bytes_per_step": B * V * 4 + B * 4,
