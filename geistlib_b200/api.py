@@ -127,6 +127,7 @@ PROTOTYPES = {
                                           c_void_p]),
     "geist_b200_batcher_verify": (C.c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t,
                                             C.c_int, C.c_int, c_void_p, c_void_p, c_void_p]),
+    "geist_b200_argmax_rows_static": (C.c_int, [C.c_int, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_void_p]),
     "geist_b200_plan": (C.c_int, [c_size_t, c_size_t, C.POINTER(c_int32), C.POINTER(c_int32), C.POINTER(c_int32),
                                   C.POINTER(c_int32)]),
 }

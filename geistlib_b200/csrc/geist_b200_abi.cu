@@ -25,6 +25,8 @@ cudaError_t launch_merge_sample(const MergeParams &p, cudaStream_t stream);
 cudaError_t launch_accept(const AcceptParams &p, cudaStream_t stream);
 cudaError_t launch_scatter_kept(const int *kept_n, const int *kept_idx, const float *kept_val, int kept_cap, int n_rows, int V, int vocab_offset, float *dense, cudaStream_t stream);
 cudaError_t launch_softmax_rows(const float *logits, long long row_stride, int n_rows, int V, const float *temperature, float *probs, double *sums, cudaStream_t stream);
+int         argmax_rows_static_max_rows(long long n_vocab);
+cudaError_t launch_argmax_rows_static(int device, const float *logits, long long row_stride, int n_rows, int V, int *out, cudaStream_t stream, const char **what);
 cudaError_t launch_post_step(const int *slot, int n_seq, int per_seq, int first, const int *tokens, const int *counts, int *hist, int hist_cap, int *hist_len, long long *hist_total, const unsigned long long *rng_tmp, unsigned long long *rng, cudaStream_t stream);
 } /* namespace gb */
 
@@ -1161,3 +1163,30 @@ extern "C" enum geist_status geist_b200_batcher_verify(struct geist_b200_batcher
     return batcher_run(b, n, sessions, k, fed, logits, row_stride, logits_on_host, append_history, true, accepted, n_out, out_tokens);
 }
 
+
+/* ------------------------------------------------ no-allocation entry -- */
+
+extern "C" enum geist_status geist_b200_argmax_rows_static(int device, const float *logits, size_t row_stride, size_t n_rows, size_t n_vocab, int32_t *out_index, void *stream) {
+    if (logits == nullptr || out_index == nullptr || n_rows == 0 || n_vocab == 0) {
+        return fail(GEIST_E_INVALID_ARG, "argmax_rows_static: logits, out_index, n_rows and n_vocab are required");
+    }
+    if (row_stride < n_vocab) {
+        return fail(GEIST_E_INVALID_ARG, "argmax_rows_static: row_stride %zu < n_vocab %zu", row_stride, n_vocab);
+    }
+    if (n_vocab > (size_t) 0x7fffffff) {
+        return fail(GEIST_E_INVALID_ARG, "argmax_rows_static: n_vocab %zu does not fit int32 ids", n_vocab);
+    }
+    const int max_rows = gb::argmax_rows_static_max_rows((long long) n_vocab);
+    if (n_rows > (size_t) max_rows) {
+        return fail(GEIST_E_INVALID_ARG,
+                    "argmax_rows_static: %zu rows of %zu exceed the built-in scratch (at most %d rows at this vocabulary: 4096 rows and 65536 slices of 8192 floats per call); "
+                    "split the batch or use geist_b200_sample_batch",
+                    n_rows, n_vocab, max_rows);
+    }
+    const char *what = "";
+    cudaError_t e    = gb::launch_argmax_rows_static(device, logits, (long long) row_stride, (int) n_rows, (int) n_vocab, out_index, static_cast<cudaStream_t>(stream), &what);
+    if (e != cudaSuccess) {
+        return fail(e == cudaErrorInvalidDevice ? GEIST_E_INVALID_ARG : GEIST_E_BACKEND, "argmax_rows_static: %s: %s", what, cudaGetErrorString(e));
+    }
+    return GEIST_OK;
+}

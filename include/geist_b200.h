@@ -307,6 +307,22 @@ enum geist_status geist_b200_batcher_verify(struct geist_b200_batcher *b, size_t
 enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history, int32_t *slices_per_row, int32_t *slice,
                                   int32_t *smem_bytes, int32_t *ring_stages);
 
+/* Greedy argmax of n_rows rows [n_rows, n_vocab] (device memory, row_stride floats apart)
+ * into out_index [n_rows] (device memory), ties -> lowest index, WITHOUT allocating: no
+ * context, no cudaMalloc, no growth on larger batches. No counterpart in the reference; it
+ * exists for callers that cannot allocate while they decode (an engine whose arena owns
+ * the whole device, a loop with a fixed per-token footprint, a thread that must stay off
+ * the driver's allocation lock). The scratch is an array built into this library
+ * (528 KB per device), so one call takes at most 4096 rows and at most 65536 slices of
+ * 8192 floats (rows * ceil(n_vocab / 8192)); beyond that it returns GEIST_E_INVALID_ARG
+ * and geist_b200_errmsg() says what would fit. Every call on a device shares that
+ * array: calls that overlap in time (different streams or threads) race and must be
+ * serialised by the caller. The first call on a device looks the array's address up
+ * (set-up; make that call before any stream capture begins). Asynchronous on `stream`
+ * (cudaStream_t as void*, NULL = the legacy default stream). */
+enum geist_status geist_b200_argmax_rows_static(int device, const float *logits, size_t row_stride, size_t n_rows,
+                                                size_t n_vocab, int32_t *out_index, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
