@@ -67,7 +67,7 @@ struct Plan {
     int    slice        = 0;
     int    stage_bytes  = 0;
     int    stages       = 0;
-    int    bitmap_words = 0;
+    int    hist_tmp     = 0;
     int    hist_cap     = 0;
     int    cand_cap     = 0;
     int    fin_cap      = 0;
@@ -95,7 +95,7 @@ bool make_plan(size_t V, size_t hist_max, Plan &pl) {
     pl.n_slices     = (int) n_slices;
     pl.slice        = (int) slice;
     pl.stage_bytes  = (int) round_up(slice * 4, 128);
-    pl.bitmap_words = hist_max ? (int) ((slice + 31) / 32) : 0;
+    pl.hist_tmp     = (int) hist_max;
     pl.hist_cap     = hist_max ? (int) std::min(hist_max, slice) : 0;
     const int caps[] = {256, 224, 192, 160, 128, 96, 64};
     for (int want_stages = 3; want_stages >= 1; want_stages--) {
@@ -103,9 +103,9 @@ bool make_plan(size_t V, size_t hist_max, Plan &pl) {
             /* short slices reserve room for every element, so that "collect everything" cannot overflow */
             const int cand_cap = slice <= 1024 ? (int) round_up(slice, 32) : cap;
             const int fin_cap  = (int) std::max<size_t>(256, std::min<size_t>(n_slices * (size_t) cand_cap, 4096));
-            /* after the ring: shared state | slice bitmap | slice id list | finisher bitmap (16 words) |
+            /* after the ring: shared state | id lists of the slices in flight | in-range ids of one slice | finisher bitmap (16 words) |
              * finisher id list | merged candidates + scratch copy | sorted kept set + its weights */
-            const size_t fixed = gb::sample_stream_fixed_smem() + (size_t) pl.bitmap_words * 4 + (size_t) pl.hist_cap * 8 + 64 + (size_t) std::min(pl.hist_cap, 512) * 8 +
+            const size_t fixed = gb::sample_stream_fixed_smem() + (size_t) (gb::kMaxStages + 1) * (size_t) pl.hist_cap * 4 + round_up((size_t) pl.hist_tmp * 2, 16) + 64 + (size_t) std::min(pl.hist_cap, 512) * 8 +
                                  (size_t) fin_cap * 16 + (size_t) gb::kFastKMax * 12 + 128;
             if (fixed + (size_t) pl.stage_bytes > kSmemMax) {
                 continue;
@@ -318,7 +318,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.slice        = pl.slice;
     p.stage_bytes  = pl.stage_bytes;
     p.stages       = pl.stages;
-    p.bitmap_words = pl.bitmap_words;
+    p.hist_tmp     = pl.hist_tmp;
     p.hist_cap     = pl.hist_cap;
     p.cand_cap     = pl.cand_cap;
     p.fin_cap      = pl.fin_cap;

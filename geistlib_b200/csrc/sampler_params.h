@@ -93,7 +93,7 @@ struct SampleParams {
     int      slice;        /* floats per slice, multiple of 4, <= kSliceMax */
     int      stage_bytes;  /* bytes of one ring stage (multiple of 128, >= 4 * slice) */
     int      stages;       /* ring depth, 1..kMaxStages */
-    int      bitmap_words; /* per-slice id bitmap (0 when no history is given) */
+    int      hist_tmp;     /* ids one row can bring (history + fed tokens); 0 when no history is given */
     int      hist_cap;     /* distinct-id entries reserved per slice */
     int      cand_cap;     /* candidates reserved per slice */
     int      fin_cap;      /* candidates the finisher can merge per row */

@@ -95,15 +95,19 @@ struct __align__(16) GroupShared {
     int       harg[kHistBins]; /* finisher: their first ids */
 };
 
-/* A work item's configuration, decoded once by worker thread 0. */
-struct ItemCfg {
-    int   row, c, s0, n;
-    int   mode, kq, pen_on, lpg;
-    int   H, E, seq, seq0;
+/* float4 of a slice that one worker warp owns: an equal share, rounded up to whole warp steps */
+__host__ __device__ __forceinline__ int share_len(int nv4) { return ((nv4 + kWorkWarps - 1) / kWorkWarps + 31) & ~31; }
+
+/* A work item's configuration, decoded once by the loader warp. */
+struct __align__(16) ItemCfg {
+    int   row, item, s0, n;         /* what the worker warps read, four words at a time */
+    int   mode, kq, flags, lpg;     /* flags: bit 0 = penalties on */
     float inv_t, rep, freq, pres;
+    int   L, nv4, c, st0;           /* float4 per warp, float4 in the slice, slice number, status bits of the id list */
+    int   H, E, seq, seq0;          /* loader only */
 };
 
-/* What a finished slice leaves for the finisher warps to publish. */
+/* What a finished slice leaves for the publisher warp. */
 struct __align__(8) Mail {
     int    row, item;
     float  smax;
@@ -112,21 +116,45 @@ struct __align__(8) Mail {
     double bulk;
 };
 
+/* What the worker warps of one slice add up, each at its own pace. */
+struct __align__(8) SliceAcc {
+    unsigned long long best;    /* (ordered key of the maximum, ~first id): larger word wins */
+    int                n_cand;  /* candidates placed so far */
+    int                arrived; /* worker warps that are done with the slice */
+    int                st;      /* status bits */
+    int                pad;
+    float              wmax[16]; /* per warp: maximum of its part ... */
+    double             wsum[16]; /* ... and its sum of expf((x - that maximum) * inv_t) */
+};
+
+constexpr int kCfgRing  = 8; /* decoded configurations kept */
+constexpr int kListRing = kMaxStages + 1; /* per-slice id lists / accumulators kept: a warp can run at most `stages` slices ahead of another */
+constexpr int kLiBits   = 14; /* an id list entry is (position in the slice) | (count << kLiBits) */
+static_assert(kSliceMax <= (1 << kLiBits), "slice positions must fit the id list entry");
+
 struct __align__(16) StreamShared {
-    unsigned long long full[kMaxStages];
+    unsigned long long full[kMaxStages];  /* the slice has landed (bulk copy -> workers) */
+    unsigned long long empty[kMaxStages]; /* every worker warp has lifted its part (workers -> loader) */
     float              gmax[kGroupCap];
     GroupShared        wk; /* workers */
     GroupShared        fn; /* finishers */
-    ItemCfg            cfg[4]; /* ring: items j .. j+2 of this CTA */
-    /* finished slices, worker thread 0 -> finisher warps */
+    ItemCfg            cfg[kCfgRing];
+    SliceAcc           acc[kListRing];
+    int                n_dl[kListRing]; /* entries of the slice's id list */
+    unsigned           tau_key[2];      /* select threshold of a row's first slice, alternating */
+    unsigned           top_key[2];      /* largest group maximum of that slice, alternating */
+    unsigned           tau_pub;         /* ordered key of the best threshold known for the row in work (only grows) */
+    __align__(16) int  thist[kHistBins]; /* the row's candidates so far, binned by value between threshold and maximum */
+    /* finished slices, worker warps -> publisher warp; slice j of this CTA uses slot j % kQueue */
     Mail         mail[kQueue];
-    volatile int q_head; /* mail written so far */
-    volatile int q_tail; /* mail consumed so far */
-    volatile int q_done; /* the worker loop has ended */
+    volatile int mail_ready[kQueue]; /* j + 1 once the slot holds slice j */
+    volatile int q_tail;    /* mail consumed so far */
+    volatile int q_done;    /* the worker loop has ended */
     volatile int q_error;
-    volatile int p_done; /* the publisher has ended */
-    volatile int l_released; /* items whose stage is free again (workers -> loader) */
-    volatile int l_decoded;  /* items whose configuration is ready (loader -> workers) */
+    volatile int p_done;    /* the publisher has ended */
+    volatile int l_decoded; /* items whose configuration and id list are ready (loader -> workers) */
+    int          w_done;    /* slices every worker warp is done with (workers -> loader) */
+    int          done_warps;
 };
 
 enum Mode { M_ARGMAX, M_TOPK, M_TOPP, M_TEMP };
@@ -915,7 +943,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
         const int    s0c   = cc * p.slice;
         const int    nc    = max(0, min(p.slice, p.V - s0c));
         const int    nv4c  = (nc + 3) >> 2;
-        const int    Lc    = (nv4c + kWorkWarps - 1) / kWorkWarps;
+        const int    Lc    = share_len(nv4c);
         const int    e0    = min(4 * w * Lc, nc);
         const int    e1    = min(4 * min((w + 1) * Lc, nv4c), nc);
         const int    seg_n = max(e1 - e0, 0);
@@ -1171,10 +1199,30 @@ __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u6
             g_prof[blockIdx.x][i_] = prof_acc[i_]; \
         }                                          \
     }
+/* finer accounting of one worker warp (warp 5) */
+__device__ long long g_prof2[256][16];
+#define PROF2_INIT()              \
+    long long prof2_acc[16] = {0}; \
+    long long prof2_t       = clock64()
+#define PROF2(i)                         \
+    if (g.tid == 160) {                  \
+        const long long t_ = clock64();  \
+        prof2_acc[i] += t_ - prof2_t;    \
+        prof2_t = t_;                    \
+    }
+#define PROF2_DONE()                                  \
+    if (g.tid == 160 && blockIdx.x < 256) {           \
+        for (int i_ = 0; i_ < 16; i_++) {             \
+            g_prof2[blockIdx.x][i_] = prof2_acc[i_];  \
+        }                                             \
+    }
 #else
 #define PROF_INIT()
 #define PROF(i)
 #define PROF_DONE()
+#define PROF2_INIT()
+#define PROF2(i)
+#define PROF2_DONE()
 #endif
 
 /*
@@ -1183,33 +1231,35 @@ __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u6
  * scratch, fence, row counter) so that the round trips overlap. Rows whose
  * counter reports the last slice go to the finisher warps' queue.
  */
-__device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh) {
+__device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh, int my_count) {
     int tail = 0;
     for (;;) {
-        int avail = 0;
-        if (lane == 0) {
-            /* bounded wait for mail or for the end of the worker loop */
-            for (long long spin = 0; spin < (1ll << 31); spin++) {
-                avail = sh->q_head - tail;
-                if (avail > 0) {
-                    break;
-                }
-                if (sh->q_done) {
-                    avail = sh->q_head - tail;
-                    if (avail <= 0) {
-                        avail = -1;
-                    }
-                    break;
-                }
-                pause_cycles(60);
+        /* bounded wait for the next slices' mail (slot j % kQueue says j + 1 once slice j is in it),
+         * or for the end of the worker loop */
+        int  avail     = tail < my_count ? 0 : -1;
+        bool done_seen = false;
+        for (long long spin = 0; avail == 0 && spin < (1ll << 31); spin++) {
+            const int      j     = tail + lane;
+            const bool     ready = j < my_count && sh->mail_ready[j % kQueue] == j + 1;
+            const unsigned ball  = __ballot_sync(0xffffffffu, ready);
+            avail                = ball == 0xffffffffu ? 32 : __ffs(~ball) - 1; /* leading run of ready slots */
+            if (avail > 0) {
+                break;
             }
-            if (avail == 0) {
-                sh->q_error = 1; /* gave up waiting: leave */
-                avail       = -1;
+            if (done_seen) {
+                avail = -1; /* the workers have left and nothing more came */
+                break;
             }
+            done_seen = __shfl_sync(0xffffffffu, sh->q_done, 0) != 0;
+            pause_cycles(60);
         }
-        avail = __shfl_sync(0xffffffffu, avail, 0);
-        __threadfence_block(); /* the mail written before q_head moved is readable */
+        if (avail == 0) {
+            if (lane == 0) {
+                sh->q_error = 1; /* gave up waiting: leave */
+            }
+            avail = -1;
+        }
+        __threadfence_block(); /* the mail written before its slot was marked is readable */
         const int nb   = min(avail, 32);
         bool      last = false;
         int       row  = -1;
@@ -1345,27 +1395,216 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
     }
 }
 
+/* ------------------------------------------------- worker warps: helpers -- */
+
+__device__ __forceinline__ float key_to_float(unsigned k) { return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k); }
+
+/* Registers of one worker thread that outlive a slice: the select threshold of the row in work. */
+struct TauState {
+    float tau;     /* a lower bound of the row's kq-th largest value */
+    int   row;     /* the row it belongs to (-1: none) */
+    float lo;      /* candidate histogram: bin = (v - lo) * scale */
+    float scale;   /* 0: no histogram for this row */
+    int   boots;   /* thresholds set so far (selects the alternating words) */
+};
+
+/*
+ * Sets the select threshold of a row on the first slice this CTA sees of it. Called by all
+ * worker threads (two group barriers). bv = the thread's maximum over its share, wkey = the
+ * ordered key of the warp's maximum. Groups of lpg = 8 / 4 / 2 / 1 lanes give 56 / 112 / 224 /
+ * 448 group maxima; tau = the kq-th largest of them, so at least kq entries of this slice alone
+ * are >= tau and tau cannot exceed the row's kq-th largest value.
+ */
+__device__ __noinline__ TauState set_row_threshold(int tid, StreamShared *sh, float bv, unsigned wkey, int lpg, int kq, int row, int boots) {
+    Grp g;
+    g.tid  = tid;
+    g.lane = tid & 31;
+    g.warp = tid >> 5;
+    g.n    = kWorkThreads;
+    g.nw   = kWorkWarps;
+    g.bar  = 1;
+    TauState ts;
+    ts.boots       = boots + 1;
+    const int bsel = boots & 1;
+    const int Gs = kWorkThreads / lpg;
+    float     gv = bv;
+    if (lpg >= 2) {
+        gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 1));
+    }
+    if (lpg >= 4) {
+        gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 2));
+    }
+    if (lpg >= 8) {
+        gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 4));
+    }
+    if ((g.lane & (lpg - 1)) == 0) {
+        sh->gmax[g.tid / lpg] = gv;
+    }
+    if (g.lane == 0) {
+        atomicMax(&sh->top_key[bsel], wkey);
+    }
+    g.sync();
+    if (g.tid == 0) {
+        sh->tau_key[bsel ^ 1] = 0xffffffffu; /* its readers have all passed the barrier above */
+        sh->top_key[bsel ^ 1] = 0u;
+        sh->tau_pub           = 0u;          /* nobody is in the previous row any more */
+    }
+    if (g.tid < kHistBins) {
+        sh->thist[g.tid] = 0;
+    }
+    /* the smallest group maximum that fewer than kq group maxima exceed (ties need no order: only
+     * the value matters). Eight threads share one value, each counts an eighth (7 .. 56 values). */
+    const int kth = min(kq, Gs);
+    const int per = Gs >> 3;
+    for (int idx = g.tid; idx < 8 * Gs; idx += g.n) {
+        const int    t     = idx >> 3, part = idx & 7;
+        const float  v     = sh->gmax[t];
+        const float *q     = sh->gmax + part * per;
+        int          above = 0;
+        for (int jg = 0; jg < per; jg++) {
+            above += q[jg] > v ? 1 : 0;
+        }
+        above += __shfl_xor_sync(0xffffffffu, above, 1);
+        above += __shfl_xor_sync(0xffffffffu, above, 2);
+        above += __shfl_xor_sync(0xffffffffu, above, 4);
+        unsigned cand_key = (part == 0 && above < kth) ? order_key(v) : 0xffffffffu;
+        cand_key          = __reduce_min_sync(0xffffffffu, cand_key);
+        if (g.lane == 0 && cand_key != 0xffffffffu) {
+            atomicMin(&sh->tau_key[bsel], cand_key);
+        }
+    }
+    g.sync();
+    const unsigned tkey = sh->tau_key[bsel];
+    /* nothing qualified: the +NaN pattern, which nothing passes */
+    ts.tau = key_to_float(tkey);
+    ts.row = row;
+    /* the row's candidates are binned between tau and this slice's maximum; whoever writes a
+     * slice's mail reads the bins from the top and raises the threshold for the slices to come
+     * (each thread computes the same map from value to bin) */
+    const float top = key_to_float(sh->top_key[bsel]);
+    ts.lo           = ts.tau;
+    ts.scale        = (top > ts.tau && top - ts.tau < CUDART_INF_F && tkey != 0xffffffffu) ? (float) kHistBins / (top - ts.tau) : 0.0f;
+    return ts;
+}
+
+/*
+ * The warp that arrived last at a slice hands its result to the publisher and, for select rows,
+ * raises the row's threshold from the histogram of the candidates seen so far.
+ */
+__device__ __noinline__ void write_mail(int lane, const SampleParams &p, StreamShared *sh, SliceAcc *acc, int j, int row, int item, int mode, bool sel, int kq, float inv_t,
+                                        float t_lo, float t_scale, bool t_valid) {
+    __threadfence_block();
+    const unsigned long long bw   = acc->best;
+    const float              smax = key_to_float((unsigned) (bw >> 32));
+    const int                sarg = (int) (0xffffffffu - (unsigned) (bw & 0xffffffffull));
+    double                   bulk = 0.0;
+    if (mode == M_TEMP || (mode == M_TOPP && sel)) {
+        /* per-warp sums move from their own maximum to the slice maximum */
+        double f = 0.0;
+        if (lane < kWorkWarps) {
+            const float wm = acc->wmax[lane];
+            f              = wm == -CUDART_INF_F ? 0.0 : acc->wsum[lane] * exp(((double) wm - (double) smax) * (double) inv_t);
+        }
+        if (mode == M_TEMP) {
+            if (lane < kWorkWarps) {
+                p.recs[item].seg[lane] = f;
+            }
+        } else {
+            bulk = warp_sum_d(f);
+        }
+    }
+    if (lane == 0) {
+        for (long long spin = 0; spin < (1ll << 31) && j - sh->q_tail >= kQueue; spin++) {
+            pause_cycles(60);
+        }
+        Mail m;
+        m.row    = row;
+        m.item   = item;
+        m.smax   = smax;
+        m.sarg   = sarg;
+        m.n_cand = acc->n_cand;
+        m.st     = acc->st;
+        m.bulk   = bulk;
+        sh->mail[j % kQueue] = m;
+        /* the accumulators serve slice j + kListRing next; nobody reaches it before this warp has
+         * released the stages in between */
+        acc->best    = 0ull;
+        acc->n_cand  = 0;
+        acc->st      = 0;
+        acc->arrived = 0;
+        __threadfence_block();
+        sh->mail_ready[j % kQueue] = j + 1;
+        atomicMax(&sh->w_done, j + 1);
+    }
+    if (sel && t_scale > 0.0f && t_valid) {
+        /* the lowest bin edge above which at least kq candidates lie, one bin lower to be safe
+         * against rounding at the edge. Lane l holds bins 8 l .. 8 l + 7. */
+        int        c[8];
+        const int4 lo4 = *reinterpret_cast<const int4 *>(&sh->thist[8 * lane]);
+        const int4 hi4 = *reinterpret_cast<const int4 *>(&sh->thist[8 * lane + 4]);
+        c[0] = lo4.x, c[1] = lo4.y, c[2] = lo4.z, c[3] = lo4.w, c[4] = hi4.x, c[5] = hi4.y, c[6] = hi4.z, c[7] = hi4.w;
+        int mine = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            mine += c[i];
+        }
+        int suffix = mine; /* candidates in this lane's bins and all higher ones */
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int dn = __shfl_down_sync(0xffffffffu, suffix, o);
+            if (lane + o < 32) {
+                suffix += dn;
+            }
+        }
+        const unsigned ball = __ballot_sync(0xffffffffu, suffix >= kq);
+        if (ball != 0u && lane == 31 - __clz(ball)) {
+            int run = suffix - mine, b = 8 * lane;
+#pragma unroll
+            for (int i = 7; i >= 0; i--) {
+                run += c[i];
+                if (run >= kq) {
+                    b = 8 * lane + i;
+                    break;
+                }
+            }
+            if (b >= 2) {
+                const float t_new = t_lo + (float) (b - 1) / t_scale;
+                if (t_new > t_lo) {
+                    atomicMax(&sh->tau_pub, order_key(t_new));
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
 /* ------------------------------------------------------------------ kernel -- */
 
 __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid_constant__ SampleParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
 
-    unsigned char *ring   = smem_raw;
-    StreamShared  *sh     = reinterpret_cast<StreamShared *>(smem_raw + (size_t) p.stages * (size_t) p.stage_bytes);
-    unsigned      *bitmap = reinterpret_cast<unsigned *>(sh + 1); /* workers: ids of the slice */
-    PenEntry      *dlist  = reinterpret_cast<PenEntry *>(bitmap + p.bitmap_words);
-    FinBuffers     fb;
+    unsigned char  *ring = smem_raw;
+    StreamShared   *sh   = reinterpret_cast<StreamShared *>(smem_raw + (size_t) p.stages * (size_t) p.stage_bytes);
+    unsigned       *dlr  = reinterpret_cast<unsigned *>(sh + 1);                             /* id lists of the slices in flight */
+    unsigned short *htmp = reinterpret_cast<unsigned short *>(dlr + kListRing * p.hist_cap); /* loader: in-range ids of one slice */
+    FinBuffers      fb;
     fb.dlist_cap = min(p.hist_cap, 512);
-    fb.bitmap    = reinterpret_cast<unsigned *>(dlist + p.hist_cap);
+    fb.bitmap    = reinterpret_cast<unsigned *>(reinterpret_cast<unsigned char *>(htmp) + ((2 * (size_t) p.hist_tmp + 15) & ~(size_t) 15));
     fb.dlist     = reinterpret_cast<PenEntry *>(fb.bitmap + 16);
     fb.fcand     = reinterpret_cast<Pair *>(fb.dlist + fb.dlist_cap); /* merged candidates of one row */
     fb.ftmp      = fb.fcand + p.fin_cap;
     fb.fsort     = fb.ftmp + p.fin_cap;                             /* kFastKMax entries */
     fb.fq        = reinterpret_cast<float *>(fb.fsort + kFastKMax); /* kFastKMax entries */
 
+    /* every CTA takes a contiguous run of the (row, slice) items, so that consecutive items mostly
+     * belong to one row and what a slice learns about its row serves the next ones */
     const int n_items  = p.n_rows * p.n_slices;
     const int G        = (int) gridDim.x;
-    const int my_count = (int) blockIdx.x < n_items ? (n_items - (int) blockIdx.x + G - 1) / G : 0;
+    const int q_items  = n_items / G, r_items = n_items - q_items * G;
+    const int my_first = (int) blockIdx.x * q_items + min((int) blockIdx.x, r_items);
+    const int my_count = q_items + ((int) blockIdx.x < r_items ? 1 : 0);
+    const int row0     = my_first / p.n_slices;
+    const int c0       = my_first - row0 * p.n_slices;
 
     /* the control words (row counters, queue slots, tickets) of this scratch set exist twice; this
      * launch uses one copy, which was zeroed during the set's previous use, and zeroes the other */
@@ -1376,25 +1615,37 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
             mbar_init(&sh->full[s], 1);
+            mbar_init(&sh->empty[s], kWorkWarps);
         }
-        sh->q_head  = 0;
-        sh->q_tail  = 0;
-        sh->q_done  = 0;
-        sh->q_error = 0;
-        sh->p_done  = 0;
-        sh->l_released = 0;
+        for (int i = 0; i < kListRing; i++) {
+            sh->acc[i].best    = 0ull;
+            sh->acc[i].n_cand  = 0;
+            sh->acc[i].arrived = 0;
+            sh->acc[i].st      = 0;
+            sh->n_dl[i]        = 0;
+        }
+        for (int i = 0; i < kQueue; i++) {
+            sh->mail_ready[i] = 0;
+        }
+        sh->tau_key[0] = 0xffffffffu;
+        sh->tau_key[1] = 0xffffffffu;
+        sh->top_key[0] = 0u;
+        sh->top_key[1] = 0u;
+        sh->tau_pub    = 0u;
+        sh->q_tail     = 0;
+        sh->q_done     = 0;
+        sh->q_error    = 0;
+        sh->p_done     = 0;
         sh->l_decoded  = 0;
-        sh->wk.n_cand  = 0;
+        sh->w_done     = 0;
+        sh->done_warps = 0;
     }
     __syncthreads();
 
-    /* this CTA's items are blockIdx.x + j * G; (row, slice) advance without divisions */
-    const int dr = G / p.n_slices, dc = G - dr * p.n_slices;
-    auto      advance = [&](int &row, int &c) {
-        row += dr;
-        c += dc;
-        if (c >= p.n_slices) {
-            c -= p.n_slices;
+    auto advance = [&](int &row, int &c) {
+        c++;
+        if (c == p.n_slices) {
+            c = 0;
             row++;
         }
     };
@@ -1414,17 +1665,20 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             bulk_g2s(dst + off, src + off, min(32768u, bytes - off), &sh->full[stage]);
         }
     };
-    /* the loader decodes the configuration of an item into shared memory a few items ahead, so that
-     * the worker warps spend no instructions and no memory round trips on it */
+    /* an item's configuration is decoded into shared memory a few items ahead, so that the worker
+     * warps spend no instructions and no memory round trips on it */
     auto decode = [&](int row, int c, const RawCfg &rc, ItemCfg *o) {
         const RowCfg r = row_config(p, row, rc, false);
         o->row         = row;
+        o->item        = row * p.n_slices + c;
         o->c           = c;
         o->s0          = c * p.slice;
         o->n           = max(0, min(p.slice, p.V - o->s0));
+        o->nv4         = (o->n + 3) >> 2;
+        o->L           = share_len(o->nv4);
         o->mode        = (int) r.mode;
         o->kq          = r.kq;
-        o->pen_on      = r.pen_on ? 1 : 0;
+        o->flags       = r.pen_on ? 1 : 0;
         o->H           = r.H;
         o->E           = r.E;
         o->seq         = r.seq;
@@ -1433,49 +1687,129 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         o->rep         = r.rep;
         o->freq        = r.freq;
         o->pres        = r.pres;
+        o->st0         = 0;
         o->lpg         = r.kq <= 40 ? 8 : (r.kq <= 80 ? 4 : (r.kq <= 160 ? 2 : 1)); /* 56 / 112 / 224 / 448 groups */
     };
 
     if (threadIdx.x >= kWorkThreads && threadIdx.x < kWorkThreads + 32) {
         /* ============================================================== loader == */
-        /* One lane: bulk copies up to `stages` items ahead of what the workers have released, item
-         * configurations up to three items ahead of it. Every wait is bounded. */
-        if (threadIdx.x != kWorkThreads) {
-            return;
-        }
-        int    irow = (int) blockIdx.x / p.n_slices, ic = (int) blockIdx.x - irow * p.n_slices; /* next item to load */
-        int    drow = irow, dcs = ic;                                                            /* next item to decode */
-        int    issued = 0, decoded = 0, istage = 0;
-        RawCfg raw{};
-        if (my_count > 0) {
+        /* Lane 0 issues the bulk copies as stages come free; the whole warp prepares each item up to
+         * kListRing items ahead of the slowest worker warp: its configuration and the list of the
+         * history ids that fall into the slice, without repeats, each with its count. Every wait is
+         * bounded. */
+        const int lane = (int) threadIdx.x - kWorkThreads;
+        int       irow = row0, ic = c0; /* next item to load */
+        int       drow = row0, dcs = c0; /* next item to decode */
+        int       issued = 0, decoded = 0, istage = 0;
+        RawCfg    raw{};
+        if (lane == 0 && my_count > 0) {
             raw = raw_config(p, drow);
         }
         long long idle = 0;
         while ((p.aligned && issued < my_count) || decoded < my_count) {
-            const int rel  = sh->l_released; /* items whose stage the workers have handed back */
-            bool      work = false;
-            if (p.aligned && issued < my_count && issued < rel + p.stages) {
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                issue(irow, ic, istage);
-                advance(irow, ic);
-                istage = istage + 1 == p.stages ? 0 : istage + 1;
-                issued++;
-                work = true;
-            }
-            if (decoded < my_count && decoded < rel + 3) {
-                decode(drow, dcs, raw, &sh->cfg[decoded & 3]);
-                advance(drow, dcs);
-                decoded++;
-                if (decoded < my_count) {
-                    raw = raw_config(p, drow); /* requested now, used on the next turn */
+            int act = 0;
+            if (lane == 0) {
+                if (p.aligned && issued < my_count) {
+                    bool ok = issued < p.stages;
+                    if (!ok) { /* the stage's previous slice must have been lifted by all worker warps */
+                        ok = mbar_try_wait(&sh->empty[istage], (unsigned) ((issued / p.stages - 1) & 1));
+                    }
+                    if (ok) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        issue(irow, ic, istage);
+                        advance(irow, ic);
+                        istage = istage + 1 == p.stages ? 0 : istage + 1;
+                        act |= 1;
+                    }
                 }
-                __threadfence_block();
-                sh->l_decoded = decoded;
-                work          = true;
+                if (decoded < my_count && decoded < *reinterpret_cast<volatile int *>(&sh->w_done) + kListRing) {
+                    act |= 2;
+                }
             }
-            if (!work) {
+            act = __shfl_sync(0xffffffffu, act, 0);
+            issued += act & 1;
+            if (act & 2) {
+                ItemCfg *o = &sh->cfg[decoded % kCfgRing];
+                if (lane == 0) {
+                    decode(drow, dcs, raw, o);
+                    advance(drow, dcs);
+                    if (decoded + 1 < my_count) {
+                        raw = raw_config(p, drow); /* requested now, used on the next turn */
+                    }
+                }
+                __syncwarp();
+                int nd = 0, ovf = 0;
+                if (o->flags & 1) {
+                    const int  H = o->H, total = o->H + o->E, s0 = o->s0, n = o->n;
+                    const int *hrow = p.hist ? p.hist + (size_t) o->seq * (size_t) p.hist_stride : nullptr;
+                    const int *erow = p.extra ? p.extra + (size_t) o->seq0 * (size_t) p.extra_stride : nullptr;
+                    /* (a) positions of the ids that fall into the slice, repeats included */
+                    int nh = 0;
+                    for (int base = 0; base < total; base += 32) {
+                        const int j  = base + lane;
+                        int       li = -1;
+                        if (j < total) {
+                            const int id = (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset;
+                            if (id >= 0 && id < p.V && id >= s0 && id - s0 < n) {
+                                li = id - s0;
+                            }
+                        }
+                        const unsigned ball = __ballot_sync(0xffffffffu, li >= 0);
+                        if (li >= 0) {
+                            const int pos = nh + __popc(ball & ((1u << lane) - 1u));
+                            if (pos < p.hist_tmp) {
+                                htmp[pos] = (unsigned short) li;
+                            }
+                        }
+                        nh += __popc(ball);
+                    }
+                    if (nh > p.hist_tmp) {
+                        ovf = 1;
+                        nh  = 0;
+                    }
+                    __syncwarp();
+                    /* (b) the first of each run of equal positions enters the list with the run's length */
+                    unsigned *dl = dlr + (size_t) (decoded % kListRing) * (size_t) p.hist_cap;
+                    for (int base = 0; base < nh; base += 32) {
+                        const int i     = base + lane;
+                        int       cnt   = 0;
+                        bool      first = i < nh;
+                        const int mine  = i < nh ? (int) htmp[i] : -1;
+                        for (int k = 0; k < nh; k++) {
+                            const int v = (int) htmp[k];
+                            if (v == mine) {
+                                cnt++;
+                                first = first && k >= i;
+                            }
+                        }
+                        const unsigned ball = __ballot_sync(0xffffffffu, first);
+                        if (first) {
+                            const int pos = nd + __popc(ball & ((1u << lane) - 1u));
+                            if (pos < p.hist_cap) {
+                                dl[pos] = (unsigned) mine | ((unsigned) cnt << kLiBits);
+                            }
+                        }
+                        nd += __popc(ball);
+                    }
+                    if (nd > p.hist_cap) { /* cannot happen when the launcher sized the room */
+                        ovf = 1;
+                        nd  = 0;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    sh->n_dl[decoded % kListRing] = nd;
+                    o->st0                        = ovf ? ST_HIST_OVERFLOW : 0;
+                    __threadfence_block();
+                    sh->l_decoded = decoded + 1;
+                }
+                decoded++;
+            }
+            if (act == 0) {
                 if (++idle > (1ll << 26)) {
-                    sh->q_error = 4; /* the workers stopped releasing stages: leave */
+                    if (lane == 0) {
+                        sh->q_error = 4; /* the workers stopped releasing stages: leave */
+                    }
                     break;
                 }
                 pause_cycles(40);
@@ -1486,7 +1820,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         return;
     }
     if (threadIdx.x >= kWorkThreads + 32 && threadIdx.x < kWorkThreads + 64) {
-        publisher_loop((int) threadIdx.x - kWorkThreads - 32, p, sh);
+        publisher_loop((int) threadIdx.x - kWorkThreads - 32, p, sh, my_count);
         return;
     }
     if (threadIdx.x >= kWorkThreads + 64) {
@@ -1502,6 +1836,12 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     }
 
     /* ================================================================ workers == */
+    /* Every worker warp walks the CTA's slices at its own pace: it owns a fixed share of each slice
+     * (float4 [warp * L, (warp + 1) * L), lanes interleaved), waits for the slice's copy, applies the
+     * penalties that fall into its share, lifts the share into registers, gives the stage back and
+     * runs its passes on registers. Warps meet only in the slice's accumulators (shared-memory
+     * atomics) and, once per row, in the barrier that sets the row's select threshold. The warp
+     * that arrives last at a slice's accumulators writes the slice's mail. */
     Grp g;
     g.tid  = (int) threadIdx.x;
     g.lane = g.tid & 31;
@@ -1509,329 +1849,298 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     g.n    = kWorkThreads;
     g.nw   = kWorkWarps;
     g.bar  = 1;
-    GroupShared *ws = &sh->wk;
 
-    /* this thread's history id of an item whose configuration is already decoded */
-    auto hist_fetch = [&](const ItemCfg *o) {
-        int id = 0;
-        if (o->pen_on && g.tid < o->H + o->E) {
-            id = (g.tid < o->H ? p.hist[(size_t) o->seq * (size_t) p.hist_stride + g.tid] : p.extra[(size_t) o->seq0 * (size_t) p.extra_stride + 1 + g.tid - o->H]) -
-                 p.vocab_offset;
-        }
-        return id;
-    };
-
-    /* bounded wait until the loader has decoded item jj */
+    /* bounded wait until the loader has prepared item jj */
     auto wait_decoded = [&](int jj) {
         for (long long spin = 0; spin < (1ll << 26) && sh->l_decoded <= jj; spin++) {
             pause_cycles(20);
         }
         return sh->l_decoded > jj;
     };
-    int      head       = 0;
-    int      hid        = 0;
-    bool     have_hid   = false;
-    unsigned phase_bits = 0u; /* parity of the next wait, one bit per stage */
+    unsigned phase_bits = 0u; /* parity of the next wait for a copy, one bit per stage */
     int      stage      = 0;
-    if (my_count > 0 && wait_decoded(0)) {
-        hid      = hist_fetch(&sh->cfg[0]);
-        have_hid = true;
-    }
+    TauState ts;
+    ts.tau   = 0.0f;
+    ts.row   = -1;
+    ts.lo    = 0.0f;
+    ts.scale = 0.0f;
+    ts.boots = 0;
 
     PROF_INIT();
+    PROF2_INIT();
 #ifdef GB_PROFILE
     prof_acc[3] = gtime();
 #endif
     for (int j = 0; j < my_count; j++) {
         PROF(0); /* loop overhead */
+        PROF2(0);
         if (!wait_decoded(j)) {
-            break; /* the loader gave up (it has flagged the error) */
+            break; /* the loader gave up (it has flagged the error); every warp stops at the same item */
         }
-        const ItemCfg *cf   = &sh->cfg[j & 3];
-        const int      row  = cf->row;
-        const int      s0   = cf->s0;
-        const int      n    = cf->n;
-        const int      mode = cf->mode;
-        const int      kq   = cf->kq;
-        const float    inv_t = cf->inv_t;
-        const bool     pen_on = cf->pen_on != 0;
-        float         *sl   = reinterpret_cast<float *>(ring + (size_t) stage * (size_t) p.stage_bytes);
-        const int      nv4  = (n + 3) >> 2;
-        const int      body = p.aligned ? (n & ~3) : 0;
-        const int      item = row * p.n_slices + cf->c;
-        int            st   = ST_OK;
-        const int      my_hid      = hid;
-        const bool     my_have_hid = have_hid;
-        have_hid                   = false;
-        if (j + 1 < my_count && sh->l_decoded > j + 1) {
-            hid      = hist_fetch(&sh->cfg[(j + 1) & 3]); /* in flight while this item is processed */
-            have_hid = true;
-        }
-        if (g.tid == 96 && cf->c == 0) {
+        const ItemCfg *cf = &sh->cfg[j % kCfgRing];
+        const int4     c0 = *reinterpret_cast<const int4 *>(&cf->row);   /* row, item, s0, n */
+        const int4     c1 = *reinterpret_cast<const int4 *>(&cf->mode);  /* mode, kq, flags, lpg */
+        const int4     c3 = *reinterpret_cast<const int4 *>(&cf->L);     /* L, nv4, c, st0 */
+        const int      row = c0.x, item = c0.y, s0 = c0.z, n = c0.w;
+        const int      mode = c1.x, kq = c1.y;
+        const bool     pen_on = (c1.z & 1) != 0;
+        const int      L = c3.x, nv4 = c3.y;
+        SliceAcc      *acc   = &sh->acc[j % kListRing];
+        float         *sl    = reinterpret_cast<float *>(ring + (size_t) stage * (size_t) p.stage_bytes);
+        const int      body  = p.aligned ? (n & ~3) : 0;
+        const int      w4lo  = min(g.warp * L, nv4);
+        const int      mine4 = min(L, nv4 - w4lo); /* float4 this warp owns (L is a multiple of 32) */
+        const float   *grow  = p.logits + (size_t) row * (size_t) p.row_stride + s0;
+        int            st    = g.warp == 0 ? c3.w : ST_OK;
+        if (g.tid == 96 && c3.z == 0) {
             p.status[row] = ST_INTERNAL; /* stands until the row's finisher writes the real status */
         }
+        PROF2(1); /* decoded + cfg */
 
-        /* ---- 1. the slice arrives in its stage; its tail is padded with -inf up to a float4 ---- */
-        {
-            if (nv4 * 4 > body) {
-                const float *grow = p.logits + (size_t) row * (size_t) p.row_stride + s0;
-                for (int i = body + g.tid; i < nv4 * 4; i += g.n) {
-                    sl[i] = i < n ? grow[i] : -CUDART_INF_F;
-                }
+        /* ---- 1. the warp's share of the slice is in the stage; the slice's tail is padded with -inf ---- */
+        if (p.aligned) {
+            const unsigned parity = (phase_bits >> stage) & 1u;
+            phase_bits ^= 1u << stage;
+            if (body > 0 && !mbar_wait_bounded(&sh->full[stage], parity)) {
+                st |= ST_LOAD_TIMEOUT;
+                (void) mbar_wait_bounded(&sh->full[stage], parity); /* a second bounded chance for the copy in flight */
             }
-            if (g.tid == 0) {
-                ws->n_dlist = 0;
-                ws->tau_key = 0xffffffffu;
-                ws->pick    = 0x7fffffff;
+            if (nv4 * 4 > body && w4lo + mine4 == nv4 && mine4 > 0 && g.lane < 4) {
+                const int i = body + g.lane; /* the last float4 is not part of the bulk copy */
+                sl[i]       = i < n ? grow[i] : -CUDART_INF_F;
             }
-            if (pen_on) {
-                for (int i = g.tid; i < p.bitmap_words; i += g.n) {
-                    bitmap[i] = 0u;
-                }
+        } else {
+            /* rows off the 16-byte grid: plain loads; before the stage is written again every warp must
+             * have lifted the slice that used it last */
+            if (j >= p.stages && !mbar_wait_bounded(&sh->empty[stage], (unsigned) ((j / p.stages - 1) & 1))) {
+                st |= ST_LOAD_TIMEOUT;
             }
-            if (body > 0) {
-                const unsigned parity = (phase_bits >> stage) & 1u;
-                phase_bits ^= 1u << stage;
-                if (!mbar_wait_bounded(&sh->full[stage], parity)) {
-                    st |= ST_LOAD_TIMEOUT;
-                    (void) mbar_wait_bounded(&sh->full[stage], parity); /* a second bounded chance for the copy in flight */
-                }
+            for (int i = 4 * w4lo + g.lane; i < 4 * (w4lo + mine4); i += 32) {
+                sl[i] = i < n ? grow[i] : -CUDART_INF_F;
             }
-            PROF(1); /* waiting for the slice */
-            g.sync();
         }
+        __syncwarp();
+        PROF(1); /* waiting for the slice */
+        PROF2(2);
 
-        /* ---- 2. penalties in shared memory, then the slice moves to registers ---- */
+        /* ---- 2. penalties on the share (the loader left the slice's distinct ids with their counts) ---- */
         if (pen_on) {
-            RowCfg r;
-            r.H    = cf->H;
-            r.E    = cf->E;
-            r.rep  = cf->rep;
-            r.freq = cf->freq;
-            r.pres = cf->pres;
-            r.hrow = p.hist ? p.hist + (size_t) cf->seq * (size_t) p.hist_stride : nullptr;
-            r.erow = p.extra ? p.extra + (size_t) cf->seq0 * (size_t) p.extra_stride : nullptr;
-            st |= apply_penalties(g, sl, s0, n, r, p.V, p.vocab_offset, bitmap, dlist, p.hist_cap, &ws->n_dlist, my_have_hid, my_hid);
+            const int       nd = sh->n_dl[j % kListRing];
+            const unsigned *dl = dlr + (size_t) (j % kListRing) * (size_t) p.hist_cap;
+            for (int i = g.lane; i < nd; i += 32) {
+                const unsigned e  = dl[i];
+                const int      li = (int) (e & ((1u << kLiBits) - 1u));
+                if ((li >> 2) >= w4lo && (li >> 2) < w4lo + mine4) {
+                    sl[li] = penalise(sl[li], (int) (e >> kLiBits), cf->rep, cf->freq, cf->pres);
+                }
+            }
+            __syncwarp();
         }
         if (p.out_logits != nullptr) {
             float *orow = p.out_logits + (size_t) row * (size_t) p.V + s0;
-            for (int i = g.tid; i < n; i += g.n) {
+            for (int i = 4 * w4lo + g.lane; i < min(4 * (w4lo + mine4), n); i += 32) {
                 orow[i] = sl[i];
             }
         }
-        /* warp w owns float4 [w*L, (w+1)*L) of the slice, lanes interleave: 128 consecutive ids per
-         * step; what a thread does not own reads as -inf, so the passes below need no bounds checks */
-        const int L      = (nv4 + kWorkWarps - 1) / kWorkWarps; /* <= 256 */
-        const int first4 = g.warp * L + g.lane;                  /* this thread's float4 are first4 + 32 i */
-        float4    x[8];
+        /* what a thread does not own reads as -inf, so the passes below need no bounds checks */
+        const int     first4 = w4lo + g.lane; /* this thread's float4 are first4 + 32 i */
+        const float4 *s4     = reinterpret_cast<const float4 *>(sl) + first4;
+        float4        x[8];
+        if (mine4 == 256) { /* the usual case: a full share */
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const bool ok = g.lane + 32 * i < L && first4 + 32 * i < nv4;
-            x[i]          = ok ? reinterpret_cast<const float4 *>(sl)[first4 + 32 * i] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+            for (int i = 0; i < 8; i++) {
+                x[i] = s4[32 * i];
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                x[i] = g.lane + 32 * i < mine4 ? s4[32 * i] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+            }
         }
-        g.sync(); /* the stage is free again */
-        if (g.tid == 0) {
-            sh->l_released = j + 1; /* the loader may refill this stage */
+        __syncwarp();
+        if (g.lane == 0) {
+            mbar_arrive(&sh->empty[stage]); /* this warp is done with the stage */
         }
-        PROF(2); /* penalties, registers, release, issue */
+        PROF(2); /* penalties, registers, release */
+        PROF2(3);
 
-        /* ---- 3. pass 1 on registers: the thread's maximum ---- */
+        /* ---- 3. the share's maximum and its first id ---- */
         float bv = -CUDART_INF_F;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             bv = fmaxf(bv, fmaxf(fmaxf(x[i].x, x[i].y), fmaxf(x[i].z, x[i].w)));
         }
-        /* local index of element q of float4 i */
-        auto li_of = [&](int i, int q) { return 4 * (first4 + 32 * i) + q; };
-
-        const bool fast_sel = kq > 0 && kq <= kFastKMax;
-        SliceRec  *rec      = p.recs + item;
-        float      smax     = bv;
-        int        sarg     = 0;
-        double     bulk     = 0.0;
-
-        if (mode == M_ARGMAX || (mode == M_TOPK && !fast_sel)) {
-            /* maximum first, then only the threads that hold it look for its first id */
-            smax = group_max(g, ws, bv);
-            if (bv == smax) {
-                int best = 0x7fffffff;
-#pragma unroll
-                for (int i = 7; i >= 0; i--) {
-                    const float xs[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
-#pragma unroll
-                    for (int q = 3; q >= 0; q--) {
-                        if (xs[q] == smax && li_of(i, q) < n && g.lane + 32 * i < L) {
-                            best = s0 + li_of(i, q);
-                        }
-                    }
-                }
-                atomicMin(&ws->pick, best);
+        PROF2(4); /* lane max (waits for the loads) */
+        /* bit 4 i + q of a lane's masks stands for element q of its float4 i (ascending ids). `real`
+         * has the bits of the elements this thread owns that exist in the row (not padding). */
+        const int own4 = min(max((mine4 - g.lane + 31) >> 5, 0), 8);
+        unsigned  real = own4 >= 8 ? 0xffffffffu : ((1u << (4 * own4)) - 1u);
+        if ((n & 3) != 0) {
+            const int d = nv4 - 1 - first4; /* distance to the slice's last float4, the only one with padding */
+            if (d >= 0 && (d & 31) == 0 && (d >> 5) < 8) {
+                real &= ~(((0xfu << (n & 3)) & 0xfu) << (4 * (d >> 5)));
             }
-            g.sync();
-            sarg = ws->pick;
-        } else if (mode == M_TEMP) {
-            smax = group_max(g, ws, bv);
-            /* per-warp sums of e_i relative to the SLICE maximum; the finisher rescales to the row
-             * maximum. -inf padding gives exp(-inf) = 0. */
-            const float ref = smax == -CUDART_INF_F ? 0.0f : smax;
-            double      acc = 0.0;
+        }
+        auto           id_of_bit = [&](int b) { return s0 + 4 * (first4 + 32 * (b >> 2)) + (b & 3); };
+        const unsigned bkey      = order_key(bv + 0.0f); /* -0 and +0 are one value, as the comparison of floats has it */
+        const unsigned wkey      = __reduce_max_sync(0xffffffffu, bkey);
+        const float    wmax      = key_to_float(wkey);
+        /* the warp's first id of its maximum matters only if it can be the slice's */
+        if (mine4 > 0 && wkey >= (unsigned) (*reinterpret_cast<volatile unsigned long long *>(&acc->best) >> 32)) {
+            unsigned eq = 0u;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                eq |= (x[i].x == wmax ? 1u : 0u) << (4 * i);
+                eq |= (x[i].y == wmax ? 1u : 0u) << (4 * i + 1);
+                eq |= (x[i].z == wmax ? 1u : 0u) << (4 * i + 2);
+                eq |= (x[i].w == wmax ? 1u : 0u) << (4 * i + 3);
+            }
+            eq &= real;
+            unsigned best = eq != 0u ? (unsigned) id_of_bit(__ffs(eq) - 1) : 0x7fffffffu;
+            best          = __reduce_min_sync(0xffffffffu, best);
+            if (g.lane == 0 && best != 0x7fffffffu) {
+                atomicMax(&acc->best, ((unsigned long long) wkey << 32) | (unsigned long long) (0xffffffffu - best));
+            }
+        }
+        PROF2(5); /* key reduce + first id */
+        PROF2(6);
+
+        const bool  sel   = (mode == M_TOPK || mode == M_TOPP) && kq > 0 && kq <= kFastKMax;
+        const float inv_t = cf->inv_t;
+        if (mode == M_TEMP) {
+            /* sum of e_i relative to the WARP's maximum; the mail writer rescales to the slice maximum and
+             * the finisher to the row maximum. -inf padding gives exp(-inf) = 0. */
+            const float ref = wmax == -CUDART_INF_F ? 0.0f : wmax;
+            double      sum = 0.0;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const float e0 = expf(scaled_arg(x[i].x, ref, inv_t));
                 const float e1 = expf(scaled_arg(x[i].y, ref, inv_t));
                 const float e2 = expf(scaled_arg(x[i].z, ref, inv_t));
                 const float e3 = expf(scaled_arg(x[i].w, ref, inv_t));
-                acc += (double) ((e0 + e1) + (e2 + e3));
+                sum += (double) ((e0 + e1) + (e2 + e3));
             }
-            acc = warp_sum_d(acc);
+            sum = warp_sum_d(sum);
             if (g.lane == 0) {
-                rec->seg[g.warp] = acc;
+                acc->wmax[g.warp] = wmax;
+                acc->wsum[g.warp] = sum;
             }
-        } else {
-            /* top-k / top-p fast path. Groups of 8 / 4 / 2 / 1 lanes: 56 / 112 / 224 / 448 group maxima per slice.
-             * tau = kq-th largest group maximum: at least kq entries of the slice are >= tau, so the
-             * slice's share of the row's kq best is among the entries it lets through. */
-            const int lpg = cf->lpg; /* 8, 4, 2 or 1 lanes per group */
-            const int Gs  = kWorkThreads / lpg;
-            float     gv  = bv;
-            if (lpg >= 2) {
-                gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 1));
-            }
-            if (lpg >= 4) {
-                gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 2));
-            }
-            if (lpg >= 8) {
-                gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 4));
-            }
-            if ((g.lane & (lpg - 1)) == 0) {
-                sh->gmax[g.tid / lpg] = gv;
-            }
-            if (mode == M_TOPP) {
-                smax = group_max(g, ws, bv); /* its barriers also publish gmax */
+        } else if (sel) {
+            /* top-k / top-p fast path. The select threshold tau is a lower bound of the row's kq-th
+             * largest value, so every entry of the row's kq best passes it wherever it lies. It is set
+             * once per row and CTA, on the first slice the CTA sees of the row (all warps meet there);
+             * the other slices of the row reuse it, raised by what the mail writers publish, and need no
+             * barrier. */
+            if (ts.row != row) {
+                ts = set_row_threshold(g.tid, sh, bv, wkey, c1.w, kq, row, ts.boots);
+                PROF(6);
             } else {
-                g.sync();
-            }
-            /* tau = the smallest group maximum that fewer than kq group maxima exceed (ties need no
-             * order: only the value matters). Eight threads share one value, each counts an eighth
-             * (Gs / 8 = 7, 14, 28 or 56 values, read as float4 where that divides). */
-            const int kth = min(kq, Gs);
-            const int per = Gs >> 3;
-            for (int idx = g.tid; idx < 8 * Gs; idx += g.n) {
-                const int    t     = idx >> 3, part = idx & 7;
-                const float  v     = sh->gmax[t];
-                const float *q     = sh->gmax + part * per;
-                int          above = 0;
-                for (int jg = 0; jg < per; jg++) {
-                    above += q[jg] > v ? 1 : 0;
-                }
-                above += __shfl_xor_sync(0xffffffffu, above, 1);
-                above += __shfl_xor_sync(0xffffffffu, above, 2);
-                above += __shfl_xor_sync(0xffffffffu, above, 4);
-                unsigned cand_key = (part == 0 && above < kth) ? order_key(v) : 0xffffffffu;
-                cand_key          = __reduce_min_sync(0xffffffffu, cand_key);
-                if (g.lane == 0 && cand_key != 0xffffffffu) {
-                    atomicMin(&ws->tau_key, cand_key);
+                const unsigned pub = *reinterpret_cast<volatile unsigned *>(&sh->tau_pub);
+                if (pub > order_key(ts.tau)) {
+                    ts.tau = key_to_float(pub);
                 }
             }
-            g.sync();
-            PROF(6);
-            const unsigned tkey = ws->tau_key;
-            /* back from the ordered key to the float (nothing qualified: +NaN pattern, nothing passes) */
-            const float    tau  = __uint_as_float((tkey & 0x80000000u) ? (tkey ^ 0x80000000u) : ~tkey);
-            Pair          *gc   = p.cands + (size_t) item * (size_t) p.cand_cap;
+            const float tau = ts.tau;
+            Pair       *gc  = p.cands + (size_t) item * (size_t) p.cand_cap;
             /* which of this thread's 32 entries pass (few threads hold any) */
             unsigned mask = 0u;
             if (bv >= tau) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    if (!(g.lane + 32 * i < L)) {
-                        continue; /* not this thread's float4: it reads as -inf but must never count */
+                    mask |= (x[i].x >= tau ? 1u : 0u) << (4 * i);
+                    mask |= (x[i].y >= tau ? 1u : 0u) << (4 * i + 1);
+                    mask |= (x[i].z >= tau ? 1u : 0u) << (4 * i + 2);
+                    mask |= (x[i].w >= tau ? 1u : 0u) << (4 * i + 3);
+                }
+                mask &= real; /* what is not this thread's reads as -inf but must never count */
+            }
+            if (__any_sync(0xffffffffu, mask != 0u)) {
+                /* one shared-memory atomic reserves room for the whole warp's candidates */
+                const int cnt  = __popc(mask);
+                int       incl = cnt;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (g.lane >= o) {
+                        incl += up;
                     }
-                    mask |= (x[i].x >= tau && li_of(i, 0) < n ? 1u : 0u) << (4 * i);
-                    mask |= (x[i].y >= tau && li_of(i, 1) < n ? 1u : 0u) << (4 * i + 1);
-                    mask |= (x[i].z >= tau && li_of(i, 2) < n ? 1u : 0u) << (4 * i + 2);
-                    mask |= (x[i].w >= tau && li_of(i, 3) < n ? 1u : 0u) << (4 * i + 3);
                 }
-            }
-            PROF(0);
-            /* one shared-memory atomic per warp reserves room for the whole warp's candidates */
-            const int cnt  = __popc(mask);
-            int       incl = cnt;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int up = __shfl_up_sync(0xffffffffu, incl, o);
-                if (g.lane >= o) {
-                    incl += up;
+                const int wtot = __shfl_sync(0xffffffffu, incl, 31);
+                int       base = 0;
+                if (g.lane == 0) {
+                    base = atomicAdd(&acc->n_cand, wtot);
                 }
-            }
-            const int wtot = __shfl_sync(0xffffffffu, incl, 31);
-            int       base = 0;
-            if (g.lane == 0 && wtot > 0) {
-                base = atomicAdd(&ws->n_cand, wtot);
-            }
-            base = __shfl_sync(0xffffffffu, base, 0);
-            if (mask != 0u) {
+                base    = __shfl_sync(0xffffffffu, base, 0);
                 int pos = base + incl - cnt;
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const float xs[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        if (mask & (1u << (4 * i + q))) {
-                            if (pos < p.cand_cap) {
-                                Pair c2;
-                                c2.v    = xs[q];
-                                c2.idx  = s0 + li_of(i, q);
-                                gc[pos] = c2; /* straight to the row's scratch */
-                            }
-                            pos++;
-                        }
+                for (unsigned m = mask; m != 0u; m &= m - 1u) { /* few threads, one or two bits each */
+                    const int b = __ffs(m) - 1;
+                    /* the value of bit b, picked from the registers by the bits of b */
+                    const int    i4 = b >> 2;
+                    const float4 h0 = (i4 & 1) ? x[1] : x[0], h1 = (i4 & 1) ? x[3] : x[2], h2 = (i4 & 1) ? x[5] : x[4], h3 = (i4 & 1) ? x[7] : x[6];
+                    const float4 q0 = (i4 & 2) ? h1 : h0, q1 = (i4 & 2) ? h3 : h2;
+                    const float4 f4 = (i4 & 4) ? q1 : q0;
+                    const float  lo = (b & 1) ? f4.y : f4.x, hi = (b & 1) ? f4.w : f4.z;
+                    const float  cv = (b & 2) ? hi : lo;
+                    if (pos < p.cand_cap) {
+                        Pair c2;
+                        c2.v    = cv;
+                        c2.idx  = id_of_bit(b);
+                        gc[pos] = c2; /* straight to the row's scratch */
+                    }
+                    pos++;
+                    if (ts.scale > 0.0f) {
+                        atomicAdd(&sh->thist[min(kHistBins - 1, max(0, __float2int_rz((cv - ts.lo) * ts.scale)))], 1);
                     }
                 }
             }
             if (mode == M_TOPP) {
-                /* everything below tau is summed here; -inf padding adds exp(-inf) = 0 */
-                const float ref = smax == -CUDART_INF_F ? 0.0f : smax;
+                /* everything below tau is summed here, relative to the warp's maximum */
+                const float ref = wmax == -CUDART_INF_F ? 0.0f : wmax;
+                double      sum = 0.0;
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     const float e0 = x[i].x >= tau ? 0.0f : expf(scaled_arg(x[i].x, ref, inv_t));
                     const float e1 = x[i].y >= tau ? 0.0f : expf(scaled_arg(x[i].y, ref, inv_t));
                     const float e2 = x[i].z >= tau ? 0.0f : expf(scaled_arg(x[i].z, ref, inv_t));
                     const float e3 = x[i].w >= tau ? 0.0f : expf(scaled_arg(x[i].w, ref, inv_t));
-                    bulk += (double) ((e0 + e1) + (e2 + e3));
+                    sum += (double) ((e0 + e1) + (e2 + e3));
                 }
-                bulk = group_sum_d(g, ws, bulk);
+                sum = warp_sum_d(sum);
+                if (g.lane == 0) {
+                    acc->wmax[g.warp] = wmax;
+                    acc->wsum[g.warp] = sum;
+                }
             }
         }
         PROF(4); /* the passes */
+        PROF2(7);
 
-        /* ---- 4. hand the slice's result to the finisher warps; they publish it ---- */
-        g.sync(); /* every candidate / segment store of this slice is ordered before the mail below */
-        if (g.tid == 64) {
-            for (long long spin = 0; spin < (1ll << 31) && head - sh->q_tail >= kQueue; spin++) {
-                pause_cycles(60);
+        /* ---- 4. arrive at the slice; the last warp hands the slice's result to the publisher ---- */
+        st = __reduce_or_sync(0xffffffffu, (unsigned) st);
+        int last = 0;
+        if (g.lane == 0) {
+            if (st != 0) {
+                atomicOr(&acc->st, st);
             }
-            Mail m;
-            m.row    = row;
-            m.item   = item;
-            m.smax   = smax;
-            m.sarg   = sarg;
-            m.n_cand = ws->n_cand;
-            ws->n_cand = 0; /* reset by the thread that read it; the next collect is two barriers away */
-            m.st     = st;
-            m.bulk   = bulk;
-            sh->mail[head % kQueue] = m;
-            __threadfence_block();
-            head++;
-            sh->q_head = head;
+            __threadfence_block(); /* this warp's candidates and sums are ordered before its arrival */
+            last = atomicAdd(&acc->arrived, 1) == kWorkWarps - 1 ? 1 : 0;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        PROF2(8); /* arrive */
+        if (last) {
+            write_mail(g.lane, p, sh, acc, j, row, item, mode, sel, kq, inv_t, ts.lo, ts.scale, ts.row == row);
         }
         PROF(5); /* mail */
+        PROF2(9);
         stage = stage + 1 == p.stages ? 0 : stage + 1;
     }
     PROF_DONE();
-    if (g.tid == 64) {
+    PROF2_DONE();
+    if (g.lane == 0) {
         __threadfence_block();
-        sh->q_done = 1;
+        if (atomicAdd(&sh->done_warps, 1) == kWorkWarps - 1) {
+            sh->q_done = 1;
+        }
     }
 }
 
@@ -1860,6 +2169,7 @@ static cudaError_t ensure_attributes(size_t smem_bytes) {
 }
 
 #ifdef GB_PROFILE
+extern "C" int geist_b200_debug_prof2(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof2, sizeof(long long) * 256 * 16); }
 extern "C" int geist_b200_debug_prof(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 512 * 8); }
 #endif
 
