@@ -40,6 +40,10 @@
 
 namespace gb {
 
+#ifndef GB_FIN_PAUSE
+#define GB_FIN_PAUSE 60
+#endif
+
 struct PenEntry {
     int   li;
     float orig;
@@ -61,6 +65,20 @@ __device__ __forceinline__ unsigned load_l2(const unsigned *p) {
     return v;
 }
 __device__ __forceinline__ int load_l2(const int *p) { return (int) load_l2(reinterpret_cast<const unsigned *>(p)); }
+
+#ifdef GB_PROFILE
+__device__ long long g_prof3[256][16]; /* finisher thread 0: cycles per phase, summed over its rows */
+#define FPROF_INIT() long long fprof_t = clock64()
+#define FPROF(i)                                              \
+    if (g.tid == 0 && blockIdx.x < 256) {                     \
+        const long long t_ = clock64();                       \
+        g_prof3[blockIdx.x][i] += t_ - fprof_t;               \
+        fprof_t = t_;                                         \
+    }
+#else
+#define FPROF_INIT()
+#define FPROF(i)
+#endif
 
 /* A set of warps that synchronise on their own named barrier. */
 struct Grp {
@@ -127,6 +145,7 @@ struct __align__(8) SliceAcc {
     double             wsum[16]; /* ... and its sum of expf((x - that maximum) * inv_t) */
 };
 
+constexpr int kFinQueue = 64; /* completed rows waiting for this CTA's finisher warps */
 constexpr int kCfgRing  = 8; /* decoded configurations kept */
 constexpr int kListRing = kMaxStages + 1; /* per-slice id lists / accumulators kept: a warp can run at most `stages` slices ahead of another */
 constexpr int kLiBits   = 14; /* an id list entry is (position in the slice) | (count << kLiBits) */
@@ -152,6 +171,9 @@ struct __align__(16) StreamShared {
     volatile int q_done;    /* the worker loop has ended */
     volatile int q_error;
     volatile int p_done;    /* the publisher has ended */
+    volatile int fin_q[kFinQueue]; /* rows this CTA completed, publisher -> finisher warps */
+    volatile int fin_head;  /* rows queued so far */
+    volatile int fin_tail;  /* rows taken so far */
     volatile int l_decoded; /* items whose configuration and id list are ready (loader -> workers) */
     int          w_done;    /* slices every worker warp is done with (workers -> loader) */
     int          done_warps;
@@ -725,8 +747,11 @@ struct FinBuffers {
 
 /* What the finisher warps request from global scratch the moment a row is theirs, so that it
  * travels while the row's configuration is still being read. */
-constexpr int kSpec      = 48; /* candidates per slice fetched before their count is known */
-constexpr int kSpecSlots = 8;  /* per finisher thread */
+constexpr int kSpecSlots = 8; /* per finisher thread: candidates fetched before the slices' counts are known */
+/* how many of each slice's candidates that is (0: the row has too many slices) */
+__device__ __forceinline__ int spec_per_slice(const SampleParams &p) {
+    return p.n_slices * 48 <= kFinThreads * kSpecSlots ? 48 : 0;
+}
 struct Prefetch {
     int4      hdr;              /* slice record header {max, arg, n_cand, st} of slice g.tid */
     long long c[kSpecSlots];    /* candidate (value, id) pairs, flat index g.tid + kFinThreads * m */
@@ -739,13 +764,14 @@ __device__ __forceinline__ Prefetch prefetch_row(const Grp &g, const SampleParam
     if (g.tid < p.n_slices) {
         pf.hdr = __ldcg(reinterpret_cast<const int4 *>(&recs[g.tid]));
     }
-    const int   flat = p.n_slices * kSpec;
+    const int   kSpec = spec_per_slice(p);
+    const int   flat  = p.n_slices * kSpec;
     const Pair *base = p.cands + (size_t) row * (size_t) p.n_slices * (size_t) p.cand_cap;
 #pragma unroll
     for (int m = 0; m < kSpecSlots; m++) {
         const int f = g.tid + kFinThreads * m;
         pf.c[m]     = 0;
-        if (f < flat && flat <= kFinThreads * kSpecSlots) {
+        if (f < flat) {
             const int cc = f / kSpec, i = f - cc * kSpec;
             pf.c[m]      = __ldcg(reinterpret_cast<const long long *>(base + (size_t) cc * (size_t) p.cand_cap + i));
         }
@@ -803,6 +829,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
     int            *kept_i = p.kept_cap > 0 ? p.kept_idx + (size_t) row * (size_t) p.kept_cap : nullptr;
     float          *kept_v = p.kept_cap > 0 ? p.kept_val + (size_t) row * (size_t) p.kept_cap : nullptr;
     int             st     = 0;
+    FPROF_INIT();
 
     /* slice headers into shared memory; every thread then derives the row's maximum, its first id,
      * the status bits and the candidate totals from them */
@@ -1018,11 +1045,13 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
         return st;
     }
 
+    FPROF(2); /* headers, row maximum */
     /* ---- top-k and top-p: merge the slices' candidates ---- */
     bool need_multipass = !(r.kq > 0 && r.kq <= kFastKMax) || !small_row || overflow || total > p.fin_cap || total < r.kq;
     if (!need_multipass) {
         /* place the pre-fetched candidates, then fetch what the pre-fetch did not cover */
-        const bool spec = p.n_slices * kSpec <= kFinThreads * kSpecSlots;
+        const int  kSpec = spec_per_slice(p);
+        const bool spec  = kSpec > 0;
         if (spec) {
 #pragma unroll
             for (int m = 0; m < kSpecSlots; m++) {
@@ -1061,9 +1090,11 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
             }
         }
         g.sync();
+        FPROF(3); /* candidates into shared memory */
         if (r.mode == M_TOPK) {
             const int k = r.k;
             select_sorted(g, sh, fb.fcand, total, k, fb.ftmp, fb.fsort);
+            FPROF(4); /* select + order */
             if (r.select_only) {
                 for (int i = g.tid; i < min(k, p.kept_cap); i += g.n) {
                     kept_i[i] = fb.fsort[i].idx + p.vocab_offset;
@@ -1102,6 +1133,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
                 }
             }
             g.sync();
+            FPROF(5); /* weights, draw, outputs */
             return st;
         }
 
@@ -1280,14 +1312,22 @@ __device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh
                 __threadfence(); /* and the other slices' records are visible to whoever saw the last count */
             }
         }
-        if (last) {
-            /* the row joins the grid-wide queue of completed rows: reserve a ticket, then fill its
-             * slot; whichever CTA's finisher warps are idle will claim it */
-            const unsigned t = atomicAdd(&p.q_ctr[0], 1u);
-            if (t < (unsigned) p.n_rows) {
-                atomicExch(&p.ready_rows[t], row + 1); /* 0 = empty */
-            } else {
-                sh->q_error = 2; /* the queue tickets do not belong to this launch: never index with them */
+        /* The CTA whose slice completes a row finishes that row. Every CTA owns a contiguous run of
+         * items, so it completes the rows that end inside its run (the CTA that holds a row's first
+         * part is through with it long before), and the finishing work spreads evenly by itself. */
+        unsigned lasts = __ballot_sync(0xffffffffu, last);
+        while (lasts != 0u) {
+            const int src = __ffs(lasts) - 1;
+            lasts &= lasts - 1u;
+            const int done_row = __shfl_sync(0xffffffffu, row, src);
+            if (lane == 0) {
+                const int h = sh->fin_head;
+                for (long long spin = 0; spin < (1ll << 31) && h - sh->fin_tail >= kFinQueue; spin++) {
+                    pause_cycles(100);
+                }
+                sh->fin_q[h % kFinQueue] = done_row;
+                __threadfence_block();
+                sh->fin_head = h + 1;
             }
         }
         if (lane == 0) {
@@ -1311,49 +1351,44 @@ __device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh
     }
 }
 
-/* The finisher warps' loop: they serve every G-th completed row of the grid. */
+/* The finisher warps' loop: they finish the rows this CTA completed, in the order they completed. */
 __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared *sh, const FinBuffers &fb) {
-    GroupShared *fs        = &sh->fn;
-    int          my_ticket = (int) blockIdx.x;
+    GroupShared *fs = &sh->fn;
+    FPROF_INIT();
 #ifdef GB_PROFILE
     long long facc[8] = {0};
     facc[6]           = gtime();
 #endif
     for (;;) {
         if (g.tid == 0) {
-            /* Completed rows take tickets in the order they complete; ticket t belongs to the
-             * finisher warps of CTA t % G, so consecutive completions spread over the grid and
-             * nobody contends for a claim. The grid is launched cooperatively (all CTAs are
-             * resident), and the wait for a ticket to be reserved is bounded. */
-            int row = -2;
-            if (my_ticket < p.n_rows) {
-                row = -1;
-                for (long long spin = 0; spin < (1ll << 24); spin++) {
-                    if ((int) load_l2(&p.q_ctr[0]) > my_ticket) {
-                        for (long long w = 0; w < (1ll << 16) && row < 0; w++) {
-                            row = load_l2(&p.ready_rows[my_ticket]) - 1; /* 0 = not filled yet */
-                            if (row < 0) {
-                                pause_cycles(100);
-                            }
-                        }
-                        if (row >= p.n_rows || (row >= 0 && atomicAdd(&p.row_counter[row], 0) != p.n_slices)) {
-                            sh->q_error = 3; /* a queued row must be complete */
-                            row         = -1;
-                        }
-                        break;
+            /* bounded wait for the next row this CTA completed, or for the end of the publisher */
+            int row = -1;
+            for (long long spin = 0; spin < (1ll << 31); spin++) {
+                const int t = sh->fin_tail;
+                if (sh->fin_head > t) {
+                    __threadfence_block();
+                    row          = sh->fin_q[t % kFinQueue];
+                    sh->fin_tail = t + 1;
+                    break;
+                }
+                if (sh->p_done) {
+                    if (sh->fin_head > t) {
+                        continue; /* queued just before the publisher left */
                     }
-                    pause_cycles(300);
+                    row = -2;
+                    break;
                 }
-                if (row == -1) {
-                    sh->q_error = 1; /* gave up waiting: leave */
-                    row         = -2;
-                }
-                my_ticket += (int) gridDim.x;
+                pause_cycles(GB_FIN_PAUSE);
             }
-            __threadfence(); /* the row's records, published by other CTAs, are visible from here on */
+            if (row == -1) {
+                sh->q_error = 1; /* gave up waiting: leave */
+                row         = -2;
+            }
+            __threadfence(); /* the row's records, some published by another CTA, are visible from here on */
             fs->cur_row = row;
         }
         g.sync();
+        FPROF(0); /* waiting for a ticket */
         const int row = fs->cur_row;
         if (row < 0) {
 #ifdef GB_PROFILE
@@ -1374,7 +1409,11 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
         const RawCfg   rc  = raw_config(p, row);   /* in flight together with ... */
         const Prefetch pf  = prefetch_row(g, p, row); /* ... the row's slice headers and first candidates */
         RowCfg         r   = row_config(p, row, rc, true);
+        FPROF(1); /* configuration and prefetch requested */
         const int      fst = finish_row(g, p, fs, r, fb, pf);
+#ifdef GB_PROFILE
+        fprof_t = clock64();
+#endif
 #ifdef GB_PROFILE
         facc[4] += clock64() - ft0;
         facc[5] += 1;
@@ -1392,6 +1431,7 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
             }
         }
         g.sync();
+        FPROF(6); /* status, generator */
     }
 }
 
@@ -1636,6 +1676,8 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         sh->q_done     = 0;
         sh->q_error    = 0;
         sh->p_done     = 0;
+        sh->fin_head   = 0;
+        sh->fin_tail   = 0;
         sh->l_decoded  = 0;
         sh->w_done     = 0;
         sh->done_warps = 0;
@@ -1709,25 +1751,29 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         while ((p.aligned && issued < my_count) || decoded < my_count) {
             int act = 0;
             if (lane == 0) {
-                if (p.aligned && issued < my_count) {
-                    bool ok = issued < p.stages;
+                int mine_issued = issued;
+                while (p.aligned && mine_issued < my_count) {
+                    bool ok = mine_issued < p.stages;
                     if (!ok) { /* the stage's previous slice must have been lifted by all worker warps */
-                        ok = mbar_try_wait(&sh->empty[istage], (unsigned) ((issued / p.stages - 1) & 1));
+                        ok = mbar_try_wait(&sh->empty[istage], (unsigned) ((mine_issued / p.stages - 1) & 1));
                     }
-                    if (ok) {
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        issue(irow, ic, istage);
-                        advance(irow, ic);
-                        istage = istage + 1 == p.stages ? 0 : istage + 1;
-                        act |= 1;
+                    if (!ok) {
+                        break;
                     }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    issue(irow, ic, istage);
+                    advance(irow, ic);
+                    istage = istage + 1 == p.stages ? 0 : istage + 1;
+                    mine_issued++;
+                    break; /* one copy per turn keeps the turns short: the items' id lists must not fall behind */
                 }
+                act |= (mine_issued - issued) << 2;
                 if (decoded < my_count && decoded < *reinterpret_cast<volatile int *>(&sh->w_done) + kListRing) {
                     act |= 2;
                 }
             }
             act = __shfl_sync(0xffffffffu, act, 0);
-            issued += act & 1;
+            issued += act >> 2;
             if (act & 2) {
                 ItemCfg *o = &sh->cfg[decoded % kCfgRing];
                 if (lane == 0) {
@@ -2169,6 +2215,13 @@ static cudaError_t ensure_attributes(size_t smem_bytes) {
 }
 
 #ifdef GB_PROFILE
+extern "C" int geist_b200_debug_prof3(long long *out, int clear) {
+    if (clear) {
+        static long long zero[256 * 16];
+        return (int) cudaMemcpyToSymbol(g_prof3, zero, sizeof(zero));
+    }
+    return (int) cudaMemcpyFromSymbol(out, g_prof3, sizeof(long long) * 256 * 16);
+}
 extern "C" int geist_b200_debug_prof2(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof2, sizeof(long long) * 256 * 16); }
 extern "C" int geist_b200_debug_prof(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 512 * 8); }
 #endif
@@ -2178,9 +2231,14 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     if (e != cudaSuccess) {
         return e;
     }
-    /* cooperative: every CTA is resident, which the finisher warps' ticket wait relies on */
+    /* no CTA ever waits for another one, so the grid needs no co-residency */
+#ifdef GB_COOP
     void *args[] = {const_cast<SampleParams *>(&p)};
     return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(sample_stream_kernel), dim3((unsigned) grid), dim3(kThreads), args, smem_bytes, stream);
+#else
+    sample_stream_kernel<<<dim3((unsigned) grid), dim3(kThreads), smem_bytes, stream>>>(p);
+    return cudaGetLastError();
+#endif
 }
 
 } /* namespace gb */
