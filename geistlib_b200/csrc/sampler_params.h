@@ -7,15 +7,22 @@
 
 namespace gb {
 
-constexpr int kWorkWarps    = 14;             /* warps that stream slices */
+#ifndef GB_WORK_WARPS
+#define GB_WORK_WARPS 14
+#endif
+#ifndef GB_FIN_WARPS
+#define GB_FIN_WARPS 4
+#endif
+constexpr int kWorkWarps    = GB_WORK_WARPS;  /* warps that stream slices */
 constexpr int kWorkThreads  = kWorkWarps * 32;
-constexpr int kFinWarps     = 4;              /* warps that finish completed rows */
+constexpr int kFinWarps     = GB_FIN_WARPS;   /* warps that finish completed rows */
 constexpr int kFinThreads   = kFinWarps * 32;
 constexpr int kQueue        = 32;             /* finished slices waiting for the publisher warp */
 constexpr int kThreads      = kWorkThreads + 64 + kFinThreads; /* workers, loader warp, publisher warp, finishers: 640 */
 constexpr int kWarps        = 32;             /* room for per-warp values in the slice record */
-constexpr int kSliceMax     = 32 * kWorkThreads; /* floats of one row slice: 8 float4 per worker thread */
-constexpr int kGroupCap     = 512;            /* group maxima per slice used for the select threshold */
+constexpr int kSliceMax     = 14336;          /* floats of one row slice: at most 8 float4 per worker thread */
+static_assert(kSliceMax <= 32 * kWorkThreads, "a worker thread holds at most 8 float4 of a slice");
+constexpr int kGroupCap     = 1024;           /* group maxima per slice used for the select threshold */
 constexpr int kTopKClamp    = 8192;           /* sampler.c:212-215 */
 constexpr int kFastKMax     = 256;            /* largest k served by the threshold fast path */
 constexpr int kNucleusProbe = 32;             /* entries the top-p fast path looks at */

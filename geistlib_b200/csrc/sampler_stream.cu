@@ -141,8 +141,8 @@ struct __align__(8) SliceAcc {
     int                arrived; /* worker warps that are done with the slice */
     int                st;      /* status bits */
     int                pad;
-    float              wmax[16]; /* per warp: maximum of its part ... */
-    double             wsum[16]; /* ... and its sum of expf((x - that maximum) * inv_t) */
+    float              wmax[32]; /* per warp: maximum of its part ... */
+    double             wsum[32]; /* ... and its sum of expf((x - that maximum) * inv_t) */
 };
 
 constexpr int kFinQueue = 64; /* completed rows waiting for this CTA's finisher warps */
@@ -2003,75 +2003,53 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                 x[i] = g.lane + 32 * i < mine4 ? s4[32 * i] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
             }
         }
-        __syncwarp();
-        if (g.lane == 0) {
-            mbar_arrive(&sh->empty[stage]); /* this warp is done with the stage */
-        }
-        PROF(2); /* penalties, registers, release */
+        PROF(2); /* penalties, registers */
         PROF2(3);
 
-        /* ---- 3. the share's maximum and its first id ---- */
+        /* ---- 3. the share's maximum; the few entries that matter are then picked from the stage ---- */
         float bv = -CUDART_INF_F;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             bv = fmaxf(bv, fmaxf(fmaxf(x[i].x, x[i].y), fmaxf(x[i].z, x[i].w)));
         }
         PROF2(4); /* lane max (waits for the loads) */
-        /* bit 4 i + q of a lane's masks stands for element q of its float4 i (ascending ids). `real`
-         * has the bits of the elements this thread owns that exist in the row (not padding). */
-        const int own4 = min(max((mine4 - g.lane + 31) >> 5, 0), 8);
-        unsigned  real = own4 >= 8 ? 0xffffffffu : ((1u << (4 * own4)) - 1u);
-        if ((n & 3) != 0) {
-            const int d = nv4 - 1 - first4; /* distance to the slice's last float4, the only one with padding */
-            if (d >= 0 && (d & 31) == 0 && (d >> 5) < 8) {
-                real &= ~(((0xfu << (n & 3)) & 0xfu) << (4 * (d >> 5)));
+        const unsigned bkey = order_key(bv + 0.0f); /* -0 and +0 are one value, as the comparison of floats has it */
+        const unsigned wkey = __reduce_max_sync(0xffffffffu, bkey);
+        const float    wmax = key_to_float(wkey);
+        /* The 32 entries of lane L, one per lane of the warp: lane l looks at element l & 3 of L's
+         * float4 number l >> 2. `look` says whether that entry exists, is L's own and is no padding. */
+        const int  e4   = g.lane >> 2, eq = g.lane & 3;
+        auto       look = [&](int L_, int &li, float &v) {
+            li            = 4 * (w4lo + L_ + 32 * e4) + eq;
+            const bool ok = L_ + 32 * e4 < mine4 && li < n;
+            v             = ok ? sl[li] : -CUDART_INF_F;
+            return ok;
+        };
+        if (mode == M_ARGMAX) {
+            /* the first id of the warp's maximum; only the lanes that hold the maximum are searched */
+            unsigned best = 0x7fffffffu;
+            for (unsigned hits = __ballot_sync(0xffffffffu, bkey == wkey && g.lane < mine4); hits != 0u; hits &= hits - 1u) {
+                int            li;
+                float          v;
+                const bool     ok = look(__ffs(hits) - 1, li, v);
+                const unsigned eb = __ballot_sync(0xffffffffu, ok && v == wmax);
+                if (eb != 0u) {
+                    best = min(best, (unsigned) (s0 + __shfl_sync(0xffffffffu, li, __ffs(eb) - 1)));
+                }
             }
-        }
-        auto           id_of_bit = [&](int b) { return s0 + 4 * (first4 + 32 * (b >> 2)) + (b & 3); };
-        const unsigned bkey      = order_key(bv + 0.0f); /* -0 and +0 are one value, as the comparison of floats has it */
-        const unsigned wkey      = __reduce_max_sync(0xffffffffu, bkey);
-        const float    wmax      = key_to_float(wkey);
-        /* the warp's first id of its maximum matters only if it can be the slice's */
-        if (mine4 > 0 && wkey >= (unsigned) (*reinterpret_cast<volatile unsigned long long *>(&acc->best) >> 32)) {
-            unsigned eq = 0u;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                eq |= (x[i].x == wmax ? 1u : 0u) << (4 * i);
-                eq |= (x[i].y == wmax ? 1u : 0u) << (4 * i + 1);
-                eq |= (x[i].z == wmax ? 1u : 0u) << (4 * i + 2);
-                eq |= (x[i].w == wmax ? 1u : 0u) << (4 * i + 3);
-            }
-            eq &= real;
-            unsigned best = eq != 0u ? (unsigned) id_of_bit(__ffs(eq) - 1) : 0x7fffffffu;
-            best          = __reduce_min_sync(0xffffffffu, best);
             if (g.lane == 0 && best != 0x7fffffffu) {
                 atomicMax(&acc->best, ((unsigned long long) wkey << 32) | (unsigned long long) (0xffffffffu - best));
             }
+        } else if (g.lane == 0 && mine4 > 0) {
+            atomicMax(&acc->best, (unsigned long long) wkey << 32); /* the maximum alone: no other mode asks where it is */
         }
         PROF2(5); /* key reduce + first id */
         PROF2(6);
 
         const bool  sel   = (mode == M_TOPK || mode == M_TOPP) && kq > 0 && kq <= kFastKMax;
         const float inv_t = cf->inv_t;
-        if (mode == M_TEMP) {
-            /* sum of e_i relative to the WARP's maximum; the mail writer rescales to the slice maximum and
-             * the finisher to the row maximum. -inf padding gives exp(-inf) = 0. */
-            const float ref = wmax == -CUDART_INF_F ? 0.0f : wmax;
-            double      sum = 0.0;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float e0 = expf(scaled_arg(x[i].x, ref, inv_t));
-                const float e1 = expf(scaled_arg(x[i].y, ref, inv_t));
-                const float e2 = expf(scaled_arg(x[i].z, ref, inv_t));
-                const float e3 = expf(scaled_arg(x[i].w, ref, inv_t));
-                sum += (double) ((e0 + e1) + (e2 + e3));
-            }
-            sum = warp_sum_d(sum);
-            if (g.lane == 0) {
-                acc->wmax[g.warp] = wmax;
-                acc->wsum[g.warp] = sum;
-            }
-        } else if (sel) {
+        float       tau   = CUDART_INF_F;
+        if (sel) {
             /* top-k / top-p fast path. The select threshold tau is a lower bound of the row's kq-th
              * largest value, so every entry of the row's kq best passes it wherever it lies. It is set
              * once per row and CTA, on the first slice the CTA sees of the row (all warps meet there);
@@ -2086,63 +2064,54 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                     ts.tau = key_to_float(pub);
                 }
             }
-            const float tau = ts.tau;
-            Pair       *gc  = p.cands + (size_t) item * (size_t) p.cand_cap;
-            /* which of this thread's 32 entries pass (few threads hold any) */
-            unsigned mask = 0u;
-            if (bv >= tau) {
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    mask |= (x[i].x >= tau ? 1u : 0u) << (4 * i);
-                    mask |= (x[i].y >= tau ? 1u : 0u) << (4 * i + 1);
-                    mask |= (x[i].z >= tau ? 1u : 0u) << (4 * i + 2);
-                    mask |= (x[i].w >= tau ? 1u : 0u) << (4 * i + 3);
-                }
-                mask &= real; /* what is not this thread's reads as -inf but must never count */
-            }
-            if (__any_sync(0xffffffffu, mask != 0u)) {
-                /* one shared-memory atomic reserves room for the whole warp's candidates */
-                const int cnt  = __popc(mask);
-                int       incl = cnt;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int up = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (g.lane >= o) {
-                        incl += up;
-                    }
-                }
-                const int wtot = __shfl_sync(0xffffffffu, incl, 31);
-                int       base = 0;
+            tau      = ts.tau;
+            Pair *gc = p.cands + (size_t) item * (size_t) p.cand_cap;
+            /* the lanes whose maximum passes hold all the candidates: their entries are looked at by the
+             * whole warp, one lane after the other (about three per slice and warp) */
+            for (unsigned hits = __ballot_sync(0xffffffffu, bv >= tau && g.lane < mine4); hits != 0u; hits &= hits - 1u) {
+                int            li;
+                float          v;
+                const bool     ok = look(__ffs(hits) - 1, li, v) && v >= tau;
+                const unsigned pb = __ballot_sync(0xffffffffu, ok);
+                int            base = 0;
                 if (g.lane == 0) {
-                    base = atomicAdd(&acc->n_cand, wtot);
+                    base = atomicAdd(&acc->n_cand, __popc(pb));
                 }
-                base    = __shfl_sync(0xffffffffu, base, 0);
-                int pos = base + incl - cnt;
-                for (unsigned m = mask; m != 0u; m &= m - 1u) { /* few threads, one or two bits each */
-                    const int b = __ffs(m) - 1;
-                    /* the value of bit b, picked from the registers by the bits of b */
-                    const int    i4 = b >> 2;
-                    const float4 h0 = (i4 & 1) ? x[1] : x[0], h1 = (i4 & 1) ? x[3] : x[2], h2 = (i4 & 1) ? x[5] : x[4], h3 = (i4 & 1) ? x[7] : x[6];
-                    const float4 q0 = (i4 & 2) ? h1 : h0, q1 = (i4 & 2) ? h3 : h2;
-                    const float4 f4 = (i4 & 4) ? q1 : q0;
-                    const float  lo = (b & 1) ? f4.y : f4.x, hi = (b & 1) ? f4.w : f4.z;
-                    const float  cv = (b & 2) ? hi : lo;
+                base = __shfl_sync(0xffffffffu, base, 0);
+                if (ok) {
+                    const int pos = base + __popc(pb & ((1u << g.lane) - 1u));
                     if (pos < p.cand_cap) {
                         Pair c2;
-                        c2.v    = cv;
-                        c2.idx  = id_of_bit(b);
+                        c2.v    = v;
+                        c2.idx  = s0 + li;
                         gc[pos] = c2; /* straight to the row's scratch */
                     }
-                    pos++;
                     if (ts.scale > 0.0f) {
-                        atomicAdd(&sh->thist[min(kHistBins - 1, max(0, __float2int_rz((cv - ts.lo) * ts.scale)))], 1);
+                        atomicAdd(&sh->thist[min(kHistBins - 1, max(0, __float2int_rz((v - ts.lo) * ts.scale)))], 1);
                     }
                 }
             }
-            if (mode == M_TOPP) {
-                /* everything below tau is summed here, relative to the warp's maximum */
-                const float ref = wmax == -CUDART_INF_F ? 0.0f : wmax;
-                double      sum = 0.0;
+        }
+        __syncwarp();
+        if (g.lane == 0) {
+            mbar_arrive(&sh->empty[stage]); /* this warp is done with the stage */
+        }
+        if (mode == M_TEMP || (mode == M_TOPP && sel)) {
+            /* sum of e_i relative to the WARP's maximum (top-p: of what stays below the threshold); the
+             * mail writer rescales to the slice maximum and the finisher to the row maximum. -inf
+             * padding gives exp(-inf) = 0. */
+            const float ref = wmax == -CUDART_INF_F ? 0.0f : wmax;
+            double      sum = 0.0;
+            if (mode == M_TEMP) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float e0 = expf(scaled_arg(x[i].x, ref, inv_t));
+                    const float e1 = expf(scaled_arg(x[i].y, ref, inv_t));
+                    const float e2 = expf(scaled_arg(x[i].z, ref, inv_t));
+                    const float e3 = expf(scaled_arg(x[i].w, ref, inv_t));
+                    sum += (double) ((e0 + e1) + (e2 + e3));
+                }
+            } else {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     const float e0 = x[i].x >= tau ? 0.0f : expf(scaled_arg(x[i].x, ref, inv_t));
@@ -2151,11 +2120,11 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                     const float e3 = x[i].w >= tau ? 0.0f : expf(scaled_arg(x[i].w, ref, inv_t));
                     sum += (double) ((e0 + e1) + (e2 + e3));
                 }
-                sum = warp_sum_d(sum);
-                if (g.lane == 0) {
-                    acc->wmax[g.warp] = wmax;
-                    acc->wsum[g.warp] = sum;
-                }
+            }
+            sum = warp_sum_d(sum);
+            if (g.lane == 0) {
+                acc->wmax[g.warp] = wmax;
+                acc->wsum[g.warp] = sum;
             }
         }
         PROF(4); /* the passes */
