@@ -479,13 +479,15 @@ __device__ void select_sorted(const Grp &g, GroupShared *sh, const Pair *cand, i
         for (int q = 0; q < 8; q++) {
             mine += sh->bins[8 * g.lane + q];
         }
-        int above = 0; /* entries owned by higher lanes */
-        for (int l = 31; l >= 1; l--) {
-            const int c = __shfl_sync(0xffffffffu, mine, l);
-            if (g.lane < l) {
-                above += c;
+        int suffix = mine; /* entries owned by this lane and all higher ones */
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int dn = __shfl_down_sync(0xffffffffu, suffix, o);
+            if (g.lane + o < 32) {
+                suffix += dn;
             }
         }
+        const int above = suffix - mine; /* entries owned by higher lanes */
         if (above < kq && above + mine >= kq) {
             int acc = above;
             for (int q = 7; q >= 0; q--) {
