@@ -1686,8 +1686,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     };
     /* an item's configuration is decoded into shared memory a few items ahead, so that the worker
      * warps spend no instructions and no memory round trips on it */
-    auto decode = [&](int row, int c, const RawCfg &rc, ItemCfg *o) {
-        const RowCfg r = row_config(p, row, rc, false);
+    auto decode = [&](int row, int c, const RowCfg &r, ItemCfg *o) {
         o->row         = row;
         o->item        = row * p.n_slices + c;
         o->c           = c;
@@ -1724,6 +1723,10 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         if (lane == 0 && my_count > 0) {
             raw = raw_config(p, drow);
         }
+        RowCfg rcur{};
+        int    rcur_row = -1;
+        int hc[4]  = {-1, -1, -1, -1}; /* this lane's share of the first 128 history ids of row hc_row */
+        int hc_row = -1;
         long long idle = 0;
         while ((p.aligned && issued < my_count) || decoded < my_count) {
             int act = 0;
@@ -1754,11 +1757,16 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             if (act & 2) {
                 ItemCfg *o = &sh->cfg[decoded % kCfgRing];
                 if (lane == 0) {
-                    decode(drow, dcs, raw, o);
-                    advance(drow, dcs);
-                    if (decoded + 1 < my_count) {
-                        raw = raw_config(p, drow); /* requested now, used on the next turn */
+                    if (rcur_row != drow) {
+                        /* a new row: its parameters were requested when the previous row began */
+                        rcur     = row_config(p, drow, raw, false);
+                        rcur_row = drow;
+                        if (drow + 1 < p.n_rows) {
+                            raw = raw_config(p, drow + 1); /* requested now, used when the next row begins */
+                        }
                     }
+                    decode(drow, dcs, rcur, o);
+                    advance(drow, dcs);
                 }
                 __syncwarp();
                 int nd = 0, ovf = 0;
@@ -1766,16 +1774,21 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                     const int  H = o->H, total = o->H + o->E, s0 = o->s0, n = o->n;
                     const int *hrow = p.hist ? p.hist + (size_t) o->seq * (size_t) p.hist_stride : nullptr;
                     const int *erow = p.extra ? p.extra + (size_t) o->seq0 * (size_t) p.extra_stride : nullptr;
+                    /* a row's ids are the same for all of its slices: the first 128 stay in registers */
+                    if (hc_row != o->row) {
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const int j = 32 * k + lane;
+                            hc[k]       = j < total ? (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset : -1;
+                        }
+                        hc_row = o->row;
+                    }
                     /* (a) positions of the ids that fall into the slice, repeats included */
-                    int nh = 0;
-                    for (int base = 0; base < total; base += 32) {
-                        const int j  = base + lane;
-                        int       li = -1;
-                        if (j < total) {
-                            const int id = (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset;
-                            if (id >= 0 && id < p.V && id >= s0 && id - s0 < n) {
-                                li = id - s0;
-                            }
+                    int  nh   = 0;
+                    auto take = [&](int id, bool have) {
+                        int li = -1;
+                        if (have && id >= 0 && id < p.V && id >= s0 && id - s0 < n) {
+                            li = id - s0;
                         }
                         const unsigned ball = __ballot_sync(0xffffffffu, li >= 0);
                         if (li >= 0) {
@@ -1785,6 +1798,16 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                             }
                         }
                         nh += __popc(ball);
+                    };
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        if (32 * k < total) {
+                            take(hc[k], 32 * k + lane < total);
+                        }
+                    }
+                    for (int base = 128; base < total; base += 32) {
+                        const int j = base + lane;
+                        take(j < total ? (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset : -1, j < total);
                     }
                     if (nh > p.hist_tmp) {
                         ovf = 1;
