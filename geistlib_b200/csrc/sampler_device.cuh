@@ -93,6 +93,19 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned 
     return ok != 0;
 }
 
+/* Non-blocking test of a phase (try_wait may suspend the thread for a while). */
+__device__ __forceinline__ bool mbar_test(unsigned long long *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+    return ok != 0;
+}
+
 /* Bounded wait. Returns false when the copy never signalled. */
 __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long *bar, unsigned parity) {
     for (int i = 0; i < (1 << 20); i++) {

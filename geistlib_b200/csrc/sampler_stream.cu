@@ -156,6 +156,7 @@ struct __align__(16) StreamShared {
     unsigned           tau_key[2];      /* select threshold of a row's first slice, alternating */
     unsigned           top_key[2];      /* largest group maximum of that slice, alternating */
     unsigned long long tau_pub;         /* (row, ordered key of the best threshold known for it): only grows */
+    int                rowids[128];      /* loader: the ids of the row in preparation */
     __align__(16) int  thist[kHistBins]; /* the row's candidates so far, binned by value between threshold and maximum */
     volatile int slice_done[kListRing]; /* j + 1 once every worker warp is done with slice j (workers -> publisher) */
     float        t_lo, t_scale;         /* the candidate histogram's map from value to bin ... */
@@ -1238,7 +1239,7 @@ __device__ long long g_prof2[256][16];
     }
 #define PROF2_DONE()                                  \
     if (g.tid == 160 && blockIdx.x < 256) {           \
-        for (int i_ = 0; i_ < 16; i_++) {             \
+        for (int i_ = 0; i_ < 12; i_++) {             \
             g_prof2[blockIdx.x][i_] = prof2_acc[i_];  \
         }                                             \
     }
@@ -1725,8 +1726,12 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         }
         RowCfg rcur{};
         int    rcur_row = -1;
-        int hc[4]  = {-1, -1, -1, -1}; /* this lane's share of the first 128 history ids of row hc_row */
+        int hc[4]   = {-1, -1, -1, -1}; /* this lane's share of the history ids of row hc_row ... */
+        int hcnt[4] = {0, 0, 0, 0};     /* ... and how often each occurs, kept by its first occurrence only */
         int hc_row = -1;
+#ifdef GB_PROFILE
+        long long lp_busy = 0, lp_idle = 0, lp_t = clock64();
+#endif
         long long idle = 0;
         while ((p.aligned && issued < my_count) || decoded < my_count) {
             int act = 0;
@@ -1735,7 +1740,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                 while (p.aligned && mine_issued < my_count) {
                     bool ok = mine_issued < p.stages;
                     if (!ok) { /* the stage's previous slice must have been lifted by all worker warps */
-                        ok = mbar_try_wait(&sh->empty[istage], (unsigned) ((mine_issued / p.stages - 1) & 1));
+                        ok = mbar_test(&sh->empty[istage], (unsigned) ((mine_issued / p.stages - 1) & 1)); /* never blocks: the items' preparation must go on */
                     }
                     if (!ok) {
                         break;
@@ -1774,68 +1779,99 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                     const int  H = o->H, total = o->H + o->E, s0 = o->s0, n = o->n;
                     const int *hrow = p.hist ? p.hist + (size_t) o->seq * (size_t) p.hist_stride : nullptr;
                     const int *erow = p.extra ? p.extra + (size_t) o->seq0 * (size_t) p.extra_stride : nullptr;
-                    /* a row's ids are the same for all of its slices: the first 128 stay in registers */
-                    if (hc_row != o->row) {
+                    unsigned  *dl   = dlr + (size_t) (decoded % kListRing) * (size_t) p.hist_cap;
+                    if (total <= 128) {
+                        /* The usual case. A row's ids are the same for all of its slices: once per row
+                         * they are read into registers (four per lane) and each is marked as the first
+                         * of its value with that value's count; a slice then only picks its own. */
+                        if (hc_row != o->row) {
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const int j  = 32 * k + lane;
+                                int       id = j < total ? (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset : -1;
+                                id           = (id >= 0 && id < p.V) ? id : -1 - j; /* unusable ids match nothing */
+                                hc[k]        = id;
+                                sh->rowids[j] = id;
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const int j   = 32 * k + lane;
+                                int       cnt = 0, before = 0;
+                                if (j < total && hc[k] >= 0) {
+                                    for (int q = 0; q < total; q++) {
+                                        const bool same = sh->rowids[q] == hc[k];
+                                        cnt += same ? 1 : 0;
+                                        before += (same && q < j) ? 1 : 0;
+                                    }
+                                }
+                                hcnt[k] = (j < total && hc[k] >= 0 && before == 0) ? cnt : 0; /* 0: not the first of its value */
+                            }
+                            __syncwarp();
+                            hc_row = o->row;
+                        }
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
-                            const int j = 32 * k + lane;
-                            hc[k]       = j < total ? (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset : -1;
-                        }
-                        hc_row = o->row;
-                    }
-                    /* (a) positions of the ids that fall into the slice, repeats included */
-                    int  nh   = 0;
-                    auto take = [&](int id, bool have) {
-                        int li = -1;
-                        if (have && id >= 0 && id < p.V && id >= s0 && id - s0 < n) {
-                            li = id - s0;
-                        }
-                        const unsigned ball = __ballot_sync(0xffffffffu, li >= 0);
-                        if (li >= 0) {
-                            const int pos = nh + __popc(ball & ((1u << lane) - 1u));
-                            if (pos < p.hist_tmp) {
-                                htmp[pos] = (unsigned short) li;
+                            if (32 * k < total) {
+                                const bool     in   = hcnt[k] > 0 && hc[k] >= s0 && hc[k] - s0 < n;
+                                const unsigned ball = __ballot_sync(0xffffffffu, in);
+                                if (in) {
+                                    const int pos = nd + __popc(ball & ((1u << lane) - 1u));
+                                    if (pos < p.hist_cap) {
+                                        dl[pos] = (unsigned) (hc[k] - s0) | ((unsigned) hcnt[k] << kLiBits);
+                                    }
+                                }
+                                nd += __popc(ball);
                             }
                         }
-                        nh += __popc(ball);
-                    };
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        if (32 * k < total) {
-                            take(hc[k], 32 * k + lane < total);
-                        }
-                    }
-                    for (int base = 128; base < total; base += 32) {
-                        const int j = base + lane;
-                        take(j < total ? (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset : -1, j < total);
-                    }
-                    if (nh > p.hist_tmp) {
-                        ovf = 1;
-                        nh  = 0;
-                    }
-                    __syncwarp();
-                    /* (b) the first of each run of equal positions enters the list with the run's length */
-                    unsigned *dl = dlr + (size_t) (decoded % kListRing) * (size_t) p.hist_cap;
-                    for (int base = 0; base < nh; base += 32) {
-                        const int i     = base + lane;
-                        int       cnt   = 0;
-                        bool      first = i < nh;
-                        const int mine  = i < nh ? (int) htmp[i] : -1;
-                        for (int k = 0; k < nh; k++) {
-                            const int v = (int) htmp[k];
-                            if (v == mine) {
-                                cnt++;
-                                first = first && k >= i;
+                    } else {
+                        /* long histories: (a) positions of the ids that fall into the slice, repeats included */
+                        int nh = 0;
+                        for (int base = 0; base < total; base += 32) {
+                            const int j  = base + lane;
+                            int       li = -1;
+                            if (j < total) {
+                                const int id = (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset;
+                                if (id >= 0 && id < p.V && id >= s0 && id - s0 < n) {
+                                    li = id - s0;
+                                }
                             }
-                        }
-                        const unsigned ball = __ballot_sync(0xffffffffu, first);
-                        if (first) {
-                            const int pos = nd + __popc(ball & ((1u << lane) - 1u));
-                            if (pos < p.hist_cap) {
-                                dl[pos] = (unsigned) mine | ((unsigned) cnt << kLiBits);
+                            const unsigned ball = __ballot_sync(0xffffffffu, li >= 0);
+                            if (li >= 0) {
+                                const int pos = nh + __popc(ball & ((1u << lane) - 1u));
+                                if (pos < p.hist_tmp) {
+                                    htmp[pos] = (unsigned short) li;
+                                }
                             }
+                            nh += __popc(ball);
                         }
-                        nd += __popc(ball);
+                        if (nh > p.hist_tmp) {
+                            ovf = 1;
+                            nh  = 0;
+                        }
+                        __syncwarp();
+                        /* (b) the first of each run of equal positions enters the list with the run's length */
+                        for (int base = 0; base < nh; base += 32) {
+                            const int i     = base + lane;
+                            int       cnt   = 0;
+                            bool      first = i < nh;
+                            const int mine  = i < nh ? (int) htmp[i] : -1;
+                            for (int k = 0; k < nh; k++) {
+                                const int v = (int) htmp[k];
+                                if (v == mine) {
+                                    cnt++;
+                                    first = first && k >= i;
+                                }
+                            }
+                            const unsigned ball = __ballot_sync(0xffffffffu, first);
+                            if (first) {
+                                const int pos = nd + __popc(ball & ((1u << lane) - 1u));
+                                if (pos < p.hist_cap) {
+                                    dl[pos] = (unsigned) mine | ((unsigned) cnt << kLiBits);
+                                }
+                            }
+                            nd += __popc(ball);
+                        }
                     }
                     if (nd > p.hist_cap) { /* cannot happen when the launcher sized the room */
                         ovf = 1;
@@ -1851,6 +1887,17 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                 }
                 decoded++;
             }
+#ifdef GB_PROFILE
+            {
+                const long long t_ = clock64();
+                if (act & 2) {
+                    lp_busy += t_ - lp_t;
+                } else {
+                    lp_idle += t_ - lp_t;
+                }
+                lp_t = t_;
+            }
+#endif
             if (act == 0) {
                 if (++idle > (1ll << 26)) {
                     if (lane == 0) {
@@ -1863,6 +1910,12 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                 idle = 0;
             }
         }
+#ifdef GB_PROFILE
+        if (lane == 0 && blockIdx.x < 256) {
+            g_prof2[blockIdx.x][12] = lp_busy;
+            g_prof2[blockIdx.x][13] = lp_idle;
+        }
+#endif
         return;
     }
     if (threadIdx.x >= kWorkThreads + 32 && threadIdx.x < kWorkThreads + 64) {
