@@ -41,9 +41,9 @@ N_SETS = 8
 SEED = 1234
 # algorithmic bytes per row: logits once + history ids + generator state in/out + token out
 BYTES_PER_ROW = 4 * V + 4 * H + 16 + 4
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload (131.99 MB + 3.91 MB), from the
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload (132.43 MB + 4.04 MB), from the
 # ncu capture summarised under profiles/; a bench run cannot measure it itself.
-NCU_TRAFFIC_BYTES = 135.9e6
+NCU_TRAFFIC_BYTES = 136.5e6
 WORKLOAD = ("B=256 rows x V=128256 fp32 logits ~ N(0,2.5^2) with 8 ids/row +12; temperature 0.8, top_k 40, "
             "top_p 0.95 (top_k precedence), repetition penalty 1.1 over 64-token history, 1 draw/row, seed 1234")
 
@@ -144,7 +144,7 @@ def run_reference(args):
     from helpers import independent_states
 
     threads = os.cpu_count() or 1
-    rows_per_step = max(threads, 32)
+    rows_per_step = max(64, 4 * threads)
     rng = np.random.default_rng(SEED)
     x = (rng.standard_normal((rows_per_step, V), dtype=np.float32) * np.float32(2.5))
     for r in range(rows_per_step):

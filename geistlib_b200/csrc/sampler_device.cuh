@@ -2,7 +2,8 @@
  * sampler_device.cuh — small device helpers shared by the sampling kernels:
  * the reference generator (src/engine/sampler.c:27-48 of geistlib), ordered
  * keys, exact exponentials for the entries that decide a draw, warp sums and
- * the mbarrier / bulk-copy wrappers (no cluster multicast anywhere).
+ * the mbarrier / bulk-copy wrappers (every copy goes to the issuing CTA's own
+ * shared memory).
  */
 #pragma once
 #include <cuda_runtime.h>
@@ -58,7 +59,7 @@ __device__ __forceinline__ long long warp_sum_ll(long long v) {
     return v;
 }
 
-/* mbarrier + bulk copy (global -> this CTA's shared memory, no multicast) */
+/* mbarrier + bulk copy (global -> this CTA's shared memory only) */
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned) __cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {

@@ -3,24 +3,31 @@
  *
  * A persistent grid (one CTA per SM) streams every logits row through the chip
  * exactly once. A row is cut into slices of at most 14336 floats; the work
- * item is (row, slice). Inside a CTA the warps are specialised:
+ * item is (row, slice); every CTA owns a contiguous run of items, so that
+ * consecutive items mostly belong to one row. Inside a CTA the warps are
+ * specialised and nobody waits for another CTA:
  *
- *   14 WORKER warps own a ring of shared-memory stages that one thread keeps
- *   full with bulk asynchronous copies (mbarrier-signalled, no cluster
- *   multicast) a few items ahead, so HBM stays busy while the CTA computes.
- *   A slice is lifted from its stage into registers (8 float4 per thread),
- *   the stage goes straight back to the copy engine, and the passes over the
- *   slice (maximum, select threshold, collect / exp-sum) run on registers.
- *   Candidates go straight to global scratch; the slice's summary is handed
- *   to the finisher warps.
+ *   The LOADER warp keeps a ring of shared-memory stages full with bulk
+ *   asynchronous copies (global -> this CTA's shared memory, signalled on
+ *   mbarriers) and prepares each item a few items ahead: its configuration and
+ *   the list of the history ids that fall into the slice, each with its count.
  *
- *   4 FINISHER warps take it from there, concurrently with the workers, which
- *   are already streaming the next slices. They publish each slice's record
- *   (a small mail queue in shared memory feeds them) and bump the row's
- *   counter; when the counter says the row is complete they merge its slice
- *   records, order the few surviving candidates, evaluate their
- *   probabilities exactly and make the draw. Nothing ever waits on another
- *   CTA, and the workers never wait on a global round trip.
+ *   14 WORKER warps walk the slices at their own pace. Each owns a fixed share
+ *   of every slice: it waits for the copy, applies the penalties that fall
+ *   into its share, reads the share once (maximum per lane), looks only at
+ *   the lanes that hold something that matters (the maximum's first id, the
+ *   entries above the row's select threshold), gives the stage back and adds
+ *   what it found to the slice's accumulators. Candidates go straight to
+ *   global scratch. The warps meet once per row, to set the row's select
+ *   threshold; every later slice of the row reuses it.
+ *
+ *   The PUBLISHER warp folds a slice as soon as its last worker warp is done:
+ *   record to global scratch, the row's counter, and a higher select threshold
+ *   for the slices to come (from a histogram of the candidates seen so far).
+ *
+ *   4 FINISHER warps finish the rows this CTA completed: they merge the row's
+ *   slice records, order the few surviving candidates, evaluate their
+ *   probabilities exactly and make the draw, while the workers stream on.
  *
  * Rows whose kept set is too large for this (top-k beyond the candidate room,
  * wide top-p nuclei) are served by the finisher warps alone with a multi-pass
