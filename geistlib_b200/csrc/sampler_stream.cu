@@ -551,7 +551,15 @@ template <class F>
 __device__ __forceinline__ void row_sweep(const Grp &g, const float *row, int V, F &&f) {
     const int     V4 = V >> 2;
     const float4 *p4 = reinterpret_cast<const float4 *>(row);
-    for (int j = g.tid; j < V4; j += g.n) {
+    int           j  = g.tid;
+    for (; j + 3 * g.n < V4; j += 4 * g.n) { /* four loads in flight per thread */
+        const float4 a = p4[j], b = p4[j + g.n], c = p4[j + 2 * g.n], d = p4[j + 3 * g.n];
+        f(a.x, 4 * j), f(a.y, 4 * j + 1), f(a.z, 4 * j + 2), f(a.w, 4 * j + 3);
+        f(b.x, 4 * (j + g.n)), f(b.y, 4 * (j + g.n) + 1), f(b.z, 4 * (j + g.n) + 2), f(b.w, 4 * (j + g.n) + 3);
+        f(c.x, 4 * (j + 2 * g.n)), f(c.y, 4 * (j + 2 * g.n) + 1), f(c.z, 4 * (j + 2 * g.n) + 2), f(c.w, 4 * (j + 2 * g.n) + 3);
+        f(d.x, 4 * (j + 3 * g.n)), f(d.y, 4 * (j + 3 * g.n) + 1), f(d.z, 4 * (j + 3 * g.n) + 2), f(d.w, 4 * (j + 3 * g.n) + 3);
+    }
+    for (; j < V4; j += g.n) {
         const float4 x = p4[j];
         f(x.x, 4 * j);
         f(x.y, 4 * j + 1);
@@ -584,11 +592,12 @@ __device__ unsigned long long bisect_rank(const Grp &g, GroupShared *sh, const f
     return prefix;
 }
 
-/* Largest composite word t with mass{word >= t} >= target (inclusive) or > target. */
+/* Largest composite word t with mass{word >= t} >= target (inclusive) or > target. The search may
+ * start from a known prefix of the word: the bits above top_bit are taken from `prefix`. */
 template <class KeyF, class MassF>
-__device__ unsigned long long bisect_mass(const Grp &g, GroupShared *sh, const float *row, int V, int idx_bits, double target, bool inclusive, KeyF &&key, MassF &&mass) {
-    unsigned long long prefix = 0;
-    for (int bit = 31 + idx_bits; bit >= 0; bit--) {
+__device__ unsigned long long bisect_mass(const Grp &g, GroupShared *sh, const float *row, int V, int idx_bits, double target, bool inclusive, KeyF &&key, MassF &&mass,
+                                          unsigned long long prefix = 0ull, int top_bit = -1) {
+    for (int bit = top_bit >= 0 ? top_bit : 31 + idx_bits; bit >= 0; bit--) {
         const unsigned long long t = prefix | (1ull << bit);
         double                   m = 0.0;
         row_sweep(g, row, V, [&](float x, int i) {
@@ -604,8 +613,157 @@ __device__ unsigned long long bisect_mass(const Grp &g, GroupShared *sh, const f
     return prefix;
 }
 
+/* Where a walk over the row in descending key order first reaches a target mass. */
+struct RadixOut {
+    bool      found;  /* false: the whole row stays below the target */
+    unsigned  key;    /* the key at which the running mass crosses */
+    double    above;  /* mass of the entries with a larger key */
+    long long n_above; /* how many those are */
+    long long ties;   /* entries with exactly this key (and mass > 0) */
+};
+
+/*
+ * The same answer as the top 32 bits of bisect_mass, in four sweeps instead of thirty-two: one
+ * byte of the key per sweep, masses and counts per byte value in shared memory (`copies` private
+ * histograms, one per warp where the room allows), then a scan from the top value down. hm / hc
+ * hold copies * 256 doubles / ints.
+ */
+template <class KeyF, class MassF>
+__device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *hc, int copies, const float *row, int V, double target, bool inclusive, KeyF &&key,
+                               MassF &&mass) {
+    RadixOut out;
+    out.found   = true;
+    out.key     = 0u;
+    out.above   = 0.0;
+    out.n_above = 0;
+    out.ties    = 0;
+    for (int level = 3; level >= 0; level--) {
+        const int shift = 8 * level;
+        for (int i = g.tid; i < copies * 256; i += g.n) {
+            hm[i] = 0.0;
+            hc[i] = 0;
+        }
+        g.sync();
+        double        *mym = hm + (g.warp % copies) * 256;
+        int           *myc = hc + (g.warp % copies) * 256;
+        const unsigned pre = out.key;
+        row_sweep(g, row, V, [&](float x, int i) {
+            const unsigned k = key(x);
+            if (level == 3 || (k >> (shift + 8)) == (pre >> (shift + 8))) {
+                const double m = mass(x, i);
+                if (m > 0.0) {
+                    const unsigned d = (k >> shift) & 255u;
+                    atomicAdd(&mym[d], m);
+                    atomicAdd(&myc[d], 1);
+                }
+            }
+        });
+        g.sync();
+        if (g.warp == 0) {
+            /* lane l owns the byte values 255 - 8 l down to 248 - 8 l: the walk order */
+            double m8[8];
+            int    c8[8];
+            double lane_m = 0.0;
+            int    lane_c = 0;
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const int b = 255 - (8 * g.lane + q);
+                m8[q]       = 0.0;
+                c8[q]       = 0;
+                for (int w = 0; w < copies; w++) {
+                    m8[q] += hm[w * 256 + b];
+                    c8[q] += hc[w * 256 + b];
+                }
+                lane_m += m8[q];
+                lane_c += c8[q];
+            }
+            double incl_m = lane_m;
+            int    incl_c = lane_c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double um = __shfl_up_sync(0xffffffffu, incl_m, o);
+                const int    uc = __shfl_up_sync(0xffffffffu, incl_c, o);
+                if (g.lane >= o) {
+                    incl_m += um;
+                    incl_c += uc;
+                }
+            }
+            const double   before = out.above + (incl_m - lane_m);
+            const bool     cross  = inclusive ? (before + lane_m >= target) : (before + lane_m > target);
+            const unsigned ball   = __ballot_sync(0xffffffffu, cross);
+            if (ball == 0u) {
+                if (g.lane == 0) {
+                    sh->b_star = -1;
+                }
+            } else if (g.lane == __ffs(ball) - 1) {
+                double run = before;
+                int    cnt = incl_c - lane_c;
+                int    b   = 255 - 8 * g.lane - 7;
+                int    tc  = c8[7];
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const bool hit = inclusive ? (run + m8[q] >= target) : (run + m8[q] > target);
+                    if (hit) {
+                        b  = 255 - (8 * g.lane + q);
+                        tc = c8[q];
+                        break;
+                    }
+                    run += m8[q];
+                    cnt += c8[q];
+                }
+                sh->b_star = b;
+                sh->S      = run;
+                sh->n_hi   = cnt;
+                sh->n_sel  = tc;
+            }
+        }
+        g.sync();
+        if (sh->b_star < 0) {
+            out.found = false;
+            g.sync();
+            return out;
+        }
+        out.key |= (unsigned) sh->b_star << shift;
+        out.above = sh->S;
+        out.n_above += (long long) sh->n_hi;
+        out.ties = (long long) sh->n_sel;
+        g.sync();
+    }
+    return out;
+}
+
+/*
+ * From the key at which a walk crosses to the composite word of the crossing entry: entries with
+ * equal keys are walked by ascending id, and `j` of them (1-based) are needed. One of a kind: one
+ * sweep finds its id. Several: the low bits of the word are bisected as before.
+ */
+template <class KeyF, class MassF>
+__device__ unsigned long long resolve_ties(const Grp &g, GroupShared *sh, const float *row, int V, int idx_bits, const RadixOut &ro, double target, bool inclusive, KeyF &&key,
+                                           MassF &&mass) {
+    if (ro.ties <= 1) {
+        if (g.tid == 0) {
+            sh->pick = 0x7fffffff;
+        }
+        g.sync();
+        row_sweep(g, row, V, [&](float x, int i) {
+            if (key(x) == ro.key && mass(x, i) > 0.0) {
+                atomicMin(&sh->pick, i);
+            }
+        });
+        g.sync();
+        const int id = sh->pick;
+        g.sync();
+        return composite(ro.key, id == 0x7fffffff ? 0 : id, idx_bits);
+    }
+    return bisect_mass(g, sh, row, V, idx_bits, target, inclusive, key, mass, (unsigned long long) ro.key << idx_bits, idx_bits - 1);
+}
+
 /* The finisher warps alone serve a row whose kept set does not fit the fast path. */
-__device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, float row_max, int row_arg) {
+__device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, float row_max, int row_arg, void *hist_mem, int hist_bytes) {
+    /* room for the byte histograms of the radix walks: per warp where it fits, else one for all */
+    const int copies = hist_bytes >= g.nw * 256 * 12 ? g.nw : 1;
+    double   *hm     = reinterpret_cast<double *>(hist_mem);
+    int      *hc     = reinterpret_cast<int *>(hm + copies * 256);
     const int    V        = p.V;
     const int    idx_bits = 32 - __clz(max(V - 1, 1));
     int          st       = ST_SLOW_PATH;
@@ -642,7 +800,11 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
     });
     group_argmax(g, sh, row_max, row_arg);
     if (r.mode == M_TOPK) {
-        const unsigned long long t_set  = bisect_rank(g, sh, gr, V, idx_bits, (long long) r.k);
+        /* the k-th entry in (value desc, id asc) order: a radix walk on counts, then the ids of its ties */
+        auto                     okey   = [](float x) { return order_key(x); };
+        auto                     one    = [](float, int) { return 1.0; };
+        const RadixOut           rs     = radix_mass(g, sh, hm, hc, copies, gr, V, (double) r.k, true, okey, one);
+        const unsigned long long t_set  = rs.found ? resolve_ties(g, sh, gr, V, idx_bits, rs, (double) r.k, true, okey, one) : 0ull;
         auto                     in_set = [&](float x, int i) { return composite(order_key(x), i, idx_bits) >= t_set; };
         if (r.select_only) {
             if (g.tid == 0) {
@@ -674,8 +836,9 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
             const double u = (double) unit_from(xorshift_next(r.rng)) * S;
             /* the pick is the earliest walk position whose running sum exceeds u: the largest
              * word t with mass{word >= t} > u */
-            unsigned long long t_pick = bisect_mass(
-                    g, sh, gr, V, idx_bits, u, false, [&](float x) { return order_key(x); }, [&](float x, int i) { return in_set(x, i) ? qof(x) : 0.0; });
+            auto                     qmass  = [&](float x, int i) { return in_set(x, i) ? qof(x) : 0.0; };
+            const RadixOut           rp     = radix_mass(g, sh, hm, hc, copies, gr, V, u, false, okey, qmass);
+            unsigned long long       t_pick = rp.found ? resolve_ties(g, sh, gr, V, idx_bits, rp, u, false, okey, qmass) : 0ull;
             if (t_pick < t_set) {
                 t_pick = t_set;
             }
@@ -705,7 +868,29 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
         auto keyf  = [](float pv) { return __float_as_uint(pv); }; /* p >= 0: the bits are ordered */
         auto massf = [](float pv, int) { return (double) pv; };
         /* cutoff: first walk position whose running sum reaches top_p, inclusive */
-        const unsigned long long t_cut = bisect_mass(g, sh, gr, V, idx_bits, (double) r.top_p, true, keyf, massf);
+        /* The radix walks look at a window of keys stretched over all 32 bits, so that the entries
+         * spread over the byte values instead of piling up in a few. Cutoff: entries with
+         * p < (1 - top_p) / V add up to less than 1 - top_p, so the walk crosses above them. */
+        auto windowed = [&](unsigned k_lo, unsigned k_hi, double target, bool inclusive, auto &&mass_in) {
+            const unsigned span = k_hi > k_lo ? k_hi - k_lo : 0u;
+            const int      ls   = span > 0u ? __clz(span) : 0;
+            auto           kw   = [&](float pv) {
+                const unsigned k = keyf(pv);
+                return k >= k_lo ? (min(k, k_hi) - k_lo) << ls : 0u;
+            };
+            auto mw = [&](float pv, int i) { return keyf(pv) >= k_lo ? mass_in(pv, i) : 0.0; };
+            RadixOut ro = radix_mass(g, sh, hm, hc, copies, gr, V, target, inclusive, kw, mw);
+            ro.key      = (ro.key >> ls) + k_lo; /* back to the key itself */
+            return ro;
+        };
+        const unsigned k_top   = keyf(__double2float_rn(1.0 / S)); /* the largest p: e = 1 at the row maximum */
+        const float    p_floor = __double2float_rn(0.5 * (1.0 - (double) r.top_p) / (double) V);
+        const unsigned k_floor = (p_floor > 0.0f && keyf(p_floor) < k_top) ? keyf(p_floor) : 0u;
+        RadixOut       rc      = windowed(k_floor, k_top, (double) r.top_p, true, massf);
+        if (!rc.found && k_floor != 0u) {
+            rc = windowed(0u, k_top, (double) r.top_p, true, massf); /* rounding kept the window short of top_p */
+        }
+        const unsigned long long t_cut = rc.found ? resolve_ties(g, sh, gr, V, idx_bits, rc, (double) r.top_p, true, keyf, massf) : 0ull;
         double                   nm    = 0.0;
         long long                ncnt  = 0;
         row_sweep(g, gr, V, [&](float pv, int i) {
@@ -717,7 +902,9 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
         const double       N      = group_sum_d(g, sh, nm);
         const long long    cut    = group_sum_ll(g, sh, ncnt);
         const double       u      = (double) unit_from(xorshift_next(r.rng)) * N;
-        unsigned long long t_pick = bisect_mass(g, sh, gr, V, idx_bits, u, false, keyf, massf);
+        auto               nmass  = [&](float pv, int i) { return composite(keyf(pv), i, idx_bits) >= t_cut ? (double) pv : 0.0; };
+        const RadixOut     rk     = windowed((unsigned) (t_cut >> idx_bits), k_top, u, false, nmass);
+        unsigned long long t_pick = rk.found ? resolve_ties(g, sh, gr, V, idx_bits, rk, u, false, keyf, nmass) : 0ull;
         if (t_pick < t_cut) {
             t_pick = t_cut; /* default: the last nucleus entry (sampler.c:292) */
         }
@@ -1210,7 +1397,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
         }
     }
     g.sync();
-    return st | multipass_row(g, p, sh, r, row_max, row_arg);
+    return st | multipass_row(g, p, sh, r, row_max, row_arg, fb.fcand, 16 * p.fin_cap);
 }
 
 /* Optional cycle accounting of worker thread 0 (build with -DGB_PROFILE): where one CTA's time goes. */
@@ -2086,15 +2273,18 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             return ok;
         };
         if (mode == M_ARGMAX) {
-            /* the first id of the warp's maximum; only the lanes that hold the maximum are searched */
+            /* the first id of the warp's maximum, if it can still be the slice's; only the lanes that hold
+             * the maximum are searched */
             unsigned best = 0x7fffffffu;
-            for (unsigned hits = __ballot_sync(0xffffffffu, bkey == wkey && g.lane < mine4); hits != 0u; hits &= hits - 1u) {
-                int            li;
-                float          v;
-                const bool     ok = look(__ffs(hits) - 1, li, v);
-                const unsigned eb = __ballot_sync(0xffffffffu, ok && v == wmax);
-                if (eb != 0u) {
-                    best = min(best, (unsigned) (s0 + __shfl_sync(0xffffffffu, li, __ffs(eb) - 1)));
+            if (wkey >= (unsigned) (*reinterpret_cast<volatile unsigned long long *>(&acc->best) >> 32)) {
+                for (unsigned hits = __ballot_sync(0xffffffffu, bkey == wkey && g.lane < mine4); hits != 0u; hits &= hits - 1u) {
+                    int            li;
+                    float          v;
+                    const bool     ok = look(__ffs(hits) - 1, li, v);
+                    const unsigned eb = __ballot_sync(0xffffffffu, ok && v == wmax);
+                    if (eb != 0u) {
+                        best = min(best, (unsigned) (s0 + __shfl_sync(0xffffffffu, li, __ffs(eb) - 1)));
+                    }
                 }
             }
             if (g.lane == 0 && best != 0x7fffffffu) {

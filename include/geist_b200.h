@@ -181,7 +181,7 @@ enum geist_status geist_b200_sample_batch(struct geist_b200_ctx *ctx, const stru
 /* Backend operator slot argmax_f32 (include/geist_backend.h:414-421): greedy
  * argmax of one [1, n] F32 row that lives on this device; ties -> lowest index.
  * Synchronous: returns after the 4-byte index is on the host. The glue that
- * unpacks struct geist_tensor is shown in INTEGRATION.md. */
+ * unpacks struct geist_tensor is a few lines in the backend that registers the slot. */
 enum geist_status geist_b200_argmax_f32(struct geist_b200_ctx *ctx, const float *logits_dev, size_t n, int32_t *out_index);
 /* The matching probe (geist_backend.h:276-326): true for q->op == ARGMAX_F32, m == 1, 1 <= d_model <= supported max. */
 int geist_b200_argmax_f32_supported(size_t m, size_t n_vocab);
