@@ -936,6 +936,7 @@ struct FinBuffers {
 
 /* What the finisher warps request from global scratch the moment a row is theirs, so that it
  * travels while the row's configuration is still being read. */
+static_assert(kFinThreads * 8 >= 1024, "the finisher threads walk a crossing segment of up to 1024 entries, 8 each");
 constexpr int kSpecSlots = 8; /* per finisher thread: candidates fetched before the slices' counts are known */
 /* how many of each slice's candidates that is (0: the row has too many slices) */
 __device__ __forceinline__ int spec_per_slice(const SampleParams &p) {
@@ -944,6 +945,7 @@ __device__ __forceinline__ int spec_per_slice(const SampleParams &p) {
 struct Prefetch {
     int4      hdr;              /* slice record header {max, arg, n_cand, st} of slice g.tid */
     long long c[kSpecSlots];    /* candidate (value, id) pairs, flat index g.tid + kFinThreads * m */
+    double    seg;              /* temperature rows: segment sum number g.tid of the row */
 };
 
 __device__ __forceinline__ Prefetch prefetch_row(const Grp &g, const SampleParams &p, int row) {
@@ -952,6 +954,10 @@ __device__ __forceinline__ Prefetch prefetch_row(const Grp &g, const SampleParam
     pf.hdr               = make_int4(0, 0, 0, 0);
     if (g.tid < p.n_slices) {
         pf.hdr = __ldcg(reinterpret_cast<const int4 *>(&recs[g.tid]));
+    }
+    pf.seg = 0.0;
+    if (g.tid < p.n_slices * kWorkWarps) {
+        pf.seg = __ldcg(&recs[g.tid / kWorkWarps].seg[g.tid % kWorkWarps]);
     }
     const int   kSpec = spec_per_slice(p);
     const int   flat  = p.n_slices * kSpec;
@@ -1098,13 +1104,14 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
             const int   cc = t / kWorkWarps;
             const float m  = slice_max(cc);
             const double sc = m == -CUDART_INF_F ? 0.0 : exp(((double) m - (double) row_max) * (double) r.inv_t);
-            return sc * __ldcg(&recs[cc].seg[t % kWorkWarps]);
+            return sc * (t == g.tid ? pf.seg : __ldcg(&recs[cc].seg[t % kWorkWarps]));
         };
         double part = 0.0;
         for (int t = g.tid; t < nseg; t += g.n) {
             part += seg_at(t);
         }
         const double S     = group_sum_d(g, sh, part);
+        FPROF(2); /* temperature: headers + segment sums */
         const double u     = (double) unit_from(xorshift_next(r.rng)) * S;
         double       carry = 0.0;
         int          found = -1;
@@ -1154,6 +1161,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
         if (found < 0) {
             found = nseg - 1;
         }
+        FPROF(3); /* temperature: scan to the crossing segment */
         /* the crossing segment, re-read from the row (L2), penalised, walked with the row maximum */
         const int    cc    = found / kWorkWarps, w = found % kWorkWarps;
         const int    s0c   = cc * p.slice;
@@ -1181,56 +1189,68 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
         if (r.pen_on && seg_n > 0) {
             st |= apply_penalties(g, wbuf, s0c + e0, seg_n, r, p.V, p.vocab_offset, fb.bitmap, fb.dlist, fb.dlist_cap, &sh->n_dlist, false, 0);
         }
-        if (g.warp == 0) {
-            int    hit  = -1;
+        FPROF(4); /* temperature: segment loaded and penalised */
+        {
+            /* every thread takes a run of consecutive entries; the runs' sums are scanned over the
+             * group and the thread whose run crosses u walks it */
+            const int per = (seg_n + g.n - 1) / g.n; /* <= 8 for 128 threads */
+            const int i0  = g.tid * per;
+            float     ev[8];
+            double    mine = 0.0;
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const int i = i0 + q;
+                ev[q]       = (q < per && i < seg_n) ? expf(scaled_arg(wbuf[i], row_max, r.inv_t)) : 0.0f;
+                mine += (double) ev[q];
+            }
+            double incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (g.lane >= o) {
+                    incl += up;
+                }
+            }
+            g.sync();
+            if (g.lane == 31) {
+                sh->wred_d[g.warp] = incl;
+            }
+            if (g.tid == 0) {
+                sh->pick = 0x7fffffff;
+            }
+            g.sync();
             double base = fbase;
-            for (int c0 = 0; c0 < seg_n && hit < 0; c0 += 128) {
-                float ev[4];
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int i = c0 + 4 * g.lane + q;
-                    ev[q]       = i < seg_n ? expf(scaled_arg(wbuf[i], row_max, r.inv_t)) : 0.0f;
+            for (int w = 0; w < g.warp; w++) {
+                base += sh->wred_d[w];
+            }
+            if (u < base + incl && i0 < seg_n) {
+                atomicMin(&sh->pick, g.tid);
+            }
+            g.sync();
+            const int pk = sh->pick;
+            if (pk == 0x7fffffff) {
+                if (g.tid == 0) { /* regrouped sums can end a hair below the segment's share */
+                    p.tokens[row] = s0c + e0 + max(seg_n - 1, 0) + p.vocab_offset;
                 }
-                const double mine = ((double) ev[0] + (double) ev[1]) + ((double) ev[2] + (double) ev[3]);
-                double       incl = mine;
+            } else if (g.tid == pk) {
+                double a   = base + (incl - mine);
+                int    hit = min(i0 + per - 1, seg_n - 1);
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const double up = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (g.lane >= o) {
-                        incl += up;
+                for (int q = 0; q < 8; q++) {
+                    a += (double) ev[q];
+                    if (q < per && u < a) {
+                        hit = i0 + q;
+                        break;
                     }
                 }
-                const unsigned ball = __ballot_sync(0xffffffffu, u < base + incl);
-                if (ball != 0u) {
-                    const int srcl = __ffs(ball) - 1;
-                    int       f    = -1;
-                    if (g.lane == srcl) {
-                        double a = base + (incl - mine);
-                        f        = c0 + 4 * g.lane + 3;
-#pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            a += (double) ev[q];
-                            if (u < a) {
-                                f = c0 + 4 * g.lane + q;
-                                break;
-                            }
-                        }
-                    }
-                    hit = min(__shfl_sync(0xffffffffu, f, srcl), seg_n - 1);
-                }
-                base += __shfl_sync(0xffffffffu, incl, 31);
+                p.tokens[row] = s0c + e0 + min(hit, seg_n - 1) + p.vocab_offset;
             }
-            if (hit < 0) {
-                hit = max(seg_n - 1, 0); /* regrouped sums can end a hair below the segment's share */
-            }
-            if (g.lane == 0) {
-                p.tokens[row] = s0c + e0 + hit + p.vocab_offset;
-                if (p.kept_cap > 0) {
-                    p.kept_n[row] = 0;
-                }
+            if (g.tid == 0 && p.kept_cap > 0) {
+                p.kept_n[row] = 0;
             }
         }
         g.sync();
+        FPROF(5); /* temperature: walk */
         return st;
     }
 
