@@ -253,3 +253,45 @@ def test_mixed_modes_in_one_launch(ctx):
     g = run_gpu(ctx, x, T, K, P, st)
     o = oracle.port.sample_batch(x, T, K, P, st)
     check_tokens(g, o)
+
+
+def test_mixed_modes_large_batch_with_penalties(ctx):
+    """Several hundred rows, all four modes interleaved row by row, two rows per generator, histories
+    of different lengths: every CTA meets rows of every kind back to back."""
+    V, S, R, H = 32000, 150, 2, 48
+    rows = S * R
+    x = normal_logits(rows, V, 2.5, 4242)
+    x[:, :6] += 11.0
+    rng = np.random.default_rng(4242)
+    modes = [(0.0, 0, 1.0), (0.8, 40, 1.0), (0.9, 0, 0.9), (1.1, 0, 1.0), (0.7, 100, 1.0), (0.8, 300, 1.0)]
+    pick = rng.integers(0, len(modes), S)
+    T = np.array([modes[i][0] for i in pick], np.float32)
+    K = np.array([modes[i][1] for i in pick], np.int32)
+    P = np.array([modes[i][2] for i in pick], np.float32)
+    h = histories(S, H, V, 4243)
+    h[:, :4] = np.arange(4)
+    hl = rng.integers(0, H + 1, S).astype(np.int32)
+    fed = rng.integers(0, V, (S, R)).astype(np.int32)
+    st = independent_states(oracle.port, 4242, S)
+    g = run_gpu(ctx, x, T, K, P, st, rows_per_seq=R, rep=1.2, freq=0.1, pres=0.05, history=h, history_len=hl, fed=fed)
+    o = oracle.port.sample_batch(x, T, K, P, st, rows_per_seq=R, rep=1.2, freq=0.1, pres=0.05, hist=h, hist_len=hl, extra=fed)
+    check_tokens(g, o)
+
+
+def test_unaligned_rows_with_penalties(ctx):
+    import torch
+    V, rows, H = 20011, 10, 32
+    x = normal_logits(rows, V, 2.5, 66)
+    h = histories(rows, H, V, 67)
+    h[:, 0] = x.argmax(axis=1)
+    buf = torch.zeros(rows * (V + 1) + 3, dtype=torch.float32, device="cuda")
+    view = buf[3:3 + rows * (V + 1)].view(rows, V + 1)[:, :V]
+    view.copy_(torch.from_numpy(x))
+    st = independent_states(oracle.port, 9, rows)
+    for (T, K, P) in [(0.0, 0, 1.0), (0.8, 40, 1.0), (1.0, 0, 1.0)]:
+        dT, dK, dP = per_seq(rows, T, K, P)
+        out = ctx.sample_batch(view, dT, dK, dP, u64_to_dev(st), rep=to_dev(np.full(rows, 1.3, np.float32)),
+                               freq=to_dev(np.full(rows, 0.2, np.float32)), history=to_dev(h),
+                               history_len=to_dev(np.full(rows, H, np.int32)))
+        o = oracle.port.sample_batch(x, T, K, P, st, rep=1.3, freq=0.2, hist=h)
+        assert np.array_equal(out["tokens"].cpu().numpy(), o["tokens"]), (T, K, P)
