@@ -103,9 +103,9 @@ bool make_plan(size_t V, size_t hist_max, Plan &pl) {
             /* short slices reserve room for every element, so that "collect everything" cannot overflow */
             const int cand_cap = slice <= 1024 ? (int) round_up(slice, 32) : cap;
             const int fin_cap  = (int) std::max<size_t>(256, std::min<size_t>(n_slices * (size_t) cand_cap, 4096));
-            /* after the ring: shared state | id lists of the slices in flight | in-range ids of one slice | finisher bitmap (16 words) |
+            /* after the ring: shared state | id lists of the slices in flight | in-range ids of one slice | finisher bitmap |
              * finisher id list | merged candidates + scratch copy | sorted kept set + its weights */
-            const size_t fixed = gb::sample_stream_fixed_smem() + (size_t) (gb::kMaxStages + 1) * (size_t) pl.hist_cap * 4 + round_up((size_t) pl.hist_tmp * 2, 16) + 64 + (size_t) std::min(pl.hist_cap, 512) * 8 +
+            const size_t fixed = gb::sample_stream_fixed_smem() + (size_t) (gb::kMaxStages + 1) * (size_t) pl.hist_cap * 4 + round_up((size_t) pl.hist_tmp * 2, 16) + 4 * (size_t) gb::kFinBitmapWords + (size_t) std::min(pl.hist_cap, 512) * 8 +
                                  (size_t) fin_cap * 16 + (size_t) gb::kFastKMax * 12 + 128;
             if (fixed + (size_t) pl.stage_bytes > kSmemMax) {
                 continue;

@@ -22,12 +22,12 @@ constexpr int kThreads      = kWorkThreads + 64 + kFinThreads; /* workers, loade
 constexpr int kWarps        = 32;             /* room for per-warp values in the slice record */
 constexpr int kSliceMax     = 14336;          /* floats of one row slice: at most 8 float4 per worker thread */
 static_assert(kSliceMax <= 32 * kWorkThreads, "a worker thread holds at most 8 float4 of a slice");
-constexpr int kGroupCap     = 1024;           /* group maxima per slice used for the select threshold */
 constexpr int kTopKClamp    = 8192;           /* sampler.c:212-215 */
 constexpr int kFastKMax     = 256;            /* largest k served by the threshold fast path */
 constexpr int kNucleusProbe = 32;             /* entries the top-p fast path looks at */
 constexpr int kMaxSlices    = 1024;           /* slices per row the finisher can merge */
 constexpr int kMaxStages    = 4;              /* depth of the bulk-copy ring */
+constexpr int kFinBitmapWords = 32;           /* finisher: one bit per entry of a crossing segment (at most 1024) */
 constexpr int kHistBins     = 256;            /* value histogram of the finisher's select */
 
 /* status word, one per row (bit set) */

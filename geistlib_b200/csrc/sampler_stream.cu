@@ -128,7 +128,7 @@ __host__ __device__ __forceinline__ int share_len(int nv4) { return ((nv4 + kWor
 /* A work item's configuration, decoded once by the loader warp. */
 struct __align__(16) ItemCfg {
     int   row, item, s0, n;         /* what the worker warps read, four words at a time */
-    int   mode, kq, flags, lpg;     /* flags: bit 0 = penalties on */
+    int   mode, kq, flags, pad0;    /* flags: bit 0 = penalties on */
     float inv_t, rep, freq, pres;
     int   L, nv4, c, st0;           /* float4 per warp, float4 in the slice, slice number, status bits of the id list */
     int   H, E, seq, seq0;          /* loader only */
@@ -154,7 +154,6 @@ static_assert(kSliceMax <= (1 << kLiBits), "slice positions must fit the id list
 struct __align__(16) StreamShared {
     unsigned long long full[kMaxStages];  /* the slice has landed (bulk copy -> workers) */
     unsigned long long empty[kMaxStages]; /* every worker warp has lifted its part (workers -> loader) */
-    float              gmax[kGroupCap];
     GroupShared        wk; /* workers */
     GroupShared        fn; /* finishers */
     ItemCfg            cfg[kCfgRing];
@@ -162,6 +161,9 @@ struct __align__(16) StreamShared {
     int                n_dl[kListRing]; /* entries of the slice's id list */
     unsigned           tau_key[2];      /* select threshold of a row's first slice, alternating */
     unsigned           top_key[2];      /* largest group maximum of that slice, alternating */
+    unsigned           low_key[2];      /* smallest group maximum of that slice, alternating */
+    int                boot_n[2];       /* groups (threads with a share) of that slice, alternating */
+    __align__(16) int  bhist[kHistBins]; /* group maxima of that slice, binned by key */
     unsigned long long tau_pub;         /* (row, ordered key of the best threshold known for it): only grows */
     int                rowids[128];      /* loader: the ids of the row in preparation */
     __align__(16) int  thist[kHistBins]; /* the row's candidates so far, binned by value between threshold and maximum */
@@ -1178,7 +1180,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
             wbuf[i] = src[i];
         }
         if (r.pen_on) {
-            for (int i = g.tid; i < 16; i += g.n) {
+            for (int i = g.tid; i < kFinBitmapWords; i += g.n) {
                 fb.bitmap[i] = 0u;
             }
             if (g.tid == 0) {
@@ -1725,12 +1727,14 @@ struct TauState {
 
 /*
  * Sets the select threshold of a row on the first slice this CTA sees of it. Called by all
- * worker threads (two group barriers). bv = the thread's maximum over its share, wkey = the
- * ordered key of the warp's maximum. Groups of lpg = 8 / 4 / 2 / 1 lanes give 56 / 112 / 224 /
- * 448 group maxima; tau = the kq-th largest of them, so at least kq entries of this slice alone
- * are >= tau and tau cannot exceed the row's kq-th largest value.
+ * worker threads (three group barriers). bv = the thread's maximum over its share (`own`: it has
+ * one), wkey = the ordered key of the warp's maximum. Every owning thread is a group of up to
+ * 32 entries; the group maxima are binned by their ordered keys into 256 bins below the largest,
+ * and tau = the lower edge of the highest bin above which at least kq group maxima lie: at least
+ * kq entries of this slice alone are >= tau, so tau cannot exceed the row's kq-th largest value.
+ * Fewer than kq groups: everything passes.
  */
-__device__ __noinline__ TauState set_row_threshold(int tid, StreamShared *sh, float bv, unsigned wkey, int lpg, int kq, int row, int boots) {
+__device__ __noinline__ TauState set_row_threshold(int tid, StreamShared *sh, float bv, bool own, unsigned wkey, int kq, int row, int boots) {
     Grp g;
     g.tid  = tid;
     g.lane = tid & 31;
@@ -1741,66 +1745,92 @@ __device__ __noinline__ TauState set_row_threshold(int tid, StreamShared *sh, fl
     TauState ts;
     ts.boots       = boots + 1;
     const int bsel = boots & 1;
-    const int Gs = kWorkThreads / lpg;
-    float     gv = bv;
-    if (lpg >= 2) {
-        gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 1));
+    const unsigned bkey = order_key(bv + 0.0f);
+    {
+        const unsigned wlo  = __reduce_min_sync(0xffffffffu, own ? bkey : 0xffffffffu);
+        const int      wown = __popc(__ballot_sync(0xffffffffu, own));
+        if (g.lane == 0 && wown > 0) {
+            atomicMax(&sh->top_key[bsel], wkey);
+            atomicMin(&sh->low_key[bsel], wlo);
+            atomicAdd(&sh->boot_n[bsel], wown);
+        }
     }
-    if (lpg >= 4) {
-        gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 2));
-    }
-    if (lpg >= 8) {
-        gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, 4));
-    }
-    if ((g.lane & (lpg - 1)) == 0) {
-        sh->gmax[g.tid / lpg] = gv;
-    }
-    if (g.lane == 0) {
-        atomicMax(&sh->top_key[bsel], wkey);
+    for (int i = g.tid; i < kHistBins; i += g.n) {
+        sh->bhist[i] = 0; /* the previous use's readers passed its last barrier long ago */
     }
     g.sync();
     if (g.tid == 0) {
-        sh->tau_key[bsel ^ 1] = 0xffffffffu; /* its readers have all passed the barrier above */
+        sh->tau_key[bsel ^ 1] = 0xffffffffu; /* their readers have all passed the barrier above */
         sh->top_key[bsel ^ 1] = 0u;
+        sh->low_key[bsel ^ 1] = 0xffffffffu;
+        sh->boot_n[bsel ^ 1]  = 0;
+        sh->t_row             = -1;
     }
-    if (g.tid == 0) {
-        sh->t_row = -1;
+    for (int i = g.tid; i < kHistBins; i += g.n) {
+        sh->thist[i] = 0;
     }
-    if (g.tid < kHistBins) {
-        sh->thist[g.tid] = 0;
+    const unsigned khi = sh->top_key[bsel];
+    /* values far below the largest all go to bin 0: the walk comes from the top */
+    const unsigned klo   = max(sh->low_key[bsel], khi > (1u << 27) ? khi - (1u << 27) : 0u);
+    const int      n_own = sh->boot_n[bsel];
+    const unsigned span  = khi - klo;
+    const int      shift = max(0, (32 - __clz(span)) - 8); /* (span >> shift) < 256 */
+    if (own && n_own >= kq) {
+        atomicAdd(&sh->bhist[(max(bkey, klo) - klo) >> shift], 1);
     }
-    /* the smallest group maximum that fewer than kq group maxima exceed (ties need no order: only
-     * the value matters). Eight threads share one value, each counts an eighth (7 .. 56 values). */
-    const int kth = min(kq, Gs);
-    const int per = Gs >> 3;
-    for (int idx = g.tid; idx < 8 * Gs; idx += g.n) {
-        const int    t     = idx >> 3, part = idx & 7;
-        const float  v     = sh->gmax[t];
-        const float *q     = sh->gmax + part * per;
-        int          above = 0;
-        for (int jg = 0; jg < per; jg++) {
-            above += q[jg] > v ? 1 : 0;
+    g.sync();
+    if (g.warp == 0) {
+        unsigned tkey = 0u; /* below everything: all entries pass */
+        if (n_own >= kq) {
+            /* lane l holds bins 8 l .. 8 l + 7; the highest bin with at least kq group maxima in it and above */
+            int        c[8];
+            const int4 lo4 = *reinterpret_cast<const int4 *>(&sh->bhist[8 * g.lane]);
+            const int4 hi4 = *reinterpret_cast<const int4 *>(&sh->bhist[8 * g.lane + 4]);
+            c[0] = lo4.x, c[1] = lo4.y, c[2] = lo4.z, c[3] = lo4.w, c[4] = hi4.x, c[5] = hi4.y, c[6] = hi4.z, c[7] = hi4.w;
+            int mine = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                mine += c[i];
+            }
+            int suffix = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int dn = __shfl_down_sync(0xffffffffu, suffix, o);
+                if (g.lane + o < 32) {
+                    suffix += dn;
+                }
+            }
+            const unsigned ball = __ballot_sync(0xffffffffu, suffix >= kq);
+            int            b    = 0;
+            if (ball != 0u && g.lane == 31 - __clz(ball)) {
+                int run = suffix - mine;
+                b       = 8 * g.lane;
+#pragma unroll
+                for (int i = 7; i >= 0; i--) {
+                    run += c[i];
+                    if (run >= kq) {
+                        b = 8 * g.lane + i;
+                        break;
+                    }
+                }
+            }
+            b    = __shfl_sync(0xffffffffu, b, ball != 0u ? 31 - __clz(ball) : 0);
+            tkey = b == 0 ? sh->low_key[bsel] : klo + ((unsigned) b << shift); /* bin 0 also holds what was clamped */
         }
-        above += __shfl_xor_sync(0xffffffffu, above, 1);
-        above += __shfl_xor_sync(0xffffffffu, above, 2);
-        above += __shfl_xor_sync(0xffffffffu, above, 4);
-        unsigned cand_key = (part == 0 && above < kth) ? order_key(v) : 0xffffffffu;
-        cand_key          = __reduce_min_sync(0xffffffffu, cand_key);
-        if (g.lane == 0 && cand_key != 0xffffffffu) {
-            atomicMin(&sh->tau_key[bsel], cand_key);
+        if (g.lane == 0) {
+            sh->tau_key[bsel] = tkey;
         }
     }
     g.sync();
     const unsigned tkey = sh->tau_key[bsel];
-    /* nothing qualified: the +NaN pattern, which nothing passes */
-    ts.tau = key_to_float(tkey);
+    ts.tau = tkey == 0u ? -CUDART_INF_F : key_to_float(tkey);
     ts.row = row;
-    /* the row's candidates are binned between tau and this slice's maximum; whoever writes a
-     * slice's mail reads the bins from the top and raises the threshold for the slices to come
-     * (each thread computes the same map from value to bin) */
-    const float top = key_to_float(sh->top_key[bsel]);
+    /* the row's candidates are binned between tau and this slice's maximum; the publisher reads the
+     * bins from the top and raises the threshold for the slices to come (each thread computes the
+     * same map from value to bin) */
+    const float top = key_to_float(khi);
     ts.lo           = ts.tau;
-    ts.scale        = (top > ts.tau && top - ts.tau < CUDART_INF_F && tkey != 0xffffffffu) ? (float) kHistBins / (top - ts.tau) : 0.0f;
+    ts.scale        = (n_own >= kq && top > ts.tau && top - ts.tau < CUDART_INF_F) ? (float) kHistBins / (top - ts.tau) : 0.0f;
     if (g.tid == 0) {
         sh->t_lo    = ts.lo;
         sh->t_scale = ts.scale;
@@ -1822,7 +1852,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     FinBuffers      fb;
     fb.dlist_cap = min(p.hist_cap, 512);
     fb.bitmap    = reinterpret_cast<unsigned *>(reinterpret_cast<unsigned char *>(htmp) + ((2 * (size_t) p.hist_tmp + 15) & ~(size_t) 15));
-    fb.dlist     = reinterpret_cast<PenEntry *>(fb.bitmap + 16);
+    fb.dlist     = reinterpret_cast<PenEntry *>(fb.bitmap + kFinBitmapWords);
     fb.fcand     = reinterpret_cast<Pair *>(fb.dlist + fb.dlist_cap); /* merged candidates of one row */
     fb.ftmp      = fb.fcand + p.fin_cap;
     fb.fsort     = fb.ftmp + p.fin_cap;                             /* kFastKMax entries */
@@ -1864,6 +1894,10 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         sh->tau_key[1] = 0xffffffffu;
         sh->top_key[0] = 0u;
         sh->top_key[1] = 0u;
+        sh->low_key[0] = 0xffffffffu;
+        sh->low_key[1] = 0xffffffffu;
+        sh->boot_n[0]  = 0;
+        sh->boot_n[1]  = 0;
         sh->tau_pub    = 0ull;
         sh->q_done     = 0;
         sh->q_error    = 0;
@@ -1921,7 +1955,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         o->freq        = r.freq;
         o->pres        = r.pres;
         o->st0         = 0;
-        o->lpg         = r.kq <= 40 ? 8 : (r.kq <= 80 ? 4 : (r.kq <= 160 ? 2 : 1)); /* 56 / 112 / 224 / 448 groups */
+        o->pad0        = 0;
     };
 
     if (threadIdx.x >= kWorkThreads && threadIdx.x < kWorkThreads + 32) {
@@ -2192,7 +2226,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         }
         const ItemCfg *cf = &sh->cfg[j % kCfgRing];
         const int4     c0 = *reinterpret_cast<const int4 *>(&cf->row);   /* row, item, s0, n */
-        const int4     c1 = *reinterpret_cast<const int4 *>(&cf->mode);  /* mode, kq, flags, lpg */
+        const int4     c1 = *reinterpret_cast<const int4 *>(&cf->mode);  /* mode, kq, flags, - */
         const int4     c3 = *reinterpret_cast<const int4 *>(&cf->L);     /* L, nv4, c, st0 */
         const int      row = c0.x, item = c0.y, s0 = c0.z, n = c0.w;
         const int      mode = c1.x, kq = c1.y;
@@ -2332,7 +2366,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
 #else
             if (ts.row != row) {
 #endif
-                ts = set_row_threshold(g.tid, sh, bv, wkey, c1.w, kq, row, ts.boots);
+                ts = set_row_threshold(g.tid, sh, bv, g.lane < mine4, wkey, kq, row, ts.boots);
                 PROF(6);
             } else {
                 const unsigned long long pub = *reinterpret_cast<volatile unsigned long long *>(&sh->tau_pub);

@@ -295,3 +295,23 @@ def test_unaligned_rows_with_penalties(ctx):
                                history_len=to_dev(np.full(rows, H, np.int32)))
         o = oracle.port.sample_batch(x, T, K, P, st, rep=1.3, freq=0.2, hist=h)
         assert np.array_equal(out["tokens"].cpu().numpy(), o["tokens"]), (T, K, P)
+
+
+def test_temperature_penalised_ids_late_in_the_crossing_segment(ctx):
+    """The draw lands among a few heavy ids that sit in the second half of one 1024-id segment and are
+    partly penalised: the finisher has to re-penalise that segment correctly at any offset."""
+    V, rows = 128256, 24
+    x = np.full((rows, V), -30.0, np.float32)
+    x += normal_logits(rows, V, 0.1, 5150)
+    rng = np.random.default_rng(5150)
+    h = histories(rows, 64, V, 5151)
+    for r in range(rows):
+        seg0 = int(rng.integers(0, V // 1024 - 1)) * 1024
+        ids = seg0 + 600 + rng.choice(400, 8, replace=False)
+        x[r, ids] = 6.0 + rng.random(8).astype(np.float32)
+        h[r, :4] = ids[:4]
+        h[r, 4:8] = ids[:4]  # twice: the frequency term counts
+    st = independent_states(oracle.port, 5150, rows)
+    g = run_gpu(ctx, x, 1.0, 0, 1.0, st, rep=1.5, freq=0.7, pres=0.3, history=h)
+    o = oracle.port.sample_batch(x, 1.0, 0, 1.0, st, rep=1.5, freq=0.7, pres=0.3, hist=h)
+    check_tokens(g, o)
