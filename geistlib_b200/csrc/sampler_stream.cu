@@ -145,6 +145,8 @@ struct __align__(8) SliceAcc {
     double             wsum[32]; /* ... and its sum of expf((x - that maximum) * inv_t) */
 };
 
+constexpr int kIdSlotBits = 8;
+constexpr int kIdSlots    = 1 << kIdSlotBits; /* open-addressing table for at most 128 ids */
 constexpr int kFinQueue = 64; /* completed rows waiting for this CTA's finisher warps */
 constexpr int kCfgRing  = 8; /* decoded configurations kept */
 constexpr int kListRing = kMaxStages + 1; /* per-slice id lists / accumulators kept: a warp can run at most `stages` slices ahead of another */
@@ -165,7 +167,8 @@ struct __align__(16) StreamShared {
     int                boot_n[2];       /* groups (threads with a share) of that slice, alternating */
     __align__(16) int  bhist[kHistBins]; /* group maxima of that slice, binned by key */
     unsigned long long tau_pub;         /* (row, ordered key of the best threshold known for it): only grows */
-    int                rowids[128];      /* loader: the ids of the row in preparation */
+    int                id_key[kIdSlots]; /* loader: the distinct ids of the row in preparation ... */
+    int                id_cnt[kIdSlots]; /* ... and how often each occurs */
     __align__(16) int  thist[kHistBins]; /* the row's candidates so far, binned by value between threshold and maximum */
     volatile int slice_done[kListRing]; /* j + 1 once every worker warp is done with slice j (workers -> publisher) */
     float        t_lo, t_scale;         /* the candidate histogram's map from value to bin ... */
@@ -1936,27 +1939,17 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     /* an item's configuration is decoded into shared memory a few items ahead, so that the worker
      * warps spend no instructions and no memory round trips on it */
     auto decode = [&](int row, int c, const RowCfg &r, ItemCfg *o) {
-        o->row         = row;
-        o->item        = row * p.n_slices + c;
-        o->c           = c;
-        o->s0          = c * p.slice;
-        o->n           = max(0, min(p.slice, p.V - o->s0));
-        o->nv4         = (o->n + 3) >> 2;
-        o->L           = share_len(o->nv4);
-        o->mode        = (int) r.mode;
-        o->kq          = r.kq;
-        o->flags       = r.pen_on ? 1 : 0;
-        o->H           = r.H;
-        o->E           = r.E;
-        o->seq         = r.seq;
-        o->seq0        = r.seq0;
-        o->inv_t       = r.inv_t;
-        o->rep         = r.rep;
-        o->freq        = r.freq;
-        o->pres        = r.pres;
-        o->st0         = 0;
-        o->pad0        = 0;
+        const int s0 = c * p.slice;
+        const int n  = max(0, min(p.slice, p.V - s0));
+        const int n4 = (n + 3) >> 2;
+        int4     *w  = reinterpret_cast<int4 *>(o); /* five stores of four words */
+        w[0]         = make_int4(row, row * p.n_slices + c, s0, n);
+        w[1]         = make_int4((int) r.mode, r.kq, r.pen_on ? 1 : 0, 0);
+        w[2]         = make_int4(__float_as_int(r.inv_t), __float_as_int(r.rep), __float_as_int(r.freq), __float_as_int(r.pres));
+        w[3]         = make_int4(share_len(n4), n4, c, 0);
+        w[4]         = make_int4(r.H, r.E, r.seq, r.seq0);
     };
+    static_assert(sizeof(ItemCfg) == 80, "decode() writes the item configuration as five int4");
 
     if (threadIdx.x >= kWorkThreads && threadIdx.x < kWorkThreads + 32) {
         /* ============================================================== loader == */
@@ -2039,21 +2032,35 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                                 int       id = j < total ? (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset : -1;
                                 id           = (id >= 0 && id < p.V) ? id : -1 - j; /* unusable ids match nothing */
                                 hc[k]        = id;
-                                sh->rowids[j] = id;
+                            }
+                            /* counts by a small open-addressing table in shared memory: the lane whose id
+                             * opened a slot speaks for that id and reads the slot's final count */
+                            for (int i = lane; i < kIdSlots; i += 32) {
+                                sh->id_key[i] = -1;
+                                sh->id_cnt[i] = 0;
+                            }
+                            __syncwarp();
+                            int slot_of[4];
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                slot_of[k] = -1;
+                                if (hc[k] >= 0) {
+                                    unsigned hsh = ((unsigned) hc[k] * 2654435761u) >> (32 - kIdSlotBits);
+                                    for (int probe = 0; probe < kIdSlots; probe++) {
+                                        const int old = atomicCAS(&sh->id_key[hsh], -1, hc[k]);
+                                        if (old == -1 || old == hc[k]) {
+                                            atomicAdd(&sh->id_cnt[hsh], 1);
+                                            slot_of[k] = old == -1 ? (int) hsh : -1; /* only the opener keeps the slot */
+                                            break;
+                                        }
+                                        hsh = (hsh + 1) & (kIdSlots - 1);
+                                    }
+                                }
                             }
                             __syncwarp();
 #pragma unroll
                             for (int k = 0; k < 4; k++) {
-                                const int j   = 32 * k + lane;
-                                int       cnt = 0, before = 0;
-                                if (j < total && hc[k] >= 0) {
-                                    for (int q = 0; q < total; q++) {
-                                        const bool same = sh->rowids[q] == hc[k];
-                                        cnt += same ? 1 : 0;
-                                        before += (same && q < j) ? 1 : 0;
-                                    }
-                                }
-                                hcnt[k] = (j < total && hc[k] >= 0 && before == 0) ? cnt : 0; /* 0: not the first of its value */
+                                hcnt[k] = slot_of[k] >= 0 ? sh->id_cnt[slot_of[k]] : 0; /* 0: another lane speaks for this id */
                             }
                             __syncwarp();
                             hc_row = o->row;
