@@ -1970,6 +1970,8 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         int hc[4]   = {-1, -1, -1, -1}; /* this lane's share of the history ids of row hc_row ... */
         int hcnt[4] = {0, 0, 0, 0};     /* ... and how often each occurs, kept by its first occurrence only */
         int hc_row = -1;
+        int hn[4]  = {-1, -1, -1, -1}; /* the next row's ids, fetched ahead (raw, before the shard offset) */
+        int hn_row = -1, hn_asked = -1, prev_item_row = -1;
 #ifdef GB_PROFILE
         long long lp_busy = 0, lp_idle = 0, lp_t = clock64();
 #endif
@@ -2029,9 +2031,12 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
 #pragma unroll
                             for (int k = 0; k < 4; k++) {
                                 const int j  = 32 * k + lane;
-                                int       id = j < total ? (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset : -1;
-                                id           = (id >= 0 && id < p.V) ? id : -1 - j; /* unusable ids match nothing */
-                                hc[k]        = id;
+                                int       id = -1;
+                                if (j < total) { /* fetched ahead while the previous row was in work, where that was possible */
+                                    id = (hn_row == o->row ? hn[k] : (j < H ? hrow[j] : erow[1 + j - H])) - p.vocab_offset;
+                                }
+                                id    = (id >= 0 && id < p.V) ? id : -1 - j; /* unusable ids match nothing */
+                                hc[k] = id;
                             }
                             /* counts by a small open-addressing table in shared memory: the lane whose id
                              * opened a slot speaks for that id and reads the slot's final count */
@@ -2132,6 +2137,32 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                         ovf = 1;
                         nd  = 0;
                     }
+                    /* the next row's ids are requested one item after this row began (its parameters have
+                     * arrived by then), so that the row change does not wait for global memory */
+                    const int nrow = o->row + 1;
+                    if (hn_row != nrow && hn_asked != nrow && nrow < p.n_rows && o->row == prev_item_row) {
+                        int seq_n = 0, H_n = 0;
+                        if (lane == 0) { /* lane 0 holds the next row's raw parameters */
+                            seq_n = raw.seq;
+                            H_n   = p.hist ? (int) min((long long) max(raw.hist_len, 0), p.hist_stride) : 0;
+                        }
+                        seq_n            = __shfl_sync(0xffffffffu, seq_n, 0);
+                        H_n              = __shfl_sync(0xffffffffu, H_n, 0);
+                        const int seq0_n = p.rows_per_seq == 1 ? nrow : nrow / p.rows_per_seq;
+                        const int E_n    = p.extra ? nrow - seq0_n * p.rows_per_seq : 0;
+                        if (H_n + E_n <= 128) {
+                            const int *hr = p.hist ? p.hist + (size_t) seq_n * (size_t) p.hist_stride : nullptr;
+                            const int *er = p.extra ? p.extra + (size_t) seq0_n * (size_t) p.extra_stride : nullptr;
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const int j = 32 * k + lane;
+                                hn[k]       = j < H_n + E_n ? (j < H_n ? hr[j] : er[1 + j - H_n]) : -1;
+                            }
+                            hn_row = nrow;
+                        }
+                        hn_asked = nrow;
+                    }
+                    prev_item_row = o->row;
                 }
                 __syncwarp();
                 if (lane == 0) {
