@@ -67,7 +67,9 @@ struct Plan {
     int    slice        = 0;
     int    stage_bytes  = 0;
     int    stages       = 0;
-    int    hist_tmp     = 0;
+    int    row_cap      = 0;
+    int    bucket_cap   = 0;
+    int    id_slots     = 0;
     int    hist_cap     = 0;
     int    cand_cap     = 0;
     int    fin_cap      = 0;
@@ -95,25 +97,45 @@ bool make_plan(size_t V, size_t hist_max, Plan &pl) {
     pl.n_slices     = (int) n_slices;
     pl.slice        = (int) slice;
     pl.stage_bytes  = (int) round_up(slice * 4, 128);
-    pl.hist_tmp     = (int) hist_max;
-    pl.hist_cap     = hist_max ? (int) std::min(hist_max, slice) : 0;
-    const int caps[] = {256, 224, 192, 160, 128, 96, 64};
+    /* histories of more than 128 ids are counted in a shared-memory table with at least two slots per id */
+    pl.id_slots     = 0;
+    pl.row_cap      = 0;
+    pl.bucket_cap   = 0;
+    if (hist_max > 128) {
+        size_t slots = 512;
+        while (slots < 2 * hist_max) {
+            slots *= 2;
+        }
+        if (slots > 16384) {
+            return false; /* 128 KB of table: no room left for the ring */
+        }
+        pl.id_slots   = (int) slots;
+        pl.row_cap    = (int) round_up(hist_max, 4);
+        pl.bucket_cap = (int) round_up(n_slices + 1, 4);
+    }
+    pl.hist_cap     = hist_max ? (int) round_up(std::min(hist_max, slice), 4) : 0; /* a multiple of 4 keeps what follows 16-byte aligned */
+    /* A slice's candidates go to global memory (cand_cap each); what shared memory limits is the room
+     * for one row's merged candidates (fin_cap): a row that brings more takes the multi-pass path.
+     * Short slices reserve room for every element, so that "collect everything" cannot overflow. */
+    const int    cand_cap = slice <= 1024 ? (int) round_up(slice, 32) : 256;
+    const size_t fin_full = std::max<size_t>(256, std::min<size_t>(n_slices * (size_t) cand_cap, 4096));
+    const size_t fins[]   = {fin_full, 2048, 1536, 1024, 768};
     for (int want_stages = 3; want_stages >= 1; want_stages--) {
-        for (int cap : caps) {
-            /* short slices reserve room for every element, so that "collect everything" cannot overflow */
-            const int cand_cap = slice <= 1024 ? (int) round_up(slice, 32) : cap;
-            const int fin_cap  = (int) std::max<size_t>(256, std::min<size_t>(n_slices * (size_t) cand_cap, 4096));
-            /* after the ring: shared state | id lists of the slices in flight | in-range ids of one slice | finisher bitmap |
-             * finisher id list | merged candidates + scratch copy | sorted kept set + its weights */
-            const size_t fixed = gb::sample_stream_fixed_smem() + (size_t) (gb::kMaxStages + 1) * (size_t) pl.hist_cap * 4 + round_up((size_t) pl.hist_tmp * 2, 16) + 4 * (size_t) gb::kFinBitmapWords + (size_t) std::min(pl.hist_cap, 512) * 8 +
-                                 (size_t) fin_cap * 16 + (size_t) gb::kFastKMax * 12 + 128;
+        for (size_t fin : fins) {
+            if (fin > fin_full) {
+                continue;
+            }
+            /* after the ring: shared state | id lists of the slices in flight | finisher bitmap | finisher id list |
+             * merged candidates + scratch copy | sorted kept set + its weights */
+            const size_t fixed = gb::sample_stream_fixed_smem() + (size_t) (gb::kMaxStages + 1) * (size_t) pl.hist_cap * 4 + 4 * (size_t) gb::kFinBitmapWords +
+                                 (size_t) std::min(pl.hist_cap, 512) * 8 + fin * 16 + (size_t) gb::kFastKMax * 12 + 128;
             if (fixed + (size_t) pl.stage_bytes > kSmemMax) {
                 continue;
             }
             const int stages = (int) std::min<size_t>(gb::kMaxStages, (kSmemMax - fixed) / (size_t) pl.stage_bytes);
             if (stages >= want_stages) {
                 pl.cand_cap = cand_cap;
-                pl.fin_cap  = fin_cap;
+                pl.fin_cap  = (int) fin;
                 pl.stages   = stages;
                 pl.smem     = fixed + (size_t) stages * (size_t) pl.stage_bytes;
                 return true;
@@ -318,7 +340,9 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.slice        = pl.slice;
     p.stage_bytes  = pl.stage_bytes;
     p.stages       = pl.stages;
-    p.hist_tmp     = pl.hist_tmp;
+    p.row_cap      = pl.row_cap;
+    p.bucket_cap   = pl.bucket_cap;
+    p.id_slots     = pl.id_slots;
     p.hist_cap     = pl.hist_cap;
     p.cand_cap     = pl.cand_cap;
     p.fin_cap      = pl.fin_cap;
@@ -338,7 +362,9 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     const size_t off_rows = round_up(off_cand + n_items * (size_t) pl.cand_cap * sizeof(gb::Pair), 256);
     const size_t off_bm   = round_up(off_rows + (size_t) grid * gen_str * 4, 256);
     const size_t off_dl   = round_up(off_bm + (size_t) grid * gen_bmw * 4, 256);
-    const size_t need     = round_up(off_dl + (size_t) grid * gen_hcap * sizeof(gb::Pair), 256);
+    const size_t off_pl   = round_up(off_dl + (size_t) grid * gen_hcap * sizeof(gb::Pair), 256);
+    const size_t off_po   = round_up(off_pl + (pl.id_slots ? n_rows * (size_t) pl.row_cap * 4 : 0), 256);
+    const size_t need     = round_up(off_po + (pl.id_slots ? n_rows * (size_t) (pl.n_slices + 1) * 4 : 0), 256);
     geist_b200_ctx::Lane *ln;
     unsigned              use_now = 0;
     {
@@ -380,6 +406,8 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.gen_bitmap_words = (int) gen_bmw;
     p.gen_dlist        = reinterpret_cast<gb::Pair *>(ln->buf + off_dl);
     p.gen_hist_cap     = (int) gen_hcap;
+    p.pre_list         = reinterpret_cast<unsigned *>(ln->buf + off_pl);
+    p.pre_off          = reinterpret_cast<int *>(ln->buf + off_po);
     CUDA_TRY(gb::launch_sample_stream(p, grid, pl.smem, st));
     return GEIST_OK;
 }

@@ -72,6 +72,15 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
+/* One 32-bit word from global to shared memory without passing through a register of the caller;
+ * complete for the issuing thread after async_copies_wait(). */
+__device__ __forceinline__ void copy_word_async(void *dst_shared, const void *src_global) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned) __cvta_generic_to_shared(dst_shared)), "l"(src_global) : "memory");
+}
+__device__ __forceinline__ void async_copies_wait() {
+    asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }

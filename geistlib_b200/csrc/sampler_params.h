@@ -100,7 +100,12 @@ struct SampleParams {
     int      slice;        /* floats per slice, multiple of 4, <= kSliceMax */
     int      stage_bytes;  /* bytes of one ring stage (multiple of 128, >= 4 * slice) */
     int      stages;       /* ring depth, 1..kMaxStages */
-    int      hist_tmp;     /* ids one row can bring (history + fed tokens); 0 when no history is given */
+    /* rows with more than 128 ids: their distinct ids are prepared by a kernel of their own */
+    int       id_slots;    /* slots of that kernel's id table (a power of two, at least twice the ids a row can bring); 0: no such rows */
+    int       row_cap;     /* entries of one row's prepared list */
+    int       bucket_cap;  /* n_slices + 1 rounded up to a multiple of 4 */
+    unsigned *pre_list;    /* [n_rows][row_cap] (position in the slice) | (count << 14), grouped by slice */
+    int      *pre_off;     /* [n_rows][n_slices + 1] where each slice's run starts */
     int      hist_cap;     /* distinct-id entries reserved per slice */
     int      cand_cap;     /* candidates reserved per slice */
     int      fin_cap;      /* candidates the finisher can merge per row */

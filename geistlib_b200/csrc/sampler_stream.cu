@@ -146,7 +146,8 @@ struct __align__(8) SliceAcc {
 };
 
 constexpr int kIdSlotBits = 8;
-constexpr int kIdSlots    = 1 << kIdSlotBits; /* open-addressing table for at most 128 ids */
+constexpr int kIdSlots    = 1 << kIdSlotBits; /* open-addressing table for at most kLoaderIds ids */
+constexpr int kLoaderIds  = 128;              /* ids of a row (history + fed tokens) that the loader warp keeps in registers */
 constexpr int kFinQueue = 64; /* completed rows waiting for this CTA's finisher warps */
 constexpr int kCfgRing  = 8; /* decoded configurations kept */
 constexpr int kListRing = kMaxStages + 1; /* per-slice id lists / accumulators kept: a warp can run at most `stages` slices ahead of another */
@@ -1851,10 +1852,9 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     unsigned char  *ring = smem_raw;
     StreamShared   *sh   = reinterpret_cast<StreamShared *>(smem_raw + (size_t) p.stages * (size_t) p.stage_bytes);
     unsigned       *dlr  = reinterpret_cast<unsigned *>(sh + 1);                             /* id lists of the slices in flight */
-    unsigned short *htmp = reinterpret_cast<unsigned short *>(dlr + kListRing * p.hist_cap); /* loader: in-range ids of one slice */
     FinBuffers      fb;
     fb.dlist_cap = min(p.hist_cap, 512);
-    fb.bitmap    = reinterpret_cast<unsigned *>(reinterpret_cast<unsigned char *>(htmp) + ((2 * (size_t) p.hist_tmp + 15) & ~(size_t) 15));
+    fb.bitmap    = reinterpret_cast<unsigned *>(dlr + kListRing * p.hist_cap);
     fb.dlist     = reinterpret_cast<PenEntry *>(fb.bitmap + kFinBitmapWords);
     fb.fcand     = reinterpret_cast<Pair *>(fb.dlist + fb.dlist_cap); /* merged candidates of one row */
     fb.ftmp      = fb.fcand + p.fin_cap;
@@ -1972,6 +1972,24 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         int hc_row = -1;
         int hn[4]  = {-1, -1, -1, -1}; /* the next row's ids, fetched ahead (raw, before the shard offset) */
         int hn_row = -1, hn_asked = -1, prev_item_row = -1;
+        int offr = 0, off_row = -1; /* lane i: where slice i's run starts in the prepared id list of row off_row */
+        int my_issued = 0; /* lane 0: copies issued, the warp's count follows at the next turn */
+        /* one copy if a stage is free; never blocks: the items' preparation must go on */
+        auto try_issue = [&]() {
+            if (p.aligned && my_issued < my_count) {
+                bool ok = my_issued < p.stages;
+                if (!ok) { /* the stage's previous slice must have been lifted by all worker warps */
+                    ok = mbar_test(&sh->empty[istage], (unsigned) ((my_issued / p.stages - 1) & 1));
+                }
+                if (ok) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    issue(irow, ic, istage);
+                    advance(irow, ic);
+                    istage = istage + 1 == p.stages ? 0 : istage + 1;
+                    my_issued++;
+                }
+            }
+        };
 #ifdef GB_PROFILE
         long long lp_busy = 0, lp_idle = 0, lp_t = clock64();
 #endif
@@ -1979,23 +1997,8 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         while ((p.aligned && issued < my_count) || decoded < my_count) {
             int act = 0;
             if (lane == 0) {
-                int mine_issued = issued;
-                while (p.aligned && mine_issued < my_count) {
-                    bool ok = mine_issued < p.stages;
-                    if (!ok) { /* the stage's previous slice must have been lifted by all worker warps */
-                        ok = mbar_test(&sh->empty[istage], (unsigned) ((mine_issued / p.stages - 1) & 1)); /* never blocks: the items' preparation must go on */
-                    }
-                    if (!ok) {
-                        break;
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    issue(irow, ic, istage);
-                    advance(irow, ic);
-                    istage = istage + 1 == p.stages ? 0 : istage + 1;
-                    mine_issued++;
-                    break; /* one copy per turn keeps the turns short: the items' id lists must not fall behind */
-                }
-                act |= (mine_issued - issued) << 2;
+                try_issue();
+                act |= (my_issued - issued) << 2;
                 if (decoded < my_count && decoded < *reinterpret_cast<volatile int *>(&sh->w_done) + kListRing) {
                     act |= 2;
                 }
@@ -2023,7 +2026,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                     const int *hrow = p.hist ? p.hist + (size_t) o->seq * (size_t) p.hist_stride : nullptr;
                     const int *erow = p.extra ? p.extra + (size_t) o->seq0 * (size_t) p.extra_stride : nullptr;
                     unsigned  *dl   = dlr + (size_t) (decoded % kListRing) * (size_t) p.hist_cap;
-                    if (total <= 128) {
+                    if (total <= kLoaderIds) {
                         /* The usual case. A row's ids are the same for all of its slices: once per row
                          * they are read into registers (four per lane) and each is marked as the first
                          * of its value with that value's count; a slice then only picks its own. */
@@ -2085,53 +2088,26 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                             }
                         }
                     } else {
-                        /* long histories: (a) positions of the ids that fall into the slice, repeats included */
-                        int nh = 0;
-                        for (int base = 0; base < total; base += 32) {
-                            const int j  = base + lane;
-                            int       li = -1;
-                            if (j < total) {
-                                const int id = (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset;
-                                if (id >= 0 && id < p.V && id >= s0 && id - s0 < n) {
-                                    li = id - s0;
-                                }
-                            }
-                            const unsigned ball = __ballot_sync(0xffffffffu, li >= 0);
-                            if (li >= 0) {
-                                const int pos = nh + __popc(ball & ((1u << lane) - 1u));
-                                if (pos < p.hist_tmp) {
-                                    htmp[pos] = (unsigned short) li;
-                                }
-                            }
-                            nh += __popc(ball);
+                        /* Long histories: a kernel that ran before this one left the row's distinct ids with
+                         * their counts in global memory, grouped by slice; a slice copies its run. */
+                        if (off_row != o->row) {
+                            offr    = lane <= p.n_slices ? p.pre_off[(size_t) o->row * (size_t) (p.n_slices + 1) + lane] : 0;
+                            off_row = o->row;
                         }
-                        if (nh > p.hist_tmp) {
-                            ovf = 1;
-                            nh  = 0;
+                        int lo, hi;
+                        if (p.n_slices < 32) {
+                            lo = __shfl_sync(0xffffffffu, offr, o->c);
+                            hi = __shfl_sync(0xffffffffu, offr, o->c + 1);
+                        } else {
+                            lo = p.pre_off[(size_t) o->row * (size_t) (p.n_slices + 1) + o->c];
+                            hi = p.pre_off[(size_t) o->row * (size_t) (p.n_slices + 1) + o->c + 1];
                         }
-                        __syncwarp();
-                        /* (b) the first of each run of equal positions enters the list with the run's length */
-                        for (int base = 0; base < nh; base += 32) {
-                            const int i     = base + lane;
-                            int       cnt   = 0;
-                            bool      first = i < nh;
-                            const int mine  = i < nh ? (int) htmp[i] : -1;
-                            for (int k = 0; k < nh; k++) {
-                                const int v = (int) htmp[k];
-                                if (v == mine) {
-                                    cnt++;
-                                    first = first && k >= i;
-                                }
-                            }
-                            const unsigned ball = __ballot_sync(0xffffffffu, first);
-                            if (first) {
-                                const int pos = nd + __popc(ball & ((1u << lane) - 1u));
-                                if (pos < p.hist_cap) {
-                                    dl[pos] = (unsigned) mine | ((unsigned) cnt << kLiBits);
-                                }
-                            }
-                            nd += __popc(ball);
+                        const unsigned *src = p.pre_list + (size_t) o->row * (size_t) p.row_cap;
+                        for (int i = lo + lane; i < hi && i - lo < p.hist_cap; i += 32) {
+                            copy_word_async(&dl[i - lo], &src[i]);
                         }
+                        async_copies_wait();
+                        nd = hi - lo;
                     }
                     if (nd > p.hist_cap) { /* cannot happen when the launcher sized the room */
                         ovf = 1;
@@ -2150,7 +2126,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
                         H_n              = __shfl_sync(0xffffffffu, H_n, 0);
                         const int seq0_n = p.rows_per_seq == 1 ? nrow : nrow / p.rows_per_seq;
                         const int E_n    = p.extra ? nrow - seq0_n * p.rows_per_seq : 0;
-                        if (H_n + E_n <= 128) {
+                        if (H_n + E_n <= kLoaderIds) {
                             const int *hr = p.hist ? p.hist + (size_t) seq_n * (size_t) p.hist_stride : nullptr;
                             const int *er = p.extra ? p.extra + (size_t) seq0_n * (size_t) p.extra_stride : nullptr;
 #pragma unroll
@@ -2507,6 +2483,91 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     }
 }
 
+/* ------------------------------------------------ long histories, prepared -- */
+
+constexpr int kRowIdThreads = 256;
+
+/* One CTA per row whose history (plus fed tokens) is longer than the stream kernel's loader keeps
+ * in registers: the row's distinct ids with their counts, grouped by the slice they fall into.
+ * pre_off[row][c] .. pre_off[row][c + 1] is slice c's run in pre_list[row]; an entry is
+ * (position in the slice) | (count << kLiBits). Shorter rows are left to the loader. */
+__global__ void __launch_bounds__(kRowIdThreads) row_ids_kernel(const __grid_constant__ SampleParams p) {
+    extern __shared__ __align__(16) int row_ids_smem[];
+    int *tkey = row_ids_smem;          /* open-addressing table: the id ... */
+    int *tcnt = tkey + p.id_slots;     /* ... and how often it occurs */
+    int *bcnt = tcnt + p.id_slots;     /* entry c + 1: distinct ids in slice c; after the scan, entry c: ids in slices < c */
+    int *bpos = bcnt + p.bucket_cap;   /* next free place of each slice's run */
+
+    const int row  = (int) blockIdx.x, tid = (int) threadIdx.x;
+    const int seq0 = p.rows_per_seq == 1 ? row : row / p.rows_per_seq;
+    const int seq  = p.slot ? p.slot[seq0] : seq0;
+    const int H    = p.hist ? (int) min((long long) max(p.hist_len[seq], 0), p.hist_stride) : 0;
+    const int E    = p.extra ? row - seq0 * p.rows_per_seq : 0;
+    if (H + E <= kLoaderIds) {
+        return;
+    }
+    const int *hrow = p.hist ? p.hist + (size_t) seq * (size_t) p.hist_stride : nullptr;
+    const int *erow = p.extra ? p.extra + (size_t) seq0 * (size_t) p.extra_stride : nullptr;
+    for (int i = tid; i < p.id_slots; i += kRowIdThreads) {
+        tkey[i] = -1;
+        tcnt[i] = 0;
+    }
+    for (int i = tid; i <= p.n_slices; i += kRowIdThreads) {
+        bcnt[i] = 0;
+    }
+    __syncthreads();
+    const unsigned smask = (unsigned) p.id_slots - 1u;
+    for (int j = tid; j < H + E; j += kRowIdThreads) {
+        const int id = (j < H ? hrow[j] : erow[1 + j - H]) - p.vocab_offset;
+        if (id >= 0 && id < p.V) {
+            unsigned hsh = ((unsigned) id * 2654435761u) & smask;
+            for (int probe = 0; probe < p.id_slots; probe++) { /* at most half of the slots are ever taken */
+                const int old = atomicCAS(&tkey[hsh], -1, id);
+                if (old == -1 || old == id) {
+                    atomicAdd(&tcnt[hsh], 1);
+                    if (old == -1) {
+                        atomicAdd(&bcnt[id / p.slice + 1], 1);
+                    }
+                    break;
+                }
+                hsh = (hsh + 1u) & smask;
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < 32) {
+        int *off   = p.pre_off + (size_t) row * (size_t) (p.n_slices + 1);
+        int  carry = 0;
+        for (int base = 0; base <= p.n_slices; base += 32) {
+            const int i    = base + tid;
+            int       incl = i <= p.n_slices ? bcnt[i] : 0;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (tid >= d) {
+                    incl += up;
+                }
+            }
+            if (i <= p.n_slices) {
+                bcnt[i] = carry + incl;
+                bpos[i] = carry + incl;
+                off[i]  = carry + incl;
+            }
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+    }
+    __syncthreads();
+    unsigned *list = p.pre_list + (size_t) row * (size_t) p.row_cap;
+    for (int i = tid; i < p.id_slots; i += kRowIdThreads) {
+        const int id = tkey[i];
+        if (id >= 0) {
+            const int c   = id / p.slice;
+            const int pos = atomicAdd(&bpos[c], 1);
+            list[pos]     = (unsigned) (id - c * p.slice) | ((unsigned) tcnt[i] << kLiBits);
+        }
+    }
+}
+
 /* ----------------------------------------------------------------- launchers -- */
 
 size_t sample_stream_fixed_smem() { return sizeof(StreamShared); }
@@ -2531,6 +2592,26 @@ static cudaError_t ensure_attributes(size_t smem_bytes) {
     return cudaSuccess;
 }
 
+static cudaError_t ensure_row_ids_attributes(size_t smem_bytes) {
+    static int  configured_smem[64] = {0};
+    int         dev                 = 0;
+    cudaError_t e                   = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    if (dev < 0 || dev >= 64) {
+        return cudaErrorInvalidDevice;
+    }
+    if (smem_bytes > 48 * 1024 && (int) smem_bytes > configured_smem[dev]) {
+        e = cudaFuncSetAttribute(row_ids_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        configured_smem[dev] = (int) smem_bytes;
+    }
+    return cudaSuccess;
+}
+
 #ifdef GB_PROFILE
 extern "C" int geist_b200_debug_prof3(long long *out, int clear) {
     if (clear) {
@@ -2547,6 +2628,18 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     cudaError_t e = ensure_attributes(smem_bytes);
     if (e != cudaSuccess) {
         return e;
+    }
+    if (p.id_slots > 0) { /* rows may bring more ids than the loader keeps in registers: prepare their lists first */
+        const size_t ids_smem = ((size_t) p.id_slots * 2 + (size_t) p.bucket_cap * 2) * sizeof(int);
+        e                     = ensure_row_ids_attributes(ids_smem);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        row_ids_kernel<<<dim3((unsigned) p.n_rows), dim3(kRowIdThreads), ids_smem, stream>>>(p);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            return e;
+        }
     }
     /* no CTA ever waits for another one, so the grid needs no co-residency */
 #ifdef GB_COOP
