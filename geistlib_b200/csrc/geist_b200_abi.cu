@@ -117,9 +117,9 @@ bool make_plan(size_t V, size_t hist_max, Plan &pl) {
     /* A slice's candidates go to global memory (cand_cap each); what shared memory limits is the room
      * for one row's merged candidates (fin_cap): a row that brings more takes the multi-pass path.
      * Short slices reserve room for every element, so that "collect everything" cannot overflow. */
-    const int    cand_cap = slice <= 1024 ? (int) round_up(slice, 32) : 256;
+    const int    cand_cap = slice <= 1024 ? (int) round_up(slice, 32) : 1024; /* a row's first slices pass about three times top-k before the threshold tightens */
     const size_t fin_full = std::max<size_t>(256, std::min<size_t>(n_slices * (size_t) cand_cap, 4096));
-    const size_t fins[]   = {fin_full, 2048, 1536, 1024, 768};
+    const size_t fins[]   = {fin_full, 3072, 2560, 2304, 2048, 1536, 1024, 768};
     for (int want_stages = 3; want_stages >= 1; want_stages--) {
         for (size_t fin : fins) {
             if (fin > fin_full) {
