@@ -364,7 +364,9 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     const size_t off_dl   = round_up(off_bm + (size_t) grid * gen_bmw * 4, 256);
     const size_t off_pl   = round_up(off_dl + (size_t) grid * gen_hcap * sizeof(gb::Pair), 256);
     const size_t off_po   = round_up(off_pl + (pl.id_slots ? n_rows * (size_t) pl.row_cap * 4 : 0), 256);
-    const size_t need     = round_up(off_po + (pl.id_slots ? n_rows * (size_t) (pl.n_slices + 1) * 4 : 0), 256);
+    const size_t slow_cap = (n_items + (size_t) grid - 1) / (size_t) grid; /* a CTA completes at most as many rows as it has items */
+    const size_t off_slow = round_up(off_po + (pl.id_slots ? n_rows * (size_t) (pl.n_slices + 1) * 4 : 0), 256);
+    const size_t need     = round_up(off_slow + (size_t) grid * slow_cap * 16, 256);
     geist_b200_ctx::Lane *ln;
     unsigned              use_now = 0;
     {
@@ -408,6 +410,8 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.gen_hist_cap     = (int) gen_hcap;
     p.pre_list         = reinterpret_cast<unsigned *>(ln->buf + off_pl);
     p.pre_off          = reinterpret_cast<int *>(ln->buf + off_po);
+    p.slow_list        = reinterpret_cast<int4 *>(ln->buf + off_slow);
+    p.slow_cap         = (int) slow_cap;
     CUDA_TRY(gb::launch_sample_stream(p, grid, pl.smem, st));
     return GEIST_OK;
 }

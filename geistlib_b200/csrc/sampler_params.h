@@ -106,6 +106,9 @@ struct SampleParams {
     int       bucket_cap;  /* n_slices + 1 rounded up to a multiple of 4 */
     unsigned *pre_list;    /* [n_rows][row_cap] (position in the slice) | (count << 14), grouped by slice */
     int      *pre_off;     /* [n_rows][n_slices + 1] where each slice's run starts */
+    /* rows left to the multi-pass path: (row, first id of the maximum, maximum, status bits), per CTA */
+    int4     *slow_list;   /* [grid][slow_cap] */
+    int       slow_cap;    /* rows one CTA can complete */
     int      hist_cap;     /* distinct-id entries reserved per slice */
     int      cand_cap;     /* candidates reserved per slice */
     int      fin_cap;      /* candidates the finisher can merge per row */

@@ -183,9 +183,12 @@ struct __align__(16) StreamShared {
     volatile int l_decoded; /* items whose configuration and id list are ready (loader -> workers) */
     int          w_done;    /* slices every worker warp is done with (workers -> loader) */
     int          done_warps;
+    int          n_slow;    /* rows left to the multi-pass path at the kernel's end */
 };
 
 enum Mode { M_ARGMAX, M_TOPK, M_TOPP, M_TEMP };
+
+constexpr int ST_DEFERRED = 1 << 30; /* inside the kernel only: the row waits for the multi-pass path at the kernel's end */
 
 /* Everything a row needs that does not depend on the slice. */
 struct RowCfg {
@@ -778,8 +781,19 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
     int         *kept_i   = p.kept_cap > 0 ? p.kept_idx + (size_t) r.row * (size_t) p.kept_cap : nullptr;
     float       *kept_v   = p.kept_cap > 0 ? p.kept_val + (size_t) r.row * (size_t) p.kept_cap : nullptr;
     /* private copy of the row, penalties applied once */
-    for (int i = g.tid; i < V; i += g.n) {
-        gr[i] = src[i];
+    if (p.aligned) { /* rows start on 16-byte boundaries: four values per load */
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+        float4       *d4 = reinterpret_cast<float4 *>(gr);
+        for (int i = g.tid; i < (V >> 2); i += g.n) {
+            d4[i] = s4[i];
+        }
+        for (int i = (V & ~3) + g.tid; i < V; i += g.n) {
+            gr[i] = src[i];
+        }
+    } else {
+        for (int i = g.tid; i < V; i += g.n) {
+            gr[i] = src[i];
+        }
     }
     if (r.pen_on) {
         unsigned *bm = p.gen_bitmap + (size_t) blockIdx.x * (size_t) p.gen_bitmap_words;
@@ -1024,7 +1038,7 @@ __device__ __forceinline__ int warp_inverse_cdf(int lane, const float *w, int n,
 }
 
 /* Runs in the finisher warps of the CTA that completed the row. Returns the row's status bits. */
-__device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, const FinBuffers &fb, const Prefetch &pf) {
+__device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, const FinBuffers &fb, const Prefetch &pf, bool defer) {
     const int       row    = r.row;
     const SliceRec *recs   = p.recs + (size_t) row * (size_t) p.n_slices;
     int            *kept_i = p.kept_cap > 0 ? p.kept_idx + (size_t) row * (size_t) p.kept_cap : nullptr;
@@ -1423,6 +1437,16 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
         }
     }
     g.sync();
+    if (defer) {
+        /* the multi-pass path sweeps the whole row several times: it is left to the end of the kernel,
+         * when all threads of the CTA are free to share it */
+        if (g.tid == 0) {
+            sh->blk_max = row_max;
+            sh->blk_arg = row_arg;
+        }
+        g.sync();
+        return st | ST_DEFERRED;
+    }
     return st | multipass_row(g, p, sh, r, row_max, row_arg, fb.fcand, 16 * p.fin_cap);
 }
 
@@ -1634,6 +1658,42 @@ __device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh
     }
 }
 
+/* Status of a finished row and, behind a sequence's last row, its generator. One thread. */
+__device__ __forceinline__ void row_epilogue(const SampleParams &p, const RowCfg &r, int row, int st) {
+    p.status[row] = st;
+    if (p.rng_out != nullptr && r.rr == p.rows_per_seq - 1) {
+        /* the sequence's generator after all of its rows drew */
+        unsigned long long s = p.rng_in ? p.rng_in[r.seq] : 1ull;
+        for (int i = 0; i < p.rows_per_seq * r.draws_per_row; i++) {
+            (void) xorshift_next(s);
+        }
+        p.rng_out[r.seq] = s;
+    }
+}
+
+/* The rows that the finisher warps left to the multi-pass path, served by all threads of the CTA
+ * once its slices are done. The ring's memory holds the radix walks' histograms. */
+__device__ __noinline__ void slow_rows(const SampleParams p, StreamShared *sh, unsigned char *ring) {
+    Grp g;
+    g.tid  = (int) threadIdx.x;
+    g.lane = g.tid & 31;
+    g.warp = g.tid >> 5;
+    g.n    = kThreads;
+    g.nw   = kThreads / 32;
+    g.bar  = 0;
+    const int n_slow = sh->n_slow;
+    for (int i = 0; i < n_slow; i++) {
+        const int4   e   = __ldcg(&p.slow_list[(size_t) blockIdx.x * (size_t) p.slow_cap + i]);
+        const RawCfg rc  = raw_config(p, e.x);
+        RowCfg       r   = row_config(p, e.x, rc, true);
+        const int    st  = e.w | multipass_row(g, p, &sh->fn, r, __int_as_float(e.z), e.y, ring, p.stages * p.stage_bytes);
+        if (g.tid == 0) {
+            row_epilogue(p, r, e.x, st);
+        }
+        g.sync();
+    }
+}
+
 /* The finisher warps' loop: they finish the rows this CTA completed, in the order they completed. */
 __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared *sh, const FinBuffers &fb) {
     GroupShared *fs = &sh->fn;
@@ -1693,7 +1753,8 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
         const Prefetch pf  = prefetch_row(g, p, row); /* ... the row's slice headers and first candidates */
         RowCfg         r   = row_config(p, row, rc, true);
         FPROF(1); /* configuration and prefetch requested */
-        const int      fst = finish_row(g, p, fs, r, fb, pf);
+        const bool     defer = sh->n_slow < p.slow_cap; /* written by this group's thread 0 only, behind a group barrier */
+        const int      fst   = finish_row(g, p, fs, r, fb, pf, defer);
 #ifdef GB_PROFILE
         fprof_t = clock64();
 #endif
@@ -1703,14 +1764,12 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
         facc[2] = gtime();
 #endif
         if (g.tid == 0) {
-            p.status[row]      = fst;
-            if (p.rng_out != nullptr && r.rr == p.rows_per_seq - 1) {
-                /* the sequence's generator after all of its rows drew */
-                unsigned long long s = p.rng_in ? p.rng_in[r.seq] : 1ull;
-                for (int i = 0; i < p.rows_per_seq * r.draws_per_row; i++) {
-                    (void) xorshift_next(s);
-                }
-                p.rng_out[r.seq] = s;
+            if (fst & ST_DEFERRED) {
+                const int n = sh->n_slow;
+                p.slow_list[(size_t) blockIdx.x * (size_t) p.slow_cap + n] = make_int4(row, fs->blk_arg, __float_as_int(fs->blk_max), fst & ~ST_DEFERRED);
+                sh->n_slow = n + 1;
+            } else {
+                row_epilogue(p, r, row, fst);
             }
         }
         g.sync();
@@ -1910,6 +1969,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         sh->l_decoded  = 0;
         sh->w_done     = 0;
         sh->done_warps = 0;
+        sh->n_slow     = 0;
     }
     __syncthreads();
 
@@ -2178,13 +2238,9 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             g_prof2[blockIdx.x][13] = lp_idle;
         }
 #endif
-        return;
-    }
-    if (threadIdx.x >= kWorkThreads + 32 && threadIdx.x < kWorkThreads + 64) {
+    } else if (threadIdx.x >= kWorkThreads + 32 && threadIdx.x < kWorkThreads + 64) {
         publisher_loop((int) threadIdx.x - kWorkThreads - 32, p, sh, my_count);
-        return;
-    }
-    if (threadIdx.x >= kWorkThreads + 64) {
+    } else if (threadIdx.x >= kWorkThreads + 64) {
         Grp g;
         g.tid  = (int) threadIdx.x - kWorkThreads - 64;
         g.lane = g.tid & 31;
@@ -2193,9 +2249,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         g.nw   = kFinWarps;
         g.bar  = 2;
         finisher_loop(g, p, sh, fb);
-        return;
-    }
-
+    } else {
     /* ================================================================ workers == */
     /* Every worker warp walks the CTA's slices at its own pace: it owns a fixed share of each slice
      * (float4 [warp * L, (warp + 1) * L), lanes interleaved), waits for the slice's copy, applies the
@@ -2480,6 +2534,14 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         if (atomicAdd(&sh->done_warps, 1) == kWorkWarps - 1) {
             sh->q_done = 1;
         }
+    }
+    } /* workers */
+
+    /* every role has ended (all of their waits are bounded): what is left are the rows that need the
+     * multi-pass path, shared by all threads */
+    __syncthreads();
+    if (sh->n_slow > 0) {
+        slow_rows(p, sh, ring);
     }
 }
 
