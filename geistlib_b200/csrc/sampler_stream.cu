@@ -637,7 +637,7 @@ struct RadixOut {
  * histograms, one per warp where the room allows), then a scan from the top value down. hm / hc
  * hold copies * 256 doubles / ints.
  */
-template <class KeyF, class MassF>
+template <bool kUnit = false, class KeyF, class MassF>
 __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *hc, int copies, const float *row, int V, double target, bool inclusive, KeyF &&key,
                                MassF &&mass) {
     RadixOut out;
@@ -659,11 +659,15 @@ __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *h
         row_sweep(g, row, V, [&](float x, int i) {
             const unsigned k = key(x);
             if (level == 3 || (k >> (shift + 8)) == (pre >> (shift + 8))) {
-                const double m = mass(x, i);
-                if (m > 0.0) {
-                    const unsigned d = (k >> shift) & 255u;
-                    atomicAdd(&mym[d], m);
+                const unsigned d = (k >> shift) & 255u;
+                if (kUnit) { /* every entry weighs one: the counts are the masses */
                     atomicAdd(&myc[d], 1);
+                } else {
+                    const double m = mass(x, i);
+                    if (m > 0.0) {
+                        atomicAdd(&mym[d], m);
+                        atomicAdd(&myc[d], 1);
+                    }
                 }
             }
         });
@@ -682,6 +686,9 @@ __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *h
                 for (int w = 0; w < copies; w++) {
                     m8[q] += hm[w * 256 + b];
                     c8[q] += hc[w * 256 + b];
+                }
+                if (kUnit) {
+                    m8[q] = (double) c8[q];
                 }
                 lane_m += m8[q];
                 lane_c += c8[q];
@@ -823,7 +830,7 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
         /* the k-th entry in (value desc, id asc) order: a radix walk on counts, then the ids of its ties */
         auto                     okey   = [](float x) { return order_key(x); };
         auto                     one    = [](float, int) { return 1.0; };
-        const RadixOut           rs     = radix_mass(g, sh, hm, hc, copies, gr, V, (double) r.k, true, okey, one);
+        const RadixOut           rs     = radix_mass<true>(g, sh, hm, hc, copies, gr, V, (double) r.k, true, okey, one);
         const unsigned long long t_set  = rs.found ? resolve_ties(g, sh, gr, V, idx_bits, rs, (double) r.k, true, okey, one) : 0ull;
         auto                     in_set = [&](float x, int i) { return composite(order_key(x), i, idx_bits) >= t_set; };
         if (r.select_only) {
