@@ -315,3 +315,72 @@ def test_temperature_penalised_ids_late_in_the_crossing_segment(ctx):
     g = run_gpu(ctx, x, 1.0, 0, 1.0, st, rep=1.5, freq=0.7, pres=0.3, history=h)
     o = oracle.port.sample_batch(x, 1.0, 0, 1.0, st, rep=1.5, freq=0.7, pres=0.3, hist=h)
     check_tokens(g, o)
+
+
+def _long_history_case(rows, V, stride, seed):
+    """Histories of mixed lengths around the 128-id limit of the loader's register path, ids drawn
+    from small pools so that most repeat, some rows with every id in one slice."""
+    rng = np.random.default_rng(seed)
+    h = np.zeros((rows, stride), np.int32)
+    lens = np.array([(0, 5, 128, 129, 130, 200, 333, stride)[r % 8] for r in range(rows)], np.int32)
+    for r in range(rows):
+        if r % 3 == 0:
+            pool = rng.integers(0, min(V, 14000), size=90)  # all in the first slice, heavy repeats
+        elif r % 3 == 1:
+            pool = rng.integers(0, V, size=40 + 10 * r)
+        else:
+            pool = np.arange(V - 300, V)  # the last ids of the row, the ragged tail of the last slice
+        h[r] = rng.choice(pool, size=stride)
+    return h, lens
+
+
+@pytest.mark.parametrize("T,K,P", [(0.0, 0, 1.0), (0.8, 40, 1.0), (1.0, 0, 1.0), (0.9, 0, 0.9)])
+def test_long_histories_of_mixed_lengths(ctx, T, K, P):
+    V, rows, stride = 128256, 48, 700
+    x = normal_logits(rows, V, 2.5, 7001)
+    h, lens = _long_history_case(rows, V, stride, 7002)
+    for r in range(rows):  # the ids that decide the row are among the penalised ones
+        top = np.argsort(-x[r])[:6]
+        h[r, :min(6, lens[r])] = top[:min(6, lens[r])]
+    st = independent_states(oracle.port, 7003, rows)
+    rep = np.where(np.arange(rows) % 2 == 0, 1.3, 1.0).astype(np.float32)
+    freq = np.where(np.arange(rows) % 4 < 2, 0.25, 0.0).astype(np.float32)
+    pres = np.full(rows, 0.1, np.float32)
+    g = run_gpu(ctx, x, T, K, P, st, rep=rep, freq=freq, pres=pres, history=h, history_len=lens, want_logits=True)
+    o = oracle.port.sample_batch(x, T, K, P, st, rep=rep, freq=freq, pres=pres, hist=h, hist_len=lens, want_logits=True)
+    assert np.array_equal(g["logits"].view(np.uint32), o["logits"].view(np.uint32))
+    check_tokens(g, o)
+    assert np.array_equal(g["rng_state"], o["rng_state"])
+
+
+def test_long_histories_with_fed_tokens_of_verify_rows(ctx):
+    V, S, R, H = 50257, 5, 6, 300
+    x = normal_logits(S * R, V, 2.5, 7101)
+    rng = np.random.default_rng(7102)
+    h = rng.choice(rng.integers(0, V, size=70), size=(S, H)).astype(np.int32)
+    lens = np.array([H, 127, 128, 126, 250], np.int32)  # 127 + up to 5 fed tokens crosses the limit inside a sequence
+    fed = np.argsort(-x.reshape(S, R, V)[:, -1], axis=1)[:, :R].astype(np.int32)
+    fed[:, 2] = fed[:, 1]  # a fed token twice: counted twice
+    st = independent_states(oracle.port, 7103, S)
+    for T in (0.0, 0.8):
+        g = run_gpu(ctx, x, T, 0, 1.0, st, rows_per_seq=R, rep=1.2, freq=0.5, pres=0.4, history=h, history_len=lens, fed=fed, want_logits=True)
+        o = oracle.port.sample_batch(x, T, 0, 1.0, st, rows_per_seq=R, rep=1.2, freq=0.5, pres=0.4, hist=h, hist_len=lens, extra=fed, want_logits=True)
+        assert np.array_equal(g["logits"].view(np.uint32), o["logits"].view(np.uint32))
+        check_tokens(g, o)
+
+
+def test_long_histories_on_a_vocabulary_shard(ctx):
+    """A shard sees only the ids of its own range; the others are skipped, not wrapped."""
+    V, rows, stride, off = 128256, 12, 512, 40000
+    vs = 32064
+    x = normal_logits(rows, V, 2.5, 7201)
+    h, lens = _long_history_case(rows, V, stride, 7202)
+    lens[:] = stride
+    shard = np.ascontiguousarray(x[:, off:off + vs])
+    dT, dK, dP = per_seq(rows, 0.0, 0, 1.0)
+    st = independent_states(oracle.port, 7203, rows)
+    out = ctx.sample_batch(to_dev(shard), dT, dK, dP, u64_to_dev(st), rep=to_dev(np.full(rows, 1.4, np.float32)),
+                           freq=to_dev(np.full(rows, 0.3, np.float32)), history=to_dev(h), history_len=to_dev(lens),
+                           vocab_offset=off, want_logits=True)
+    o = oracle.port.sample_batch(x, 0.0, 0, 1.0, st, rep=1.4, freq=0.3, hist=h, want_logits=True)
+    assert np.array_equal(out["logits"].cpu().numpy().view(np.uint32), o["logits"][:, off:off + vs].view(np.uint32))
