@@ -24,7 +24,10 @@ constexpr int kSliceMax     = 14336;          /* floats of one row slice: at mos
 static_assert(kSliceMax <= 32 * kWorkThreads, "a worker thread holds at most 8 float4 of a slice");
 constexpr int kTopKClamp    = 8192;           /* sampler.c:212-215 */
 constexpr int kFastKMax     = 256;            /* largest k served by the threshold fast path */
-constexpr int kNucleusProbe = 32;             /* entries the top-p fast path looks at */
+#ifndef GB_NUCLEUS_PROBE
+#define GB_NUCLEUS_PROBE 32
+#endif
+constexpr int kNucleusProbe = GB_NUCLEUS_PROBE; /* entries the top-p fast path looks at */
 constexpr int kMaxSlices    = 1024;           /* slices per row the finisher can merge */
 constexpr int kMaxStages    = 4;              /* depth of the bulk-copy ring */
 constexpr int kFinBitmapWords = 32;           /* finisher: one bit per entry of a crossing segment (at most 1024) */
