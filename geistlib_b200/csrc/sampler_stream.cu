@@ -211,9 +211,10 @@ struct RawCfg {
     float T, top_p;
     int   top_k, hist_len;
     float rep, freq, pres;
+    unsigned long long rng; /* the sequence's generator word (only when asked for) */
 };
 
-__device__ __forceinline__ RawCfg raw_config(const SampleParams &p, int row) {
+__device__ __forceinline__ RawCfg raw_config(const SampleParams &p, int row, bool want_rng = false) {
     RawCfg    c;
     const int seq0 = p.rows_per_seq == 1 ? row : row / p.rows_per_seq;
     c.seq          = p.slot ? p.slot[seq0] : seq0;
@@ -224,6 +225,7 @@ __device__ __forceinline__ RawCfg raw_config(const SampleParams &p, int row) {
     c.rep          = p.rep ? p.rep[c.seq] : 1.0f;
     c.freq         = p.freq ? p.freq[c.seq] : 0.0f;
     c.pres         = p.pres ? p.pres[c.seq] : 0.0f;
+    c.rng          = (want_rng && p.rng_in) ? p.rng_in[c.seq] : 1ull; /* travels with the other parameters */
     return c;
 }
 
@@ -257,7 +259,7 @@ __device__ __forceinline__ RowCfg row_config(const SampleParams &p, int row, con
     r.draws_per_row = (r.T > 0.0f && !r.select_only) ? 1 : 0;
     r.rng           = 1ull;
     if (want_rng) {
-        r.rng = p.rng_in ? p.rng_in[r.seq] : 1ull;
+        r.rng = c.rng;
         for (int i = 0; i < r.rr * r.draws_per_row; i++) {
             (void) xorshift_next(r.rng);
         }
@@ -1691,7 +1693,7 @@ __device__ __noinline__ void slow_rows(const SampleParams p, StreamShared *sh, u
     const int n_slow = sh->n_slow;
     for (int i = 0; i < n_slow; i++) {
         const int4   e   = __ldcg(&p.slow_list[(size_t) blockIdx.x * (size_t) p.slow_cap + i]);
-        const RawCfg rc  = raw_config(p, e.x);
+        const RawCfg rc  = raw_config(p, e.x, true);
         RowCfg       r   = row_config(p, e.x, rc, true);
         const int    st  = e.w | multipass_row(g, p, &sh->fn, r, __int_as_float(e.z), e.y, ring, p.stages * p.stage_bytes);
         if (g.tid == 0) {
@@ -1756,7 +1758,7 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
 #ifdef GB_PROFILE
         const long long ft0 = clock64();
 #endif
-        const RawCfg   rc  = raw_config(p, row);   /* in flight together with ... */
+        const RawCfg   rc  = raw_config(p, row, true); /* in flight together with ... */
         const Prefetch pf  = prefetch_row(g, p, row); /* ... the row's slice headers and first candidates */
         RowCfg         r   = row_config(p, row, rc, true);
         FPROF(1); /* configuration and prefetch requested */
