@@ -969,7 +969,17 @@ static_assert(kFinThreads * 8 >= 1024, "the finisher threads walk a crossing seg
 constexpr int kSpecSlots = 8; /* per finisher thread: candidates fetched before the slices' counts are known */
 /* how many of each slice's candidates that is (0: the row has too many slices) */
 __device__ __forceinline__ int spec_per_slice(const SampleParams &p) {
-    return p.n_slices * 48 <= kFinThreads * kSpecSlots ? 48 : 0;
+    return p.n_slices * 64 <= kFinThreads * kSpecSlots ? 64 : (p.n_slices * 48 <= kFinThreads * kSpecSlots ? 48 : 0);
+}
+/* flat index of the request -> (slice, position) */
+__device__ __forceinline__ void spec_split(int f, int k_spec, int &cc, int &i) {
+    if (k_spec == 64) {
+        cc = f >> 6;
+        i  = f & 63;
+    } else {
+        cc = f / 48;
+        i  = f - cc * 48;
+    }
 }
 struct Prefetch {
     int4      hdr;              /* slice record header {max, arg, n_cand, st} of slice g.tid */
@@ -996,8 +1006,9 @@ __device__ __forceinline__ Prefetch prefetch_row(const Grp &g, const SampleParam
         const int f = g.tid + kFinThreads * m;
         pf.c[m]     = 0;
         if (f < flat) {
-            const int cc = f / kSpec, i = f - cc * kSpec;
-            pf.c[m]      = __ldcg(reinterpret_cast<const long long *>(base + (size_t) cc * (size_t) p.cand_cap + i));
+            int cc, i;
+            spec_split(f, kSpec, cc, i);
+            pf.c[m] = __ldcg(reinterpret_cast<const long long *>(base + (size_t) cc * (size_t) p.cand_cap + i));
         }
     }
     return pf;
@@ -1295,7 +1306,8 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
             for (int m = 0; m < kSpecSlots; m++) {
                 const int f = g.tid + kFinThreads * m;
                 if (f < p.n_slices * kSpec) {
-                    const int cc = f / kSpec, i = f - cc * kSpec;
+                    int cc, i;
+                    spec_split(f, kSpec, cc, i);
                     if (i < sh->bins[cc]) {
                         int off = 0;
                         for (int q = 0; q < cc; q++) {
