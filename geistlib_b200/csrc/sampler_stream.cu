@@ -2495,6 +2495,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
         if (g.lane == 0) {
             mbar_arrive(&sh->empty[stage]); /* this warp is done with the stage */
         }
+        PROF2(10); /* threshold + candidates */
         if (mode == M_TEMP || (mode == M_TOPP && sel)) {
             /* sum of e_i relative to the WARP's maximum (top-p: of what stays below the threshold); the
              * mail writer rescales to the slice maximum and the finisher to the row maximum. -inf
@@ -2513,10 +2514,12 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
             } else {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    const float e0 = x[i].x >= tau ? 0.0f : expf(scaled_arg(x[i].x, ref, inv_t));
-                    const float e1 = x[i].y >= tau ? 0.0f : expf(scaled_arg(x[i].y, ref, inv_t));
-                    const float e2 = x[i].z >= tau ? 0.0f : expf(scaled_arg(x[i].z, ref, inv_t));
-                    const float e3 = x[i].w >= tau ? 0.0f : expf(scaled_arg(x[i].w, ref, inv_t));
+                    /* what passed the threshold is a candidate and counts there: its argument becomes -inf
+                     * (exp gives 0), so that the 32 evaluations stay one straight line and overlap */
+                    const float e0 = expf(x[i].x >= tau ? -CUDART_INF_F : scaled_arg(x[i].x, ref, inv_t));
+                    const float e1 = expf(x[i].y >= tau ? -CUDART_INF_F : scaled_arg(x[i].y, ref, inv_t));
+                    const float e2 = expf(x[i].z >= tau ? -CUDART_INF_F : scaled_arg(x[i].z, ref, inv_t));
+                    const float e3 = expf(x[i].w >= tau ? -CUDART_INF_F : scaled_arg(x[i].w, ref, inv_t));
                     sum += (double) ((e0 + e1) + (e2 + e3));
                 }
             }
