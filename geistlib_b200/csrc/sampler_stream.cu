@@ -776,7 +776,7 @@ __device__ unsigned long long resolve_ties(const Grp &g, GroupShared *sh, const 
     return bisect_mass(g, sh, row, V, idx_bits, target, inclusive, key, mass, (unsigned long long) ro.key << idx_bits, idx_bits - 1);
 }
 
-/* The finisher warps alone serve a row whose kept set does not fit the fast path. */
+/* All threads of the CTA serve a row whose kept set does not fit the one-pass path. */
 __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, float row_max, int row_arg, void *hist_mem, int hist_bytes) {
     /* room for the byte histograms of the radix walks: per warp where it fits, else one for all */
     const int copies = hist_bytes >= g.nw * 256 * 12 ? g.nw : 1;
@@ -1058,7 +1058,7 @@ __device__ __forceinline__ int warp_inverse_cdf(int lane, const float *w, int n,
 }
 
 /* Runs in the finisher warps of the CTA that completed the row. Returns the row's status bits. */
-__device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, const FinBuffers &fb, const Prefetch &pf, bool defer) {
+__device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, const FinBuffers &fb, const Prefetch &pf) {
     const int       row    = r.row;
     const SliceRec *recs   = p.recs + (size_t) row * (size_t) p.n_slices;
     int            *kept_i = p.kept_cap > 0 ? p.kept_idx + (size_t) row * (size_t) p.kept_cap : nullptr;
@@ -1458,17 +1458,14 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
         }
     }
     g.sync();
-    if (defer) {
-        /* the multi-pass path sweeps the whole row several times: it is left to the end of the kernel,
-         * when all threads of the CTA are free to share it */
-        if (g.tid == 0) {
-            sh->blk_max = row_max;
-            sh->blk_arg = row_arg;
-        }
-        g.sync();
-        return st | ST_DEFERRED;
+    /* the multi-pass path sweeps the whole row several times: it is left to the end of the kernel,
+     * when all threads of the CTA are free to share it */
+    if (g.tid == 0) {
+        sh->blk_max = row_max;
+        sh->blk_arg = row_arg;
     }
-    return st | multipass_row(g, p, sh, r, row_max, row_arg, fb.fcand, 16 * p.fin_cap);
+    g.sync();
+    return st | ST_DEFERRED;
 }
 
 /* Optional cycle accounting of worker thread 0 (build with -DGB_PROFILE): where one CTA's time goes. */
@@ -1774,8 +1771,7 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
         const Prefetch pf  = prefetch_row(g, p, row); /* ... the row's slice headers and first candidates */
         RowCfg         r   = row_config(p, row, rc, true);
         FPROF(1); /* configuration and prefetch requested */
-        const bool     defer = sh->n_slow < p.slow_cap; /* written by this group's thread 0 only, behind a group barrier */
-        const int      fst   = finish_row(g, p, fs, r, fb, pf, defer);
+        const int      fst = finish_row(g, p, fs, r, fb, pf);
 #ifdef GB_PROFILE
         fprof_t = clock64();
 #endif
@@ -1786,9 +1782,13 @@ __device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared 
 #endif
         if (g.tid == 0) {
             if (fst & ST_DEFERRED) {
-                const int n = sh->n_slow;
-                p.slow_list[(size_t) blockIdx.x * (size_t) p.slow_cap + n] = make_int4(row, fs->blk_arg, __float_as_int(fs->blk_max), fst & ~ST_DEFERRED);
-                sh->n_slow = n + 1;
+                const int n = sh->n_slow; /* a CTA completes at most slow_cap rows */
+                if (n < p.slow_cap) {
+                    p.slow_list[(size_t) blockIdx.x * (size_t) p.slow_cap + n] = make_int4(row, fs->blk_arg, __float_as_int(fs->blk_max), fst & ~ST_DEFERRED);
+                    sh->n_slow = n + 1;
+                } else {
+                    p.status[row] = ST_INTERNAL;
+                }
             } else {
                 row_epilogue(p, r, row, fst);
             }
