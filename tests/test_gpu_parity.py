@@ -384,3 +384,33 @@ def test_long_histories_on_a_vocabulary_shard(ctx):
                            vocab_offset=off, want_logits=True)
     o = oracle.port.sample_batch(x, 0.0, 0, 1.0, st, rep=1.4, freq=0.3, hist=h, want_logits=True)
     assert np.array_equal(out["logits"].cpu().numpy().view(np.uint32), o["logits"][:, off:off + vs].view(np.uint32))
+
+
+def test_many_multi_pass_rows_per_block(ctx):
+    """Every row needs the multi-pass path (top-k beyond the one-pass limit, wide nuclei), several per
+    thread block: they are queued while the block streams and served at its end."""
+    V, rows = 32000, 480
+    x = normal_logits(rows, V, 2.5, 8101)
+    T = np.where(np.arange(rows) % 2 == 0, 0.8, 1.0).astype(np.float32)
+    K = np.where(np.arange(rows) % 2 == 0, 300, 0).astype(np.int32)
+    P = np.where(np.arange(rows) % 2 == 0, 1.0, 0.97).astype(np.float32)
+    st = independent_states(oracle.port, 8102, rows)
+    g = run_gpu(ctx, x, T, K, P, st)
+    o = oracle.port.sample_batch(x, T, K, P, st)
+    check_tokens(g, o)
+    assert np.array_equal(g["rng_state"], o["rng_state"])
+    assert (g["status"] & 2).all()  # informational bit: the multi-pass path served the row
+
+
+def test_wide_topk_with_long_histories(ctx):
+    """Top-k 200 with 600-id histories: less shared-memory room for a row's merged candidates, so some
+    rows change to the multi-pass path; the tokens do not depend on which path served a row."""
+    V, rows, H = 128256, 64, 600
+    x = normal_logits(rows, V, 2.5, 8201)
+    h = histories(rows, H, V, 8202)
+    for r in range(rows):
+        h[r, :20] = np.argsort(-x[r])[:20]
+    st = independent_states(oracle.port, 8203, rows)
+    g = run_gpu(ctx, x, 0.9, 200, 1.0, st, rep=1.2, freq=0.1, history=h)
+    o = oracle.port.sample_batch(x, 0.9, 200, 1.0, st, rep=1.2, freq=0.1, hist=h)
+    check_tokens(g, o)
