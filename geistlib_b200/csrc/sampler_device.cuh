@@ -15,8 +15,9 @@
 namespace gb {
 
 __device__ __forceinline__ unsigned order_key(float x) {
-    /* monotone map float -> uint32 (larger float, larger key) */
-    unsigned b = __float_as_uint(x);
+    /* monotone map float -> uint32 (larger float, larger key); -0 and +0 are one value, as the
+     * comparison of floats has it (x + 0 turns -0 into +0 and leaves everything else alone) */
+    unsigned b = __float_as_uint(x + 0.0f);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 

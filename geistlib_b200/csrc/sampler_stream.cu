@@ -886,8 +886,11 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
     } else {
         /* top-p with any nucleus size: the copy becomes e_i, then p_i (sampler.c:245-255) */
         double acc = 0.0;
+        /* e_i as a correctly rounded expf gives it: with a nucleus of tens of thousands of ids an
+         * exponential that is off by a fraction of an ulp on average moves the running sum by more than
+         * the distance between two neighbours of the walk */
         row_rewrite(g, gr, V, [&](float x, int) {
-            const float e = expf(scaled_arg(x, row_max, r.inv_t));
+            const float e = exp_exact(scaled_arg(x, row_max, r.inv_t));
             acc += (double) e;
             return e;
         });

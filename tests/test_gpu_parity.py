@@ -414,3 +414,32 @@ def test_wide_topk_with_long_histories(ctx):
     g = run_gpu(ctx, x, 0.9, 200, 1.0, st, rep=1.2, freq=0.1, history=h)
     o = oracle.port.sample_batch(x, 0.9, 200, 1.0, st, rep=1.2, freq=0.1, hist=h)
     check_tokens(g, o)
+
+
+def test_signed_zeros_are_one_value(ctx):
+    """-0.0 and +0.0 compare equal in the reference's sort and argmax, so ties between them go to the
+    lower id; a key built from the bit pattern alone would put every +0.0 first."""
+    V, rows = 1582, 96
+    rng = np.random.default_rng(8301)
+    x = (np.round(rng.standard_normal((rows, V)).astype(np.float32) * 0.02) / 2).astype(np.float32)  # only +0.0 and -0.0
+    assert np.signbit(x).any() and not np.signbit(x).all()
+    x[::3, 7] = 0.5  # some rows with one clear maximum
+    st = independent_states(oracle.port, 8302, rows)
+    for (T, K, P) in [(0.0, 0, 1.0), (0.3, 40, 1.0), (1.5, 200, 1.0), (1.0, 300, 1.0), (1.0, 0, 0.3)]:
+        g = run_gpu(ctx, x, T, K, P, st, kept_cap=40)
+        o = oracle.port.sample_batch(x, T, K, P, st, detail_cap=40)
+        check_tokens(g, o)
+        if K == 40:
+            assert np.array_equal(g["kept_idx"], o["detail_idx"])
+
+
+def test_topp_nucleus_of_most_of_the_vocabulary(ctx):
+    """Nearly flat rows: the nucleus holds over a hundred thousand ids a few 1e-6 apart, so the draw
+    lands on the reference's id only if every e_i is the correctly rounded one."""
+    V, rows = 151936, 256
+    x = normal_logits(rows, V, 0.01, 8401)
+    st = independent_states(oracle.port, 8402, rows)
+    P = np.where(np.arange(rows) % 2 == 0, 0.9, 0.99).astype(np.float32)
+    g = run_gpu(ctx, x, 1.0, 0, P, st)
+    o = oracle.port.sample_batch(x, 1.0, 0, P, st)
+    check_tokens(g, o)
