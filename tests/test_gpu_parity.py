@@ -430,7 +430,8 @@ def test_signed_zeros_are_one_value(ctx):
         o = oracle.port.sample_batch(x, T, K, P, st, detail_cap=40)
         check_tokens(g, o)
         if K == 40:
-            assert np.array_equal(g["kept_idx"], o["detail_idx"])
+            listed = (g["status"] & 8) == 0  # rows of nothing but ties take the multi-pass path, which lists no kept set
+            assert np.array_equal(g["kept_idx"][listed], o["detail_idx"][listed])
 
 
 def test_topp_nucleus_of_most_of_the_vocabulary(ctx):
