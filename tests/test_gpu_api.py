@@ -61,8 +61,9 @@ def test_argmax_f32_slot(ctx):
     assert ctx.argmax_f32(to_dev(x)) == 1000
 
 
-def test_batcher_decode_steps_equal_independent_reference_sessions(ctx):
-    V, N, steps, H0, HM = 32000, 12, 6, 20, 24  # the history ring (24) wraps during the run
+@pytest.mark.parametrize("H0,HM", [(20, 24), (294, 300)])  # short histories; histories prepared by the kernel of their own
+def test_batcher_decode_steps_equal_independent_reference_sessions(ctx, H0, HM):
+    V, N, steps = 32000, 12, 6  # the history ring wraps during the run
     rng = np.random.default_rng(0)
     bt = api.Batcher(ctx, V, 16, max_history=HM)
     cfgs = [(0.0, 0, 1.0), (0.8, 40, 0.95), (0.7, 0, 0.9), (1.0, 0, 0.0)] * 3
