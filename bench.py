@@ -43,7 +43,7 @@ SEED = 1234
 BYTES_PER_ROW = 4 * V + 4 * H + 16 + 4
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload (132.70 MB + 4.60 MB), from the
 # ncu capture summarised under profiles/; a bench run cannot measure it itself.
-NCU_TRAFFIC_BYTES = 137.1e6
+NCU_TRAFFIC_BYTES = 137.9e6
 WORKLOAD = ("B=256 rows x V=128256 fp32 logits ~ N(0,2.5^2) with 8 ids/row +12; temperature 0.8, top_k 40, "
             "top_p 0.95 (top_k precedence), repetition penalty 1.1 over 64-token history, 1 draw/row, seed 1234")
 
