@@ -85,3 +85,72 @@ def test_random_batch_matches_the_oracle(ctx, seed):
         if m:
             rel = np.abs(kp[r, :m] - ref["detail_prob"][r, :m]) / np.maximum(ref["detail_prob"][r, :m], 1e-30)
             assert rel.max() <= 1e-5, (c["what"], r)  # fp32 probabilities: 1e-5 relative
+
+
+@pytest.mark.parametrize("seed,HM", [(9100, 24), (9101, 24), (9102, 200), (9103, 200)])
+def test_random_session_traffic_through_the_batcher(ctx, seed, HM):
+    """Sessions open and close, decode steps and verify passes take random subsets of them in random
+    order; every session must behave like a reference session of its own (generator word, history
+    ring of HM ids, sampler options)."""
+    from geistlib_b200 import api
+    port = oracle.port
+    V, MAXS = 6000, 12
+    rg = np.random.default_rng(seed)
+    bt = api.Batcher(ctx, V, MAXS, max_history=HM)
+    live = {}  # session id -> dict(cfg, state, hist)
+
+    def open_one():
+        T = float(rg.choice([0.0, 0.6, 1.0])); K = int(rg.choice([0, 1, 20, 300])); P = float(rg.choice([1.0, 0.9, 0.5]))
+        rep = float(rg.choice([1.0, 1.2])); freq = float(rg.choice([0.0, 0.3])); pres = float(rg.choice([0.0, 0.2]))
+        sd = int(rg.integers(1, 1 << 30))
+        s = bt.open(temperature=T, top_p=P, top_k=K, seed=sd, rep=rep, freq=freq, pres=pres)
+        h = rg.integers(0, V, int(rg.integers(0, HM + 1))).astype(np.int32)
+        if len(h):
+            bt.push_history(s, h)
+        live[s] = dict(cfg=(T, K, P, rep, freq, pres), state=port.rng_seed(sd), hist=list(h))
+
+    def ref_rows(s, x, rows_per_seq=1, fed=None):
+        T, K, P, rep, freq, pres = live[s]["cfg"]
+        hh = np.array(live[s]["hist"][-HM:], np.int32)[None, :]
+        kw = dict(rep=rep, freq=freq, pres=pres)
+        if hh.shape[1]:
+            kw["hist"] = hh
+        if fed is not None:
+            kw["extra"] = fed[None, :]
+        return port.sample_batch(x, T, K, P, [live[s]["state"]], rows_per_seq=rows_per_seq, **kw)
+
+    for _ in range(3):
+        open_one()
+    for op in range(40):
+        what = rg.choice(["open", "close", "step", "step", "step", "verify"])
+        if what == "open" and len(live) < MAXS:
+            open_one()
+        elif what == "close" and len(live) > 1:
+            s = int(rg.choice(list(live)))
+            bt.close_session(s)
+            del live[s]
+        elif what == "step":
+            ss = [int(s) for s in rg.permutation(list(live))[:int(rg.integers(1, len(live) + 1))]]
+            x = (rg.standard_normal((len(ss), V)) * 2.5).astype(np.float32)
+            got = bt.step(ss, to_dev(x) if op % 2 else x)
+            for i, s in enumerate(ss):
+                o = ref_rows(s, x[i:i + 1])
+                assert got[i] == o["tokens"][0], (op, s, live[s]["cfg"])
+                live[s]["state"] = int(o["rng_state"][0])
+                live[s]["hist"].append(int(got[i]))
+                assert bt.get_rng(s) == live[s]["state"]
+        elif what == "verify":
+            ss = [int(s) for s in rg.permutation(list(live))[:int(rg.integers(1, len(live) + 1))]]
+            k = int(rg.integers(1, 7))
+            x = (rg.standard_normal((len(ss) * k, V)) * 2.5).astype(np.float32)
+            x[:, :3] += 9.0  # a few likely tokens, so that some proposals are accepted
+            fed = rg.integers(0, 3, (len(ss), k)).astype(np.int32)
+            acc, nout, toks = bt.verify(ss, fed, to_dev(x))
+            for i, s in enumerate(ss):
+                o = ref_rows(s, x[i * k:(i + 1) * k], rows_per_seq=k, fed=fed[i])
+                a, em = port.spec_accept(fed[i], o["tokens"])
+                assert acc[i] == a and nout[i] == len(em) and np.array_equal(toks[i, :nout[i]], em), (op, s, k)
+                live[s]["state"] = int(o["rng_state"][0])
+                live[s]["hist"].extend(int(t) for t in em[1:])  # em[0] is the pending token: it joined the history when it was sampled
+                assert bt.get_rng(s) == live[s]["state"]
+    bt.close()
