@@ -152,8 +152,10 @@ struct geist_b200_batch {
     const float   *frequency_penalty;  /* per sequence or NULL   (EXTENSION) */
     const float   *presence_penalty;   /* per sequence or NULL   (EXTENSION) */
     const int32_t *history;            /* [*, history_stride] or NULL */
-    size_t         history_stride;     /* also the longest history a row can have; with rows_per_seq at most 8192 ids per row
-                                        * (GEIST_E_UNSUPPORTED beyond). Rows of more than 128 ids cost one more kernel launch. */
+    size_t         history_stride;     /* also the longest history a row can have. GEIST_E_UNSUPPORTED when the id lists of the
+                                        * slices in flight no longer fit shared memory beside one stage of logits (about 7000 ids
+                                        * per row at 128256 columns, never more than 8192). Rows of more than 128 ids cost one
+                                        * more kernel launch. */
     const int32_t *history_len;        /* per sequence */
     const int32_t *fed_tokens;         /* optional [n_seq, fed_stride]: row r also counts fed[1..r] */
     size_t         fed_stride;
