@@ -444,3 +444,19 @@ def test_topp_nucleus_of_most_of_the_vocabulary(ctx):
     g = run_gpu(ctx, x, 1.0, 0, P, st)
     o = oracle.port.sample_batch(x, 1.0, 0, P, st)
     check_tokens(g, o)
+
+
+def test_history_sizes_up_to_the_limit(ctx):
+    """4000 ids per row still run (one ring stage less), 9000 are refused with a message."""
+    from geistlib_b200 import api
+    V, rows = 128256, 6
+    x = normal_logits(rows, V, 2.5, 8501)
+    h = histories(rows, 4000, V, 8502)
+    h[:, :8] = np.argsort(-x, axis=1)[:, :8]
+    st = independent_states(oracle.port, 8503, rows)
+    for (T, K) in [(0.0, 0), (0.8, 40)]:
+        g = run_gpu(ctx, x, T, K, 1.0, st, rep=1.3, freq=0.05, history=h)
+        o = oracle.port.sample_batch(x, T, K, 1.0, st, rep=1.3, freq=0.05, hist=h)
+        check_tokens(g, o)
+    with pytest.raises(api.GeistError):
+        run_gpu(ctx, x, 0.0, 0, 1.0, st, rep=1.3, history=histories(rows, 9000, V, 8504))
