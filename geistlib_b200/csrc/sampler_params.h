@@ -112,6 +112,7 @@ struct SampleParams {
     /* rows left to the multi-pass path: (row, first id of the maximum, maximum, status bits), per CTA */
     int4     *slow_list;   /* [grid][slow_cap] */
     int       slow_cap;    /* rows one CTA can complete */
+    int       chained;     /* 1: launched as a programmatic dependent of the kernel before it; waits for it before any global access */
     int      hist_cap;     /* distinct-id entries reserved per slice */
     int      cand_cap;     /* candidates reserved per slice */
     int      fin_cap;      /* candidates the finisher can merge per row */

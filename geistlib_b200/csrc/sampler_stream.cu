@@ -1954,6 +1954,15 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
     const int row0     = my_first / p.n_slices;
     const int c0       = my_first - row0 * p.n_slices;
 
+    if (p.chained) {
+        /* Launched as a programmatic dependent of the kernel before it in the stream: the thread block may
+         * have been placed while that kernel's last blocks were still at work. Everything it touches in
+         * global memory waits here for that kernel to be complete and visible, so the stream's order is
+         * kept; what is saved is the gap between two grids. The kernel behind this one may be placed
+         * likewise. */
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;");
+    }
     /* the control words (row counters, queue slots, tickets) of this scratch set exist twice; this
      * launch uses one copy, which was zeroed during the set's previous use, and zeroes the other */
     for (int i = (int) blockIdx.x * kThreads + (int) threadIdx.x; i < p.clear_words; i += G * kThreads) {
@@ -2772,8 +2781,21 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     void *args[] = {const_cast<SampleParams *>(&p)};
     return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(sample_stream_kernel), dim3((unsigned) grid), dim3(kThreads), args, smem_bytes, stream);
 #else
-    sample_stream_kernel<<<dim3((unsigned) grid), dim3(kThreads), smem_bytes, stream>>>(p);
-    return cudaGetLastError();
+    {
+        SampleParams        pc = p;
+        cudaLaunchConfig_t  cfg{};
+        cudaLaunchAttribute attr[1];
+        pc.chained           = 1;
+        cfg.gridDim          = dim3((unsigned) grid);
+        cfg.blockDim         = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem_bytes;
+        cfg.stream           = stream;
+        attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs                                          = attr;
+        cfg.numAttrs                                       = 1;
+        return cudaLaunchKernelEx(&cfg, sample_stream_kernel, pc);
+    }
 #endif
 }
 
