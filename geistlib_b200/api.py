@@ -128,6 +128,7 @@ PROTOTYPES = {
     "geist_b200_batcher_verify": (C.c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t,
                                             C.c_int, C.c_int, c_void_p, c_void_p, c_void_p]),
     "geist_b200_argmax_rows_static": (C.c_int, [C.c_int, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_void_p]),
+    "geist_b200_grid": (C.c_int, [c_size_t, c_size_t, c_size_t, C.POINTER(c_int32), C.POINTER(c_int32)]),
     "geist_b200_plan": (C.c_int, [c_size_t, c_size_t, C.POINTER(c_int32), C.POINTER(c_int32), C.POINTER(c_int32),
                                   C.POINTER(c_int32)]),
 }
@@ -303,6 +304,13 @@ def plan(n_vocab: int, max_history: int = 0):
     c, s, m, r = c_int32(), c_int32(), c_int32(), c_int32()
     _check(lib.geist_b200_plan(n_vocab, max_history, C.byref(c), C.byref(s), C.byref(m), C.byref(r)))
     return {"slices_per_row": c.value, "slice": s.value, "smem_bytes": m.value, "ring_stages": r.value}
+
+
+def grid(n_vocab: int, n_rows: int, max_history: int = 0):
+    """Thread blocks of one launch over n_rows rows, and how many of them an SM holds at a time."""
+    g, per = c_int32(), c_int32()
+    _check(lib.geist_b200_grid(n_vocab, max_history, n_rows, C.byref(g), C.byref(per)))
+    return {"thread_blocks": g.value, "blocks_per_sm": per.value}
 
 
 class Batcher:

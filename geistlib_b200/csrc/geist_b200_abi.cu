@@ -2,7 +2,8 @@
  * geist_b200_abi.cu — the C ABI declared in include/geist_b200.h: argument
  * checks, launch planning, the sampler.h host-pointer surface, sessions and
  * the multi-session batcher. All numeric work happens in the kernels of
- * sampler_kernels.cu; nothing here computes a token on the CPU.
+ * sampler_stream.cu, sampler_aux.cu and sampler_static.cu; nothing here
+ * computes a token on the CPU.
  */
 #include <cuda_runtime.h>
 
@@ -19,8 +20,10 @@
 #include "sampler_params.h"
 
 namespace gb {
-size_t      sample_stream_fixed_smem();
-cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, cudaStream_t stream);
+size_t      sample_stream_smem(int n_slices, int long_ids);
+cudaError_t sample_stream_ctas_per_sm(size_t smem_bytes, int *out);
+cudaError_t finish_rows_max_ctas(int sms, int *out);
+cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, int finish_grid, cudaStream_t stream);
 cudaError_t launch_merge_sample(const MergeParams &p, cudaStream_t stream);
 cudaError_t launch_accept(const AcceptParams &p, cudaStream_t stream);
 cudaError_t launch_scatter_kept(const int *kept_n, const int *kept_idx, const float *kept_val, int kept_cap, int n_rows, int V, int vocab_offset, float *dense, cudaStream_t stream);
@@ -65,23 +68,19 @@ constexpr int    kLanes   = 4;          /* launches of one context that may over
 struct Plan {
     int    n_slices     = 0;
     int    slice        = 0;
-    int    stage_bytes  = 0;
-    int    stages       = 0;
     int    row_cap      = 0;
     int    bucket_cap   = 0;
     int    id_slots     = 0;
     int    hist_cap     = 0;
-    int    cand_cap     = 0;
-    int    fin_cap      = 0;
     size_t smem         = 0;
-    int    sms          = 0;
+    int    ctas         = 0; /* thread blocks of the stream kernel the device holds at once (its grid never exceeds this) */
+    int    fin_ctas     = 0; /* ... and of the finishing kernel */
 };
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 /* hist_max = 0: no history pointer will be given. Rows are cut into the fewest slices of at
- * most kSliceMax floats; whatever shared memory the candidate / history / finisher buffers
- * leave goes to the bulk-copy ring. */
+ * most kSliceMax floats. */
 bool make_plan(size_t V, size_t hist_max, Plan &pl) {
     int            dev = 0;
     cudaDeviceProp prop;
@@ -90,59 +89,42 @@ bool make_plan(size_t V, size_t hist_max, Plan &pl) {
     }
     const size_t n_slices = (V + gb::kSliceMax - 1) / gb::kSliceMax;
     const size_t slice    = round_up((V + n_slices - 1) / n_slices, 4);
-    if (n_slices > 1 && (n_slices - 1) * slice >= V) {
+    if (n_slices > (size_t) gb::kMaxSlices || (n_slices > 1 && (n_slices - 1) * slice >= V)) {
         return false;
     }
-    pl.sms          = prop.multiProcessorCount;
     pl.n_slices     = (int) n_slices;
     pl.slice        = (int) slice;
-    pl.stage_bytes  = (int) round_up(slice * 4, 128);
-    /* histories of more than 128 ids are counted in a shared-memory table with at least two slots per id */
+    /* histories of more than kRowIds ids are counted by a kernel of their own, in a shared-memory table with at
+     * least two slots per id */
     pl.id_slots     = 0;
     pl.row_cap      = 0;
     pl.bucket_cap   = 0;
-    if (hist_max > 128) {
-        size_t slots = 512;
+    if (hist_max > (size_t) gb::kRowIds) {
+        size_t slots = 1024;
         while (slots < 2 * hist_max) {
             slots *= 2;
         }
         if (slots > 16384) {
-            return false; /* 128 KB of table: no room left for the ring */
+            return false; /* 128 KB of table */
         }
         pl.id_slots   = (int) slots;
         pl.row_cap    = (int) round_up(hist_max, 4);
         pl.bucket_cap = (int) round_up(n_slices + 1, 4);
     }
-    pl.hist_cap     = hist_max ? (int) round_up(std::min(hist_max, slice), 4) : 0; /* a multiple of 4 keeps what follows 16-byte aligned */
-    /* A slice's candidates go to global memory (cand_cap each); what shared memory limits is the room
-     * for one row's merged candidates (fin_cap): a row that brings more takes the multi-pass path.
-     * Short slices reserve room for every element, so that "collect everything" cannot overflow. */
-    const int    cand_cap = slice <= 1024 ? (int) round_up(slice, 32) : 1024; /* a row's first slices pass about three times top-k before the threshold tightens */
-    const size_t fin_full = std::max<size_t>(256, std::min<size_t>(n_slices * (size_t) cand_cap, 4096));
-    const size_t fins[]   = {fin_full, 3072, 2560, 2304, 2048, 1536, 1024, 768};
-    for (int want_stages = 3; want_stages >= 1; want_stages--) {
-        for (size_t fin : fins) {
-            if (fin > fin_full) {
-                continue;
-            }
-            /* after the ring: shared state | id lists of the slices in flight | finisher bitmap | finisher id list |
-             * merged candidates + scratch copy | sorted kept set + its weights */
-            const size_t fixed = gb::sample_stream_fixed_smem() + (size_t) (gb::kMaxStages + 1) * (size_t) pl.hist_cap * 4 + 4 * (size_t) gb::kFinBitmapWords +
-                                 (size_t) std::min(pl.hist_cap, 512) * 8 + fin * 16 + (size_t) gb::kFastKMax * 12 + 128;
-            if (fixed + (size_t) pl.stage_bytes > kSmemMax) {
-                continue;
-            }
-            const int stages = (int) std::min<size_t>(gb::kMaxStages, (kSmemMax - fixed) / (size_t) pl.stage_bytes);
-            if (stages >= want_stages) {
-                pl.cand_cap = cand_cap;
-                pl.fin_cap  = (int) fin;
-                pl.stages   = stages;
-                pl.smem     = fixed + (size_t) stages * (size_t) pl.stage_bytes;
-                return true;
-            }
-        }
+    pl.hist_cap = hist_max ? (int) round_up(std::min<size_t>(hist_max, 1024), 4) : 0; /* the finisher walks segments of at most 1024 ids */
+    pl.smem     = gb::sample_stream_smem(pl.n_slices, pl.id_slots > 0 ? 1 : 0);
+    if (pl.smem > kSmemMax) {
+        return false;
     }
-    return false;
+    int per_sm = 0;
+    if (gb::sample_stream_ctas_per_sm(pl.smem, &per_sm) != cudaSuccess || per_sm < 1) {
+        return false;
+    }
+    pl.ctas = per_sm * prop.multiProcessorCount;
+    if (gb::finish_rows_max_ctas(prop.multiProcessorCount, &pl.fin_ctas) != cudaSuccess || pl.fin_ctas < 1) {
+        return false;
+    }
+    return true;
 }
 
 struct PlanCache {
@@ -198,15 +180,15 @@ struct geist_b200_ctx {
     };
     Small *d_small = nullptr;
     Small *h_small = nullptr; /* pinned */
+    std::mutex small_mu;      /* one synchronous host-pointer call at a time stages through the two words above */
 
-    /* kernel scratch: slice records, candidates, row counters, multi-pass row copies. kLanes
+    /* kernel scratch: part records, candidate groups, segment sums, row counters, multi-pass row copies. kLanes
      * independent sets, used round-robin, so that up to kLanes launches may overlap on the GPU. */
     struct Lane {
         unsigned char *buf         = nullptr;
         size_t         bytes       = 0;
-        int           *counters    = nullptr; /* row counters | ready-row slots | 2 queue tickets */
+        int           *counters    = nullptr; /* one flag per row copy of the multi-pass path */
         size_t         counter_cap = 0;
-        unsigned       uses        = 0;       /* which of the two copies of the control words is live */
     } lane[kLanes];
     unsigned   next_lane = 0;
     std::mutex lane_mu;
@@ -338,14 +320,10 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.kept_val     = b->kept_prob;
     p.n_slices     = pl.n_slices;
     p.slice        = pl.slice;
-    p.stage_bytes  = pl.stage_bytes;
-    p.stages       = pl.stages;
     p.row_cap      = pl.row_cap;
     p.bucket_cap   = pl.bucket_cap;
     p.id_slots     = pl.id_slots;
     p.hist_cap     = pl.hist_cap;
-    p.cand_cap     = pl.cand_cap;
-    p.fin_cap      = pl.fin_cap;
     p.aligned      = ((reinterpret_cast<uintptr_t>(b->logits) & 15u) == 0 && (b->row_stride & 3u) == 0) ? 1 : 0;
     p.flags        = flags;
     cudaStream_t st = as_stream(stream);
@@ -353,22 +331,26 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     /* scratch of this launch */
     const size_t n_rows   = (size_t) p.n_rows;
     const size_t n_items  = n_rows * (size_t) pl.n_slices;
-    const int    grid     = (int) std::min<size_t>((size_t) pl.sms, n_items);
+    const int    grid     = (int) std::min<size_t>((size_t) pl.ctas, n_items);
+    const size_t q_items  = n_items / (size_t) grid; /* the shortest run of items a thread block takes */
+    const size_t parts    = std::min<size_t>((size_t) pl.n_slices, ((size_t) pl.n_slices - 1 + q_items - 1) / q_items + 1);
+    p.parts_max           = (int) parts;
     const size_t gen_str  = round_up(b->n_vocab, 4);
     const size_t gen_bmw  = (b->n_vocab + 31) / 32;
     const size_t gen_hcap = hist_max ? std::min(hist_max, b->n_vocab) : 0;
     const size_t off_recs = 0;
-    const size_t off_cand = round_up(off_recs + n_items * sizeof(gb::SliceRec), 256);
-    const size_t off_rows = round_up(off_cand + n_items * (size_t) pl.cand_cap * sizeof(gb::Pair), 256);
-    const size_t off_bm   = round_up(off_rows + (size_t) grid * gen_str * 4, 256);
-    const size_t off_dl   = round_up(off_bm + (size_t) grid * gen_bmw * 4, 256);
-    const size_t off_pl   = round_up(off_dl + (size_t) grid * gen_hcap * sizeof(gb::Pair), 256);
+    const size_t off_gv   = round_up(off_recs + n_rows * parts * sizeof(gb::PartRec), 256);
+    const size_t off_gb   = round_up(off_gv + n_rows * parts * (size_t) gb::kPartGroups * 16, 256);
+    const size_t off_seg  = round_up(off_gb + n_rows * parts * (size_t) gb::kPartGroups * 4, 256);
+    const int    fin_grid = (int) std::min<size_t>((size_t) pl.fin_ctas, n_rows);
+    const size_t slots    = (size_t) fin_grid; /* row copies of the multi-pass path: one per finishing thread block that can run at a time */
+    const size_t off_rows = round_up(off_seg + n_items * (size_t) gb::kWarps * sizeof(gb::SegRec), 256);
+    const size_t off_bm   = round_up(off_rows + slots * gen_str * 4, 256);
+    const size_t off_dl   = round_up(off_bm + slots * gen_bmw * 4, 256);
+    const size_t off_pl   = round_up(off_dl + slots * gen_hcap * sizeof(gb::Pair), 256);
     const size_t off_po   = round_up(off_pl + (pl.id_slots ? n_rows * (size_t) pl.row_cap * 4 : 0), 256);
-    const size_t slow_cap = (n_items + (size_t) grid - 1) / (size_t) grid; /* a CTA completes at most as many rows as it has items */
-    const size_t off_slow = round_up(off_po + (pl.id_slots ? n_rows * (size_t) (pl.n_slices + 1) * 4 : 0), 256);
-    const size_t need     = round_up(off_slow + (size_t) grid * slow_cap * 16, 256);
+    const size_t need     = round_up(off_po + (pl.id_slots ? n_rows * (size_t) (pl.n_slices + 1) * 4 : 0), 256);
     geist_b200_ctx::Lane *ln;
-    unsigned              use_now = 0;
     {
         std::lock_guard<std::mutex> lk(ctx->lane_mu);
         ln = &ctx->lane[ctx->next_lane++ % kLanes];
@@ -379,29 +361,24 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
             CUDA_TRY(cudaMalloc((void **) &ln->buf, need));
             ln->bytes = need;
         }
-        if (ln->counter_cap < n_rows) {
+        if (ln->counter_cap < slots) {
             cudaFree(ln->counters);
             ln->counters    = nullptr;
             ln->counter_cap = 0;
-            const size_t cap = round_up(n_rows, 1024);
-            /* two copies of {[cap] row counters | [cap] queue slots | 4 ticket words}, all zero: a launch
-             * works on one copy and zeroes the other for the set's next use */
-            CUDA_TRY(cudaMalloc((void **) &ln->counters, 2 * (2 * cap + 4) * sizeof(int)));
-            CUDA_TRY(cudaMemset(ln->counters, 0, 2 * (2 * cap + 4) * sizeof(int)));
+            const size_t cap = round_up(slots, 1024);
+            /* one flag per row copy of the multi-pass path, zero between launches (whoever takes a copy gives it
+             * back). Zeroed on the launch's own stream, so the first kernel that uses them comes behind it. */
+            CUDA_TRY(cudaMalloc((void **) &ln->counters, cap * sizeof(int)));
+            CUDA_TRY(cudaMemsetAsync(ln->counters, 0, cap * sizeof(int), st));
             ln->counter_cap = cap;
-            ln->uses        = 0;
         }
-        use_now = ln->uses++;
     }
-    const size_t ctl_words = 2 * ln->counter_cap + 4;
-    int         *ctl       = ln->counters + (use_now & 1u) * ctl_words;
-    p.row_counter      = ctl;
-    p.ready_rows       = ctl + ln->counter_cap;
-    p.q_ctr            = reinterpret_cast<unsigned *>(ctl + 2 * ln->counter_cap);
-    p.clear_ptr        = ln->counters + ((use_now + 1u) & 1u) * ctl_words;
-    p.clear_words      = (int) ctl_words;
-    p.recs             = reinterpret_cast<gb::SliceRec *>(ln->buf + off_recs);
-    p.cands            = reinterpret_cast<gb::Pair *>(ln->buf + off_cand);
+    p.pool             = ln->counters;
+    p.pool_slots       = (int) slots;
+    p.recs             = reinterpret_cast<gb::PartRec *>(ln->buf + off_recs);
+    p.grp_v            = reinterpret_cast<float4 *>(ln->buf + off_gv);
+    p.grp_b            = reinterpret_cast<int *>(ln->buf + off_gb);
+    p.segs             = reinterpret_cast<gb::SegRec *>(ln->buf + off_seg);
     p.gen_rows         = reinterpret_cast<float *>(ln->buf + off_rows);
     p.gen_stride       = (long long) gen_str;
     p.gen_bitmap       = reinterpret_cast<unsigned *>(ln->buf + off_bm);
@@ -410,9 +387,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.gen_hist_cap     = (int) gen_hcap;
     p.pre_list         = reinterpret_cast<unsigned *>(ln->buf + off_pl);
     p.pre_off          = reinterpret_cast<int *>(ln->buf + off_po);
-    p.slow_list        = reinterpret_cast<int4 *>(ln->buf + off_slow);
-    p.slow_cap         = (int) slow_cap;
-    CUDA_TRY(gb::launch_sample_stream(p, grid, pl.smem, st));
+    CUDA_TRY(gb::launch_sample_stream(p, grid, pl.smem, fin_grid, st));
     return GEIST_OK;
 }
 
@@ -515,7 +490,25 @@ extern "C" enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history,
         *smem_bytes = (int32_t) pl.smem;
     }
     if (ring_stages) {
-        *ring_stages = pl.stages;
+        *ring_stages = gb::kStages;
+    }
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_grid(size_t n_vocab, size_t max_history, size_t n_rows, int32_t *thread_blocks, int32_t *blocks_per_sm) {
+    Plan pl;
+    if (n_vocab == 0 || n_rows == 0 || !g_plans.get(n_vocab, max_history, pl)) {
+        return fail(GEIST_E_UNSUPPORTED, "grid: no launch shape for n_vocab=%zu, history=%zu", n_vocab, max_history);
+    }
+    int            dev = 0;
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+    if (thread_blocks) {
+        *thread_blocks = (int32_t) std::min<size_t>((size_t) pl.ctas, n_rows * (size_t) pl.n_slices);
+    }
+    if (blocks_per_sm) {
+        *blocks_per_sm = pl.ctas / prop.multiProcessorCount;
     }
     return GEIST_OK;
 }
@@ -711,6 +704,7 @@ extern "C" enum geist_status geist_b200_argmax_f32(struct geist_b200_ctx *ctx, c
     if (ctx == nullptr || logits_dev == nullptr || out_index == nullptr || n == 0) {
         return fail(GEIST_E_INVALID_ARG, "argmax_f32: bad argument");
     }
+    std::lock_guard<std::mutex> lk(ctx->small_mu); /* callers on several threads share the context's staging words */
     CUDA_TRY(cudaSetDevice(ctx->device));
     geist_b200_ctx::Small *h = ctx->h_small;
     memset(h, 0, sizeof *h);

@@ -69,6 +69,15 @@ __device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned coun
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+/* Several barriers, then one pair of fences for all of them. */
+__device__ __forceinline__ void mbar_init_only(unsigned long long *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }

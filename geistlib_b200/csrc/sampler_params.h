@@ -4,34 +4,30 @@
  */
 #pragma once
 #include <stdint.h>
+#include <vector_types.h>
 
 namespace gb {
 
-#ifndef GB_WORK_WARPS
-#define GB_WORK_WARPS 14
-#endif
-#ifndef GB_FIN_WARPS
-#define GB_FIN_WARPS 4
-#endif
-constexpr int kWorkWarps    = GB_WORK_WARPS;  /* warps that stream slices */
-constexpr int kWorkThreads  = kWorkWarps * 32;
-constexpr int kFinWarps     = GB_FIN_WARPS;   /* warps that finish completed rows */
-constexpr int kFinThreads   = kFinWarps * 32;
-constexpr int kQueue        = 32;             /* finished slices waiting for the publisher warp */
-constexpr int kThreads      = kWorkThreads + 64 + kFinThreads; /* workers, loader warp, publisher warp, finishers: 640 */
-constexpr int kWarps        = 32;             /* room for per-warp values in the slice record */
-constexpr int kSliceMax     = 14336;          /* floats of one row slice: at most 8 float4 per worker thread */
-static_assert(kSliceMax <= 32 * kWorkThreads, "a worker thread holds at most 8 float4 of a slice");
+constexpr int kWarps        = 8;              /* warps of one thread block; each streams its own share of every slice */
+constexpr int kThreads      = kWarps * 32;
+constexpr int kNV4          = 8;              /* float4 one thread holds of a slice */
+constexpr int kSliceMax     = kThreads * kNV4 * 4; /* floats of one row slice: 8192 */
+constexpr int kStages       = 2;              /* depth of each warp's bulk-copy ring */
+constexpr int kWarpStageBytes = kSliceMax * 4 / kWarps; /* one warp's share of a slice: 4 KB */
+constexpr int kCtasPerSm    = 2;              /* thread blocks the launch bounds ask for per SM */
 constexpr int kTopKClamp    = 8192;           /* sampler.c:212-215 */
 constexpr int kFastKMax     = 256;            /* largest k served by the threshold fast path */
 #ifndef GB_NUCLEUS_PROBE
 #define GB_NUCLEUS_PROBE 32
 #endif
 constexpr int kNucleusProbe = GB_NUCLEUS_PROBE; /* entries the top-p fast path looks at */
-constexpr int kMaxSlices    = 1024;           /* slices per row the finisher can merge */
-constexpr int kMaxStages    = 4;              /* depth of the bulk-copy ring */
+constexpr int kMaxSlices    = 1024;           /* slices per row */
+constexpr int kMaxParts     = 64;             /* thread blocks a row may be spread over before the finisher gives the row to the multi-pass path */
 constexpr int kFinBitmapWords = 32;           /* finisher: one bit per entry of a crossing segment (at most 1024) */
-constexpr int kHistBins     = 256;            /* value histogram of the finisher's select */
+constexpr int kHistBins     = 256;            /* value histograms (threshold, select) */
+constexpr int kGroupCapWarp = 160;            /* candidate groups (one float4 each) a warp can hold of one row part */
+constexpr int kPartGroups   = kWarps * kGroupCapWarp; /* ... and a whole thread block: 1280 */
+constexpr int kRowIds       = 256;            /* ids of a row (history + fed tokens) counted inside the stream kernel, one per thread */
 
 /* status word, one per row (bit set) */
 enum : int {
@@ -52,15 +48,22 @@ struct Pair {
     int   idx;
 };
 
-/* What one CTA leaves behind for one (row, slice) work item. */
-struct __align__(16) SliceRec {
-    float  max;         /* slice maximum after penalties */
-    int    arg;         /* first global id of that maximum */
-    int    n_cand;      /* candidates this slice found (may exceed the reserved room) */
-    int    st;          /* status bits raised while processing the slice */
-    double bulk;        /* top-p: sum of expf((x - max) * inv_t) over the non-candidates */
-    double pad;
-    double seg[kWarps]; /* temperature: per-warp sums of expf((x - max) * inv_t), id order */
+/* What one thread block leaves behind for its part of a row (a run of consecutive slices). */
+struct __align__(16) PartRec {
+    float  max;      /* maximum of the part after penalties */
+    int    arg;      /* first global id of that maximum */
+    int    n_groups; /* candidate groups this part found (more than kPartGroups: some were dropped) */
+    int    st;       /* status bits raised while the part streamed */
+    float  tau;      /* the part's final select threshold: a lower bound of the row's kq-th largest value */
+    float  bulk_ref; /* top-p: the sum below is relative to this value ... */
+    double bulk_sum; /* ... sum of expf((x - bulk_ref) * inv_t) over everything outside the candidate groups */
+};
+
+/* Temperature rows: one warp's share of one slice, ids in order. */
+struct __align__(16) SegRec {
+    float  ref;  /* maximum of the segment */
+    float  pad;
+    double sum;  /* sum of expf((x - ref) * inv_t) over the segment */
 };
 
 struct SampleParams {
@@ -101,37 +104,29 @@ struct SampleParams {
     /* launch shape */
     int      n_slices;     /* work items per row */
     int      slice;        /* floats per slice, multiple of 4, <= kSliceMax */
-    int      stage_bytes;  /* bytes of one ring stage (multiple of 128, >= 4 * slice) */
-    int      stages;       /* ring depth, 1..kMaxStages */
-    /* rows with more than 128 ids: their distinct ids are prepared by a kernel of their own */
+    int      parts_max;    /* thread blocks one row can be spread over */
+    /* rows with more than kRowIds ids: their distinct ids are prepared by a kernel of their own */
     int       id_slots;    /* slots of that kernel's id table (a power of two, at least twice the ids a row can bring); 0: no such rows */
     int       row_cap;     /* entries of one row's prepared list */
     int       bucket_cap;  /* n_slices + 1 rounded up to a multiple of 4 */
     unsigned *pre_list;    /* [n_rows][row_cap] (position in the slice) | (count << 14), grouped by slice */
     int      *pre_off;     /* [n_rows][n_slices + 1] where each slice's run starts */
-    /* rows left to the multi-pass path: (row, first id of the maximum, maximum, status bits), per CTA */
-    int4     *slow_list;   /* [grid][slow_cap] */
-    int       slow_cap;    /* rows one CTA can complete */
-    int       chained;     /* 1: launched as a programmatic dependent of the kernel before it; waits for it before any global access */
-    int      hist_cap;     /* distinct-id entries reserved per slice */
-    int      cand_cap;     /* candidates reserved per slice */
-    int      fin_cap;      /* candidates the finisher can merge per row */
+    int      hist_cap;     /* distinct-id entries the finisher reserves for one walked segment */
     int      aligned;      /* rows start on 16-byte boundaries: bulk copies allowed */
     unsigned flags;
 
     /* scratch in global memory (one lane of the context's scratch) */
-    int       *row_counter; /* [n_rows] slices published per row; zero when the launch starts */
-    int       *ready_rows;  /* [n_rows] grid-wide queue of completed rows: row + 1, 0 = empty */
-    unsigned  *q_ctr;       /* {tickets reserved, tickets claimed}, zero when the launch starts */
-    int       *clear_ptr;   /* the other copy of these control words, zeroed by this launch */
-    int        clear_words;
-    SliceRec  *recs;        /* [n_rows * n_slices] */
-    Pair      *cands;       /* [n_rows * n_slices, cand_cap] */
-    float     *gen_rows;    /* [grid, gen_stride]: a CTA's private copy of one row for the multi-pass path */
+    int       *pool;        /* [pool_slots] 1: the row copy of this number is taken; zero between launches */
+    int        pool_slots;
+    PartRec   *recs;        /* [n_rows, parts_max] */
+    float4    *grp_v;       /* [n_rows, parts_max, kPartGroups] candidate groups: four consecutive values ... */
+    int       *grp_b;       /* ... and the global id of the first */
+    SegRec    *segs;        /* [n_rows, n_slices, kWarps] temperature rows */
+    float     *gen_rows;    /* [pool_slots, gen_stride]: private copies of one row for the multi-pass path */
     long long  gen_stride;  /* floats */
-    unsigned  *gen_bitmap;  /* [grid, gen_bitmap_words] */
+    unsigned  *gen_bitmap;  /* [pool_slots, gen_bitmap_words] */
     int        gen_bitmap_words;
-    Pair      *gen_dlist;   /* [grid, gen_hist_cap] (id, original value) */
+    Pair      *gen_dlist;   /* [pool_slots, gen_hist_cap] (id, original value) */
     int        gen_hist_cap;
 };
 

@@ -1,37 +1,30 @@
 /*
  * sampler_stream.cu — the logits -> token kernel (sm_100a).
  *
- * A persistent grid (one CTA per SM) streams every logits row through the chip
- * exactly once. A row is cut into slices of at most 14336 floats; the work
- * item is (row, slice); every CTA owns a contiguous run of items, so that
- * consecutive items mostly belong to one row. Inside a CTA the warps are
- * specialised and nobody waits for another CTA:
+ * Every logits row crosses the chip exactly once. A row is cut into slices of at most 8192 floats; the work item
+ * is (row, slice); the grid is two thread blocks of 8 warps per SM, and every thread block owns a contiguous run
+ * of the row-major item list. The consecutive slices of one row inside a run are a PART of that row.
  *
- *   The LOADER warp keeps a ring of shared-memory stages full with bulk
- *   asynchronous copies (global -> this CTA's shared memory, signalled on
- *   mbarriers) and prepares each item a few items ahead: its configuration and
- *   the list of the history ids that fall into the slice, each with its count.
+ *   Streaming. Every warp owns a fixed share of each slice (256 float4) and keeps its own ring of two stages
+ *   full with bulk asynchronous copies (global -> this thread block's shared memory, signalled on the warp's own
+ *   mbarriers): it waits for its share, applies the penalties that fall into it, lifts it into registers, asks
+ *   for the share two items ahead and works on the registers. Inside a part no warp waits for another one.
  *
- *   14 WORKER warps walk the slices at their own pace. Each owns a fixed share
- *   of every slice: it waits for the copy, applies the penalties that fall
- *   into its share, reads the share once (maximum per lane), looks only at
- *   the lanes that hold something that matters (the maximum's first id, the
- *   entries above the row's select threshold), gives the stage back and adds
- *   what it found to the slice's accumulators. Candidates go straight to
- *   global scratch. The warps meet once per row, to set the row's select
- *   threshold; every later slice of the row reuses it.
+ *   Greedy rows keep (maximum, first id) per warp. Top-k / top-p rows pick candidates against a select
+ *   threshold tau, a lower bound of the row's kq-th largest value: the part's first slice sets it (the thread
+ *   maxima of all warps are binned by key; the only barriers inside a part), a histogram of the candidates
+ *   raises it as the part streams. What is kept is the float4 GROUP that holds a candidate (four values and the
+ *   id of the first), placed by one ballot and two stores into the warp's own list. Temperature and top-p rows
+ *   also sum expf((x - warp maximum) * inv_t) per warp and slice.
  *
- *   The PUBLISHER warp folds a slice as soon as its last worker warp is done:
- *   record to global scratch, the row's counter, and a higher select threshold
- *   for the slices to come (from a histogram of the candidates seen so far).
+ *   Part boundaries. The thread block meets, writes one record and its candidate groups to global scratch and
+ *   adds the part's slices to the row's counter. The thread block whose add completes the row finishes it: it
+ *   merges the parts' records, expands and orders the few surviving candidates, evaluates their probabilities
+ *   exactly and makes the draw (its own part's candidates never leave shared memory). The other thread block of
+ *   the SM streams on meanwhile.
  *
- *   4 FINISHER warps finish the rows this CTA completed: they merge the row's
- *   slice records, order the few surviving candidates, evaluate their
- *   probabilities exactly and make the draw, while the workers stream on.
- *
- * Rows whose kept set is too large for this (top-k beyond the candidate room,
- * wide top-p nuclei) are served by the finisher warps alone with a multi-pass
- * bisection over a private copy of the row in global scratch.
+ * Rows whose kept set is too large for this (top-k beyond 256, wide top-p nuclei) are served by the finishing
+ * thread block with radix walks over a private copy of the row in global scratch.
  *
  * Semantics follow geistlib's CPU sampler:
  *   mode dispatch ............ src/archs/transformer/forward/head.c:172-183
@@ -47,54 +40,20 @@
 
 namespace gb {
 
-#ifndef GB_FIN_PAUSE
-#define GB_FIN_PAUSE 60
-#endif
-
 struct PenEntry {
     int   li;
     float orig;
 };
 
-/* A short, bounded pause between two polls of a flag (the sleep instruction's granularity is far
- * coarser than the waits here). */
-__device__ __forceinline__ void pause_cycles(int cycles) {
-    const long long t0 = clock64();
-    while (clock64() - t0 < cycles) {
-    }
-}
-
-/* A load that is served by the L2, where the other SMs' atomics and stores land (a cached load can
- * keep returning an old line of this SM's L1). */
-__device__ __forceinline__ unsigned load_l2(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ int load_l2(const int *p) { return (int) load_l2(reinterpret_cast<const unsigned *>(p)); }
-
-#ifdef GB_PROFILE
-__device__ long long g_prof3[256][16]; /* finisher thread 0: cycles per phase, summed over its rows */
-#define FPROF_INIT() long long fprof_t = clock64()
-#define FPROF(i)                                              \
-    if (g.tid == 0 && blockIdx.x < 256) {                     \
-        const long long t_ = clock64();                       \
-        g_prof3[blockIdx.x][i] += t_ - fprof_t;               \
-        fprof_t = t_;                                         \
-    }
-#else
-#define FPROF_INIT()
-#define FPROF(i)
-#endif
-
 __device__ __forceinline__ float key_to_float(unsigned k) { return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k); }
 
-/* A set of warps that synchronise on their own named barrier. */
+
+/* The threads that share a reduction: here always the whole thread block. */
 struct Grp {
     int tid, lane, warp; /* position inside the group */
     int n, nw;           /* threads, warps */
-    int bar;             /* hardware barrier id (0 is left to __syncthreads) */
-    __device__ __forceinline__ void sync() const { asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(n) : "memory"); }
+    int bar;             /* unused: the group is the thread block */
+    __device__ __forceinline__ void sync() const { __syncthreads(); }
 };
 
 /* Reduction scratch, one instance per group. */
@@ -122,69 +81,12 @@ struct __align__(16) GroupShared {
     int       harg[kHistBins]; /* finisher: their first ids */
 };
 
-/* float4 of a slice that one worker warp owns: an equal share, rounded up to whole warp steps */
-__host__ __device__ __forceinline__ int share_len(int nv4) { return ((nv4 + kWorkWarps - 1) / kWorkWarps + 31) & ~31; }
+/* float4 of a slice that one warp owns: an equal share, rounded up to whole warp steps */
+__host__ __device__ __forceinline__ int share_len(int nv4) { return ((nv4 + kWarps - 1) / kWarps + 31) & ~31; }
 
-/* A work item's configuration, decoded once by the loader warp. */
-struct __align__(16) ItemCfg {
-    int   row, item, s0, n;         /* what the worker warps read, four words at a time */
-    int   mode, kq, flags, pad0;    /* flags: bit 0 = penalties on */
-    float inv_t, rep, freq, pres;
-    int   L, nv4, c, st0;           /* float4 per warp, float4 in the slice, slice number, status bits of the id list */
-    int   H, E, seq, seq0;          /* loader only */
-};
-
-/* What the worker warps of one slice add up, each at its own pace. */
-struct __align__(8) SliceAcc {
-    unsigned long long best;    /* (ordered key of the maximum, ~first id): larger word wins */
-    int                n_cand;  /* candidates placed so far */
-    int                arrived; /* worker warps that are done with the slice */
-    int                st;      /* status bits */
-    int                pad;
-    float              wmax[32]; /* per warp: maximum of its part ... */
-    double             wsum[32]; /* ... and its sum of expf((x - that maximum) * inv_t) */
-};
-
-constexpr int kIdSlotBits = 8;
-constexpr int kIdSlots    = 1 << kIdSlotBits; /* open-addressing table for at most kLoaderIds ids */
-constexpr int kLoaderIds  = 128;              /* ids of a row (history + fed tokens) that the loader warp keeps in registers */
-constexpr int kFinQueue = 64; /* completed rows waiting for this CTA's finisher warps */
-constexpr int kCfgRing  = 8; /* decoded configurations kept */
-constexpr int kListRing = kMaxStages + 1; /* per-slice id lists / accumulators kept: a warp can run at most `stages` slices ahead of another */
-constexpr int kLiBits   = 14; /* an id list entry is (position in the slice) | (count << kLiBits) */
+constexpr int kLiBits = 14; /* an id list entry is (position in the slice) | (count << kLiBits) */
 static_assert(kSliceMax <= (1 << kLiBits), "slice positions must fit the id list entry");
-
-struct __align__(16) StreamShared {
-    unsigned long long full[kMaxStages];  /* the slice has landed (bulk copy -> workers) */
-    unsigned long long empty[kMaxStages]; /* every worker warp has lifted its part (workers -> loader) */
-    GroupShared        wk; /* workers */
-    GroupShared        fn; /* finishers */
-    ItemCfg            cfg[kCfgRing];
-    SliceAcc           acc[kListRing];
-    int                n_dl[kListRing]; /* entries of the slice's id list */
-    unsigned           tau_key[2];      /* select threshold of a row's first slice, alternating */
-    unsigned           top_key[2];      /* largest group maximum of that slice, alternating */
-    unsigned           low_key[2];      /* smallest group maximum of that slice, alternating */
-    int                boot_n[2];       /* groups (threads with a share) of that slice, alternating */
-    __align__(16) int  bhist[kHistBins]; /* group maxima of that slice, binned by key */
-    unsigned long long tau_pub;         /* (row, ordered key of the best threshold known for it): only grows */
-    int                id_key[kIdSlots]; /* loader: the distinct ids of the row in preparation ... */
-    int                id_cnt[kIdSlots]; /* ... and how often each occurs */
-    __align__(16) int  thist[kHistBins]; /* the row's candidates so far, binned by value between threshold and maximum */
-    volatile int slice_done[kListRing]; /* j + 1 once every worker warp is done with slice j (workers -> publisher) */
-    float        t_lo, t_scale;         /* the candidate histogram's map from value to bin ... */
-    int          t_row;                 /* ... and the row it belongs to */
-    volatile int q_done;    /* the worker loop has ended */
-    volatile int q_error;
-    volatile int p_done;    /* the publisher has ended */
-    volatile int fin_q[kFinQueue]; /* rows this CTA completed, publisher -> finisher warps */
-    volatile int fin_head;  /* rows queued so far */
-    volatile int fin_tail;  /* rows taken so far */
-    volatile int l_decoded; /* items whose configuration and id list are ready (loader -> workers) */
-    int          w_done;    /* slices every worker warp is done with (workers -> loader) */
-    int          done_warps;
-    int          n_slow;    /* rows left to the multi-pass path at the kernel's end */
-};
+static_assert((long long) kMaxSlices * kSliceMax <= (1ll << 28), "a candidate group keeps four flag bits above the id of its first value");
 
 enum Mode { M_ARGMAX, M_TOPK, M_TOPP, M_TEMP };
 
@@ -446,117 +348,7 @@ __device__ __forceinline__ long long group_sum_ll(const Grp &g, GroupShared *sh,
     return t;
 }
 
-/* ------------------------------------------- finisher: ordered select of kq -- */
-
-/*
- * cand[0..total) hold distinct ids, total >= kq >= 1. Writes the kq best in
- * (value desc, id asc) order to sorted[0..kq). A histogram over the
- * candidates' key range finds the bin that holds the kq-th entry; entries in
- * higher bins are in, only that one bin is ranked exactly. tmp has room for
- * `total` pairs. Called by the whole group.
- */
-__device__ void select_sorted(const Grp &g, GroupShared *sh, const Pair *cand, int total, int kq, Pair *tmp, Pair *sorted) {
-    unsigned lo = 0xffffffffu, hi = 0u;
-    for (int i = g.tid; i < total; i += g.n) {
-        const unsigned key = order_key(cand[i].v);
-        lo                 = min(lo, key);
-        hi                 = max(hi, key);
-    }
-    lo = __reduce_min_sync(0xffffffffu, lo);
-    hi = __reduce_max_sync(0xffffffffu, hi);
-    g.sync();
-    if (g.lane == 0) {
-        sh->wred_a[g.warp]                               = (int) lo;
-        reinterpret_cast<unsigned *>(sh->wred_f)[g.warp] = hi;
-    }
-    for (int i = g.tid; i < kHistBins; i += g.n) {
-        sh->bins[i] = 0;
-    }
-    if (g.tid == 0) {
-        sh->n_sel    = 0;
-        sh->n_border = 0;
-        sh->b_star   = 0;
-        sh->n_hi     = 0;
-    }
-    g.sync();
-    lo = 0xffffffffu;
-    hi = 0u;
-    for (int w = 0; w < g.nw; w++) {
-        lo = min(lo, (unsigned) sh->wred_a[w]);
-        hi = max(hi, reinterpret_cast<unsigned *>(sh->wred_f)[w]);
-    }
-    const unsigned range = hi >= lo ? hi - lo : 0u;
-    const int      shift = max(0, (32 - __clz(range)) - 8); /* (range >> shift) < 256 */
-    for (int i = g.tid; i < total; i += g.n) {
-        atomicAdd(&sh->bins[(order_key(cand[i].v) - lo) >> shift], 1);
-    }
-    g.sync();
-    if (g.warp == 0) {
-        /* b* = largest bin with count(bins >= b*) >= kq; lane l owns bins [8l, 8l+8) */
-        int mine = 0;
-#pragma unroll
-        for (int q = 0; q < 8; q++) {
-            mine += sh->bins[8 * g.lane + q];
-        }
-        int suffix = mine; /* entries owned by this lane and all higher ones */
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int dn = __shfl_down_sync(0xffffffffu, suffix, o);
-            if (g.lane + o < 32) {
-                suffix += dn;
-            }
-        }
-        const int above = suffix - mine; /* entries owned by higher lanes */
-        if (above < kq && above + mine >= kq) {
-            int acc = above;
-            for (int q = 7; q >= 0; q--) {
-                const int c = sh->bins[8 * g.lane + q];
-                if (acc + c >= kq) {
-                    sh->b_star = 8 * g.lane + q;
-                    sh->n_hi   = acc;
-                    break;
-                }
-                acc += c;
-            }
-        }
-    }
-    g.sync();
-    const int b_star = sh->b_star, n_hi = sh->n_hi;
-    /* entries above the bin fill tmp from the front, the bin's entries from the back */
-    for (int i = g.tid; i < total; i += g.n) {
-        const int bin = (int) ((order_key(cand[i].v) - lo) >> shift);
-        if (bin > b_star) {
-            tmp[atomicAdd(&sh->n_sel, 1)] = cand[i];
-        } else if (bin == b_star) {
-            tmp[total - 1 - atomicAdd(&sh->n_border, 1)] = cand[i];
-        }
-    }
-    g.sync();
-    const int nb   = sh->n_border;
-    const int need = kq - n_hi;
-    for (int i = g.tid; i < nb; i += g.n) {
-        const Pair me   = tmp[total - 1 - i];
-        int        rank = 0;
-        for (int j = 0; j < nb; j++) {
-            const Pair o = tmp[total - 1 - j];
-            rank += pair_before(o.v, o.idx, me.v, me.idx) ? 1 : 0;
-        }
-        if (rank < need) {
-            sorted[n_hi + rank] = me;
-        }
-    }
-    for (int i = g.tid; i < n_hi; i += g.n) {
-        const Pair me   = tmp[i];
-        int        rank = 0;
-        for (int j = 0; j < n_hi; j++) {
-            rank += pair_before(tmp[j].v, tmp[j].idx, me.v, me.idx) ? 1 : 0;
-        }
-        sorted[rank] = me;
-    }
-    g.sync();
-}
-
-/* ------------------------------------------------- multi-pass path (finisher) -- */
+/* ------------------------------------------------------------ multi-pass path -- */
 
 template <class F>
 __device__ __forceinline__ void row_sweep(const Grp &g, const float *row, int V, F &&f) {
@@ -587,20 +379,6 @@ __device__ __forceinline__ void row_rewrite(const Grp &g, float *row, int V, F &
     for (int i = g.tid; i < V; i += g.n) {
         row[i] = f(row[i], i);
     }
-}
-
-/* Largest composite word t such that at least `want` entries are >= t. */
-__device__ unsigned long long bisect_rank(const Grp &g, GroupShared *sh, const float *row, int V, int idx_bits, long long want) {
-    unsigned long long prefix = 0;
-    for (int bit = 31 + idx_bits; bit >= 0; bit--) {
-        const unsigned long long t   = prefix | (1ull << bit);
-        long long                cnt = 0;
-        row_sweep(g, row, V, [&](float x, int i) { cnt += composite(order_key(x), i, idx_bits) >= t ? 1 : 0; });
-        if (group_sum_ll(g, sh, cnt) >= want) {
-            prefix = t;
-        }
-    }
-    return prefix;
 }
 
 /* Largest composite word t with mass{word >= t} >= target (inclusive) or > target. The search may
@@ -776,8 +554,8 @@ __device__ unsigned long long resolve_ties(const Grp &g, GroupShared *sh, const 
     return bisect_mass(g, sh, row, V, idx_bits, target, inclusive, key, mass, (unsigned long long) ro.key << idx_bits, idx_bits - 1);
 }
 
-/* All threads of the CTA serve a row whose kept set does not fit the one-pass path. */
-__device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, float row_max, int row_arg, void *hist_mem, int hist_bytes) {
+/* All threads of the thread block serve a row whose kept set does not fit the one-pass path. */
+__device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, float row_max, int row_arg, void *hist_mem, int hist_bytes, int slot) {
     /* room for the byte histograms of the radix walks: per warp where it fits, else one for all */
     const int copies = hist_bytes >= g.nw * 256 * 12 ? g.nw : 1;
     double   *hm     = reinterpret_cast<double *>(hist_mem);
@@ -785,7 +563,7 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
     const int    V        = p.V;
     const int    idx_bits = 32 - __clz(max(V - 1, 1));
     int          st       = ST_SLOW_PATH;
-    float       *gr       = p.gen_rows + (size_t) blockIdx.x * (size_t) p.gen_stride;
+    float       *gr       = p.gen_rows + (size_t) slot * (size_t) p.gen_stride;
     const float *src      = p.logits + (size_t) r.row * (size_t) p.row_stride;
     int         *kept_i   = p.kept_cap > 0 ? p.kept_idx + (size_t) r.row * (size_t) p.kept_cap : nullptr;
     float       *kept_v   = p.kept_cap > 0 ? p.kept_val + (size_t) r.row * (size_t) p.kept_cap : nullptr;
@@ -805,7 +583,7 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
         }
     }
     if (r.pen_on) {
-        unsigned *bm = p.gen_bitmap + (size_t) blockIdx.x * (size_t) p.gen_bitmap_words;
+        unsigned *bm = p.gen_bitmap + (size_t) slot * (size_t) p.gen_bitmap_words;
         for (int i = g.tid; i < p.gen_bitmap_words; i += g.n) {
             bm[i] = 0u;
         }
@@ -813,7 +591,7 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
             sh->n_dlist = 0;
         }
         g.sync();
-        st |= apply_penalties(g, gr, 0, V, r, V, p.vocab_offset, bm, reinterpret_cast<PenEntry *>(p.gen_dlist + (size_t) blockIdx.x * (size_t) p.gen_hist_cap), p.gen_hist_cap,
+        st |= apply_penalties(g, gr, 0, V, r, V, p.vocab_offset, bm, reinterpret_cast<PenEntry *>(p.gen_dlist + (size_t) slot * (size_t) p.gen_hist_cap), p.gen_hist_cap,
                               &sh->n_dlist, false, 0);
     } else {
         g.sync();
@@ -956,67 +734,6 @@ __device__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *s
     return st;
 }
 
-/* ---------------------------------------------------------------- finisher -- */
-
-struct FinBuffers {
-    Pair     *fcand, *ftmp, *fsort;
-    float    *fq;
-    unsigned *bitmap; /* 16 words: ids of one walked segment */
-    PenEntry *dlist;
-    int       dlist_cap;
-};
-
-/* What the finisher warps request from global scratch the moment a row is theirs, so that it
- * travels while the row's configuration is still being read. */
-static_assert(kFinThreads * 8 >= 1024, "the finisher threads walk a crossing segment of up to 1024 entries, 8 each");
-constexpr int kSpecSlots = 8; /* per finisher thread: candidates fetched before the slices' counts are known */
-/* how many of each slice's candidates that is (0: the row has too many slices) */
-__device__ __forceinline__ int spec_per_slice(const SampleParams &p) {
-    return p.n_slices * 64 <= kFinThreads * kSpecSlots ? 64 : (p.n_slices * 48 <= kFinThreads * kSpecSlots ? 48 : 0);
-}
-/* flat index of the request -> (slice, position) */
-__device__ __forceinline__ void spec_split(int f, int k_spec, int &cc, int &i) {
-    if (k_spec == 64) {
-        cc = f >> 6;
-        i  = f & 63;
-    } else {
-        cc = f / 48;
-        i  = f - cc * 48;
-    }
-}
-struct Prefetch {
-    int4      hdr;              /* slice record header {max, arg, n_cand, st} of slice g.tid */
-    long long c[kSpecSlots];    /* candidate (value, id) pairs, flat index g.tid + kFinThreads * m */
-    double    seg;              /* temperature rows: segment sum number g.tid of the row */
-};
-
-__device__ __forceinline__ Prefetch prefetch_row(const Grp &g, const SampleParams &p, int row) {
-    Prefetch        pf;
-    const SliceRec *recs = p.recs + (size_t) row * (size_t) p.n_slices;
-    pf.hdr               = make_int4(0, 0, 0, 0);
-    if (g.tid < p.n_slices) {
-        pf.hdr = __ldcg(reinterpret_cast<const int4 *>(&recs[g.tid]));
-    }
-    pf.seg = 0.0;
-    if (g.tid < p.n_slices * kWorkWarps) {
-        pf.seg = __ldcg(&recs[g.tid / kWorkWarps].seg[g.tid % kWorkWarps]);
-    }
-    const int   kSpec = spec_per_slice(p);
-    const int   flat  = p.n_slices * kSpec;
-    const Pair *base = p.cands + (size_t) row * (size_t) p.n_slices * (size_t) p.cand_cap;
-#pragma unroll
-    for (int m = 0; m < kSpecSlots; m++) {
-        const int f = g.tid + kFinThreads * m;
-        pf.c[m]     = 0;
-        if (f < flat) {
-            int cc, i;
-            spec_split(f, kSpec, cc, i);
-            pf.c[m] = __ldcg(reinterpret_cast<const long long *>(base + (size_t) cc * (size_t) p.cand_cap + i));
-        }
-    }
-    return pf;
-}
-
 /* Warp 0 of the group: S = sum of w[0..n) and the first i with u(S) < w[0] + .. + w[i] (n - 1 if
  * none), for n <= 256. u01 is the unit draw; the comparison is made against u01 * S like the
  * reference's inverse CDF (sampler.c:90-102). Sums are formed lane-wise and scanned across the
@@ -1060,75 +777,302 @@ __device__ __forceinline__ int warp_inverse_cdf(int lane, const float *w, int n,
     return pick;
 }
 
-/* Runs in the finisher warps of the CTA that completed the row. Returns the row's status bits. */
-__device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, const FinBuffers &fb, const Prefetch &pf) {
-    const int       row    = r.row;
-    const SliceRec *recs   = p.recs + (size_t) row * (size_t) p.n_slices;
-    int            *kept_i = p.kept_cap > 0 ? p.kept_idx + (size_t) row * (size_t) p.kept_cap : nullptr;
-    float          *kept_v = p.kept_cap > 0 ? p.kept_val + (size_t) row * (size_t) p.kept_cap : nullptr;
-    int             st     = 0;
-    FPROF_INIT();
-
-    /* slice headers into shared memory; every thread then derives the row's maximum, its first id,
-     * the status bits and the candidate totals from them */
-    const bool small_row = p.n_slices <= kHistBins;
-    g.sync();
-    if (small_row) {
-        for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
-            const int4 h = cc == g.tid ? pf.hdr : __ldcg(reinterpret_cast<const int4 *>(&recs[cc]));
-            sh->hmax[cc] = __int_as_float(h.x);
-            sh->harg[cc] = h.y;
-            sh->bins[cc] = h.z;
-            st |= h.w;
+/* Status of a finished row and, behind a sequence's last row, its generator. One thread. */
+__device__ __forceinline__ void row_epilogue(const SampleParams &p, const RowCfg &r, int row, int st, unsigned long long rng0) {
+    p.status[row] = st;
+    if (p.rng_out != nullptr && r.rr == p.rows_per_seq - 1) {
+        /* the sequence's generator (rng0: the word it came with) after all of its rows drew */
+        unsigned long long s = rng0;
+        for (int i = 0; i < p.rows_per_seq * r.draws_per_row; i++) {
+            (void) xorshift_next(s);
         }
+        p.rng_out[r.seq] = s;
+    }
+}
+
+/* ------------------------------------------------------------ shared state -- */
+
+/* What the warps of one thread block share. The ring (every warp's two stages) lies in front of it in dynamic
+ * shared memory, the candidate groups of the part in work behind it. */
+struct __align__(16) StreamShared {
+    unsigned long long full[kWarps][kStages]; /* warp w's share of item j has landed in its stage j % kStages */
+    /* the part in work */
+    unsigned           tau_key;   /* ordered key of the raised select threshold (0: not raised yet) */
+    int                tau_lock;  /* one warp at a time reads the candidate histogram */
+    int                st;        /* status bits of the part */
+    int                rl_n;      /* entries of the row's id list */
+    unsigned           wkey[kWarps], wlow[kWarps]; /* first slice: largest / smallest group maximum per warp */
+    int                wown[kWarps];               /* ... and how many groups the warp holds */
+    int                wn[kWarps], wn_all[kWarps]; /* candidate groups per warp: held / found */
+    unsigned long long best[kWarps];               /* (key of the maximum, ~first id) per warp */
+    float              wb_ref[kWarps];             /* top-p: per warp, sum of expf((x - ref) * inv_t) over what is no candidate */
+    double             wb_sum[kWarps];
+    int                bhist[kHistBins];           /* first slice: group maxima binned by key */
+    int                thist[kHistBins];           /* candidates binned by value between threshold and maximum */
+    int                rl_id[kRowIds], rl_cnt[kRowIds]; /* the row's distinct history ids and their counts */
+    RawCfg             raw_nxt;         /* parameters of the next row of this run, copied in while the part streams */
+    int                nxt_ids[kRowIds]; /* that row's history ids (raw): the first words of its history row ... */
+    int                nxt_ext[kRowIds]; /* ... and the tokens fed before it */
+};
+
+/* What the threads of one finishing thread block share; the merged candidate list lies behind it. */
+struct __align__(16) FinishShared {
+    GroupShared gs; /* reductions of the whole thread block */
+    float       pmax[kMaxParts], ptau[kMaxParts], pbref[kMaxParts];
+    int         parg[kMaxParts], pn[kMaxParts], poff[kMaxParts];
+    double      pbsum[kMaxParts];
+    int         bhist[kHistBins]; /* select histogram */
+    int         n_sel, n_border, n_ent, slot;
+    unsigned    fin_bitmap[kFinBitmapWords];
+    Pair        fsort[kFastKMax];
+    float       fq[kFastKMax];
+    PenEntry    fdlist[512];
+};
+
+constexpr int kGroupBytes = kPartGroups * 20; /* float4 + first id per group */
+constexpr int kFinCap     = 2048;             /* candidates the finisher can order per row (8 per thread) */
+constexpr int kFinPer     = kFinCap / kThreads;
+constexpr int kFinBytes   = kWarps * 256 * 12;    /* finisher: the merged candidate list; the multi-pass path keeps one byte histogram per warp there */
+static_assert(kFinCap * (int) sizeof(Pair) <= kFinBytes, "the merged list fits");
+static_assert(kGroupBytes >= 4 * kRowIds * 4, "the id table of a part's set-up lies in the groups' memory");
+
+__device__ __forceinline__ int cta_of_item(int i, int q, int r) { return i < r * (q + 1) ? i / (q + 1) : r + (i - r * (q + 1)) / q; }
+
+/* Highest bin b with at least kq entries in bins >= b (0 when there is none); the whole warp calls, every lane gets it. */
+__device__ __forceinline__ int top_bin(const int *hist, int lane, int kq) {
+    int cc[8], mine = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        cc[i] = *reinterpret_cast<const volatile int *>(&hist[8 * lane + i]);
+        mine += cc[i];
+    }
+    int suffix = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int dn = __shfl_down_sync(0xffffffffu, suffix, o);
+        if (lane + o < 32) {
+            suffix += dn;
+        }
+    }
+    const unsigned ball = __ballot_sync(0xffffffffu, suffix >= kq);
+    int            b    = 0;
+    if (ball != 0u && lane == 31 - __clz(ball)) {
+        int run = suffix - mine;
+        b       = 8 * lane;
+#pragma unroll
+        for (int i = 7; i >= 0; i--) {
+            run += cc[i];
+            if (run >= kq) {
+                b = 8 * lane + i;
+                break;
+            }
+        }
+    }
+    return __shfl_sync(0xffffffffu, b, ball != 0u ? 31 - __clz(ball) : 0);
+}
+
+/* Group f of this thread block's own candidates: the warps' lists one after the other. */
+__device__ __forceinline__ int own_slot(const StreamShared *sh, int f) {
+    int w = 0;
+#pragma unroll
+    for (int i = 0; i < kWarps - 1; i++) {
+        const int n = sh->wn[i];
+        if (w == i && f >= n) {
+            f -= n;
+            w = i + 1;
+        }
+    }
+    return w * kGroupCapWarp + f;
+}
+
+/* ------------------------------------------- finisher: ordered select of kq -- */
+
+/*
+ * cand[0..total) hold distinct ids, total >= kq >= 1, total <= kFinCap. Writes the kq best in (value desc, id asc)
+ * order to sorted[0..kq). Every thread lifts its entries into registers; a histogram over their key range finds
+ * the bin that holds the kq-th entry; entries in higher bins are in, only that one bin is ranked exactly. cand is
+ * overwritten. Called by the whole thread block.
+ */
+__device__ void select_sorted(const Grp &g, FinishShared *sh, Pair *cand, int total, int kq, Pair *sorted) {
+    Pair     e[kFinPer];
+    unsigned lo = 0xffffffffu, hi = 0u;
+#pragma unroll
+    for (int i = 0; i < kFinPer; i++) {
+        const int f = g.tid + kThreads * i;
+        if (f < total) {
+            e[i]             = cand[f];
+            const unsigned k = order_key(e[i].v);
+            lo               = min(lo, k);
+            hi               = max(hi, k);
+        }
+    }
+    lo = __reduce_min_sync(0xffffffffu, lo);
+    hi = __reduce_max_sync(0xffffffffu, hi);
+    g.sync(); /* earlier readers of the scratch are done; every entry is in a register */
+    if (g.lane == 0) {
+        sh->gs.wred_a[g.warp]                               = (int) lo;
+        reinterpret_cast<unsigned *>(sh->gs.wred_f)[g.warp] = hi;
+    }
+    if (g.tid < kHistBins) {
+        sh->bhist[g.tid] = 0;
+    }
+    if (g.tid == 0) {
+        sh->n_sel    = 0;
+        sh->n_border = 0;
+    }
+    g.sync();
+#pragma unroll
+    for (int w = 0; w < kWarps; w++) {
+        lo = min(lo, (unsigned) sh->gs.wred_a[w]);
+        hi = max(hi, reinterpret_cast<unsigned *>(sh->gs.wred_f)[w]);
+    }
+    const unsigned range = hi >= lo ? hi - lo : 0u;
+    const int      shift = max(0, (32 - __clz(range)) - 8); /* (range >> shift) < 256 */
+#pragma unroll
+    for (int i = 0; i < kFinPer; i++) {
+        if (g.tid + kThreads * i < total) {
+            atomicAdd(&sh->bhist[(order_key(e[i].v) - lo) >> shift], 1);
+        }
+    }
+    g.sync();
+    /* b* = largest bin with count(bins >= b*) >= kq; every warp finds it for itself */
+    const int b_star = top_bin(sh->bhist, g.lane, kq);
+    int       n_hi   = 0;
+    for (int b = b_star + 1 + g.lane; b < kHistBins; b += 32) {
+        n_hi += sh->bhist[b];
+    }
+    n_hi = __reduce_add_sync(0xffffffffu, n_hi);
+    /* entries above the bin fill cand from the front, the bin's entries follow */
+#pragma unroll
+    for (int i = 0; i < kFinPer; i++) {
+        if (g.tid + kThreads * i < total) {
+            const int bin = (int) ((order_key(e[i].v) - lo) >> shift);
+            if (bin > b_star) {
+                cand[atomicAdd(&sh->n_sel, 1)] = e[i];
+            } else if (bin == b_star) {
+                cand[n_hi + atomicAdd(&sh->n_border, 1)] = e[i];
+            }
+        }
+    }
+    g.sync();
+    const int nb   = sh->n_border;
+    const int need = kq - n_hi;
+    for (int i = g.tid; i < n_hi + nb; i += g.n) {
+        const Pair me   = cand[i];
+        int        rank = 0;
+        if (i < n_hi) {
+            for (int j = 0; j < n_hi; j++) {
+                rank += pair_before(cand[j].v, cand[j].idx, me.v, me.idx) ? 1 : 0;
+            }
+            sorted[rank] = me;
+        } else {
+            for (int j = n_hi; j < n_hi + nb; j++) {
+                rank += pair_before(cand[j].v, cand[j].idx, me.v, me.idx) ? 1 : 0;
+            }
+            if (rank < need) {
+                sorted[n_hi + rank] = me;
+            }
+        }
+    }
+    g.sync();
+}
+
+/* ---------------------------------------------------------------- finisher -- */
+
+/*
+ * One row, all threads of a finishing thread block. Merges the parts' records, then by mode: argmax; temperature
+ * (segment sums, then the crossing segment re-read and walked); top-k / top-p over the merged candidates. cmem:
+ * room for the merged list. Returns the row's status bits (ST_DEFERRED: the multi-pass path has to serve it).
+ */
+__device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, FinishShared *sh, RowCfg &r, unsigned char *cmem, int q_items, int r_items, const float4 (&sv)[3], const int (&sb)[3]) {
+    constexpr int kSpec = 3;
+    const int  row     = r.row;
+    int       *kept_i  = p.kept_cap > 0 ? p.kept_idx + (size_t) row * (size_t) p.kept_cap : nullptr;
+    float     *kept_v  = p.kept_cap > 0 ? p.kept_val + (size_t) row * (size_t) p.kept_cap : nullptr;
+    Pair      *cbuf    = reinterpret_cast<Pair *>(cmem);
+    GroupShared *gs    = &sh->gs;
+    const int  b_first = cta_of_item(row * p.n_slices, q_items, r_items);
+    const int  b_last  = cta_of_item(row * p.n_slices + p.n_slices - 1, q_items, r_items);
+    const int  n_parts = b_last - b_first + 1;
+    int        st      = 0;
+
+    g.sync();
+    if (n_parts > kMaxParts) {
+        /* a row spread over that many thread blocks (a handful of rows on the whole chip): its maximum is
+         * taken from the records one by one, everything else is left to the multi-pass path */
+        float m = -CUDART_INF_F;
+        int   a = 0x7fffffff;
+        for (int i = g.tid; i < n_parts; i += g.n) {
+            const int4  h  = __ldcg(reinterpret_cast<const int4 *>(p.recs + (size_t) row * (size_t) p.parts_max + i));
+            const float pm = __int_as_float(h.x);
+            st |= h.w;
+            if (a == 0x7fffffff || pair_before(pm, h.y, m, a)) {
+                m = pm;
+                a = h.y;
+            }
+        }
+        st = __reduce_or_sync(0xffffffffu, st);
+        if (g.lane == 0) {
+            gs->wred_l[g.warp] = st;
+        }
+        group_argmax(g, gs, m, a);
+        for (int w = 0; w < g.nw; w++) {
+            st |= (int) gs->wred_l[w];
+        }
+        if (r.mode == M_ARGMAX) {
+            if (g.tid == 0) {
+                p.tokens[row] = a + p.vocab_offset;
+                if (p.kept_cap > 0) {
+                    p.kept_n[row] = 0;
+                }
+            }
+            return st;
+        }
+        if (g.tid == 0) {
+            gs->blk_max = m;
+            gs->blk_arg = a;
+        }
+        g.sync();
+        return st | ST_DEFERRED;
+    }
+    if (g.tid < n_parts) {
+        const PartRec *rec = p.recs + (size_t) row * (size_t) p.parts_max + g.tid;
+        const int4     h   = __ldcg(reinterpret_cast<const int4 *>(rec));
+        const int4     h2  = __ldcg(reinterpret_cast<const int4 *>(rec) + 1);
+        sh->pmax[g.tid]    = __int_as_float(h.x);
+        sh->parg[g.tid]    = h.y;
+        sh->pn[g.tid]      = h.z;
+        sh->ptau[g.tid]    = __int_as_float(h2.x);
+        sh->pbref[g.tid]   = __int_as_float(h2.y);
+        sh->pbsum[g.tid]   = __hiloint2double(h2.w, h2.z);
+        st |= h.w;
     }
     st = __reduce_or_sync(0xffffffffu, st);
     if (g.lane == 0) {
-        sh->wred_a[g.warp] = st;
+        gs->wred_a[g.warp] = st;
     }
     g.sync();
     for (int w = 0; w < g.nw; w++) {
-        st |= sh->wred_a[w];
+        st |= gs->wred_a[w];
     }
-    float row_max  = -CUDART_INF_F;
+    float row_max  = -CUDART_INF_F, tau_row = -CUDART_INF_F;
     int   row_arg  = 0x7fffffff;
-    int   total    = 0;
+    int   others   = 0;
     bool  overflow = false;
-    if (small_row) {
-        for (int cc = 0; cc < p.n_slices; cc++) {
-            const float m = sh->hmax[cc];
-            const int   a = sh->harg[cc];
-            if (row_arg == 0x7fffffff || pair_before(m, a, row_max, row_arg)) {
-                row_max = m;
-                row_arg = a;
-            }
-            const int nc = sh->bins[cc];
-            overflow |= nc > p.cand_cap;
-            total += nc;
+    for (int i = 0; i < n_parts; i++) {
+        const float m = sh->pmax[i];
+        const int   a = sh->parg[i];
+        if (row_arg == 0x7fffffff || pair_before(m, a, row_max, row_arg)) {
+            row_max = m;
+            row_arg = a;
         }
-    } else {
-        /* very long rows: the records are read straight from global memory */
-        int rst = 0;
-        for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
-            const int4  h = __ldcg(reinterpret_cast<const int4 *>(&recs[cc]));
-            const float m = __int_as_float(h.x);
-            rst |= h.w;
-            if (row_arg == 0x7fffffff || pair_before(m, h.y, row_max, row_arg)) {
-                row_max = m;
-                row_arg = h.y;
-            }
+        tau_row = fmaxf(tau_row, sh->ptau[i]);
+        overflow |= sh->pn[i] > kPartGroups;
+        if (g.tid == 0) {
+            sh->poff[i] = others;
         }
-        rst = __reduce_or_sync(0xffffffffu, rst);
-        g.sync();
-        if (g.lane == 0) {
-            sh->wred_l[g.warp] = rst;
-        }
-        group_argmax(g, sh, row_max, row_arg);
-        for (int w = 0; w < g.nw; w++) {
-            st |= (int) sh->wred_l[w];
-        }
+        others += sh->pn[i];
     }
-    auto slice_max = [&](int cc) { return small_row ? sh->hmax[cc] : __ldcg(&recs[cc].max); };
 
     if (r.mode == M_ARGMAX) {
         if (g.tid == 0) {
@@ -1141,20 +1085,19 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
     }
 
     if (r.mode == M_TEMP) {
-        /* segment sums, rescaled from their slice maximum to the row maximum, in id order */
-        const int nseg   = p.n_slices * kWorkWarps;
-        auto      seg_at = [&](int t) {
-            const int   cc = t / kWorkWarps;
-            const float m  = slice_max(cc);
-            const double sc = m == -CUDART_INF_F ? 0.0 : exp(((double) m - (double) row_max) * (double) r.inv_t);
-            return sc * (t == g.tid ? pf.seg : __ldcg(&recs[cc].seg[t % kWorkWarps]));
+        /* segment sums (one per warp and slice, ids in order), moved from their own maximum to the row maximum */
+        const int     nseg   = p.n_slices * kWarps;
+        const SegRec *segs   = p.segs + (size_t) row * (size_t) nseg;
+        auto          seg_at = [&](int t) {
+            const float  ref = __ldcg(&segs[t].ref);
+            const double sm  = __ldcg(&segs[t].sum);
+            return ref == -CUDART_INF_F ? 0.0 : sm * exp(((double) ref - (double) row_max) * (double) r.inv_t);
         };
         double part = 0.0;
         for (int t = g.tid; t < nseg; t += g.n) {
             part += seg_at(t);
         }
-        const double S     = group_sum_d(g, sh, part);
-        FPROF(2); /* temperature: headers + segment sums */
+        const double S     = group_sum_d(g, gs, part);
         const double u     = (double) unit_from(xorshift_next(r.rng)) * S;
         double       carry = 0.0;
         int          found = -1;
@@ -1172,41 +1115,40 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
             }
             g.sync();
             if (g.lane == 31) {
-                sh->wred_d[g.warp] = incl;
+                gs->wred_d[g.warp] = incl;
             }
             if (g.tid == 0) {
-                sh->pick = 0x7fffffff;
+                gs->pick = 0x7fffffff;
             }
             g.sync();
             double woff = carry;
             for (int w = 0; w < g.warp; w++) {
-                woff += sh->wred_d[w];
+                woff += gs->wred_d[w];
             }
             incl += woff;
             if (t < nseg && u < incl) {
-                atomicMin(&sh->pick, t);
+                atomicMin(&gs->pick, t);
             }
             g.sync();
-            const int pk = sh->pick;
+            const int pk = gs->pick;
             if (pk != 0x7fffffff) {
                 if (t == pk) {
-                    sh->S = incl - val;
+                    gs->S = incl - val;
                 }
                 g.sync();
                 found = pk;
-                fbase = sh->S;
+                fbase = gs->S;
                 break;
             }
             for (int w = 0; w < g.nw; w++) {
-                carry += sh->wred_d[w];
+                carry += gs->wred_d[w];
             }
         }
         if (found < 0) {
             found = nseg - 1;
         }
-        FPROF(3); /* temperature: scan to the crossing segment */
         /* the crossing segment, re-read from the row (L2), penalised, walked with the row maximum */
-        const int    cc    = found / kWorkWarps, w = found % kWorkWarps;
+        const int    cc    = found / kWarps, w = found % kWarps;
         const int    s0c   = cc * p.slice;
         const int    nc    = max(0, min(p.slice, p.V - s0c));
         const int    nv4c  = (nc + 3) >> 2;
@@ -1214,7 +1156,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
         const int    e0    = min(4 * w * Lc, nc);
         const int    e1    = min(4 * min((w + 1) * Lc, nv4c), nc);
         const int    seg_n = max(e1 - e0, 0);
-        float       *wbuf  = reinterpret_cast<float *>(fb.fcand); /* >= 512 floats */
+        float       *wbuf  = reinterpret_cast<float *>(cmem); /* >= 1024 floats */
         const float *src   = p.logits + (size_t) row * (size_t) p.row_stride + s0c + e0;
         g.sync();
         for (int i = g.tid; i < seg_n; i += g.n) {
@@ -1222,26 +1164,25 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
         }
         if (r.pen_on) {
             for (int i = g.tid; i < kFinBitmapWords; i += g.n) {
-                fb.bitmap[i] = 0u;
+                sh->fin_bitmap[i] = 0u;
             }
             if (g.tid == 0) {
-                sh->n_dlist = 0;
+                gs->n_dlist = 0;
             }
         }
         g.sync();
         if (r.pen_on && seg_n > 0) {
-            st |= apply_penalties(g, wbuf, s0c + e0, seg_n, r, p.V, p.vocab_offset, fb.bitmap, fb.dlist, fb.dlist_cap, &sh->n_dlist, false, 0);
+            st |= apply_penalties(g, wbuf, s0c + e0, seg_n, r, p.V, p.vocab_offset, sh->fin_bitmap, sh->fdlist, min(p.hist_cap, 512), &gs->n_dlist, false, 0);
         }
-        FPROF(4); /* temperature: segment loaded and penalised */
         {
             /* every thread takes a run of consecutive entries; the runs' sums are scanned over the
              * group and the thread whose run crosses u walks it */
-            const int per = (seg_n + g.n - 1) / g.n; /* <= 8 for 128 threads */
+            const int per = (seg_n + g.n - 1) / g.n; /* <= 4 */
             const int i0  = g.tid * per;
-            float     ev[8];
+            float     ev[4];
             double    mine = 0.0;
 #pragma unroll
-            for (int q = 0; q < 8; q++) {
+            for (int q = 0; q < 4; q++) {
                 const int i = i0 + q;
                 ev[q]       = (q < per && i < seg_n) ? expf(scaled_arg(wbuf[i], row_max, r.inv_t)) : 0.0f;
                 mine += (double) ev[q];
@@ -1256,21 +1197,21 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
             }
             g.sync();
             if (g.lane == 31) {
-                sh->wred_d[g.warp] = incl;
+                gs->wred_d[g.warp] = incl;
             }
             if (g.tid == 0) {
-                sh->pick = 0x7fffffff;
+                gs->pick = 0x7fffffff;
             }
             g.sync();
             double base = fbase;
-            for (int w = 0; w < g.warp; w++) {
-                base += sh->wred_d[w];
+            for (int ww = 0; ww < g.warp; ww++) {
+                base += gs->wred_d[ww];
             }
             if (u < base + incl && i0 < seg_n) {
-                atomicMin(&sh->pick, g.tid);
+                atomicMin(&gs->pick, g.tid);
             }
             g.sync();
-            const int pk = sh->pick;
+            const int pk = gs->pick;
             if (pk == 0x7fffffff) {
                 if (g.tid == 0) { /* regrouped sums can end a hair below the segment's share */
                     p.tokens[row] = s0c + e0 + max(seg_n - 1, 0) + p.vocab_offset;
@@ -1279,7 +1220,7 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
                 double a   = base + (incl - mine);
                 int    hit = min(i0 + per - 1, seg_n - 1);
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
+                for (int q = 0; q < 4; q++) {
                     a += (double) ev[q];
                     if (q < per && u < a) {
                         hit = i0 + q;
@@ -1293,85 +1234,80 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
             }
         }
         g.sync();
-        FPROF(5); /* temperature: walk */
         return st;
     }
 
-    FPROF(2); /* headers, row maximum */
-    /* ---- top-k and top-p: merge the slices' candidates ---- */
-    bool need_multipass = !(r.kq > 0 && r.kq <= kFastKMax) || !small_row || overflow || total > p.fin_cap || total < r.kq;
+    /* ---- top-k and top-p: merge the parts' candidate groups ---- */
+    const int n_groups       = others;
+    bool      need_multipass = !(r.kq > 0 && r.kq <= kFastKMax) || overflow || n_groups > 2 * kFinCap;
     if (!need_multipass) {
-        /* place the pre-fetched candidates, then fetch what the pre-fetch did not cover */
-        const int  kSpec = spec_per_slice(p);
-        const bool spec  = kSpec > 0;
-        if (spec) {
-#pragma unroll
-            for (int m = 0; m < kSpecSlots; m++) {
-                const int f = g.tid + kFinThreads * m;
-                if (f < p.n_slices * kSpec) {
-                    int cc, i;
-                    spec_split(f, kSpec, cc, i);
-                    if (i < sh->bins[cc]) {
-                        int off = 0;
-                        for (int q = 0; q < cc; q++) {
-                            off += sh->bins[q];
-                        }
-                        Pair v;
-                        v.v               = __int_as_float((int) (pf.c[m] & 0xffffffffll));
-                        v.idx             = (int) (pf.c[m] >> 32);
-                        fb.fcand[off + i] = v;
-                    }
+        if (g.tid == 0) {
+            sh->n_ent = 0;
+        }
+        g.sync();
+        const bool  keep_all = r.mode == M_TOPP; /* every marked entry was left out of the bulk sums */
+        auto        place    = [&](float v, int idx) {
+            if (idx < p.V && (keep_all || v >= tau_row)) {
+                const int pos = atomicAdd(&sh->n_ent, 1);
+                if (pos < kFinCap) {
+                    cbuf[pos].v   = v;
+                    cbuf[pos].idx = idx;
                 }
             }
+        };
+        /* a group is four consecutive values, the id of the first and, in the id's top four bits, which of them passed */
+        auto place_group = [&](const float4 &v, int raw) {
+            const int      b  = raw & 0x0fffffff;
+            const unsigned cm = (unsigned) raw >> 28;
+            if (cm & 1u) place(v.x, b);
+            if (cm & 2u) place(v.y, b + 1);
+            if (cm & 4u) place(v.z, b + 2);
+            if (cm & 8u) place(v.w, b + 3);
+        };
+#pragma unroll
+        for (int k = 0; k < kSpec; k++) { /* what was asked for before the counts were known */
+            if (k < n_parts && g.tid < sh->pn[k]) {
+                place_group(sv[k], sb[k]);
+            }
         }
-        const int first = spec ? kSpec : 0;
-        for (int cc = g.warp; cc < p.n_slices; cc += g.nw) {
-            const int nc = sh->bins[cc];
-            if (nc > first) {
-                int off = 0;
-                for (int i = 0; i < cc; i++) {
-                    off += sh->bins[i];
-                }
-                const long long *src = reinterpret_cast<const long long *>(p.cands + ((size_t) row * (size_t) p.n_slices + (size_t) cc) * (size_t) p.cand_cap);
-                for (int i = first + g.lane; i < nc; i += 32) {
-                    const long long w = __ldcg(src + i);
-                    Pair            v;
-                    v.v               = __int_as_float((int) (w & 0xffffffffll));
-                    v.idx             = (int) (w >> 32);
-                    fb.fcand[off + i] = v;
-                }
+        for (int pi = 0; pi < n_parts; pi++) { /* and the rest */
+            const size_t base = ((size_t) row * (size_t) p.parts_max + (size_t) pi) * (size_t) kPartGroups;
+            for (int f = g.tid + (pi < kSpec ? kThreads : 0); f < sh->pn[pi]; f += g.n) {
+                place_group(__ldcg(p.grp_v + base + f), __ldcg(p.grp_b + base + f));
             }
         }
         g.sync();
-        FPROF(3); /* candidates into shared memory */
-        if (r.mode == M_TOPK) {
+        const int total = sh->n_ent;
+        if (total > kFinCap || total < r.kq) {
+            need_multipass = true;
+        }
+        if (!need_multipass && r.mode == M_TOPK) {
             const int k = r.k;
-            select_sorted(g, sh, fb.fcand, total, k, fb.ftmp, fb.fsort);
-            FPROF(4); /* select + order */
+            select_sorted(g, sh, cbuf, total, k, sh->fsort);
             if (r.select_only) {
                 for (int i = g.tid; i < min(k, p.kept_cap); i += g.n) {
-                    kept_i[i] = fb.fsort[i].idx + p.vocab_offset;
-                    kept_v[i] = fb.fsort[i].v;
+                    kept_i[i] = sh->fsort[i].idx + p.vocab_offset;
+                    kept_v[i] = sh->fsort[i].v;
                 }
                 if (g.tid == 0) {
                     p.kept_n[row] = k;
-                    p.tokens[row] = fb.fsort[0].idx + p.vocab_offset;
+                    p.tokens[row] = sh->fsort[0].idx + p.vocab_offset;
                 }
                 g.sync();
                 return st;
             }
             /* sampler.c:217-222: softmax over the k kept logits (max = the first), one draw */
-            const float m = fb.fsort[0].v;
+            const float m = sh->fsort[0].v;
             for (int i = g.tid; i < k; i += g.n) {
-                fb.fq[i] = exp_exact(scaled_arg(fb.fsort[i].v, m, r.inv_t));
+                sh->fq[i] = exp_exact(scaled_arg(sh->fsort[i].v, m, r.inv_t));
             }
             g.sync();
             if (g.warp == 0) {
                 double    S;
-                const int pick = warp_inverse_cdf(g.lane, fb.fq, k, unit_from(xorshift_next(r.rng)), &S);
+                const int pick = warp_inverse_cdf(g.lane, sh->fq, k, unit_from(xorshift_next(r.rng)), &S);
                 if (g.lane == 0) {
-                    p.tokens[row] = fb.fsort[pick].idx + p.vocab_offset;
-                    sh->S         = S;
+                    p.tokens[row] = sh->fsort[pick].idx + p.vocab_offset;
+                    gs->S         = S;
                     if (p.kept_cap > 0) {
                         p.kept_n[row] = k;
                     }
@@ -1379,1218 +1315,799 @@ __device__ int finish_row(const Grp &g, const SampleParams &p, GroupShared *sh, 
             }
             if (p.kept_cap > 0) {
                 g.sync();
-                const double S = sh->S;
+                const double S = gs->S;
                 for (int i = g.tid; i < min(k, p.kept_cap); i += g.n) {
-                    kept_i[i] = fb.fsort[i].idx + p.vocab_offset;
-                    kept_v[i] = __double2float_rn((double) fb.fq[i] / S);
+                    kept_i[i] = sh->fsort[i].idx + p.vocab_offset;
+                    kept_v[i] = __double2float_rn((double) sh->fq[i] / S);
                 }
             }
             g.sync();
-            FPROF(5); /* weights, draw, outputs */
             return st;
         }
-
-        /* top-p over a small nucleus (sampler.c:245-300). Candidates get their exact e_i relative
-         * to the row maximum; the rest of the row was summed per slice with expf relative to the
-         * slice maximum and is rescaled here. */
-        double part = 0.0;
-        for (int i = g.tid; i < total; i += g.n) {
-            const float e = exp_exact(scaled_arg(fb.fcand[i].v, row_max, r.inv_t));
-            fb.fcand[i].v = e;
-            part += (double) e;
-        }
-        for (int cc = g.tid; cc < p.n_slices; cc += g.n) {
-            const float  m  = slice_max(cc);
-            const double sc = m == -CUDART_INF_F ? 0.0 : exp(((double) m - (double) row_max) * (double) r.inv_t);
-            part += sc * __ldcg(&recs[cc].bulk);
-        }
-        const double S = group_sum_d(g, sh, part);
-        for (int i = g.tid; i < total; i += g.n) {
-            fb.fcand[i].v = __double2float_rn((double) fb.fcand[i].v / S); /* p_i as the reference normalises it */
-        }
-        g.sync();
-        /* the walk order is (p desc, id asc); the row's kq most probable ids are all candidates */
-        const int kq = min(r.kq, total);
-        select_sorted(g, sh, fb.fcand, total, kq, fb.ftmp, fb.fsort);
-        if (g.tid == 0) {
-            const float p_floor = fb.fsort[kq - 1].v; /* nothing outside fsort has a larger p */
-            double      cum     = 0.0;
-            int         cut     = -1;
-            for (int i = 0; i < kq; i++) {
-                cum += (double) fb.fsort[i].v;
-                if (cum >= (double) r.top_p) {
-                    cut = i + 1;
-                    break;
-                }
+        if (!need_multipass) {
+            /* top-p over a small nucleus (sampler.c:245-300). Candidates get their exact e_i relative to the row
+             * maximum; the rest of the row was summed per part with expf relative to a maximum of its own and is
+             * rescaled here. */
+            double part = 0.0;
+            for (int i = g.tid; i < total; i += g.n) {
+                const float e = exp_exact(scaled_arg(cbuf[i].v, row_max, r.inv_t));
+                cbuf[i].v     = e;
+                part += (double) e;
             }
-            const bool all_in = kq >= p.V;
-            bool       ok     = cut > 0 && (fb.fsort[cut - 1].v > p_floor || all_in);
-            if (cut < 0 && all_in) { /* never reached top_p: the nucleus is the whole row */
-                cut = kq;
-                ok  = true;
+            if (g.tid < n_parts) {
+                const float  ref = sh->pbref[g.tid];
+                const double sc  = ref == -CUDART_INF_F ? 0.0 : exp(((double) ref - (double) row_max) * (double) r.inv_t);
+                part += sc * sh->pbsum[g.tid];
             }
-            if (ok) {
-                double N = 0.0;
-                for (int i = 0; i < cut; i++) {
-                    N += (double) fb.fsort[i].v;
-                }
-                const double u    = (double) unit_from(xorshift_next(r.rng)) * N;
-                double       a    = 0.0;
-                int          pick = cut - 1;
-                for (int i = 0; i < cut; i++) {
-                    a += (double) fb.fsort[i].v;
-                    if (u < a) {
-                        pick = i;
+            const double S = group_sum_d(g, gs, part);
+            for (int i = g.tid; i < total; i += g.n) {
+                cbuf[i].v = __double2float_rn((double) cbuf[i].v / S); /* p_i as the reference normalises it */
+            }
+            g.sync();
+            /* the walk order is (p desc, id asc); the row's kq most probable ids are all candidates */
+            const int kq = min(r.kq, total);
+            select_sorted(g, sh, cbuf, total, kq, sh->fsort);
+            if (g.tid == 0) {
+                const float p_floor = sh->fsort[kq - 1].v; /* nothing outside fsort has a larger p */
+                double      cum     = 0.0;
+                int         cut     = -1;
+                for (int i = 0; i < kq; i++) {
+                    cum += (double) sh->fsort[i].v;
+                    if (cum >= (double) r.top_p) {
+                        cut = i + 1;
                         break;
                     }
                 }
-                p.tokens[row] = fb.fsort[pick].idx + p.vocab_offset;
-                if (p.kept_cap > 0) {
-                    p.kept_n[row] = cut;
-                    for (int i = 0; i < min(cut, p.kept_cap); i++) {
-                        kept_i[i] = fb.fsort[i].idx + p.vocab_offset;
-                        kept_v[i] = __double2float_rn((double) fb.fsort[i].v / N);
+                const bool all_in = kq >= p.V;
+                bool       ok     = cut > 0 && (sh->fsort[cut - 1].v > p_floor || all_in);
+                if (cut < 0 && all_in) { /* never reached top_p: the nucleus is the whole row */
+                    cut = kq;
+                    ok  = true;
+                }
+                if (ok) {
+                    double N = 0.0;
+                    for (int i = 0; i < cut; i++) {
+                        N += (double) sh->fsort[i].v;
+                    }
+                    const double u    = (double) unit_from(xorshift_next(r.rng)) * N;
+                    double       a    = 0.0;
+                    int          pick = cut - 1;
+                    for (int i = 0; i < cut; i++) {
+                        a += (double) sh->fsort[i].v;
+                        if (u < a) {
+                            pick = i;
+                            break;
+                        }
+                    }
+                    p.tokens[row] = sh->fsort[pick].idx + p.vocab_offset;
+                    if (p.kept_cap > 0) {
+                        p.kept_n[row] = cut;
+                        for (int i = 0; i < min(cut, p.kept_cap); i++) {
+                            kept_i[i] = sh->fsort[i].idx + p.vocab_offset;
+                            kept_v[i] = __double2float_rn((double) sh->fsort[i].v / N);
+                        }
                     }
                 }
+                gs->flag = ok ? 1 : 0;
             }
-            sh->flag = ok ? 1 : 0;
-        }
-        g.sync();
-        if (sh->flag) {
-            return st;
+            g.sync();
+            if (gs->flag) {
+                return st;
+            }
         }
     }
     g.sync();
-    /* the multi-pass path sweeps the whole row several times: it is left to the end of the kernel,
-     * when all threads of the CTA are free to share it */
     if (g.tid == 0) {
-        sh->blk_max = row_max;
-        sh->blk_arg = row_arg;
+        gs->blk_max = row_max;
+        gs->blk_arg = row_arg;
     }
     g.sync();
     return st | ST_DEFERRED;
 }
 
-/* Optional cycle accounting of worker thread 0 (build with -DGB_PROFILE): where one CTA's time goes. */
+/* ------------------------------------------------------------------ kernel -- */
+
+/* Optional time line of every thread block (build with -DGB_PROFILE): %globaltimer at five points of its life. */
 #ifdef GB_PROFILE
-__device__ long long g_prof[512][8]; /* [0,256) workers, [256,512) finishers */
-__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define PROF_INIT()              \
-    long long prof_acc[8] = {0}; \
-    long long prof_t      = clock64()
-#define PROF(i)                         \
-    if (g.tid == 0) {                   \
+__device__ long long g_prof[1024][8];
+__device__ __forceinline__ long long gtime() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define PROF(i)                                        \
+    if (threadIdx.x == 0 && blockIdx.x < 1024) {       \
+        g_prof[blockIdx.x][i] = gtime();               \
+    }
+#define PROF_ONCE(i)                                                       \
+    if (threadIdx.x == 0 && blockIdx.x < 1024 && g_prof[blockIdx.x][i] == 0) { \
+        g_prof[blockIdx.x][i] = gtime();                                   \
+    }
+__device__ long long g_cyc[1024][kWarps][8];
+#define CYC_INIT()              \
+    long long cyc_acc[8] = {0}; \
+    long long cyc_t      = clock64()
+#define CYC(i)                          \
+    {                                   \
         const long long t_ = clock64(); \
-        prof_acc[i] += t_ - prof_t;     \
-        prof_t = t_;                    \
+        cyc_acc[i] += t_ - cyc_t;       \
+        cyc_t = t_;                     \
     }
-#define PROF_DONE()                                \
-    prof_acc[7] = gtime();                         \
-    if (g.tid == 0 && blockIdx.x < 256) {          \
-        for (int i_ = 0; i_ < 8; i_++) {           \
-            g_prof[blockIdx.x][i_] = prof_acc[i_]; \
-        }                                          \
-    }
-/* finer accounting of one worker warp (warp 5) */
-__device__ long long g_prof2[256][16];
-#define PROF2_INIT()              \
-    long long prof2_acc[16] = {0}; \
-    long long prof2_t       = clock64()
-#define PROF2(i)                         \
-    if (g.tid == 160) {                  \
-        const long long t_ = clock64();  \
-        prof2_acc[i] += t_ - prof2_t;    \
-        prof2_t = t_;                    \
-    }
-#define PROF2_DONE()                                  \
-    if (g.tid == 160 && blockIdx.x < 256) {           \
-        for (int i_ = 0; i_ < 12; i_++) {             \
-            g_prof2[blockIdx.x][i_] = prof2_acc[i_];  \
-        }                                             \
+#define CYC_DONE()                                                  \
+    if ((threadIdx.x & 31) == 0 && blockIdx.x < 1024) {             \
+        for (int i_ = 0; i_ < 8; i_++) {                            \
+            g_cyc[blockIdx.x][threadIdx.x >> 5][i_] = cyc_acc[i_];  \
+        }                                                           \
     }
 #else
-#define PROF_INIT()
 #define PROF(i)
-#define PROF_DONE()
-#define PROF2_INIT()
-#define PROF2(i)
-#define PROF2_DONE()
+#define PROF_ONCE(i)
+#define CYC_INIT()
+#define CYC(i)
+#define CYC_DONE()
 #endif
+
+/* How many ids (history + tokens fed before this row) a row brings. */
+__device__ __forceinline__ int row_id_count(const SampleParams &p, int hist_len, int row) {
+    const int seq0 = p.rows_per_seq == 1 ? row : row / p.rows_per_seq;
+    const int H    = p.hist ? (int) min((long long) max(hist_len, 0), p.hist_stride) : 0;
+    const int E    = p.extra ? row - seq0 * p.rows_per_seq : 0;
+    return H + E;
+}
 
 /*
- * The publisher warp takes the CTA's slices in order, each as soon as the last worker warp is done
- * with it: it folds the warps' results into the slice's record (global scratch), frees the
- * slice's accumulators, raises the row's select threshold from the histogram of the candidates
- * seen so far, and counts the slice at its row. The CTA whose slice completes a row finishes that
- * row: every CTA owns a contiguous run of items, so it completes the rows that end inside its run
- * (the CTA that holds a row's first part is through with it long before), and the finishing work
- * spreads evenly by itself.
+ * A row's parameters cost up to two dependent memory round trips (slot -> parameters and history ids). Warp 0
+ * fetches them for the NEXT row of the run with 4-byte asynchronous copies into shared memory, one step per
+ * slice of the part in work, so that nothing waits for them when that row begins. The history ids are asked for
+ * before the row's history length is known: the first kRowIds words of the session's history row (they exist,
+ * whatever the length is), and the tokens fed before this row into a list of their own. `stage`: 0 nothing asked
+ * yet, 1 the slot, 2 everything. Called by all lanes of warp 0.
  */
-__device__ void publisher_loop(int lane, const SampleParams &p, StreamShared *sh, int my_count) {
-    int  next      = 0; /* the slice to take next */
-    bool done_seen = false;
-    while (next < my_count) {
-        /* ---- fold every slice that is ready (shared memory only); lane b keeps the b-th one's record ---- */
-        int    n_new = 0;
-        int    my_row = -1, my_item = 0;
-        int4   my_h   = make_int4(0, 0, 0, 0);
-        double my_bulk = 0.0;
-        while (n_new < 32 && next < my_count && sh->slice_done[next % kListRing] == next + 1) {
-            const int j = next;
-            __threadfence_block(); /* what the worker warps left before they arrived is readable */
-            const ItemCfg *cf   = &sh->cfg[j % kCfgRing]; /* stays until w_done moves past j */
-            SliceAcc      *acc  = &sh->acc[j % kListRing];
-            const int      row  = cf->row, item = cf->item, mode = cf->mode, kq = cf->kq;
-            const float    inv_t = cf->inv_t;
-            const bool     sel  = (mode == M_TOPK || mode == M_TOPP) && kq > 0 && kq <= kFastKMax;
-            const unsigned long long bw   = acc->best;
-            const float              smax = key_to_float((unsigned) (bw >> 32));
-            double                   bulk = 0.0;
-            if (mode == M_TEMP || (mode == M_TOPP && sel)) {
-                /* per-warp sums move from their own maximum to the slice maximum */
-                double f = 0.0;
-                if (lane < kWorkWarps) {
-                    const float wm = acc->wmax[lane];
-                    f              = wm == -CUDART_INF_F ? 0.0 : acc->wsum[lane] * exp(((double) wm - (double) smax) * (double) inv_t);
-                }
-                if (mode == M_TEMP) {
-                    if (lane < kWorkWarps) {
-                        p.recs[item].seg[lane] = f;
-                    }
-                } else {
-                    bulk = warp_sum_d(f);
-                }
-            }
-            if (lane == n_new) {
-                my_row  = row;
-                my_item = item;
-                my_h.x  = __float_as_int(smax);
-                my_h.y  = (int) (0xffffffffu - (unsigned) (bw & 0xffffffffull));
-                my_h.z  = acc->n_cand;
-                my_h.w  = acc->st;
-                my_bulk = bulk;
-            }
-            __syncwarp();
-            if (lane == 0) {
-                /* the accumulators serve slice j + kListRing next */
-                acc->best    = 0ull;
-                acc->n_cand  = 0;
-                acc->st      = 0;
-                acc->arrived = 0;
-                __threadfence_block();
-                *reinterpret_cast<volatile int *>(&sh->w_done) = j + 1; /* the loader may prepare item j + kListRing */
-            }
-            /* the row's threshold: the lowest bin edge above which at least kq candidates lie, one bin
-             * lower to be safe against rounding at the edge. Lane l holds bins 8 l .. 8 l + 7. */
-            if (sel && sh->t_row == row && sh->t_scale > 0.0f) {
-                const float t_lo = sh->t_lo, t_scale = sh->t_scale;
-                int         c[8];
-                const int4  lo4 = *reinterpret_cast<const int4 *>(&sh->thist[8 * lane]);
-                const int4  hi4 = *reinterpret_cast<const int4 *>(&sh->thist[8 * lane + 4]);
-                c[0] = lo4.x, c[1] = lo4.y, c[2] = lo4.z, c[3] = lo4.w, c[4] = hi4.x, c[5] = hi4.y, c[6] = hi4.z, c[7] = hi4.w;
-                int mine = 0;
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    mine += c[i];
-                }
-                int suffix = mine; /* candidates in this lane's bins and all higher ones */
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int dn = __shfl_down_sync(0xffffffffu, suffix, o);
-                    if (lane + o < 32) {
-                        suffix += dn;
-                    }
-                }
-                const unsigned ball = __ballot_sync(0xffffffffu, suffix >= kq);
-                if (ball != 0u && lane == 31 - __clz(ball)) {
-                    int run = suffix - mine, b = 8 * lane;
-#pragma unroll
-                    for (int i = 7; i >= 0; i--) {
-                        run += c[i];
-                        if (run >= kq) {
-                            b = 8 * lane + i;
-                            break;
-                        }
-                    }
-                    if (b >= 2 && sh->t_row == row) {
-                        const float t_new = t_lo + (float) (b - 1) / t_scale;
-                        if (t_new > t_lo) {
-                            atomicMax(&sh->tau_pub, ((unsigned long long) (unsigned) row << 32) | order_key(t_new));
-                        }
-                    }
-                }
-            }
-            __syncwarp();
-            n_new++;
-            next++;
-        }
-        if (n_new == 0) {
-            /* bounded wait for the next slice, or for the end of the worker loop */
-            bool ready = false;
-            for (long long spin = 0; spin < (1ll << 31); spin++) {
-                ready = sh->slice_done[next % kListRing] == next + 1;
-                if (ready || done_seen) {
-                    break;
-                }
-                done_seen = sh->q_done != 0; /* look once more after the workers have left */
-                pause_cycles(40);
-            }
-            if (!ready) {
-                if (lane == 0 && !done_seen) {
-                    sh->q_error = 1; /* gave up waiting */
-                }
-                break;
-            }
-            continue;
-        }
-        /* ---- publish the folded slices, one per lane, so that their round trips overlap ---- */
-        bool last = false;
-        if (lane < n_new) {
-            SliceRec *rec                  = p.recs + my_item;
-            *reinterpret_cast<int4 *>(rec) = my_h;
-            rec->bulk                      = my_bulk;
-            __threadfence(); /* the slice's record and candidates are visible before the counter moves */
-            last = atomicAdd(&p.row_counter[my_row], 1) == p.n_slices - 1;
-            if (last) {
-                __threadfence(); /* and the other slices' records are visible to whoever saw the last count */
+constexpr int kPrefetchDone = 2;
+__device__ __forceinline__ void prefetch_step(const SampleParams &p, StreamShared *sh, int row, int lane, int &stage) {
+    const int seq0 = p.rows_per_seq == 1 ? row : row / p.rows_per_seq;
+    if (stage == 0) {
+        if (lane == 0) {
+            if (p.slot) {
+                copy_word_async(&sh->raw_nxt.seq, &p.slot[seq0]);
+            } else {
+                sh->raw_nxt.seq = seq0;
             }
         }
-        for (unsigned lasts = __ballot_sync(0xffffffffu, last); lasts != 0u; lasts &= lasts - 1u) {
-            const int done_row = __shfl_sync(0xffffffffu, my_row, __ffs(lasts) - 1);
-            if (lane == 0) {
-                const int hq = sh->fin_head;
-                for (long long spin = 0; spin < (1ll << 31) && hq - sh->fin_tail >= kFinQueue; spin++) {
-                    pause_cycles(100);
-                }
-                sh->fin_q[hq % kFinQueue] = done_row;
-                __threadfence_block();
-                sh->fin_head = hq + 1;
-            }
+        stage = 1;
+        if (p.slot) {
+            return; /* the slot must arrive first */
         }
     }
-    if (lane == 0) {
-        __threadfence_block();
-        sh->p_done = 1;
-#ifdef GB_PROFILE
-        if (blockIdx.x < 256) {
-            g_prof[256 + blockIdx.x][3] = gtime();
-        }
-#endif
+    async_copies_wait();
+    __syncwarp();
+    const int seq = *reinterpret_cast<volatile int *>(&sh->raw_nxt.seq);
+    if (lane == 0) copy_word_async(&sh->raw_nxt.T, &p.temperature[seq]);
+    if (lane == 1) copy_word_async(&sh->raw_nxt.top_k, &p.top_k[seq]);
+    if (lane == 2) copy_word_async(&sh->raw_nxt.top_p, &p.top_p[seq]);
+    if (lane == 3) { if (p.hist) copy_word_async(&sh->raw_nxt.hist_len, &p.hist_len[seq]); else sh->raw_nxt.hist_len = 0; }
+    if (lane == 4) { if (p.rep) copy_word_async(&sh->raw_nxt.rep, &p.rep[seq]); else sh->raw_nxt.rep = 1.0f; }
+    if (lane == 5) { if (p.freq) copy_word_async(&sh->raw_nxt.freq, &p.freq[seq]); else sh->raw_nxt.freq = 0.0f; }
+    if (lane == 6) { if (p.pres) copy_word_async(&sh->raw_nxt.pres, &p.pres[seq]); else sh->raw_nxt.pres = 0.0f; }
+    if (lane == 7 || lane == 8) {
+        unsigned *dst = reinterpret_cast<unsigned *>(&sh->raw_nxt.rng) + (lane - 7);
+        if (p.rng_in) copy_word_async(dst, reinterpret_cast<const unsigned *>(&p.rng_in[seq]) + (lane - 7)); else *dst = lane == 7 ? 1u : 0u;
     }
+    if (p.hist) {
+        const int hs = (int) min((long long) kRowIds, p.hist_stride);
+        for (int t = lane; t < hs; t += 32) {
+            copy_word_async(&sh->nxt_ids[t], &p.hist[(size_t) seq * (size_t) p.hist_stride + t]);
+        }
+    }
+    if (p.extra) {
+        const int E = min(row - seq0 * p.rows_per_seq, kRowIds);
+        for (int t = lane; t < E; t += 32) {
+            copy_word_async(&sh->nxt_ext[t], &p.extra[(size_t) seq0 * (size_t) p.extra_stride + 1 + t]);
+        }
+    }
+    stage = kPrefetchDone;
 }
 
-/* Status of a finished row and, behind a sequence's last row, its generator. One thread. */
-__device__ __forceinline__ void row_epilogue(const SampleParams &p, const RowCfg &r, int row, int st) {
-    p.status[row] = st;
-    if (p.rng_out != nullptr && r.rr == p.rows_per_seq - 1) {
-        /* the sequence's generator after all of its rows drew */
-        unsigned long long s = p.rng_in ? p.rng_in[r.seq] : 1ull;
-        for (int i = 0; i < p.rows_per_seq * r.draws_per_row; i++) {
-            (void) xorshift_next(s);
-        }
-        p.rng_out[r.seq] = s;
-    }
-}
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(const __grid_constant__ SampleParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    unsigned char *ring    = smem_raw;
+    StreamShared  *sh      = reinterpret_cast<StreamShared *>(smem_raw + (size_t) kWarps * kStages * kWarpStageBytes);
+    unsigned char *gmem    = reinterpret_cast<unsigned char *>(sh + 1); /* candidate groups of the part in work */
+    float4        *grp_v   = reinterpret_cast<float4 *>(gmem);
+    int           *grp_b   = reinterpret_cast<int *>(gmem + (size_t) kPartGroups * 16);
+    int           *sl_off  = reinterpret_cast<int *>(gmem + kGroupBytes); /* long histories: where each slice's run of the prepared list starts */
 
-/* The rows that the finisher warps left to the multi-pass path, served by all threads of the CTA
- * once its slices are done. The ring's memory holds the radix walks' histograms. */
-__device__ __noinline__ void slow_rows(const SampleParams p, StreamShared *sh, unsigned char *ring) {
     Grp g;
     g.tid  = (int) threadIdx.x;
     g.lane = g.tid & 31;
     g.warp = g.tid >> 5;
     g.n    = kThreads;
-    g.nw   = kThreads / 32;
+    g.nw   = kWarps;
     g.bar  = 0;
-    const int n_slow = sh->n_slow;
-    for (int i = 0; i < n_slow; i++) {
-        const int4   e   = __ldcg(&p.slow_list[(size_t) blockIdx.x * (size_t) p.slow_cap + i]);
-        const RawCfg rc  = raw_config(p, e.x, true);
-        RowCfg       r   = row_config(p, e.x, rc, true);
-        const int    st  = e.w | multipass_row(g, p, &sh->fn, r, __int_as_float(e.z), e.y, ring, p.stages * p.stage_bytes);
-        if (g.tid == 0) {
-            row_epilogue(p, r, e.x, st);
-        }
-        g.sync();
-    }
-}
+    const int      tid = g.tid, lane = g.lane, warp = g.warp;
+    const unsigned lt  = (1u << lane) - 1u;
 
-/* The finisher warps' loop: they finish the rows this CTA completed, in the order they completed. */
-__device__ void finisher_loop(const Grp &g, const SampleParams &p, StreamShared *sh, const FinBuffers &fb) {
-    GroupShared *fs = &sh->fn;
-    FPROF_INIT();
-#ifdef GB_PROFILE
-    long long facc[8] = {0};
-    facc[6]           = gtime();
-#endif
-    for (;;) {
-        if (g.tid == 0) {
-            /* bounded wait for the next row this CTA completed, or for the end of the publisher */
-            int row = -1;
-            for (long long spin = 0; spin < (1ll << 31); spin++) {
-                const int t = sh->fin_tail;
-                if (sh->fin_head > t) {
-                    __threadfence_block();
-                    row          = sh->fin_q[t % kFinQueue];
-                    sh->fin_tail = t + 1;
-                    break;
-                }
-                if (sh->p_done) {
-                    if (sh->fin_head > t) {
-                        continue; /* queued just before the publisher left */
-                    }
-                    row = -2;
-                    break;
-                }
-                pause_cycles(GB_FIN_PAUSE);
-            }
-            if (row == -1) {
-                sh->q_error = 1; /* gave up waiting: leave */
-                row         = -2;
-            }
-            __threadfence(); /* the row's records, some published by another CTA, are visible from here on */
-            fs->cur_row = row;
-        }
-        g.sync();
-        FPROF(0); /* waiting for a ticket */
-        const int row = fs->cur_row;
-        if (row < 0) {
-#ifdef GB_PROFILE
-            facc[7] = gtime();
-            if (g.tid == 0 && blockIdx.x < 256) {
-                for (int i_ = 0; i_ < 8; i_++) {
-                    if (i_ != 3) {
-                        g_prof[256 + blockIdx.x][i_] = facc[i_];
-                    }
-                }
-            }
-#endif
-            return;
-        }
-#ifdef GB_PROFILE
-        const long long ft0 = clock64();
-#endif
-        const RawCfg   rc  = raw_config(p, row, true); /* in flight together with ... */
-        const Prefetch pf  = prefetch_row(g, p, row); /* ... the row's slice headers and first candidates */
-        RowCfg         r   = row_config(p, row, rc, true);
-        FPROF(1); /* configuration and prefetch requested */
-        const int      fst = finish_row(g, p, fs, r, fb, pf);
-#ifdef GB_PROFILE
-        fprof_t = clock64();
-#endif
-#ifdef GB_PROFILE
-        facc[4] += clock64() - ft0;
-        facc[5] += 1;
-        facc[2] = gtime();
-#endif
-        if (g.tid == 0) {
-            if (fst & ST_DEFERRED) {
-                const int n = sh->n_slow; /* a CTA completes at most slow_cap rows */
-                if (n < p.slow_cap) {
-                    p.slow_list[(size_t) blockIdx.x * (size_t) p.slow_cap + n] = make_int4(row, fs->blk_arg, __float_as_int(fs->blk_max), fst & ~ST_DEFERRED);
-                    sh->n_slow = n + 1;
-                } else {
-                    p.status[row] = ST_INTERNAL;
-                }
-            } else {
-                row_epilogue(p, r, row, fst);
-            }
-        }
-        g.sync();
-        FPROF(6); /* status, generator */
-    }
-}
-
-/* ------------------------------------------------- worker warps: helpers -- */
-
-/* Registers of one worker thread that outlive a slice: the select threshold of the row in work. */
-struct TauState {
-    float tau;     /* a lower bound of the row's kq-th largest value */
-    int   row;     /* the row it belongs to (-1: none) */
-    float lo;      /* candidate histogram: bin = (v - lo) * scale */
-    float scale;   /* 0: no histogram for this row */
-    int   boots;   /* thresholds set so far (selects the alternating words) */
-};
-
-/*
- * Sets the select threshold of a row on the first slice this CTA sees of it. Called by all
- * worker threads (three group barriers). bv = the thread's maximum over its share (`own`: it has
- * one), wkey = the ordered key of the warp's maximum. Every owning thread is a group of up to
- * 32 entries; the group maxima are binned by their ordered keys into 256 bins below the largest,
- * and tau = the lower edge of the highest bin above which at least kq group maxima lie: at least
- * kq entries of this slice alone are >= tau, so tau cannot exceed the row's kq-th largest value.
- * Fewer than kq groups: everything passes.
- */
-__device__ __noinline__ TauState set_row_threshold(int tid, StreamShared *sh, float bv, bool own, unsigned wkey, int kq, int row, int boots) {
-    Grp g;
-    g.tid  = tid;
-    g.lane = tid & 31;
-    g.warp = tid >> 5;
-    g.n    = kWorkThreads;
-    g.nw   = kWorkWarps;
-    g.bar  = 1;
-    TauState ts;
-    ts.boots       = boots + 1;
-    const int bsel = boots & 1;
-    const unsigned bkey = order_key(bv + 0.0f);
-    {
-        const unsigned wlo  = __reduce_min_sync(0xffffffffu, own ? bkey : 0xffffffffu);
-        const int      wown = __popc(__ballot_sync(0xffffffffu, own));
-        if (g.lane == 0 && wown > 0) {
-            atomicMax(&sh->top_key[bsel], wkey);
-            atomicMin(&sh->low_key[bsel], wlo);
-            atomicAdd(&sh->boot_n[bsel], wown);
-        }
-    }
-    for (int i = g.tid; i < kHistBins; i += g.n) {
-        sh->bhist[i] = 0; /* the previous use's readers passed its last barrier long ago */
-    }
-    g.sync();
-    if (g.tid == 0) {
-        sh->tau_key[bsel ^ 1] = 0xffffffffu; /* their readers have all passed the barrier above */
-        sh->top_key[bsel ^ 1] = 0u;
-        sh->low_key[bsel ^ 1] = 0xffffffffu;
-        sh->boot_n[bsel ^ 1]  = 0;
-        sh->t_row             = -1;
-    }
-    for (int i = g.tid; i < kHistBins; i += g.n) {
-        sh->thist[i] = 0;
-    }
-    const unsigned khi = sh->top_key[bsel];
-    /* values far below the largest all go to bin 0: the walk comes from the top */
-    const unsigned klo   = max(sh->low_key[bsel], khi > (1u << 27) ? khi - (1u << 27) : 0u);
-    const int      n_own = sh->boot_n[bsel];
-    const unsigned span  = khi - klo;
-    const int      shift = max(0, (32 - __clz(span)) - 8); /* (span >> shift) < 256 */
-    if (own && n_own >= kq) {
-        atomicAdd(&sh->bhist[(max(bkey, klo) - klo) >> shift], 1);
-    }
-    g.sync();
-    if (g.warp == 0) {
-        unsigned tkey = 0u; /* below everything: all entries pass */
-        if (n_own >= kq) {
-            /* lane l holds bins 8 l .. 8 l + 7; the highest bin with at least kq group maxima in it and above */
-            int        c[8];
-            const int4 lo4 = *reinterpret_cast<const int4 *>(&sh->bhist[8 * g.lane]);
-            const int4 hi4 = *reinterpret_cast<const int4 *>(&sh->bhist[8 * g.lane + 4]);
-            c[0] = lo4.x, c[1] = lo4.y, c[2] = lo4.z, c[3] = lo4.w, c[4] = hi4.x, c[5] = hi4.y, c[6] = hi4.z, c[7] = hi4.w;
-            int mine = 0;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                mine += c[i];
-            }
-            int suffix = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int dn = __shfl_down_sync(0xffffffffu, suffix, o);
-                if (g.lane + o < 32) {
-                    suffix += dn;
-                }
-            }
-            const unsigned ball = __ballot_sync(0xffffffffu, suffix >= kq);
-            int            b    = 0;
-            if (ball != 0u && g.lane == 31 - __clz(ball)) {
-                int run = suffix - mine;
-                b       = 8 * g.lane;
-#pragma unroll
-                for (int i = 7; i >= 0; i--) {
-                    run += c[i];
-                    if (run >= kq) {
-                        b = 8 * g.lane + i;
-                        break;
-                    }
-                }
-            }
-            b    = __shfl_sync(0xffffffffu, b, ball != 0u ? 31 - __clz(ball) : 0);
-            tkey = b == 0 ? sh->low_key[bsel] : klo + ((unsigned) b << shift); /* bin 0 also holds what was clamped */
-        }
-        if (g.lane == 0) {
-            sh->tau_key[bsel] = tkey;
-        }
-    }
-    g.sync();
-    const unsigned tkey = sh->tau_key[bsel];
-    ts.tau = tkey == 0u ? -CUDART_INF_F : key_to_float(tkey);
-    ts.row = row;
-    /* the row's candidates are binned between tau and this slice's maximum; the publisher reads the
-     * bins from the top and raises the threshold for the slices to come (each thread computes the
-     * same map from value to bin) */
-    const float top = key_to_float(khi);
-    ts.lo           = ts.tau;
-    ts.scale        = (n_own >= kq && top > ts.tau && top - ts.tau < CUDART_INF_F) ? (float) kHistBins / (top - ts.tau) : 0.0f;
-    if (g.tid == 0) {
-        sh->t_lo    = ts.lo;
-        sh->t_scale = ts.scale;
-        __threadfence_block();
-        sh->t_row = row; /* the publisher raises the threshold of this row from now on */
-    }
-    return ts;
-}
-
-/* ------------------------------------------------------------------ kernel -- */
-
-__global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid_constant__ SampleParams p) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-
-    unsigned char  *ring = smem_raw;
-    StreamShared   *sh   = reinterpret_cast<StreamShared *>(smem_raw + (size_t) p.stages * (size_t) p.stage_bytes);
-    unsigned       *dlr  = reinterpret_cast<unsigned *>(sh + 1);                             /* id lists of the slices in flight */
-    FinBuffers      fb;
-    fb.dlist_cap = min(p.hist_cap, 512);
-    fb.bitmap    = reinterpret_cast<unsigned *>(dlr + kListRing * p.hist_cap);
-    fb.dlist     = reinterpret_cast<PenEntry *>(fb.bitmap + kFinBitmapWords);
-    fb.fcand     = reinterpret_cast<Pair *>(fb.dlist + fb.dlist_cap); /* merged candidates of one row */
-    fb.ftmp      = fb.fcand + p.fin_cap;
-    fb.fsort     = fb.ftmp + p.fin_cap;                             /* kFastKMax entries */
-    fb.fq        = reinterpret_cast<float *>(fb.fsort + kFastKMax); /* kFastKMax entries */
-
-    /* every CTA takes a contiguous run of the (row, slice) items, so that consecutive items mostly
-     * belong to one row and what a slice learns about its row serves the next ones */
+    /* every thread block takes a contiguous run of the (row, slice) items */
     const int n_items  = p.n_rows * p.n_slices;
     const int G        = (int) gridDim.x;
     const int q_items  = n_items / G, r_items = n_items - q_items * G;
     const int my_first = (int) blockIdx.x * q_items + min((int) blockIdx.x, r_items);
     const int my_count = q_items + ((int) blockIdx.x < r_items ? 1 : 0);
-    const int row0     = my_first / p.n_slices;
-    const int c0       = my_first - row0 * p.n_slices;
 
-    if (p.chained) {
-        /* Launched as a programmatic dependent of the kernel before it in the stream: the thread block may
-         * have been placed while that kernel's last blocks were still at work. Everything it touches in
-         * global memory waits here for that kernel to be complete and visible, so the stream's order is
-         * kept; what is saved is the gap between two grids. The kernel behind this one may be placed
-         * likewise. */
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        asm volatile("griddepcontrol.launch_dependents;");
-    }
-    /* the control words (row counters, queue slots, tickets) of this scratch set exist twice; this
-     * launch uses one copy, which was zeroed during the set's previous use, and zeroes the other */
-    for (int i = (int) blockIdx.x * kThreads + (int) threadIdx.x; i < p.clear_words; i += G * kThreads) {
-        p.clear_ptr[i] = 0;
-    }
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; s++) {
-            mbar_init(&sh->full[s], 1);
-            mbar_init(&sh->empty[s], kWorkWarps);
+    if (tid == 0) {
+        for (int w = 0; w < kWarps; w++) {
+            for (int s = 0; s < kStages; s++) {
+                mbar_init_only(&sh->full[w][s], 1);
+            }
         }
-        for (int i = 0; i < kListRing; i++) {
-            sh->acc[i].best    = 0ull;
-            sh->acc[i].n_cand  = 0;
-            sh->acc[i].arrived = 0;
-            sh->acc[i].st      = 0;
-            sh->n_dl[i]        = 0;
-        }
-        for (int i = 0; i < kListRing; i++) {
-            sh->slice_done[i] = 0;
-        }
-        sh->t_row = -1;
-        sh->tau_key[0] = 0xffffffffu;
-        sh->tau_key[1] = 0xffffffffu;
-        sh->top_key[0] = 0u;
-        sh->top_key[1] = 0u;
-        sh->low_key[0] = 0xffffffffu;
-        sh->low_key[1] = 0xffffffffu;
-        sh->boot_n[0]  = 0;
-        sh->boot_n[1]  = 0;
-        sh->tau_pub    = 0ull;
-        sh->q_done     = 0;
-        sh->q_error    = 0;
-        sh->p_done     = 0;
-        sh->fin_head   = 0;
-        sh->fin_tail   = 0;
-        sh->l_decoded  = 0;
-        sh->w_done     = 0;
-        sh->done_warps = 0;
-        sh->n_slow     = 0;
+        mbar_init_fence();
     }
     __syncthreads();
-
-    auto advance = [&](int &row, int &c) {
-        c++;
-        if (c == p.n_slices) {
-            c = 0;
-            row++;
-        }
-    };
-
-    /* the loader keeps the ring full: the jj-th item of this CTA goes to stage jj % stages */
-    auto issue = [&](int row, int c, int stage) {
-        const int      s0    = c * p.slice;
-        const int      n     = max(0, min(p.slice, p.V - s0));
-        const unsigned bytes = (unsigned) (n & ~3) * 4u;
-        if (bytes == 0u) {
-            return;
-        }
-        unsigned char       *dst = ring + (size_t) stage * (size_t) p.stage_bytes;
-        const unsigned char *src = reinterpret_cast<const unsigned char *>(p.logits + (size_t) row * (size_t) p.row_stride + s0);
-        mbar_expect_tx(&sh->full[stage], bytes);
-        for (unsigned off = 0; off < bytes; off += 32768u) {
-            bulk_g2s(dst + off, src + off, min(32768u, bytes - off), &sh->full[stage]);
-        }
-    };
-    /* an item's configuration is decoded into shared memory a few items ahead, so that the worker
-     * warps spend no instructions and no memory round trips on it */
-    auto decode = [&](int row, int c, const RowCfg &r, ItemCfg *o) {
-        const int s0 = c * p.slice;
-        const int n  = max(0, min(p.slice, p.V - s0));
-        const int n4 = (n + 3) >> 2;
-        int4     *w  = reinterpret_cast<int4 *>(o); /* five stores of four words */
-        w[0]         = make_int4(row, row * p.n_slices + c, s0, n);
-        w[1]         = make_int4((int) r.mode, r.kq, r.pen_on ? 1 : 0, 0);
-        w[2]         = make_int4(__float_as_int(r.inv_t), __float_as_int(r.rep), __float_as_int(r.freq), __float_as_int(r.pres));
-        w[3]         = make_int4(share_len(n4), n4, c, 0);
-        w[4]         = make_int4(r.H, r.E, r.seq, r.seq0);
-    };
-    static_assert(sizeof(ItemCfg) == 80, "decode() writes the item configuration as five int4");
-
-    if (threadIdx.x >= kWorkThreads && threadIdx.x < kWorkThreads + 32) {
-        /* ============================================================== loader == */
-        /* Lane 0 issues the bulk copies as stages come free; the whole warp prepares each item up to
-         * kListRing items ahead of the slowest worker warp: its configuration and the list of the
-         * history ids that fall into the slice, without repeats, each with its count. Every wait is
-         * bounded. */
-        const int lane = (int) threadIdx.x - kWorkThreads;
-        int       irow = row0, ic = c0; /* next item to load */
-        int       drow = row0, dcs = c0; /* next item to decode */
-        int       issued = 0, decoded = 0, istage = 0;
-        RawCfg    raw{};
-        if (lane == 0 && my_count > 0) {
-            raw = raw_config(p, drow);
-        }
-        RowCfg rcur{};
-        int    rcur_row = -1;
-        int hc[4]   = {-1, -1, -1, -1}; /* this lane's share of the history ids of row hc_row ... */
-        int hcnt[4] = {0, 0, 0, 0};     /* ... and how often each occurs, kept by its first occurrence only */
-        int hc_row = -1;
-        int hn[4]  = {-1, -1, -1, -1}; /* the next row's ids, fetched ahead (raw, before the shard offset) */
-        int hn_row = -1, hn_asked = -1, prev_item_row = -1;
-        int offr = 0, off_row = -1; /* lane i: where slice i's run starts in the prepared id list of row off_row */
-        bool lists_ready = false;   /* the kernel that prepares the lists has been waited for */
-        int my_issued = 0; /* lane 0: copies issued, the warp's count follows at the next turn */
-        /* one copy if a stage is free; never blocks: the items' preparation must go on */
-        auto try_issue = [&]() {
-            if (p.aligned && my_issued < my_count) {
-                bool ok = my_issued < p.stages;
-                if (!ok) { /* the stage's previous slice must have been lifted by all worker warps */
-                    ok = mbar_test(&sh->empty[istage], (unsigned) ((my_issued / p.stages - 1) & 1));
-                }
-                if (ok) {
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    issue(irow, ic, istage);
-                    advance(irow, ic);
-                    istage = istage + 1 == p.stages ? 0 : istage + 1;
-                    my_issued++;
-                }
-            }
-        };
+    /* Launched as a programmatic dependent of the kernel before it in the stream: the thread block may have
+     * been placed while that kernel's last blocks were still at work. Everything it touches in global memory
+     * waits here for that kernel to be complete and visible, so the stream's order is kept; what is saved is
+     * the gap between two grids. The kernel behind this one may be placed likewise. */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
 #ifdef GB_PROFILE
-        long long lp_busy = 0, lp_idle = 0, lp_t = clock64();
+    if (tid == 0 && blockIdx.x < 1024) {
+        for (int i = 1; i < 8; i++) {
+            g_prof[blockIdx.x][i] = 0;
+        }
+    }
 #endif
-        long long idle = 0;
-        while ((p.aligned && issued < my_count) || decoded < my_count) {
-            int act = 0;
-            if (lane == 0) {
-                try_issue();
-                act |= (my_issued - issued) << 2;
-                if (decoded < my_count && decoded < *reinterpret_cast<volatile int *>(&sh->w_done) + kListRing) {
-                    act |= 2;
-                }
+    PROF(0);
+
+    /* ---- the warp's own ring: lane 0 asks for the warp's share of the item kStages ahead ---- */
+    unsigned char *wring = ring + (size_t) warp * kStages * kWarpStageBytes;
+    int irow = my_first / p.n_slices, ic = my_first - irow * p.n_slices, ijj = 0; /* the next item to request */
+    auto issue_next = [&]() {
+        const int s0 = ic * p.slice, n = min(p.slice, p.V - s0);
+        const int nv4 = (n + 3) >> 2, nfull = n >> 2;
+        const int L = share_len(nv4), w4lo = min(warp * L, nv4), mine4 = min(L, nv4 - w4lo);
+        const int full4 = max(0, min(mine4, nfull - w4lo));
+        const int stage = ijj % kStages;
+        if (full4 > 0) {
+            mbar_expect_tx(&sh->full[warp][stage], (unsigned) full4 * 16u);
+            bulk_g2s(wring + (size_t) stage * kWarpStageBytes, p.logits + (size_t) irow * (size_t) p.row_stride + s0 + 4 * w4lo, (unsigned) full4 * 16u, &sh->full[warp][stage]);
+        }
+        ijj++;
+        ic++;
+        if (ic == p.n_slices) {
+            ic = 0;
+            irow++;
+        }
+    };
+    if (lane == 0 && p.aligned) {
+        for (int jj = 0; jj < min(kStages, my_count); jj++) {
+            issue_next();
+        }
+    }
+
+    CYC_INIT();
+    int j  = 0;
+    int pf = 0; /* warp 0: how far the parameters of the row that begins next have been fetched */
+    while (j < my_count) {
+        const int  item0 = my_first + j, row = item0 / p.n_slices, c0 = item0 - row * p.n_slices;
+        const int  part_len   = min(p.n_slices - c0, my_count - j);
+        const bool final_part = j + part_len == my_count;
+        CYC(7);
+        if (warp == 0) { /* what has not been fetched while the previous part streamed (first part, short parts) */
+            while (pf < kPrefetchDone) {
+                prefetch_step(p, sh, row, lane, pf);
             }
-            act = __shfl_sync(0xffffffffu, act, 0);
-            issued += act >> 2;
-            if (act & 2) {
-                ItemCfg *o = &sh->cfg[decoded % kCfgRing];
-                if (lane == 0) {
-                    if (rcur_row != drow) {
-                        /* a new row: its parameters were requested when the previous row began */
-                        rcur     = row_config(p, drow, raw, false);
-                        rcur_row = drow;
-                        if (drow + 1 < p.n_rows) {
-                            raw = raw_config(p, drow + 1); /* requested now, used when the next row begins */
-                        }
-                    }
-                    decode(drow, dcs, rcur, o);
-                    advance(drow, dcs);
-                }
-                __syncwarp();
-                int nd = 0, ovf = 0;
-                if (o->flags & 1) {
-                    const int  H = o->H, total = o->H + o->E, s0 = o->s0, n = o->n;
-                    const int *hrow = p.hist ? p.hist + (size_t) o->seq * (size_t) p.hist_stride : nullptr;
-                    const int *erow = p.extra ? p.extra + (size_t) o->seq0 * (size_t) p.extra_stride : nullptr;
-                    unsigned  *dl   = dlr + (size_t) (decoded % kListRing) * (size_t) p.hist_cap;
-                    if (total <= kLoaderIds) {
-                        /* The usual case. A row's ids are the same for all of its slices: once per row
-                         * they are read into registers (four per lane) and each is marked as the first
-                         * of its value with that value's count; a slice then only picks its own. */
-                        if (hc_row != o->row) {
-#pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                const int j  = 32 * k + lane;
-                                int       id = -1;
-                                if (j < total) { /* fetched ahead while the previous row was in work, where that was possible */
-                                    id = (hn_row == o->row ? hn[k] : (j < H ? hrow[j] : erow[1 + j - H])) - p.vocab_offset;
-                                }
-                                id    = (id >= 0 && id < p.V) ? id : -1 - j; /* unusable ids match nothing */
-                                hc[k] = id;
-                            }
-                            /* counts by a small open-addressing table in shared memory: the lane whose id
-                             * opened a slot speaks for that id and reads the slot's final count */
-                            for (int i = lane; i < kIdSlots; i += 32) {
-                                sh->id_key[i] = -1;
-                                sh->id_cnt[i] = 0;
-                            }
-                            __syncwarp();
-                            int slot_of[4];
-#pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                slot_of[k] = -1;
-                                if (hc[k] >= 0) {
-                                    unsigned hsh = ((unsigned) hc[k] * 2654435761u) >> (32 - kIdSlotBits);
-                                    for (int probe = 0; probe < kIdSlots; probe++) {
-                                        const int old = atomicCAS(&sh->id_key[hsh], -1, hc[k]);
-                                        if (old == -1 || old == hc[k]) {
-                                            atomicAdd(&sh->id_cnt[hsh], 1);
-                                            slot_of[k] = old == -1 ? (int) hsh : -1; /* only the opener keeps the slot */
-                                            break;
-                                        }
-                                        hsh = (hsh + 1) & (kIdSlots - 1);
-                                    }
-                                }
-                            }
-                            __syncwarp();
-#pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                hcnt[k] = slot_of[k] >= 0 ? sh->id_cnt[slot_of[k]] : 0; /* 0: another lane speaks for this id */
-                            }
-                            __syncwarp();
-                            hc_row = o->row;
-                        }
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            if (32 * k < total) {
-                                const bool     in   = hcnt[k] > 0 && hc[k] >= s0 && hc[k] - s0 < n;
-                                const unsigned ball = __ballot_sync(0xffffffffu, in);
-                                if (in) {
-                                    const int pos = nd + __popc(ball & ((1u << lane) - 1u));
-                                    if (pos < p.hist_cap) {
-                                        dl[pos] = (unsigned) (hc[k] - s0) | ((unsigned) hcnt[k] << kLiBits);
-                                    }
-                                }
-                                nd += __popc(ball);
-                            }
-                        }
-                    } else {
-                        /* Long histories: a kernel that ran before this one left the row's distinct ids with
-                         * their counts in global memory, grouped by slice; a slice copies its run. */
-                        if (!lists_ready) {
-                            /* this kernel may have been started while that one was still running
-                             * (programmatic dependent launch): its lists are complete and visible from here on */
-                            if (lane == 0) { /* the ring fills meanwhile */
-                                for (int i = 1; i < p.stages; i++) {
-                                    try_issue();
-                                }
-                            }
-                            __syncwarp();
-                            asm volatile("griddepcontrol.wait;" ::: "memory");
-                            lists_ready = true;
-                        }
-                        if (off_row != o->row) {
-                            offr    = lane <= p.n_slices ? p.pre_off[(size_t) o->row * (size_t) (p.n_slices + 1) + lane] : 0;
-                            off_row = o->row;
-                        }
-                        int lo, hi;
-                        if (p.n_slices < 32) {
-                            lo = __shfl_sync(0xffffffffu, offr, o->c);
-                            hi = __shfl_sync(0xffffffffu, offr, o->c + 1);
-                        } else {
-                            lo = p.pre_off[(size_t) o->row * (size_t) (p.n_slices + 1) + o->c];
-                            hi = p.pre_off[(size_t) o->row * (size_t) (p.n_slices + 1) + o->c + 1];
-                        }
-                        const unsigned *src = p.pre_list + (size_t) o->row * (size_t) p.row_cap;
-                        for (int i = lo + lane; i < hi && i - lo < p.hist_cap; i += 32) {
-                            copy_word_async(&dl[i - lo], &src[i]);
-                        }
-                        async_copies_wait();
-                        nd = hi - lo;
-                    }
-                    if (nd > p.hist_cap) { /* cannot happen when the launcher sized the room */
-                        ovf = 1;
-                        nd  = 0;
-                    }
-                    /* the next row's ids are requested one item after this row began (its parameters have
-                     * arrived by then), so that the row change does not wait for global memory */
-                    const int nrow = o->row + 1;
-                    if (hn_row != nrow && hn_asked != nrow && nrow < p.n_rows && o->row == prev_item_row) {
-                        int seq_n = 0, H_n = 0;
-                        if (lane == 0) { /* lane 0 holds the next row's raw parameters */
-                            seq_n = raw.seq;
-                            H_n   = p.hist ? (int) min((long long) max(raw.hist_len, 0), p.hist_stride) : 0;
-                        }
-                        seq_n            = __shfl_sync(0xffffffffu, seq_n, 0);
-                        H_n              = __shfl_sync(0xffffffffu, H_n, 0);
-                        const int seq0_n = p.rows_per_seq == 1 ? nrow : nrow / p.rows_per_seq;
-                        const int E_n    = p.extra ? nrow - seq0_n * p.rows_per_seq : 0;
-                        if (H_n + E_n <= kLoaderIds) {
-                            const int *hr = p.hist ? p.hist + (size_t) seq_n * (size_t) p.hist_stride : nullptr;
-                            const int *er = p.extra ? p.extra + (size_t) seq0_n * (size_t) p.extra_stride : nullptr;
-#pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                const int j = 32 * k + lane;
-                                hn[k]       = j < H_n + E_n ? (j < H_n ? hr[j] : er[1 + j - H_n]) : -1;
-                            }
-                            hn_row = nrow;
-                        }
-                        hn_asked = nrow;
-                    }
-                    prev_item_row = o->row;
-                }
-                __syncwarp();
-                if (lane == 0) {
-                    sh->n_dl[decoded % kListRing] = nd;
-                    o->st0                        = ovf ? ST_HIST_OVERFLOW : 0;
-                    __threadfence_block();
-                    sh->l_decoded = decoded + 1;
-                }
-                decoded++;
+            async_copies_wait();
+            pf = 0;
+        }
+        __syncthreads();
+        int   mode, kq, n_ids, my_id = -1;
+        float inv_t, rep, freq, pres;
+        bool  pen_on;
+        {
+            const RawCfg raw = sh->raw_nxt;
+            const RowCfg r   = row_config(p, row, raw, false); /* what the finisher needs more of is derived again when the row is complete */
+            mode   = (int) r.mode;
+            kq     = r.kq;
+            inv_t  = r.inv_t;
+            n_ids  = r.H + r.E;
+            pen_on = r.pen_on && n_ids > 0;
+            rep    = r.rep;
+            freq   = r.freq;
+            pres   = r.pres;
+            if (tid < n_ids && n_ids <= kRowIds) {
+                my_id = tid < r.H ? sh->nxt_ids[tid] : sh->nxt_ext[tid - r.H];
             }
-#ifdef GB_PROFILE
-            {
-                const long long t_ = clock64();
-                if (act & 2) {
-                    lp_busy += t_ - lp_t;
-                } else {
-                    lp_idle += t_ - lp_t;
-                }
-                lp_t = t_;
+        }
+        const bool  sel     = (mode == M_TOPK || mode == M_TOPP) && kq > 0 && kq <= kFastKMax;
+        const bool  sums    = mode == M_TEMP || (mode == M_TOPP && sel);
+        const bool  long_ids = n_ids > kRowIds;
+        const int   b_first = cta_of_item(row * p.n_slices, q_items, r_items);
+        const int   part_idx = (int) blockIdx.x - b_first;
+        const int   n_parts = cta_of_item(row * p.n_slices + p.n_slices - 1, q_items, r_items) - b_first + 1;
+
+        /* ---- part set-up ---- */
+        if (tid == 0) {
+            sh->st       = 0;
+            sh->tau_key  = 0u;
+            sh->tau_lock = 0;
+            sh->rl_n     = 0;
+        }
+        if (tid < kHistBins) {
+            sh->thist[tid] = 0;
+            sh->bhist[tid] = 0;
+        }
+        if (pen_on && !long_ids) {
+            /* the row's distinct ids with their counts: an open-addressing table in the groups' memory (free
+             * between two parts), one id per thread; the thread whose id opened a slot speaks for that id */
+            int *id_key = reinterpret_cast<int *>(gmem);
+            int *id_cnt = id_key + 2 * kRowIds;
+            for (int i = tid; i < 2 * kRowIds; i += kThreads) {
+                id_key[i] = -1;
+                id_cnt[i] = 0;
             }
-#endif
-            if (act == 0) {
-                if (++idle > (1ll << 26)) {
-                    if (lane == 0) {
-                        sh->q_error = 4; /* the workers stopped releasing stages: leave */
-                    }
-                    break;
+            int id = my_id;
+            if (tid < n_ids) {
+                id -= p.vocab_offset;
+                if (id < 0 || id >= p.V) {
+                    id = -1;
                 }
-                pause_cycles(40);
             } else {
-                idle = 0;
+                id = -1;
+            }
+            __syncthreads();
+            int slot = -1;
+            if (id >= 0) {
+                unsigned h = ((unsigned) id * 2654435761u) >> (32 - 9);
+                for (int probe = 0; probe < 2 * kRowIds; probe++) {
+                    const int old = atomicCAS(&id_key[h], -1, id);
+                    if (old == -1 || old == id) {
+                        atomicAdd(&id_cnt[h], 1);
+                        slot = old == -1 ? (int) h : -1;
+                        break;
+                    }
+                    h = (h + 1) & (2 * kRowIds - 1);
+                }
+            }
+            __syncthreads();
+            if (slot >= 0) {
+                const int pos   = atomicAdd(&sh->rl_n, 1);
+                sh->rl_id[pos]  = id;
+                sh->rl_cnt[pos] = id_cnt[slot];
+            }
+        } else if (pen_on) {
+            /* long histories: a kernel that ran before this one left the row's distinct ids with their counts
+             * in global memory, grouped by slice; the part copies where its slices' runs start */
+            const int *off = p.pre_off + (size_t) row * (size_t) (p.n_slices + 1) + c0;
+            for (int i = tid; i <= part_len; i += kThreads) {
+                sl_off[i] = off[i];
             }
         }
-#ifdef GB_PROFILE
-        if (lane == 0 && blockIdx.x < 256) {
-            g_prof2[blockIdx.x][12] = lp_busy;
-            g_prof2[blockIdx.x][13] = lp_idle;
-        }
+        __syncthreads();
+        static_assert(2 * kRowIds == 512, "the id table's hash keeps 9 bits");
+
+        CYC(5);
+        unsigned run_key = 0u; /* this warp's maximum of the part so far (key) and its first id */
+        int      run_arg = 0x7fffffff;
+        float    tau_reg = -CUDART_INF_F, t_lo = 0.0f, t_scale = 0.0f;
+        int      wcnt = 0, since = 0; /* this warp's candidate groups of the part; those since it last looked at the threshold */
+        float    b_ref = -CUDART_INF_F; /* top-p: running sum of what is no candidate, relative to b_ref */
+        double   b_sum = 0.0;
+        int      wst   = 0;
+        float4  *seg_v = grp_v + warp * kGroupCapWarp;
+        int     *seg_b = grp_b + warp * kGroupCapWarp;
+
+        /* ---- the part's slices, every warp on its own ---- */
+        for (int s = 0; s < part_len; s++, j++) {
+            const int      stage  = j % kStages;
+            const unsigned parity = (unsigned) (j / kStages) & 1u;
+            const int      c = c0 + s, s0 = c * p.slice, n = min(p.slice, p.V - s0);
+            const int      nv4 = (n + 3) >> 2, body = n & ~3;
+            const int      L = share_len(nv4), w4lo = min(warp * L, nv4), mine4 = min(L, nv4 - w4lo);
+            float         *sl   = reinterpret_cast<float *>(wring + (size_t) stage * kWarpStageBytes); /* local index = slice index - 4 * w4lo */
+            const float   *grow = p.logits + (size_t) row * (size_t) p.row_stride + s0;
+#ifndef GB_X1
+            if (warp == 0 && !final_part && pf < kPrefetchDone) {
+                prefetch_step(p, sh, row + 1, lane, pf); /* one step per slice: the step before has long arrived */
+            }
 #endif
-    } else if (threadIdx.x >= kWorkThreads + 32 && threadIdx.x < kWorkThreads + 64) {
-        publisher_loop((int) threadIdx.x - kWorkThreads - 32, p, sh, my_count);
-    } else if (threadIdx.x >= kWorkThreads + 64) {
-        Grp g;
-        g.tid  = (int) threadIdx.x - kWorkThreads - 64;
-        g.lane = g.tid & 31;
-        g.warp = g.tid >> 5;
-        g.n    = kFinThreads;
-        g.nw   = kFinWarps;
-        g.bar  = 2;
-        finisher_loop(g, p, sh, fb);
-    } else {
-    /* ================================================================ workers == */
-    /* Every worker warp walks the CTA's slices at its own pace: it owns a fixed share of each slice
-     * (float4 [warp * L, (warp + 1) * L), lanes interleaved), waits for the slice's copy, applies the
-     * penalties that fall into its share, lifts the share into registers, gives the stage back and
-     * runs its passes on registers. Warps meet only in the slice's accumulators (shared-memory
-     * atomics) and, once per row, in the barrier that sets the row's select threshold. The warp
-     * that arrives last at a slice's accumulators writes the slice's mail. */
-    Grp g;
-    g.tid  = (int) threadIdx.x;
-    g.lane = g.tid & 31;
-    g.warp = g.tid >> 5;
-    g.n    = kWorkThreads;
-    g.nw   = kWorkWarps;
-    g.bar  = 1;
-
-    /* bounded wait until the loader has prepared item jj */
-    auto wait_decoded = [&](int jj) {
-        for (long long spin = 0; spin < (1ll << 26) && sh->l_decoded <= jj; spin++) {
-            pause_cycles(20);
-        }
-        return sh->l_decoded > jj;
-    };
-    unsigned phase_bits = 0u; /* parity of the next wait for a copy, one bit per stage */
-    int      stage      = 0;
-    TauState ts;
-    ts.tau   = 0.0f;
-    ts.row   = -1;
-    ts.lo    = 0.0f;
-    ts.scale = 0.0f;
-    ts.boots = 0;
-
-    PROF_INIT();
-    PROF2_INIT();
-#ifdef GB_PROFILE
-    prof_acc[3] = gtime();
-#endif
-    for (int j = 0; j < my_count; j++) {
-        PROF(0); /* loop overhead */
-        PROF2(0);
-        if (!wait_decoded(j)) {
-            break; /* the loader gave up (it has flagged the error); every warp stops at the same item */
-        }
-        const ItemCfg *cf = &sh->cfg[j % kCfgRing];
-        const int4     c0 = *reinterpret_cast<const int4 *>(&cf->row);   /* row, item, s0, n */
-        const int4     c1 = *reinterpret_cast<const int4 *>(&cf->mode);  /* mode, kq, flags, - */
-        const int4     c3 = *reinterpret_cast<const int4 *>(&cf->L);     /* L, nv4, c, st0 */
-        const int      row = c0.x, item = c0.y, s0 = c0.z, n = c0.w;
-        const int      mode = c1.x, kq = c1.y;
-        const bool     pen_on = (c1.z & 1) != 0;
-        const int      L = c3.x, nv4 = c3.y;
-        SliceAcc      *acc   = &sh->acc[j % kListRing];
-        float         *sl    = reinterpret_cast<float *>(ring + (size_t) stage * (size_t) p.stage_bytes);
-        const int      body  = p.aligned ? (n & ~3) : 0;
-        const int      w4lo  = min(g.warp * L, nv4);
-        const int      mine4 = min(L, nv4 - w4lo); /* float4 this warp owns (L is a multiple of 32) */
-        const float   *grow  = p.logits + (size_t) row * (size_t) p.row_stride + s0;
-        int            st    = g.warp == 0 ? c3.w : ST_OK;
-        if (g.tid == 96 && c3.z == 0) {
-            p.status[row] = ST_INTERNAL; /* stands until the row's finisher writes the real status */
-        }
-        PROF2(1); /* decoded + cfg */
-
-        /* ---- 1. the warp's share of the slice is in the stage; the slice's tail is padded with -inf ---- */
-        if (p.aligned) {
-            const unsigned parity = (phase_bits >> stage) & 1u;
-            phase_bits ^= 1u << stage;
-            if (body > 0 && !mbar_wait_bounded(&sh->full[stage], parity)) {
-                st |= ST_LOAD_TIMEOUT;
-                (void) mbar_wait_bounded(&sh->full[stage], parity); /* a second bounded chance for the copy in flight */
-            }
-            if (nv4 * 4 > body && w4lo + mine4 == nv4 && mine4 > 0 && g.lane < 4) {
-                const int i = body + g.lane; /* the last float4 is not part of the bulk copy */
-                sl[i]       = i < n ? grow[i] : -CUDART_INF_F;
-            }
-        } else {
-            /* rows off the 16-byte grid: plain loads; before the stage is written again every warp must
-             * have lifted the slice that used it last */
-            if (j >= p.stages && !mbar_wait_bounded(&sh->empty[stage], (unsigned) ((j / p.stages - 1) & 1))) {
-                st |= ST_LOAD_TIMEOUT;
-            }
-            for (int i = 4 * w4lo + g.lane; i < 4 * (w4lo + mine4); i += 32) {
-                sl[i] = i < n ? grow[i] : -CUDART_INF_F;
-            }
-        }
-        __syncwarp();
-        PROF(1); /* waiting for the slice */
-        PROF2(2);
-
-        /* ---- 2. penalties on the share (the loader left the slice's distinct ids with their counts) ---- */
-        if (pen_on) {
-            const int       nd = sh->n_dl[j % kListRing];
-            const unsigned *dl = dlr + (size_t) (j % kListRing) * (size_t) p.hist_cap;
-            for (int i = g.lane; i < nd; i += 32) {
-                const unsigned e  = dl[i];
-                const int      li = (int) (e & ((1u << kLiBits) - 1u));
-                if ((li >> 2) >= w4lo && (li >> 2) < w4lo + mine4) {
-                    sl[li] = penalise(sl[li], (int) (e >> kLiBits), cf->rep, cf->freq, cf->pres);
+            CYC(4);
+            /* ---- 1. the warp's share of the slice is in its stage; the slice's tail is padded with -inf ---- */
+            if (p.aligned) {
+                const int full4 = max(0, min(mine4, (n >> 2) - w4lo));
+                if (full4 > 0 && !mbar_wait_bounded(&sh->full[warp][stage], parity)) {
+                    wst |= ST_LOAD_TIMEOUT;
+                    (void) mbar_wait_bounded(&sh->full[warp][stage], parity); /* a second bounded chance for the copy in flight */
+                }
+                if (nv4 * 4 > body && w4lo + mine4 == nv4 && mine4 > 0 && lane < 4) {
+                    const int i       = body + lane; /* the last float4 is not part of the bulk copy */
+                    sl[i - 4 * w4lo]  = i < n ? grow[i] : -CUDART_INF_F;
+                }
+            } else {
+                /* rows off the 16-byte grid: plain loads into the warp's own stage */
+                for (int i = lane; i < 4 * mine4; i += 32) {
+                    const int gi = 4 * w4lo + i;
+                    sl[i]        = gi < n ? grow[gi] : -CUDART_INF_F;
                 }
             }
             __syncwarp();
-        }
-        if (p.out_logits != nullptr) {
-            float *orow = p.out_logits + (size_t) row * (size_t) p.V + s0;
-            for (int i = 4 * w4lo + g.lane; i < min(4 * (w4lo + mine4), n); i += 32) {
-                orow[i] = sl[i];
-            }
-        }
-        /* what a thread does not own reads as -inf, so the passes below need no bounds checks */
-        const int     first4 = w4lo + g.lane; /* this thread's float4 are first4 + 32 i */
-        const float4 *s4     = reinterpret_cast<const float4 *>(sl) + first4;
-        float4        x[8];
-        if (mine4 == 256) { /* the usual case: a full share */
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                x[i] = s4[32 * i];
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                x[i] = g.lane + 32 * i < mine4 ? s4[32 * i] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
-            }
-        }
-        PROF(2); /* penalties, registers */
-        PROF2(3);
+            CYC(0);
 
-        /* ---- 3. the share's maximum; the few entries that matter are then picked from the stage ---- */
-        float bv = -CUDART_INF_F;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            bv = fmaxf(bv, fmaxf(fmaxf(x[i].x, x[i].y), fmaxf(x[i].z, x[i].w)));
-        }
-        PROF2(4); /* lane max (waits for the loads) */
-        const unsigned bkey = order_key(bv + 0.0f); /* -0 and +0 are one value, as the comparison of floats has it */
-        const unsigned wkey = __reduce_max_sync(0xffffffffu, bkey);
-        const float    wmax = key_to_float(wkey);
-        /* The 32 entries of lane L, one per lane of the warp: lane l looks at element l & 3 of L's
-         * float4 number l >> 2. `look` says whether that entry exists, is L's own and is no padding. */
-        const int  e4   = g.lane >> 2, eq = g.lane & 3;
-        auto       look = [&](int L_, int &li, float &v) {
-            li            = 4 * (w4lo + L_ + 32 * e4) + eq;
-            const bool ok = L_ + 32 * e4 < mine4 && li < n;
-            v             = ok ? sl[li] : -CUDART_INF_F;
-            return ok;
-        };
-        if (mode == M_ARGMAX) {
-            /* the first id of the warp's maximum, if it can still be the slice's; only the lanes that hold
-             * the maximum are searched */
-            unsigned best = 0x7fffffffu;
-            if (wkey >= (unsigned) (*reinterpret_cast<volatile unsigned long long *>(&acc->best) >> 32)) {
-                for (unsigned hits = __ballot_sync(0xffffffffu, bkey == wkey && g.lane < mine4); hits != 0u; hits &= hits - 1u) {
-                    int            li;
-                    float          v;
-                    const bool     ok = look(__ffs(hits) - 1, li, v);
-                    const unsigned eb = __ballot_sync(0xffffffffu, ok && v == wmax);
-                    if (eb != 0u) {
-                        best = min(best, (unsigned) (s0 + __shfl_sync(0xffffffffu, li, __ffs(eb) - 1)));
+            /* ---- 2. penalties on the share ---- */
+            if (pen_on) {
+                if (!long_ids) {
+                    const int rn = sh->rl_n;
+                    for (int e = lane; e < rn; e += 32) {
+                        const int li = sh->rl_id[e] - s0;
+                        if (li >= 4 * w4lo && li < 4 * (w4lo + mine4) && li < n) {
+                            sl[li - 4 * w4lo] = penalise(sl[li - 4 * w4lo], sh->rl_cnt[e], rep, freq, pres);
+                        }
+                    }
+                } else {
+                    const unsigned *src = p.pre_list + (size_t) row * (size_t) p.row_cap;
+                    const int       lo = sl_off[s], hi = sl_off[s + 1];
+                    for (int i = lo + lane; i < hi; i += 32) {
+                        const unsigned e  = src[i];
+                        const int      li = (int) (e & ((1u << kLiBits) - 1u));
+                        if (li >= 4 * w4lo && li < 4 * (w4lo + mine4) && li < n) {
+                            sl[li - 4 * w4lo] = penalise(sl[li - 4 * w4lo], (int) (e >> kLiBits), rep, freq, pres);
+                        }
                     }
                 }
+                __syncwarp();
             }
-            if (g.lane == 0 && best != 0x7fffffffu) {
-                atomicMax(&acc->best, ((unsigned long long) wkey << 32) | (unsigned long long) (0xffffffffu - best));
+            if (p.out_logits != nullptr) {
+                float *orow = p.out_logits + (size_t) row * (size_t) p.V + s0;
+                for (int i = 4 * w4lo + lane; i < min(4 * (w4lo + mine4), n); i += 32) {
+                    orow[i] = sl[i - 4 * w4lo];
+                }
             }
-        } else if (g.lane == 0 && mine4 > 0) {
-            atomicMax(&acc->best, (unsigned long long) wkey << 32); /* the maximum alone: no other mode asks where it is */
-        }
-        PROF2(5); /* key reduce + first id */
-        PROF2(6);
 
-        const bool  sel   = (mode == M_TOPK || mode == M_TOPP) && kq > 0 && kq <= kFastKMax;
-        const float inv_t = cf->inv_t;
-        float       tau   = CUDART_INF_F;
-        if (sel) {
-            /* top-k / top-p fast path. The select threshold tau is a lower bound of the row's kq-th
-             * largest value, so every entry of the row's kq best passes it wherever it lies. It is set
-             * once per row and CTA, on the first slice the CTA sees of the row (all warps meet there);
-             * the other slices of the row reuse it, raised by what the mail writers publish, and need no
-             * barrier. */
-#ifdef GB_FAKE_TAU
-            if (ts.row != row) { /* experiment only: a constant that suits the synthetic rows */
-                ts.tau = 7.0f; ts.row = row; ts.lo = 7.0f; ts.scale = 0.0f;
-            } else if (false) {
-#else
-            if (ts.row != row) {
+            /* ---- 3. the share in registers; what a thread does not own reads as -inf ---- */
+            const float4 *s4 = reinterpret_cast<const float4 *>(sl) + lane;
+            float4        x[kNV4];
+            float         gm[kNV4]; /* maximum of each float4 group */
+            float         bv = -CUDART_INF_F;
+#pragma unroll
+            for (int i = 0; i < kNV4; i++) {
+                x[i]  = lane + 32 * i < mine4 ? s4[32 * i] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+                gm[i] = fmaxf(fmaxf(x[i].x, x[i].y), fmaxf(x[i].z, x[i].w));
+                bv    = fmaxf(bv, gm[i]);
+            }
+            CYC(1);
+#ifndef GB_X2
+            /* the stage is free again: the warp refills it itself */
+            __syncwarp();
+            if (lane == 0 && p.aligned && j + kStages < my_count) {
+#ifndef GB_X4
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 #endif
-                ts = set_row_threshold(g.tid, sh, bv, g.lane < mine4, wkey, kq, row, ts.boots);
-                PROF(6);
-            } else {
-                const unsigned long long pub = *reinterpret_cast<volatile unsigned long long *>(&sh->tau_pub);
-                if ((int) (pub >> 32) == row && (unsigned) pub > order_key(ts.tau)) {
-                    ts.tau = key_to_float((unsigned) pub);
+                issue_next();
+            }
+#endif
+            CYC(3);
+            const unsigned bkey = order_key(bv + 0.0f); /* -0 and +0 are one value, as the comparison of floats has it */
+            const bool     own  = lane < mine4;
+            const unsigned wkey = __reduce_max_sync(0xffffffffu, own ? bkey : 0u);
+            const float    wmax = wkey == 0u ? -CUDART_INF_F : key_to_float(wkey);
+
+            if (mode == M_ARGMAX) {
+                if (wkey > run_key) { /* rare: the warp's running maximum moves; its first id in this slice */
+                    int best = 0x7fffffff;
+                    if (own && bkey == wkey) {
+#pragma unroll
+                        for (int i = kNV4 - 1; i >= 0; i--) {
+                            const int b = 4 * (w4lo + lane + 32 * i);
+                            if (x[i].w == wmax) best = b + 3;
+                            if (x[i].z == wmax) best = b + 2;
+                            if (x[i].y == wmax) best = b + 1;
+                            if (x[i].x == wmax) best = b;
+                        }
+                    }
+                    best    = __reduce_min_sync(0xffffffffu, best);
+                    run_key = wkey;
+                    run_arg = s0 + best;
+                }
+            } else if (wkey > run_key) {
+                run_key = wkey; /* the maximum alone: no other mode asks where it is */
+            }
+
+            float tau = CUDART_INF_F;
+            if (sel) {
+                if (s == 0) {
+                    /* The part's first slice sets the threshold; all warps meet here (the only barriers inside a
+                     * part). The thread maxima (wide k: the float4 maxima) are binned by their ordered keys into 256
+                     * bins below the largest, and tau = the lower edge of the highest bin above which at least kq of
+                     * them lie: at least kq entries of this slice alone are >= tau, so tau cannot exceed the row's
+                     * kq-th largest value. Fewer than kq groups: everything passes. */
+                    const bool fine = kq > 64;
+                    float      gmin = bv;
+                    int        ng   = own ? 1 : 0;
+                    if (fine) {
+                        gmin = CUDART_INF_F;
+                        ng   = 0;
+#pragma unroll
+                        for (int i = 0; i < kNV4; i++) {
+                            if (lane + 32 * i < mine4) {
+                                gmin = fminf(gmin, gm[i]);
+                                ng++;
+                            }
+                        }
+                    }
+                    const unsigned wlow = __reduce_min_sync(0xffffffffu, own ? order_key(gmin + 0.0f) : 0xffffffffu);
+                    ng                  = __reduce_add_sync(0xffffffffu, ng);
+                    if (lane == 0) {
+                        sh->wkey[warp] = wkey;
+                        sh->wlow[warp] = wlow;
+                        sh->wown[warp] = ng;
+                    }
+                    __syncthreads();
+                    unsigned khi = 0u, klo = 0xffffffffu;
+                    int      n_own = 0;
+#pragma unroll
+                    for (int w = 0; w < kWarps; w++) {
+                        khi = max(khi, sh->wkey[w]);
+                        klo = min(klo, sh->wlow[w]);
+                        n_own += sh->wown[w];
+                    }
+                    /* values far below the largest all go to bin 0: the walk comes from the top */
+                    const unsigned klo2  = max(klo, khi > (1u << 27) ? khi - (1u << 27) : 0u);
+                    const unsigned span  = khi - klo2;
+                    const int      shift = max(0, (32 - __clz(span)) - 8); /* (span >> shift) < 256 */
+                    if (n_own >= kq) {
+                        if (fine) {
+#pragma unroll
+                            for (int i = 0; i < kNV4; i++) {
+                                if (lane + 32 * i < mine4) {
+                                    atomicAdd(&sh->bhist[(max(order_key(gm[i] + 0.0f), klo2) - klo2) >> shift], 1);
+                                }
+                            }
+                        } else if (own) {
+                            atomicAdd(&sh->bhist[(max(bkey, klo2) - klo2) >> shift], 1);
+                        }
+                    }
+                    __syncthreads();
+                    unsigned tkey = 0u; /* below everything: all entries pass */
+                    if (n_own >= kq) { /* every warp reads the bins for itself */
+                        const int b = top_bin(sh->bhist, lane, kq);
+                        tkey        = b == 0 ? klo : klo2 + ((unsigned) b << shift); /* bin 0 also holds what was clamped */
+                    }
+                    tau_reg = tkey == 0u ? -CUDART_INF_F : key_to_float(tkey);
+                    /* the part's candidates are binned between tau and this slice's maximum; the bins are read from
+                     * the top to raise the threshold for the slices to come */
+                    const float top = key_to_float(khi);
+                    t_lo            = tau_reg;
+                    t_scale         = (n_own >= kq && top > tau_reg && top - tau_reg < CUDART_INF_F) ? (float) kHistBins / (top - tau_reg) : 0.0f;
+                }
+                const unsigned pkey = *reinterpret_cast<volatile unsigned *>(&sh->tau_key);
+                tau                 = pkey == 0u ? tau_reg : fmaxf(tau_reg, key_to_float(pkey));
+                /* candidates: the float4 groups whose maximum passes; one ballot per group of the warp, places
+                 * counted from the warp's own cursor, no atomics on the way */
+#pragma unroll
+                for (int i = 0; i < kNV4; i++) {
+                    const bool     hit = gm[i] >= tau && lane + 32 * i < mine4;
+                    const unsigned m   = __ballot_sync(0xffffffffu, hit);
+                    if (m != 0u) {
+                        if (hit) {
+                            const int pos = wcnt + __popc(m & lt);
+                            if (pos < kGroupCapWarp) {
+                                /* which of the four pass: the finisher takes those, the sums below leave those out */
+                                const unsigned cm = (x[i].x >= tau ? 1u : 0u) | (x[i].y >= tau ? 2u : 0u) | (x[i].z >= tau ? 4u : 0u) | (x[i].w >= tau ? 8u : 0u);
+                                seg_v[pos]        = x[i];
+                                seg_b[pos]        = (s0 + 4 * (w4lo + lane + 32 * i)) | (int) (cm << 28);
+                            }
+                            if (t_scale > 0.0f) {
+                                atomicAdd(&sh->thist[min(kHistBins - 1, max(0, __float2int_rz((gm[i] - t_lo) * t_scale)))], 1);
+                            }
+                        }
+                        wcnt += __popc(m);
+                        since += __popc(m);
+                    }
                 }
             }
-            tau      = ts.tau;
-            Pair *gc = p.cands + (size_t) item * (size_t) p.cand_cap;
-            /* the lanes whose maximum passes hold all the candidates: their entries are looked at by the
-             * whole warp, one lane after the other (about three per slice and warp) */
-            for (unsigned hits = __ballot_sync(0xffffffffu, bv >= tau && g.lane < mine4); hits != 0u; hits &= hits - 1u) {
-                int            li;
-                float          v;
-                const bool     ok = look(__ffs(hits) - 1, li, v) && v >= tau;
-                const unsigned pb = __ballot_sync(0xffffffffu, ok);
-                int            base = 0;
-                if (g.lane == 0) {
-                    base = atomicAdd(&acc->n_cand, __popc(pb));
-                }
-                base = __shfl_sync(0xffffffffu, base, 0);
-                if (ok) {
-                    const int pos = base + __popc(pb & ((1u << g.lane) - 1u));
-                    if (pos < p.cand_cap) {
-                        Pair c2;
-                        c2.v    = v;
-                        c2.idx  = s0 + li;
-                        gc[pos] = c2; /* straight to the row's scratch */
-                    }
-                    if (ts.scale > 0.0f) {
-                        atomicAdd(&sh->thist[min(kHistBins - 1, max(0, __float2int_rz((v - ts.lo) * ts.scale)))], 1);
-                    }
-                }
-            }
-        }
-        __syncwarp();
-        if (g.lane == 0) {
-            mbar_arrive(&sh->empty[stage]); /* this warp is done with the stage */
-        }
-        PROF2(10); /* threshold + candidates */
-        if (mode == M_TEMP || (mode == M_TOPP && sel)) {
-            /* sum of e_i relative to the WARP's maximum (top-p: of what stays below the threshold); the
-             * mail writer rescales to the slice maximum and the finisher to the row maximum. -inf
-             * padding gives exp(-inf) = 0. */
-            const float ref = wmax == -CUDART_INF_F ? 0.0f : wmax;
-            double      sum = 0.0;
-            if (mode == M_TEMP) {
+            if (sums) {
+                /* sum of e_i relative to the WARP's maximum of this slice (top-p: of what is in no candidate
+                 * group); -inf padding gives exp(-inf) = 0 */
+                const float ref = wmax == -CUDART_INF_F ? 0.0f : wmax;
+                double      sum = 0.0;
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const float e0 = expf(scaled_arg(x[i].x, ref, inv_t));
-                    const float e1 = expf(scaled_arg(x[i].y, ref, inv_t));
-                    const float e2 = expf(scaled_arg(x[i].z, ref, inv_t));
-                    const float e3 = expf(scaled_arg(x[i].w, ref, inv_t));
-                    sum += (double) ((e0 + e1) + (e2 + e3));
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    /* what passed the threshold is a candidate and counts there: its argument becomes -inf
-                     * (exp gives 0), so that the 32 evaluations stay one straight line and overlap */
+                for (int i = 0; i < kNV4; i++) {
+                    /* a candidate's argument becomes -inf (exp gives 0), so that the evaluations stay one straight
+                     * line and overlap */
                     const float e0 = expf(x[i].x >= tau ? -CUDART_INF_F : scaled_arg(x[i].x, ref, inv_t));
                     const float e1 = expf(x[i].y >= tau ? -CUDART_INF_F : scaled_arg(x[i].y, ref, inv_t));
                     const float e2 = expf(x[i].z >= tau ? -CUDART_INF_F : scaled_arg(x[i].z, ref, inv_t));
                     const float e3 = expf(x[i].w >= tau ? -CUDART_INF_F : scaled_arg(x[i].w, ref, inv_t));
                     sum += (double) ((e0 + e1) + (e2 + e3));
                 }
+                sum = warp_sum_d(sum);
+                if (mode == M_TEMP) {
+                    if (lane == 0) {
+                        SegRec sr;
+                        sr.ref = wmax;
+                        sr.pad = 0.0f;
+                        sr.sum = sum;
+                        p.segs[((size_t) row * (size_t) p.n_slices + (size_t) c) * kWarps + warp] = sr;
+                    }
+                } else if (wmax != -CUDART_INF_F) {
+                    if (wmax > b_ref) {
+                        b_sum = b_ref == -CUDART_INF_F ? 0.0 : b_sum * exp(((double) b_ref - (double) wmax) * (double) inv_t);
+                        b_ref = wmax;
+                    }
+                    b_sum += sum * exp(((double) wmax - (double) b_ref) * (double) inv_t);
+                }
             }
-            sum = warp_sum_d(sum);
-            if (g.lane == 0) {
-                acc->wmax[g.warp] = wmax;
-                acc->wsum[g.warp] = sum;
+            if (sel && since >= 8 && t_scale > 0.0f) {
+                /* after a few new candidates of its own the warp looks whether the threshold can go up: the lowest
+                 * bin edge above which at least kq candidates lie, one bin lower to be safe against rounding */
+                since  = 0;
+                int go = 0;
+                if (lane == 0) {
+                    go = atomicCAS(&sh->tau_lock, 0, 1) == 0 ? 1 : 0;
+                }
+                go = __shfl_sync(0xffffffffu, go, 0);
+                if (go) {
+                    const int b = top_bin(sh->thist, lane, kq);
+                    if (lane == 0) {
+                        if (b >= 2) {
+                            const float t_new = t_lo + (float) (b - 1) / t_scale;
+                            if (t_new > t_lo) {
+                                atomicMax(&sh->tau_key, order_key(t_new));
+                            }
+                        }
+                        __threadfence_block();
+                        sh->tau_lock = 0;
+                    }
+                }
             }
+#ifdef GB_X2
+            __syncwarp();
+            if (lane == 0 && p.aligned && j + kStages < my_count) {
+#ifndef GB_X4
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
+                issue_next();
+            }
+#endif
+            CYC(2);
         }
-        PROF(4); /* the passes */
-        PROF2(7);
 
-        /* ---- 4. arrive at the slice; the last warp hands the slice's result to the publisher ---- */
-        st = __reduce_or_sync(0xffffffffu, (unsigned) st);
-        int last = 0;
-        if (g.lane == 0) {
-            if (st != 0) {
-                atomicOr(&acc->st, st);
+        /* ---- the part is through: one record and the candidate groups go to global scratch ---- */
+        wst = __reduce_or_sync(0xffffffffu, (unsigned) wst);
+        if (lane == 0) {
+            sh->best[warp]   = ((unsigned long long) run_key << 32) | (unsigned long long) (0xffffffffu - (unsigned) run_arg);
+            sh->wn[warp]     = min(wcnt, kGroupCapWarp);
+            sh->wn_all[warp] = wcnt;
+            sh->wb_ref[warp] = b_ref;
+            sh->wb_sum[warp] = b_sum;
+            if (wst != 0) {
+                atomicOr(&sh->st, wst);
             }
-            __threadfence_block(); /* this warp's candidates and sums are ordered before its arrival */
-            last = atomicAdd(&acc->arrived, 1) == kWorkWarps - 1 ? 1 : 0;
         }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        PROF2(8); /* arrive */
-        if (last && g.lane == 0) {
-            sh->slice_done[j % kListRing] = j + 1; /* the publisher takes it from here */
+        __syncthreads();
+        int held = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) {
+            held += sh->wn[w];
         }
-        PROF(5); /* mail */
-        PROF2(9);
-        stage = stage + 1 == p.stages ? 0 : stage + 1;
+        if (tid == 0) {
+            unsigned long long bw    = 0ull;
+            int                n_all = 0;
+            float              bref  = -CUDART_INF_F;
+#pragma unroll
+            for (int w = 0; w < kWarps; w++) {
+                bw = max(bw, sh->best[w]);
+                n_all += sh->wn_all[w];
+                bref = fmaxf(bref, sh->wb_ref[w]);
+            }
+            double bsum = 0.0;
+            if (mode == M_TOPP && sel) {
+#pragma unroll
+                for (int w = 0; w < kWarps; w++) {
+                    const float wr = sh->wb_ref[w];
+                    if (wr != -CUDART_INF_F) {
+                        bsum += sh->wb_sum[w] * exp(((double) wr - (double) bref) * (double) inv_t);
+                    }
+                }
+            }
+            const unsigned pkey = sh->tau_key;
+            int4           h, h2;
+            h.x  = __float_as_int((unsigned) (bw >> 32) == 0u ? -CUDART_INF_F : key_to_float((unsigned) (bw >> 32)));
+            h.y  = (int) (0xffffffffu - (unsigned) (bw & 0xffffffffull));
+            h.z  = held == n_all ? n_all : kPartGroups + 1; /* a warp ran out of room for its groups */
+            h.w  = sh->st;
+            h2.x = __float_as_int(pkey == 0u ? tau_reg : fmaxf(tau_reg, key_to_float(pkey)));
+            h2.y = __float_as_int(bref);
+            h2.z = __double2loint(bsum);
+            h2.w = __double2hiint(bsum);
+            PartRec *rec = p.recs + (size_t) row * (size_t) p.parts_max + part_idx;
+            reinterpret_cast<int4 *>(rec)[0] = h;
+            reinterpret_cast<int4 *>(rec)[1] = h2;
+        }
+        const size_t at = ((size_t) row * (size_t) p.parts_max + (size_t) part_idx) * (size_t) kPartGroups;
+        for (int f = tid; f < held; f += kThreads) {
+            const int slot  = own_slot(sh, f);
+            p.grp_v[at + f] = grp_v[slot];
+            p.grp_b[at + f] = grp_b[slot];
+        }
+        __syncthreads(); /* the lists are free for the next part */
     }
-    PROF_DONE();
-    PROF2_DONE();
-    if (g.lane == 0) {
-        __threadfence_block();
-        if (atomicAdd(&sh->done_warps, 1) == kWorkWarps - 1) {
-            sh->q_done = 1;
-        }
-    }
-    } /* workers */
+}
 
-    /* every role has ended (all of their waits are bounded): what is left are the rows that need the
-     * multi-pass path, shared by all threads */
-    __syncthreads();
-    if (sh->n_slow > 0) {
-        slow_rows(p, sh, ring);
+/* ----------------------------------------------------------- finishing kernel -- */
+
+/*
+ * Runs behind the stream kernel: one thread block finishes one row at a time (rows blockIdx.x, blockIdx.x +
+ * gridDim.x, ...). It merges the records that the row's parts left, orders the few surviving candidates,
+ * evaluates their probabilities exactly, makes the draw, writes the row's status and, behind a sequence's last
+ * row, its generator. Rows whose kept set does not fit serve themselves with the multi-pass path over a private
+ * copy of the row; the copies come from a small pool that the thread blocks claim slots of.
+ */
+__global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_constant__ SampleParams p, int q_items, int r_items) {
+    extern __shared__ __align__(128) unsigned char fsmem[];
+    FinishShared  *sh   = reinterpret_cast<FinishShared *>(fsmem);
+    unsigned char *cmem = reinterpret_cast<unsigned char *>(sh + 1);
+
+    Grp g;
+    g.tid  = (int) threadIdx.x;
+    g.lane = g.tid & 31;
+    g.warp = g.tid >> 5;
+    g.n    = kThreads;
+    g.nw   = kWarps;
+    g.bar  = 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory"); /* the stream kernel's records are complete and visible */
+    asm volatile("griddepcontrol.launch_dependents;");
+    for (int row = (int) blockIdx.x; row < p.n_rows; row += (int) gridDim.x) {
+        /* the first 256 groups of the row's first three parts are asked for together with the row's parameters,
+         * before the parts' counts are known (what lies beyond a part's count is ignored) */
+        float4 sv[3];
+        int    sb[3];
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            sv[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            sb[k] = 0;
+            if (k < p.parts_max) {
+                const size_t at = ((size_t) row * (size_t) p.parts_max + (size_t) k) * (size_t) kPartGroups + (size_t) g.tid;
+                sv[k]           = __ldcg(p.grp_v + at);
+                sb[k]           = __ldcg(p.grp_b + at);
+            }
+        }
+        const RawCfg rc = raw_config(p, row, true);
+        RowCfg       r  = row_config(p, row, rc, true);
+        int          st = finish_row(g, p, sh, r, cmem, q_items, r_items, sv, sb);
+        if (st & ST_DEFERRED) {
+            /* the multi-pass path: all threads of this thread block, over a private copy of the row */
+            __syncthreads();
+            const float bm = sh->gs.blk_max;
+            const int   ba = sh->gs.blk_arg;
+            if (g.tid == 0) {
+                /* claim a row copy: bounded search, the holders always make progress */
+                int got = -1;
+                for (long long t = 0; t < (1ll << 24) && got < 0; t++) {
+                    const int c = (int) ((blockIdx.x + t) % (unsigned) p.pool_slots);
+                    if (atomicCAS(&p.pool[c], 0, 1) == 0) {
+                        got = c;
+                    }
+                }
+                __threadfence();
+                sh->slot = got;
+            }
+            __syncthreads();
+            const int slot = sh->slot;
+            if (slot < 0) {
+                st = (st & ~ST_DEFERRED) | ST_INTERNAL;
+            } else {
+                st = (st & ~ST_DEFERRED) | multipass_row(g, p, &sh->gs, r, bm, ba, cmem, kFinBytes, slot);
+                __syncthreads();
+                if (g.tid == 0) {
+                    __threadfence();
+                    atomicExch(&p.pool[slot], 0);
+                }
+            }
+        }
+        if (g.tid == 0) {
+            row_epilogue(p, r, row, st, rc.rng);
+        }
+        __syncthreads();
     }
 }
 
@@ -2598,10 +2115,10 @@ __global__ void __launch_bounds__(kThreads, 1) sample_stream_kernel(const __grid
 
 constexpr int kRowIdThreads = 256;
 
-/* One CTA per row whose history (plus fed tokens) is longer than the stream kernel's loader keeps
- * in registers: the row's distinct ids with their counts, grouped by the slice they fall into.
+/* One CTA per row whose history (plus fed tokens) is longer than the stream kernel counts
+ * by itself: the row's distinct ids with their counts, grouped by the slice they fall into.
  * pre_off[row][c] .. pre_off[row][c + 1] is slice c's run in pre_list[row]; an entry is
- * (position in the slice) | (count << kLiBits). Shorter rows are left to the loader. */
+ * (position in the slice) | (count << kLiBits). Shorter rows are left to the stream kernel. */
 __global__ void __launch_bounds__(kRowIdThreads) row_ids_kernel(const __grid_constant__ SampleParams p) {
     extern __shared__ __align__(16) int row_ids_smem[];
     int *tkey = row_ids_smem;          /* open-addressing table: the id ... */
@@ -2617,7 +2134,7 @@ __global__ void __launch_bounds__(kRowIdThreads) row_ids_kernel(const __grid_con
     const int seq  = p.slot ? p.slot[seq0] : seq0;
     const int H    = p.hist ? (int) min((long long) max(p.hist_len[seq], 0), p.hist_stride) : 0;
     const int E    = p.extra ? row - seq0 * p.rows_per_seq : 0;
-    if (H + E <= kLoaderIds) {
+    if (H + E <= kRowIds) {
         return;
     }
     const int *hrow = p.hist ? p.hist + (size_t) seq * (size_t) p.hist_stride : nullptr;
@@ -2684,7 +2201,18 @@ __global__ void __launch_bounds__(kRowIdThreads) row_ids_kernel(const __grid_con
 
 /* ----------------------------------------------------------------- launchers -- */
 
-size_t sample_stream_fixed_smem() { return sizeof(StreamShared); }
+#ifdef GB_PROFILE
+extern "C" int geist_b200_debug_prof(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 1024 * 8); }
+extern "C" int geist_b200_debug_cyc(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_cyc, sizeof(long long) * 1024 * kWarps * 8); }
+#endif
+
+size_t sample_stream_smem(int n_slices, int long_ids) {
+    size_t b = (size_t) kWarps * kStages * kWarpStageBytes + sizeof(StreamShared) + (size_t) kGroupBytes;
+    if (long_ids) {
+        b += (((size_t) n_slices + 1) * 4 + 15) & ~(size_t) 15;
+    }
+    return b;
+}
 
 static cudaError_t ensure_attributes(size_t smem_bytes) {
     static int  configured_smem[64] = {0};
@@ -2701,9 +2229,23 @@ static cudaError_t ensure_attributes(size_t smem_bytes) {
         if (e != cudaSuccess) {
             return e;
         }
+        /* two thread blocks per SM need nearly all of its shared memory: ask for the largest carve-out */
+        e = cudaFuncSetAttribute(sample_stream_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int) cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) {
+            return e;
+        }
         configured_smem[dev] = (int) smem_bytes;
     }
     return cudaSuccess;
+}
+
+/* Thread blocks of the stream kernel that one SM of the current device holds at this much shared memory. */
+cudaError_t sample_stream_ctas_per_sm(size_t smem_bytes, int *out) {
+    cudaError_t e = ensure_attributes(smem_bytes);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(out, sample_stream_kernel, kThreads, smem_bytes);
 }
 
 static cudaError_t ensure_row_ids_attributes(size_t smem_bytes) {
@@ -2726,24 +2268,49 @@ static cudaError_t ensure_row_ids_attributes(size_t smem_bytes) {
     return cudaSuccess;
 }
 
-#ifdef GB_PROFILE
-extern "C" int geist_b200_debug_prof3(long long *out, int clear) {
-    if (clear) {
-        static long long zero[256 * 16];
-        return (int) cudaMemcpyToSymbol(g_prof3, zero, sizeof(zero));
-    }
-    return (int) cudaMemcpyFromSymbol(out, g_prof3, sizeof(long long) * 256 * 16);
-}
-extern "C" int geist_b200_debug_prof2(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof2, sizeof(long long) * 256 * 16); }
-extern "C" int geist_b200_debug_prof(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 512 * 8); }
-#endif
+size_t finish_rows_smem() { return sizeof(FinishShared) + (size_t) kFinBytes; }
 
-cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, cudaStream_t stream) {
-    cudaError_t e = ensure_attributes(smem_bytes);
+static cudaError_t ensure_finish_attributes() {
+    static int  configured[64] = {0};
+    int         dev            = 0;
+    cudaError_t e              = cudaGetDevice(&dev);
     if (e != cudaSuccess) {
         return e;
     }
-    if (p.id_slots > 0) { /* rows may bring more ids than the loader keeps in registers: prepare their lists first */
+    if (dev < 0 || dev >= 64) {
+        return cudaErrorInvalidDevice;
+    }
+    if (!configured[dev]) {
+        e = cudaFuncSetAttribute(finish_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) finish_rows_smem());
+        if (e != cudaSuccess) {
+            return e;
+        }
+        configured[dev] = 1;
+    }
+    return cudaSuccess;
+}
+
+/* Thread blocks of the finishing kernel that the current device holds at once. */
+cudaError_t finish_rows_max_ctas(int sms, int *out) {
+    cudaError_t e = ensure_finish_attributes();
+    if (e != cudaSuccess) {
+        return e;
+    }
+    int per_sm = 0;
+    e          = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, finish_rows_kernel, kThreads, finish_rows_smem());
+    *out       = per_sm * sms;
+    return e;
+}
+
+cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, int finish_grid, cudaStream_t stream) {
+    cudaError_t e = ensure_attributes(smem_bytes);
+    if (e == cudaSuccess) {
+        e = ensure_finish_attributes();
+    }
+    if (e != cudaSuccess) {
+        return e;
+    }
+    if (p.id_slots > 0) { /* rows may bring more ids than the stream kernel counts by itself: prepare their lists first */
         const size_t ids_smem = ((size_t) p.id_slots * 2 + (size_t) p.bucket_cap * 2) * sizeof(int);
         e                     = ensure_row_ids_attributes(ids_smem);
         if (e != cudaSuccess) {
@@ -2754,49 +2321,29 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
         if (e != cudaSuccess) {
             return e;
         }
-#ifndef GB_COOP
-        /* programmatic dependent launch: the stream kernel's thread blocks start as soon as that kernel
-         * lets them, and its loader waits for the lists (griddepcontrol.wait) before it reads one.
-         * Worth it for small batches, where start-up is a good part of the launch (64 rows: 27.0 -> 23.3 us);
-         * with several waves of list blocks the early start only gets in their way (4096 rows: +4 %). */
-        if (p.n_rows > 4 * grid) {
-            sample_stream_kernel<<<dim3((unsigned) grid), dim3(kThreads), smem_bytes, stream>>>(p);
-            return cudaGetLastError();
-        }
-        cudaLaunchConfig_t   cfg{};
-        cudaLaunchAttribute attr[1];
-        cfg.gridDim          = dim3((unsigned) grid);
-        cfg.blockDim         = dim3(kThreads);
-        cfg.dynamicSmemBytes = smem_bytes;
-        cfg.stream           = stream;
-        attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs                                          = attr;
-        cfg.numAttrs                                       = 1;
-        return cudaLaunchKernelEx(&cfg, sample_stream_kernel, p);
-#endif
     }
-    /* no CTA ever waits for another one, so the grid needs no co-residency */
-#ifdef GB_COOP
-    void *args[] = {const_cast<SampleParams *>(&p)};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(sample_stream_kernel), dim3((unsigned) grid), dim3(kThreads), args, smem_bytes, stream);
-#else
-    {
-        SampleParams        pc = p;
-        cudaLaunchConfig_t  cfg{};
-        cudaLaunchAttribute attr[1];
-        pc.chained           = 1;
-        cfg.gridDim          = dim3((unsigned) grid);
-        cfg.blockDim         = dim3(kThreads);
-        cfg.dynamicSmemBytes = smem_bytes;
-        cfg.stream           = stream;
-        attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs                                          = attr;
-        cfg.numAttrs                                       = 1;
-        return cudaLaunchKernelEx(&cfg, sample_stream_kernel, pc);
+    /* Programmatic dependent launch, both kernels: the thread blocks are placed while the kernel before them
+     * in the stream drains, and wait (griddepcontrol.wait) until that kernel is complete and visible before they
+     * touch global memory. No thread block ever waits for another one of its grid, so neither grid needs
+     * co-residency. */
+    cudaLaunchConfig_t  cfg{};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim          = dim3((unsigned) grid);
+    cfg.blockDim         = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream           = stream;
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs                                          = attr;
+    cfg.numAttrs                                       = 1;
+    e = cudaLaunchKernelEx(&cfg, sample_stream_kernel, p);
+    if (e != cudaSuccess) {
+        return e;
     }
-#endif
+    const int n_items = p.n_rows * p.n_slices;
+    cfg.gridDim          = dim3((unsigned) finish_grid);
+    cfg.dynamicSmemBytes = finish_rows_smem();
+    return cudaLaunchKernelEx(&cfg, finish_rows_kernel, p, n_items / grid, n_items % grid);
 }
 
 } /* namespace gb */

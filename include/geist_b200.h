@@ -310,6 +310,11 @@ enum geist_status geist_b200_batcher_verify(struct geist_b200_batcher *b, size_t
 enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history, int32_t *slices_per_row, int32_t *slice,
                                   int32_t *smem_bytes, int32_t *ring_stages);
 
+/* How one launch over n_rows rows of this vocabulary is spread over the current device: the number of thread
+ * blocks (each takes a contiguous run of (row, slice) items) and how many of them one SM holds at a time. */
+enum geist_status geist_b200_grid(size_t n_vocab, size_t max_history, size_t n_rows, int32_t *thread_blocks,
+                                  int32_t *blocks_per_sm);
+
 /* Greedy argmax of n_rows rows [n_rows, n_vocab] (device memory, row_stride floats apart)
  * into out_index [n_rows] (device memory), ties -> lowest index, WITHOUT allocating: no
  * context, no cudaMalloc, no growth on larger batches. No counterpart in the reference; it
