@@ -23,7 +23,7 @@ namespace gb {
 size_t      sample_stream_smem(int n_slices, int long_ids);
 cudaError_t sample_stream_ctas_per_sm(size_t smem_bytes, int *out);
 cudaError_t finish_rows_max_ctas(int sms, int *out);
-cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, int finish_grid, cudaStream_t stream);
+cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, int finish_grid, bool second_finisher, cudaStream_t stream);
 cudaError_t launch_merge_sample(const MergeParams &p, cudaStream_t stream);
 cudaError_t launch_accept(const AcceptParams &p, cudaStream_t stream);
 cudaError_t launch_scatter_kept(const int *kept_n, const int *kept_idx, const float *kept_val, int kept_cap, int n_rows, int V, int vocab_offset, float *dense, cudaStream_t stream);
@@ -338,10 +338,9 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     const size_t gen_str  = round_up(b->n_vocab, 4);
     const size_t gen_bmw  = (b->n_vocab + 31) / 32;
     const size_t gen_hcap = hist_max ? std::min(hist_max, b->n_vocab) : 0;
-    const size_t off_recs = 0;
-    const size_t off_gv   = round_up(off_recs + n_rows * parts * sizeof(gb::PartRec), 256);
-    const size_t off_gb   = round_up(off_gv + n_rows * parts * (size_t) gb::kPartGroups * 16, 256);
-    const size_t off_seg  = round_up(off_gb + n_rows * parts * (size_t) gb::kPartGroups * 4, 256);
+    const size_t off_gv   = 0;
+    const size_t off_gb   = round_up(off_gv + n_rows * parts * (size_t) gb::kPartSlots * 16, 256);
+    const size_t off_seg  = round_up(off_gb + n_rows * parts * (size_t) gb::kPartSlots * 4, 256);
     const int    fin_grid = (int) std::min<size_t>((size_t) pl.fin_ctas, n_rows);
     const size_t slots    = (size_t) fin_grid; /* row copies of the multi-pass path: one per finishing thread block that can run at a time */
     const size_t off_rows = round_up(off_seg + n_items * (size_t) gb::kWarps * sizeof(gb::SegRec), 256);
@@ -349,7 +348,8 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     const size_t off_dl   = round_up(off_bm + slots * gen_bmw * 4, 256);
     const size_t off_pl   = round_up(off_dl + slots * gen_hcap * sizeof(gb::Pair), 256);
     const size_t off_po   = round_up(off_pl + (pl.id_slots ? n_rows * (size_t) pl.row_cap * 4 : 0), 256);
-    const size_t need     = round_up(off_po + (pl.id_slots ? n_rows * (size_t) (pl.n_slices + 1) * 4 : 0), 256);
+    const size_t off_def  = round_up(off_po + (pl.id_slots ? n_rows * (size_t) (pl.n_slices + 1) * 4 : 0), 256);
+    const size_t need     = round_up(off_def + (n_rows + 4) * 4, 256);
     geist_b200_ctx::Lane *ln;
     {
         std::lock_guard<std::mutex> lk(ctx->lane_mu);
@@ -373,9 +373,10 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
             ln->counter_cap = cap;
         }
     }
+    p.def_count        = reinterpret_cast<int *>(ln->buf + off_def);
+    p.def_rows         = p.def_count + 4;
     p.pool             = ln->counters;
     p.pool_slots       = (int) slots;
-    p.recs             = reinterpret_cast<gb::PartRec *>(ln->buf + off_recs);
     p.grp_v            = reinterpret_cast<float4 *>(ln->buf + off_gv);
     p.grp_b            = reinterpret_cast<int *>(ln->buf + off_gb);
     p.segs             = reinterpret_cast<gb::SegRec *>(ln->buf + off_seg);
@@ -387,7 +388,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.gen_hist_cap     = (int) gen_hcap;
     p.pre_list         = reinterpret_cast<unsigned *>(ln->buf + off_pl);
     p.pre_off          = reinterpret_cast<int *>(ln->buf + off_po);
-    CUDA_TRY(gb::launch_sample_stream(p, grid, pl.smem, fin_grid, st));
+    CUDA_TRY(gb::launch_sample_stream(p, grid, pl.smem, fin_grid, true, st));
     return GEIST_OK;
 }
 

@@ -73,6 +73,9 @@ __attribute__((weak)) void geist_backend_set_error(struct geist_backend *be, enu
     pthread_mutex_unlock(&be->err_mu);
 }
 
+/* Likewise the engine's shared all-null table (include/geist_backend.h:613-617). */
+__attribute__((weak)) const struct geist_backend_fused geist_backend_no_fused = {0};
+
 /* ---- the two slot functions ---- */
 
 /* include/geist_backend.h:326: the load-time probe. Only ARGMAX_F32 is answered with yes, for the decode

@@ -27,6 +27,7 @@ constexpr int kFinBitmapWords = 32;           /* finisher: one bit per entry of 
 constexpr int kHistBins     = 256;            /* value histograms (threshold, select) */
 constexpr int kGroupCapWarp = 160;            /* candidate groups (one float4 each) a warp can hold of one row part */
 constexpr int kPartGroups   = kWarps * kGroupCapWarp; /* ... and a whole thread block: 1280 */
+constexpr int kPartSlots    = kPartGroups + 2;        /* a part in global scratch: its record in the first two 16-byte slots, then its groups */
 constexpr int kRowIds       = 256;            /* ids of a row (history + fed tokens) counted inside the stream kernel, one per thread */
 
 /* status word, one per row (bit set) */
@@ -116,10 +117,11 @@ struct SampleParams {
     unsigned flags;
 
     /* scratch in global memory (one lane of the context's scratch) */
+    int       *def_count;   /* rows the first finishing kernel left to the second one ... */
+    int       *def_rows;    /* [n_rows] ... and which */
     int       *pool;        /* [pool_slots] 1: the row copy of this number is taken; zero between launches */
     int        pool_slots;
-    PartRec   *recs;        /* [n_rows, parts_max] */
-    float4    *grp_v;       /* [n_rows, parts_max, kPartGroups] candidate groups: four consecutive values ... */
+    float4    *grp_v;       /* [n_rows, parts_max, kPartSlots] per part: its PartRec (two slots), then its candidate groups: four consecutive values ... */
     int       *grp_b;       /* ... and the global id of the first */
     SegRec    *segs;        /* [n_rows, n_slices, kWarps] temperature rows */
     float     *gen_rows;    /* [pool_slots, gen_stride]: private copies of one row for the multi-pass path */

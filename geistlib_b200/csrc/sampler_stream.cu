@@ -40,6 +40,52 @@
 
 namespace gb {
 
+/* Optional time line of every thread block (build with -DGB_PROFILE): %globaltimer at five points of its life. */
+#ifdef GB_PROFILE
+__device__ long long g_prof[1024][16];
+__device__ __forceinline__ long long gtime() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define PROF(i)                                        \
+    if (threadIdx.x == 0 && blockIdx.x < 1024) {       \
+        g_prof[blockIdx.x][i] = gtime();               \
+    }
+#define PROF_ONCE(i)                                                       \
+    if (threadIdx.x == 0 && blockIdx.x < 1024 && g_prof[blockIdx.x][i] == 0) { \
+        g_prof[blockIdx.x][i] = gtime();                                   \
+    }
+#ifdef GB_PROFILE_CYC
+__device__ long long g_cyc[1024][kWarps][8];
+#define CYC_INIT()              \
+    long long cyc_acc[8] = {0}; \
+    long long cyc_t      = clock64()
+#define CYC(i)                          \
+    {                                   \
+        const long long t_ = clock64(); \
+        cyc_acc[i] += t_ - cyc_t;       \
+        cyc_t = t_;                     \
+    }
+#define CYC_DONE()                                                  \
+    if ((threadIdx.x & 31) == 0 && blockIdx.x < 1024) {             \
+        for (int i_ = 0; i_ < 8; i_++) {                            \
+            g_cyc[blockIdx.x][threadIdx.x >> 5][i_] = cyc_acc[i_];  \
+        }                                                           \
+    }
+#else
+#define CYC_INIT()
+#define CYC(i)
+#define CYC_DONE()
+#endif
+#else
+#define PROF(i)
+#define PROF_ONCE(i)
+#define CYC_INIT()
+#define CYC(i)
+#define CYC_DONE()
+#endif
+
 struct PenEntry {
     int   li;
     float orig;
@@ -815,6 +861,8 @@ struct __align__(16) StreamShared {
     int                nxt_ext[kRowIds]; /* ... and the tokens fed before it */
 };
 
+constexpr int kStagedParts = 4;
+
 /* What the threads of one finishing thread block share; the merged candidate list lies behind it. */
 struct __align__(16) FinishShared {
     GroupShared gs; /* reductions of the whole thread block */
@@ -827,11 +875,14 @@ struct __align__(16) FinishShared {
     Pair        fsort[kFastKMax];
     float       fq[kFastKMax];
     PenEntry    fdlist[512];
+    float4      st_v[kStagedParts][kThreads]; /* the first 256 slots of the row's first parts, as they came in ... */
+    int         st_b[kStagedParts][kThreads]; /* ... in one round trip */
 };
 
 constexpr int kGroupBytes = kPartGroups * 20; /* float4 + first id per group */
 constexpr int kFinCap     = 2048;             /* candidates the finisher can order per row (8 per thread) */
 constexpr int kFinPer     = kFinCap / kThreads;
+constexpr int kRankAll    = 384;              /* up to this many candidates are ranked one against all */
 constexpr int kFinBytes   = kWarps * 256 * 12;    /* finisher: the merged candidate list; the multi-pass path keeps one byte histogram per warp there */
 static_assert(kFinCap * (int) sizeof(Pair) <= kFinBytes, "the merged list fits");
 static_assert(kGroupBytes >= 4 * kRowIds * 4, "the id table of a part's set-up lies in the groups' memory");
@@ -984,8 +1035,8 @@ __device__ void select_sorted(const Grp &g, FinishShared *sh, Pair *cand, int to
  * (segment sums, then the crossing segment re-read and walked); top-k / top-p over the merged candidates. cmem:
  * room for the merged list. Returns the row's status bits (ST_DEFERRED: the multi-pass path has to serve it).
  */
-__device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, FinishShared *sh, RowCfg &r, unsigned char *cmem, int q_items, int r_items, const float4 (&sv)[3], const int (&sb)[3]) {
-    constexpr int kSpec = 3;
+template <bool kFast>
+__device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, FinishShared *sh, RowCfg &r, unsigned char *cmem, int q_items, int r_items) {
     const int  row     = r.row;
     int       *kept_i  = p.kept_cap > 0 ? p.kept_idx + (size_t) row * (size_t) p.kept_cap : nullptr;
     float     *kept_v  = p.kept_cap > 0 ? p.kept_val + (size_t) row * (size_t) p.kept_cap : nullptr;
@@ -996,6 +1047,27 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
     const int  n_parts = b_last - b_first + 1;
     int        st      = 0;
 
+    g.sync(); /* the staging of the row before is no longer read */
+    {
+        /* one round trip: the first 256 slots (record + 254 groups) of up to four parts, whatever their counts are */
+        float4 tv[kStagedParts];
+        int    tb[kStagedParts];
+#pragma unroll
+        for (int k = 0; k < kStagedParts; k++) {
+            tv[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            tb[k] = 0;
+            if (k < n_parts) {
+                const size_t at = ((size_t) row * (size_t) p.parts_max + (size_t) k) * (size_t) kPartSlots + (size_t) g.tid;
+                tv[k]           = __ldcg(p.grp_v + at);
+                tb[k]           = __ldcg(p.grp_b + at);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kStagedParts; k++) {
+            sh->st_v[k][g.tid] = tv[k];
+            sh->st_b[k][g.tid] = tb[k];
+        }
+    }
     g.sync();
     if (n_parts > kMaxParts) {
         /* a row spread over that many thread blocks (a handful of rows on the whole chip): its maximum is
@@ -1003,7 +1075,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
         float m = -CUDART_INF_F;
         int   a = 0x7fffffff;
         for (int i = g.tid; i < n_parts; i += g.n) {
-            const int4  h  = __ldcg(reinterpret_cast<const int4 *>(p.recs + (size_t) row * (size_t) p.parts_max + i));
+            const int4  h  = __ldcg(reinterpret_cast<const int4 *>(p.grp_v + ((size_t) row * (size_t) p.parts_max + (size_t) i) * (size_t) kPartSlots));
             const float pm = __int_as_float(h.x);
             st |= h.w;
             if (a == 0x7fffffff || pair_before(pm, h.y, m, a)) {
@@ -1036,15 +1108,21 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
         return st | ST_DEFERRED;
     }
     if (g.tid < n_parts) {
-        const PartRec *rec = p.recs + (size_t) row * (size_t) p.parts_max + g.tid;
-        const int4     h   = __ldcg(reinterpret_cast<const int4 *>(rec));
-        const int4     h2  = __ldcg(reinterpret_cast<const int4 *>(rec) + 1);
-        sh->pmax[g.tid]    = __int_as_float(h.x);
-        sh->parg[g.tid]    = h.y;
-        sh->pn[g.tid]      = h.z;
-        sh->ptau[g.tid]    = __int_as_float(h2.x);
-        sh->pbref[g.tid]   = __int_as_float(h2.y);
-        sh->pbsum[g.tid]   = __hiloint2double(h2.w, h2.z);
+        int4 h, h2;
+        if (g.tid < kStagedParts) { /* the record came in with the part's first slots */
+            h  = *reinterpret_cast<const int4 *>(&sh->st_v[g.tid][0]);
+            h2 = *reinterpret_cast<const int4 *>(&sh->st_v[g.tid][1]);
+        } else {
+            const int4 *rec = reinterpret_cast<const int4 *>(p.grp_v + ((size_t) row * (size_t) p.parts_max + (size_t) g.tid) * (size_t) kPartSlots);
+            h               = __ldcg(rec);
+            h2              = __ldcg(rec + 1);
+        }
+        sh->pmax[g.tid]  = __int_as_float(h.x);
+        sh->parg[g.tid]  = h.y;
+        sh->pn[g.tid]    = h.z;
+        sh->ptau[g.tid]  = __int_as_float(h2.x);
+        sh->pbref[g.tid] = __int_as_float(h2.y);
+        sh->pbsum[g.tid] = __hiloint2double(h2.w, h2.z);
         st |= h.w;
     }
     st = __reduce_or_sync(0xffffffffu, st);
@@ -1052,6 +1130,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
         gs->wred_a[g.warp] = st;
     }
     g.sync();
+    PROF(9);
     for (int w = 0; w < g.nw; w++) {
         st |= gs->wred_a[w];
     }
@@ -1084,6 +1163,10 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
         return st;
     }
 
+    if (kFast && r.mode != M_TOPK) {
+        return st | ST_DEFERRED; /* temperature and top-p rows are finished by the kernel behind this one */
+    }
+    if constexpr (!kFast) {
     if (r.mode == M_TEMP) {
         /* segment sums (one per warp and slice, ids in order), moved from their own maximum to the row maximum */
         const int     nseg   = p.n_slices * kWarps;
@@ -1237,6 +1320,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
         return st;
     }
 
+    }
     /* ---- top-k and top-p: merge the parts' candidate groups ---- */
     const int n_groups       = others;
     bool      need_multipass = !(r.kq > 0 && r.kq <= kFastKMax) || overflow || n_groups > 2 * kFinCap;
@@ -1245,45 +1329,94 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
             sh->n_ent = 0;
         }
         g.sync();
-        const bool  keep_all = r.mode == M_TOPP; /* every marked entry was left out of the bulk sums */
-        auto        place    = [&](float v, int idx) {
-            if (idx < p.V && (keep_all || v >= tau_row)) {
-                const int pos = atomicAdd(&sh->n_ent, 1);
-                if (pos < kFinCap) {
-                    cbuf[pos].v   = v;
-                    cbuf[pos].idx = idx;
+        const bool keep_all = r.mode == M_TOPP; /* every marked entry was left out of the bulk sums */
+        /* A group is four consecutive values, the id of the first and, in the id's top four bits, which of them
+         * passed. The whole warp calls: the entries that stay are counted over the warp and get their places
+         * with one atomic per warp. */
+        auto place_group = [&](bool valid, const float4 &v, int raw) {
+            const int      b  = raw & 0x0fffffff;
+            const unsigned cm = valid ? (unsigned) raw >> 28 : 0u;
+            const bool     k0 = (cm & 1u) && b < p.V && (keep_all || v.x >= tau_row);
+            const bool     k1 = (cm & 2u) && b + 1 < p.V && (keep_all || v.y >= tau_row);
+            const bool     k2 = (cm & 4u) && b + 2 < p.V && (keep_all || v.z >= tau_row);
+            const bool     k3 = (cm & 8u) && b + 3 < p.V && (keep_all || v.w >= tau_row);
+            const int      cnt = (int) k0 + (int) k1 + (int) k2 + (int) k3;
+            if (__ballot_sync(0xffffffffu, cnt > 0) == 0u) {
+                return;
+            }
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (g.lane >= o) {
+                    incl += up;
                 }
             }
-        };
-        /* a group is four consecutive values, the id of the first and, in the id's top four bits, which of them passed */
-        auto place_group = [&](const float4 &v, int raw) {
-            const int      b  = raw & 0x0fffffff;
-            const unsigned cm = (unsigned) raw >> 28;
-            if (cm & 1u) place(v.x, b);
-            if (cm & 2u) place(v.y, b + 1);
-            if (cm & 4u) place(v.z, b + 2);
-            if (cm & 8u) place(v.w, b + 3);
-        };
-#pragma unroll
-        for (int k = 0; k < kSpec; k++) { /* what was asked for before the counts were known */
-            if (k < n_parts && g.tid < sh->pn[k]) {
-                place_group(sv[k], sb[k]);
+            int base = 0;
+            if (g.lane == 31) {
+                base = atomicAdd(&sh->n_ent, incl);
             }
-        }
-        for (int pi = 0; pi < n_parts; pi++) { /* and the rest */
-            const size_t base = ((size_t) row * (size_t) p.parts_max + (size_t) pi) * (size_t) kPartGroups;
-            for (int f = g.tid + (pi < kSpec ? kThreads : 0); f < sh->pn[pi]; f += g.n) {
-                place_group(__ldcg(p.grp_v + base + f), __ldcg(p.grp_b + base + f));
+            base    = __shfl_sync(0xffffffffu, base, 31);
+            int pos = base + incl - cnt;
+            if (k0) { if (pos < kFinCap) { cbuf[pos].v = v.x; cbuf[pos].idx = b; } pos++; }
+            if (k1) { if (pos < kFinCap) { cbuf[pos].v = v.y; cbuf[pos].idx = b + 1; } pos++; }
+            if (k2) { if (pos < kFinCap) { cbuf[pos].v = v.z; cbuf[pos].idx = b + 2; } pos++; }
+            if (k3) { if (pos < kFinCap) { cbuf[pos].v = v.w; cbuf[pos].idx = b + 3; } pos++; }
+        };
+        /* one loop over the groups of all parts (rolled: code that runs once per row costs what it weighs) */
+#pragma unroll 1
+        for (int f0 = 0; f0 < others; f0 += g.n) {
+            const int  f  = f0 + g.tid;
+            const bool ok = f < others;
+            int        pi = 0;
+            for (int q = 1; q < n_parts; q++) {
+                if (f >= sh->poff[q]) {
+                    pi = q; /* offsets ascend */
+                }
             }
+            const int slot = f - sh->poff[pi] + 2; /* behind the part's record */
+            float4    v    = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            int       b    = 0;
+            if (ok) {
+                if (pi < kStagedParts && slot < kThreads) {
+                    v = sh->st_v[pi][slot];
+                    b = sh->st_b[pi][slot];
+                } else {
+                    const size_t at = ((size_t) row * (size_t) p.parts_max + (size_t) pi) * (size_t) kPartSlots + (size_t) slot;
+                    v               = __ldcg(p.grp_v + at);
+                    b               = __ldcg(p.grp_b + at);
+                }
+            }
+            place_group(ok, v, b);
         }
         g.sync();
+        PROF(10);
         const int total = sh->n_ent;
         if (total > kFinCap || total < r.kq) {
             need_multipass = true;
         }
         if (!need_multipass && r.mode == M_TOPK) {
             const int k = r.k;
-            select_sorted(g, sh, cbuf, total, k, sh->fsort);
+            if (total <= kRankAll) {
+                /* few candidates: every entry is ranked against all others (a short loop that stays in the
+                 * instruction cache, instead of the histogram select's long straight-line code) */
+#pragma unroll 1
+                for (int i = g.tid; i < total; i += g.n) {
+                    const Pair me   = cbuf[i];
+                    int        rank = 0;
+#pragma unroll 4
+                    for (int j = 0; j < total; j++) {
+                        rank += pair_before(cbuf[j].v, cbuf[j].idx, me.v, me.idx) ? 1 : 0;
+                    }
+                    if (rank < k) {
+                        sh->fsort[rank] = me;
+                    }
+                }
+                g.sync();
+            } else {
+                select_sorted(g, sh, cbuf, total, k, sh->fsort);
+            }
+            PROF(11);
             if (r.select_only) {
                 for (int i = g.tid; i < min(k, p.kept_cap); i += g.n) {
                     kept_i[i] = sh->fsort[i].idx + p.vocab_offset;
@@ -1302,7 +1435,32 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
                 sh->fq[i] = exp_exact(scaled_arg(sh->fsort[i].v, m, r.inv_t));
             }
             g.sync();
-            if (g.warp == 0) {
+            PROF(12);
+            if (k <= 64) {
+                if (g.tid == 0) { /* sampler.c:90-102 as it stands: two short loops by one thread */
+                    double S = 0.0;
+#pragma unroll 1
+                    for (int i = 0; i < k; i++) {
+                        S += (double) sh->fq[i];
+                    }
+                    const double u    = (double) unit_from(xorshift_next(r.rng)) * S;
+                    double       a    = 0.0;
+                    int          pick = k - 1;
+#pragma unroll 1
+                    for (int i = 0; i < k; i++) {
+                        a += (double) sh->fq[i];
+                        if (u < a) {
+                            pick = i;
+                            break;
+                        }
+                    }
+                    p.tokens[row] = sh->fsort[pick].idx + p.vocab_offset;
+                    gs->S         = S;
+                    if (p.kept_cap > 0) {
+                        p.kept_n[row] = k;
+                    }
+                }
+            } else if (g.warp == 0) {
                 double    S;
                 const int pick = warp_inverse_cdf(g.lane, sh->fq, k, unit_from(xorshift_next(r.rng)), &S);
                 if (g.lane == 0) {
@@ -1324,6 +1482,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
             g.sync();
             return st;
         }
+        if constexpr (!kFast) {
         if (!need_multipass) {
             /* top-p over a small nucleus (sampler.c:245-300). Candidates get their exact e_i relative to the row
              * maximum; the rest of the row was summed per part with expf relative to a maximum of its own and is
@@ -1395,6 +1554,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
                 return st;
             }
         }
+        }
     }
     g.sync();
     if (g.tid == 0) {
@@ -1406,46 +1566,6 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
 }
 
 /* ------------------------------------------------------------------ kernel -- */
-
-/* Optional time line of every thread block (build with -DGB_PROFILE): %globaltimer at five points of its life. */
-#ifdef GB_PROFILE
-__device__ long long g_prof[1024][8];
-__device__ __forceinline__ long long gtime() {
-    long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define PROF(i)                                        \
-    if (threadIdx.x == 0 && blockIdx.x < 1024) {       \
-        g_prof[blockIdx.x][i] = gtime();               \
-    }
-#define PROF_ONCE(i)                                                       \
-    if (threadIdx.x == 0 && blockIdx.x < 1024 && g_prof[blockIdx.x][i] == 0) { \
-        g_prof[blockIdx.x][i] = gtime();                                   \
-    }
-__device__ long long g_cyc[1024][kWarps][8];
-#define CYC_INIT()              \
-    long long cyc_acc[8] = {0}; \
-    long long cyc_t      = clock64()
-#define CYC(i)                          \
-    {                                   \
-        const long long t_ = clock64(); \
-        cyc_acc[i] += t_ - cyc_t;       \
-        cyc_t = t_;                     \
-    }
-#define CYC_DONE()                                                  \
-    if ((threadIdx.x & 31) == 0 && blockIdx.x < 1024) {             \
-        for (int i_ = 0; i_ < 8; i_++) {                            \
-            g_cyc[blockIdx.x][threadIdx.x >> 5][i_] = cyc_acc[i_];  \
-        }                                                           \
-    }
-#else
-#define PROF(i)
-#define PROF_ONCE(i)
-#define CYC_INIT()
-#define CYC(i)
-#define CYC_DONE()
-#endif
 
 /* How many ids (history + tokens fed before this row) a row brings. */
 __device__ __forceinline__ int row_id_count(const SampleParams &p, int hist_len, int row) {
@@ -1551,31 +1671,47 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
     asm volatile("griddepcontrol.launch_dependents;");
 #ifdef GB_PROFILE
     if (tid == 0 && blockIdx.x < 1024) {
-        for (int i = 1; i < 8; i++) {
+        for (int i = 1; i < 16; i++) {
             g_prof[blockIdx.x][i] = 0;
         }
     }
 #endif
     PROF(0);
+    if (blockIdx.x == 0 && tid == 0) {
+        p.def_count[0] = 0; /* the list of rows left to the second finishing kernel starts empty */
+    }
 
     /* ---- the warp's own ring: lane 0 asks for the warp's share of the item kStages ahead ---- */
     unsigned char *wring = ring + (size_t) warp * kStages * kWarpStageBytes;
-    int irow = my_first / p.n_slices, ic = my_first - irow * p.n_slices, ijj = 0; /* the next item to request */
+    /* a row's slices have one of two shapes: the full one and the row's last one; what the warp owns of each */
+    const int n_full = min(p.slice, p.V), n_last = p.V - (p.n_slices - 1) * p.slice;
+    int       w4lo_f, mine4_f, w4lo_l, mine4_l;
+    {
+        const int nv4f = (n_full + 3) >> 2, Lf = share_len(nv4f);
+        w4lo_f         = min(warp * Lf, nv4f);
+        mine4_f        = min(Lf, nv4f - w4lo_f);
+        const int nv4l = (n_last + 3) >> 2, Ll = share_len(nv4l);
+        w4lo_l         = min(warp * Ll, nv4l);
+        mine4_l        = min(Ll, nv4l - w4lo_l);
+    }
+    const int    bulk4_f = max(0, min(mine4_f, (n_full >> 2) - w4lo_f)); /* float4 of the share that a bulk copy brings */
+    const int    bulk4_l = max(0, min(mine4_l, (n_last >> 2) - w4lo_l));
+    int          irow = my_first / p.n_slices, ic = my_first - irow * p.n_slices, ijj = 0; /* the next item to request */
+    const float *isrc = p.logits + (size_t) irow * (size_t) p.row_stride + (size_t) ic * (size_t) p.slice; /* ... and where its slice starts */
     auto issue_next = [&]() {
-        const int s0 = ic * p.slice, n = min(p.slice, p.V - s0);
-        const int nv4 = (n + 3) >> 2, nfull = n >> 2;
-        const int L = share_len(nv4), w4lo = min(warp * L, nv4), mine4 = min(L, nv4 - w4lo);
-        const int full4 = max(0, min(mine4, nfull - w4lo));
-        const int stage = ijj % kStages;
-        if (full4 > 0) {
-            mbar_expect_tx(&sh->full[warp][stage], (unsigned) full4 * 16u);
-            bulk_g2s(wring + (size_t) stage * kWarpStageBytes, p.logits + (size_t) irow * (size_t) p.row_stride + s0 + 4 * w4lo, (unsigned) full4 * 16u, &sh->full[warp][stage]);
+        const bool last  = ic == p.n_slices - 1;
+        const int  b4    = last ? bulk4_l : bulk4_f;
+        const int  stage = ijj % kStages;
+        if (b4 > 0) {
+            mbar_expect_tx(&sh->full[warp][stage], (unsigned) b4 * 16u);
+            bulk_g2s(wring + (size_t) stage * kWarpStageBytes, isrc + 4 * (last ? w4lo_l : w4lo_f), (unsigned) b4 * 16u, &sh->full[warp][stage]);
         }
         ijj++;
         ic++;
-        if (ic == p.n_slices) {
+        isrc += p.slice;
+        if (last) {
             ic = 0;
-            irow++;
+            isrc += p.row_stride - (long long) p.n_slices * p.slice; /* on to the next row */
         }
     };
     if (lane == 0 && p.aligned) {
@@ -1591,7 +1727,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
         const int  item0 = my_first + j, row = item0 / p.n_slices, c0 = item0 - row * p.n_slices;
         const int  part_len   = min(p.n_slices - c0, my_count - j);
         const bool final_part = j + part_len == my_count;
-        CYC(7);
+        CYC(6);
         if (warp == 0) { /* what has not been fetched while the previous part streamed (first part, short parts) */
             while (pf < kPrefetchDone) {
                 prefetch_step(p, sh, row, lane, pf);
@@ -1700,27 +1836,30 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
         for (int s = 0; s < part_len; s++, j++) {
             const int      stage  = j % kStages;
             const unsigned parity = (unsigned) (j / kStages) & 1u;
-            const int      c = c0 + s, s0 = c * p.slice, n = min(p.slice, p.V - s0);
-            const int      nv4 = (n + 3) >> 2, body = n & ~3;
-            const int      L = share_len(nv4), w4lo = min(warp * L, nv4), mine4 = min(L, nv4 - w4lo);
+            const int      c      = c0 + s, s0 = c * p.slice;
+            const bool     last_c = c == p.n_slices - 1;
+            const int      n = last_c ? n_last : n_full, nv4 = (n + 3) >> 2, body = n & ~3;
+            const int      w4lo = last_c ? w4lo_l : w4lo_f, mine4 = last_c ? mine4_l : mine4_f;
             float         *sl   = reinterpret_cast<float *>(wring + (size_t) stage * kWarpStageBytes); /* local index = slice index - 4 * w4lo */
             const float   *grow = p.logits + (size_t) row * (size_t) p.row_stride + s0;
-#ifndef GB_X1
+            bool           wrote = !p.aligned; /* the warp wrote into its stage with ordinary stores */
             if (warp == 0 && !final_part && pf < kPrefetchDone) {
                 prefetch_step(p, sh, row + 1, lane, pf); /* one step per slice: the step before has long arrived */
             }
-#endif
             CYC(4);
             /* ---- 1. the warp's share of the slice is in its stage; the slice's tail is padded with -inf ---- */
             if (p.aligned) {
-                const int full4 = max(0, min(mine4, (n >> 2) - w4lo));
+                const int full4 = last_c ? bulk4_l : bulk4_f;
                 if (full4 > 0 && !mbar_wait_bounded(&sh->full[warp][stage], parity)) {
                     wst |= ST_LOAD_TIMEOUT;
                     (void) mbar_wait_bounded(&sh->full[warp][stage], parity); /* a second bounded chance for the copy in flight */
                 }
-                if (nv4 * 4 > body && w4lo + mine4 == nv4 && mine4 > 0 && lane < 4) {
-                    const int i       = body + lane; /* the last float4 is not part of the bulk copy */
-                    sl[i - 4 * w4lo]  = i < n ? grow[i] : -CUDART_INF_F;
+                if (nv4 * 4 > body && w4lo + mine4 == nv4 && mine4 > 0) {
+                    wrote = true;
+                    if (lane < 4) {
+                        const int i      = body + lane; /* the last float4 is not part of the bulk copy */
+                        sl[i - 4 * w4lo] = i < n ? grow[i] : -CUDART_INF_F;
+                    }
                 }
             } else {
                 /* rows off the 16-byte grid: plain loads into the warp's own stage */
@@ -1734,6 +1873,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
 
             /* ---- 2. penalties on the share ---- */
             if (pen_on) {
+                wrote = true;
                 if (!long_ids) {
                     const int rn = sh->rl_n;
                     for (int e = lane; e < rn; e += 32) {
@@ -1774,16 +1914,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                 bv    = fmaxf(bv, gm[i]);
             }
             CYC(1);
-#ifndef GB_X2
-            /* the stage is free again: the warp refills it itself */
-            __syncwarp();
-            if (lane == 0 && p.aligned && j + kStages < my_count) {
-#ifndef GB_X4
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
-                issue_next();
-            }
-#endif
             CYC(3);
             const unsigned bkey = order_key(bv + 0.0f); /* -0 and +0 are one value, as the comparison of floats has it */
             const bool     own  = lane < mine4;
@@ -1861,8 +1991,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                                     atomicAdd(&sh->bhist[(max(order_key(gm[i] + 0.0f), klo2) - klo2) >> shift], 1);
                                 }
                             }
-                        } else if (own) {
-                            atomicAdd(&sh->bhist[(max(bkey, klo2) - klo2) >> shift], 1);
+                        } else {
+                            /* most thread maxima fall into a few low bins: the lanes of a warp that share a bin
+                             * add once for all of them */
+                            const int      bin   = own ? (int) ((max(bkey, klo2) - klo2) >> shift) : -1;
+                            const unsigned peers = __match_any_sync(0xffffffffu, bin);
+                            if (own && lane == __ffs(peers) - 1) {
+                                atomicAdd(&sh->bhist[bin], __popc(peers));
+                            }
                         }
                     }
                     __syncthreads();
@@ -1878,32 +2014,53 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                     t_lo            = tau_reg;
                     t_scale         = (n_own >= kq && top > tau_reg && top - tau_reg < CUDART_INF_F) ? (float) kHistBins / (top - tau_reg) : 0.0f;
                 }
+                CYC(7);
                 const unsigned pkey = *reinterpret_cast<volatile unsigned *>(&sh->tau_key);
                 tau                 = pkey == 0u ? tau_reg : fmaxf(tau_reg, key_to_float(pkey));
-                /* candidates: the float4 groups whose maximum passes; one ballot per group of the warp, places
-                 * counted from the warp's own cursor, no atomics on the way */
+                /* Candidates: the float4 groups whose maximum passes. Which of a thread's eight groups do is one bit
+                 * each; the groups that hold any are then taken one after the other by ONE rolled loop (rarely run
+                 * code inside the hot loop is kept in one copy: it has to come from the instruction cache each
+                 * time), the values re-read from the stage, places counted from the warp's own cursor. */
+                unsigned mybits = 0u;
 #pragma unroll
                 for (int i = 0; i < kNV4; i++) {
-                    const bool     hit = gm[i] >= tau && lane + 32 * i < mine4;
+                    mybits |= (gm[i] >= tau && lane + 32 * i < mine4) ? (1u << i) : 0u;
+                }
+                unsigned gany = __reduce_or_sync(0xffffffffu, mybits);
+#pragma unroll 1
+                while (gany != 0u) {
+                    const int i = __ffs(gany) - 1;
+                    gany &= gany - 1u;
+                    const bool     hit = ((mybits >> i) & 1u) != 0u;
                     const unsigned m   = __ballot_sync(0xffffffffu, hit);
-                    if (m != 0u) {
-                        if (hit) {
-                            const int pos = wcnt + __popc(m & lt);
-                            if (pos < kGroupCapWarp) {
-                                /* which of the four pass: the finisher takes those, the sums below leave those out */
-                                const unsigned cm = (x[i].x >= tau ? 1u : 0u) | (x[i].y >= tau ? 2u : 0u) | (x[i].z >= tau ? 4u : 0u) | (x[i].w >= tau ? 8u : 0u);
-                                seg_v[pos]        = x[i];
-                                seg_b[pos]        = (s0 + 4 * (w4lo + lane + 32 * i)) | (int) (cm << 28);
-                            }
-                            if (t_scale > 0.0f) {
-                                atomicAdd(&sh->thist[min(kHistBins - 1, max(0, __float2int_rz((gm[i] - t_lo) * t_scale)))], 1);
-                            }
+                    if (hit) {
+                        const float4 v   = s4[32 * i];
+                        const int    pos = wcnt + __popc(m & lt);
+                        if (pos < kGroupCapWarp) {
+                            /* which of the four pass: the finisher takes those, the sums below leave those out */
+                            const unsigned cm = (v.x >= tau ? 1u : 0u) | (v.y >= tau ? 2u : 0u) | (v.z >= tau ? 4u : 0u) | (v.w >= tau ? 8u : 0u);
+                            seg_v[pos]        = v;
+                            seg_b[pos]        = (s0 + 4 * (w4lo + lane + 32 * i)) | (int) (cm << 28);
                         }
-                        wcnt += __popc(m);
-                        since += __popc(m);
+                        if (t_scale > 0.0f) {
+                            const float gmax = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+                            atomicAdd(&sh->thist[min(kHistBins - 1, max(0, __float2int_rz((gmax - t_lo) * t_scale)))], 1);
+                        }
                     }
+                    wcnt += __popc(m);
+                    since += __popc(m);
                 }
             }
+            CYC(2);
+            /* the stage is free again: the warp refills it itself */
+            __syncwarp();
+            if (lane == 0 && p.aligned && j + kStages < my_count) {
+                if (wrote) { /* ordinary stores of this warp come before the copy engine's */
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                issue_next();
+            }
+            CYC(1);
             if (sums) {
                 /* sum of e_i relative to the WARP's maximum of this slice (top-p: of what is in no candidate
                  * group); -inf padding gives exp(-inf) = 0 */
@@ -1959,18 +2116,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                     }
                 }
             }
-#ifdef GB_X2
-            __syncwarp();
-            if (lane == 0 && p.aligned && j + kStages < my_count) {
-#ifndef GB_X4
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
-                issue_next();
-            }
-#endif
             CYC(2);
         }
 
+        PROF(2);
         /* ---- the part is through: one record and the candidate groups go to global scratch ---- */
         wst = __reduce_or_sync(0xffffffffu, (unsigned) wst);
         if (lane == 0) {
@@ -2019,29 +2168,36 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             h2.y = __float_as_int(bref);
             h2.z = __double2loint(bsum);
             h2.w = __double2hiint(bsum);
-            PartRec *rec = p.recs + (size_t) row * (size_t) p.parts_max + part_idx;
-            reinterpret_cast<int4 *>(rec)[0] = h;
-            reinterpret_cast<int4 *>(rec)[1] = h2;
+            int4 *rec = reinterpret_cast<int4 *>(p.grp_v + ((size_t) row * (size_t) p.parts_max + (size_t) part_idx) * (size_t) kPartSlots);
+            rec[0]    = h; /* the part's record takes the first two slots of its group list */
+            rec[1]    = h2;
         }
-        const size_t at = ((size_t) row * (size_t) p.parts_max + (size_t) part_idx) * (size_t) kPartGroups;
+        const size_t at = ((size_t) row * (size_t) p.parts_max + (size_t) part_idx) * (size_t) kPartSlots + 2;
         for (int f = tid; f < held; f += kThreads) {
             const int slot  = own_slot(sh, f);
             p.grp_v[at + f] = grp_v[slot];
             p.grp_b[at + f] = grp_b[slot];
         }
         __syncthreads(); /* the lists are free for the next part */
+        CYC(6);
     }
+    CYC_DONE();
+    PROF(4);
 }
 
 /* ----------------------------------------------------------- finishing kernel -- */
 
 /*
- * Runs behind the stream kernel: one thread block finishes one row at a time (rows blockIdx.x, blockIdx.x +
- * gridDim.x, ...). It merges the records that the row's parts left, orders the few surviving candidates,
- * evaluates their probabilities exactly, makes the draw, writes the row's status and, behind a sequence's last
- * row, its generator. Rows whose kept set does not fit serve themselves with the multi-pass path over a private
- * copy of the row; the copies come from a small pool that the thread blocks claim slots of.
+ * Run behind the stream kernel. finish_rows_kernel<true>: one thread block finishes one row at a time (rows
+ * blockIdx.x, blockIdx.x + gridDim.x, ...): it merges the records that the row's parts left; greedy rows end
+ * there; top-k rows (k <= 256) get their few surviving candidates ordered, their probabilities evaluated exactly
+ * and the draw made. Every other row (temperature, top-p, kept sets too large for this) is put on a list for
+ * finish_rows_kernel<false>, which is launched behind it and carries the code for those: segment walks, nucleus
+ * sums, and the multi-pass path over a private copy of the row (the copies come from a small pool that the
+ * thread blocks claim slots of). Both write the row's status and, behind a sequence's last row, its generator.
+ * The split keeps the kernel that every launch needs small.
  */
+template <bool kFast>
 __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_constant__ SampleParams p, int q_items, int r_items) {
     extern __shared__ __align__(128) unsigned char fsmem[];
     FinishShared  *sh   = reinterpret_cast<FinishShared *>(fsmem);
@@ -2054,53 +2210,52 @@ __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_c
     g.n    = kThreads;
     g.nw   = kWarps;
     g.bar  = 0;
-    asm volatile("griddepcontrol.wait;" ::: "memory"); /* the stream kernel's records are complete and visible */
+    asm volatile("griddepcontrol.wait;" ::: "memory"); /* the records of the kernel before this one are complete and visible */
     asm volatile("griddepcontrol.launch_dependents;");
-    for (int row = (int) blockIdx.x; row < p.n_rows; row += (int) gridDim.x) {
-        /* the first 256 groups of the row's first three parts are asked for together with the row's parameters,
-         * before the parts' counts are known (what lies beyond a part's count is ignored) */
-        float4 sv[3];
-        int    sb[3];
-#pragma unroll
-        for (int k = 0; k < 3; k++) {
-            sv[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            sb[k] = 0;
-            if (k < p.parts_max) {
-                const size_t at = ((size_t) row * (size_t) p.parts_max + (size_t) k) * (size_t) kPartGroups + (size_t) g.tid;
-                sv[k]           = __ldcg(p.grp_v + at);
-                sb[k]           = __ldcg(p.grp_b + at);
-            }
-        }
+    PROF(kFast ? 5 : 7);
+    const int n_todo = kFast ? p.n_rows : min(__ldcg(p.def_count), p.n_rows);
+    for (int it = (int) blockIdx.x; it < n_todo; it += (int) gridDim.x) {
+        const int row = kFast ? it : __ldcg(&p.def_rows[it]);
         const RawCfg rc = raw_config(p, row, true);
         RowCfg       r  = row_config(p, row, rc, true);
-        int          st = finish_row(g, p, sh, r, cmem, q_items, r_items, sv, sb);
+        PROF(8);
+        int          st = finish_row<kFast>(g, p, sh, r, cmem, q_items, r_items);
+        PROF(13);
         if (st & ST_DEFERRED) {
-            /* the multi-pass path: all threads of this thread block, over a private copy of the row */
-            __syncthreads();
-            const float bm = sh->gs.blk_max;
-            const int   ba = sh->gs.blk_arg;
-            if (g.tid == 0) {
-                /* claim a row copy: bounded search, the holders always make progress */
-                int got = -1;
-                for (long long t = 0; t < (1ll << 24) && got < 0; t++) {
-                    const int c = (int) ((blockIdx.x + t) % (unsigned) p.pool_slots);
-                    if (atomicCAS(&p.pool[c], 0, 1) == 0) {
-                        got = c;
-                    }
-                }
-                __threadfence();
-                sh->slot = got;
-            }
-            __syncthreads();
-            const int slot = sh->slot;
-            if (slot < 0) {
-                st = (st & ~ST_DEFERRED) | ST_INTERNAL;
-            } else {
-                st = (st & ~ST_DEFERRED) | multipass_row(g, p, &sh->gs, r, bm, ba, cmem, kFinBytes, slot);
-                __syncthreads();
+            if constexpr (kFast) {
                 if (g.tid == 0) {
+                    p.def_rows[atomicAdd(p.def_count, 1)] = row; /* at most n_rows entries */
+                }
+                __syncthreads();
+                continue;
+            } else {
+                /* the multi-pass path: all threads of this thread block, over a private copy of the row */
+                __syncthreads();
+                const float bm = sh->gs.blk_max;
+                const int   ba = sh->gs.blk_arg;
+                if (g.tid == 0) {
+                    /* claim a row copy: bounded search, the holders always make progress */
+                    int got = -1;
+                    for (long long t = 0; t < (1ll << 24) && got < 0; t++) {
+                        const int c = (int) ((blockIdx.x + t) % (unsigned) p.pool_slots);
+                        if (atomicCAS(&p.pool[c], 0, 1) == 0) {
+                            got = c;
+                        }
+                    }
                     __threadfence();
-                    atomicExch(&p.pool[slot], 0);
+                    sh->slot = got;
+                }
+                __syncthreads();
+                const int slot = sh->slot;
+                if (slot < 0) {
+                    st = (st & ~ST_DEFERRED) | ST_INTERNAL;
+                } else {
+                    st = (st & ~ST_DEFERRED) | multipass_row(g, p, &sh->gs, r, bm, ba, cmem, kFinBytes, slot);
+                    __syncthreads();
+                    if (g.tid == 0) {
+                        __threadfence();
+                        atomicExch(&p.pool[slot], 0);
+                    }
                 }
             }
         }
@@ -2109,6 +2264,7 @@ __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_c
         }
         __syncthreads();
     }
+    PROF(kFast ? 6 : 7);
 }
 
 /* ------------------------------------------------ long histories, prepared -- */
@@ -2202,8 +2358,10 @@ __global__ void __launch_bounds__(kRowIdThreads) row_ids_kernel(const __grid_con
 /* ----------------------------------------------------------------- launchers -- */
 
 #ifdef GB_PROFILE
-extern "C" int geist_b200_debug_prof(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 1024 * 8); }
+extern "C" int geist_b200_debug_prof(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 1024 * 16); }
+#ifdef GB_PROFILE_CYC
 extern "C" int geist_b200_debug_cyc(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_cyc, sizeof(long long) * 1024 * kWarps * 8); }
+#endif
 #endif
 
 size_t sample_stream_smem(int n_slices, int long_ids) {
@@ -2281,7 +2439,10 @@ static cudaError_t ensure_finish_attributes() {
         return cudaErrorInvalidDevice;
     }
     if (!configured[dev]) {
-        e = cudaFuncSetAttribute(finish_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) finish_rows_smem());
+        e = cudaFuncSetAttribute(finish_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) finish_rows_smem());
+        if (e == cudaSuccess) {
+            e = cudaFuncSetAttribute(finish_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) finish_rows_smem());
+        }
         if (e != cudaSuccess) {
             return e;
         }
@@ -2297,12 +2458,12 @@ cudaError_t finish_rows_max_ctas(int sms, int *out) {
         return e;
     }
     int per_sm = 0;
-    e          = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, finish_rows_kernel, kThreads, finish_rows_smem());
+    e          = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, finish_rows_kernel<false>, kThreads, finish_rows_smem());
     *out       = per_sm * sms;
     return e;
 }
 
-cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, int finish_grid, cudaStream_t stream) {
+cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, int finish_grid, bool second_finisher, cudaStream_t stream) {
     cudaError_t e = ensure_attributes(smem_bytes);
     if (e == cudaSuccess) {
         e = ensure_finish_attributes();
@@ -2343,7 +2504,11 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     const int n_items = p.n_rows * p.n_slices;
     cfg.gridDim          = dim3((unsigned) finish_grid);
     cfg.dynamicSmemBytes = finish_rows_smem();
-    return cudaLaunchKernelEx(&cfg, finish_rows_kernel, p, n_items / grid, n_items % grid);
+    e = cudaLaunchKernelEx(&cfg, finish_rows_kernel<true>, p, n_items / grid, n_items % grid);
+    if (e != cudaSuccess || !second_finisher) {
+        return e;
+    }
+    return cudaLaunchKernelEx(&cfg, finish_rows_kernel<false>, p, n_items / grid, n_items % grid);
 }
 
 } /* namespace gb */
