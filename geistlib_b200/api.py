@@ -24,6 +24,7 @@ STATUS_NAMES = ["GEIST_OK", "GEIST_E_OOM", "GEIST_E_INVALID_ARG", "GEIST_E_INTER
                 "GEIST_E_IO", "GEIST_E_FORMAT", "GEIST_E_UNSUPPORTED", "GEIST_E_NOT_FOUND", "GEIST_E_BACKEND",
                 "GEIST_E_INVALID_STATE", "GEIST_E_TOO_MANY_TOKENS"]
 ROW_LOAD_TIMEOUT, ROW_SLOW_PATH, ROW_HIST_OVERFLOW, ROW_KEPT_PARTIAL, ROW_INTERNAL = 1, 2, 4, 8, 16
+FINISH_AUTO, FINISH_GREEDY_TOPK, FINISH_GENERAL = 0, 1, 2
 ROW_INVALID = ROW_LOAD_TIMEOUT | ROW_HIST_OVERFLOW | ROW_INTERNAL
 SPEC_KMAX = 16
 
@@ -56,6 +57,9 @@ class Batch(C.Structure):
         ("out_logits", c_void_p),
         ("kept_cap", c_int32), ("kept_n", c_void_p), ("kept_idx", c_void_p), ("kept_prob", c_void_p),
         ("vocab_offset", c_int32),
+        ("softcap", c_void_p),
+        ("logit_mask", c_void_p), ("logit_mask_stride", c_size_t),
+        ("finish_hint", c_int32),
     ]
 
 
@@ -166,7 +170,8 @@ class Context:
     def sample_batch(self, logits, temperature, top_k, top_p, rng_state, rows_per_seq: int = 1,
                      rep=None, freq=None, pres=None, history=None, history_len=None, fed=None,
                      slot=None, kept_cap: int = 0, want_logits: bool = False, vocab_offset: int = 0,
-                     select_only: bool = False, stream=None, out=None, sync: bool = True, launch: bool = True):
+                     select_only: bool = False, stream=None, out=None, sync: bool = True, launch: bool = True,
+                     softcap=None, logit_mask=None, finish_hint: int = 0):
         """logits: CUDA float32 [rows, V] (rows = n_seq * rows_per_seq). Per-sequence
         arguments are CUDA tensors of length n_seq (or of the slot table's size).
         Returns a dict of CUDA tensors; ``out`` lets a caller reuse a previous dict."""
@@ -217,6 +222,11 @@ class Context:
         b.kept_idx = _ptr(out["kept_idx"])
         b.kept_prob = _ptr(out["kept_prob"])
         b.vocab_offset = vocab_offset
+        b.softcap = _ptr(softcap)
+        if logit_mask is not None:  # CUDA int32 [n_seq, words]: bit i set = column i may be sampled
+            b.logit_mask = logit_mask.data_ptr()
+            b.logit_mask_stride = logit_mask.stride(0)
+        b.finish_hint = finish_hint
         if stream is None:
             stream = torch.cuda.current_stream(dev).cuda_stream
         fn = lib.geist_b200_shard_select if select_only else lib.geist_b200_sample_batch
@@ -272,13 +282,13 @@ class Context:
         torch.cuda.synchronize(dense.device)
         return dense
 
-    def shard_merge_sample(self, cand_val, cand_gid, cand_n, temperature, top_k, rng_state, kept_cap: int = 0):
+    def shard_merge_sample(self, cand_val, cand_gid, cand_n, temperature, top_k, rng_state, kept_cap: int = 0, out=None, sync: bool = True):
         """cand_*: [n_shards, n_rows, stride] / [n_shards, n_rows] CUDA tensors (after the all-gather)."""
         import torch
 
         G, rows, stride = cand_val.shape
         dev = cand_val.device
-        out = {
+        out = out or {
             "tokens": torch.empty(rows, dtype=torch.int32, device=dev),
             "status": torch.empty(rows, dtype=torch.int32, device=dev),
             "rng_state": torch.empty_like(rng_state),
@@ -296,7 +306,8 @@ class Context:
         m.kept_n, m.kept_idx, m.kept_prob = _ptr(out["kept_n"]), _ptr(out["kept_idx"]), _ptr(out["kept_prob"])
         st = torch.cuda.current_stream(dev).cuda_stream
         _check(lib.geist_b200_shard_merge_sample(self.handle, C.byref(m), c_void_p(st)))
-        torch.cuda.synchronize(dev)
+        if sync:
+            torch.cuda.synchronize(dev)
         return out
 
 

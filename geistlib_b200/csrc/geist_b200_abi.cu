@@ -281,6 +281,12 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     if (b->kept_cap < 0 || (b->kept_cap > 0 && (b->kept_n == nullptr || b->kept_idx == nullptr || b->kept_prob == nullptr))) {
         return fail(GEIST_E_INVALID_ARG, "sample_batch: kept_cap > 0 needs kept_n, kept_idx and kept_prob");
     }
+    if (b->logit_mask != nullptr && b->logit_mask_stride * 32 < b->n_vocab) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: logit_mask_stride %zu words hold fewer than n_vocab %zu bits", b->logit_mask_stride, b->n_vocab);
+    }
+    if (b->finish_hint < GEIST_B200_FINISH_AUTO || b->finish_hint > GEIST_B200_FINISH_GENERAL) {
+        return fail(GEIST_E_INVALID_ARG, "sample_batch: finish_hint %d is not one of GEIST_B200_FINISH_*", b->finish_hint);
+    }
     if ((flags & gb::F_SELECT_ONLY) && b->kept_cap <= 0) {
         return fail(GEIST_E_INVALID_ARG, "shard_select: kept_cap must hold the shard's candidates");
     }
@@ -304,6 +310,9 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.rep          = b->repetition_penalty;
     p.freq         = b->frequency_penalty;
     p.pres         = b->presence_penalty;
+    p.softcap      = b->softcap;
+    p.mask         = b->logit_mask;
+    p.mask_stride  = (long long) b->logit_mask_stride;
     p.hist         = b->history;
     p.hist_stride  = (long long) b->history_stride;
     p.hist_len     = b->history_len;
@@ -326,6 +335,9 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.hist_cap     = pl.hist_cap;
     p.aligned      = ((reinterpret_cast<uintptr_t>(b->logits) & 15u) == 0 && (b->row_stride & 3u) == 0) ? 1 : 0;
     p.flags        = flags;
+    if ((flags & gb::F_SELECT_ONLY) == 0u) { /* a shard's select is a top-k row whatever its parameters say: the small kernel takes k <= kFastKMax, the general one the rest */
+        p.flags |= b->finish_hint == GEIST_B200_FINISH_GREEDY_TOPK ? gb::F_FAST_ONLY : (b->finish_hint == GEIST_B200_FINISH_GENERAL ? gb::F_REST_ONLY : 0u);
+    }
     cudaStream_t st = as_stream(stream);
 
     /* scratch of this launch */
@@ -1122,7 +1134,11 @@ enum geist_status batcher_run(geist_b200_batcher *b, size_t n, const int32_t *se
             if (s0 < 2 * seq_chunk) {
                 CUDA_TRY(cudaStreamWaitEvent(cs, b->ev[0], 0));
             }
-            CUDA_TRY(cudaMemcpy2DAsync(b->d_logits + s0 * k * b->V, b->V * 4, logits + s0 * k * row_stride, row_stride * 4, b->V * 4, ns * k, cudaMemcpyHostToDevice, cs));
+            if (row_stride == b->V) { /* dense rows: one linear copy per chunk */
+                CUDA_TRY(cudaMemcpyAsync(b->d_logits + s0 * k * b->V, logits + s0 * k * row_stride, ns * k * b->V * 4, cudaMemcpyHostToDevice, cs));
+            } else {
+                CUDA_TRY(cudaMemcpy2DAsync(b->d_logits + s0 * k * b->V, b->V * 4, logits + s0 * k * row_stride, row_stride * 4, b->V * 4, ns * k, cudaMemcpyHostToDevice, cs));
+            }
             d.logits     = b->d_logits + s0 * k * b->V;
             d.row_stride = b->V;
             d.n_seq      = ns;

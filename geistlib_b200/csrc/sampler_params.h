@@ -42,6 +42,8 @@ enum : int {
 
 enum : unsigned {
     F_SELECT_ONLY = 1u << 0, /* vocabulary shard: emit the row's best k (value, global id), no draw */
+    F_FAST_ONLY   = 1u << 1, /* the caller vouches that every row is greedy or top-k <= kFastKMax: only the small finishing kernel runs */
+    F_REST_ONLY   = 1u << 2, /* the caller expects no such rows: only the general finishing kernel runs, over all rows */
 };
 
 struct Pair {
@@ -83,6 +85,9 @@ struct SampleParams {
     const float *rep;         /* [n_seq] or null */
     const float *freq;        /* [n_seq] or null */
     const float *pres;        /* [n_seq] or null */
+    const float *softcap;     /* [n_seq] or null: final-logit soft cap of the sequence's model (0 = none) */
+    const unsigned *mask;     /* [n_seq in call order, mask_stride] or null: bit i set = column i may be sampled */
+    long long       mask_stride; /* 32-bit words per mask row */
 
     const int *hist;          /* [n_seq, hist_stride] or null */
     long long  hist_stride;

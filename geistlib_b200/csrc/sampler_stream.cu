@@ -147,6 +147,8 @@ struct RowCfg {
     bool               select_only, pen_on;
     int                H, E;
     float              rep, freq, pres;
+    float              cap;  /* > 0: the row is sampled from tanhf(x / cap) * cap */
+    const unsigned    *mrow; /* the sequence's mask of allowed columns, or null */
     const int         *hrow, *erow;
     unsigned long long rng; /* generator state this row starts from */
     int                draws_per_row;
@@ -159,6 +161,7 @@ struct RawCfg {
     float T, top_p;
     int   top_k, hist_len;
     float rep, freq, pres;
+    float cap;
     unsigned long long rng; /* the sequence's generator word (only when asked for) */
 };
 
@@ -173,6 +176,7 @@ __device__ __forceinline__ RawCfg raw_config(const SampleParams &p, int row, boo
     c.rep          = p.rep ? p.rep[c.seq] : 1.0f;
     c.freq         = p.freq ? p.freq[c.seq] : 0.0f;
     c.pres         = p.pres ? p.pres[c.seq] : 0.0f;
+    c.cap          = p.softcap ? p.softcap[c.seq] : 0.0f;
     c.rng          = (want_rng && p.rng_in) ? p.rng_in[c.seq] : 1ull; /* travels with the other parameters */
     return c;
 }
@@ -218,6 +222,9 @@ __device__ __forceinline__ RowCfg row_config(const SampleParams &p, int row, con
     r.rep    = c.rep > 0.0f ? c.rep : 1.0f;
     r.freq   = c.freq;
     r.pres   = c.pres;
+    /* head.c:145-159: the cap is skipped for greedy rows (monotone, the argmax is the same) */
+    r.cap    = (c.cap > 0.0f && r.T > 0.0f) ? c.cap : 0.0f;
+    r.mrow   = p.mask ? p.mask + (size_t) r.seq0 * (size_t) p.mask_stride : nullptr;
     r.hrow   = p.hist ? p.hist + (size_t) r.seq * (size_t) p.hist_stride : nullptr;
     r.erow   = p.extra ? p.extra + (size_t) r.seq0 * (size_t) p.extra_stride : nullptr; /* per call, not per slot */
     return r;
@@ -225,6 +232,39 @@ __device__ __forceinline__ RowCfg row_config(const SampleParams &p, int row, con
 
 __device__ __forceinline__ int hist_id(const RowCfg &r, int j, int vocab_offset) {
     return (j < r.H ? r.hrow[j] : r.erow[1 + j - r.H]) - vocab_offset;
+}
+
+/* What happens to a logit before the penalties: the final-logit soft cap in the reference's own expression
+ * (head.c:154, :286), then the mask of allowed columns (bit i of the sequence's mask row: column i may be
+ * sampled; a masked column reads as -inf). `i` is the column inside this call's logits. */
+__device__ __forceinline__ float soft_cap(float x, float c) {
+    return __fmul_rn(tanhf(__fdiv_rn(x, c)), c);
+}
+__device__ __forceinline__ float prologue_one(float x, int i, float cap, const unsigned *mrow) {
+    if (cap > 0.0f) {
+        x = soft_cap(x, cap);
+    }
+    if (mrow != nullptr && ((mrow[i >> 5] >> (i & 31)) & 1u) == 0u) {
+        x = -CUDART_INF_F;
+    }
+    return x;
+}
+
+/* The same over a warp's share of a slice in its stage (sl: the share's first float; e0: its index inside the
+ * slice; mine4 float4 groups, lane-strided; n: the slice's length, what lies behind it stays -inf). Kept out of
+ * line: the stream kernel's loop stays short for the launches that have neither cap nor mask. */
+__device__ __noinline__ void prologue_share(float *sl, int lane, int mine4, int e0, int n, int s0, float cap, const unsigned *mrow) {
+    float4 *w4 = reinterpret_cast<float4 *>(sl) + lane;
+    for (int i = 0; lane + 32 * i < mine4; i++) {
+        const int e = e0 + 4 * (lane + 32 * i);
+        float4    v = w4[32 * i];
+        if (e + 0 < n) v.x = prologue_one(v.x, s0 + e + 0, cap, mrow);
+        if (e + 1 < n) v.y = prologue_one(v.y, s0 + e + 1, cap, mrow);
+        if (e + 2 < n) v.z = prologue_one(v.z, s0 + e + 2, cap, mrow);
+        if (e + 3 < n) v.w = prologue_one(v.w, s0 + e + 3, cap, mrow);
+        w4[32 * i] = v;
+    }
+    __syncwarp();
 }
 
 __device__ __forceinline__ float penalise(float x, int cnt, float rep, float freq, float pres) {
@@ -628,6 +668,12 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
             gr[i] = src[i];
         }
     }
+    if (r.cap > 0.0f || r.mrow != nullptr) {
+        g.sync();
+        const float     cap  = r.cap;
+        const unsigned *mrow = r.mrow;
+        row_rewrite(g, gr, V, [&](float x, int i) { return prologue_one(x, i, cap, mrow); });
+    }
     if (r.pen_on) {
         unsigned *bm = p.gen_bitmap + (size_t) slot * (size_t) p.gen_bitmap_words;
         for (int i = g.tid; i < p.gen_bitmap_words; i += g.n) {
@@ -856,6 +902,8 @@ struct __align__(16) StreamShared {
     int                bhist[kHistBins];           /* first slice: group maxima binned by key */
     int                thist[kHistBins];           /* candidates binned by value between threshold and maximum */
     int                rl_id[kRowIds], rl_cnt[kRowIds]; /* the row's distinct history ids and their counts */
+    float              cap;             /* the part's soft cap and mask row (0 / null: none) */
+    const unsigned    *mrow;
     RawCfg             raw_nxt;         /* parameters of the next row of this run, copied in while the part streams */
     int                nxt_ids[kRowIds]; /* that row's history ids (raw): the first words of its history row ... */
     int                nxt_ext[kRowIds]; /* ... and the tokens fed before it */
@@ -1078,7 +1126,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
             const int4  h  = __ldcg(reinterpret_cast<const int4 *>(p.grp_v + ((size_t) row * (size_t) p.parts_max + (size_t) i) * (size_t) kPartSlots));
             const float pm = __int_as_float(h.x);
             st |= h.w;
-            if (a == 0x7fffffff || pair_before(pm, h.y, m, a)) {
+            if (pair_before(pm, h.y, m, a)) {
                 m = pm;
                 a = h.y;
             }
@@ -1141,7 +1189,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
     for (int i = 0; i < n_parts; i++) {
         const float m = sh->pmax[i];
         const int   a = sh->parg[i];
-        if (row_arg == 0x7fffffff || pair_before(m, a, row_max, row_arg)) {
+        if (pair_before(m, a, row_max, row_arg)) { /* rows that are not greedy carry no id: the plain maximum */
             row_max = m;
             row_arg = a;
         }
@@ -1243,7 +1291,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
         const float *src   = p.logits + (size_t) row * (size_t) p.row_stride + s0c + e0;
         g.sync();
         for (int i = g.tid; i < seg_n; i += g.n) {
-            wbuf[i] = src[i];
+            wbuf[i] = prologue_one(src[i], s0c + e0 + i, r.cap, r.mrow);
         }
         if (r.pen_on) {
             for (int i = g.tid; i < kFinBitmapWords; i += g.n) {
@@ -1609,6 +1657,7 @@ __device__ __forceinline__ void prefetch_step(const SampleParams &p, StreamShare
     if (lane == 4) { if (p.rep) copy_word_async(&sh->raw_nxt.rep, &p.rep[seq]); else sh->raw_nxt.rep = 1.0f; }
     if (lane == 5) { if (p.freq) copy_word_async(&sh->raw_nxt.freq, &p.freq[seq]); else sh->raw_nxt.freq = 0.0f; }
     if (lane == 6) { if (p.pres) copy_word_async(&sh->raw_nxt.pres, &p.pres[seq]); else sh->raw_nxt.pres = 0.0f; }
+    if (lane == 9) { if (p.softcap) copy_word_async(&sh->raw_nxt.cap, &p.softcap[seq]); else sh->raw_nxt.cap = 0.0f; }
     if (lane == 7 || lane == 8) {
         unsigned *dst = reinterpret_cast<unsigned *>(&sh->raw_nxt.rng) + (lane - 7);
         if (p.rng_in) copy_word_async(dst, reinterpret_cast<const unsigned *>(&p.rng_in[seq]) + (lane - 7)); else *dst = lane == 7 ? 1u : 0u;
@@ -1738,7 +1787,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
         __syncthreads();
         int   mode, kq, n_ids, my_id = -1;
         float inv_t, rep, freq, pres;
-        bool  pen_on;
+        bool  pen_on, pro_on;
         {
             const RawCfg raw = sh->raw_nxt;
             const RowCfg r   = row_config(p, row, raw, false); /* what the finisher needs more of is derived again when the row is complete */
@@ -1750,6 +1799,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             rep    = r.rep;
             freq   = r.freq;
             pres   = r.pres;
+            pro_on = r.cap > 0.0f || r.mrow != nullptr;
+            if (tid == 0) { /* read again by the warps only if pro_on; the barriers of the part set-up lie between */
+                sh->cap  = r.cap;
+                sh->mrow = r.mrow;
+            }
             if (tid < n_ids && n_ids <= kRowIds) {
                 my_id = tid < r.H ? sh->nxt_ids[tid] : sh->nxt_ext[tid - r.H];
             }
@@ -1870,6 +1924,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             }
             __syncwarp();
             CYC(0);
+
+            /* ---- 1b. soft cap and mask, in place ---- */
+            if (pro_on) {
+                wrote = true;
+                prologue_share(sl, lane, mine4, 4 * w4lo, n, s0, sh->cap, sh->mrow);
+            }
 
             /* ---- 2. penalties on the share ---- */
             if (pen_on) {
@@ -2213,9 +2273,10 @@ __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_c
     asm volatile("griddepcontrol.wait;" ::: "memory"); /* the records of the kernel before this one are complete and visible */
     asm volatile("griddepcontrol.launch_dependents;");
     PROF(kFast ? 5 : 7);
-    const int n_todo = kFast ? p.n_rows : min(__ldcg(p.def_count), p.n_rows);
+    const bool all_rows = kFast || (p.flags & F_REST_ONLY) != 0u;
+    const int  n_todo   = all_rows ? p.n_rows : min(__ldcg(p.def_count), p.n_rows);
     for (int it = (int) blockIdx.x; it < n_todo; it += (int) gridDim.x) {
-        const int row = kFast ? it : __ldcg(&p.def_rows[it]);
+        const int row = all_rows ? it : __ldcg(&p.def_rows[it]);
         const RawCfg rc = raw_config(p, row, true);
         RowCfg       r  = row_config(p, row, rc, true);
         PROF(8);
@@ -2223,11 +2284,18 @@ __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_c
         PROF(13);
         if (st & ST_DEFERRED) {
             if constexpr (kFast) {
-                if (g.tid == 0) {
-                    p.def_rows[atomicAdd(p.def_count, 1)] = row; /* at most n_rows entries */
+                if ((p.flags & F_FAST_ONLY) == 0u) {
+                    if (g.tid == 0) {
+                        p.def_rows[atomicAdd(p.def_count, 1)] = row; /* at most n_rows entries */
+                    }
+                    __syncthreads();
+                    continue;
                 }
-                __syncthreads();
-                continue;
+                /* the caller said that no such row would come and no kernel behind this one takes it */
+                st = (st & ~ST_DEFERRED) | ST_INTERNAL;
+                if (g.tid == 0) {
+                    p.tokens[row] = -1;
+                }
             } else {
                 /* the multi-pass path: all threads of this thread block, over a private copy of the row */
                 __syncthreads();
@@ -2504,9 +2572,11 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     const int n_items = p.n_rows * p.n_slices;
     cfg.gridDim          = dim3((unsigned) finish_grid);
     cfg.dynamicSmemBytes = finish_rows_smem();
-    e = cudaLaunchKernelEx(&cfg, finish_rows_kernel<true>, p, n_items / grid, n_items % grid);
-    if (e != cudaSuccess || !second_finisher) {
-        return e;
+    if ((p.flags & F_REST_ONLY) == 0u) {
+        e = cudaLaunchKernelEx(&cfg, finish_rows_kernel<true>, p, n_items / grid, n_items % grid);
+        if (e != cudaSuccess || !second_finisher || (p.flags & F_FAST_ONLY) != 0u) {
+            return e;
+        }
     }
     return cudaLaunchKernelEx(&cfg, finish_rows_kernel<false>, p, n_items / grid, n_items % grid);
 }

@@ -174,6 +174,33 @@ struct geist_b200_batch {
     float   *kept_prob; /* [rows, kept_cap] probability renormalised inside the kept set */
 
     int32_t vocab_offset; /* id of column 0; added to every id written, subtracted from history ids */
+
+    /* Final-logit soft cap (head.c:145-159, :279-288): per sequence or NULL. A row whose sequence has c > 0 and
+     * T > 0 is sampled from tanhf(x / c) * c; greedy rows skip it, as the reference does (monotone). Applied to
+     * the logits as they stream in, before mask and penalties; out_logits shows the capped values. */
+    const float *softcap;
+
+    /* Constrained decoding (EXTENSION): optional [n_seq, logit_mask_stride] 32-bit words in call order; bit i of
+     * a sequence's row set = column i may be sampled, clear = the column reads as -inf (after the soft cap,
+     * before the penalties). All rows of a sequence share its mask row. */
+    const uint32_t *logit_mask;
+    size_t          logit_mask_stride; /* words per mask row, >= ceil(n_vocab / 32) */
+
+    /* Which finishing kernels the launch carries: see GEIST_B200_FINISH_* below. 0 = both. */
+    int32_t finish_hint;
+};
+
+/* finish_hint. The stream kernel is followed by a small finishing kernel (greedy rows, top-k rows with
+ * k <= 256) and a general one (temperature, top-p, wider top-k) that takes what the small one leaves. A caller
+ * that knows its sessions' sampler settings can drop the one it does not need and save its launch:
+ *   AUTO         both kernels; any mix of rows.
+ *   GREEDY_TOPK  the small kernel only. A row that is neither greedy nor top-k <= 256 is not sampled: its
+ *                row_status carries GEIST_B200_ROW_INTERNAL and its token is -1.
+ *   GENERAL      the general kernel only, over all rows (it can finish every kind of row). */
+enum {
+    GEIST_B200_FINISH_AUTO        = 0,
+    GEIST_B200_FINISH_GREEDY_TOPK = 1,
+    GEIST_B200_FINISH_GENERAL     = 2,
 };
 
 /* Replaces the sampler dispatch of finalize_logits_one_row / _batch

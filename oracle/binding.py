@@ -63,6 +63,20 @@ class Port:
         L.orc_merge_candidates.argtypes = [C.c_size_t, _f32p, _i32p, C.c_size_t, _f32p, _i32p]
         L.orc_sample_ordered.restype = C.c_int32
         L.orc_sample_ordered.argtypes = [C.c_size_t, _f32p, _i32p, C.c_float, C.POINTER(C.c_uint64)]
+        L.orc_softcap.restype = None
+        L.orc_softcap.argtypes = [C.c_size_t, _f32p, C.c_float]
+        L.orc_propose_drafts_ngram.restype = C.c_size_t
+        L.orc_propose_drafts_ngram.argtypes = [_i32p, C.c_size_t, C.c_int32, C.c_size_t, C.c_size_t, _i32p, C.POINTER(C.c_size_t)]
+
+    def softcap(self, logits, c: float):
+        """tanhf(x / c) * c of every entry (a copy)."""
+        out = np.array(logits, dtype=np.float32, copy=True, order="C")
+        self.lib.orc_softcap(out.size, out.reshape(-1), c)
+        return out
+
+    def propose_drafts(self, history, seed: int, k_max: int, max_suffix: int = 4):
+        """(drafts incl. the seed, match length) of the n-gram drafter."""
+        return _drafts(self.lib.orc_propose_drafts_ngram, history, seed, k_max, max_suffix)
 
     # -- generator
     def rng_seed(self, seed: int) -> int:
@@ -215,6 +229,14 @@ class Ref:
         L.ref_topk_detail.argtypes = [C.c_size_t, _f32p, C.c_int, C.c_float, _i32p, _f32p, C.c_void_p, C.POINTER(C.c_double)]
         L.ref_topp_detail.restype = C.c_long
         L.ref_topp_detail.argtypes = [C.c_size_t, _f32p, C.c_float, C.c_float, C.c_size_t, _i32p, _f32p, _f32p, C.POINTER(C.c_double)]
+        if hasattr(L, "ref_softcap"):
+            L.ref_softcap.restype = None
+            L.ref_softcap.argtypes = [C.c_size_t, _f32p, C.c_float]
+
+    def softcap(self, logits, c: float):
+        out = np.array(logits, dtype=np.float32, copy=True, order="C")
+        self.lib.ref_softcap(out.size, out.reshape(-1), c)
+        return out
 
     def rng_seed(self, seed: int) -> int:
         return int(self.lib.ref_rng_seed_state(seed))
@@ -285,6 +307,27 @@ class Ref:
         return int(n), idx[:m].copy(), pn[:m].copy(), pq[:m].copy(), float(s.value)
 
 
+def _drafts(fn, history, seed, k_max, max_suffix):
+    h = np.ascontiguousarray(history, np.int32)
+    out = np.full(max(int(k_max), 1), -1, np.int32)
+    L = C.c_size_t(0)
+    hp = h if h.size else np.zeros(1, np.int32)
+    n = int(fn(hp, h.size, int(seed), int(k_max), int(max_suffix), out, C.byref(L)))
+    return out[:n].copy(), int(L.value)
+
+
+class RefDrafter:
+    """The reference's own propose_drafts_ngram (session.c:437-513) behind oracle/ref_drafter_harness.c."""
+
+    def __init__(self, path: Path):
+        L = self.lib = C.CDLL(str(path))
+        L.ref_propose_drafts_ngram.restype = C.c_size_t
+        L.ref_propose_drafts_ngram.argtypes = [_i32p, C.c_size_t, C.c_int32, C.c_size_t, C.c_size_t, _i32p, C.POINTER(C.c_size_t)]
+
+    def propose_drafts(self, history, seed: int, k_max: int, max_suffix: int = 4):
+        return _drafts(self.lib.ref_propose_drafts_ngram, history, seed, k_max, max_suffix)
+
+
 def _load(cls, path: Path):
     return cls(path) if path.exists() else None
 
@@ -294,3 +337,4 @@ if not (HERE / "liboracle.so").exists():
 port: Port = Port(HERE / "liboracle.so")
 ref = _load(Ref, HERE / "_ref" / "libgeist_ref.so")
 ref_release = _load(Ref, HERE / "_ref" / "libgeist_ref_release.so")
+ref_drafter = _load(RefDrafter, HERE / "_ref" / "libgeist_ref_drafter.so")

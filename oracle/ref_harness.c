@@ -12,6 +12,9 @@
  *   ref_softmax          softmax_into + normalise          (sampler.c:68-85, :253-255)
  *   ref_topk_detail      kept set + probabilities of top-k (sampler.c:178-228)
  *   ref_topp_detail      nucleus + probabilities of top-p  (sampler.c:232-305)
+ *   ref_softcap          the output head's final-logit soft cap, the reference's expression with this
+ *                        host's tanhf (src/archs/transformer/forward/head.c:148-159, :279-288; the head
+ *                        itself does not compile outside its engine, so the one-line loop is restated)
  *
  * Everything numeric below is executed by the reference's own code; this file
  * only loops, dispatches and copies results out.
@@ -248,4 +251,11 @@ long ref_topp_detail(size_t V, const float *row, float top_p, float T, size_t ca
     free(probs);
     free(pairs);
     return (long) cutoff;
+}
+
+/* head.c:152-155 / :284-287: p[i] = tanhf(p[i] / c) * c, in place. */
+void ref_softcap(size_t n, float *p, float c) {
+    for (size_t i = 0; i < n; i++) {
+        p[i] = tanhf(p[i] / c) * c;
+    }
 }

@@ -532,3 +532,85 @@ int32_t orc_sample_ordered(size_t k, const float *val, const int32_t *gid, float
     double sum = exp_weights(val, k, T, q);
     return gid[inverse_cdf(q, k, sum, rng_state)];
 }
+
+/* -------------------------------------------------------------- soft cap -- */
+
+/* The output head's final-logit soft cap, in place: p[i] = tanhf(p[i] / c) * c
+ * (src/archs/transformer/forward/head.c:152-155, :284-287). Division, tanhf and
+ * product are three separately rounded binary32 steps. */
+void orc_softcap(size_t n, float *p, float c) {
+    for (size_t i = 0; i < n; i++) {
+        float q = p[i] / c;
+        q       = tanhf(q);
+        p[i]    = q * c;
+    }
+}
+
+/* ---------------------------------------------------------- n-gram drafter -- */
+
+/*
+ * Restates propose_drafts_ngram (src/engine/session.c:437-513). The context is
+ * history + [seed]; for L = min(max_suffix, 8) down to 1 its last L tokens (L - 1
+ * history tokens and the seed) are looked for at every earlier position p of the
+ * history, newest first. A position counts only if at least one token follows the
+ * match inside the history; among those the one with the most following tokens
+ * (capped at k_max - 1) wins, the newest on ties, and the search of this L stops
+ * as soon as a position offers k_max - 1 of them. The first L with a match ends
+ * the search. out[0] = seed, out[1..] = the tokens that followed; returns their
+ * number including the seed; *match_L = L, or 0 without a match.
+ */
+size_t orc_propose_drafts_ngram(const int32_t *history, size_t history_n, int32_t seed, size_t k_max, size_t max_suffix, int32_t *out, size_t *match_L) {
+    out[0] = seed;
+    if (match_L) {
+        *match_L = 0;
+    }
+    if (k_max <= 1 || history_n == 0) {
+        return 1;
+    }
+    if (max_suffix > 8) {
+        max_suffix = 8;
+    }
+    const size_t want = k_max - 1;
+    for (size_t L = max_suffix; L >= 1; L--) {
+        if (L - 1 > history_n) {
+            continue;
+        }
+        const size_t tail  = history_n - (L - 1); /* where the context's history part starts; also the number of start positions */
+        size_t       best  = 0, best_follow = 0;
+        int          found = 0;
+        for (size_t p = tail; p-- > 0;) {
+            if (history[p + L - 1] != seed || p + L >= history_n) {
+                continue;
+            }
+            size_t i = 0;
+            while (i + 1 < L && history[p + i] == history[tail + i]) {
+                i++;
+            }
+            if (i + 1 < L) {
+                continue;
+            }
+            size_t follow = history_n - (p + L);
+            if (follow > want) {
+                follow = want;
+            }
+            if (!found || follow > best_follow) {
+                best        = p;
+                best_follow = follow;
+                found       = 1;
+                if (follow >= want) {
+                    break;
+                }
+            }
+        }
+        if (found) {
+            for (size_t i = 0; i < best_follow; i++) {
+                out[1 + i] = history[best + L + i];
+            }
+            if (match_L) {
+                *match_L = L;
+            }
+            return 1 + best_follow;
+        }
+    }
+    return 1;
+}

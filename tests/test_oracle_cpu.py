@@ -196,3 +196,47 @@ def test_shard_merge_equals_unsharded_topk():
     tok, st = port.sample_ordered(mv, mg, 0.7, port.rng_seed(31337))
     ref = port.sample_batch(x[None, :], 0.7, k, 0.9, [port.rng_seed(31337)])
     assert tok == ref["tokens"][0] and st == int(ref["rng_state"][0])
+
+
+# ------------------------------------------------------------ soft cap, drafter --
+
+def test_softcap_port_equals_reference_expression():
+    """head.c:152-155: p = tanhf(p / c) * c; the port and the harness around the reference agree bit for bit."""
+    x = (np.random.default_rng(11).standard_normal(200000) * 40).astype(np.float32)
+    x[:4] = [0.0, -0.0, np.inf, -np.inf]
+    y = port.softcap(x, 30.0)
+    assert y[2] == 30.0 and y[3] == -30.0 and np.abs(y).max() <= 30.0
+    assert np.all(np.diff(y[np.argsort(x, kind="stable")]) >= 0), "monotone"
+    if oracle.ref is not None:
+        assert np.array_equal(y.view(np.uint32), oracle.ref.softcap(x, 30.0).view(np.uint32))
+
+
+def test_drafter_known_answers():
+    """session.c:437-513 by hand: longest suffix first, most following context, newest on ties."""
+    d = port.propose_drafts
+    assert d([], 5, 8)[0].tolist() == [5] and d([], 5, 8)[1] == 0
+    assert d([1, 2, 3], 9, 8)[0].tolist() == [9] and d([1, 2, 3], 9, 8)[1] == 0      # seed never seen
+    out, L = d([1, 2, 3, 4, 1, 2], 3, 4)          # context ...1 2 [3]: matches position 0..2, then 4 1 2 follow
+    assert L == 3 and out.tolist() == [3, 4, 1, 2]
+    out, L = d([7, 3, 8, 9, 7, 3, 5], 3, 3, 1)    # L = 1: two places; the older one offers 2 tokens, the newer 1
+    assert L == 1 and out.tolist() == [3, 8, 9]
+    out, L = d([3, 8, 9, 3, 8, 9, 4], 3, 3, 1)    # tie on following context: the newest place wins
+    assert L == 1 and out.tolist() == [3, 8, 9]
+    out, L = d([1, 2, 3], 3, 4)                   # the only match sits at the tail: nothing follows
+    assert L == 0 and out.tolist() == [3]
+    out, L = d([1, 2, 3, 4], 2, 1)                # k_max 1: the seed alone
+    assert L == 0 and out.tolist() == [2]
+    out, L = d(list(range(10)) * 2, 0, 16, 20)    # max_suffix is clamped to 8
+    assert L == 8 and out.tolist() == list(range(10))
+
+
+@pytest.mark.skipif(oracle.ref_drafter is None, reason="oracle/_ref not built")
+def test_drafter_port_equals_reference_function():
+    """The restatement against the reference's own propose_drafts_ngram on random small-alphabet histories."""
+    rng = np.random.default_rng(2026)
+    for _ in range(4000):
+        n, voc = int(rng.integers(0, 64)), int(rng.integers(1, 7))
+        h = rng.integers(0, voc, n).astype(np.int32)
+        seed, k, ms = int(rng.integers(0, voc)), int(rng.integers(1, 17)), int(rng.integers(1, 12))
+        a, b = port.propose_drafts(h, seed, k, ms), oracle.ref_drafter.propose_drafts(h, seed, k, ms)
+        assert np.array_equal(a[0], b[0]) and a[1] == b[1], (h, seed, k, ms, a, b)
