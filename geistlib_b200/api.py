@@ -131,6 +131,16 @@ PROTOTYPES = {
                                           c_void_p]),
     "geist_b200_batcher_verify": (C.c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t,
                                             C.c_int, C.c_int, c_void_p, c_void_p, c_void_p]),
+    "geist_b200_batcher_decode_step": (C.c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, C.c_int, C.c_int,
+                                                 c_void_p]),
+    "geist_b200_session_peek_next_token": (c_int32, [c_void_p, c_int32]),
+    "geist_b200_session_peek_logits": (c_void_p, [c_void_p, c_int32, C.POINTER(c_size_t)]),
+    "geist_b200_session_set_softcap": (C.c_int, [c_void_p, c_int32, C.c_float]),
+    "geist_b200_session_set_logit_mask": (C.c_int, [c_void_p, c_int32, c_void_p, c_size_t]),
+    "geist_b200_draft_ngram": (C.c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_size_t,
+                                         c_size_t, c_void_p, c_void_p, c_void_p]),
+    "geist_b200_batcher_propose_drafts": (C.c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_size_t, c_void_p, c_void_p,
+                                                    c_void_p]),
     "geist_b200_argmax_rows_static": (C.c_int, [C.c_int, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_void_p]),
     "geist_b200_grid": (C.c_int, [c_size_t, c_size_t, c_size_t, C.POINTER(c_int32), C.POINTER(c_int32)]),
     "geist_b200_plan": (C.c_int, [c_size_t, c_size_t, C.POINTER(c_int32), C.POINTER(c_int32), C.POINTER(c_int32),
@@ -311,6 +321,21 @@ class Context:
         return out
 
 
+def draft_ngram(ctx: Context, histories, history_len, seeds, k_max: int, max_suffix: int = 4, out_capacity: Optional[int] = None):
+    """histories: host int32 [n, stride]. Returns (drafts [n, out_capacity], n_drafts [n], match_L [n])."""
+    h = np.ascontiguousarray(histories, np.int32)
+    n, stride = h.shape
+    hl = np.ascontiguousarray(history_len, np.int32)
+    sd = np.ascontiguousarray(seeds, np.int32)
+    cap = k_max + 1 if out_capacity is None else out_capacity
+    d = np.empty((n, max(cap, 1)), np.int32)
+    nd = np.empty(n, np.int32)
+    L = np.empty(n, np.int32)
+    _check(lib.geist_b200_draft_ngram(ctx.handle, n, h.ctypes.data_as(c_void_p), stride, hl.ctypes.data_as(c_void_p), sd.ctypes.data_as(c_void_p),
+                                      k_max, max_suffix, cap, d.ctypes.data_as(c_void_p), nd.ctypes.data_as(c_void_p), L.ctypes.data_as(c_void_p)))
+    return d, nd, L
+
+
 def plan(n_vocab: int, max_history: int = 0):
     c, s, m, r = c_int32(), c_int32(), c_int32(), c_int32()
     _check(lib.geist_b200_plan(n_vocab, max_history, C.byref(c), C.byref(s), C.byref(m), C.byref(r)))
@@ -376,6 +401,47 @@ class Batcher:
         _check(lib.geist_b200_batcher_step(self.handle, ss.size, ss.ctypes.data_as(c_void_p), c_void_p(ptr), stride,
                                            on_host, int(append_history), out.ctypes.data_as(c_void_p)))
         return out
+
+    def decode_step(self, sessions: Sequence[int], logits, append_history: bool = True) -> np.ndarray:
+        """Returns each session's pending token; the token sampled from `logits` becomes pending."""
+        ss = np.ascontiguousarray(sessions, np.int32)
+        out = np.empty(ss.size, np.int32)
+        ptr, stride, on_host = _logits_arg(logits)
+        _check(lib.geist_b200_batcher_decode_step(self.handle, ss.size, ss.ctypes.data_as(c_void_p), c_void_p(ptr), stride,
+                                                  on_host, int(append_history), out.ctypes.data_as(c_void_p)))
+        return out
+
+    def peek_next_token(self, s: int) -> int:
+        return int(lib.geist_b200_session_peek_next_token(self.handle, s))
+
+    def peek_logits(self, s: int):
+        """numpy view of the session's staging row (valid until its next sampling call), or None."""
+        n = c_size_t(0)
+        p = lib.geist_b200_session_peek_logits(self.handle, s, C.byref(n))
+        if not p:
+            return None
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n.value,))
+
+    def set_softcap(self, s: int, c: float):
+        _check(lib.geist_b200_session_set_softcap(self.handle, s, c))
+
+    def set_logit_mask(self, s: int, allowed_words):
+        if allowed_words is None:
+            _check(lib.geist_b200_session_set_logit_mask(self.handle, s, None, 0))
+            return
+        w = np.ascontiguousarray(allowed_words).view(np.uint32)
+        _check(lib.geist_b200_session_set_logit_mask(self.handle, s, w.ctypes.data_as(c_void_p), w.size))
+
+    def propose_drafts(self, sessions: Sequence[int], k_max: int, out_capacity: Optional[int] = None):
+        """(drafts [n, out_capacity], n_drafts [n], match_L [n]) from the sessions' pending tokens and history rings."""
+        ss = np.ascontiguousarray(sessions, np.int32)
+        cap = k_max + 1 if out_capacity is None else out_capacity
+        d = np.empty((ss.size, max(cap, 1)), np.int32)
+        nd = np.empty(ss.size, np.int32)
+        L = np.empty(ss.size, np.int32)
+        _check(lib.geist_b200_batcher_propose_drafts(self.handle, ss.size, ss.ctypes.data_as(c_void_p), k_max, cap,
+                                                     d.ctypes.data_as(c_void_p), nd.ctypes.data_as(c_void_p), L.ctypes.data_as(c_void_p)))
+        return d, nd, L
 
     def verify(self, sessions: Sequence[int], fed, logits, append_history: bool = True):
         """fed: host int32 [n, k]; logits [n*k, V]. Returns (accepted[n], n_out[n], out_tokens[n, k+1])."""

@@ -31,6 +31,9 @@ cudaError_t launch_softmax_rows(const float *logits, long long row_stride, int n
 int         argmax_rows_static_max_rows(long long n_vocab);
 cudaError_t launch_argmax_rows_static(int device, const float *logits, long long row_stride, int n_rows, int V, int *out, cudaStream_t stream, const char **what);
 cudaError_t launch_post_step(const int *slot, int n_seq, int per_seq, int first, const int *tokens, const int *counts, int *hist, int hist_cap, int *hist_len, long long *hist_total, const unsigned long long *rng_tmp, unsigned long long *rng, cudaStream_t stream);
+cudaError_t launch_draft_ngram(const int *slot, int n_seq, const int *hist, long long stride, const int *hist_len, const long long *hist_total, const int *seeds, const int *skip_last,
+                               int k_max, int max_suffix, int min_L, int out_stride, int *drafts, int *n_drafts, int *match_L, cudaStream_t stream);
+cudaError_t launch_softcap_row(float *row, int n, float c, cudaStream_t stream);
 } /* namespace gb */
 
 /* ------------------------------------------------------------- errors -- */
@@ -783,6 +786,31 @@ struct geist_b200_batcher {
     std::vector<char> used;
     std::vector<char> pen_active;
     size_t            n_pen_active = 0;
+
+    /* host mirrors of what the slots hold, for decisions that need no device round trip */
+    std::vector<float> h_T, h_P, h_cap;
+    std::vector<int>   h_K;
+    size_t             n_cap_active = 0;
+    /* the pending token of a session (arch.c:133-161): what its last sampled row predicted, not yet handed out */
+    std::vector<int>  pending;          /* -1: none */
+    std::vector<char> pending_in_hist;  /* the sampler appended it to the history ring when it was drawn */
+    int              *d_pending = nullptr;
+    float            *d_cap     = nullptr;
+    /* allowed-column masks, one row per slot, all ones until a session sets one */
+    uint32_t         *d_mask       = nullptr;
+    size_t            mask_words   = 0;
+    std::vector<char> mask_active;
+    size_t            n_mask_active = 0;
+    /* where the logits row that a session was last sampled from lies (peek_logits) */
+    struct LastRow {
+        const float *ptr     = nullptr; /* device pointer of the row */
+        bool         valid   = false;
+    };
+    std::vector<LastRow>            last_row;
+    std::vector<std::vector<float>> peek_stage; /* session-owned host copies, filled on demand */
+    float                          *d_peek = nullptr;
+    /* drafter scratch */
+    int *d_drafts = nullptr, *d_ndrafts = nullptr, *d_matchL = nullptr, *d_skip = nullptr;
 };
 
 extern "C" void geist_b200_batcher_destroy(struct geist_b200_batcher *b) {
@@ -792,7 +820,8 @@ extern "C" void geist_b200_batcher_destroy(struct geist_b200_batcher *b) {
     cudaSetDevice(b->ctx->device);
     cudaDeviceSynchronize();
     void *dev[] = {b->d_T, b->d_P, b->d_rep, b->d_freq, b->d_pres, b->d_K, b->d_rng, b->d_rng_tmp, b->d_hist, b->d_hist_len, b->d_hist_tot, b->d_slot, b->d_tokens,
-                   b->d_status, b->d_fed, b->d_accepted, b->d_nemit, b->d_emitted, b->d_ones, b->d_logits};
+                   b->d_status, b->d_fed, b->d_accepted, b->d_nemit, b->d_emitted, b->d_ones, b->d_logits, b->d_pending, b->d_cap, b->d_mask, b->d_peek,
+                   b->d_drafts, b->d_ndrafts, b->d_matchL, b->d_skip};
     for (void *p : dev) {
         cudaFree(p);
     }
@@ -831,6 +860,16 @@ extern "C" enum geist_status geist_b200_batcher_create(struct geist_b200_ctx *ct
     b->max_history  = max_history;
     b->used.assign(max_sessions, 0);
     b->pen_active.assign(max_sessions, 0);
+    b->h_T.assign(max_sessions, 0.0f);
+    b->h_P.assign(max_sessions, 1.0f);
+    b->h_K.assign(max_sessions, 0);
+    b->h_cap.assign(max_sessions, 0.0f);
+    b->pending.assign(max_sessions, -1);
+    b->pending_in_hist.assign(max_sessions, 0);
+    b->mask_active.assign(max_sessions, 0);
+    b->last_row.assign(max_sessions, geist_b200_batcher::LastRow{});
+    b->peek_stage.resize(max_sessions);
+    b->mask_words = (n_vocab + 31) / 32;
     const size_t S = max_sessions, R = S * GEIST_B200_SPEC_KMAX;
     cudaError_t  e = cudaSuccess;
     auto         A = [&](void **p, size_t bytes) {
@@ -860,6 +899,13 @@ extern "C" enum geist_status geist_b200_batcher_create(struct geist_b200_ctx *ct
     A((void **) &b->d_nemit, S * 4);
     A((void **) &b->d_emitted, S * (GEIST_B200_SPEC_KMAX + 1) * 4);
     A((void **) &b->d_ones, S * 4);
+    A((void **) &b->d_pending, S * 4);
+    A((void **) &b->d_cap, S * 4);
+    A((void **) &b->d_peek, n_vocab * 4);
+    A((void **) &b->d_drafts, S * (GEIST_B200_SPEC_KMAX + 1) * 4);
+    A((void **) &b->d_ndrafts, S * 4);
+    A((void **) &b->d_matchL, S * 4);
+    A((void **) &b->d_skip, S * 4);
     b->h_pin_ints = S * (1 + 2 + 2 * GEIST_B200_SPEC_KMAX + GEIST_B200_SPEC_KMAX + GEIST_B200_SPEC_KMAX + 1) + 64;
     if (e == cudaSuccess) {
         e = cudaHostAlloc((void **) &b->h_pin, b->h_pin_ints * 4, cudaHostAllocDefault);
@@ -873,6 +919,9 @@ extern "C" enum geist_status geist_b200_batcher_create(struct geist_b200_ctx *ct
     if (e == cudaSuccess) {
         std::vector<int> ones(S, 1);
         e = cudaMemcpy(b->d_ones, ones.data(), S * 4, cudaMemcpyHostToDevice);
+    }
+    if (e == cudaSuccess) {
+        e = cudaMemset(b->d_pending, 0xff, S * 4); /* -1: nothing pending */
     }
     if (e != cudaSuccess) {
         geist_b200_batcher_destroy(b);
@@ -940,9 +989,20 @@ extern "C" enum geist_status geist_b200_session_open(struct geist_b200_batcher *
     CUDA_TRY(cudaMemcpy(b->d_rng + s, &r.state, 8, cudaMemcpyHostToDevice));
     CUDA_TRY(cudaMemcpy(b->d_hist_len + s, &zero, 4, cudaMemcpyHostToDevice));
     CUDA_TRY(cudaMemcpy(b->d_hist_tot + s, &zero64, 8, cudaMemcpyHostToDevice));
+    const int   none = -1;
+    const float nocap = 0.0f;
+    CUDA_TRY(cudaMemcpy(b->d_pending + s, &none, 4, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(b->d_cap + s, &nocap, 4, cudaMemcpyHostToDevice));
     b->used[s]       = 1;
     b->pen_active[s] = active ? 1 : 0;
     b->n_pen_active += active ? 1 : 0;
+    b->h_T[s]        = T;
+    b->h_P[s]        = P;
+    b->h_K[s]        = K;
+    b->h_cap[s]      = 0.0f;
+    b->pending[s]    = -1;
+    b->pending_in_hist[s] = 0;
+    b->last_row[s]   = geist_b200_batcher::LastRow{};
     *out_session = (int32_t) s;
     return GEIST_OK;
 }
@@ -957,7 +1017,17 @@ extern "C" enum geist_status geist_b200_session_close(struct geist_b200_batcher 
     }
     b->n_pen_active -= b->pen_active[(size_t) session] ? 1 : 0;
     b->pen_active[(size_t) session] = 0;
-    b->used[(size_t) session]       = 0;
+    b->n_cap_active -= b->h_cap[(size_t) session] > 0.0f ? 1 : 0;
+    b->h_cap[(size_t) session] = 0.0f;
+    if (b->mask_active[(size_t) session]) { /* the slot's mask row goes back to all ones for whoever opens it next */
+        cudaSetDevice(b->ctx->device);
+        cudaMemset(b->d_mask + (size_t) session * b->mask_words, 0xff, b->mask_words * 4);
+        b->mask_active[(size_t) session] = 0;
+        b->n_mask_active--;
+    }
+    b->pending[(size_t) session]  = -1;
+    b->last_row[(size_t) session] = geist_b200_batcher::LastRow{};
+    b->used[(size_t) session]     = 0;
     return GEIST_OK;
 }
 
@@ -974,6 +1044,11 @@ extern "C" enum geist_status geist_b200_session_reset(struct geist_b200_batcher 
     const int       zero   = 0;
     CUDA_TRY(cudaMemcpy(b->d_hist_len + session, &zero, 4, cudaMemcpyHostToDevice));
     CUDA_TRY(cudaMemcpy(b->d_hist_tot + session, &zero64, 8, cudaMemcpyHostToDevice));
+    const int none = -1;
+    CUDA_TRY(cudaMemcpy(b->d_pending + session, &none, 4, cudaMemcpyHostToDevice));
+    b->pending[(size_t) session]         = -1;
+    b->pending_in_hist[(size_t) session] = 0;
+    b->last_row[(size_t) session]        = geist_b200_batcher::LastRow{};
     return GEIST_OK;
 }
 
@@ -1041,7 +1116,7 @@ namespace {
 
 /* Shared by step and verify: k rows per session, optional accept. */
 enum geist_status batcher_run(geist_b200_batcher *b, size_t n, const int32_t *sessions, size_t k, const geist_token_t *fed, const float *logits, size_t row_stride,
-                              int logits_on_host, int append_history, bool verify, int32_t *accepted, int32_t *n_out, geist_token_t *out_tokens) {
+                              int logits_on_host, int append_history, bool verify, int32_t *accepted, int32_t *n_out, geist_token_t *out_tokens, bool hand_out_pending = false) {
     if (b == nullptr || sessions == nullptr || logits == nullptr || out_tokens == nullptr || n == 0) {
         return fail(GEIST_E_INVALID_ARG, "batcher: missing argument");
     }
@@ -1067,7 +1142,22 @@ enum geist_status batcher_run(geist_b200_batcher *b, size_t n, const int32_t *se
             return fail(GEIST_E_INVALID_ARG, "batcher: session %d appears twice in one call", sessions[i]);
         }
         seen[(size_t) sessions[i]] = 1;
+        /* arch.c:138-140: nothing pending, nothing to hand out or to verify from */
+        if ((hand_out_pending || (verify && fed[i * k] < 0)) && b->pending[(size_t) sessions[i]] < 0) {
+            return fail(GEIST_E_INVALID_STATE, "batcher: session %d has no pending token (sample a row for it first)", sessions[i]);
+        }
     }
+    /* which finishing kernels the launch needs: the sessions' sampler settings are known here */
+    bool any_fast = false, any_rest = false;
+    for (size_t i = 0; i < n; i++) {
+        const size_t sl   = (size_t) sessions[i];
+        const float  T    = b->h_T[sl];
+        const int    K    = b->h_K[sl];
+        const bool   fast = !(T > 0.0f) || (K > 1 && (size_t) K < b->V && K <= gb::kFastKMax);
+        any_fast |= fast;
+        any_rest |= !fast;
+    }
+    const int32_t hint = !any_rest ? GEIST_B200_FINISH_GREEDY_TOPK : (!any_fast ? GEIST_B200_FINISH_GENERAL : GEIST_B200_FINISH_AUTO);
     CUDA_TRY(cudaSetDevice(b->ctx->device));
     cudaStream_t st   = b->ctx->stream;
     const size_t rows = n * k;
@@ -1083,9 +1173,21 @@ enum geist_status batcher_run(geist_b200_batcher *b, size_t n, const int32_t *se
     CUDA_TRY(cudaMemcpyAsync(b->d_slot, h_slot, n * 4, cudaMemcpyHostToDevice, st));
     if (verify) {
         memcpy(h_fed, fed, rows * 4);
+        for (size_t i = 0; i < n; i++) {
+            if (h_fed[i * k] < 0) { /* the caller left the first fed token to the session: its pending token */
+                h_fed[i * k] = b->pending[(size_t) sessions[i]];
+            }
+        }
         CUDA_TRY(cudaMemcpyAsync(b->d_fed, h_fed, rows * 4, cudaMemcpyHostToDevice, st));
     }
     const bool pen = b->n_pen_active > 0 && b->max_history > 0;
+    if (logits_on_host) { /* the staging block is about to be overwritten: rows remembered in it are gone */
+        for (auto &lr : b->last_row) {
+            if (lr.valid && b->d_logits != nullptr && lr.ptr >= b->d_logits && lr.ptr < b->d_logits + b->d_logits_cap) {
+                lr.valid = false;
+            }
+        }
+    }
 
     geist_b200_batch d{};
     d.n_vocab            = b->V;
@@ -1102,6 +1204,10 @@ enum geist_status batcher_run(geist_b200_batcher *b, size_t n, const int32_t *se
     d.fed_stride         = k;
     d.rng_in             = reinterpret_cast<const uint64_t *>(b->d_rng);
     d.rng_out            = reinterpret_cast<uint64_t *>(b->d_rng_tmp);
+    d.softcap            = b->n_cap_active > 0 ? b->d_cap : nullptr;
+    d.logit_mask         = b->n_mask_active > 0 ? b->d_mask : nullptr;
+    d.logit_mask_stride  = b->mask_words;
+    d.finish_hint        = hint;
 
     if (!logits_on_host) {
         d.logits     = logits;
@@ -1184,12 +1290,25 @@ enum geist_status batcher_run(geist_b200_batcher *b, size_t n, const int32_t *se
             return fail(GEIST_E_BACKEND, "batcher: row %zu reported status 0x%x", i, h_stat[i]);
         }
     }
+    const float *dev_rows = logits_on_host ? b->d_logits : logits;
+    const size_t dev_stride = logits_on_host ? b->V : row_stride;
     if (verify) {
         memcpy(accepted, h_acc, n * 4);
         memcpy(n_out, h_nem, n * 4);
         memcpy(out_tokens, h_emit, n * (k + 1) * 4);
+        for (size_t i = 0; i < n; i++) { /* session.c:627-634: the last emitted token still has to go through the model */
+            b->pending[(size_t) sessions[i]]  = -1;
+            b->last_row[(size_t) sessions[i]] = geist_b200_batcher::LastRow{};
+        }
     } else {
-        memcpy(out_tokens, h_tok, rows * 4);
+        for (size_t i = 0; i < n; i++) {
+            const size_t sl = (size_t) sessions[i];
+            out_tokens[i]   = hand_out_pending ? b->pending[sl] : h_tok[i]; /* arch.c:141-147: return, then advance */
+            b->pending[sl]  = h_tok[i];
+            b->pending_in_hist[sl] = (append_history && b->max_history) ? 1 : 0;
+            b->last_row[sl].ptr    = dev_rows + i * dev_stride;
+            b->last_row[sl].valid  = true;
+        }
     }
     return GEIST_OK;
 }
@@ -1204,6 +1323,231 @@ extern "C" enum geist_status geist_b200_batcher_step(struct geist_b200_batcher *
 extern "C" enum geist_status geist_b200_batcher_verify(struct geist_b200_batcher *b, size_t n, const int32_t *sessions, size_t k, const geist_token_t *fed, const float *logits,
                                                        size_t row_stride, int logits_on_host, int append_history, int32_t *accepted, int32_t *n_out, geist_token_t *out_tokens) {
     return batcher_run(b, n, sessions, k, fed, logits, row_stride, logits_on_host, append_history, true, accepted, n_out, out_tokens);
+}
+
+/* arch.c:133-147, batched: hands out each session's pending token and makes the token sampled from `logits`
+ * (the model's output for that pending token) the new pending one. */
+extern "C" enum geist_status geist_b200_batcher_decode_step(struct geist_b200_batcher *b, size_t n, const int32_t *sessions, const float *logits, size_t row_stride,
+                                                            int logits_on_host, int append_history, geist_token_t *out_tokens) {
+    return batcher_run(b, n, sessions, 1, nullptr, logits, row_stride, logits_on_host, append_history, false, nullptr, nullptr, out_tokens, true);
+}
+
+extern "C" geist_token_t geist_b200_session_peek_next_token(struct geist_b200_batcher *b, int32_t session) {
+    if (b == nullptr) {
+        return -1;
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    return slot_ok(b, session) ? b->pending[(size_t) session] : -1;
+}
+
+extern "C" enum geist_status geist_b200_session_set_softcap(struct geist_b200_batcher *b, int32_t session, float softcap) {
+    if (b == nullptr || softcap != softcap || softcap < 0.0f) {
+        return fail(GEIST_E_INVALID_ARG, "session_set_softcap: NULL batcher or a cap that is negative or NaN");
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    if (!slot_ok(b, session)) {
+        return fail(GEIST_E_INVALID_ARG, "session_set_softcap: session %d is not open", session);
+    }
+    CUDA_TRY(cudaSetDevice(b->ctx->device));
+    CUDA_TRY(cudaMemcpy(b->d_cap + session, &softcap, 4, cudaMemcpyHostToDevice));
+    b->n_cap_active += (softcap > 0.0f ? 1 : 0) - (b->h_cap[(size_t) session] > 0.0f ? 1 : 0);
+    b->h_cap[(size_t) session] = softcap;
+    return GEIST_OK;
+}
+
+extern "C" enum geist_status geist_b200_session_set_logit_mask(struct geist_b200_batcher *b, int32_t session, const uint32_t *allowed, size_t n_words) {
+    if (b == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "session_set_logit_mask: NULL batcher");
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    if (!slot_ok(b, session)) {
+        return fail(GEIST_E_INVALID_ARG, "session_set_logit_mask: session %d is not open", session);
+    }
+    if (allowed != nullptr && n_words < b->mask_words) {
+        return fail(GEIST_E_INVALID_ARG, "session_set_logit_mask: %zu words hold fewer than n_vocab %zu bits", n_words, b->V);
+    }
+    if (allowed == nullptr && !b->mask_active[(size_t) session]) {
+        return GEIST_OK;
+    }
+    CUDA_TRY(cudaSetDevice(b->ctx->device));
+    if (b->d_mask == nullptr) { /* first mask of this batcher: one row per slot, every column allowed */
+        CUDA_TRY(cudaMalloc((void **) &b->d_mask, b->max_sessions * b->mask_words * 4));
+        CUDA_TRY(cudaMemset(b->d_mask, 0xff, b->max_sessions * b->mask_words * 4));
+    }
+    uint32_t *row = b->d_mask + (size_t) session * b->mask_words;
+    if (allowed != nullptr) {
+        CUDA_TRY(cudaMemcpy(row, allowed, b->mask_words * 4, cudaMemcpyHostToDevice));
+    } else {
+        CUDA_TRY(cudaMemset(row, 0xff, b->mask_words * 4));
+    }
+    const char now = allowed != nullptr ? 1 : 0;
+    b->n_mask_active += (size_t) now - (size_t) b->mask_active[(size_t) session];
+    b->mask_active[(size_t) session] = now;
+    return GEIST_OK;
+}
+
+/* geist_session_peek_logits (geist_util.h:195-211, arch.c:163-195): the row the session's pending token was
+ * sampled from, copied into storage that belongs to the session, with the model's soft cap applied. */
+extern "C" const float *geist_b200_session_peek_logits(struct geist_b200_batcher *b, int32_t session, size_t *n_logits) {
+    if (n_logits == nullptr) {
+        return nullptr;
+    }
+    *n_logits = 0;
+    if (b == nullptr) {
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    if (!slot_ok(b, session) || !b->last_row[(size_t) session].valid || b->pending[(size_t) session] < 0) {
+        return nullptr; /* nothing pending */
+    }
+    if (cudaSetDevice(b->ctx->device) != cudaSuccess) {
+        return nullptr;
+    }
+    cudaStream_t        st    = b->ctx->stream;
+    std::vector<float> &stage = b->peek_stage[(size_t) session];
+    try {
+        stage.resize(b->V);
+    } catch (const std::bad_alloc &) {
+        fail(GEIST_E_OOM, "session_peek_logits: no host memory for %zu floats", b->V);
+        return nullptr;
+    }
+    const float c  = b->h_cap[(size_t) session];
+    cudaError_t e  = cudaMemcpyAsync(b->d_peek, b->last_row[(size_t) session].ptr, b->V * 4, cudaMemcpyDeviceToDevice, st);
+    if (e == cudaSuccess && c > 0.0f) {
+        e = gb::launch_softcap_row(b->d_peek, (int) b->V, c, st);
+    }
+    if (e == cudaSuccess) {
+        e = cudaMemcpyAsync(stage.data(), b->d_peek, b->V * 4, cudaMemcpyDeviceToHost, st);
+    }
+    if (e == cudaSuccess) {
+        e = cudaStreamSynchronize(st);
+    }
+    if (e != cudaSuccess) {
+        fail(GEIST_E_BACKEND, "session_peek_logits: %s", cudaGetErrorString(e));
+        return nullptr;
+    }
+    *n_logits = b->V;
+    return stage.data();
+}
+
+namespace {
+int spec_min_L() { /* session.c:583-591: GEIST_SPEC_MIN_L, default 2, read once */
+    static const int v = [] {
+        const char *env = getenv("GEIST_SPEC_MIN_L");
+        const long  x   = env != nullptr ? atol(env) : 2;
+        return x <= 0 ? 1 : (x > 8 ? 8 : (int) x);
+    }();
+    return v;
+}
+} /* namespace */
+
+/* The n-gram drafter over caller-held histories (session.c:437-513): host arrays in, host arrays out, the search
+ * itself on the device. No lazy gate here: n_drafts is what the search found. */
+extern "C" enum geist_status geist_b200_draft_ngram(struct geist_b200_ctx *ctx, size_t n_seq, const geist_token_t *histories, size_t history_stride, const int32_t *history_len,
+                                                    const geist_token_t *seeds, size_t k_max, size_t max_suffix, size_t out_capacity, geist_token_t *out_drafts, int32_t *n_drafts,
+                                                    int32_t *match_L) {
+    if (ctx == nullptr || n_seq == 0 || history_len == nullptr || seeds == nullptr || out_drafts == nullptr || n_drafts == nullptr || (histories == nullptr && history_stride > 0)) {
+        return fail(GEIST_E_INVALID_ARG, "draft_ngram: missing argument");
+    }
+    if (k_max == 0 || k_max > GEIST_B200_SPEC_KMAX || out_capacity < k_max + 1 || max_suffix == 0) { /* session.c:540-549 */
+        return fail(GEIST_E_INVALID_ARG, "draft_ngram: k_max must be in [1, %d], out_capacity >= k_max + 1, max_suffix >= 1", GEIST_B200_SPEC_KMAX);
+    }
+    if (n_seq > (1u << 20) || history_stride > 0x7fffffffu) {
+        return fail(GEIST_E_INVALID_ARG, "draft_ngram: sizes out of range");
+    }
+    for (size_t i = 0; i < n_seq; i++) {
+        if (history_len[i] < 0 || (size_t) history_len[i] > history_stride) {
+            return fail(GEIST_E_INVALID_ARG, "draft_ngram: history_len[%zu] = %d outside [0, history_stride]", i, history_len[i]);
+        }
+    }
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    std::lock_guard<std::mutex> lk(ctx->small_mu);
+    const size_t hs = std::max<size_t>(history_stride, 1);
+    int         *d  = nullptr;
+    /* one allocation: histories | lens | seeds | drafts | n | L */
+    const size_t ints = n_seq * (hs + 2 + out_capacity + 2);
+    CUDA_TRY(cudaMalloc((void **) &d, ints * 4));
+    int *d_h = d, *d_len = d_h + n_seq * hs, *d_seed = d_len + n_seq, *d_out = d_seed + n_seq, *d_n = d_out + n_seq * out_capacity, *d_L = d_n + n_seq;
+    cudaStream_t st = ctx->stream;
+    cudaError_t  e  = cudaSuccess;
+    if (history_stride > 0) {
+        e = cudaMemcpyAsync(d_h, histories, n_seq * hs * 4, cudaMemcpyHostToDevice, st);
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_len, history_len, n_seq * 4, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_seed, seeds, n_seq * 4, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d_out, 0xff, n_seq * out_capacity * 4, st);
+    if (e == cudaSuccess) {
+        e = gb::launch_draft_ngram(nullptr, (int) n_seq, d_h, (long long) hs, d_len, nullptr, d_seed, nullptr, (int) k_max, (int) std::min<size_t>(max_suffix, 8), 1, (int) out_capacity, d_out,
+                                   d_n, d_L, st);
+    }
+    std::vector<int> hL(n_seq);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(out_drafts, d_out, n_seq * out_capacity * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(n_drafts, d_n, n_seq * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(hL.data(), d_L, n_seq * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d);
+    if (e != cudaSuccess) {
+        return fail(GEIST_E_BACKEND, "draft_ngram: %s", cudaGetErrorString(e));
+    }
+    if (match_L != nullptr) {
+        memcpy(match_L, hL.data(), n_seq * 4);
+    }
+    return GEIST_OK;
+}
+
+/* The drafting half of geist_session_decode_speculative (session.c:532-591) for n sessions at once: seed = the
+ * session's pending token, context = the session's history ring on the device, max_suffix 4, then the lazy gate.
+ * A session that should decode one token the plain way comes back with n_drafts = 1. */
+extern "C" enum geist_status geist_b200_batcher_propose_drafts(struct geist_b200_batcher *b, size_t n, const int32_t *sessions, size_t k_max, size_t out_capacity,
+                                                               geist_token_t *out_drafts, int32_t *n_drafts, int32_t *match_L) {
+    if (b == nullptr || sessions == nullptr || n == 0 || out_drafts == nullptr || n_drafts == nullptr) {
+        return fail(GEIST_E_INVALID_ARG, "batcher_propose_drafts: missing argument");
+    }
+    if (k_max == 0 || k_max > GEIST_B200_SPEC_KMAX || out_capacity < k_max + 1) { /* session.c:540-549 */
+        return fail(GEIST_E_INVALID_ARG, "batcher_propose_drafts: k_max must be in [1, %d] and out_capacity >= k_max + 1", GEIST_B200_SPEC_KMAX);
+    }
+    if (n > b->max_sessions) {
+        return fail(GEIST_E_INVALID_ARG, "batcher_propose_drafts: %zu sessions in one call, batcher holds %zu", n, b->max_sessions);
+    }
+    std::lock_guard<std::mutex> lk(b->mu);
+    int *h_slot = b->h_pin, *h_seed = h_slot + b->max_sessions, *h_skip = h_seed + b->max_sessions; /* the pinned block is larger than 3 * max_sessions ints */
+    int *h_out  = h_skip + b->max_sessions;
+    for (size_t i = 0; i < n; i++) {
+        if (!slot_ok(b, sessions[i])) {
+            return fail(GEIST_E_INVALID_ARG, "batcher_propose_drafts: session %d is not open", sessions[i]);
+        }
+        const size_t sl = (size_t) sessions[i];
+        if (b->pending[sl] < 0) {
+            return fail(GEIST_E_INVALID_STATE, "batcher_propose_drafts: session %d has no pending token", sessions[i]);
+        }
+        h_slot[i] = sessions[i];
+        h_seed[i] = b->pending[sl];
+        h_skip[i] = b->pending_in_hist[sl] ? 1 : 0;
+    }
+    CUDA_TRY(cudaSetDevice(b->ctx->device));
+    cudaStream_t st = b->ctx->stream;
+    const int    oc = GEIST_B200_SPEC_KMAX + 1; /* row length of the device-side draft table */
+    CUDA_TRY(cudaMemcpyAsync(b->d_slot, h_slot, n * 4, cudaMemcpyHostToDevice, st));
+    CUDA_TRY(cudaMemcpyAsync(b->d_pending, h_seed, n * 4, cudaMemcpyHostToDevice, st));
+    CUDA_TRY(cudaMemcpyAsync(b->d_skip, h_skip, n * 4, cudaMemcpyHostToDevice, st));
+    CUDA_TRY(cudaMemsetAsync(b->d_drafts, 0xff, n * oc * 4, st));
+    CUDA_TRY(gb::launch_draft_ngram(b->d_slot, (int) n, b->d_hist, (long long) std::max<size_t>(b->max_history, 1), b->d_hist_len, b->d_hist_tot, b->d_pending, b->d_skip, (int) k_max, 4,
+                                    spec_min_L(), oc, b->d_drafts, b->d_ndrafts, b->d_matchL, st));
+    int *h_n = h_out + n * oc, *h_L = h_n + n;
+    CUDA_TRY(cudaMemcpyAsync(h_out, b->d_drafts, n * oc * 4, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaMemcpyAsync(h_n, b->d_ndrafts, n * 4, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaMemcpyAsync(h_L, b->d_matchL, n * 4, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    for (size_t i = 0; i < n; i++) {
+        for (size_t j = 0; j < out_capacity; j++) {
+            out_drafts[i * out_capacity + j] = (j < (size_t) oc && (int) j < h_n[i]) ? h_out[i * oc + j] : -1;
+        }
+        n_drafts[i] = h_n[i];
+        if (match_L != nullptr) {
+            match_L[i] = h_L[i];
+        }
+    }
+    return GEIST_OK;
 }
 
 

@@ -157,6 +157,108 @@ __global__ void post_step_kernel(const int *slot, int n_seq, int per_seq, int fi
     }
 }
 
+/* ---------------------------------------------------------- n-gram drafter -- */
+
+/*
+ * propose_drafts_ngram of session.c:437-513, one thread block per sequence. The context is the sequence's
+ * history plus the seed (the token its model predicts next). For L = min(max_suffix, 8) down to 1 the last L
+ * context tokens are looked for at every earlier place p of the history; a place counts if something follows
+ * it inside the history. The reference walks the places newest first, keeps the one with the most following
+ * tokens (capped at k_max - 1) and the newer one on ties: since the capped number can only fall as p grows,
+ * that is the largest (follow, p) pair, which is what the threads reduce with one 64-bit maximum. The first L
+ * with a match ends the search. drafts[b][0] = seed, [1..] the tokens that followed; n_drafts[b] their number;
+ * match_L[b] = L or 0. Below min_L (the lazy gate of session.c:583-591) the sequence is told to decode one
+ * token the plain way: n_drafts[b] = 1, match_L stays what was found.
+ *
+ * The history of sequence b is hist[seq * stride + ((base[seq] + i) % stride)], i < len: a ring when base is
+ * given, a flat row when it is null. skip_last[b] = 1 leaves the newest entry out (the seed itself, when the
+ * sampler already appended it).
+ */
+constexpr int kDraftThreads = 128;
+__global__ void __launch_bounds__(kDraftThreads) draft_ngram_kernel(const int *slot, const int *hist, long long stride, const int *hist_len, const long long *hist_total,
+                                                                     const int *seeds, const int *skip_last, int k_max, int max_suffix, int min_L, int out_stride,
+                                                                     int *drafts, int *n_drafts, int *match_L) {
+    const int       b    = (int) blockIdx.x;
+    const int       seq  = slot ? slot[b] : b;
+    const int       full = hist_len[seq];
+    const int       len  = max(0, full - (skip_last ? skip_last[b] : 0));
+    const long long base = hist_total ? hist_total[seq] - (long long) full : 0ll;
+    const int      *row  = hist + (size_t) seq * (size_t) stride;
+    const int       seed = seeds[seq];
+    auto            H    = [&](int i) { return row[(size_t) ((base + (long long) i) % stride)]; };
+    __shared__ unsigned long long best;
+    int *out = drafts + (size_t) b * (size_t) out_stride;
+    if (threadIdx.x == 0) {
+        out[0]     = seed;
+        n_drafts[b] = 1;
+        match_L[b]  = 0;
+    }
+    if (k_max <= 1 || len == 0) {
+        return;
+    }
+    const int want = k_max - 1;
+    for (int L = min(max_suffix, 8); L >= 1; L--) {
+        if (L - 1 > len) {
+            continue;
+        }
+        const int tail = len - (L - 1); /* the context's history part starts here; also the number of places */
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            best = 0ull;
+        }
+        __syncthreads();
+        unsigned long long mine = 0ull;
+        for (int p = (int) threadIdx.x; p < tail; p += kDraftThreads) {
+            if (p + L >= len || H(p + L - 1) != seed) {
+                continue;
+            }
+            bool ok = true;
+            for (int i = 0; i + 1 < L && ok; i++) {
+                ok = H(p + i) == H(tail + i);
+            }
+            if (ok) {
+                const int follow = min(len - (p + L), want);
+                mine             = max(mine, ((unsigned long long) follow << 32) | (unsigned long long) (unsigned) (p + 1));
+            }
+        }
+        if (mine != 0ull) {
+            atomicMax(&best, mine);
+        }
+        __syncthreads();
+        const unsigned long long got = best;
+        if (got != 0ull) {
+            const int follow = (int) (got >> 32), p = (int) (got & 0xffffffffull) - 1;
+            for (int i = (int) threadIdx.x; i < follow; i += kDraftThreads) {
+                out[1 + i] = H(p + L + i);
+            }
+            if (threadIdx.x == 0) {
+                match_L[b]  = L;
+                n_drafts[b] = (1 + follow > 1 && L >= min_L) ? 1 + follow : 1;
+            }
+            return;
+        }
+    }
+}
+
+cudaError_t launch_draft_ngram(const int *slot, int n_seq, const int *hist, long long stride, const int *hist_len, const long long *hist_total, const int *seeds, const int *skip_last,
+                               int k_max, int max_suffix, int min_L, int out_stride, int *drafts, int *n_drafts, int *match_L, cudaStream_t stream) {
+    draft_ngram_kernel<<<n_seq, kDraftThreads, 0, stream>>>(slot, hist, stride, hist_len, hist_total, seeds, skip_last, k_max, max_suffix, min_L, out_stride, drafts, n_drafts, match_L);
+    return cudaGetLastError();
+}
+
+/* The output head's soft cap on one dense row, in place: what peek_logits hands to value consumers
+ * (arch.c:185-195; the expression of head.c:154). */
+__global__ void softcap_row_kernel(float *row, int n, float c) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        row[i] = __fmul_rn(tanhf(__fdiv_rn(row[i], c)), c);
+    }
+}
+
+cudaError_t launch_softcap_row(float *row, int n, float c, cudaStream_t stream) {
+    softcap_row_kernel<<<(n + 1023) / 1024, 256, 0, stream>>>(row, n, c);
+    return cudaGetLastError();
+}
+
 /* ------------------------------------------------------------- dense helpers -- */
 
 /* probs[row, :] = 0, then kept entries scattered: the post-filter probability vector. */

@@ -86,7 +86,7 @@ struct SampleParams {
     const float *freq;        /* [n_seq] or null */
     const float *pres;        /* [n_seq] or null */
     const float *softcap;     /* [n_seq] or null: final-logit soft cap of the sequence's model (0 = none) */
-    const unsigned *mask;     /* [n_seq in call order, mask_stride] or null: bit i set = column i may be sampled */
+    const unsigned *mask;     /* [n_seq, mask_stride] or null: bit i set = column i may be sampled */
     long long       mask_stride; /* 32-bit words per mask row */
 
     const int *hist;          /* [n_seq, hist_stride] or null */

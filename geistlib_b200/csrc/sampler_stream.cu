@@ -224,7 +224,7 @@ __device__ __forceinline__ RowCfg row_config(const SampleParams &p, int row, con
     r.pres   = c.pres;
     /* head.c:145-159: the cap is skipped for greedy rows (monotone, the argmax is the same) */
     r.cap    = (c.cap > 0.0f && r.T > 0.0f) ? c.cap : 0.0f;
-    r.mrow   = p.mask ? p.mask + (size_t) r.seq0 * (size_t) p.mask_stride : nullptr;
+    r.mrow   = p.mask ? p.mask + (size_t) r.seq * (size_t) p.mask_stride : nullptr;
     r.hrow   = p.hist ? p.hist + (size_t) r.seq * (size_t) p.hist_stride : nullptr;
     r.erow   = p.extra ? p.extra + (size_t) r.seq0 * (size_t) p.extra_stride : nullptr; /* per call, not per slot */
     return r;

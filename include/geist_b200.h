@@ -331,6 +331,58 @@ enum geist_status geist_b200_batcher_verify(struct geist_b200_batcher *b, size_t
                                             int logits_on_host, int append_history, int32_t *accepted,
                                             int32_t *n_out, geist_token_t *out_tokens);
 
+/* ---- pending token (arch.c:133-161) ------------------------------------------
+ * A session holds the token its last sampled row predicted until somebody hands it out:
+ * geist_b200_batcher_step samples a row and makes the token pending (and returns it);
+ * geist_b200_batcher_decode_step is op_decode_step's cadence, batched: it returns each session's
+ * pending token and makes the token sampled from `logits` (the model's output for that pending
+ * token) the new pending one; GEIST_E_INVALID_STATE, with nothing changed, when a session has
+ * none pending. geist_b200_batcher_verify takes fed[i][0] from the session when the caller
+ * writes a negative id there (same error when nothing is pending) and leaves the session without
+ * a pending token: the last emitted one still has to go through the model. */
+enum geist_status geist_b200_batcher_decode_step(struct geist_b200_batcher *b, size_t n, const int32_t *sessions,
+                                                 const float *logits, size_t row_stride, int logits_on_host,
+                                                 int append_history, geist_token_t *out_tokens);
+/* op_peek_next_token (arch.c:155-160): the pending token, -1 when there is none. */
+geist_token_t geist_b200_session_peek_next_token(struct geist_b200_batcher *b, int32_t session);
+
+/* geist_session_peek_logits (geist_util.h:195-211; arch.c:163-195): the logits row the pending token
+ * was sampled from, as a HOST copy that belongs to the session and stays valid until the session's
+ * next sampling call; the model's soft cap (below) is applied, penalties and mask are not. NULL and
+ * *n_logits = 0 when nothing is pending. The row is read where it lay when it was sampled: device
+ * logits passed to the batcher must still be alive and unchanged; host logits are read from the
+ * batcher's own staging copy, which lives until its next call with host logits. */
+const float *geist_b200_session_peek_logits(struct geist_b200_batcher *b, int32_t session, size_t *n_logits);
+
+/* The final-logit soft cap of the session's model (config.logit_softcap, head.c:145-159); 0 = none. */
+enum geist_status geist_b200_session_set_softcap(struct geist_b200_batcher *b, int32_t session, float softcap);
+/* Constrained decoding (EXTENSION): bit i of `allowed` set = column i may be sampled; n_words >=
+ * ceil(n_vocab / 32); NULL lifts the mask. HOST array, copied. Holds until it is replaced or lifted. */
+enum geist_status geist_b200_session_set_logit_mask(struct geist_b200_batcher *b, int32_t session, const uint32_t *allowed,
+                                                    size_t n_words);
+
+/* ---- n-gram drafter (session.c:437-513) -----------------------------------------
+ * propose_drafts_ngram for n_seq sequences at once, searched on the device: the longest suffix
+ * (<= max_suffix, at most 8) of history + [seed] that occurs earlier in the history, the place with
+ * the most following tokens, the most recent on ties. HOST arrays: histories [n_seq, history_stride],
+ * history_len [n_seq], seeds [n_seq]; out_drafts [n_seq, out_capacity] (drafts[0] = seed, unused
+ * tail -1), n_drafts [n_seq] (>= 1), match_L [n_seq] or NULL (0 = no match). As in
+ * geist_session_decode_speculative (session.c:540-549): 1 <= k_max <= GEIST_B200_SPEC_KMAX and
+ * out_capacity >= k_max + 1, else GEIST_E_INVALID_ARG. Synchronous. */
+enum geist_status geist_b200_draft_ngram(struct geist_b200_ctx *ctx, size_t n_seq, const geist_token_t *histories,
+                                         size_t history_stride, const int32_t *history_len, const geist_token_t *seeds,
+                                         size_t k_max, size_t max_suffix, size_t out_capacity, geist_token_t *out_drafts,
+                                         int32_t *n_drafts, int32_t *match_L);
+/* The drafting half of geist_session_decode_speculative (session.c:553-591) for n sessions: seed = the
+ * session's pending token (GEIST_E_INVALID_STATE when none), context = the session's history ring on
+ * the device (its last max_history tokens), max_suffix 4, then the lazy gate: a session whose match is
+ * shorter than GEIST_SPEC_MIN_L (environment, default 2, read once) or that found nothing comes back
+ * with n_drafts = 1 and decodes one token the plain way. The rows with n_drafts > 1 go through the
+ * model's verify pass and geist_b200_batcher_verify. */
+enum geist_status geist_b200_batcher_propose_drafts(struct geist_b200_batcher *b, size_t n, const int32_t *sessions,
+                                                    size_t k_max, size_t out_capacity, geist_token_t *out_drafts,
+                                                    int32_t *n_drafts, int32_t *match_L);
+
 /* Launch-shape report for one vocabulary size on the current device: slices a
  * row is cut into, floats per slice, shared memory per CTA, depth of the
  * bulk-copy ring. GEIST_E_UNSUPPORTED when the row cannot be served. */
