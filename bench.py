@@ -50,7 +50,10 @@ N_SETS = 8
 SEED = 1234
 # algorithmic bytes per row: logits once + history ids + generator state in/out + token out
 BYTES_PER_ROW = 4 * V + 4 * H + 16 + 4
-KERNELS_PER_STEP = 3  # sample_stream_kernel, finish_rows_kernel<fast>, finish_rows_kernel<rest>
+# sample_stream_kernel and the small finishing kernel: every session of the workload samples top-k 40, which the caller
+# (here as in the session batcher) tells the launch with finish_hint = GREEDY_TOPK; without the hint a third kernel
+# (the general finisher, idle for these rows) is launched as well -- the "finish_hint=AUTO" entry of `modes`
+KERNELS_PER_STEP = 2
 WORKLOAD = ("B=256 rows x V=128256 fp32 logits ~ N(0,2.5^2) with 8 ids/row +12; temperature 0.8, top_k 40, "
             "top_p 0.95 (top_k precedence), repetition penalty 1.1 over 64-token history, 1 draw/row, seed 1234")
 
@@ -240,7 +243,7 @@ def main():
     rng_b = None
     for i, x in enumerate(sets):
         src = rng_a if i % 2 == 0 else rng_b
-        o = ctx.sample_batch(x, dT, dK, dP, src, rep=dRep, history=hist, history_len=dHl, launch=False)
+        o = ctx.sample_batch(x, dT, dK, dP, src, rep=dRep, history=hist, history_len=dHl, launch=False, finish_hint=api.FINISH_GREEDY_TOPK)
         if i % 2 == 0:
             rng_b = o["rng_state"]
         else:
@@ -342,7 +345,7 @@ def main():
         mode("temperature", T, 0, 1.0, False)
         mode("top_p0.95_gaussian(wide nucleus)", T, 0, TOP_P, False)
         # the same launches with the caller's hint on which finishing kernel they need (one launch fewer)
-        mode("headline, finish_hint=GREEDY_TOPK", T, TOP_K, TOP_P, True, api.FINISH_GREEDY_TOPK)
+        mode("headline, finish_hint=AUTO", T, TOP_K, TOP_P, True, api.FINISH_AUTO)
         mode("greedy, finish_hint=GREEDY_TOPK", 0.0, 0, 1.0, False, api.FINISH_GREEDY_TOPK)
         mode("temperature, finish_hint=GENERAL", T, 0, 1.0, False, api.FINISH_GENERAL)
 
@@ -501,7 +504,7 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows_per_gpu": B, "l2": f"inputs rotate over {N_SETS} sets of 131 MB (> 126 MB L2)",
-                       "launch": {**api.plan(V, H), **api.grid(V, B, H)}, "rows_invalid": bad, "rows_on_slow_path": slow,
+                       "launch": {**api.plan(V, H), **api.grid(V, B, H)}, "finish_hint": "GREEDY_TOPK", "rows_invalid": bad, "rows_on_slow_path": slow,
                        "library": str(LIB_PATH)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "traffic_source": traffic_src, "peak_kind": peak_kind, "bytes_per_launch": B * BYTES_PER_ROW,

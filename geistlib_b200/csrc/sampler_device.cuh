@@ -126,11 +126,28 @@ __device__ __forceinline__ bool mbar_test(unsigned long long *bar, unsigned pari
     return ok != 0;
 }
 
-/* Bounded wait. Returns false when the copy never signalled. */
+/* Bounded wait: gives up kWaitLimitNs after it began (one second of %globaltimer; the count of rounds is a
+ * second limit, should the timer not advance). Returns false when the copy never signalled; the caller then
+ * stops asking for copies and reports the rows it touches as not loaded. */
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long *bar, unsigned parity) {
-    for (int i = 0; i < (1 << 20); i++) {
-        if (mbar_try_wait(bar, parity)) {
-            return true;
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    const unsigned long long t0 = global_ns();
+    for (int round = 0; round < (1 << 22); round++) {
+        for (int i = 0; i < 64; i++) {
+            if (mbar_try_wait(bar, parity)) {
+                return true;
+            }
+        }
+        if (global_ns() - t0 > kWaitLimitNs) {
+            return false;
         }
     }
     return false;

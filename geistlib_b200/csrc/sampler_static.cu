@@ -170,7 +170,9 @@ int argmax_rows_static_max_rows(long long n_vocab) {
  * Looks the scratch address up on first use of a device (with that device current) and
  * launches. Returns cudaSuccess or the failing call's code; *what names the call.
  * Nothing here allocates device memory: cudaGetSymbolAddress only returns where the
- * module's own image already placed the array.
+ * module's own image already placed the array. The address is looked up once per device and
+ * kept for the life of the process: after cudaDeviceReset (or any other teardown of the
+ * device's primary context) it is stale and this entry must not be called again.
  */
 cudaError_t launch_argmax_rows_static(int device, const float *logits, long long row_stride, int n_rows, int V, int *out, cudaStream_t stream, const char **what) {
     static std::mutex     mu;
@@ -180,10 +182,28 @@ cudaError_t launch_argmax_rows_static(int device, const float *logits, long long
         *what = "device index";
         return cudaErrorInvalidDevice;
     }
-    cudaError_t e = cudaSetDevice(device);
+    /* the caller's current device is put back on every way out */
+    struct DeviceGuard {
+        int prev = -1;
+        ~DeviceGuard() {
+            if (prev >= 0) {
+                cudaSetDevice(prev);
+            }
+        }
+    } guard;
+    int         cur = -1;
+    cudaError_t e   = cudaGetDevice(&cur);
     if (e != cudaSuccess) {
-        *what = "cudaSetDevice";
+        *what = "cudaGetDevice";
         return e;
+    }
+    if (cur != device) {
+        e = cudaSetDevice(device);
+        if (e != cudaSuccess) {
+            *what = "cudaSetDevice";
+            return e;
+        }
+        guard.prev = cur;
     }
     StaticScratch *scratch;
     {

@@ -17,14 +17,23 @@
  *   id of the first), placed by one ballot and two stores into the warp's own list. Temperature and top-p rows
  *   also sum expf((x - warp maximum) * inv_t) per warp and slice.
  *
- *   Part boundaries. The thread block meets, writes one record and its candidate groups to global scratch and
- *   adds the part's slices to the row's counter. The thread block whose add completes the row finishes it: it
- *   merges the parts' records, expands and orders the few surviving candidates, evaluates their probabilities
- *   exactly and makes the draw (its own part's candidates never leave shared memory). The other thread block of
- *   the SM streams on meanwhile.
+ *   Before any of this a row's share may pass the soft cap tanhf(x / c) * c and the mask of allowed columns,
+ *   in place in the stage (head.c:145-159; only launches that carry one pay for it).
  *
- * Rows whose kept set is too large for this (top-k beyond 256, wide top-p nuclei) are served by the finishing
- * thread block with radix walks over a private copy of the row in global scratch.
+ *   Part boundaries. The thread block meets and writes the part's record (maximum, first id, threshold, sums;
+ *   two 16-byte slots) followed by its candidate groups to the part's place in global scratch. Nothing else is
+ *   shared between thread blocks: no counters, no thread block waits for another one.
+ *
+ *   Finishing is left to kernels of their own behind the stream kernel, launched as programmatic dependents so
+ *   that their thread blocks are placed while the kernel before them drains. finish_rows_kernel<true>: one thread
+ *   block per row merges the parts' records; greedy rows end there; top-k rows (k <= 256) get their surviving
+ *   candidates ordered, their probabilities evaluated exactly (double exp rounded once) and the draw made; every
+ *   other row goes on a list. finish_rows_kernel<false> takes that list: temperature rows walk the per-warp
+ *   segment sums and re-read the one segment that the draw falls into; top-p rows with a small nucleus are
+ *   served from the candidates and the sums of the rest; rows whose kept set is too large for one pass (top-k
+ *   beyond 256, wide nuclei) get radix walks over a private copy of the row in global scratch (the multi-pass
+ *   path, ROW_SLOW_PATH). A caller that knows its rows' modes drops the kernel it does not need (F_FAST_ONLY /
+ *   F_REST_ONLY). Histories of more than kRowIds ids are counted per row by row_ids_kernel ahead of all this.
  *
  * Semantics follow geistlib's CPU sampler:
  *   mode dispatch ............ src/archs/transformer/forward/head.c:172-183
@@ -40,7 +49,11 @@
 
 namespace gb {
 
-/* Optional time line of every thread block (build with -DGB_PROFILE): %globaltimer at five points of its life. */
+/* Optional instrumentation, compiled in with -DGB_PROFILE (and -DGB_PROFILE_CYC): PROF(i) stamps %globaltimer
+ * at fixed points of a thread block's life (stream kernel 0-4, finishing kernels 5-13), MP(i) at the stages of
+ * the multi-pass path, CYC(i) adds up a warp's cycles per section of the stream kernel's slice loop (0 wait for
+ * data, 1 load + maxima + refill, 2 argmax / capture / raise, 4 loop top, 5 part set-up, 6 part end, 7 first
+ * slice's threshold). The arrays are read back through geist_b200_debug_*. All of it is empty otherwise. */
 #ifdef GB_PROFILE
 __device__ long long g_prof[1024][16];
 __device__ __forceinline__ long long gtime() {
@@ -55,6 +68,11 @@ __device__ __forceinline__ long long gtime() {
 #define PROF_ONCE(i)                                                       \
     if (threadIdx.x == 0 && blockIdx.x < 1024 && g_prof[blockIdx.x][i] == 0) { \
         g_prof[blockIdx.x][i] = gtime();                                   \
+    }
+__device__ long long g_mp[1024][24];
+#define MP(i)                                          \
+    if (threadIdx.x == 0 && blockIdx.x < 1024) {       \
+        g_mp[blockIdx.x][i] = gtime();                 \
     }
 #ifdef GB_PROFILE_CYC
 __device__ long long g_cyc[1024][kWarps][8];
@@ -79,6 +97,7 @@ __device__ long long g_cyc[1024][kWarps][8];
 #define CYC_DONE()
 #endif
 #else
+#define MP(i)
 #define PROF(i)
 #define PROF_ONCE(i)
 #define CYC_INIT()
@@ -441,12 +460,17 @@ __device__ __forceinline__ void row_sweep(const Grp &g, const float *row, int V,
     const int     V4 = V >> 2;
     const float4 *p4 = reinterpret_cast<const float4 *>(row);
     int           j  = g.tid;
-    for (; j + 3 * g.n < V4; j += 4 * g.n) { /* four loads in flight per thread */
-        const float4 a = p4[j], b = p4[j + g.n], c = p4[j + 2 * g.n], d = p4[j + 3 * g.n];
-        f(a.x, 4 * j), f(a.y, 4 * j + 1), f(a.z, 4 * j + 2), f(a.w, 4 * j + 3);
-        f(b.x, 4 * (j + g.n)), f(b.y, 4 * (j + g.n) + 1), f(b.z, 4 * (j + g.n) + 2), f(b.w, 4 * (j + g.n) + 3);
-        f(c.x, 4 * (j + 2 * g.n)), f(c.y, 4 * (j + 2 * g.n) + 1), f(c.z, 4 * (j + 2 * g.n) + 2), f(c.w, 4 * (j + 2 * g.n) + 3);
-        f(d.x, 4 * (j + 3 * g.n)), f(d.y, 4 * (j + 3 * g.n) + 1), f(d.z, 4 * (j + 3 * g.n) + 2), f(d.w, 4 * (j + 3 * g.n) + 3);
+    for (; j + 7 * g.n < V4; j += 8 * g.n) { /* eight loads in flight per thread */
+        float4 v[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            v[q] = p4[j + q * g.n];
+        }
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            const int b = 4 * (j + q * g.n);
+            f(v[q].x, b), f(v[q].y, b + 1), f(v[q].z, b + 2), f(v[q].w, b + 3);
+        }
     }
     for (; j < V4; j += g.n) {
         const float4 x = p4[j];
@@ -462,7 +486,27 @@ __device__ __forceinline__ void row_sweep(const Grp &g, const float *row, int V,
 
 template <class F>
 __device__ __forceinline__ void row_rewrite(const Grp &g, float *row, int V, F &&f) {
-    for (int i = g.tid; i < V; i += g.n) {
+    /* private copies start on 16-byte boundaries: four values per access, four accesses in flight per thread */
+    const int V4 = V >> 2;
+    float4   *p4 = reinterpret_cast<float4 *>(row);
+    int       j  = g.tid;
+    for (; j + 3 * g.n < V4; j += 4 * g.n) {
+        float4 a = p4[j], b = p4[j + g.n], c = p4[j + 2 * g.n], d = p4[j + 3 * g.n];
+        a.x = f(a.x, 4 * j), a.y = f(a.y, 4 * j + 1), a.z = f(a.z, 4 * j + 2), a.w = f(a.w, 4 * j + 3);
+        p4[j] = a;
+        b.x = f(b.x, 4 * (j + g.n)), b.y = f(b.y, 4 * (j + g.n) + 1), b.z = f(b.z, 4 * (j + g.n) + 2), b.w = f(b.w, 4 * (j + g.n) + 3);
+        p4[j + g.n] = b;
+        c.x = f(c.x, 4 * (j + 2 * g.n)), c.y = f(c.y, 4 * (j + 2 * g.n) + 1), c.z = f(c.z, 4 * (j + 2 * g.n) + 2), c.w = f(c.w, 4 * (j + 2 * g.n) + 3);
+        p4[j + 2 * g.n] = c;
+        d.x = f(d.x, 4 * (j + 3 * g.n)), d.y = f(d.y, 4 * (j + 3 * g.n) + 1), d.z = f(d.z, 4 * (j + 3 * g.n) + 2), d.w = f(d.w, 4 * (j + 3 * g.n) + 3);
+        p4[j + 3 * g.n] = d;
+    }
+    for (; j < V4; j += g.n) {
+        float4 x = p4[j];
+        x.x = f(x.x, 4 * j), x.y = f(x.y, 4 * j + 1), x.z = f(x.z, 4 * j + 2), x.w = f(x.w, 4 * j + 3);
+        p4[j] = x;
+    }
+    for (int i = (V4 << 2) + g.tid; i < V; i += g.n) {
         row[i] = f(row[i], i);
     }
 }
@@ -504,8 +548,12 @@ struct RadixOut {
  * hold copies * 256 doubles / ints.
  */
 template <bool kUnit = false, class KeyF, class MassF>
-__device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *hc, int copies, const float *row, int V, double target, bool inclusive, KeyF &&key,
+__device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *hc, int copies, double scale, const float *row, int V, double target, bool inclusive, KeyF &&key,
                                MassF &&mass) {
+    /* masses are summed as 64-bit fixed point (mass * scale, truncated): integer adds in shared memory are one
+     * instruction whatever the conflicts, and the sums do not depend on the order. The caller picks a scale that
+     * keeps the row's total below 2^63. */
+    unsigned long long *hq = reinterpret_cast<unsigned long long *>(hm);
     RadixOut out;
     out.found   = true;
     out.key     = 0u;
@@ -515,11 +563,11 @@ __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *h
     for (int level = 3; level >= 0; level--) {
         const int shift = 8 * level;
         for (int i = g.tid; i < copies * 256; i += g.n) {
-            hm[i] = 0.0;
+            hq[i] = 0ull;
             hc[i] = 0;
         }
         g.sync();
-        double        *mym = hm + (g.warp % copies) * 256;
+        unsigned long long *mym = hq + (g.warp % copies) * 256;
         int           *myc = hc + (g.warp % copies) * 256;
         const unsigned pre = out.key;
         row_sweep(g, row, V, [&](float x, int i) {
@@ -531,7 +579,7 @@ __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *h
                 } else {
                     const double m = mass(x, i);
                     if (m > 0.0) {
-                        atomicAdd(&mym[d], m);
+                        atomicAdd(&mym[d], __double2ull_rz(m * scale));
                         atomicAdd(&myc[d], 1);
                     }
                 }
@@ -547,15 +595,13 @@ __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *h
 #pragma unroll
             for (int q = 0; q < 8; q++) {
                 const int b = 255 - (8 * g.lane + q);
-                m8[q]       = 0.0;
-                c8[q]       = 0;
+                unsigned long long q8 = 0ull;
+                c8[q]                 = 0;
                 for (int w = 0; w < copies; w++) {
-                    m8[q] += hm[w * 256 + b];
+                    q8 += hq[w * 256 + b];
                     c8[q] += hc[w * 256 + b];
                 }
-                if (kUnit) {
-                    m8[q] = (double) c8[q];
-                }
+                m8[q] = kUnit ? (double) c8[q] : (double) q8 / scale;
                 lane_m += m8[q];
                 lane_c += c8[q];
             }
@@ -653,6 +699,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
     const float *src      = p.logits + (size_t) r.row * (size_t) p.row_stride;
     int         *kept_i   = p.kept_cap > 0 ? p.kept_idx + (size_t) r.row * (size_t) p.kept_cap : nullptr;
     float       *kept_v   = p.kept_cap > 0 ? p.kept_val + (size_t) r.row * (size_t) p.kept_cap : nullptr;
+    MP(0);
     /* private copy of the row, penalties applied once */
     if (p.aligned) { /* rows start on 16-byte boundaries: four values per load */
         const float4 *s4 = reinterpret_cast<const float4 *>(src);
@@ -688,6 +735,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
     } else {
         g.sync();
     }
+    MP(1);
     /* the fast path's slice records need not carry the maximum: take it from the copy */
     row_max = -CUDART_INF_F;
     row_arg = 0x7fffffff;
@@ -698,11 +746,12 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
         }
     });
     group_argmax(g, sh, row_max, row_arg);
+    MP(2);
     if (r.mode == M_TOPK) {
         /* the k-th entry in (value desc, id asc) order: a radix walk on counts, then the ids of its ties */
         auto                     okey   = [](float x) { return order_key(x); };
         auto                     one    = [](float, int) { return 1.0; };
-        const RadixOut           rs     = radix_mass<true>(g, sh, hm, hc, copies, gr, V, (double) r.k, true, okey, one);
+        const RadixOut           rs     = radix_mass<true>(g, sh, hm, hc, copies, 1.0, gr, V, (double) r.k, true, okey, one);
         const unsigned long long t_set  = rs.found ? resolve_ties(g, sh, gr, V, idx_bits, rs, (double) r.k, true, okey, one) : 0ull;
         auto                     in_set = [&](float x, int i) { return composite(order_key(x), i, idx_bits) >= t_set; };
         if (r.select_only) {
@@ -736,7 +785,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
             /* the pick is the earliest walk position whose running sum exceeds u: the largest
              * word t with mass{word >= t} > u */
             auto                     qmass  = [&](float x, int i) { return in_set(x, i) ? qof(x) : 0.0; };
-            const RadixOut           rp     = radix_mass(g, sh, hm, hc, copies, gr, V, u, false, okey, qmass);
+            const RadixOut           rp     = radix_mass(g, sh, hm, hc, copies, 0x1p49, gr, V, u, false, okey, qmass); /* weights <= 1, at most 8192 of them */
             unsigned long long       t_pick = rp.found ? resolve_ties(g, sh, gr, V, idx_bits, rp, u, false, okey, qmass) : 0ull;
             if (t_pick < t_set) {
                 t_pick = t_set;
@@ -765,8 +814,10 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
             return e;
         });
         const double S = group_sum_d(g, sh, acc);
+        MP(3);
         row_rewrite(g, gr, V, [&](float e, int) { return __double2float_rn((double) e / S); });
         g.sync();
+        MP(4);
         auto keyf  = [](float pv) { return __float_as_uint(pv); }; /* p >= 0: the bits are ordered */
         auto massf = [](float pv, int) { return (double) pv; };
         /* cutoff: first walk position whose running sum reaches top_p, inclusive */
@@ -781,7 +832,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
                 return k >= k_lo ? (min(k, k_hi) - k_lo) << ls : 0u;
             };
             auto mw = [&](float pv, int i) { return keyf(pv) >= k_lo ? mass_in(pv, i) : 0.0; };
-            RadixOut ro = radix_mass(g, sh, hm, hc, copies, gr, V, target, inclusive, kw, mw);
+            RadixOut ro = radix_mass(g, sh, hm, hc, copies, 0x1p62, gr, V, target, inclusive, kw, mw); /* probabilities: the row adds up to 1 */
             ro.key      = (ro.key >> ls) + k_lo; /* back to the key itself */
             return ro;
         };
@@ -792,7 +843,9 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
         if (!rc.found && k_floor != 0u) {
             rc = windowed(0u, k_top, (double) r.top_p, true, massf); /* rounding kept the window short of top_p */
         }
+        MP(5);
         const unsigned long long t_cut = rc.found ? resolve_ties(g, sh, gr, V, idx_bits, rc, (double) r.top_p, true, keyf, massf) : 0ull;
+        MP(6);
         double                   nm    = 0.0;
         long long                ncnt  = 0;
         row_sweep(g, gr, V, [&](float pv, int i) {
@@ -802,11 +855,14 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
             }
         });
         const double       N      = group_sum_d(g, sh, nm);
+        MP(7);
         const long long    cut    = group_sum_ll(g, sh, ncnt);
         const double       u      = (double) unit_from(xorshift_next(r.rng)) * N;
         auto               nmass  = [&](float pv, int i) { return composite(keyf(pv), i, idx_bits) >= t_cut ? (double) pv : 0.0; };
         const RadixOut     rk     = windowed((unsigned) (t_cut >> idx_bits), k_top, u, false, nmass);
+        MP(8);
         unsigned long long t_pick = rk.found ? resolve_ties(g, sh, gr, V, idx_bits, rk, u, false, keyf, nmass) : 0ull;
+        MP(9);
         if (t_pick < t_cut) {
             t_pick = t_cut; /* default: the last nucleus entry (sampler.c:292) */
         }
@@ -823,6 +879,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
         }
     }
     g.sync();
+    MP(10);
     return st;
 }
 
@@ -1770,8 +1827,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
     }
 
     CYC_INIT();
-    int j  = 0;
-    int pf = 0; /* warp 0: how far the parameters of the row that begins next have been fetched */
+    int j         = 0;
+    int ring_dead = -1; /* the item at which a copy of this warp failed to arrive in time (-1: none) */
+    int pf        = 0; /* warp 0: how far the parameters of the row that begins next have been fetched */
     while (j < my_count) {
         const int  item0 = my_first + j, row = item0 / p.n_slices, c0 = item0 - row * p.n_slices;
         const int  part_len   = min(p.n_slices - c0, my_count - j);
@@ -1904,9 +1962,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             /* ---- 1. the warp's share of the slice is in its stage; the slice's tail is padded with -inf ---- */
             if (p.aligned) {
                 const int full4 = last_c ? bulk4_l : bulk4_f;
-                if (full4 > 0 && !mbar_wait_bounded(&sh->full[warp][stage], parity)) {
+                if (ring_dead >= 0) {
+                    wst |= ST_LOAD_TIMEOUT; /* every row the warp still touches is reported as not loaded */
+                } else if (full4 > 0 && !mbar_wait_bounded(&sh->full[warp][stage], parity)) {
                     wst |= ST_LOAD_TIMEOUT;
-                    (void) mbar_wait_bounded(&sh->full[warp][stage], parity); /* a second bounded chance for the copy in flight */
+                    ring_dead = j; /* the warp asks for no further copy and waits for none; see the kernel's end */
                 }
                 if (nv4 * 4 > body && w4lo + mine4 == nv4 && mine4 > 0) {
                     wrote = true;
@@ -1933,13 +1993,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
 
             /* ---- 2. penalties on the share ---- */
             if (pen_on) {
-                wrote = true;
+                bool touched = false; /* most shares hold none of the row's ids: those need no fence before the refill */
                 if (!long_ids) {
                     const int rn = sh->rl_n;
                     for (int e = lane; e < rn; e += 32) {
                         const int li = sh->rl_id[e] - s0;
                         if (li >= 4 * w4lo && li < 4 * (w4lo + mine4) && li < n) {
                             sl[li - 4 * w4lo] = penalise(sl[li - 4 * w4lo], sh->rl_cnt[e], rep, freq, pres);
+                            touched           = true;
                         }
                     }
                 } else {
@@ -1950,10 +2011,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                         const int      li = (int) (e & ((1u << kLiBits) - 1u));
                         if (li >= 4 * w4lo && li < 4 * (w4lo + mine4) && li < n) {
                             sl[li - 4 * w4lo] = penalise(sl[li - 4 * w4lo], (int) (e >> kLiBits), rep, freq, pres);
+                            touched           = true;
                         }
                     }
                 }
-                __syncwarp();
+                wrote |= __any_sync(0xffffffffu, touched); /* also orders the stores before the loads below */
             }
             if (p.out_logits != nullptr) {
                 float *orow = p.out_logits + (size_t) row * (size_t) p.V + s0;
@@ -1974,7 +2036,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                 bv    = fmaxf(bv, gm[i]);
             }
             CYC(1);
-            CYC(3);
             const unsigned bkey = order_key(bv + 0.0f); /* -0 and +0 are one value, as the comparison of floats has it */
             const bool     own  = lane < mine4;
             const unsigned wkey = __reduce_max_sync(0xffffffffu, own ? bkey : 0u);
@@ -2114,7 +2175,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             CYC(2);
             /* the stage is free again: the warp refills it itself */
             __syncwarp();
-            if (lane == 0 && p.aligned && j + kStages < my_count) {
+            if (lane == 0 && p.aligned && j + kStages < my_count && ring_dead < 0) {
                 if (wrote) { /* ordinary stores of this warp come before the copy engine's */
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
@@ -2241,6 +2302,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
         __syncthreads(); /* the lists are free for the next part */
         CYC(6);
     }
+    if (ring_dead >= 0 && p.aligned) {
+        /* copies that were asked for before the warp gave up (the item it gave up on and the one behind it) may
+         * still be on their way into this thread block's shared memory: one more bounded wait for each before the
+         * thread block may end */
+        for (int jj = ring_dead; jj < min(ring_dead + kStages, my_count); jj++) {
+            (void) mbar_wait_bounded(&sh->full[warp][jj % kStages], (unsigned) (jj / kStages) & 1u);
+        }
+    }
     CYC_DONE();
     PROF(4);
 }
@@ -2270,14 +2339,20 @@ __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_c
     g.n    = kThreads;
     g.nw   = kWarps;
     g.bar  = 0;
+    const bool all_rows = kFast || (p.flags & F_REST_ONLY) != 0u;
+    /* The first row's parameters are inputs of the launch, written before the stream kernel began: they may be
+     * read while that kernel's last thread blocks are still at work. Everything it wrote waits for the line below. */
+    RawCfg rc0{};
+    if (all_rows && (int) blockIdx.x < p.n_rows) {
+        rc0 = raw_config(p, (int) blockIdx.x, true);
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory"); /* the records of the kernel before this one are complete and visible */
     asm volatile("griddepcontrol.launch_dependents;");
     PROF(kFast ? 5 : 7);
-    const bool all_rows = kFast || (p.flags & F_REST_ONLY) != 0u;
     const int  n_todo   = all_rows ? p.n_rows : min(__ldcg(p.def_count), p.n_rows);
     for (int it = (int) blockIdx.x; it < n_todo; it += (int) gridDim.x) {
         const int row = all_rows ? it : __ldcg(&p.def_rows[it]);
-        const RawCfg rc = raw_config(p, row, true);
+        const RawCfg rc = (all_rows && it == (int) blockIdx.x) ? rc0 : raw_config(p, row, true);
         RowCfg       r  = row_config(p, row, rc, true);
         PROF(8);
         int          st = finish_row<kFast>(g, p, sh, r, cmem, q_items, r_items);
@@ -2426,6 +2501,7 @@ __global__ void __launch_bounds__(kRowIdThreads) row_ids_kernel(const __grid_con
 /* ----------------------------------------------------------------- launchers -- */
 
 #ifdef GB_PROFILE
+extern "C" int geist_b200_debug_mp(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_mp, sizeof(long long) * 1024 * 24); }
 extern "C" int geist_b200_debug_prof(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 1024 * 16); }
 #ifdef GB_PROFILE_CYC
 extern "C" int geist_b200_debug_cyc(long long *out) { return (int) cudaMemcpyFromSymbol(out, g_cyc, sizeof(long long) * 1024 * kWarps * 8); }

@@ -152,10 +152,10 @@ struct geist_b200_batch {
     const float   *frequency_penalty;  /* per sequence or NULL   (EXTENSION) */
     const float   *presence_penalty;   /* per sequence or NULL   (EXTENSION) */
     const int32_t *history;            /* [*, history_stride] or NULL */
-    size_t         history_stride;     /* also the longest history a row can have. GEIST_E_UNSUPPORTED when the id lists of the
-                                        * slices in flight no longer fit shared memory beside one stage of logits (about 7000 ids
-                                        * per row at 128256 columns, never more than 8192). Rows of more than 128 ids cost one
-                                        * more kernel launch. */
+    size_t         history_stride;     /* also the longest history a row can have: at most 8192 ids per row (history plus
+                                        * fed tokens), else GEIST_E_UNSUPPORTED. A batch whose rows can bring more than 256 ids
+                                        * costs one more kernel launch (the rows' distinct ids are counted ahead of the stream
+                                        * kernel). */
     const int32_t *history_len;        /* per sequence */
     const int32_t *fed_tokens;         /* optional [n_seq, fed_stride]: row r also counts fed[1..r] */
     size_t         fed_stride;
@@ -384,8 +384,8 @@ enum geist_status geist_b200_batcher_propose_drafts(struct geist_b200_batcher *b
                                                     int32_t *n_drafts, int32_t *match_L);
 
 /* Launch-shape report for one vocabulary size on the current device: slices a
- * row is cut into, floats per slice, shared memory per CTA, depth of the
- * bulk-copy ring. GEIST_E_UNSUPPORTED when the row cannot be served. */
+ * row is cut into, floats per slice, shared memory per thread block, stages of
+ * each warp's bulk-copy ring. GEIST_E_UNSUPPORTED when the row cannot be served. */
 enum geist_status geist_b200_plan(size_t n_vocab, size_t max_history, int32_t *slices_per_row, int32_t *slice,
                                   int32_t *smem_bytes, int32_t *ring_stages);
 
@@ -405,8 +405,13 @@ enum geist_status geist_b200_grid(size_t n_vocab, size_t max_history, size_t n_r
  * and geist_b200_errmsg() says what would fit. Every call on a device shares that
  * array: calls that overlap in time (different streams or threads) race and must be
  * serialised by the caller. The first call on a device looks the array's address up
- * (set-up; make that call before any stream capture begins). Asynchronous on `stream`
- * (cudaStream_t as void*, NULL = the legacy default stream). */
+ * (set-up; make that call before any stream capture begins) and keeps it for the life of
+ * the process: after cudaDeviceReset on that device the entry must not be called again.
+ * Asynchronous on `stream` (cudaStream_t as void*, NULL = the legacy default stream): the
+ * indices are in DEVICE memory once the stream reaches that point, so a caller that needs
+ * one on the host (the synchronous argmax_f32 backend slot does) adds a 4-byte copy and a
+ * stream synchronise of its own. The calling thread's current device is the same after the
+ * call as before it. */
 enum geist_status geist_b200_argmax_rows_static(int device, const float *logits, size_t row_stride, size_t n_rows,
                                                 size_t n_vocab, int32_t *out_index, void *stream);
 
