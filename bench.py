@@ -352,11 +352,11 @@ def main():
     # ---- the other configurations of the reference's table (rank 0's GPU; device-resident)
     configs = {}
     if not args.no_configs and rank == 0:
-        def run_cfg(name, xs_np, Tn, Kn, Pn, st_np, rows_per_seq=1, sample=None, hbytes=0, **pen):
+        def run_cfg(name, xs_np, Tn, Kn, Pn, st_np, rows_per_seq=1, sample=None, hbytes=0, hint=0, **pen):
             rows, Vn = xs_np[0].shape
             nseq = rows // rows_per_seq
             cT, cK, cP = per_seq(nseq, Tn, Kn, Pn)
-            kw, okw = {}, {}
+            kw, okw = {"finish_hint": hint}, {}  # the hint a caller that knows the sessions' settings gives (the batcher does)
             if "hist" in pen:
                 kw["history"] = to_dev(pen["hist"])
                 kw["history_len"] = to_dev(np.full(nseq, pen["hist"].shape[1], np.int32))
@@ -384,7 +384,7 @@ def main():
                 checked = rows
             nbytes = rows * (4 * Vn + 4) + nseq * 16 + hbytes
             configs[name] = {"us_per_launch": sec * 1e6, "rows_per_s": rows / sec, "hbm_frac": nbytes / sec / 1e9 / peak,
-                             "rows_checked_against_cpu": checked, "tokens_match_cpu": match,
+                             "finish_hint": ["AUTO", "GREEDY_TOPK", "GENERAL"][hint], "rows_checked_against_cpu": checked, "tokens_match_cpu": match,
                              "rows_invalid": int((out["status"] & api.ROW_INVALID).ne(0).sum().item()),
                              "rows_on_slow_path": int((out["status"] & api.ROW_SLOW_PATH).ne(0).sum().item())}
             del xs, ds, out
@@ -392,12 +392,12 @@ def main():
 
         # config 2: batched greedy + frequency / presence penalties over 256-id histories, 64 x 151936
         run_cfg("c2_greedy_penalties_64x151936", [normal_logits(64, 151936, 3.0, 7 + i) for i in range(4)], 0.0, 0, 1.0,
-                independent_states(port, 7, 64), hist=histories(64, 256, 151936, 7), freq=0.2, pres=0.3, hbytes=64 * 256 * 4)
+                independent_states(port, 7, 64), hist=histories(64, 256, 151936, 7), freq=0.2, pres=0.3, hbytes=64 * 256 * 4, hint=api.FINISH_GREEDY_TOPK)
         # config 3: nucleus sampling over heavy-tailed rows, 256 x 262144
         r3 = np.random.default_rng(99)
         run_cfg("c3_top_p_gumbel_256x262144", [gumbel_logits(256, 262144, 4.0, 99 + i) for i in range(2)],
                 r3.uniform(0.5, 1.2, 256).astype(np.float32), 0, r3.uniform(0.8, 0.98, 256).astype(np.float32), seq_states(port, 99, 256),
-                sample=np.arange(0, 256, 8))
+                sample=np.arange(0, 256, 8), hint=api.FINISH_GENERAL)
         # config 4: speculative verify rows, 32 sequences x 7 rows x 128256, temperature 1
         def c4(seed):
             d = normal_logits(32 * 6, 128256, 2.5, seed).reshape(32, 6, 128256)
@@ -405,10 +405,10 @@ def main():
             t[:, :6] = d + normal_logits(32 * 6, 128256, 0.5, seed + 1).reshape(32, 6, 128256)
             t[:, 6] = normal_logits(32, 128256, 2.5, seed + 2)
             return t.reshape(32 * 7, 128256)
-        run_cfg("c4_verify_rows_32x7x128256", [c4(2024), c4(3024)], 1.0, 0, 1.0, independent_states(port, 2024, 32), rows_per_seq=7)
+        run_cfg("c4_verify_rows_32x7x128256", [c4(2024), c4(3024)], 1.0, 0, 1.0, independent_states(port, 2024, 32), rows_per_seq=7, hint=api.FINISH_GENERAL)
         # config 5: 4096 x 128256, top-k 50 + repetition penalty over 1024-id histories (every 128th row checked)
         run_cfg("c5_top_k50_penalties_4096x128256", [normal_logits(4096, 128256, 2.5, 31337)], 0.7, 50, 0.9, independent_states(port, 31337, 4096),
-                hist=histories(4096, 1024, 128256, 31337), rep=1.15, sample=np.arange(0, 4096, 128), hbytes=4096 * 1024 * 4)
+                hist=histories(4096, 1024, 128256, 31337), rep=1.15, sample=np.arange(0, 4096, 128), hbytes=4096 * 1024 * 4, hint=api.FINISH_GREEDY_TOPK)
 
     # ---- multi-GPU legs on configuration 5: vocabulary shards over NCCL, and its rows split N ways
     vocab_shards = None
@@ -468,7 +468,7 @@ def main():
                         "rows_per_s": rows5 / (total_ms * 1e-3), "gathered_bytes_per_rank": int(world * rows5 * (k5 * 8 + 4))}
         # the same rows split over the ranks (strong scaling of configuration 5)
         a, b = rank * rows5 // world, (rank + 1) * rows5 // world
-        part = ctx.sample_batch(x5[a:b], T5[a:b], K5[a:b], P5[a:b], st5[a:b], rep=rep5[a:b], history=h5[a:b], history_len=hl5[a:b], launch=False)
+        part = ctx.sample_batch(x5[a:b], T5[a:b], K5[a:b], P5[a:b], st5[a:b], rep=rep5[a:b], history=h5[a:b], history_len=hl5[a:b], launch=False, finish_hint=api.FINISH_GREEDY_TOPK)
         sec = time_desc_list([part], 20)
         part_same = torch.tensor([1 if torch.equal(part["tokens"], full["tokens"][a:b]) else 0], device=dev)
         dist.all_reduce(part_same, op=dist.ReduceOp.MIN)
