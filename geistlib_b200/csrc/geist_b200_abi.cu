@@ -130,6 +130,45 @@ bool make_plan(size_t V, size_t hist_max, Plan &pl) {
     return true;
 }
 
+/* How a launch's (row, slice) items are dealt out to the stream kernel's thread blocks (gb::RunMap), the grid that
+ * goes with it, and over how many thread blocks a row can be spread. A thread block's cost is taken as its items
+ * plus five items' worth for every part of a row it touches (set-up, the first slice's threshold, the record). */
+struct Deal {
+    gb::RunMap map;
+    int        grid;
+    int        parts_max;
+};
+Deal deal_items(size_t n_rows, int n_slices, int ctas) {
+    const size_t S = (size_t) n_slices, n_items = n_rows * S;
+    constexpr size_t kPartCost = 5;
+    /* equal runs of items */
+    Deal         a;
+    a.grid                = (int) std::min<size_t>((size_t) ctas, n_items);
+    const size_t q        = n_items / (size_t) a.grid, rem = n_items % (size_t) a.grid;
+    a.map                 = gb::RunMap{gb::RUN_ITEMS, (int) q, (int) rem, 1};
+    a.parts_max           = (int) std::min<size_t>(S, (S - 1 + q - 1) / q + 1);
+    const size_t a_items  = q + (rem ? 1 : 0);
+    const size_t a_cost   = a_items + kPartCost * std::min<size_t>((a_items - 1 + S - 1) / S + 1, a_items);
+    /* rows kept whole, or cut into equal parts */
+    Deal   b;
+    size_t b_cost;
+    const size_t P = n_rows < (size_t) ctas ? std::min<size_t>((size_t) ctas / n_rows, S) : 1;
+    if (P <= 1) {
+        b.grid               = (int) std::min<size_t>((size_t) ctas, n_rows);
+        const size_t qr      = n_rows / (size_t) b.grid, rr = n_rows % (size_t) b.grid;
+        b.map                = gb::RunMap{gb::RUN_ROWS, (int) qr, (int) rr, 1};
+        b.parts_max          = 1;
+        const size_t rows_mx = qr + (rr ? 1 : 0);
+        b_cost               = rows_mx * (S + kPartCost);
+    } else {
+        b.grid      = (int) (n_rows * P);
+        b.map       = gb::RunMap{gb::RUN_PARTS, (int) (S / P), (int) (S % P), (int) P};
+        b.parts_max = (int) P;
+        b_cost      = S / P + (S % P ? 1 : 0) + kPartCost;
+    }
+    return b_cost <= a_cost ? b : a;
+}
+
 struct PlanCache {
     std::mutex mu;
     struct Key {
@@ -346,10 +385,11 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     /* scratch of this launch */
     const size_t n_rows   = (size_t) p.n_rows;
     const size_t n_items  = n_rows * (size_t) pl.n_slices;
-    const int    grid     = (int) std::min<size_t>((size_t) pl.ctas, n_items);
-    const size_t q_items  = n_items / (size_t) grid; /* the shortest run of items a thread block takes */
-    const size_t parts    = std::min<size_t>((size_t) pl.n_slices, ((size_t) pl.n_slices - 1 + q_items - 1) / q_items + 1);
-    p.parts_max           = (int) parts;
+    const Deal   deal     = deal_items(n_rows, pl.n_slices, pl.ctas);
+    const int    grid     = deal.grid;
+    const size_t parts    = (size_t) deal.parts_max;
+    p.parts_max           = deal.parts_max;
+    p.map                 = deal.map;
     const size_t gen_str  = round_up(b->n_vocab, 4);
     const size_t gen_bmw  = (b->n_vocab + 31) / 32;
     const size_t gen_hcap = hist_max ? std::min(hist_max, b->n_vocab) : 0;
@@ -521,7 +561,7 @@ extern "C" enum geist_status geist_b200_grid(size_t n_vocab, size_t max_history,
     CUDA_TRY(cudaGetDevice(&dev));
     CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
     if (thread_blocks) {
-        *thread_blocks = (int32_t) std::min<size_t>((size_t) pl.ctas, n_rows * (size_t) pl.n_slices);
+        *thread_blocks = (int32_t) deal_items(n_rows, pl.n_slices, pl.ctas).grid;
     }
     if (blocks_per_sm) {
         *blocks_per_sm = pl.ctas / prop.multiProcessorCount;

@@ -69,6 +69,21 @@ struct __align__(16) SegRec {
     double sum;  /* sum of expf((x - ref) * inv_t) over the segment */
 };
 
+/* Which (row, slice) items a thread block of the stream kernel takes: always one contiguous run of the row-major
+ * item list. The host picks the cheaper of two ways to cut the list (a part of a row costs a thread block
+ * about as much as five slices):
+ *   RUN_ITEMS  runs of equal length (q or q + 1 items, the first r blocks the longer ones); runs may begin and
+ *              end inside a row;
+ *   RUN_ROWS   whole rows (q or q + 1 rows per block), when there are at least as many rows as blocks or one
+ *              block per row comes out cheaper;
+ *   RUN_PARTS  every row cut into P runs of q or q + 1 slices, when there are fewer rows than blocks. */
+enum RunMode { RUN_ITEMS = 0, RUN_ROWS = 1, RUN_PARTS = 2 };
+struct RunMap {
+    int mode;
+    int q, r;
+    int P; /* RUN_PARTS: thread blocks per row */
+};
+
 struct SampleParams {
     const float *logits;      /* [n_rows, V], row_stride floats apart */
     long long    row_stride;
@@ -111,6 +126,7 @@ struct SampleParams {
     int      n_slices;     /* work items per row */
     int      slice;        /* floats per slice, multiple of 4, <= kSliceMax */
     int      parts_max;    /* thread blocks one row can be spread over */
+    RunMap   map;          /* how the items are dealt out to the stream kernel's thread blocks */
     /* rows with more than kRowIds ids: their distinct ids are prepared by a kernel of their own */
     int       id_slots;    /* slots of that kernel's id table (a power of two, at least twice the ids a row can bring); 0: no such rows */
     int       row_cap;     /* entries of one row's prepared list */

@@ -992,7 +992,35 @@ constexpr int kFinBytes   = kWarps * 256 * 12;    /* finisher: the merged candid
 static_assert(kFinCap * (int) sizeof(Pair) <= kFinBytes, "the merged list fits");
 static_assert(kGroupBytes >= 4 * kRowIds * 4, "the id table of a part's set-up lies in the groups' memory");
 
-__device__ __forceinline__ int cta_of_item(int i, int q, int r) { return i < r * (q + 1) ? i / (q + 1) : r + (i - r * (q + 1)) / q; }
+/* n things dealt out in runs of q + 1 (the first r runs) and q: which run holds thing i */
+__device__ __forceinline__ int run_of(int i, int q, int r) { return i < r * (q + 1) ? i / (q + 1) : r + (i - r * (q + 1)) / q; }
+
+/* The thread block that streams item i, and the run [first, first + count) of thread block b (RunMap). */
+__device__ __forceinline__ int cta_of_item(const SampleParams &p, int i) {
+    const RunMap &m = p.map;
+    if (m.mode == RUN_ITEMS) {
+        return run_of(i, m.q, m.r);
+    }
+    const int row = i / p.n_slices;
+    if (m.mode == RUN_ROWS) {
+        return run_of(row, m.q, m.r);
+    }
+    return row * m.P + run_of(i - row * p.n_slices, m.q, m.r);
+}
+__device__ __forceinline__ void run_of_cta(const SampleParams &p, int b, int &first, int &count) {
+    const RunMap &m = p.map;
+    if (m.mode == RUN_ITEMS) {
+        first = b * m.q + min(b, m.r);
+        count = m.q + (b < m.r ? 1 : 0);
+    } else if (m.mode == RUN_ROWS) {
+        first = (b * m.q + min(b, m.r)) * p.n_slices;
+        count = (m.q + (b < m.r ? 1 : 0)) * p.n_slices;
+    } else {
+        const int row = b / m.P, j = b - row * m.P;
+        first         = row * p.n_slices + j * m.q + min(j, m.r);
+        count         = m.q + (j < m.r ? 1 : 0);
+    }
+}
 
 /* Highest bin b with at least kq entries in bins >= b (0 when there is none); the whole warp calls, every lane gets it. */
 __device__ __forceinline__ int top_bin(const int *hist, int lane, int kq) {
@@ -1141,14 +1169,14 @@ __device__ void select_sorted(const Grp &g, FinishShared *sh, Pair *cand, int to
  * room for the merged list. Returns the row's status bits (ST_DEFERRED: the multi-pass path has to serve it).
  */
 template <bool kFast>
-__device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, FinishShared *sh, RowCfg &r, unsigned char *cmem, int q_items, int r_items) {
+__device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, FinishShared *sh, RowCfg &r, unsigned char *cmem) {
     const int  row     = r.row;
     int       *kept_i  = p.kept_cap > 0 ? p.kept_idx + (size_t) row * (size_t) p.kept_cap : nullptr;
     float     *kept_v  = p.kept_cap > 0 ? p.kept_val + (size_t) row * (size_t) p.kept_cap : nullptr;
     Pair      *cbuf    = reinterpret_cast<Pair *>(cmem);
     GroupShared *gs    = &sh->gs;
-    const int  b_first = cta_of_item(row * p.n_slices, q_items, r_items);
-    const int  b_last  = cta_of_item(row * p.n_slices + p.n_slices - 1, q_items, r_items);
+    const int  b_first = cta_of_item(p, row * p.n_slices);
+    const int  b_last  = cta_of_item(p, row * p.n_slices + p.n_slices - 1);
     const int  n_parts = b_last - b_first + 1;
     int        st      = 0;
 
@@ -1754,11 +1782,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
     const unsigned lt  = (1u << lane) - 1u;
 
     /* every thread block takes a contiguous run of the (row, slice) items */
-    const int n_items  = p.n_rows * p.n_slices;
-    const int G        = (int) gridDim.x;
-    const int q_items  = n_items / G, r_items = n_items - q_items * G;
-    const int my_first = (int) blockIdx.x * q_items + min((int) blockIdx.x, r_items);
-    const int my_count = q_items + ((int) blockIdx.x < r_items ? 1 : 0);
+    int my_first, my_count;
+    run_of_cta(p, (int) blockIdx.x, my_first, my_count);
 
     if (tid == 0) {
         for (int w = 0; w < kWarps; w++) {
@@ -1869,9 +1894,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
         const bool  sel     = (mode == M_TOPK || mode == M_TOPP) && kq > 0 && kq <= kFastKMax;
         const bool  sums    = mode == M_TEMP || (mode == M_TOPP && sel);
         const bool  long_ids = n_ids > kRowIds;
-        const int   b_first = cta_of_item(row * p.n_slices, q_items, r_items);
+        const int   b_first = cta_of_item(p, row * p.n_slices);
         const int   part_idx = (int) blockIdx.x - b_first;
-        const int   n_parts = cta_of_item(row * p.n_slices + p.n_slices - 1, q_items, r_items) - b_first + 1;
+        const int   n_parts = cta_of_item(p, row * p.n_slices + p.n_slices - 1) - b_first + 1;
 
         /* ---- part set-up ---- */
         if (tid == 0) {
@@ -2327,7 +2352,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
  * The split keeps the kernel that every launch needs small.
  */
 template <bool kFast>
-__global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_constant__ SampleParams p, int q_items, int r_items) {
+__global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_constant__ SampleParams p) {
     extern __shared__ __align__(128) unsigned char fsmem[];
     FinishShared  *sh   = reinterpret_cast<FinishShared *>(fsmem);
     unsigned char *cmem = reinterpret_cast<unsigned char *>(sh + 1);
@@ -2355,7 +2380,7 @@ __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_c
         const RawCfg rc = (all_rows && it == (int) blockIdx.x) ? rc0 : raw_config(p, row, true);
         RowCfg       r  = row_config(p, row, rc, true);
         PROF(8);
-        int          st = finish_row<kFast>(g, p, sh, r, cmem, q_items, r_items);
+        int          st = finish_row<kFast>(g, p, sh, r, cmem);
         PROF(13);
         if (st & ST_DEFERRED) {
             if constexpr (kFast) {
@@ -2645,16 +2670,15 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     if (e != cudaSuccess) {
         return e;
     }
-    const int n_items = p.n_rows * p.n_slices;
     cfg.gridDim          = dim3((unsigned) finish_grid);
     cfg.dynamicSmemBytes = finish_rows_smem();
     if ((p.flags & F_REST_ONLY) == 0u) {
-        e = cudaLaunchKernelEx(&cfg, finish_rows_kernel<true>, p, n_items / grid, n_items % grid);
+        e = cudaLaunchKernelEx(&cfg, finish_rows_kernel<true>, p);
         if (e != cudaSuccess || !second_finisher || (p.flags & F_FAST_ONLY) != 0u) {
             return e;
         }
     }
-    return cudaLaunchKernelEx(&cfg, finish_rows_kernel<false>, p, n_items / grid, n_items % grid);
+    return cudaLaunchKernelEx(&cfg, finish_rows_kernel<false>, p);
 }
 
 } /* namespace gb */
