@@ -1570,20 +1570,45 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
             g.sync();
             PROF(12);
             if (k <= 64) {
-                if (g.tid == 0) { /* sampler.c:90-102 as it stands: two short loops by one thread */
+                if (g.tid == 0) { /* sampler.c:90-102 as it stands: the sum and the walk in the reference's order, by one thread */
                     double S = 0.0;
 #pragma unroll 1
-                    for (int i = 0; i < k; i++) {
-                        S += (double) sh->fq[i];
+                    for (int i0 = 0; i0 < k; i0 += 8) { /* eight weights per round: their loads overlap, the sum keeps its order */
+                        float w8[8];
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            w8[q] = i0 + q < k ? sh->fq[i0 + q] : 0.0f;
+                        }
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            S += (double) w8[q]; /* adding +0 behind the last weight changes nothing */
+                        }
                     }
                     const double u    = (double) unit_from(xorshift_next(r.rng)) * S;
                     double       a    = 0.0;
                     int          pick = k - 1;
 #pragma unroll 1
-                    for (int i = 0; i < k; i++) {
-                        a += (double) sh->fq[i];
-                        if (u < a) {
-                            pick = i;
+                    for (int i0 = 0; i0 < k; i0 += 8) {
+                        float w8[8];
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            w8[q] = i0 + q < k ? sh->fq[i0 + q] : 0.0f;
+                        }
+                        double pre[8]; /* the running sums behind each of the eight, in walk order */
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            a += (double) w8[q];
+                            pre[q] = a;
+                        }
+                        int first = 8;
+#pragma unroll
+                        for (int q = 7; q >= 0; q--) {
+                            if (u < pre[q] && i0 + q < k) {
+                                first = q;
+                            }
+                        }
+                        if (first < 8) {
+                            pick = i0 + first;
                             break;
                         }
                     }
