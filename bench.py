@@ -346,7 +346,8 @@ def main():
         mode("top_p0.95_gaussian(wide nucleus)", T, 0, TOP_P, False)
         # the same launches with the caller's hint on which finishing kernel they need (one launch fewer)
         mode("headline, finish_hint=AUTO", T, TOP_K, TOP_P, True, api.FINISH_AUTO)
-        mode("greedy, finish_hint=GREEDY_TOPK", 0.0, 0, 1.0, False, api.FINISH_GREEDY_TOPK)
+        mode("greedy, finish_hint=GREEDY (one kernel)", 0.0, 0, 1.0, False, api.FINISH_GREEDY)
+        mode("greedy+penalties, finish_hint=GREEDY (one kernel)", 0.0, 0, 1.0, True, api.FINISH_GREEDY)
         mode("temperature, finish_hint=GENERAL", T, 0, 1.0, False, api.FINISH_GENERAL)
 
     # ---- the other configurations of the reference's table (rank 0's GPU; device-resident)
@@ -384,7 +385,7 @@ def main():
                 checked = rows
             nbytes = rows * (4 * Vn + 4) + nseq * 16 + hbytes
             configs[name] = {"us_per_launch": sec * 1e6, "rows_per_s": rows / sec, "hbm_frac": nbytes / sec / 1e9 / peak,
-                             "finish_hint": ["AUTO", "GREEDY_TOPK", "GENERAL"][hint], "rows_checked_against_cpu": checked, "tokens_match_cpu": match,
+                             "finish_hint": ["AUTO", "GREEDY_TOPK", "GENERAL", "GREEDY"][hint], "rows_checked_against_cpu": checked, "tokens_match_cpu": match,
                              "rows_invalid": int((out["status"] & api.ROW_INVALID).ne(0).sum().item()),
                              "rows_on_slow_path": int((out["status"] & api.ROW_SLOW_PATH).ne(0).sum().item())}
             del xs, ds, out
@@ -392,7 +393,7 @@ def main():
 
         # config 2: batched greedy + frequency / presence penalties over 256-id histories, 64 x 151936
         run_cfg("c2_greedy_penalties_64x151936", [normal_logits(64, 151936, 3.0, 7 + i) for i in range(4)], 0.0, 0, 1.0,
-                independent_states(port, 7, 64), hist=histories(64, 256, 151936, 7), freq=0.2, pres=0.3, hbytes=64 * 256 * 4, hint=api.FINISH_GREEDY_TOPK)
+                independent_states(port, 7, 64), hist=histories(64, 256, 151936, 7), freq=0.2, pres=0.3, hbytes=64 * 256 * 4, hint=api.FINISH_GREEDY)
         # config 3: nucleus sampling over heavy-tailed rows, 256 x 262144
         r3 = np.random.default_rng(99)
         run_cfg("c3_top_p_gumbel_256x262144", [gumbel_logits(256, 262144, 4.0, 99 + i) for i in range(2)],

@@ -326,7 +326,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     if (b->logit_mask != nullptr && b->logit_mask_stride * 32 < b->n_vocab) {
         return fail(GEIST_E_INVALID_ARG, "sample_batch: logit_mask_stride %zu words hold fewer than n_vocab %zu bits", b->logit_mask_stride, b->n_vocab);
     }
-    if (b->finish_hint < GEIST_B200_FINISH_AUTO || b->finish_hint > GEIST_B200_FINISH_GENERAL) {
+    if (b->finish_hint < GEIST_B200_FINISH_AUTO || b->finish_hint > GEIST_B200_FINISH_GREEDY) {
         return fail(GEIST_E_INVALID_ARG, "sample_batch: finish_hint %d is not one of GEIST_B200_FINISH_*", b->finish_hint);
     }
     if ((flags & gb::F_SELECT_ONLY) && b->kept_cap <= 0) {
@@ -379,6 +379,9 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.flags        = flags;
     if ((flags & gb::F_SELECT_ONLY) == 0u) { /* a shard's select is a top-k row whatever its parameters say: the small kernel takes k <= kFastKMax, the general one the rest */
         p.flags |= b->finish_hint == GEIST_B200_FINISH_GREEDY_TOPK ? gb::F_FAST_ONLY : (b->finish_hint == GEIST_B200_FINISH_GENERAL ? gb::F_REST_ONLY : 0u);
+        if (b->finish_hint == GEIST_B200_FINISH_GREEDY) {
+            p.flags |= gb::F_FAST_ONLY | gb::F_GREEDY_ONLY; /* where rows are split over thread blocks the small finishing kernel still merges them */
+        }
     }
     cudaStream_t st = as_stream(stream);
 
@@ -1188,7 +1191,7 @@ enum geist_status batcher_run(geist_b200_batcher *b, size_t n, const int32_t *se
         }
     }
     /* which finishing kernels the launch needs: the sessions' sampler settings are known here */
-    bool any_fast = false, any_rest = false;
+    bool any_fast = false, any_rest = false, all_greedy = true;
     for (size_t i = 0; i < n; i++) {
         const size_t sl   = (size_t) sessions[i];
         const float  T    = b->h_T[sl];
@@ -1196,8 +1199,12 @@ enum geist_status batcher_run(geist_b200_batcher *b, size_t n, const int32_t *se
         const bool   fast = !(T > 0.0f) || (K > 1 && (size_t) K < b->V && K <= gb::kFastKMax);
         any_fast |= fast;
         any_rest |= !fast;
+        all_greedy &= !(T > 0.0f);
     }
-    const int32_t hint = !any_rest ? GEIST_B200_FINISH_GREEDY_TOPK : (!any_fast ? GEIST_B200_FINISH_GENERAL : GEIST_B200_FINISH_AUTO);
+    int32_t hint = !any_rest ? GEIST_B200_FINISH_GREEDY_TOPK : (!any_fast ? GEIST_B200_FINISH_GENERAL : GEIST_B200_FINISH_AUTO);
+    if (all_greedy) {
+        hint = GEIST_B200_FINISH_GREEDY;
+    }
     CUDA_TRY(cudaSetDevice(b->ctx->device));
     cudaStream_t st   = b->ctx->stream;
     const size_t rows = n * k;

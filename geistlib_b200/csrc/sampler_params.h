@@ -43,6 +43,7 @@ enum : int {
 enum : unsigned {
     F_SELECT_ONLY = 1u << 0, /* vocabulary shard: emit the row's best k (value, global id), no draw */
     F_FAST_ONLY   = 1u << 1, /* the caller vouches that every row is greedy or top-k <= kFastKMax: only the small finishing kernel runs */
+    F_GREEDY_ONLY = 1u << 3, /* the caller vouches that every row is greedy: where a thread block streams whole rows it writes their tokens itself and no finishing kernel runs */
     F_REST_ONLY   = 1u << 2, /* the caller expects no such rows: only the general finishing kernel runs, over all rows */
 };
 

@@ -959,6 +959,8 @@ struct __align__(16) StreamShared {
     int                bhist[kHistBins];           /* first slice: group maxima binned by key */
     int                thist[kHistBins];           /* candidates binned by value between threshold and maximum */
     int                rl_id[kRowIds], rl_cnt[kRowIds]; /* the row's distinct history ids and their counts */
+    unsigned long long cur_rng;         /* the generator word the part's sequence came with, its sequence, and whether the row is the sequence's last */
+    int                cur_seq, cur_last;
     float              cap;             /* the part's soft cap and mask row (0 / null: none) */
     const unsigned    *mrow;
     RawCfg             raw_nxt;         /* parameters of the next row of this run, copied in while the part streams */
@@ -1909,8 +1911,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             pres   = r.pres;
             pro_on = r.cap > 0.0f || r.mrow != nullptr;
             if (tid == 0) { /* read again by the warps only if pro_on; the barriers of the part set-up lie between */
-                sh->cap  = r.cap;
-                sh->mrow = r.mrow;
+                sh->cap      = r.cap;
+                sh->mrow     = r.mrow;
+                sh->cur_rng  = raw.rng;
+                sh->cur_seq  = r.seq;
+                sh->cur_last = r.rr == p.rows_per_seq - 1 ? 1 : 0;
             }
             if (tid < n_ids && n_ids <= kRowIds) {
                 my_id = tid < r.H ? sh->nxt_ids[tid] : sh->nxt_ext[tid - r.H];
@@ -2342,6 +2347,24 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             int4 *rec = reinterpret_cast<int4 *>(p.grp_v + ((size_t) row * (size_t) p.parts_max + (size_t) part_idx) * (size_t) kPartSlots);
             rec[0]    = h; /* the part's record takes the first two slots of its group list */
             rec[1]    = h2;
+            if ((p.flags & F_GREEDY_ONLY) != 0u && p.map.mode == RUN_ROWS) {
+                /* the whole row went through this thread block and the caller said it is greedy: the token is
+                 * known here and no finishing kernel follows. A row that is not greedy after all is reported. */
+                int stq = h.w;
+                if (mode == M_ARGMAX) {
+                    p.tokens[row] = h.y + p.vocab_offset;
+                } else {
+                    p.tokens[row] = -1;
+                    stq |= ST_INTERNAL;
+                }
+                if (p.kept_cap > 0) {
+                    p.kept_n[row] = 0;
+                }
+                p.status[row] = stq;
+                if (p.rng_out != nullptr && sh->cur_last) {
+                    p.rng_out[sh->cur_seq] = sh->cur_rng; /* greedy rows draw nothing (sampler.c:106-112) */
+                }
+            }
         }
         const size_t at = ((size_t) row * (size_t) p.parts_max + (size_t) part_idx) * (size_t) kPartSlots + 2;
         for (int f = tid; f < held; f += kThreads) {
@@ -2697,6 +2720,9 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     }
     cfg.gridDim          = dim3((unsigned) finish_grid);
     cfg.dynamicSmemBytes = finish_rows_smem();
+    if ((p.flags & F_GREEDY_ONLY) != 0u && p.map.mode == RUN_ROWS) {
+        return cudaSuccess; /* the stream kernel wrote the tokens itself */
+    }
     if ((p.flags & F_REST_ONLY) == 0u) {
         e = cudaLaunchKernelEx(&cfg, finish_rows_kernel<true>, p);
         if (e != cudaSuccess || !second_finisher || (p.flags & F_FAST_ONLY) != 0u) {

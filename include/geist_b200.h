@@ -196,11 +196,16 @@ struct geist_b200_batch {
  *   AUTO         both kernels; any mix of rows.
  *   GREEDY_TOPK  the small kernel only. A row that is neither greedy nor top-k <= 256 is not sampled: its
  *                row_status carries GEIST_B200_ROW_INTERNAL and its token is -1.
- *   GENERAL      the general kernel only, over all rows (it can finish every kind of row). */
+ *   GENERAL      the general kernel only, over all rows (it can finish every kind of row).
+ *   GREEDY       every row is greedy (T <= 0). Where the launch deals whole rows to its thread blocks (batches
+ *                of about half the device's thread-block slots and more) the stream kernel writes the tokens
+ *                itself and no finishing kernel is launched; elsewhere like GREEDY_TOPK. A row with T > 0 is
+ *                not sampled: GEIST_B200_ROW_INTERNAL, token -1. */
 enum {
     GEIST_B200_FINISH_AUTO        = 0,
     GEIST_B200_FINISH_GREEDY_TOPK = 1,
     GEIST_B200_FINISH_GENERAL     = 2,
+    GEIST_B200_FINISH_GREEDY      = 3,
 };
 
 /* Replaces the sampler dispatch of finalize_logits_one_row / _batch

@@ -153,6 +153,36 @@ def test_finish_hint_same_tokens(ctx):
     check_tokens(run_gpu(ctx, x, Tm, 0, Pm, st, finish_hint=api.FINISH_GENERAL), oracle.port.sample_batch(x, Tm, 0, Pm, st))
 
 
+@pytest.mark.parametrize("rows,V,R", [(256, 5000, 1), (200, 40000, 1), (64, 128256, 1), (300, 9000, 1), (240, 3000, 3)])
+def test_finish_hint_greedy(ctx, rows, V, R):
+    """All rows greedy and the caller says so: whole-row launches write the tokens from the stream kernel alone
+    (no finishing kernel), split-row launches merge as usual; ids, status and generator words as without the hint."""
+    x = normal_logits(rows, V, 3.0, 77 + rows)
+    x[3, :] = 1.5           # all equal: lowest index
+    x[5, V // 3:] = x[5].max() + 2.0
+    S = rows // R
+    st = independent_states(oracle.port, 5, S)
+    h = histories(S, 40, V, 6)
+    g = run_gpu(ctx, x, 0.0, 0, 1.0, st, rows_per_seq=R, finish_hint=api.FINISH_GREEDY, freq=0.4, history=h)
+    o = oracle.port.sample_batch(x, 0.0, 0, 1.0, st, rows_per_seq=R, freq=0.4, hist=h)
+    check_tokens(g, o)
+    assert np.array_equal(g["rng_state"], st), "greedy rows draw nothing"
+
+
+def test_finish_hint_greedy_wrong_is_loud(ctx):
+    from helpers import u64_to_dev
+    rows, V = 256, 4000
+    x = normal_logits(rows, V, 3.0, 9)
+    T = np.zeros(rows, np.float32)
+    T[17] = 0.7
+    dT, dK, dP = to_dev(T), to_dev(np.zeros(rows, np.int32)), to_dev(np.ones(rows, np.float32))
+    out = ctx.sample_batch(to_dev(x), dT, dK, dP, u64_to_dev(independent_states(oracle.port, 1, rows)), finish_hint=api.FINISH_GREEDY)
+    status, tok = out["status"].cpu().numpy(), out["tokens"].cpu().numpy()
+    assert status[17] & api.ROW_INTERNAL and tok[17] == -1
+    ok = np.arange(rows) != 17
+    assert (status[ok] & api.ROW_INVALID == 0).all() and np.array_equal(tok[ok], x[ok].argmax(axis=1))
+
+
 def test_finish_hint_wrong_is_loud(ctx):
     """GREEDY_TOPK with a temperature row in the batch: that row reports ROW_INTERNAL and token -1, the others are sampled."""
     import torch
@@ -172,7 +202,7 @@ def test_finish_hint_wrong_is_loud(ctx):
     o = oracle.port.sample_batch(x, T, K, 1.0, st)
     assert np.array_equal(tok[ok], o["tokens"][ok])
     with pytest.raises(api.GeistError, match="GEIST_E_INVALID_ARG"):
-        ctx.sample_batch(to_dev(x), dT, dK, dP, u64_to_dev(st), finish_hint=7)
+        ctx.sample_batch(to_dev(x), dT, dK, dP, u64_to_dev(st), finish_hint=9)
 
 
 # ------------------------------------- every mode against the reference's own code --
