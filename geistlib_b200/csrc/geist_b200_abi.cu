@@ -132,15 +132,17 @@ bool make_plan(size_t V, size_t hist_max, Plan &pl) {
 
 /* How a launch's (row, slice) items are dealt out to the stream kernel's thread blocks (gb::RunMap), the grid that
  * goes with it, and over how many thread blocks a row can be spread. A thread block's cost is taken as its items
- * plus five items' worth for every part of a row it touches (set-up, the first slice's threshold, the record). */
+ * plus kPartCost items' worth for every part of a row it touches (set-up, the first slice's threshold, the
+ * record): five where rows may be top-k rows (measured: 256 whole rows beat 296 equal runs by 5 us of 51), one
+ * where the caller said they are temperature / top-p rows (their parts set no threshold; equal runs measured
+ * 6 - 10 % faster there), eight where the caller said they are greedy (whole rows need no finishing kernel). */
 struct Deal {
     gb::RunMap map;
     int        grid;
     int        parts_max;
 };
-Deal deal_items(size_t n_rows, int n_slices, int ctas) {
+Deal deal_items(size_t n_rows, int n_slices, int ctas, size_t kPartCost = 5) {
     const size_t S = (size_t) n_slices, n_items = n_rows * S;
-    constexpr size_t kPartCost = 5;
     /* equal runs of items */
     Deal         a;
     a.grid                = (int) std::min<size_t>((size_t) ctas, n_items);
@@ -388,7 +390,8 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     /* scratch of this launch */
     const size_t n_rows   = (size_t) p.n_rows;
     const size_t n_items  = n_rows * (size_t) pl.n_slices;
-    const Deal   deal     = deal_items(n_rows, pl.n_slices, pl.ctas);
+    const size_t part_cost = (flags & gb::F_SELECT_ONLY) ? 5 : (b->finish_hint == GEIST_B200_FINISH_GENERAL ? 1 : (b->finish_hint == GEIST_B200_FINISH_GREEDY ? 8 : 5));
+    const Deal   deal     = deal_items(n_rows, pl.n_slices, pl.ctas, part_cost);
     const int    grid     = deal.grid;
     const size_t parts    = (size_t) deal.parts_max;
     p.parts_max           = deal.parts_max;

@@ -987,6 +987,7 @@ struct __align__(16) FinishShared {
 };
 
 constexpr int kGroupBytes = kPartGroups * 20; /* float4 + first id per group */
+constexpr int kListSmem   = 1024;             /* prepared id-list entries of a part that are kept in shared memory */
 constexpr int kFinCap     = 2048;             /* candidates the finisher can order per row (8 per thread) */
 constexpr int kFinPer     = kFinCap / kThreads;
 constexpr int kRankAll    = 384;              /* up to this many candidates are ranked one against all */
@@ -1797,6 +1798,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
     float4        *grp_v   = reinterpret_cast<float4 *>(gmem);
     int           *grp_b   = reinterpret_cast<int *>(gmem + (size_t) kPartGroups * 16);
     int           *sl_off  = reinterpret_cast<int *>(gmem + kGroupBytes); /* long histories: where each slice's run of the prepared list starts */
+    unsigned      *sl_list = reinterpret_cast<unsigned *>(gmem + kGroupBytes + ((((size_t) p.n_slices + 1) * 4 + 15) & ~(size_t) 15)); /* ... and the part's entries, when they fit */
 
     Grp g;
     g.tid  = (int) threadIdx.x;
@@ -1984,6 +1986,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             for (int i = tid; i <= part_len; i += kThreads) {
                 sl_off[i] = off[i];
             }
+            /* the part's entries themselves come along when there are at most kListSmem of them: the slices then
+             * read them from shared memory instead of paying a round trip to L2 each */
+            const int e_lo = off[0], e_n = off[part_len] - e_lo;
+            if (e_n <= kListSmem) {
+                const unsigned *src = p.pre_list + (size_t) row * (size_t) p.row_cap + e_lo;
+                for (int i = tid; i < e_n; i += kThreads) {
+                    sl_list[i] = src[i];
+                }
+            }
         }
         __syncthreads();
         static_assert(2 * kRowIds == 512, "the id table's hash keeps 9 bits");
@@ -2060,9 +2071,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                     }
                 } else {
                     const unsigned *src = p.pre_list + (size_t) row * (size_t) p.row_cap;
-                    const int       lo = sl_off[s], hi = sl_off[s + 1];
+                    const int       lo = sl_off[s], hi = sl_off[s + 1], e_lo = sl_off[0];
+                    const bool      in_smem = sl_off[part_len] - e_lo <= kListSmem;
                     for (int i = lo + lane; i < hi; i += 32) {
-                        const unsigned e  = src[i];
+                        const unsigned e  = in_smem ? sl_list[i - e_lo] : src[i];
                         const int      li = (int) (e & ((1u << kLiBits) - 1u));
                         if (li >= 4 * w4lo && li < 4 * (w4lo + mine4) && li < n) {
                             sl[li - 4 * w4lo] = penalise(sl[li - 4 * w4lo], (int) (e >> kLiBits), rep, freq, pres);
@@ -2585,6 +2597,7 @@ size_t sample_stream_smem(int n_slices, int long_ids) {
     size_t b = (size_t) kWarps * kStages * kWarpStageBytes + sizeof(StreamShared) + (size_t) kGroupBytes;
     if (long_ids) {
         b += (((size_t) n_slices + 1) * 4 + 15) & ~(size_t) 15;
+        b += (size_t) kListSmem * 4;
     }
     return b;
 }
