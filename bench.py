@@ -69,11 +69,17 @@ def measured_peak():
 
 
 def ncu_traffic():
-    """dram bytes of one step of this workload, from the committed ncu summary (a bench run cannot measure it)."""
+    """DRAM bytes of one step of this workload from the committed ncu summary (a bench run cannot measure them), and
+    whether the kernel sources are still the ones the capture was taken with."""
+    import hashlib
     p = ROOT / "profiles" / "traffic.json"
     try:
         d = json.loads(p.read_text())
-        return float(d["dram_bytes_per_step"]), d.get("source", str(p.name))
+        h = hashlib.sha256()
+        for f in d["kernel_sources"]:
+            h.update((ROOT / f).read_bytes())
+        same = h.hexdigest() == d["kernel_sources_sha256"]
+        return float(d["dram_bytes_per_step"]), d.get("source", p.name) + ("" if same else " [kernel sources changed since that capture]")
     except Exception:
         return None, "no ncu capture committed for this build"
 
