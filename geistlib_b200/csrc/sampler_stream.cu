@@ -2253,15 +2253,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                 /* sum of e_i relative to the WARP's maximum of this slice (top-p: of what is in no candidate
                  * group); -inf padding gives exp(-inf) = 0 */
                 const float ref = wmax == -CUDART_INF_F ? 0.0f : wmax;
+                const float k2  = inv_t * 1.4426950408889634f; /* e^(a / T) = 2^(a * log2(e) / T) */
                 double      sum = 0.0;
 #pragma unroll
                 for (int i = 0; i < kNV4; i++) {
                     /* a candidate's argument becomes -inf (exp gives 0), so that the evaluations stay one straight
                      * line and overlap */
-                    const float e0 = expf(x[i].x >= tau ? -CUDART_INF_F : scaled_arg(x[i].x, ref, inv_t));
-                    const float e1 = expf(x[i].y >= tau ? -CUDART_INF_F : scaled_arg(x[i].y, ref, inv_t));
-                    const float e2 = expf(x[i].z >= tau ? -CUDART_INF_F : scaled_arg(x[i].z, ref, inv_t));
-                    const float e3 = expf(x[i].w >= tau ? -CUDART_INF_F : scaled_arg(x[i].w, ref, inv_t));
+                    const float e0 = exp2_fast(x[i].x >= tau ? -CUDART_INF_F : (x[i].x - ref) * k2);
+                    const float e1 = exp2_fast(x[i].y >= tau ? -CUDART_INF_F : (x[i].y - ref) * k2);
+                    const float e2 = exp2_fast(x[i].z >= tau ? -CUDART_INF_F : (x[i].z - ref) * k2);
+                    const float e3 = exp2_fast(x[i].w >= tau ? -CUDART_INF_F : (x[i].w - ref) * k2);
                     sum += (double) ((e0 + e1) + (e2 + e3));
                 }
                 sum = warp_sum_d(sum);
