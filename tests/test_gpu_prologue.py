@@ -218,3 +218,28 @@ def test_mode_against_reference_sampler(ctx, mode, T, K, P):
     st = seq_states(oracle.port, 1000, rows)
     g = run_gpu(ctx, x, T, K, P, st)
     check_tokens(g, oracle.ref.sample(x, T, K, P, st))
+
+
+# ------------------------------------------------------ how the items are dealt out --
+
+@pytest.mark.parametrize("V", [700, 9000, 20000])  # 1, 2 and 3 slices per row
+def test_run_maps_over_row_counts(ctx, V):
+    """Row counts on both sides of every switch between the three ways of cutting the item list (whole rows,
+    rows cut into equal parts, equal runs of items), with each hint's weighting: the tokens never depend on it."""
+    sm2 = 2 * 148
+    counts = sorted({1, 2, 3, 37, 73, 74, 75, 147, 148, 149, 150, 200, 255, 256, 257, sm2 - 1, sm2, sm2 + 1, 300, 2 * sm2 - 1, 2 * sm2, 2 * sm2 + 1, 640})
+    rows_max = max(counts)
+    x = normal_logits(rows_max, V, 2.5, 4000 + V)
+    x[:, :3] += 6.0
+    st = independent_states(oracle.port, 4000, rows_max)
+    h = histories(rows_max, 24, V, 4001)
+    for mode, (T, K, P), hints in [("greedy", (0.0, 0, 1.0), (api.FINISH_AUTO, api.FINISH_GREEDY_TOPK, api.FINISH_GREEDY)),
+                                   ("topk", (0.8, 40, 1.0), (api.FINISH_AUTO, api.FINISH_GREEDY_TOPK)),
+                                   ("temp", (1.0, 0, 1.0), (api.FINISH_AUTO, api.FINISH_GENERAL))]:
+        o = oracle.port.sample_batch(x, T, K, P, st, rep=1.1, hist=h)
+        for n in counts:
+            for hint in hints:
+                g = run_gpu(ctx, x[:n], T, K, P, st[:n], rep=1.1, history=h[:n], finish_hint=hint)
+                bad = np.nonzero(g["tokens"] != o["tokens"][:n])[0]
+                assert bad.size == 0, (mode, n, hint, bad[:5])
+                assert np.array_equal(g["rng_state"], o["rng_state"][:n]), (mode, n, hint)
