@@ -407,7 +407,9 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     const size_t off_rows = round_up(off_seg + n_items * (size_t) gb::kWarps * sizeof(gb::SegRec), 256);
     const size_t off_bm   = round_up(off_rows + slots * gen_str * 4, 256);
     const size_t off_dl   = round_up(off_bm + slots * gen_bmw * 4, 256);
-    const size_t off_pl   = round_up(off_dl + slots * gen_hcap * sizeof(gb::Pair), 256);
+    const size_t gen_lcap = std::min<size_t>(b->n_vocab, 16384); /* entries of one histogram bin that the multi-pass path picks out of a row */
+    const size_t off_ls   = round_up(off_dl + slots * gen_hcap * sizeof(gb::Pair), 256);
+    const size_t off_pl   = round_up(off_ls + slots * gen_lcap * sizeof(gb::Pair), 256);
     const size_t off_po   = round_up(off_pl + (pl.id_slots ? n_rows * (size_t) pl.row_cap * 4 : 0), 256);
     const size_t off_def  = round_up(off_po + (pl.id_slots ? n_rows * (size_t) (pl.n_slices + 1) * 4 : 0), 256);
     const size_t need     = round_up(off_def + (n_rows + 4) * 4, 256);
@@ -447,6 +449,8 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.gen_bitmap_words = (int) gen_bmw;
     p.gen_dlist        = reinterpret_cast<gb::Pair *>(ln->buf + off_dl);
     p.gen_hist_cap     = (int) gen_hcap;
+    p.gen_list         = reinterpret_cast<gb::Pair *>(ln->buf + off_ls);
+    p.gen_list_cap     = (int) gen_lcap;
     p.pre_list         = reinterpret_cast<unsigned *>(ln->buf + off_pl);
     p.pre_off          = reinterpret_cast<int *>(ln->buf + off_po);
     CUDA_TRY(gb::launch_sample_stream(p, grid, pl.smem, fin_grid, true, st));

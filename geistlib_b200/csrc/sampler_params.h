@@ -151,6 +151,8 @@ struct SampleParams {
     unsigned  *gen_bitmap;  /* [pool_slots, gen_bitmap_words] */
     int        gen_bitmap_words;
     Pair      *gen_dlist;   /* [pool_slots, gen_hist_cap] (id, original value) */
+    Pair      *gen_list;    /* [pool_slots, gen_list_cap] (probability, id): the entries of one histogram bin, picked out of the row */
+    int        gen_list_cap;
     int        gen_hist_cap;
 };
 

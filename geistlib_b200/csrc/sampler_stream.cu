@@ -511,15 +511,30 @@ __device__ __forceinline__ void row_rewrite(const Grp &g, float *row, int V, F &
     }
 }
 
+/* A walk is written against "something that calls f(value, id) for every entry": the whole private copy of a
+ * row, or a short list of (value, id) pairs picked out of it. */
+template <class F>
+__device__ __forceinline__ void list_sweep(const Grp &g, const Pair *list, int n, F &&f) {
+    int j = g.tid;
+    for (; j + 3 * g.n < n; j += 4 * g.n) {
+        const Pair a = list[j], b = list[j + g.n], c = list[j + 2 * g.n], d = list[j + 3 * g.n];
+        f(a.v, a.idx), f(b.v, b.idx), f(c.v, c.idx), f(d.v, d.idx);
+    }
+    for (; j < n; j += g.n) {
+        const Pair a = list[j];
+        f(a.v, a.idx);
+    }
+}
+
 /* Largest composite word t with mass{word >= t} >= target (inclusive) or > target. The search may
  * start from a known prefix of the word: the bits above top_bit are taken from `prefix`. */
-template <class KeyF, class MassF>
-__device__ unsigned long long bisect_mass(const Grp &g, GroupShared *sh, const float *row, int V, int idx_bits, double target, bool inclusive, KeyF &&key, MassF &&mass,
+template <class Sweep, class KeyF, class MassF>
+__device__ unsigned long long bisect_mass(const Grp &g, GroupShared *sh, Sweep &&sweep, int idx_bits, double target, bool inclusive, KeyF &&key, MassF &&mass,
                                           unsigned long long prefix = 0ull, int top_bit = -1) {
     for (int bit = top_bit >= 0 ? top_bit : 31 + idx_bits; bit >= 0; bit--) {
         const unsigned long long t = prefix | (1ull << bit);
         double                   m = 0.0;
-        row_sweep(g, row, V, [&](float x, int i) {
+        sweep([&](float x, int i) {
             if (composite(key(x), i, idx_bits) >= t) {
                 m += mass(x, i);
             }
@@ -547,9 +562,9 @@ struct RadixOut {
  * histograms, one per warp where the room allows), then a scan from the top value down. hm / hc
  * hold copies * 256 doubles / ints.
  */
-template <bool kUnit = false, class KeyF, class MassF>
-__device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *hc, int copies, double scale, const float *row, int V, double target, bool inclusive, KeyF &&key,
-                               MassF &&mass) {
+template <bool kUnit = false, class Sweep, class KeyF, class MassF>
+__device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *hc, int copies, double scale, Sweep &&sweep, double target, bool inclusive, KeyF &&key,
+                               MassF &&mass, int last_level = 0) {
     /* masses are summed as 64-bit fixed point (mass * scale, truncated): integer adds in shared memory are one
      * instruction whatever the conflicts, and the sums do not depend on the order. The caller picks a scale that
      * keeps the row's total below 2^63. */
@@ -560,7 +575,7 @@ __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *h
     out.above   = 0.0;
     out.n_above = 0;
     out.ties    = 0;
-    for (int level = 3; level >= 0; level--) {
+    for (int level = 3; level >= last_level; level--) { /* last_level 3: the top byte alone; the histograms then stay as they are for the caller */
         const int shift = 8 * level;
         for (int i = g.tid; i < copies * 256; i += g.n) {
             hq[i] = 0ull;
@@ -570,7 +585,7 @@ __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *h
         unsigned long long *mym = hq + (g.warp % copies) * 256;
         int           *myc = hc + (g.warp % copies) * 256;
         const unsigned pre = out.key;
-        row_sweep(g, row, V, [&](float x, int i) {
+        sweep([&](float x, int i) {
             const unsigned k = key(x);
             if (level == 3 || (k >> (shift + 8)) == (pre >> (shift + 8))) {
                 const unsigned d = (k >> shift) & 255u;
@@ -665,15 +680,15 @@ __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *h
  * equal keys are walked by ascending id, and `j` of them (1-based) are needed. One of a kind: one
  * sweep finds its id. Several: the low bits of the word are bisected as before.
  */
-template <class KeyF, class MassF>
-__device__ unsigned long long resolve_ties(const Grp &g, GroupShared *sh, const float *row, int V, int idx_bits, const RadixOut &ro, double target, bool inclusive, KeyF &&key,
+template <class Sweep, class KeyF, class MassF>
+__device__ unsigned long long resolve_ties(const Grp &g, GroupShared *sh, Sweep &&sweep, int idx_bits, const RadixOut &ro, double target, bool inclusive, KeyF &&key,
                                            MassF &&mass) {
     if (ro.ties <= 1) {
         if (g.tid == 0) {
             sh->pick = 0x7fffffff;
         }
         g.sync();
-        row_sweep(g, row, V, [&](float x, int i) {
+        sweep([&](float x, int i) {
             if (key(x) == ro.key && mass(x, i) > 0.0) {
                 atomicMin(&sh->pick, i);
             }
@@ -683,11 +698,11 @@ __device__ unsigned long long resolve_ties(const Grp &g, GroupShared *sh, const 
         g.sync();
         return composite(ro.key, id == 0x7fffffff ? 0 : id, idx_bits);
     }
-    return bisect_mass(g, sh, row, V, idx_bits, target, inclusive, key, mass, (unsigned long long) ro.key << idx_bits, idx_bits - 1);
+    return bisect_mass(g, sh, sweep, idx_bits, target, inclusive, key, mass, (unsigned long long) ro.key << idx_bits, idx_bits - 1);
 }
 
 /* All threads of the thread block serve a row whose kept set does not fit the one-pass path. */
-__device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, float row_max, int row_arg, void *hist_mem, int hist_bytes, int slot) {
+__device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, GroupShared *sh, RowCfg &r, float row_max, int row_arg, void *hist_mem, int hist_bytes, int slot, void *save_mem) {
     /* room for the byte histograms of the radix walks: per warp where it fits, else one for all */
     const int copies = hist_bytes >= g.nw * 256 * 12 ? g.nw : 1;
     double   *hm     = reinterpret_cast<double *>(hist_mem);
@@ -699,6 +714,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
     const float *src      = p.logits + (size_t) r.row * (size_t) p.row_stride;
     int         *kept_i   = p.kept_cap > 0 ? p.kept_idx + (size_t) r.row * (size_t) p.kept_cap : nullptr;
     float       *kept_v   = p.kept_cap > 0 ? p.kept_val + (size_t) r.row * (size_t) p.kept_cap : nullptr;
+    auto         row_sw   = [&](auto &&f) { row_sweep(g, gr, V, f); }; /* every entry of the private copy */
     MP(0);
     /* private copy of the row, penalties applied once */
     if (p.aligned) { /* rows start on 16-byte boundaries: four values per load */
@@ -751,8 +767,8 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
         /* the k-th entry in (value desc, id asc) order: a radix walk on counts, then the ids of its ties */
         auto                     okey   = [](float x) { return order_key(x); };
         auto                     one    = [](float, int) { return 1.0; };
-        const RadixOut           rs     = radix_mass<true>(g, sh, hm, hc, copies, 1.0, gr, V, (double) r.k, true, okey, one);
-        const unsigned long long t_set  = rs.found ? resolve_ties(g, sh, gr, V, idx_bits, rs, (double) r.k, true, okey, one) : 0ull;
+        const RadixOut           rs     = radix_mass<true>(g, sh, hm, hc, copies, 1.0, row_sw, (double) r.k, true, okey, one);
+        const unsigned long long t_set  = rs.found ? resolve_ties(g, sh, row_sw, idx_bits, rs, (double) r.k, true, okey, one) : 0ull;
         auto                     in_set = [&](float x, int i) { return composite(order_key(x), i, idx_bits) >= t_set; };
         if (r.select_only) {
             if (g.tid == 0) {
@@ -785,8 +801,8 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
             /* the pick is the earliest walk position whose running sum exceeds u: the largest
              * word t with mass{word >= t} > u */
             auto                     qmass  = [&](float x, int i) { return in_set(x, i) ? qof(x) : 0.0; };
-            const RadixOut           rp     = radix_mass(g, sh, hm, hc, copies, 0x1p49, gr, V, u, false, okey, qmass); /* weights <= 1, at most 8192 of them */
-            unsigned long long       t_pick = rp.found ? resolve_ties(g, sh, gr, V, idx_bits, rp, u, false, okey, qmass) : 0ull;
+            const RadixOut           rp     = radix_mass(g, sh, hm, hc, copies, 0x1p49, row_sw, u, false, okey, qmass); /* weights <= 1, at most 8192 of them */
+            unsigned long long       t_pick = rp.found ? resolve_ties(g, sh, row_sw, idx_bits, rp, u, false, okey, qmass) : 0ull;
             if (t_pick < t_set) {
                 t_pick = t_set;
             }
@@ -832,45 +848,173 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
                 return k >= k_lo ? (min(k, k_hi) - k_lo) << ls : 0u;
             };
             auto mw = [&](float pv, int i) { return keyf(pv) >= k_lo ? mass_in(pv, i) : 0.0; };
-            RadixOut ro = radix_mass(g, sh, hm, hc, copies, 0x1p62, gr, V, target, inclusive, kw, mw); /* probabilities: the row adds up to 1 */
+            RadixOut ro = radix_mass(g, sh, hm, hc, copies, 0x1p62, row_sw, target, inclusive, kw, mw); /* probabilities: the row adds up to 1 */
             ro.key      = (ro.key >> ls) + k_lo; /* back to the key itself */
             return ro;
         };
         const unsigned k_top   = keyf(__double2float_rn(1.0 / S)); /* the largest p: e = 1 at the row maximum */
         const float    p_floor = __double2float_rn(0.5 * (1.0 - (double) r.top_p) / (double) V);
         const unsigned k_floor = (p_floor > 0.0f && keyf(p_floor) < k_top) ? keyf(p_floor) : 0u;
-        RadixOut       rc      = windowed(k_floor, k_top, (double) r.top_p, true, massf);
-        if (!rc.found && k_floor != 0u) {
-            rc = windowed(0u, k_top, (double) r.top_p, true, massf); /* rounding kept the window short of top_p */
-        }
-        MP(5);
-        const unsigned long long t_cut = rc.found ? resolve_ties(g, sh, gr, V, idx_bits, rc, (double) r.top_p, true, keyf, massf) : 0ull;
-        MP(6);
-        double                   nm    = 0.0;
-        long long                ncnt  = 0;
-        row_sweep(g, gr, V, [&](float pv, int i) {
-            if (composite(keyf(pv), i, idx_bits) >= t_cut) {
-                nm += (double) pv;
-                ncnt++;
+        const unsigned long long id_mask = (1ull << idx_bits) - 1ull;
+        unsigned long long t_cut = 0ull, t_pick = 0ull;
+        long long          cut   = 0;
+        bool               have_cut = false, have_pick = false;
+        double             N = 0.0, u = 0.0;
+        /*
+         * Short way. One sweep bins the row by the top byte of the window's key (mass and count per bin). The
+         * walk crosses top_p inside one bin: its entries (a few hundred on rows of this kind) are picked out into
+         * a list, and the crossing entry is found on the list, target reduced by the mass of the bins above. The
+         * draw is walked the same way: the bins' masses are known already (the crossing bin's is what of it lies
+         * in the nucleus), the bin it falls into is picked out if it is another one, and the entry is found on
+         * that list. Three sweeps of the row instead of a dozen and more. Whatever does not fit (a bin with more
+         * entries than the list holds, sums that round apart) takes the long way below.
+         */
+        {
+            const unsigned span = k_top > k_floor ? k_top - k_floor : 0u;
+            const int      ls   = span > 0u ? __clz(span) : 0;
+            auto           kw   = [&](float pv) {
+                const unsigned k = keyf(pv);
+                return k >= k_floor ? (min(k, k_top) - k_floor) << ls : 0u;
+            };
+            auto mwin = [&](float pv, int) { return keyf(pv) >= k_floor ? (double) pv : 0.0; };
+            Pair               *list = p.gen_list + (size_t) slot * (size_t) p.gen_list_cap;
+            unsigned long long *sq   = reinterpret_cast<unsigned long long *>(save_mem); /* the bins' masses and counts, kept */
+            int                *sc   = reinterpret_cast<int *>(sq + 256);
+            auto pick_out = [&](int bin) { /* the entries of one bin into the list; all threads get their number */
+                if (g.tid == 0) {
+                    sh->n_sel = 0;
+                }
+                g.sync();
+                row_sweep(g, gr, V, [&](float pv, int i) {
+                    if (keyf(pv) >= k_floor && (int) (kw(pv) >> 24) == bin && pv > 0.0f) {
+                        const int pos = atomicAdd(&sh->n_sel, 1);
+                        if (pos < p.gen_list_cap) {
+                            list[pos].v   = pv;
+                            list[pos].idx = i;
+                        }
+                    }
+                });
+                __threadfence_block();
+                g.sync();
+                const int n = sh->n_sel;
+                g.sync();
+                return n;
+            };
+            const RadixOut r3 = radix_mass(g, sh, hm, hc, copies, 0x1p62, row_sw, (double) r.top_p, true, kw, mwin, 3);
+            MP(11);
+            if (r3.found && r3.ties <= (long long) p.gen_list_cap && p.gen_list_cap > 0) {
+                const int b_cut = (int) (r3.key >> 24);
+                if (g.tid < 256) { /* the histograms of the sweep are still there: their sums are kept for the draw */
+                    unsigned long long q = 0ull;
+                    int                c = 0;
+                    for (int w = 0; w < copies; w++) {
+                        q += reinterpret_cast<unsigned long long *>(hm)[w * 256 + g.tid];
+                        c += hc[w * 256 + g.tid];
+                    }
+                    sq[g.tid] = q;
+                    sc[g.tid] = c;
+                }
+                g.sync();
+                int  n_list = pick_out(b_cut);
+                MP(12);
+                auto lst_sw = [&](auto &&f) { list_sweep(g, list, n_list, f); };
+                if (n_list <= p.gen_list_cap) {
+                    const double   tgt = (double) r.top_p - r3.above;
+                    const RadixOut rc  = radix_mass(g, sh, hm, hc, copies, 0x1p62, lst_sw, tgt, true, keyf, massf);
+                    if (rc.found) {
+                        MP(13);
+                        t_cut      = resolve_ties(g, sh, lst_sw, idx_bits, rc, tgt, true, keyf, massf);
+                        MP(14);
+                        double nm  = 0.0;
+                        long long ncnt = 0;
+                        lst_sw([&](float pv, int i) {
+                            if (composite(keyf(pv), i, idx_bits) >= t_cut) {
+                                nm += (double) pv;
+                                ncnt++;
+                            }
+                        });
+                        const double in_bin = group_sum_d(g, sh, nm);
+                        N                   = r3.above + in_bin;
+                        cut                 = r3.n_above + group_sum_ll(g, sh, ncnt);
+                        have_cut            = true;
+                        u                   = (double) unit_from(xorshift_next(r.rng)) * N;
+                        /* the bin the draw falls into: a walk over the kept bins from the top, the crossing bin with
+                         * its share of the nucleus */
+                        if (g.tid == 0) {
+                            double run = 0.0;
+                            int    bp  = -1;
+                            for (int bin = 255; bin >= b_cut && bp < 0; bin--) {
+                                const double mb = bin == b_cut ? in_bin : (double) sq[bin] / 0x1p62;
+                                if (u < run + mb) {
+                                    bp = bin;
+                                } else {
+                                    run += mb;
+                                }
+                            }
+                            sh->b_star = bp;
+                            sh->S      = run;
+                        }
+                        g.sync();
+                        MP(15);
+                        const int    b_pick  = sh->b_star;
+                        const double above_p = sh->S;
+                        g.sync();
+                        if (b_pick < 0) {
+                            have_pick = true; /* rounding left u at the very end: the last nucleus entry (sampler.c:292) */
+                        } else if (b_pick == b_cut) {
+                            auto           nml = [&](float pv, int i) { return composite(keyf(pv), i, idx_bits) >= t_cut ? (double) pv : 0.0; };
+                            const double   ut  = u - above_p;
+                            const RadixOut rk  = radix_mass(g, sh, hm, hc, copies, 0x1p62, lst_sw, ut, false, keyf, nml);
+                            t_pick             = rk.found ? resolve_ties(g, sh, lst_sw, idx_bits, rk, ut, false, keyf, nml) : 0ull;
+                            have_pick          = true;
+                        } else if (sc[b_pick] <= p.gen_list_cap) {
+                            n_list = pick_out(b_pick);
+                            MP(16);
+                            if (n_list <= p.gen_list_cap) {
+                                const double   ut = u - above_p;
+                                const RadixOut rk = radix_mass(g, sh, hm, hc, copies, 0x1p62, lst_sw, ut, false, keyf, massf);
+                                t_pick            = rk.found ? resolve_ties(g, sh, lst_sw, idx_bits, rk, ut, false, keyf, massf) : 0ull;
+                                have_pick         = true;
+                            }
+                        }
+                    }
+                }
             }
-        });
-        const double       N      = group_sum_d(g, sh, nm);
-        MP(7);
-        const long long    cut    = group_sum_ll(g, sh, ncnt);
-        const double       u      = (double) unit_from(xorshift_next(r.rng)) * N;
-        auto               nmass  = [&](float pv, int i) { return composite(keyf(pv), i, idx_bits) >= t_cut ? (double) pv : 0.0; };
-        const RadixOut     rk     = windowed((unsigned) (t_cut >> idx_bits), k_top, u, false, nmass);
-        MP(8);
-        unsigned long long t_pick = rk.found ? resolve_ties(g, sh, gr, V, idx_bits, rk, u, false, keyf, nmass) : 0ull;
-        MP(9);
+        }
+        if (!have_cut) { /* the long way: radix walks over the whole row */
+            RadixOut rc = windowed(k_floor, k_top, (double) r.top_p, true, massf);
+            if (!rc.found && k_floor != 0u) {
+                rc = windowed(0u, k_top, (double) r.top_p, true, massf); /* rounding kept the window short of top_p */
+            }
+            MP(5);
+            t_cut = rc.found ? resolve_ties(g, sh, row_sw, idx_bits, rc, (double) r.top_p, true, keyf, massf) : 0ull;
+            MP(6);
+            double    nm   = 0.0;
+            long long ncnt = 0;
+            row_sweep(g, gr, V, [&](float pv, int i) {
+                if (composite(keyf(pv), i, idx_bits) >= t_cut) {
+                    nm += (double) pv;
+                    ncnt++;
+                }
+            });
+            N   = group_sum_d(g, sh, nm);
+            MP(7);
+            cut = group_sum_ll(g, sh, ncnt);
+            u   = (double) unit_from(xorshift_next(r.rng)) * N;
+        }
+        if (!have_pick) {
+            auto           nmass = [&](float pv, int i) { return composite(keyf(pv), i, idx_bits) >= t_cut ? (double) pv : 0.0; };
+            const RadixOut rk    = windowed((unsigned) (t_cut >> idx_bits), k_top, u, false, nmass);
+            MP(8);
+            t_pick = rk.found ? resolve_ties(g, sh, row_sw, idx_bits, rk, u, false, keyf, nmass) : 0ull;
+            MP(9);
+        }
         if (t_pick < t_cut) {
             t_pick = t_cut; /* default: the last nucleus entry (sampler.c:292) */
         }
-        row_sweep(g, gr, V, [&](float pv, int i) {
-            if (composite(keyf(pv), i, idx_bits) == t_pick) {
-                p.tokens[r.row] = i + p.vocab_offset;
-            }
-        });
+        if (g.tid == 0) { /* the word names its entry: the id is in its low bits */
+            p.tokens[r.row] = min((int) (id_mask - (t_pick & id_mask)), V - 1) + p.vocab_offset;
+        }
         if (g.tid == 0 && p.kept_cap > 0) {
             p.kept_n[r.row] = (int) cut;
         }
@@ -2479,7 +2623,7 @@ __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_c
                 if (slot < 0) {
                     st = (st & ~ST_DEFERRED) | ST_INTERNAL;
                 } else {
-                    st = (st & ~ST_DEFERRED) | multipass_row(g, p, &sh->gs, r, bm, ba, cmem, kFinBytes, slot);
+                    st = (st & ~ST_DEFERRED) | multipass_row(g, p, &sh->gs, r, bm, ba, cmem, kFinBytes, slot, &sh->st_v[0][0]); /* the staging of the parts' first slots is free by now: 3 KB of it keep a histogram */
                     __syncthreads();
                     if (g.tid == 0) {
                         __threadfence();
