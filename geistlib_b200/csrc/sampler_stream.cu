@@ -511,6 +511,36 @@ __device__ __forceinline__ void row_rewrite(const Grp &g, float *row, int V, F &
     }
 }
 
+/* out[i] = f(in[i], i): both rows on 16-byte boundaries (in may be out). */
+template <class F>
+__device__ __forceinline__ void row_map(const Grp &g, const float *in, float *out, int V, F &&f) {
+    const int     V4 = V >> 2;
+    const float4 *i4 = reinterpret_cast<const float4 *>(in);
+    float4       *o4 = reinterpret_cast<float4 *>(out);
+    int           j  = g.tid;
+    for (; j + 3 * g.n < V4; j += 4 * g.n) {
+        float4 v[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            v[q] = i4[j + q * g.n];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int b = 4 * (j + q * g.n);
+            v[q].x = f(v[q].x, b), v[q].y = f(v[q].y, b + 1), v[q].z = f(v[q].z, b + 2), v[q].w = f(v[q].w, b + 3);
+            o4[j + q * g.n] = v[q];
+        }
+    }
+    for (; j < V4; j += g.n) {
+        float4 x = i4[j];
+        x.x = f(x.x, 4 * j), x.y = f(x.y, 4 * j + 1), x.z = f(x.z, 4 * j + 2), x.w = f(x.w, 4 * j + 3);
+        o4[j] = x;
+    }
+    for (int i = (V4 << 2) + g.tid; i < V; i += g.n) {
+        out[i] = f(in[i], i);
+    }
+}
+
 /* A walk is written against "something that calls f(value, id) for every entry": the whole private copy of a
  * row, or a short list of (value, id) pairs picked out of it. */
 template <class F>
@@ -564,7 +594,7 @@ struct RadixOut {
  */
 template <bool kUnit = false, class Sweep, class KeyF, class MassF>
 __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *hc, int copies, double scale, Sweep &&sweep, double target, bool inclusive, KeyF &&key,
-                               MassF &&mass, int last_level = 0) {
+                               MassF &&mass, int last_level = 0, bool top_filled = false) {
     /* masses are summed as 64-bit fixed point (mass * scale, truncated): integer adds in shared memory are one
      * instruction whatever the conflicts, and the sums do not depend on the order. The caller picks a scale that
      * keeps the row's total below 2^63. */
@@ -577,6 +607,7 @@ __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *h
     out.ties    = 0;
     for (int level = 3; level >= last_level; level--) { /* last_level 3: the top byte alone; the histograms then stay as they are for the caller */
         const int shift = 8 * level;
+        if (!(top_filled && level == 3)) { /* top_filled: the caller binned the top byte itself while it had the entries in hand */
         for (int i = g.tid; i < copies * 256; i += g.n) {
             hq[i] = 0ull;
             hc[i] = 0;
@@ -600,6 +631,7 @@ __device__ RadixOut radix_mass(const Grp &g, GroupShared *sh, double *hm, int *h
                 }
             }
         });
+        }
         g.sync();
         if (g.warp == 0) {
             /* lane l owns the byte values 255 - 8 l down to 248 - 8 l: the walk order */
@@ -714,10 +746,15 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
     const float *src      = p.logits + (size_t) r.row * (size_t) p.row_stride;
     int         *kept_i   = p.kept_cap > 0 ? p.kept_idx + (size_t) r.row * (size_t) p.kept_cap : nullptr;
     float       *kept_v   = p.kept_cap > 0 ? p.kept_val + (size_t) r.row * (size_t) p.kept_cap : nullptr;
-    auto         row_sw   = [&](auto &&f) { row_sweep(g, gr, V, f); }; /* every entry of the private copy */
+    /* Nothing changes the row's values (no penalties, cap or mask) and it lies on a 16-byte boundary: it is read
+     * where it is, and the private copy only takes what a top-p row is rewritten into. */
+    const bool   in_place = !r.pen_on && !(r.cap > 0.0f) && r.mrow == nullptr && p.aligned != 0;
+    const float *cur      = in_place ? src : gr; /* what the sweeps read */
+    auto         row_sw   = [&](auto &&f) { row_sweep(g, cur, V, f); };
     MP(0);
     /* private copy of the row, penalties applied once */
-    if (p.aligned) { /* rows start on 16-byte boundaries: four values per load */
+    if (in_place) {
+    } else if (p.aligned) { /* rows start on 16-byte boundaries: four values per load */
         const float4 *s4 = reinterpret_cast<const float4 *>(src);
         float4       *d4 = reinterpret_cast<float4 *>(gr);
         for (int i = g.tid; i < (V >> 2); i += g.n) {
@@ -755,7 +792,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
     /* the fast path's slice records need not carry the maximum: take it from the copy */
     row_max = -CUDART_INF_F;
     row_arg = 0x7fffffff;
-    row_sweep(g, gr, V, [&](float x, int i) {
+    row_sweep(g, cur, V, [&](float x, int i) {
         if (row_arg == 0x7fffffff || pair_before(x, i, row_max, row_arg)) {
             row_max = x;
             row_arg = i;
@@ -775,7 +812,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
                 sh->n_sel = 0;
             }
             g.sync();
-            row_sweep(g, gr, V, [&](float x, int i) {
+            row_sweep(g, cur, V, [&](float x, int i) {
                 if (in_set(x, i)) {
                     const int pos = atomicAdd(&sh->n_sel, 1);
                     if (pos < p.kept_cap) {
@@ -791,7 +828,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
         } else {
             auto   qof = [&](float x) { return (double) exp_exact(scaled_arg(x, row_max, r.inv_t)); };
             double m   = 0.0;
-            row_sweep(g, gr, V, [&](float x, int i) {
+            row_sweep(g, cur, V, [&](float x, int i) {
                 if (in_set(x, i)) {
                     m += qof(x);
                 }
@@ -806,7 +843,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
             if (t_pick < t_set) {
                 t_pick = t_set;
             }
-            row_sweep(g, gr, V, [&](float x, int i) {
+            row_sweep(g, cur, V, [&](float x, int i) {
                 if (composite(order_key(x), i, idx_bits) == t_pick) {
                     p.tokens[r.row] = i + p.vocab_offset;
                 }
@@ -824,14 +861,41 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
         /* e_i as a correctly rounded expf gives it: with a nucleus of tens of thousands of ids an
          * exponential that is off by a fraction of an ulp on average moves the running sum by more than
          * the distance between two neighbours of the walk */
-        row_rewrite(g, gr, V, [&](float x, int) {
+        row_map(g, cur, gr, V, [&](float x, int) {
             const float e = exp_exact(scaled_arg(x, row_max, r.inv_t));
             acc += (double) e;
             return e;
         });
+        cur            = gr; /* from here on the sweeps read the rewritten copy */
         const double S = group_sum_d(g, sh, acc);
         MP(3);
-        row_rewrite(g, gr, V, [&](float e, int) { return __double2float_rn((double) e / S); });
+        /* p_i; and while every p_i is in hand it is binned by the top byte of the window's key (what the short way
+         * below starts from) */
+        const unsigned k_top_w   = __float_as_uint(__double2float_rn(1.0 / S));
+        const float    p_floor_w = __double2float_rn(0.5 * (1.0 - (double) r.top_p) / (double) V);
+        const unsigned k_floor_w = (p_floor_w > 0.0f && __float_as_uint(p_floor_w) < k_top_w) ? __float_as_uint(p_floor_w) : 0u;
+        const unsigned span_w    = k_top_w > k_floor_w ? k_top_w - k_floor_w : 0u;
+        const int      ls_w      = span_w > 0u ? __clz(span_w) : 0;
+        {
+            unsigned long long *hq = reinterpret_cast<unsigned long long *>(hm);
+            for (int i = g.tid; i < copies * 256; i += g.n) {
+                hq[i] = 0ull;
+                hc[i] = 0;
+            }
+            g.sync();
+            unsigned long long *mym = hq + (g.warp % copies) * 256;
+            int                *myc = hc + (g.warp % copies) * 256;
+            row_rewrite(g, gr, V, [&](float e, int) {
+                const float    pv = __double2float_rn((double) e / S);
+                const unsigned k  = __float_as_uint(pv);
+                if (k >= k_floor_w && pv > 0.0f) {
+                    const unsigned d = ((min(k, k_top_w) - k_floor_w) << ls_w) >> 24;
+                    atomicAdd(&mym[d], __double2ull_rz((double) pv * 0x1p62));
+                    atomicAdd(&myc[d], 1);
+                }
+                return pv;
+            });
+        }
         g.sync();
         MP(4);
         auto keyf  = [](float pv) { return __float_as_uint(pv); }; /* p >= 0: the bits are ordered */
@@ -900,7 +964,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
                 g.sync();
                 return n;
             };
-            const RadixOut r3 = radix_mass(g, sh, hm, hc, copies, 0x1p62, row_sw, (double) r.top_p, true, kw, mwin, 3);
+            const RadixOut r3 = radix_mass(g, sh, hm, hc, copies, 0x1p62, row_sw, (double) r.top_p, true, kw, mwin, 3, true);
             MP(11);
             if (r3.found && r3.ties <= (long long) p.gen_list_cap && p.gen_list_cap > 0) {
                 const int b_cut = (int) (r3.key >> 24);
