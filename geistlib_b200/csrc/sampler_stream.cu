@@ -751,6 +751,29 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
     const bool   in_place = !r.pen_on && !(r.cap > 0.0f) && r.mrow == nullptr && p.aligned != 0;
     const float *cur      = in_place ? src : gr; /* what the sweeps read */
     auto         row_sw   = [&](auto &&f) { row_sweep(g, cur, V, f); };
+    /* the entries that pred(value, id) names, picked out of the row into this thread block's list (any order);
+     * every thread gets their number, which may exceed the list's room: the caller checks */
+    Pair *list     = p.gen_list + (size_t) slot * (size_t) p.gen_list_cap;
+    auto  pick_out = [&](auto &&pred) {
+        if (g.tid == 0) {
+            sh->n_sel = 0;
+        }
+        g.sync();
+        row_sweep(g, cur, V, [&](float x, int i) {
+            if (pred(x, i)) {
+                const int pos = atomicAdd(&sh->n_sel, 1);
+                if (pos < p.gen_list_cap) {
+                    list[pos].v   = x;
+                    list[pos].idx = i;
+                }
+            }
+        });
+        __threadfence_block();
+        g.sync();
+        const int n = sh->n_sel;
+        g.sync();
+        return n;
+    };
     MP(0);
     /* private copy of the row, penalties applied once */
     if (in_place) {
@@ -804,23 +827,57 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
         /* the k-th entry in (value desc, id asc) order: a radix walk on counts, then the ids of its ties */
         auto                     okey   = [](float x) { return order_key(x); };
         auto                     one    = [](float, int) { return 1.0; };
-        const RadixOut           rs     = radix_mass<true>(g, sh, hm, hc, copies, 1.0, row_sw, (double) r.k, true, okey, one);
-        const unsigned long long t_set  = rs.found ? resolve_ties(g, sh, row_sw, idx_bits, rs, (double) r.k, true, okey, one) : 0ull;
-        auto                     in_set = [&](float x, int i) { return composite(order_key(x), i, idx_bits) >= t_set; };
-        if (r.select_only) {
-            if (g.tid == 0) {
-                sh->n_sel = 0;
-            }
-            g.sync();
-            row_sweep(g, cur, V, [&](float x, int i) {
-                if (in_set(x, i)) {
-                    const int pos = atomicAdd(&sh->n_sel, 1);
-                    if (pos < p.kept_cap) {
-                        kept_i[pos] = i + p.vocab_offset;
-                        kept_v[pos] = x;
+        /* The set's last entry, the short way: one sweep counts the entries per top byte of the key, the byte value
+         * in which the k-th falls is picked out into the list and the k-th is found there. The long way (four
+         * sweeps, ties by bisection) stays for what does not fit the list. */
+        unsigned long long t_set    = 0ull;
+        bool               have_set = false;
+        int                n_list   = 0;
+        auto               lst_sw   = [&](auto &&f) { list_sweep(g, list, n_list, f); };
+        if (p.gen_list_cap > 0) {
+            const RadixOut r3 = radix_mass<true>(g, sh, hm, hc, copies, 1.0, row_sw, (double) r.k, true, okey, one, 3);
+            if (r3.found && r3.ties <= (long long) p.gen_list_cap) {
+                const unsigned top = r3.key >> 24;
+                n_list             = pick_out([&](float x, int) { return (order_key(x) >> 24) == top; });
+                if (n_list <= p.gen_list_cap) {
+                    const double   tgt = (double) r.k - r3.above;
+                    const RadixOut rc  = radix_mass<true>(g, sh, hm, hc, copies, 1.0, lst_sw, tgt, true, okey, one);
+                    if (rc.found) {
+                        t_set    = resolve_ties(g, sh, lst_sw, idx_bits, rc, tgt, true, okey, one);
+                        have_set = true;
                     }
                 }
-            });
+            }
+        }
+        if (!have_set) {
+            const RadixOut rs = radix_mass<true>(g, sh, hm, hc, copies, 1.0, row_sw, (double) r.k, true, okey, one);
+            t_set             = rs.found ? resolve_ties(g, sh, row_sw, idx_bits, rs, (double) r.k, true, okey, one) : 0ull;
+        }
+        auto in_set = [&](float x, int i) { return composite(order_key(x), i, idx_bits) >= t_set; };
+        /* the kept set itself (at most 8192 entries) goes into the list: its sum and the draw are found there */
+        n_list            = p.gen_list_cap > 0 ? pick_out(in_set) : p.gen_list_cap + 1;
+        const bool listed = n_list <= p.gen_list_cap;
+        if (r.select_only) {
+            if (listed) {
+                for (int j = g.tid; j < min(n_list, p.kept_cap); j += g.n) {
+                    kept_i[j] = list[j].idx + p.vocab_offset;
+                    kept_v[j] = list[j].v;
+                }
+            } else {
+                if (g.tid == 0) {
+                    sh->n_sel = 0;
+                }
+                g.sync();
+                row_sweep(g, cur, V, [&](float x, int i) {
+                    if (in_set(x, i)) {
+                        const int pos = atomicAdd(&sh->n_sel, 1);
+                        if (pos < p.kept_cap) {
+                            kept_i[pos] = i + p.vocab_offset;
+                            kept_v[pos] = x;
+                        }
+                    }
+                });
+            }
             if (g.tid == 0) {
                 p.kept_n[r.row] = r.k;
                 p.tokens[r.row] = row_arg + p.vocab_offset;
@@ -828,26 +885,32 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
         } else {
             auto   qof = [&](float x) { return (double) exp_exact(scaled_arg(x, row_max, r.inv_t)); };
             double m   = 0.0;
-            row_sweep(g, cur, V, [&](float x, int i) {
-                if (in_set(x, i)) {
-                    m += qof(x);
+            auto   set_sw = [&](auto &&f) { /* the kept set: from the list, else filtered out of the row */
+                if (listed) {
+                    list_sweep(g, list, n_list, f);
+                } else {
+                    row_sweep(g, cur, V, [&](float x, int i) {
+                        if (in_set(x, i)) {
+                            f(x, i);
+                        }
+                    });
                 }
-            });
+            };
+            set_sw([&](float x, int) { m += qof(x); });
             const double S = group_sum_d(g, sh, m);
             const double u = (double) unit_from(xorshift_next(r.rng)) * S;
             /* the pick is the earliest walk position whose running sum exceeds u: the largest
              * word t with mass{word >= t} > u */
-            auto                     qmass  = [&](float x, int i) { return in_set(x, i) ? qof(x) : 0.0; };
-            const RadixOut           rp     = radix_mass(g, sh, hm, hc, copies, 0x1p49, row_sw, u, false, okey, qmass); /* weights <= 1, at most 8192 of them */
-            unsigned long long       t_pick = rp.found ? resolve_ties(g, sh, row_sw, idx_bits, rp, u, false, okey, qmass) : 0ull;
+            auto                     qmass  = [&](float x, int) { return qof(x); };
+            const RadixOut           rp     = radix_mass(g, sh, hm, hc, copies, 0x1p49, set_sw, u, false, okey, qmass); /* weights <= 1, at most 8192 of them */
+            unsigned long long       t_pick = rp.found ? resolve_ties(g, sh, set_sw, idx_bits, rp, u, false, okey, qmass) : 0ull;
             if (t_pick < t_set) {
                 t_pick = t_set;
             }
-            row_sweep(g, cur, V, [&](float x, int i) {
-                if (composite(order_key(x), i, idx_bits) == t_pick) {
-                    p.tokens[r.row] = i + p.vocab_offset;
-                }
-            });
+            if (g.tid == 0) { /* the word names its entry */
+                const unsigned long long id_mask = (1ull << idx_bits) - 1ull;
+                p.tokens[r.row]                  = min((int) (id_mask - (t_pick & id_mask)), V - 1) + p.vocab_offset;
+            }
             if (g.tid == 0 && p.kept_cap > 0) {
                 p.kept_n[r.row] = r.k;
             }
@@ -941,29 +1004,9 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
                 return k >= k_floor ? (min(k, k_top) - k_floor) << ls : 0u;
             };
             auto mwin = [&](float pv, int) { return keyf(pv) >= k_floor ? (double) pv : 0.0; };
-            Pair               *list = p.gen_list + (size_t) slot * (size_t) p.gen_list_cap;
             unsigned long long *sq   = reinterpret_cast<unsigned long long *>(save_mem); /* the bins' masses and counts, kept */
             int                *sc   = reinterpret_cast<int *>(sq + 256);
-            auto pick_out = [&](int bin) { /* the entries of one bin into the list; all threads get their number */
-                if (g.tid == 0) {
-                    sh->n_sel = 0;
-                }
-                g.sync();
-                row_sweep(g, gr, V, [&](float pv, int i) {
-                    if (keyf(pv) >= k_floor && (int) (kw(pv) >> 24) == bin && pv > 0.0f) {
-                        const int pos = atomicAdd(&sh->n_sel, 1);
-                        if (pos < p.gen_list_cap) {
-                            list[pos].v   = pv;
-                            list[pos].idx = i;
-                        }
-                    }
-                });
-                __threadfence_block();
-                g.sync();
-                const int n = sh->n_sel;
-                g.sync();
-                return n;
-            };
+            auto in_bin_of = [&](int bin) { return [&, bin](float pv, int) { return keyf(pv) >= k_floor && (int) (kw(pv) >> 24) == bin && pv > 0.0f; }; };
             const RadixOut r3 = radix_mass(g, sh, hm, hc, copies, 0x1p62, row_sw, (double) r.top_p, true, kw, mwin, 3, true);
             MP(11);
             if (r3.found && r3.ties <= (long long) p.gen_list_cap && p.gen_list_cap > 0) {
@@ -979,7 +1022,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
                     sc[g.tid] = c;
                 }
                 g.sync();
-                int  n_list = pick_out(b_cut);
+                int  n_list = pick_out(in_bin_of(b_cut));
                 MP(12);
                 auto lst_sw = [&](auto &&f) { list_sweep(g, list, n_list, f); };
                 if (n_list <= p.gen_list_cap) {
@@ -1032,7 +1075,7 @@ __device__ __noinline__ int multipass_row(const Grp &g, const SampleParams &p, G
                             t_pick             = rk.found ? resolve_ties(g, sh, lst_sw, idx_bits, rk, ut, false, keyf, nml) : 0ull;
                             have_pick          = true;
                         } else if (sc[b_pick] <= p.gen_list_cap) {
-                            n_list = pick_out(b_pick);
+                            n_list = pick_out(in_bin_of(b_pick));
                             MP(16);
                             if (n_list <= p.gen_list_cap) {
                                 const double   ut = u - above_p;
