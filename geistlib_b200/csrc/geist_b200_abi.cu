@@ -23,7 +23,7 @@ namespace gb {
 size_t      sample_stream_smem(int n_slices, int long_ids);
 cudaError_t sample_stream_ctas_per_sm(size_t smem_bytes, int *out);
 cudaError_t finish_rows_max_ctas(int sms, int *out);
-cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, int finish_grid, bool second_finisher, cudaStream_t stream);
+cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, int finish_grid, cudaStream_t stream);
 cudaError_t launch_merge_sample(const MergeParams &p, cudaStream_t stream);
 cudaError_t launch_accept(const AcceptParams &p, cudaStream_t stream);
 cudaError_t launch_scatter_kept(const int *kept_n, const int *kept_idx, const float *kept_val, int kept_cap, int n_rows, int V, int vocab_offset, float *dense, cudaStream_t stream);
@@ -380,7 +380,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.aligned      = ((reinterpret_cast<uintptr_t>(b->logits) & 15u) == 0 && (b->row_stride & 3u) == 0) ? 1 : 0;
     p.flags        = flags;
     if ((flags & gb::F_SELECT_ONLY) == 0u) { /* a shard's select is a top-k row whatever its parameters say: the small kernel takes k <= kFastKMax, the general one the rest */
-        p.flags |= b->finish_hint == GEIST_B200_FINISH_GREEDY_TOPK ? gb::F_FAST_ONLY : (b->finish_hint == GEIST_B200_FINISH_GENERAL ? gb::F_REST_ONLY : 0u);
+        p.flags |= b->finish_hint == GEIST_B200_FINISH_GREEDY_TOPK ? gb::F_FAST_ONLY : 0u;
         if (b->finish_hint == GEIST_B200_FINISH_GREEDY) {
             p.flags |= gb::F_FAST_ONLY | gb::F_GREEDY_ONLY; /* where rows are split over thread blocks the small finishing kernel still merges them */
         }
@@ -411,8 +411,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     const size_t off_ls   = round_up(off_dl + slots * gen_hcap * sizeof(gb::Pair), 256);
     const size_t off_pl   = round_up(off_ls + slots * gen_lcap * sizeof(gb::Pair), 256);
     const size_t off_po   = round_up(off_pl + (pl.id_slots ? n_rows * (size_t) pl.row_cap * 4 : 0), 256);
-    const size_t off_def  = round_up(off_po + (pl.id_slots ? n_rows * (size_t) (pl.n_slices + 1) * 4 : 0), 256);
-    const size_t need     = round_up(off_def + (n_rows + 4) * 4, 256);
+    const size_t need     = round_up(off_po + (pl.id_slots ? n_rows * (size_t) (pl.n_slices + 1) * 4 : 0), 256) + 256;
     geist_b200_ctx::Lane *ln;
     {
         std::lock_guard<std::mutex> lk(ctx->lane_mu);
@@ -436,8 +435,6 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
             ln->counter_cap = cap;
         }
     }
-    p.def_count        = reinterpret_cast<int *>(ln->buf + off_def);
-    p.def_rows         = p.def_count + 4;
     p.pool             = ln->counters;
     p.pool_slots       = (int) slots;
     p.grp_v            = reinterpret_cast<float4 *>(ln->buf + off_gv);
@@ -453,7 +450,7 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     p.gen_list_cap     = (int) gen_lcap;
     p.pre_list         = reinterpret_cast<unsigned *>(ln->buf + off_pl);
     p.pre_off          = reinterpret_cast<int *>(ln->buf + off_po);
-    CUDA_TRY(gb::launch_sample_stream(p, grid, pl.smem, fin_grid, true, st));
+    CUDA_TRY(gb::launch_sample_stream(p, grid, pl.smem, fin_grid, st));
     return GEIST_OK;
 }
 

@@ -42,9 +42,8 @@ enum : int {
 
 enum : unsigned {
     F_SELECT_ONLY = 1u << 0, /* vocabulary shard: emit the row's best k (value, global id), no draw */
-    F_FAST_ONLY   = 1u << 1, /* the caller vouches that every row is greedy or top-k <= kFastKMax: only the small finishing kernel runs */
+    F_FAST_ONLY   = 1u << 1, /* the caller vouches that every row is greedy or top-k <= kFastKMax: the small finishing kernel runs instead of the general one */
     F_GREEDY_ONLY = 1u << 3, /* the caller vouches that every row is greedy: where a thread block streams whole rows it writes their tokens itself and no finishing kernel runs */
-    F_REST_ONLY   = 1u << 2, /* the caller expects no such rows: only the general finishing kernel runs, over all rows */
 };
 
 struct Pair {
@@ -139,8 +138,6 @@ struct SampleParams {
     unsigned flags;
 
     /* scratch in global memory (one lane of the context's scratch) */
-    int       *def_count;   /* rows the first finishing kernel left to the second one ... */
-    int       *def_rows;    /* [n_rows] ... and which */
     int       *pool;        /* [pool_slots] 1: the row copy of this number is taken; zero between launches */
     int        pool_slots;
     float4    *grp_v;       /* [n_rows, parts_max, kPartSlots] per part: its PartRec (two slots), then its candidate groups: four consecutive values ... */

@@ -24,16 +24,17 @@
  *   two 16-byte slots) followed by its candidate groups to the part's place in global scratch. Nothing else is
  *   shared between thread blocks: no counters, no thread block waits for another one.
  *
- *   Finishing is left to kernels of their own behind the stream kernel, launched as programmatic dependents so
- *   that their thread blocks are placed while the kernel before them drains. finish_rows_kernel<true>: one thread
- *   block per row merges the parts' records; greedy rows end there; top-k rows (k <= 256) get their surviving
- *   candidates ordered, their probabilities evaluated exactly (double exp rounded once) and the draw made; every
- *   other row goes on a list. finish_rows_kernel<false> takes that list: temperature rows walk the per-warp
- *   segment sums and re-read the one segment that the draw falls into; top-p rows with a small nucleus are
- *   served from the candidates and the sums of the rest; rows whose kept set is too large for one pass (top-k
- *   beyond 256, wide nuclei) get radix walks over a private copy of the row in global scratch (the multi-pass
- *   path, ROW_SLOW_PATH). A caller that knows its rows' modes drops the kernel it does not need (F_FAST_ONLY /
- *   F_REST_ONLY). Histories of more than kRowIds ids are counted per row by row_ids_kernel ahead of all this.
+ *   Finishing is left to a kernel of its own behind the stream kernel, launched as a programmatic dependent so
+ *   that its thread blocks are placed while the stream kernel drains: one thread block per row merges the parts'
+ *   records; greedy rows end there; top-k rows (k <= 256) get their surviving candidates ordered, their
+ *   probabilities evaluated exactly (double exp rounded once) and the draw made; temperature rows walk the
+ *   per-warp segment sums and re-read the one segment that the draw falls into; top-p rows with a small nucleus
+ *   are served from the candidates and the sums of the rest; rows whose kept set is too large for one pass
+ *   (top-k beyond 256, wide nuclei) are worked on a private copy of the row in global scratch (the multi-pass
+ *   path, ROW_SLOW_PATH). finish_rows_kernel<false> carries all of that; finish_rows_kernel<true> carries greedy
+ *   and top-k alone and is launched instead when the caller vouched for such rows (F_FAST_ONLY); with
+ *   F_GREEDY_ONLY thread blocks that stream whole rows write the tokens themselves and no finishing kernel runs.
+ *   Histories of more than kRowIds ids are counted per row by row_ids_kernel ahead of all this.
  *
  * Semantics follow geistlib's CPU sampler:
  *   mode dispatch ............ src/archs/transformer/forward/head.c:172-183
@@ -155,7 +156,7 @@ static_assert((long long) kMaxSlices * kSliceMax <= (1ll << 28), "a candidate gr
 
 enum Mode { M_ARGMAX, M_TOPK, M_TOPP, M_TEMP };
 
-constexpr int ST_DEFERRED = 1 << 30; /* inside the kernel only: the row waits for the multi-pass path at the kernel's end */
+constexpr int ST_DEFERRED = 1 << 30; /* inside the kernel only: the one-pass finish could not serve the row (the multi-pass path has to, or the kernel lacks the code) */
 
 /* Everything a row needs that does not depend on the slice. */
 struct RowCfg {
@@ -1551,7 +1552,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
     }
 
     if (kFast && r.mode != M_TOPK) {
-        return st | ST_DEFERRED; /* temperature and top-p rows are finished by the kernel behind this one */
+        return st | ST_DEFERRED; /* temperature and top-p rows: the general finishing kernel's */
     }
     if constexpr (!kFast) {
     if (r.mode == M_TEMP) {
@@ -2088,9 +2089,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
     }
 #endif
     PROF(0);
-    if (blockIdx.x == 0 && tid == 0) {
-        p.def_count[0] = 0; /* the list of rows left to the second finishing kernel starts empty */
-    }
 
     /* ---- the warp's own ring: lane 0 asks for the warp's share of the item kStages ahead ---- */
     unsigned char *wring = ring + (size_t) warp * kStages * kWarpStageBytes;
@@ -2654,14 +2652,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
 /* ----------------------------------------------------------- finishing kernel -- */
 
 /*
- * Run behind the stream kernel. finish_rows_kernel<true>: one thread block finishes one row at a time (rows
- * blockIdx.x, blockIdx.x + gridDim.x, ...): it merges the records that the row's parts left; greedy rows end
- * there; top-k rows (k <= 256) get their few surviving candidates ordered, their probabilities evaluated exactly
- * and the draw made. Every other row (temperature, top-p, kept sets too large for this) is put on a list for
- * finish_rows_kernel<false>, which is launched behind it and carries the code for those: segment walks, nucleus
- * sums, and the multi-pass path over a private copy of the row (the copies come from a small pool that the
- * thread blocks claim slots of). Both write the row's status and, behind a sequence's last row, its generator.
- * The split keeps the kernel that every launch needs small.
+ * Run behind the stream kernel, one thread block per row at a time (rows blockIdx.x, blockIdx.x + gridDim.x, ...):
+ * it merges the records that the row's parts left and finishes the row. finish_rows_kernel<false> carries the
+ * code for every kind of row: greedy, top-k, temperature (segment walks), top-p (nucleus sums), and the
+ * multi-pass path over a private copy of the row (the copies come from a small pool that the thread blocks claim
+ * slots of). finish_rows_kernel<true> carries greedy and top-k (k <= 256) alone: a tenth of the code, 7 - 8 us
+ * less per launch; it is launched instead when the caller vouched for such rows, and reports any other row as
+ * ROW_INTERNAL. Both write the row's status and, behind a sequence's last row, its generator.
  */
 template <bool kFast>
 __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_constant__ SampleParams p) {
@@ -2676,34 +2673,24 @@ __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_c
     g.n    = kThreads;
     g.nw   = kWarps;
     g.bar  = 0;
-    const bool all_rows = kFast || (p.flags & F_REST_ONLY) != 0u;
     /* The first row's parameters are inputs of the launch, written before the stream kernel began: they may be
      * read while that kernel's last thread blocks are still at work. Everything it wrote waits for the line below. */
     RawCfg rc0{};
-    if (all_rows && (int) blockIdx.x < p.n_rows) {
+    if ((int) blockIdx.x < p.n_rows) {
         rc0 = raw_config(p, (int) blockIdx.x, true);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory"); /* the records of the kernel before this one are complete and visible */
     asm volatile("griddepcontrol.launch_dependents;");
     PROF(kFast ? 5 : 7);
-    const int  n_todo   = all_rows ? p.n_rows : min(__ldcg(p.def_count), p.n_rows);
-    for (int it = (int) blockIdx.x; it < n_todo; it += (int) gridDim.x) {
-        const int row = all_rows ? it : __ldcg(&p.def_rows[it]);
-        const RawCfg rc = (all_rows && it == (int) blockIdx.x) ? rc0 : raw_config(p, row, true);
+    for (int row = (int) blockIdx.x; row < p.n_rows; row += (int) gridDim.x) {
+        const RawCfg rc = row == (int) blockIdx.x ? rc0 : raw_config(p, row, true);
         RowCfg       r  = row_config(p, row, rc, true);
         PROF(8);
         int          st = finish_row<kFast>(g, p, sh, r, cmem);
         PROF(13);
         if (st & ST_DEFERRED) {
             if constexpr (kFast) {
-                if ((p.flags & F_FAST_ONLY) == 0u) {
-                    if (g.tid == 0) {
-                        p.def_rows[atomicAdd(p.def_count, 1)] = row; /* at most n_rows entries */
-                    }
-                    __syncthreads();
-                    continue;
-                }
-                /* the caller said that no such row would come and no kernel behind this one takes it */
+                /* the caller said that no such row would come: this kernel does not carry the code for it */
                 st = (st & ~ST_DEFERRED) | ST_INTERNAL;
                 if (g.tid == 0) {
                     p.tokens[row] = -1;
@@ -2945,7 +2932,7 @@ cudaError_t finish_rows_max_ctas(int sms, int *out) {
     return e;
 }
 
-cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, int finish_grid, bool second_finisher, cudaStream_t stream) {
+cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_bytes, int finish_grid, cudaStream_t stream) {
     cudaError_t e = ensure_attributes(smem_bytes);
     if (e == cudaSuccess) {
         e = ensure_finish_attributes();
@@ -2988,11 +2975,11 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     if ((p.flags & F_GREEDY_ONLY) != 0u && p.map.mode == RUN_ROWS) {
         return cudaSuccess; /* the stream kernel wrote the tokens itself */
     }
-    if ((p.flags & F_REST_ONLY) == 0u) {
-        e = cudaLaunchKernelEx(&cfg, finish_rows_kernel<true>, p);
-        if (e != cudaSuccess || !second_finisher || (p.flags & F_FAST_ONLY) != 0u) {
-            return e;
-        }
+    /* one finishing kernel per launch: the small one when the caller vouched for greedy / top-k rows, else the
+     * general one (it finishes every kind of row; a third kernel in the chain of dependent launches cost 7 - 8 us
+     * even when it had no row to take, as much as the general kernel costs more than the small one) */
+    if ((p.flags & F_FAST_ONLY) != 0u) {
+        return cudaLaunchKernelEx(&cfg, finish_rows_kernel<true>, p);
     }
     return cudaLaunchKernelEx(&cfg, finish_rows_kernel<false>, p);
 }
