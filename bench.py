@@ -50,9 +50,9 @@ N_SETS = 8
 SEED = 1234
 # algorithmic bytes per row: logits once + history ids + generator state in/out + token out
 BYTES_PER_ROW = 4 * V + 4 * H + 16 + 4
-# sample_stream_kernel and the small finishing kernel: every session of the workload samples top-k 40, which the caller
-# (here as in the session batcher) tells the launch with finish_hint = GREEDY_TOPK; without the hint a third kernel
-# (the general finisher, idle for these rows) is launched as well -- the "finish_hint=AUTO" entry of `modes`
+# sample_stream_kernel and one finishing kernel: every session of the workload samples top-k 40, which the caller
+# (here as in the session batcher) tells the launch with finish_hint = GREEDY_TOPK, so the small finishing kernel
+# runs; without the hint the general one does -- the "finish_hint=AUTO" entry of `modes`
 KERNELS_PER_STEP = 2
 WORKLOAD = ("B=256 rows x V=128256 fp32 logits ~ N(0,2.5^2) with 8 ids/row +12; temperature 0.8, top_k 40, "
             "top_p 0.95 (top_k precedence), repetition penalty 1.1 over 64-token history, 1 draw/row, seed 1234")
