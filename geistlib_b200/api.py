@@ -23,7 +23,7 @@ GEIST_OK = 0
 STATUS_NAMES = ["GEIST_OK", "GEIST_E_OOM", "GEIST_E_INVALID_ARG", "GEIST_E_INTERNAL", "GEIST_E_FILE_NOT_FOUND",
                 "GEIST_E_IO", "GEIST_E_FORMAT", "GEIST_E_UNSUPPORTED", "GEIST_E_NOT_FOUND", "GEIST_E_BACKEND",
                 "GEIST_E_INVALID_STATE", "GEIST_E_TOO_MANY_TOKENS"]
-ROW_LOAD_TIMEOUT, ROW_SLOW_PATH, ROW_HIST_OVERFLOW, ROW_KEPT_PARTIAL, ROW_INTERNAL = 1, 2, 4, 8, 16
+ROW_LOAD_TIMEOUT, ROW_SLOW_PATH, ROW_HIST_OVERFLOW, ROW_KEPT_PARTIAL, ROW_INTERNAL, ROW_RETRY = 1, 2, 4, 8, 16, 32
 FINISH_AUTO, FINISH_GREEDY_TOPK, FINISH_GENERAL, FINISH_GREEDY = 0, 1, 2, 3
 ROW_INVALID = ROW_LOAD_TIMEOUT | ROW_HIST_OVERFLOW | ROW_INTERNAL
 SPEC_KMAX = 16

@@ -1260,87 +1260,114 @@ enum geist_status batcher_run(geist_b200_batcher *b, size_t n, const int32_t *se
     d.logit_mask_stride  = b->mask_words;
     d.finish_hint        = hint;
 
-    if (!logits_on_host) {
-        d.logits     = logits;
-        d.row_stride = row_stride;
-        d.n_seq      = n;
-        d.slot       = b->d_slot;
-        d.fed_tokens = (pen && verify) ? b->d_fed : nullptr;
-        d.tokens     = b->d_tokens;
-        d.row_status = b->d_status;
-        enum geist_status s = geist_b200_sample_batch(b->ctx, &d, st);
-        if (s != GEIST_OK) {
-            return s;
-        }
-    } else {
-        /* host logits: copy in chunks of sequences on two streams so that one chunk's kernel
-         * runs under the next chunk's copy */
-        if (b->d_logits_cap < rows * b->V) {
-            cudaFree(b->d_logits);
-            b->d_logits     = nullptr;
-            b->d_logits_cap = 0;
-            CUDA_TRY(cudaMalloc((void **) &b->d_logits, rows * b->V * sizeof(float)));
-            b->d_logits_cap = rows * b->V;
-        }
-        CUDA_TRY(cudaEventRecord(b->ev[0], st)); /* slots / fed are on the way */
-        const size_t seq_chunk = std::max<size_t>(1, (32 + k - 1) / k);
-        int          which     = 0;
-        for (size_t s0 = 0; s0 < n; s0 += seq_chunk, which ^= 1) {
-            const size_t ns = std::min(seq_chunk, n - s0);
-            cudaStream_t cs = b->copy_stream[which];
-            if (s0 < 2 * seq_chunk) {
-                CUDA_TRY(cudaStreamWaitEvent(cs, b->ev[0], 0));
-            }
-            if (row_stride == b->V) { /* dense rows: one linear copy per chunk */
-                CUDA_TRY(cudaMemcpyAsync(b->d_logits + s0 * k * b->V, logits + s0 * k * row_stride, ns * k * b->V * 4, cudaMemcpyHostToDevice, cs));
-            } else {
-                CUDA_TRY(cudaMemcpy2DAsync(b->d_logits + s0 * k * b->V, b->V * 4, logits + s0 * k * row_stride, row_stride * 4, b->V * 4, ns * k, cudaMemcpyHostToDevice, cs));
-            }
-            d.logits     = b->d_logits + s0 * k * b->V;
-            d.row_stride = b->V;
-            d.n_seq      = ns;
-            d.slot       = b->d_slot + s0;
-            d.fed_tokens = (pen && verify) ? b->d_fed + s0 * k : nullptr;
-            d.tokens     = b->d_tokens + s0 * k;
-            d.row_status = b->d_status + s0 * k;
-            enum geist_status s = geist_b200_sample_batch(b->ctx, &d, cs);
+    /* the sampling launch(es); run a second time without the hint when a row asked for that */
+    auto launch_sampling = [&](bool copy_in) -> enum geist_status {
+        if (!logits_on_host) {
+            d.logits     = logits;
+            d.row_stride = row_stride;
+            d.n_seq      = n;
+            d.slot       = b->d_slot;
+            d.fed_tokens = (pen && verify) ? b->d_fed : nullptr;
+            d.tokens     = b->d_tokens;
+            d.row_status = b->d_status;
+            enum geist_status s = geist_b200_sample_batch(b->ctx, &d, st);
             if (s != GEIST_OK) {
                 return s;
             }
+        } else {
+            /* host logits: copy in chunks of sequences on two streams so that one chunk's kernel
+             * runs under the next chunk's copy */
+            if (b->d_logits_cap < rows * b->V) {
+                cudaFree(b->d_logits);
+                b->d_logits     = nullptr;
+                b->d_logits_cap = 0;
+                CUDA_TRY(cudaMalloc((void **) &b->d_logits, rows * b->V * sizeof(float)));
+                b->d_logits_cap = rows * b->V;
+            }
+            CUDA_TRY(cudaEventRecord(b->ev[0], st)); /* slots / fed are on the way */
+            const size_t seq_chunk = std::max<size_t>(1, (32 + k - 1) / k);
+            int          which     = 0;
+            for (size_t s0 = 0; s0 < n; s0 += seq_chunk, which ^= 1) {
+                const size_t ns = std::min(seq_chunk, n - s0);
+                cudaStream_t cs = b->copy_stream[which];
+                if (s0 < 2 * seq_chunk) {
+                    CUDA_TRY(cudaStreamWaitEvent(cs, b->ev[0], 0));
+                }
+                if (!copy_in) {
+                /* second time round: the rows are on the device already */
+            } else if (row_stride == b->V) { /* dense rows: one linear copy per chunk */
+                    CUDA_TRY(cudaMemcpyAsync(b->d_logits + s0 * k * b->V, logits + s0 * k * row_stride, ns * k * b->V * 4, cudaMemcpyHostToDevice, cs));
+                } else {
+                    CUDA_TRY(cudaMemcpy2DAsync(b->d_logits + s0 * k * b->V, b->V * 4, logits + s0 * k * row_stride, row_stride * 4, b->V * 4, ns * k, cudaMemcpyHostToDevice, cs));
+                }
+                d.logits     = b->d_logits + s0 * k * b->V;
+                d.row_stride = b->V;
+                d.n_seq      = ns;
+                d.slot       = b->d_slot + s0;
+                d.fed_tokens = (pen && verify) ? b->d_fed + s0 * k : nullptr;
+                d.tokens     = b->d_tokens + s0 * k;
+                d.row_status = b->d_status + s0 * k;
+                enum geist_status s = geist_b200_sample_batch(b->ctx, &d, cs);
+                if (s != GEIST_OK) {
+                    return s;
+                }
+            }
+            for (int i = 0; i < 2; i++) {
+                CUDA_TRY(cudaEventRecord(b->ev[1], b->copy_stream[i]));
+                CUDA_TRY(cudaStreamWaitEvent(st, b->ev[1], 0));
+            }
         }
-        for (int i = 0; i < 2; i++) {
-            CUDA_TRY(cudaEventRecord(b->ev[1], b->copy_stream[i]));
-            CUDA_TRY(cudaStreamWaitEvent(st, b->ev[1], 0));
-        }
-    }
+        return GEIST_OK;
+    };
     const int *append_tok = b->d_tokens;
     const int *append_cnt = b->d_ones;
     int        per_seq    = 1;
     int        first      = 0;
     if (verify) {
-        gb::AcceptParams ap{b->d_fed, b->d_tokens, (int) n, (int) k, b->d_accepted, b->d_nemit, b->d_emitted};
-        CUDA_TRY(gb::launch_accept(ap, st));
         append_tok = b->d_emitted;
         append_cnt = b->d_nemit;
         per_seq    = (int) k + 1;
         first      = 1; /* emitted[0] is the pending token, which joined the history when it was sampled */
     }
+    for (int attempt = 0; attempt < 2; attempt++) {
+        const enum geist_status ls = launch_sampling(attempt == 0);
+        if (ls != GEIST_OK) {
+            return ls;
+        }
+        if (verify) {
+            gb::AcceptParams ap{b->d_fed, b->d_tokens, (int) n, (int) k, b->d_accepted, b->d_nemit, b->d_emitted};
+            CUDA_TRY(gb::launch_accept(ap, st));
+        }
+        CUDA_TRY(cudaMemcpyAsync(h_stat, b->d_status, rows * 4, cudaMemcpyDeviceToHost, st));
+        if (verify) {
+            CUDA_TRY(cudaMemcpyAsync(h_acc, b->d_accepted, n * 4, cudaMemcpyDeviceToHost, st));
+            CUDA_TRY(cudaMemcpyAsync(h_nem, b->d_nemit, n * 4, cudaMemcpyDeviceToHost, st));
+            CUDA_TRY(cudaMemcpyAsync(h_emit, b->d_emitted, n * (k + 1) * 4, cudaMemcpyDeviceToHost, st));
+        } else {
+            CUDA_TRY(cudaMemcpyAsync(h_tok, b->d_tokens, rows * 4, cudaMemcpyDeviceToHost, st));
+        }
+        CUDA_TRY(cudaStreamSynchronize(st));
+        bool retry = false;
+        for (size_t i = 0; i < rows; i++) {
+            if (h_stat[i] & (GEIST_B200_ROW_LOAD_TIMEOUT | GEIST_B200_ROW_HIST_OVERFLOW | GEIST_B200_ROW_INTERNAL)) {
+                return fail(GEIST_E_BACKEND, "batcher: row %zu reported status 0x%x", i, h_stat[i]);
+            }
+            retry |= (h_stat[i] & GEIST_B200_ROW_RETRY) != 0;
+        }
+        if (!retry) {
+            break;
+        }
+        if (attempt == 1) {
+            return fail(GEIST_E_BACKEND, "batcher: a row asked to be launched again twice");
+        }
+        /* a top-k row with more candidates than the small finishing kernel holds (rare: thousands of equal values
+         * at the top): the whole call again with the general kernel; nothing of the first attempt was committed */
+        d.finish_hint = GEIST_B200_FINISH_AUTO;
+    }
+    /* committed behind the host's look at the status: generator words and history ring (asynchronous: the next call
+     * is ordered behind it on the same stream) */
     CUDA_TRY(gb::launch_post_step(b->d_slot, (int) n, per_seq, first, (append_history && b->max_history) ? append_tok : nullptr, append_cnt, b->d_hist, (int) b->max_history,
                                   b->d_hist_len, b->d_hist_tot, b->d_rng_tmp, b->d_rng, st));
-    CUDA_TRY(cudaMemcpyAsync(h_stat, b->d_status, rows * 4, cudaMemcpyDeviceToHost, st));
-    if (verify) {
-        CUDA_TRY(cudaMemcpyAsync(h_acc, b->d_accepted, n * 4, cudaMemcpyDeviceToHost, st));
-        CUDA_TRY(cudaMemcpyAsync(h_nem, b->d_nemit, n * 4, cudaMemcpyDeviceToHost, st));
-        CUDA_TRY(cudaMemcpyAsync(h_emit, b->d_emitted, n * (k + 1) * 4, cudaMemcpyDeviceToHost, st));
-    } else {
-        CUDA_TRY(cudaMemcpyAsync(h_tok, b->d_tokens, rows * 4, cudaMemcpyDeviceToHost, st));
-    }
-    CUDA_TRY(cudaStreamSynchronize(st));
-    for (size_t i = 0; i < rows; i++) {
-        if (h_stat[i] & (GEIST_B200_ROW_LOAD_TIMEOUT | GEIST_B200_ROW_HIST_OVERFLOW | GEIST_B200_ROW_INTERNAL)) {
-            return fail(GEIST_E_BACKEND, "batcher: row %zu reported status 0x%x", i, h_stat[i]);
-        }
-    }
     const float *dev_rows = logits_on_host ? b->d_logits : logits;
     const size_t dev_stride = logits_on_host ? b->V : row_stride;
     if (verify) {

@@ -38,6 +38,7 @@ enum : int {
     ST_HIST_OVERFLOW = 1 << 2, /* more distinct history ids than the launch reserved */
     ST_KEPT_PARTIAL  = 1 << 3, /* kept-set list not materialised (only kept_n is valid) */
     ST_INTERNAL      = 1 << 4, /* an invariant of the select failed; row result is invalid */
+    ST_RETRY         = 1 << 5, /* the small finishing kernel met a top-k row whose candidates did not fit its lists: not sampled, to be launched again without the hint */
 };
 
 enum : unsigned {

@@ -1711,23 +1711,41 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
     }
     /* ---- top-k and top-p: merge the parts' candidate groups ---- */
     const int n_groups       = others;
-    bool      need_multipass = !(r.kq > 0 && r.kq <= kFastKMax) || overflow || n_groups > 2 * kFinCap;
+    bool      need_multipass = !(r.kq > 0 && r.kq <= kFastKMax) || overflow || n_groups > 8 * kFinCap; /* what counts is how many stay above the row's threshold: checked below */
     if (!need_multipass) {
-        if (g.tid == 0) {
-            sh->n_ent = 0;
-        }
-        g.sync();
         const bool keep_all = r.mode == M_TOPP; /* every marked entry was left out of the bulk sums */
+        /* The candidates of all parts are merged in up to three rounds of one rolled loop. Round 0 keeps what
+         * passes the row's threshold (the largest of the parts' thresholds). A row cut into many parts can have far
+         * more of those than k (every part kept at least k of its own): if they do not fit, round 1 bins them by
+         * value between the threshold and the row's maximum, and round 2 keeps the bins from the top down to the
+         * one in which the kq-th falls. */
+        float bin_scale = 0.0f;
+        int   bin_min   = 0;
+        auto  bin_of    = [&](float v) { return min(kHistBins - 1, max(0, __float2int_rz((v - tau_row) * bin_scale))); };
+        int   round     = 0;
         /* A group is four consecutive values, the id of the first and, in the id's top four bits, which of them
          * passed. The whole warp calls: the entries that stay are counted over the warp and get their places
          * with one atomic per warp. */
         auto place_group = [&](bool valid, const float4 &v, int raw) {
             const int      b  = raw & 0x0fffffff;
             const unsigned cm = valid ? (unsigned) raw >> 28 : 0u;
-            const bool     k0 = (cm & 1u) && b < p.V && (keep_all || v.x >= tau_row);
-            const bool     k1 = (cm & 2u) && b + 1 < p.V && (keep_all || v.y >= tau_row);
-            const bool     k2 = (cm & 4u) && b + 2 < p.V && (keep_all || v.z >= tau_row);
-            const bool     k3 = (cm & 8u) && b + 3 < p.V && (keep_all || v.w >= tau_row);
+            bool           k0 = (cm & 1u) && b < p.V && (keep_all || v.x >= tau_row);
+            bool           k1 = (cm & 2u) && b + 1 < p.V && (keep_all || v.y >= tau_row);
+            bool           k2 = (cm & 4u) && b + 2 < p.V && (keep_all || v.z >= tau_row);
+            bool           k3 = (cm & 8u) && b + 3 < p.V && (keep_all || v.w >= tau_row);
+            if (round == 1) {
+                if (k0) atomicAdd(&sh->bhist[bin_of(v.x)], 1);
+                if (k1) atomicAdd(&sh->bhist[bin_of(v.y)], 1);
+                if (k2) atomicAdd(&sh->bhist[bin_of(v.z)], 1);
+                if (k3) atomicAdd(&sh->bhist[bin_of(v.w)], 1);
+                return;
+            }
+            if (round == 2) {
+                k0 = k0 && bin_of(v.x) >= bin_min;
+                k1 = k1 && bin_of(v.y) >= bin_min;
+                k2 = k2 && bin_of(v.z) >= bin_min;
+                k3 = k3 && bin_of(v.w) >= bin_min;
+            }
             const int      cnt = (int) k0 + (int) k1 + (int) k2 + (int) k3;
             if (__ballot_sync(0xffffffffu, cnt > 0) == 0u) {
                 return;
@@ -1751,35 +1769,65 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
             if (k2) { if (pos < kFinCap) { cbuf[pos].v = v.z; cbuf[pos].idx = b + 2; } pos++; }
             if (k3) { if (pos < kFinCap) { cbuf[pos].v = v.w; cbuf[pos].idx = b + 3; } pos++; }
         };
-        /* one loop over the groups of all parts (rolled: code that runs once per row costs what it weighs) */
+        int total = 0;
 #pragma unroll 1
-        for (int f0 = 0; f0 < others; f0 += g.n) {
-            const int  f  = f0 + g.tid;
-            const bool ok = f < others;
-            int        pi = 0;
-            for (int q = 1; q < n_parts; q++) {
-                if (f >= sh->poff[q]) {
-                    pi = q; /* offsets ascend */
-                }
+        for (round = 0; round < 3; round++) {
+            if (g.tid == 0) {
+                sh->n_ent = 0;
             }
-            const int slot = f - sh->poff[pi] + 2; /* behind the part's record */
-            float4    v    = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            int       b    = 0;
-            if (ok) {
-                if (pi < kStagedParts && slot < kThreads) {
-                    v = sh->st_v[pi][slot];
-                    b = sh->st_b[pi][slot];
-                } else {
-                    const size_t at = ((size_t) row * (size_t) p.parts_max + (size_t) pi) * (size_t) kPartSlots + (size_t) slot;
-                    v               = __ldcg(p.grp_v + at);
-                    b               = __ldcg(p.grp_b + at);
-                }
+            if (round == 1 && g.tid < kHistBins) {
+                sh->bhist[g.tid] = 0;
             }
-            place_group(ok, v, b);
+            g.sync();
+            /* one loop over the groups of all parts (rolled: code that runs once per row costs what it weighs) */
+#pragma unroll 1
+            for (int f0 = 0; f0 < others; f0 += g.n) {
+                const int  f  = f0 + g.tid;
+                const bool ok = f < others;
+                int        pi = 0;
+                for (int q = 1; q < n_parts; q++) {
+                    if (f >= sh->poff[q]) {
+                        pi = q; /* offsets ascend */
+                    }
+                }
+                const int slot = f - sh->poff[pi] + 2; /* behind the part's record */
+                float4    v    = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                int       b    = 0;
+                if (ok) {
+                    if (pi < kStagedParts && slot < kThreads) {
+                        v = sh->st_v[pi][slot];
+                        b = sh->st_b[pi][slot];
+                    } else {
+                        const size_t at = ((size_t) row * (size_t) p.parts_max + (size_t) pi) * (size_t) kPartSlots + (size_t) slot;
+                        v               = __ldcg(p.grp_v + at);
+                        b               = __ldcg(p.grp_b + at);
+                    }
+                }
+                place_group(ok, v, b);
+            }
+            g.sync();
+            if (round == 1) { /* the bin in which the kq-th candidate from the top falls */
+                if (g.warp == 0) {
+                    const int bb = top_bin(sh->bhist, g.lane, r.kq);
+                    if (g.lane == 0) {
+                        gs->b_star = bb;
+                    }
+                }
+                g.sync();
+                bin_min = gs->b_star;
+                g.sync();
+                if (bin_min <= 0) {
+                    break; /* nothing to gain: the candidates sit in the lowest bin (many equal values) */
+                }
+                continue;
+            }
+            total = sh->n_ent;
+            if (round == 2 || total <= kFinCap || keep_all || !(row_max > tau_row) || !(row_max - tau_row < CUDART_INF_F)) {
+                break;
+            }
+            bin_scale = (float) kHistBins / (row_max - tau_row);
         }
-        g.sync();
         PROF(10);
-        const int total = sh->n_ent;
         if (total > kFinCap || total < r.kq) {
             need_multipass = true;
         }
@@ -2690,8 +2738,10 @@ __global__ void __launch_bounds__(kThreads, 2) finish_rows_kernel(const __grid_c
         PROF(13);
         if (st & ST_DEFERRED) {
             if constexpr (kFast) {
-                /* the caller said that no such row would come: this kernel does not carry the code for it */
-                st = (st & ~ST_DEFERRED) | ST_INTERNAL;
+                /* This kernel does not carry the code for the row. A top-k row whose candidates did not fit (many
+                 * equal values at the top) is the caller's to launch again without the hint; any other kind of
+                 * row the caller said would not come. */
+                st = (st & ~ST_DEFERRED) | (r.mode == M_TOPK ? ST_RETRY : ST_INTERNAL);
                 if (g.tid == 0) {
                     p.tokens[row] = -1;
                 }

@@ -119,6 +119,7 @@ void              geist_b200_ctx_destroy(struct geist_b200_ctx *ctx);
 #define GEIST_B200_ROW_HIST_OVERFLOW (1 << 2) /* result invalid */
 #define GEIST_B200_ROW_KEPT_PARTIAL  (1 << 3) /* kept_idx / kept_val not filled, kept_n is */
 #define GEIST_B200_ROW_INTERNAL      (1 << 4) /* result invalid */
+#define GEIST_B200_ROW_RETRY         (1 << 5) /* finish_hint GREEDY_TOPK / GREEDY only: not sampled (token -1), see there */
 
 /*
  * One launch over n_seq * rows_per_seq logits rows. All pointers are DEVICE
@@ -195,7 +196,10 @@ struct geist_b200_batch {
  * 7 - 8 us less per launch). A caller that knows its sessions' sampler settings says which:
  *   AUTO         the general kernel; any mix of rows.
  *   GREEDY_TOPK  the small kernel. A row that is neither greedy nor top-k <= 256 is not sampled: its
- *                row_status carries GEIST_B200_ROW_INTERNAL and its token is -1.
+ *                row_status carries GEIST_B200_ROW_INTERNAL and its token is -1. A top-k row whose candidates
+ *                do not fit the small kernel's lists (thousands of equal values at the top of the row) is not
+ *                sampled either and says GEIST_B200_ROW_RETRY: launch its sequence again without the hint,
+ *                from the same rng_in (geist_b200_batcher_* do that themselves).
  *   GENERAL      the general kernel, as AUTO; tells the launch that its rows are temperature / top-p rows,
  *                for which another way of dealing the rows out to the thread blocks is faster.
  *   GREEDY       every row is greedy (T <= 0). Where the launch deals whole rows to its thread blocks (batches

@@ -243,3 +243,31 @@ def test_run_maps_over_row_counts(ctx, V):
                 bad = np.nonzero(g["tokens"] != o["tokens"][:n])[0]
                 assert bad.size == 0, (mode, n, hint, bad[:5])
                 assert np.array_equal(g["rng_state"], o["rng_state"][:n]), (mode, n, hint)
+
+
+def test_small_finisher_hands_back_rows_whose_candidates_overflow(ctx):
+    """GREEDY_TOPK promises greedy / top-k rows, not easy ones. A top-k row with thousands of equal values at the
+    top (more candidates than the small kernel's lists hold) comes back unsampled with ROW_RETRY; launched again
+    without the hint it is sampled. The batcher does that second launch itself."""
+    from helpers import u64_to_dev
+    rows, V = 6, 128256
+    x = normal_logits(rows, V, 2.5, 4242)
+    x[0, 1000:9000] = 30.0          # 8000 ties at the top: the k kept are the lowest ids among them
+    x[1, :] = 1.0                   # a flat row
+    x[2, ::3] = x[2].max() + 1.0    # every third entry tied
+    st = independent_states(oracle.port, 4242, rows)
+    for K in (40, 200):
+        o = oracle.port.sample_batch(x, 0.9, K, 1.0, st)
+        dT, dK, dP = to_dev(np.full(rows, 0.9, np.float32)), to_dev(np.full(rows, K, np.int32)), to_dev(np.ones(rows, np.float32))
+        out = ctx.sample_batch(to_dev(x), dT, dK, dP, u64_to_dev(st), finish_hint=api.FINISH_GREEDY_TOPK)
+        status, tok = out["status"].cpu().numpy(), out["tokens"].cpu().numpy()
+        assert (status[:3] & api.ROW_RETRY).all() and (tok[:3] == -1).all()
+        assert (status[3:] & (api.ROW_RETRY | api.ROW_INVALID) == 0).all() and np.array_equal(tok[3:], o["tokens"][3:])
+        check_tokens(run_gpu(ctx, x, 0.9, K, 1.0, st), o)  # the same rows without the hint
+    bt = api.Batcher(ctx, V, 8)
+    sess = [bt.open(temperature=0.9, top_k=40, top_p=1.0, seed=4242 + i) for i in range(rows)]  # all top-k: the batcher gives the hint
+    got = bt.step(sess, to_dev(x))
+    assert np.array_equal(got, oracle.port.sample_batch(x, 0.9, 40, 1.0, st)["tokens"])
+    for i, s_ in enumerate(sess):
+        assert bt.get_rng(s_) == oracle.port.rng_advance(int(st[i]), 1)
+    bt.close()
