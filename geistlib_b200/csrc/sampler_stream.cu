@@ -1211,6 +1211,7 @@ struct __align__(16) StreamShared {
     int                bhist[kHistBins];           /* first slice: group maxima binned by key */
     int                thist[kHistBins];           /* candidates binned by value between threshold and maximum */
     int                rl_id[kRowIds], rl_cnt[kRowIds]; /* the row's distinct history ids and their counts */
+    float              wsq[kWarps];     /* top-k: the threshold at which each warp last cleared its candidate list of what had fallen below */
     unsigned long long cur_rng;         /* the generator word the part's sequence came with, its sequence, and whether the row is the sequence's last */
     int                cur_seq, cur_last;
     float              cap;             /* the part's soft cap and mask row (0 / null: none) */
@@ -1239,6 +1240,7 @@ struct __align__(16) FinishShared {
 };
 
 constexpr int kGroupBytes = kPartGroups * 20; /* float4 + first id per group */
+constexpr int kSqueezeAt  = 64;               /* a warp holding more candidate groups than this looks whether the threshold has left some behind */
 constexpr int kListSmem   = 1024;             /* prepared id-list entries of a part that are kept in shared memory */
 constexpr int kFinCap     = 2048;             /* candidates the finisher can order per row (8 per thread) */
 constexpr int kFinPer     = kFinCap / kThreads;
@@ -2238,6 +2240,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             sh->thist[tid] = 0;
             sh->bhist[tid] = 0;
         }
+        if (tid < kWarps) {
+            sh->wsq[tid] = -CUDART_INF_F;
+        }
         if (pen_on && !long_ids) {
             /* the row's distinct ids with their counts: an open-addressing table in the groups' memory (free
              * between two parts), one id per thread; the thread whose id opened a slot speaks for that id */
@@ -2600,6 +2605,41 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                         __threadfence_block();
                         sh->tau_lock = 0;
                     }
+                }
+            }
+            if (mode == M_TOPK && wcnt > kSqueezeAt && wcnt <= kGroupCapWarp) {
+                /* The threshold has gone up since most of the warp's groups were taken: those whose maximum has
+                 * fallen below it cannot hold one of the row's kq largest any more and leave the list (top-k rows
+                 * only: a top-p row's candidates were left out of its sums and must all arrive). Without this a
+                 * wide k fills a warp's list before the row is through. */
+                const unsigned pk    = *reinterpret_cast<volatile unsigned *>(&sh->tau_key);
+                const float    tau_c = pk == 0u ? tau_reg : fmaxf(tau_reg, key_to_float(pk));
+                if (tau_c > sh->wsq[warp]) {
+                    int kept = 0;
+                    for (int base = 0; base < wcnt; base += 32) {
+                        const int j    = base + lane;
+                        float4    v    = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        int       bb   = 0;
+                        bool      keep = false;
+                        if (j < wcnt) {
+                            v    = seg_v[j];
+                            bb   = seg_b[j];
+                            keep = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)) >= tau_c;
+                        }
+                        const unsigned m = __ballot_sync(0xffffffffu, keep); /* every lane has read its entry before any is overwritten */
+                        if (keep) {
+                            const int pos = kept + __popc(m & lt);
+                            seg_v[pos]    = v;
+                            seg_b[pos]    = bb;
+                        }
+                        kept += __popc(m);
+                        __syncwarp();
+                    }
+                    wcnt = kept;
+                    if (lane == 0) {
+                        sh->wsq[warp] = tau_c;
+                    }
+                    __syncwarp();
                 }
             }
             CYC(2);
