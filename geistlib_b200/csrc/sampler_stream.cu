@@ -1716,15 +1716,15 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
     bool      need_multipass = !(r.kq > 0 && r.kq <= kFastKMax) || overflow || n_groups > 8 * kFinCap; /* what counts is how many stay above the row's threshold: checked below */
     if (!need_multipass) {
         const bool keep_all = r.mode == M_TOPP; /* every marked entry was left out of the bulk sums */
-        /* The candidates of all parts are merged in up to three rounds of one rolled loop. Round 0 keeps what
+        /* The candidates of all parts are merged in up to three passes of one rolled loop. The first keeps what
          * passes the row's threshold (the largest of the parts' thresholds). A row cut into many parts can have far
-         * more of those than k (every part kept at least k of its own): if they do not fit, round 1 bins them by
-         * value between the threshold and the row's maximum, and round 2 keeps the bins from the top down to the
+         * more of those than k (every part kept at least k of its own): if they do not fit, a second pass bins them
+         * by value between the threshold and the row's maximum, and a third keeps the bins from the top down to the
          * one in which the kq-th falls. */
         float bin_scale = 0.0f;
         int   bin_min   = 0;
         auto  bin_of    = [&](float v) { return min(kHistBins - 1, max(0, __float2int_rz((v - tau_row) * bin_scale))); };
-        int   round     = 0;
+        int   pass      = 0; /* 0 keep by threshold, 1 bin, 2 keep by bin */
         /* A group is four consecutive values, the id of the first and, in the id's top four bits, which of them
          * passed. The whole warp calls: the entries that stay are counted over the warp and get their places
          * with one atomic per warp. */
@@ -1735,14 +1735,14 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
             bool           k1 = (cm & 2u) && b + 1 < p.V && (keep_all || v.y >= tau_row);
             bool           k2 = (cm & 4u) && b + 2 < p.V && (keep_all || v.z >= tau_row);
             bool           k3 = (cm & 8u) && b + 3 < p.V && (keep_all || v.w >= tau_row);
-            if (round == 1) {
+            if (pass == 1) {
                 if (k0) atomicAdd(&sh->bhist[bin_of(v.x)], 1);
                 if (k1) atomicAdd(&sh->bhist[bin_of(v.y)], 1);
                 if (k2) atomicAdd(&sh->bhist[bin_of(v.z)], 1);
                 if (k3) atomicAdd(&sh->bhist[bin_of(v.w)], 1);
                 return;
             }
-            if (round == 2) {
+            if (pass == 2) {
                 k0 = k0 && bin_of(v.x) >= bin_min;
                 k1 = k1 && bin_of(v.y) >= bin_min;
                 k2 = k2 && bin_of(v.z) >= bin_min;
@@ -1773,11 +1773,11 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
         };
         int total = 0;
 #pragma unroll 1
-        for (round = 0; round < 3; round++) {
+        for (pass = 0; pass < 3; pass++) {
             if (g.tid == 0) {
                 sh->n_ent = 0;
             }
-            if (round == 1 && g.tid < kHistBins) {
+            if (pass == 1 && g.tid < kHistBins) {
                 sh->bhist[g.tid] = 0;
             }
             g.sync();
@@ -1808,7 +1808,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
                 place_group(ok, v, b);
             }
             g.sync();
-            if (round == 1) { /* the bin in which the kq-th candidate from the top falls */
+            if (pass == 1) { /* the bin in which the kq-th candidate from the top falls */
                 if (g.warp == 0) {
                     const int bb = top_bin(sh->bhist, g.lane, r.kq);
                     if (g.lane == 0) {
@@ -1824,7 +1824,7 @@ __device__ __forceinline__ int finish_row(const Grp &g, const SampleParams &p, F
                 continue;
             }
             total = sh->n_ent;
-            if (round == 2 || total <= kFinCap || keep_all || !(row_max > tau_row) || !(row_max - tau_row < CUDART_INF_F)) {
+            if (pass == 2 || total <= kFinCap || keep_all || !(row_max > tau_row) || !(row_max - tau_row < CUDART_INF_F)) {
                 break;
             }
             bin_scale = (float) kHistBins / (row_max - tau_row);
