@@ -20,24 +20,128 @@ __global__ void __launch_bounds__(256) merge_sample_kernel(const __grid_constant
     float    *q     = reinterpret_cast<float *>(srt + cap);
     __shared__ int    n_total;
     __shared__ double S_sh;
-    if (threadIdx.x == 0) {
-        n_total = 0;
-    }
-    __syncthreads();
-    for (int s = 0; s < p.n_shards; s++) {
-        const int    nc  = min(p.cand_n[(size_t) s * p.n_rows + row], p.k_stride);
-        const size_t off = ((size_t) s * p.n_rows + row) * (size_t) p.k_stride;
-        __shared__ int base;
+    constexpr int kFlatShards = 64;
+    __shared__ int s_off[kFlatShards + 1]; /* where each shard's list starts in ml (up to kFlatShards shards) */
+    if (p.n_shards <= kFlatShards) {
+        /* counts first, all at once; then every entry of every list in one flat loop: two round trips to memory
+         * for the whole row instead of two per shard */
+        if (threadIdx.x < p.n_shards) {
+            s_off[threadIdx.x + 1] = min(p.cand_n[(size_t) threadIdx.x * p.n_rows + row], p.k_stride);
+        }
+        __syncthreads();
         if (threadIdx.x == 0) {
-            base = n_total;
-            n_total += nc;
+            s_off[0] = 0;
+            for (int s = 0; s < p.n_shards; s++) {
+                s_off[s + 1] += s_off[s];
+            }
+            n_total = s_off[p.n_shards];
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < nc; i += blockDim.x) {
-            ml[base + i].v   = p.cand_val[off + i];
-            ml[base + i].idx = p.cand_gid[off + i];
+        const int all = n_total;
+        for (int j = threadIdx.x; j < all; j += blockDim.x) {
+            int sh = 0;
+            while (j >= s_off[sh + 1]) {
+                sh++;
+            }
+            const size_t at = ((size_t) sh * p.n_rows + row) * (size_t) p.k_stride + (size_t) (j - s_off[sh]);
+            ml[j].v         = p.cand_val[at];
+            ml[j].idx       = p.cand_gid[at];
         }
         __syncthreads();
+    } else {
+        /* every thread walks the shards' counts itself: no meeting per shard */
+        int lo = 0;
+        for (int s = 0; s < p.n_shards; s++) {
+            const int    nc  = min(p.cand_n[(size_t) s * p.n_rows + row], p.k_stride);
+            const size_t off = ((size_t) s * p.n_rows + row) * (size_t) p.k_stride;
+            for (int i = threadIdx.x; i < nc; i += blockDim.x) {
+                ml[lo + i].v   = p.cand_val[off + i];
+                ml[lo + i].idx = p.cand_gid[off + i];
+            }
+            lo += nc;
+        }
+        if (threadIdx.x == 0) {
+            n_total = lo;
+        }
+        __syncthreads();
+    }
+    /* The key of the row's k-th largest candidate, by a radix select over the merged list (one byte of the ordered
+     * key per step, counts in shared memory); what lies below it is dropped before the ordering, which ranks every
+     * entry against all others (with eight shards of fifty: 400 x 400 comparisons against about 50 x 50). */
+    {
+        const int kk = min(min(max(p.top_k[row], 1), kTopKClamp), n_total);
+        __shared__ int      hist[256];
+        __shared__ unsigned pre_key;
+        __shared__ int      need_sh, n_keep;
+        if (threadIdx.x == 0) {
+            pre_key = 0u;
+            need_sh = kk;
+            n_keep  = 0;
+        }
+        const int all = n_total;
+        for (int level = 3; level >= 0 && all > kk; level--) {
+            const int shift = 8 * level;
+            hist[threadIdx.x & 255] = 0; /* blockDim.x == 256 */
+            __syncthreads();
+            const unsigned pre = pre_key;
+            for (int t = threadIdx.x; t < all; t += blockDim.x) {
+                const unsigned key = order_key(ml[t].v + 0.0f);
+                if (level == 3 || (key >> (shift + 8)) == (pre >> (shift + 8))) {
+                    atomicAdd(&hist[(key >> shift) & 255u], 1);
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x < 32) { /* lane l owns the byte values 255 - 8 l down to 248 - 8 l: from the top */
+                const int lane = threadIdx.x, need = need_sh;
+                int       c8[8], mine = 0;
+#pragma unroll
+                for (int q8 = 0; q8 < 8; q8++) {
+                    c8[q8] = hist[255 - (8 * lane + q8)];
+                    mine += c8[q8];
+                }
+                int incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) {
+                        incl += up;
+                    }
+                }
+                const unsigned ball = __ballot_sync(0xffffffffu, incl >= need);
+                if (ball != 0u && lane == __ffs(ball) - 1) {
+                    int run = incl - mine;
+                    for (int q8 = 0; q8 < 8; q8++) {
+                        if (run + c8[q8] >= need) {
+                            pre_key = pre | ((unsigned) (255 - (8 * lane + q8)) << shift);
+                            need_sh = need - run;
+                            break;
+                        }
+                        run += c8[q8];
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        if (all > kk) {
+            const unsigned tk = pre_key;
+            for (int t0 = 0; t0 < all; t0 += blockDim.x) { /* compact into srt, then back */
+                const int  t    = t0 + threadIdx.x;
+                const bool keep = t < all && order_key(ml[t].v + 0.0f) >= tk;
+                if (keep) {
+                    srt[atomicAdd(&n_keep, 1)] = ml[t];
+                }
+            }
+            __syncthreads();
+            const int nk = n_keep;
+            for (int t = threadIdx.x; t < nk; t += blockDim.x) {
+                ml[t] = srt[t];
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                n_total = nk;
+            }
+            __syncthreads();
+        }
     }
     const int total = n_total;
     for (int t = threadIdx.x; t < total; t += blockDim.x) {
@@ -72,18 +176,45 @@ __global__ void __launch_bounds__(256) merge_sample_kernel(const __grid_constant
     }
     __syncthreads();
     if (threadIdx.x == 0) {
+        /* sampler.c:90-102: the sum and the walk in the reference's order, eight weights per step so that their
+         * loads overlap */
         double S = 0.0;
-        for (int i = 0; i < k; i++) {
-            S += (double) q[i];
+        for (int i0 = 0; i0 < k; i0 += 8) {
+            float w8[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                w8[j] = i0 + j < k ? q[i0 + j] : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                S += (double) w8[j];
+            }
         }
         unsigned long long rng  = p.rng_in[row];
         const double       u    = (double) unit_from(xorshift_next(rng)) * S;
         double             a    = 0.0;
         int                pick = k - 1;
-        for (int i = 0; i < k; i++) {
-            a += (double) q[i];
-            if (u < a) {
-                pick = i;
+        for (int i0 = 0; i0 < k; i0 += 8) {
+            float w8[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                w8[j] = i0 + j < k ? q[i0 + j] : 0.0f;
+            }
+            double pre[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                a += (double) w8[j];
+                pre[j] = a;
+            }
+            int first = 8;
+#pragma unroll
+            for (int j = 7; j >= 0; j--) {
+                if (u < pre[j] && i0 + j < k) {
+                    first = j;
+                }
+            }
+            if (first < 8) {
+                pick = i0 + first;
                 break;
             }
         }
