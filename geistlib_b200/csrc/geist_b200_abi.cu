@@ -232,6 +232,8 @@ struct geist_b200_ctx {
         unsigned char *buf         = nullptr;
         size_t         bytes       = 0;
         int           *counters    = nullptr; /* one flag per row copy of the multi-pass path */
+        int           *arrive      = nullptr; /* one counter per row: parts that have published (greedy launches); zero between launches */
+        size_t         arrive_cap  = 0;
         size_t         counter_cap = 0;
     } lane[kLanes];
     unsigned   next_lane = 0;
@@ -285,6 +287,7 @@ extern "C" void geist_b200_ctx_destroy(struct geist_b200_ctx *c) {
     for (auto &ln : c->lane) {
         cudaFree(ln.buf);
         cudaFree(ln.counters);
+        cudaFree(ln.arrive);
     }
     cudaFree(c->d_row);
     cudaFree(c->d_small);
@@ -434,8 +437,19 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
             CUDA_TRY(cudaMemsetAsync(ln->counters, 0, cap * sizeof(int), st));
             ln->counter_cap = cap;
         }
+        if ((p.flags & gb::F_GREEDY_ONLY) != 0u && ln->arrive_cap < n_rows) {
+            cudaFree(ln->arrive);
+            ln->arrive     = nullptr;
+            ln->arrive_cap = 0;
+            const size_t cap = round_up(n_rows, 1024);
+            /* zeroed on the launch's own stream; whoever completes a row puts its counter back */
+            CUDA_TRY(cudaMalloc((void **) &ln->arrive, cap * sizeof(int)));
+            CUDA_TRY(cudaMemsetAsync(ln->arrive, 0, cap * sizeof(int), st));
+            ln->arrive_cap = cap;
+        }
     }
     p.pool             = ln->counters;
+    p.arrive           = ln->arrive;
     p.pool_slots       = (int) slots;
     p.grp_v            = reinterpret_cast<float4 *>(ln->buf + off_gv);
     p.grp_b            = reinterpret_cast<int *>(ln->buf + off_gb);

@@ -44,7 +44,7 @@ enum : int {
 enum : unsigned {
     F_SELECT_ONLY = 1u << 0, /* vocabulary shard: emit the row's best k (value, global id), no draw */
     F_FAST_ONLY   = 1u << 1, /* the caller vouches that every row is greedy or top-k <= kFastKMax: the small finishing kernel runs instead of the general one */
-    F_GREEDY_ONLY = 1u << 3, /* the caller vouches that every row is greedy: where a thread block streams whole rows it writes their tokens itself and no finishing kernel runs */
+    F_GREEDY_ONLY = 1u << 3, /* the caller vouches that every row is greedy: the stream kernel writes the tokens itself (the thread block that streamed the whole row, or the last of its parts to arrive) and no finishing kernel runs */
 };
 
 struct Pair {
@@ -139,6 +139,7 @@ struct SampleParams {
     unsigned flags;
 
     /* scratch in global memory (one lane of the context's scratch) */
+    int       *arrive;      /* [n_rows] greedy launches: how many parts of the row have published their record; zero between launches */
     int       *pool;        /* [pool_slots] 1: the row copy of this number is taken; zero between launches */
     int        pool_slots;
     float4    *grp_v;       /* [n_rows, parts_max, kPartSlots] per part: its PartRec (two slots), then its candidate groups: four consecutive values ... */

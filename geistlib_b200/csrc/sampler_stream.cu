@@ -2697,22 +2697,46 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             int4 *rec = reinterpret_cast<int4 *>(p.grp_v + ((size_t) row * (size_t) p.parts_max + (size_t) part_idx) * (size_t) kPartSlots);
             rec[0]    = h; /* the part's record takes the first two slots of its group list */
             rec[1]    = h2;
-            if ((p.flags & F_GREEDY_ONLY) != 0u && p.map.mode == RUN_ROWS) {
-                /* the whole row went through this thread block and the caller said it is greedy: the token is
-                 * known here and no finishing kernel follows. A row that is not greedy after all is reported. */
-                int stq = h.w;
-                if (mode == M_ARGMAX) {
-                    p.tokens[row] = h.y + p.vocab_offset;
-                } else {
-                    p.tokens[row] = -1;
-                    stq |= ST_INTERNAL;
+            if ((p.flags & F_GREEDY_ONLY) != 0u) {
+                /* The caller said that every row is greedy: no finishing kernel follows. A row that went through
+                 * this thread block as a whole is known here. A row cut into parts is finished by whichever of its
+                 * parts arrives last: every part publishes its record, then counts itself in; the one that finds
+                 * all the others counted reads their records and puts the counter back to zero for the next launch.
+                 * Nobody waits for anybody. A row that is not greedy after all is reported. */
+                int  best_arg = h.y, stq = h.w;
+                bool mine     = n_parts == 1;
+                if (!mine) {
+                    __threadfence();
+                    if (atomicAdd(&p.arrive[row], 1) == n_parts - 1) {
+                        __threadfence();
+                        p.arrive[row] = 0;
+                        float m       = -CUDART_INF_F;
+                        best_arg      = 0x7fffffff;
+                        for (int q = 0; q < n_parts; q++) {
+                            const int4 o = __ldcg(reinterpret_cast<const int4 *>(p.grp_v + ((size_t) row * (size_t) p.parts_max + (size_t) q) * (size_t) kPartSlots));
+                            stq |= o.w;
+                            if (pair_before(__int_as_float(o.x), o.y, m, best_arg)) {
+                                m        = __int_as_float(o.x);
+                                best_arg = o.y;
+                            }
+                        }
+                        mine = true;
+                    }
                 }
-                if (p.kept_cap > 0) {
-                    p.kept_n[row] = 0;
-                }
-                p.status[row] = stq;
-                if (p.rng_out != nullptr && sh->cur_last) {
-                    p.rng_out[sh->cur_seq] = sh->cur_rng; /* greedy rows draw nothing (sampler.c:106-112) */
+                if (mine) {
+                    if (mode == M_ARGMAX) {
+                        p.tokens[row] = best_arg + p.vocab_offset;
+                    } else {
+                        p.tokens[row] = -1;
+                        stq |= ST_INTERNAL;
+                    }
+                    if (p.kept_cap > 0) {
+                        p.kept_n[row] = 0;
+                    }
+                    p.status[row] = stq;
+                    if (p.rng_out != nullptr && sh->cur_last) {
+                        p.rng_out[sh->cur_seq] = sh->cur_rng; /* greedy rows draw nothing (sampler.c:106-112) */
+                    }
                 }
             }
         }
@@ -3062,8 +3086,8 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     }
     cfg.gridDim          = dim3((unsigned) finish_grid);
     cfg.dynamicSmemBytes = finish_rows_smem();
-    if ((p.flags & F_GREEDY_ONLY) != 0u && p.map.mode == RUN_ROWS) {
-        return cudaSuccess; /* the stream kernel wrote the tokens itself */
+    if ((p.flags & F_GREEDY_ONLY) != 0u) {
+        return cudaSuccess; /* the stream kernel writes the tokens itself */
     }
     /* one finishing kernel per launch: the small one when the caller vouched for greedy / top-k rows, else the
      * general one (it finishes every kind of row; a third kernel in the chain of dependent launches cost 7 - 8 us

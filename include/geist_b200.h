@@ -202,10 +202,9 @@ struct geist_b200_batch {
  *                from the same rng_in (geist_b200_batcher_* do that themselves).
  *   GENERAL      the general kernel, as AUTO; tells the launch that its rows are temperature / top-p rows,
  *                for which another way of dealing the rows out to the thread blocks is faster.
- *   GREEDY       every row is greedy (T <= 0). Where the launch deals whole rows to its thread blocks (batches
- *                of about half the device's thread-block slots and more) the stream kernel writes the tokens
- *                itself and no finishing kernel is launched; elsewhere like GREEDY_TOPK. A row with T > 0 is
- *                not sampled: GEIST_B200_ROW_INTERNAL, token -1. */
+ *   GREEDY       every row is greedy (T <= 0): the stream kernel writes the tokens itself (the thread block that
+ *                streamed the whole row, or the last of the row's parts to publish its record) and no finishing
+ *                kernel is launched. A row with T > 0 is not sampled: GEIST_B200_ROW_INTERNAL, token -1. */
 enum {
     GEIST_B200_FINISH_AUTO        = 0,
     GEIST_B200_FINISH_GREEDY_TOPK = 1,
