@@ -399,6 +399,9 @@ static enum geist_status launch_batch(struct geist_b200_ctx *ctx, const struct g
     const size_t parts    = (size_t) deal.parts_max;
     p.parts_max           = deal.parts_max;
     p.map                 = deal.map;
+    if ((p.flags & gb::F_FAST_ONLY) != 0u && (p.flags & gb::F_GREEDY_ONLY) == 0u && deal.map.mode == gb::RUN_ROWS && b->kept_cap == 0) {
+        p.flags |= gb::F_INLINE_TOPK; /* whole rows per thread block: the stream kernel finishes them itself */
+    }
     const size_t gen_str  = round_up(b->n_vocab, 4);
     const size_t gen_bmw  = (b->n_vocab + 31) / 32;
     const size_t gen_hcap = hist_max ? std::min(hist_max, b->n_vocab) : 0;

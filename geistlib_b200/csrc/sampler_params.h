@@ -44,6 +44,7 @@ enum : int {
 enum : unsigned {
     F_SELECT_ONLY = 1u << 0, /* vocabulary shard: emit the row's best k (value, global id), no draw */
     F_FAST_ONLY   = 1u << 1, /* the caller vouches that every row is greedy or top-k <= kFastKMax: the small finishing kernel runs instead of the general one */
+    F_INLINE_TOPK = 1u << 2, /* with F_FAST_ONLY, whole rows per thread block and no kept-set output: the stream kernel finishes top-k rows itself from its own candidate lists; no finishing kernel runs; what does not fit asks for ST_RETRY */
     F_GREEDY_ONLY = 1u << 3, /* the caller vouches that every row is greedy: the stream kernel writes the tokens itself (the thread block that streamed the whole row, or the last of its parts to arrive) and no finishing kernel runs */
 };
 

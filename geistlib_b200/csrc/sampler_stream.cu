@@ -1195,6 +1195,7 @@ __device__ __forceinline__ void row_epilogue(const SampleParams &p, const RowCfg
 
 /* What the warps of one thread block share. The ring (every warp's two stages) lies in front of it in dynamic
  * shared memory, the candidate groups of the part in work behind it. */
+constexpr int kInlineCap = 1024; /* candidates of a row that the stream kernel can order by itself */
 struct __align__(16) StreamShared {
     unsigned long long full[kWarps][kStages]; /* warp w's share of item j has landed in its stage j % kStages */
     /* the part in work */
@@ -1211,6 +1212,11 @@ struct __align__(16) StreamShared {
     int                bhist[kHistBins];           /* first slice: group maxima binned by key */
     int                thist[kHistBins];           /* candidates binned by value between threshold and maximum */
     int                rl_id[kRowIds], rl_cnt[kRowIds]; /* the row's distinct history ids and their counts */
+    /* finishing inside the stream kernel (F_INLINE_TOPK): the row's candidates, its k best in order, their weights */
+    int                fin_n, cur_rr;
+    Pair               fin_c[kInlineCap];
+    Pair               fin_s[kFastKMax];
+    float              fin_q[kFastKMax];
     float              wsq[kWarps];     /* top-k: the threshold at which each warp last cleared its candidate list of what had fallen below */
     unsigned long long cur_rng;         /* the generator word the part's sequence came with, its sequence, and whether the row is the sequence's last */
     int                cur_seq, cur_last;
@@ -2039,6 +2045,123 @@ __device__ __forceinline__ int row_id_count(const SampleParams &p, int hist_len,
 }
 
 /*
+ * A top-k row that went through one thread block as a whole, finished by that thread block from its own candidate
+ * lists (all threads call): the candidates above the part's final threshold are gathered, ranked one against all,
+ * the k best get their exact weights and the draw is made as in finish_row. What does not fit here (a warp's list
+ * ran over, more than kInlineCap candidates, fewer than k) is handed back with ST_RETRY.
+ */
+__device__ __noinline__ void inline_finish_topk(const SampleParams &p, StreamShared *sh, const float4 *grp_v, const int *grp_b, int row, int held, bool complete, float tau_fin,
+                                                int k, float inv_t, int st_bits) {
+    const int tid = (int) threadIdx.x;
+    if (tid == 0) {
+        sh->fin_n = 0;
+    }
+    __syncthreads();
+    for (int f = tid; f < held; f += kThreads) {
+        const int      slot = own_slot(sh, f);
+        const float4   v    = grp_v[slot];
+        const int      raw  = grp_b[slot];
+        const int      b    = raw & 0x0fffffff;
+        const unsigned cm   = (unsigned) raw >> 28;
+        const float    c4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            if (((cm >> c) & 1u) != 0u && b + c < p.V && c4[c] >= tau_fin) {
+                const int pos = atomicAdd(&sh->fin_n, 1);
+                if (pos < kInlineCap) {
+                    sh->fin_c[pos].v   = c4[c];
+                    sh->fin_c[pos].idx = b + c;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const int  total = sh->fin_n;
+    const bool ok    = complete && total <= kInlineCap && total >= k && k <= kFastKMax;
+    if (ok) {
+#pragma unroll 1
+        for (int i = tid; i < total; i += kThreads) {
+            const Pair me   = sh->fin_c[i];
+            int        rank = 0;
+#pragma unroll 4
+            for (int j = 0; j < total; j++) {
+                rank += pair_before(sh->fin_c[j].v, sh->fin_c[j].idx, me.v, me.idx) ? 1 : 0;
+            }
+            if (rank < k) {
+                sh->fin_s[rank] = me;
+            }
+        }
+        __syncthreads();
+        const float m = sh->fin_s[0].v;
+        for (int i = tid; i < k; i += kThreads) {
+            sh->fin_q[i] = exp_exact(scaled_arg(sh->fin_s[i].v, m, inv_t));
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        unsigned long long rng = sh->cur_rng; /* the sequence's word; this row starts cur_rr draws behind it */
+        for (int i = 0; i < sh->cur_rr; i++) {
+            (void) xorshift_next(rng);
+        }
+        int tok = -1;
+        if (ok) {
+            /* sampler.c:90-102: the sum and the walk in the reference's order, eight weights per step (their loads overlap) */
+            double S = 0.0;
+#pragma unroll 1
+            for (int i0 = 0; i0 < k; i0 += 8) {
+                float w8[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    w8[q] = i0 + q < k ? sh->fin_q[i0 + q] : 0.0f;
+                }
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    S += (double) w8[q];
+                }
+            }
+            const double u    = (double) unit_from(xorshift_next(rng)) * S;
+            double       a    = 0.0;
+            int          pick = k - 1;
+#pragma unroll 1
+            for (int i0 = 0; i0 < k; i0 += 8) {
+                float w8[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    w8[q] = i0 + q < k ? sh->fin_q[i0 + q] : 0.0f;
+                }
+                double pre[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    a += (double) w8[q];
+                    pre[q] = a;
+                }
+                int first = 8;
+#pragma unroll
+                for (int q = 7; q >= 0; q--) {
+                    if (u < pre[q] && i0 + q < k) {
+                        first = q;
+                    }
+                }
+                if (first < 8) {
+                    pick = i0 + first;
+                    break;
+                }
+            }
+            tok = sh->fin_s[pick].idx + p.vocab_offset;
+        } else {
+            (void) xorshift_next(rng);
+            st_bits |= ST_RETRY;
+        }
+        p.tokens[row] = tok;
+        p.status[row] = st_bits;
+        if (p.rng_out != nullptr && sh->cur_last) {
+            p.rng_out[sh->cur_seq] = rng; /* the word after the sequence's last row */
+        }
+    }
+    __syncthreads();
+}
+
+/*
  * A row's parameters cost up to two dependent memory round trips (slot -> parameters and history ids). Warp 0
  * fetches them for the NEXT row of the run with 4-byte asynchronous copies into shared memory, one step per
  * slice of the part in work, so that nothing waits for them when that row begins. The history ids are asked for
@@ -2217,6 +2340,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                 sh->cur_rng  = raw.rng;
                 sh->cur_seq  = r.seq;
                 sh->cur_last = r.rr == p.rows_per_seq - 1 ? 1 : 0;
+                sh->cur_rr   = r.rr;
             }
             if (tid < n_ids && n_ids <= kRowIds) {
                 my_id = tid < r.H ? sh->nxt_ids[tid] : sh->nxt_ext[tid - r.H];
@@ -2664,6 +2788,27 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
         for (int w = 0; w < kWarps; w++) {
             held += sh->wn[w];
         }
+        if ((p.flags & F_INLINE_TOPK) != 0u && mode != M_ARGMAX) {
+            /* whole rows, top-k: finished here, nothing goes to global scratch (every row of such a launch is one
+             * part); a row of another kind is reported as the small finishing kernel would */
+            if (mode == M_TOPK) {
+                int n_all = 0;
+#pragma unroll
+                for (int w = 0; w < kWarps; w++) {
+                    n_all += sh->wn_all[w];
+                }
+                const unsigned pkey = sh->tau_key;
+                inline_finish_topk(p, sh, grp_v, grp_b, row, held, held == n_all, pkey == 0u ? tau_reg : fmaxf(tau_reg, key_to_float(pkey)), kq, inv_t, sh->st);
+            } else {
+                if (tid == 0) {
+                    p.tokens[row] = -1;
+                    p.status[row] = sh->st | ST_INTERNAL;
+                }
+                __syncthreads();
+            }
+            CYC(6);
+            continue;
+        }
         if (tid == 0) {
             unsigned long long bw    = 0ull;
             int                n_all = 0;
@@ -2697,7 +2842,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             int4 *rec = reinterpret_cast<int4 *>(p.grp_v + ((size_t) row * (size_t) p.parts_max + (size_t) part_idx) * (size_t) kPartSlots);
             rec[0]    = h; /* the part's record takes the first two slots of its group list */
             rec[1]    = h2;
-            if ((p.flags & F_GREEDY_ONLY) != 0u) {
+            if ((p.flags & (F_GREEDY_ONLY | F_INLINE_TOPK)) != 0u) { /* in a launch that finishes its top-k rows here, the greedy ones are finished here as well */
                 /* The caller said that every row is greedy: no finishing kernel follows. A row that went through
                  * this thread block as a whole is known here. A row cut into parts is finished by whichever of its
                  * parts arrives last: every part publishes its record, then counts itself in; the one that finds
@@ -2726,7 +2871,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                 if (mine) {
                     if (mode == M_ARGMAX) {
                         p.tokens[row] = best_arg + p.vocab_offset;
-                    } else {
+                    } else { /* only with F_GREEDY_ONLY: the other flag's rows of other kinds never come here */
                         p.tokens[row] = -1;
                         stq |= ST_INTERNAL;
                     }
@@ -3086,7 +3231,7 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     }
     cfg.gridDim          = dim3((unsigned) finish_grid);
     cfg.dynamicSmemBytes = finish_rows_smem();
-    if ((p.flags & F_GREEDY_ONLY) != 0u) {
+    if ((p.flags & (F_GREEDY_ONLY | F_INLINE_TOPK)) != 0u) {
         return cudaSuccess; /* the stream kernel writes the tokens itself */
     }
     /* one finishing kernel per launch: the small one when the caller vouched for greedy / top-k rows, else the

@@ -271,3 +271,37 @@ def test_small_finisher_hands_back_rows_whose_candidates_overflow(ctx):
     for i, s_ in enumerate(sess):
         assert bt.get_rng(s_) == oracle.port.rng_advance(int(st[i]), 1)
     bt.close()
+
+
+def test_stream_kernel_finishes_whole_rows_itself(ctx):
+    """GREEDY_TOPK on a launch that deals whole rows: no finishing kernel runs, the stream kernel's thread blocks
+    finish greedy and top-k rows from their own lists. Same tokens and generator words as without the hint; rows
+    whose candidates do not fit come back with ROW_RETRY."""
+    from helpers import u64_to_dev
+    rows, V = 200, 128256
+    x = normal_logits(rows, V, 2.5, 777)
+    x[:, :5] += 7.0
+    x[3, 2000:9000] = 40.0   # thousands of ties at the top
+    x[4, :] = 0.5            # flat
+    st = independent_states(oracle.port, 777, rows)
+    h = histories(rows, 64, V, 778)
+    T = np.where(np.arange(rows) % 5 == 0, 0.0, 0.8).astype(np.float32)
+    K = np.where(np.arange(rows) % 3 == 0, 200, 40).astype(np.int32)
+    o = oracle.port.sample_batch(x, T, K, 1.0, st, rep=1.1, hist=h)
+    assert api.grid(V, rows, 64)["thread_blocks"] == rows  # whole rows
+    dT, dK, dP = to_dev(T), to_dev(K), to_dev(np.ones(rows, np.float32))
+    out = ctx.sample_batch(to_dev(x), dT, dK, dP, u64_to_dev(st), rep=to_dev(np.full(rows, 1.1, np.float32)), history=to_dev(h),
+                           history_len=to_dev(np.full(rows, 64, np.int32)), finish_hint=api.FINISH_GREEDY_TOPK)
+    status, tok = out["status"].cpu().numpy(), out["tokens"].cpu().numpy()
+    retry = (status & api.ROW_RETRY) != 0
+    assert retry[3] and retry[4] and retry.sum() == 2 and (tok[retry] == -1).all()
+    assert (status[~retry] & api.ROW_INVALID == 0).all()
+    assert np.array_equal(tok[~retry], o["tokens"][~retry])
+    from helpers import u64_from_dev
+    assert np.array_equal(u64_from_dev(out["rng_state"]), o["rng_state"])
+    # verify rows (three per sequence) through the same path
+    S, R = 66, 3
+    xv = normal_logits(S * R, V, 2.5, 779)
+    sv = independent_states(oracle.port, 779, S)
+    g = run_gpu(ctx, xv, 0.9, 50, 1.0, sv, rows_per_seq=R, finish_hint=api.FINISH_GREEDY_TOPK)
+    check_tokens(g, oracle.port.sample_batch(xv, 0.9, 50, 1.0, sv, rows_per_seq=R))
