@@ -195,11 +195,13 @@ struct geist_b200_batch {
  * for every kind of row, or a small one for greedy rows and top-k rows with k <= 256 (a tenth of the code,
  * 7 - 8 us less per launch). A caller that knows its sessions' sampler settings says which:
  *   AUTO         the general kernel; any mix of rows.
- *   GREEDY_TOPK  the small kernel. A row that is neither greedy nor top-k <= 256 is not sampled: its
- *                row_status carries GEIST_B200_ROW_INTERNAL and its token is -1. A top-k row whose candidates
- *                do not fit the small kernel's lists (thousands of equal values at the top of the row) is not
- *                sampled either and says GEIST_B200_ROW_RETRY: launch its sequence again without the hint,
- *                from the same rng_in (geist_b200_batcher_* do that themselves).
+ *   GREEDY_TOPK  the small kernel; or none at all: where the launch deals whole rows to its thread blocks
+ *                (batches of about half the device's thread-block slots and more, no kept-set output) the
+ *                stream kernel finishes the rows itself. A row that is neither greedy nor top-k <= 256 is not
+ *                sampled: its row_status carries GEIST_B200_ROW_INTERNAL and its token is -1. A top-k row whose
+ *                candidates do not fit the lists of this path (thousands of equal values at the top of the
+ *                row) is not sampled either and says GEIST_B200_ROW_RETRY: launch its sequence again without
+ *                the hint, from the same rng_in (geist_b200_batcher_* do that themselves).
  *   GENERAL      the general kernel, as AUTO; tells the launch that its rows are temperature / top-p rows,
  *                for which another way of dealing the rows out to the thread blocks is faster.
  *   GREEDY       every row is greedy (T <= 0): the stream kernel writes the tokens itself (the thread block that
