@@ -436,7 +436,9 @@ def main():
         full = ctx.sample_batch(x5, T5, K5, P5, st5, rep=rep5, history=h5, history_len=hl5)
         Vs = V5 // world
         shard = x5[:, rank * Vs:(rank + 1) * Vs].contiguous()
-        sel_out = None
+        # the select's descriptor is filled once and launched again every iteration, like the headline's
+        sel_out = ctx.sample_batch(shard, T5, K5, P5, st5, rep=rep5, history=h5, history_len=hl5, kept_cap=k5, vocab_offset=rank * Vs,
+                                   select_only=True, launch=False)
         gv = torch.empty(world, rows5, k5, dtype=torch.float32, device=dev)
         gi = torch.empty(world, rows5, k5, dtype=torch.int32, device=dev)
         gn = torch.empty(world, rows5, dtype=torch.int32, device=dev)
@@ -447,8 +449,7 @@ def main():
         for it in range(n_it + 2):
             all_barrier()
             ev[0].record()
-            sel_out = ctx.sample_batch(shard, T5, K5, P5, st5, rep=rep5, history=h5, history_len=hl5, kept_cap=k5, vocab_offset=rank * Vs,
-                                       select_only=True, out=sel_out, sync=False)
+            ctx.relaunch(sel_out, stream)
             ev[1].record()
             dist.all_gather_into_tensor(gv, sel_out["kept_prob"])
             dist.all_gather_into_tensor(gi, sel_out["kept_idx"])

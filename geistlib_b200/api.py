@@ -245,11 +245,13 @@ class Context:
             if sync:
                 torch.cuda.synchronize(dev)
         out["_desc"] = b  # the filled struct geist_b200_batch, for callers that relaunch it themselves
+        out["_select"] = select_only
         return out
 
     def relaunch(self, out, stream: int) -> None:
         """Launch a descriptor prepared by sample_batch(..., launch=False) again (asynchronous)."""
-        _check(lib.geist_b200_sample_batch(self.handle, C.byref(out["_desc"]), c_void_p(stream)))
+        fn = lib.geist_b200_shard_select if out.get("_select") else lib.geist_b200_sample_batch
+        _check(fn(self.handle, C.byref(out["_desc"]), c_void_p(stream)))
 
     def argmax_f32(self, row) -> int:
         idx = c_int32(-1)

@@ -1202,7 +1202,6 @@ struct __align__(16) StreamShared {
     unsigned           tau_key;   /* ordered key of the raised select threshold (0: not raised yet) */
     int                tau_lock;  /* one warp at a time reads the candidate histogram */
     int                st;        /* status bits of the part */
-    int                rl_n;      /* entries of the row's id list */
     unsigned           wkey[kWarps], wlow[kWarps]; /* first slice: largest / smallest group maximum per warp */
     int                wown[kWarps];               /* ... and how many groups the warp holds */
     int                wn[kWarps], wn_all[kWarps]; /* candidate groups per warp: held / found */
@@ -1211,10 +1210,11 @@ struct __align__(16) StreamShared {
     double             wb_sum[kWarps];
     int                bhist[kHistBins];           /* first slice: group maxima binned by key */
     int                thist[kHistBins];           /* candidates binned by value between threshold and maximum */
-    int                rl_id[kRowIds], rl_cnt[kRowIds]; /* the row's distinct history ids and their counts */
+    int                rl_id[kRowIds], rl_cnt[kRowIds + 4]; /* the row's distinct history ids as (offset in the share | count << 10 | tag << 20),
+                                                             * grouped by the (slice, warp) share they fall into, and where each group's run starts */
     /* finishing inside the stream kernel (F_INLINE_TOPK): the row's candidates, its k best in order, their weights */
     int                fin_n, cur_rr;
-    Pair               fin_c[kInlineCap];
+    alignas(8) Pair    fin_c[kInlineCap]; /* also holds the draw's running sums (doubles) once the ranking is done */
     Pair               fin_s[kFastKMax];
     float              fin_q[kFastKMax];
     float              wsq[kWarps];     /* top-k: the threshold at which each warp last cleared its candidate list of what had fallen below */
@@ -2358,7 +2358,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             sh->st       = 0;
             sh->tau_key  = 0u;
             sh->tau_lock = 0;
-            sh->rl_n     = 0;
+            sh->fin_n    = 0;
         }
         if (tid < kHistBins) {
             sh->thist[tid] = 0;
@@ -2368,13 +2368,19 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             sh->wsq[tid] = -CUDART_INF_F;
         }
         if (pen_on && !long_ids) {
-            /* the row's distinct ids with their counts: an open-addressing table in the groups' memory (free
-             * between two parts), one id per thread; the thread whose id opened a slot speaks for that id */
+            /* The row's distinct ids with their counts: an open-addressing table in the groups' memory (free
+             * between two parts), one id per thread; the thread whose id opened a slot speaks for that id. The ids
+             * are then grouped by the (slice, warp) share of the part that they fall into, so that a warp looks at
+             * its own share's run alone (most shares hold none): kRowIds groups, slice c of the part and slice
+             * c + 32 share one and tell their ids apart by a tag. Entry: offset in the share | count << 10 | tag << 20. */
             int *id_key = reinterpret_cast<int *>(gmem);
             int *id_cnt = id_key + 2 * kRowIds;
             for (int i = tid; i < 2 * kRowIds; i += kThreads) {
                 id_key[i] = -1;
                 id_cnt[i] = 0;
+            }
+            for (int i = tid; i <= kRowIds; i += kThreads) {
+                sh->rl_cnt[i] = 0; /* entry g + 1: ids in group g; after the scan, entry g: ids in the groups before g */
             }
             int id = my_id;
             if (tid < n_ids) {
@@ -2385,8 +2391,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             } else {
                 id = -1;
             }
+            /* which group holds the id (-1: a slice of another part of the row), and the rest of its entry */
+            auto group_of = [&](int gid, int &rest) {
+                const int c = gid / p.slice;
+                if (c < c0 || c >= c0 + part_len) {
+                    return -1;
+                }
+                const int local = gid - c * p.slice;
+                const int L     = share_len(((c == p.n_slices - 1 ? n_last : n_full) + 3) >> 2); /* float4 per warp */
+                const int w     = (local >> 2) / L;
+                rest            = (local - 4 * w * L) | (((c - c0) >> 5) << 20);
+                return ((c - c0) & 31) * kWarps + w;
+            };
             __syncthreads();
-            int slot = -1;
+            int slot = -1, place = -1;
             if (id >= 0) {
                 unsigned h = ((unsigned) id * 2654435761u) >> (32 - 9);
                 for (int probe = 0; probe < 2 * kRowIds; probe++) {
@@ -2398,12 +2416,41 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                     }
                     h = (h + 1) & (2 * kRowIds - 1);
                 }
+                if (slot >= 0) {
+                    int       rest;
+                    const int grp = group_of(id, rest);
+                    if (grp >= 0) {
+                        place = atomicAdd(&sh->rl_cnt[grp + 1], 1);
+                    }
+                }
             }
             __syncthreads();
-            if (slot >= 0) {
-                const int pos   = atomicAdd(&sh->rl_n, 1);
-                sh->rl_id[pos]  = id;
-                sh->rl_cnt[pos] = id_cnt[slot];
+            if (warp == 0) { /* running sums over the kRowIds counters, eight per lane */
+                int v[8], run = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    run += sh->rl_cnt[1 + 8 * lane + i];
+                    v[i] = run;
+                }
+                int before = run;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int o = __shfl_up_sync(0xffffffffu, before, d);
+                    if (lane >= d) {
+                        before += o;
+                    }
+                }
+                before -= run;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    sh->rl_cnt[1 + 8 * lane + i] = before + v[i];
+                }
+            }
+            __syncthreads();
+            if (place >= 0) {
+                int       rest;
+                const int grp = group_of(id, rest);
+                sh->rl_id[sh->rl_cnt[grp] + place] = rest | (id_cnt[slot] << 10);
             }
         } else if (pen_on) {
             /* long histories: a kernel that ran before this one left the row's distinct ids with their counts
@@ -2487,12 +2534,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             if (pen_on) {
                 bool touched = false; /* most shares hold none of the row's ids: those need no fence before the refill */
                 if (!long_ids) {
-                    const int rn = sh->rl_n;
-                    for (int e = lane; e < rn; e += 32) {
-                        const int li = sh->rl_id[e] - s0;
-                        if (li >= 4 * w4lo && li < 4 * (w4lo + mine4) && li < n) {
-                            sl[li - 4 * w4lo] = penalise(sl[li - 4 * w4lo], sh->rl_cnt[e], rep, freq, pres);
-                            touched           = true;
+                    const int grp = (s & 31) * kWarps + warp;
+                    const int lo = sh->rl_cnt[grp], hi = sh->rl_cnt[grp + 1];
+                    for (int e = lo + lane; e < hi; e += 32) {
+                        const unsigned en = (unsigned) sh->rl_id[e];
+                        if ((int) (en >> 20) == (s >> 5)) {
+                            float *q = sl + (en & 0x3ffu);
+                            *q       = penalise(*q, (int) ((en >> 10) & 0x3ffu), rep, freq, pres);
+                            touched  = true;
                         }
                     }
                 } else {
