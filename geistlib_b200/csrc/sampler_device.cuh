@@ -110,6 +110,12 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, unsigned by
                  : "memory");
 }
 
+/* Asks for a run of global memory to be brought into L2 (nothing is read and there is no completion to wait
+ * for; address and size on the 16-byte grid). */
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, unsigned bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
     unsigned ok;
     asm volatile(

@@ -2252,6 +2252,23 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
      * been placed while that kernel's last blocks were still at work. Everything it touches in global memory
      * waits here for that kernel to be complete and visible, so the stream's order is kept; what is saved is
      * the gap between two grids. The kernel behind this one may be placed likewise. */
+    if (lane == 0 && p.aligned) {
+        /* While it waits, the thread block asks L2 for what its ring will copy first (the warp's shares of the run's
+         * first kStages items). Nothing is read: a line that the kernel before this one is still writing arrives in
+         * L2 with its stores either way. Back to back this is worth 0.5 us per launch: the last thread blocks of the
+         * grid before leave DRAM idle. */
+        const int n_full_ = min(p.slice, p.V), n_last_ = p.V - (p.n_slices - 1) * p.slice;
+        for (int jj = 0; jj < min(kStages, my_count); jj++) {
+            const int item = my_first + jj, r_ = item / p.n_slices, c_ = item - r_ * p.n_slices;
+            const int n_   = c_ == p.n_slices - 1 ? n_last_ : n_full_;
+            const int nv4_ = (n_ + 3) >> 2, L_ = share_len(nv4_);
+            const int lo_  = min(warp * L_, nv4_);
+            const int b4_  = max(0, min(min(L_, nv4_ - lo_), (n_ >> 2) - lo_));
+            if (b4_ > 0) {
+                bulk_prefetch_l2(p.logits + (size_t) r_ * (size_t) p.row_stride + (size_t) c_ * (size_t) p.slice + 4 * lo_, (unsigned) b4_ * 16u);
+            }
+        }
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
 #ifdef GB_PROFILE
@@ -2319,6 +2336,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             pf = 0;
         }
         __syncthreads();
+        PROF_ONCE(1);
         int   mode, kq, n_ids, my_id = -1;
         float inv_t, rep, freq, pres;
         bool  pen_on, pro_on;
@@ -2472,6 +2490,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
         __syncthreads();
         static_assert(2 * kRowIds == 512, "the id table's hash keeps 9 bits");
 
+        PROF_ONCE(3);
         CYC(5);
         unsigned run_key = 0u; /* this warp's maximum of the part so far (key) and its first id */
         int      run_arg = 0x7fffffff;
@@ -2678,6 +2697,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                     t_scale         = (n_own >= kq && top > tau_reg && top - tau_reg < CUDART_INF_F) ? (float) kHistBins / (top - tau_reg) : 0.0f;
                 }
                 CYC(7);
+                PROF_ONCE(7);
                 const unsigned pkey = *reinterpret_cast<volatile unsigned *>(&sh->tau_key);
                 tau                 = pkey == 0u ? tau_reg : fmaxf(tau_reg, key_to_float(pkey));
                 /* Candidates: the float4 groups whose maximum passes. Which of a thread's eight groups do is one bit
