@@ -2215,7 +2215,19 @@ __device__ __forceinline__ void prefetch_step(const SampleParams &p, StreamShare
     stage = kPrefetchDone;
 }
 
+/* Which kinds of rows an instantiation of the stream kernel carries the code for: every one carries greedy rows;
+ * K_SEL adds the candidate select of top-k rows, K_SUMS the sums of temperature and top-p rows (and top-p's select).
+ * A launch whose caller vouched for its rows' kinds (finish_hint) runs the instantiation without the rest: less
+ * code to fetch, fewer live registers in the slice loop; likewise a launch without histories runs one without the
+ * penalties' code. A row of a kind that is not carried is streamed as a
+ * greedy row and reported (ROW_INTERNAL) where the launch's rows are finished. */
+constexpr int K_SEL = 1, K_SUMS = 2, K_PEN = 4, K_PLAIN = 8; /* K_PEN: the launch brings history ids or fed tokens (penalties) */
+template <int kKinds>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(const __grid_constant__ SampleParams p) {
+    /* K_PLAIN: rows on the 16-byte grid, no soft cap, mask or logits output, no row with more ids than the thread
+     * block counts by itself: the launch's host side has checked it, the code for the rest is left out */
+    constexpr bool kPlain  = (kKinds & K_PLAIN) != 0;
+    const bool     aligned = kPlain || p.aligned != 0;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     unsigned char *ring    = smem_raw;
     StreamShared  *sh      = reinterpret_cast<StreamShared *>(smem_raw + (size_t) kWarps * kStages * kWarpStageBytes);
@@ -2252,7 +2264,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
      * been placed while that kernel's last blocks were still at work. Everything it touches in global memory
      * waits here for that kernel to be complete and visible, so the stream's order is kept; what is saved is
      * the gap between two grids. The kernel behind this one may be placed likewise. */
-    if (lane == 0 && p.aligned) {
+    if (lane == 0 && aligned) {
         /* While it waits, the thread block asks L2 for what its ring will copy first (the warp's shares of the run's
          * first kStages items). Nothing is read: a line that the kernel before this one is still writing arrives in
          * L2 with its stores either way. Back to back this is worth 0.5 us per launch: the last thread blocks of the
@@ -2313,7 +2325,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             isrc += p.row_stride - (long long) p.n_slices * p.slice; /* on to the next row */
         }
     };
-    if (lane == 0 && p.aligned) {
+    if (lane == 0 && aligned) {
         for (int jj = 0; jj < min(kStages, my_count); jj++) {
             issue_next();
         }
@@ -2347,11 +2359,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             kq     = r.kq;
             inv_t  = r.inv_t;
             n_ids  = r.H + r.E;
-            pen_on = r.pen_on && n_ids > 0;
+            pen_on = (kKinds & K_PEN) != 0 && r.pen_on && n_ids > 0;
             rep    = r.rep;
             freq   = r.freq;
             pres   = r.pres;
-            pro_on = r.cap > 0.0f || r.mrow != nullptr;
+            pro_on = !kPlain && (r.cap > 0.0f || r.mrow != nullptr);
             if (tid == 0) { /* read again by the warps only if pro_on; the barriers of the part set-up lie between */
                 sh->cap      = r.cap;
                 sh->mrow     = r.mrow;
@@ -2364,9 +2376,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                 my_id = tid < r.H ? sh->nxt_ids[tid] : sh->nxt_ext[tid - r.H];
             }
         }
-        const bool  sel     = (mode == M_TOPK || mode == M_TOPP) && kq > 0 && kq <= kFastKMax;
-        const bool  sums    = mode == M_TEMP || (mode == M_TOPP && sel);
-        const bool  long_ids = n_ids > kRowIds;
+        /* the kind the row is streamed as */
+        const int   smode   = ((kKinds & K_SUMS) == 0 && (mode == M_TEMP || mode == M_TOPP)) || ((kKinds & K_SEL) == 0 && mode == M_TOPK) ? (int) M_ARGMAX : mode;
+        const bool  sel     = (kKinds & K_SEL) != 0 && (smode == M_TOPK || ((kKinds & K_SUMS) != 0 && smode == M_TOPP)) && kq > 0 && kq <= kFastKMax;
+        const bool  sums    = (kKinds & K_SUMS) != 0 && (smode == M_TEMP || (smode == M_TOPP && sel));
+        const bool  long_ids = !kPlain && n_ids > kRowIds;
         const int   b_first = cta_of_item(p, row * p.n_slices);
         const int   part_idx = (int) blockIdx.x - b_first;
         const int   n_parts = cta_of_item(p, row * p.n_slices + p.n_slices - 1) - b_first + 1;
@@ -2512,13 +2526,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             const int      w4lo = last_c ? w4lo_l : w4lo_f, mine4 = last_c ? mine4_l : mine4_f;
             float         *sl   = reinterpret_cast<float *>(wring + (size_t) stage * kWarpStageBytes); /* local index = slice index - 4 * w4lo */
             const float   *grow = p.logits + (size_t) row * (size_t) p.row_stride + s0;
-            bool           wrote = !p.aligned; /* the warp wrote into its stage with ordinary stores */
+            bool           wrote = !aligned; /* the warp wrote into its stage with ordinary stores */
             if (warp == 0 && !final_part && pf < kPrefetchDone) {
                 prefetch_step(p, sh, row + 1, lane, pf); /* one step per slice: the step before has long arrived */
             }
             CYC(4);
             /* ---- 1. the warp's share of the slice is in its stage; the slice's tail is padded with -inf ---- */
-            if (p.aligned) {
+            if (aligned) {
                 const int full4 = last_c ? bulk4_l : bulk4_f;
                 if (ring_dead >= 0) {
                     wst |= ST_LOAD_TIMEOUT; /* every row the warp still touches is reported as not loaded */
@@ -2578,7 +2592,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                 }
                 wrote |= __any_sync(0xffffffffu, touched); /* also orders the stores before the loads below */
             }
-            if (p.out_logits != nullptr) {
+            if (!kPlain && p.out_logits != nullptr) {
                 float *orow = p.out_logits + (size_t) row * (size_t) p.V + s0;
                 for (int i = 4 * w4lo + lane; i < min(4 * (w4lo + mine4), n); i += 32) {
                     orow[i] = sl[i - 4 * w4lo];
@@ -2602,7 +2616,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             const unsigned wkey = __reduce_max_sync(0xffffffffu, own ? bkey : 0u);
             const float    wmax = wkey == 0u ? -CUDART_INF_F : key_to_float(wkey);
 
-            if (mode == M_ARGMAX) {
+            if (smode == M_ARGMAX) {
                 if (wkey > run_key) { /* rare: the warp's running maximum moves; its first id in this slice */
                     int best = 0x7fffffff;
                     if (own && bkey == wkey) {
@@ -2737,7 +2751,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             CYC(2);
             /* the stage is free again: the warp refills it itself */
             __syncwarp();
-            if (lane == 0 && p.aligned && j + kStages < my_count && ring_dead < 0) {
+            if (lane == 0 && aligned && j + kStages < my_count && ring_dead < 0) {
                 if (wrote) { /* ordinary stores of this warp come before the copy engine's */
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
@@ -2761,7 +2775,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                     sum += (double) ((e0 + e1) + (e2 + e3));
                 }
                 sum = warp_sum_d(sum);
-                if (mode == M_TEMP) {
+                if (smode == M_TEMP) {
                     if (lane == 0) {
                         SegRec sr;
                         sr.ref = wmax;
@@ -2800,7 +2814,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                     }
                 }
             }
-            if (mode == M_TOPK && wcnt > kSqueezeAt && wcnt <= kGroupCapWarp) {
+            if ((kKinds & K_SEL) != 0 && smode == M_TOPK && wcnt > kSqueezeAt && wcnt <= kGroupCapWarp) {
                 /* The threshold has gone up since most of the warp's groups were taken: those whose maximum has
                  * fallen below it cannot hold one of the row's kq largest any more and leave the list (top-k rows
                  * only: a top-p row's candidates were left out of its sums and must all arrive). Without this a
@@ -2963,7 +2977,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
         __syncthreads(); /* the lists are free for the next part */
         CYC(6);
     }
-    if (ring_dead >= 0 && p.aligned) {
+    if (ring_dead >= 0 && aligned) {
         /* copies that were asked for before the warp gave up (the item it gave up on and the one behind it) may
          * still be on their way into this thread block's shared memory: one more bounded wait for each before the
          * thread block may end */
@@ -3180,14 +3194,22 @@ static cudaError_t ensure_attributes(size_t smem_bytes) {
         return cudaErrorInvalidDevice;
     }
     if ((int) smem_bytes > configured_smem[dev]) {
-        e = cudaFuncSetAttribute(sample_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
-        if (e != cudaSuccess) {
-            return e;
-        }
         /* two thread blocks per SM need nearly all of its shared memory: ask for the largest carve-out */
-        e = cudaFuncSetAttribute(sample_stream_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int) cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) {
-            return e;
+        const void *kernels[12] = {
+                reinterpret_cast<const void *>(sample_stream_kernel<K_SEL | K_SUMS | K_PEN>), reinterpret_cast<const void *>(sample_stream_kernel<K_SEL | K_PEN>),
+                reinterpret_cast<const void *>(sample_stream_kernel<K_PEN>),                  reinterpret_cast<const void *>(sample_stream_kernel<K_SEL | K_SUMS>),
+                reinterpret_cast<const void *>(sample_stream_kernel<K_SEL>),                  reinterpret_cast<const void *>(sample_stream_kernel<0>),
+                reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN | K_SEL | K_SUMS | K_PEN>), reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN | K_SEL | K_PEN>),
+                reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN | K_PEN>),        reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN | K_SEL | K_SUMS>),
+                reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN | K_SEL>),        reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN>)};
+        for (const void *k : kernels) {
+            e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
+            if (e == cudaSuccess) {
+                e = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, (int) cudaSharedmemCarveoutMaxShared);
+            }
+            if (e != cudaSuccess) {
+                return e;
+            }
         }
         configured_smem[dev] = (int) smem_bytes;
     }
@@ -3200,7 +3222,7 @@ cudaError_t sample_stream_ctas_per_sm(size_t smem_bytes, int *out) {
     if (e != cudaSuccess) {
         return e;
     }
-    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(out, sample_stream_kernel, kThreads, smem_bytes);
+    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(out, sample_stream_kernel<K_SEL | K_SUMS | K_PEN>, kThreads, smem_bytes);
 }
 
 static cudaError_t ensure_row_ids_attributes(size_t smem_bytes) {
@@ -3294,7 +3316,33 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs                                          = attr;
     cfg.numAttrs                                       = 1;
-    e = cudaLaunchKernelEx(&cfg, sample_stream_kernel, p);
+    /* the instantiation that carries no more than the kinds of rows the caller vouched for, and the penalties' code
+     * only where the launch brings ids */
+    const bool pen   = p.hist != nullptr || p.extra != nullptr;
+    const int  kinds = (p.flags & F_SELECT_ONLY) != 0u ? (K_SEL | K_SUMS) : (p.flags & F_GREEDY_ONLY) != 0u ? 0 : (p.flags & F_FAST_ONLY) != 0u ? K_SEL : (K_SEL | K_SUMS);
+    const bool plain = p.aligned != 0 && p.softcap == nullptr && p.mask == nullptr && p.out_logits == nullptr && p.id_slots == 0;
+#define GB_STREAM_CASE(K)                                                  \
+    case (K):                                                              \
+        e = cudaLaunchKernelEx(&cfg, sample_stream_kernel<(K)>, p);        \
+        break;
+    switch (kinds | (pen ? K_PEN : 0) | (plain ? K_PLAIN : 0)) {
+        GB_STREAM_CASE(K_SEL | K_SUMS | K_PEN)
+        GB_STREAM_CASE(K_SEL | K_PEN)
+        GB_STREAM_CASE(K_PEN)
+        GB_STREAM_CASE(K_SEL | K_SUMS)
+        GB_STREAM_CASE(K_SEL)
+        GB_STREAM_CASE(0)
+        GB_STREAM_CASE(K_PLAIN | K_SEL | K_SUMS | K_PEN)
+        GB_STREAM_CASE(K_PLAIN | K_SEL | K_PEN)
+        GB_STREAM_CASE(K_PLAIN | K_PEN)
+        GB_STREAM_CASE(K_PLAIN | K_SEL | K_SUMS)
+        GB_STREAM_CASE(K_PLAIN | K_SEL)
+        GB_STREAM_CASE(K_PLAIN)
+    default:
+        e = cudaErrorInvalidValue;
+        break;
+    }
+#undef GB_STREAM_CASE
     if (e != cudaSuccess) {
         return e;
     }
