@@ -287,6 +287,17 @@ __device__ __noinline__ void prologue_share(float *sl, int lane, int mine4, int 
     __syncwarp();
 }
 
+/* The same with the division by rep done as a double product with 1 / rep (rounded to double once per part): the
+ * float nearest to x * rcp is the correctly rounded x / rep for every pair of floats (a quotient of two 24-bit
+ * numbers is at least 2^-49 of itself away from every midpoint of two floats, the product's error is below 2^-52),
+ * and the slice loop keeps clear of the division's out-of-line slow path: a call inside that loop costs every
+ * slice. */
+__device__ __forceinline__ float penalise_rcp(float x, int cnt, double rcp, float rep, float freq, float pres) {
+    x = x > 0.0f ? __double2float_rn(__dmul_rn((double) x, rcp)) : __fmul_rn(x, rep);
+    x = __fsub_rn(x, __fmul_rn((float) cnt, freq));
+    return __fsub_rn(x, pres);
+}
+
 __device__ __forceinline__ float penalise(float x, int cnt, float rep, float freq, float pres) {
     x = x > 0.0f ? __fdiv_rn(x, rep) : __fmul_rn(x, rep);
     x = __fsub_rn(x, __fmul_rn((float) cnt, freq));
@@ -2050,7 +2061,7 @@ __device__ __forceinline__ int row_id_count(const SampleParams &p, int hist_len,
  * the k best get their exact weights and the draw is made as in finish_row. What does not fit here (a warp's list
  * ran over, more than kInlineCap candidates, fewer than k) is handed back with ST_RETRY.
  */
-__device__ __noinline__ void inline_finish_topk(const SampleParams &p, StreamShared *sh, const float4 *grp_v, const int *grp_b, int row, int held, bool complete, float tau_fin,
+__device__ __forceinline__ void inline_finish_topk(const SampleParams &p, StreamShared *sh, const float4 *grp_v, const int *grp_b, int row, int held, bool complete, float tau_fin,
                                                 int k, float inv_t, int st_bits) {
     const int tid = (int) threadIdx.x;
     if (tid == 0) {
@@ -2221,11 +2232,11 @@ __device__ __forceinline__ void prefetch_step(const SampleParams &p, StreamShare
  * code to fetch, fewer live registers in the slice loop; likewise a launch without histories runs one without the
  * penalties' code. A row of a kind that is not carried is streamed as a
  * greedy row and reported (ROW_INTERNAL) where the launch's rows are finished. */
-constexpr int K_SEL = 1, K_SUMS = 2, K_PEN = 4, K_PLAIN = 8; /* K_PEN: the launch brings history ids or fed tokens (penalties) */
+constexpr int K_SEL = 1, K_SUMS = 2, K_PEN = 4, K_PLAIN = 8, K_SHORT = 16; /* K_PEN: the launch brings history ids or fed tokens (penalties) */
 template <int kKinds>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(const __grid_constant__ SampleParams p) {
-    /* K_PLAIN: rows on the 16-byte grid, no soft cap, mask or logits output, no row with more ids than the thread
-     * block counts by itself: the launch's host side has checked it, the code for the rest is left out */
+    /* K_PLAIN: rows on the 16-byte grid, no soft cap, mask or logits output; K_SHORT: no row with more ids than the
+     * thread block counts by itself. The launch's host side has checked it, the code for the rest is left out. */
     constexpr bool kPlain  = (kKinds & K_PLAIN) != 0;
     const bool     aligned = kPlain || p.aligned != 0;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -2380,7 +2391,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
         const int   smode   = ((kKinds & K_SUMS) == 0 && (mode == M_TEMP || mode == M_TOPP)) || ((kKinds & K_SEL) == 0 && mode == M_TOPK) ? (int) M_ARGMAX : mode;
         const bool  sel     = (kKinds & K_SEL) != 0 && (smode == M_TOPK || ((kKinds & K_SUMS) != 0 && smode == M_TOPP)) && kq > 0 && kq <= kFastKMax;
         const bool  sums    = (kKinds & K_SUMS) != 0 && (smode == M_TEMP || (smode == M_TOPP && sel));
-        const bool  long_ids = !kPlain && n_ids > kRowIds;
+        const bool  long_ids = (kKinds & K_SHORT) == 0 && n_ids > kRowIds;
         const int   b_first = cta_of_item(p, row * p.n_slices);
         const int   part_idx = (int) blockIdx.x - b_first;
         const int   n_parts = cta_of_item(p, row * p.n_slices + p.n_slices - 1) - b_first + 1;
@@ -2506,6 +2517,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
 
         PROF_ONCE(3);
         CYC(5);
+        const double rep_rcp = pen_on ? 1.0 / (double) rep : 1.0;
         unsigned run_key = 0u; /* this warp's maximum of the part so far (key) and its first id */
         int      run_arg = 0x7fffffff;
         float    tau_reg = -CUDART_INF_F, t_lo = 0.0f, t_scale = 0.0f;
@@ -2573,7 +2585,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                         const unsigned en = (unsigned) sh->rl_id[e];
                         if ((int) (en >> 20) == (s >> 5)) {
                             float *q = sl + (en & 0x3ffu);
-                            *q       = penalise(*q, (int) ((en >> 10) & 0x3ffu), rep, freq, pres);
+                            *q       = penalise_rcp(*q, (int) ((en >> 10) & 0x3ffu), rep_rcp, rep, freq, pres);
                             touched  = true;
                         }
                     }
@@ -2585,7 +2597,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                         const unsigned e  = in_smem ? sl_list[i - e_lo] : src[i];
                         const int      li = (int) (e & ((1u << kLiBits) - 1u));
                         if (li >= 4 * w4lo && li < 4 * (w4lo + mine4) && li < n) {
-                            sl[li - 4 * w4lo] = penalise(sl[li - 4 * w4lo], (int) (e >> kLiBits), rep, freq, pres);
+                            sl[li - 4 * w4lo] = penalise_rcp(sl[li - 4 * w4lo], (int) (e >> kLiBits), rep_rcp, rep, freq, pres);
                             touched           = true;
                         }
                     }
@@ -3195,13 +3207,15 @@ static cudaError_t ensure_attributes(size_t smem_bytes) {
     }
     if ((int) smem_bytes > configured_smem[dev]) {
         /* two thread blocks per SM need nearly all of its shared memory: ask for the largest carve-out */
-        const void *kernels[12] = {
-                reinterpret_cast<const void *>(sample_stream_kernel<K_SEL | K_SUMS | K_PEN>), reinterpret_cast<const void *>(sample_stream_kernel<K_SEL | K_PEN>),
-                reinterpret_cast<const void *>(sample_stream_kernel<K_PEN>),                  reinterpret_cast<const void *>(sample_stream_kernel<K_SEL | K_SUMS>),
-                reinterpret_cast<const void *>(sample_stream_kernel<K_SEL>),                  reinterpret_cast<const void *>(sample_stream_kernel<0>),
-                reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN | K_SEL | K_SUMS | K_PEN>), reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN | K_SEL | K_PEN>),
-                reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN | K_PEN>),        reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN | K_SEL | K_SUMS>),
-                reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN | K_SEL>),        reinterpret_cast<const void *>(sample_stream_kernel<K_PLAIN>)};
+#define GB_STREAM_ALL(X)                                                                                                                     \
+    X(K_SEL | K_SUMS | K_PEN) X(K_SEL | K_PEN) X(K_PEN) X(K_SEL | K_SUMS | K_PEN | K_SHORT) X(K_SEL | K_PEN | K_SHORT) X(K_PEN | K_SHORT)      \
+    X(K_SEL | K_SUMS | K_SHORT) X(K_SEL | K_SHORT) X(K_SHORT)                                                                                  \
+    X(K_PLAIN | K_SEL | K_SUMS | K_PEN) X(K_PLAIN | K_SEL | K_PEN) X(K_PLAIN | K_PEN)                                                         \
+    X(K_PLAIN | K_SEL | K_SUMS | K_PEN | K_SHORT) X(K_PLAIN | K_SEL | K_PEN | K_SHORT) X(K_PLAIN | K_PEN | K_SHORT)                            \
+    X(K_PLAIN | K_SEL | K_SUMS | K_SHORT) X(K_PLAIN | K_SEL | K_SHORT) X(K_PLAIN | K_SHORT)
+#define GB_STREAM_PTR(K) reinterpret_cast<const void *>(sample_stream_kernel<(K)>),
+        const void *kernels[] = {GB_STREAM_ALL(GB_STREAM_PTR)};
+#undef GB_STREAM_PTR
         for (const void *k : kernels) {
             e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
             if (e == cudaSuccess) {
@@ -3320,24 +3334,14 @@ cudaError_t launch_sample_stream(const SampleParams &p, int grid, size_t smem_by
      * only where the launch brings ids */
     const bool pen   = p.hist != nullptr || p.extra != nullptr;
     const int  kinds = (p.flags & F_SELECT_ONLY) != 0u ? (K_SEL | K_SUMS) : (p.flags & F_GREEDY_ONLY) != 0u ? 0 : (p.flags & F_FAST_ONLY) != 0u ? K_SEL : (K_SEL | K_SUMS);
-    const bool plain = p.aligned != 0 && p.softcap == nullptr && p.mask == nullptr && p.out_logits == nullptr && p.id_slots == 0;
+    const bool plain     = p.aligned != 0 && p.softcap == nullptr && p.mask == nullptr && p.out_logits == nullptr;
+    const bool short_ids = !pen || p.id_slots == 0; /* no row brings more ids than a thread block counts by itself */
 #define GB_STREAM_CASE(K)                                                  \
     case (K):                                                              \
         e = cudaLaunchKernelEx(&cfg, sample_stream_kernel<(K)>, p);        \
         break;
-    switch (kinds | (pen ? K_PEN : 0) | (plain ? K_PLAIN : 0)) {
-        GB_STREAM_CASE(K_SEL | K_SUMS | K_PEN)
-        GB_STREAM_CASE(K_SEL | K_PEN)
-        GB_STREAM_CASE(K_PEN)
-        GB_STREAM_CASE(K_SEL | K_SUMS)
-        GB_STREAM_CASE(K_SEL)
-        GB_STREAM_CASE(0)
-        GB_STREAM_CASE(K_PLAIN | K_SEL | K_SUMS | K_PEN)
-        GB_STREAM_CASE(K_PLAIN | K_SEL | K_PEN)
-        GB_STREAM_CASE(K_PLAIN | K_PEN)
-        GB_STREAM_CASE(K_PLAIN | K_SEL | K_SUMS)
-        GB_STREAM_CASE(K_PLAIN | K_SEL)
-        GB_STREAM_CASE(K_PLAIN)
+    switch (kinds | (pen ? K_PEN : 0) | (plain ? K_PLAIN : 0) | (short_ids ? K_SHORT : 0)) {
+        GB_STREAM_ALL(GB_STREAM_CASE)
     default:
         e = cudaErrorInvalidValue;
         break;
