@@ -53,7 +53,7 @@ BYTES_PER_ROW = 4 * V + 4 * H + 16 + 4
 # sample_stream_kernel alone: every session of the workload samples top-k 40, which the caller (here as in the
 # session batcher) tells the launch with finish_hint = GREEDY_TOPK; the 256 rows are dealt out as whole rows, so the
 # stream kernel's thread blocks finish them from their own candidate lists and no finishing kernel is launched.
-# Without the hint the general finishing kernel runs behind it -- the "finish_hint=AUTO" entry of `modes`
+# Without the hint the general finishing kernel runs behind it -- the "..., no hint" entries of `modes`
 KERNELS_PER_STEP = 1
 WORKLOAD = ("B=256 rows x V=128256 fp32 logits ~ N(0,2.5^2) with 8 ids/row +12; temperature 0.8, top_k 40, "
             "top_p 0.95 (top_k precedence), repetition penalty 1.1 over 64-token history, 1 draw/row, seed 1234")
@@ -346,16 +346,20 @@ def main():
             modes[name] = {"rows_per_s": world * B / sec, "us_per_launch": sec * 1e6,
                            "hbm_frac": B * (4 * V + 20 + (4 * H if pen else 0)) / sec / 1e9 / peak,
                            "rows_on_slow_path": int((st & api.ROW_SLOW_PATH).ne(0).sum().item())}
-        mode("greedy", 0.0, 0, 1.0, False)
-        mode("greedy+penalties", 0.0, 0, 1.0, True)
-        mode("top_k40", T, TOP_K, 1.0, False)
-        mode("temperature", T, 0, 1.0, False)
-        mode("top_p0.95_gaussian(wide nucleus)", T, 0, TOP_P, False)
-        # the same launches with the caller's hint on which finishing kernel they need (one launch fewer)
-        mode("headline, finish_hint=AUTO", T, TOP_K, TOP_P, True, api.FINISH_AUTO)
-        mode("greedy, finish_hint=GREEDY (one kernel)", 0.0, 0, 1.0, False, api.FINISH_GREEDY)
-        mode("greedy+penalties, finish_hint=GREEDY (one kernel)", 0.0, 0, 1.0, True, api.FINISH_GREEDY)
-        mode("temperature, finish_hint=GENERAL", T, 0, 1.0, False, api.FINISH_GENERAL)
+        # every mode as the session batcher launches it (the batcher derives the finishing hint from its sessions'
+        # sampler settings), and the same launch without a hint (what a bare sample_batch call without one gets)
+        HINTS = {api.FINISH_AUTO: "AUTO", api.FINISH_GREEDY: "GREEDY", api.FINISH_GREEDY_TOPK: "GREEDY_TOPK", api.FINISH_GENERAL: "GENERAL"}
+        for name, (t, k, p, pen, hint) in {
+                "greedy": (0.0, 0, 1.0, False, api.FINISH_GREEDY),
+                "greedy+penalties": (0.0, 0, 1.0, True, api.FINISH_GREEDY),
+                "top_k40": (T, TOP_K, 1.0, False, api.FINISH_GREEDY_TOPK),
+                "top_k40+penalties (the headline)": (T, TOP_K, TOP_P, True, api.FINISH_GREEDY_TOPK),
+                "temperature": (T, 0, 1.0, False, api.FINISH_GENERAL),
+                "top_p0.95_gaussian(wide nucleus)": (T, 0, TOP_P, False, api.FINISH_GENERAL)}.items():
+            mode(name, t, k, p, pen, hint)
+            modes[name]["finish_hint"] = HINTS[hint]
+            mode(name + ", no hint", t, k, p, pen, api.FINISH_AUTO)
+            modes[name + ", no hint"]["finish_hint"] = "AUTO"
 
     # ---- the other configurations of the reference's table (rank 0's GPU; device-resident)
     configs = {}

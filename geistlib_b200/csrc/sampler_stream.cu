@@ -1228,6 +1228,7 @@ struct __align__(16) StreamShared {
     alignas(8) Pair    fin_c[kInlineCap]; /* also holds the draw's running sums (doubles) once the ranking is done */
     Pair               fin_s[kFastKMax];
     float              fin_q[kFastKMax];
+    int                wcur[kWarps];    /* groups in each warp's list (the lanes count themselves in) */
     float              wsq[kWarps];     /* top-k: the threshold at which each warp last cleared its candidate list of what had fallen below */
     unsigned long long cur_rng;         /* the generator word the part's sequence came with, its sequence, and whether the row is the sequence's last */
     int                cur_seq, cur_last;
@@ -2408,6 +2409,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
             sh->bhist[tid] = 0;
         }
         if (tid < kWarps) {
+            sh->wcur[tid] = 0;
             sh->wsq[tid] = -CUDART_INF_F;
         }
         if (pen_on && !long_ids) {
@@ -2727,24 +2729,23 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                 const unsigned pkey = *reinterpret_cast<volatile unsigned *>(&sh->tau_key);
                 tau                 = pkey == 0u ? tau_reg : fmaxf(tau_reg, key_to_float(pkey));
                 /* Candidates: the float4 groups whose maximum passes. Which of a thread's eight groups do is one bit
-                 * each; the groups that hold any are then taken one after the other by ONE rolled loop (rarely run
-                 * code inside the hot loop is kept in one copy: it has to come from the instruction cache each
-                 * time), the values re-read from the stage, places counted from the warp's own cursor. */
+                 * each; a lane that holds any takes them one after the other in ONE rolled loop (rarely run code
+                 * inside the hot loop is kept in one copy: it has to come from the instruction cache each time), the
+                 * values re-read from the stage. */
                 unsigned mybits = 0u;
 #pragma unroll
                 for (int i = 0; i < kNV4; i++) {
                     mybits |= (gm[i] >= tau && lane + 32 * i < mine4) ? (1u << i) : 0u;
                 }
-                unsigned gany = __reduce_or_sync(0xffffffffu, mybits);
-#pragma unroll 1
-                while (gany != 0u) {
-                    const int i = __ffs(gany) - 1;
-                    gany &= gany - 1u;
-                    const bool     hit = ((mybits >> i) & 1u) != 0u;
-                    const unsigned m   = __ballot_sync(0xffffffffu, hit);
-                    if (hit) {
+                if (__any_sync(0xffffffffu, mybits != 0u)) {
+                    /* every lane that holds candidates places its groups itself, the places counted in shared memory:
+                     * one pass whatever the number of lanes and groups (the order inside the list means nothing) */
+                    unsigned mb = mybits;
+                    while (mb != 0u) {
+                        const int i = __ffs(mb) - 1;
+                        mb &= mb - 1u;
                         const float4 v   = s4[32 * i];
-                        const int    pos = wcnt + __popc(m & lt);
+                        const int    pos = atomicAdd(&sh->wcur[warp], 1);
                         if (pos < kGroupCapWarp) {
                             /* which of the four pass: the finisher takes those, the sums below leave those out */
                             const unsigned cm = (v.x >= tau ? 1u : 0u) | (v.y >= tau ? 2u : 0u) | (v.z >= tau ? 4u : 0u) | (v.w >= tau ? 8u : 0u);
@@ -2756,8 +2757,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                             atomicAdd(&sh->thist[min(kHistBins - 1, max(0, __float2int_rz((gmax - t_lo) * t_scale)))], 1);
                         }
                     }
-                    wcnt += __popc(m);
-                    since += __popc(m);
+                    __syncwarp();
+                    const int now = *reinterpret_cast<volatile int *>(&sh->wcur[warp]);
+                    since += now - wcnt;
+                    wcnt = now;
                 }
             }
             CYC(2);
@@ -2856,6 +2859,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) sample_stream_kernel(con
                     }
                     wcnt = kept;
                     if (lane == 0) {
+                        sh->wcur[warp] = kept;
                         sh->wsq[warp] = tau_c;
                     }
                     __syncwarp();
