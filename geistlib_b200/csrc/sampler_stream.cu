@@ -14,8 +14,9 @@
  *   threshold tau, a lower bound of the row's kq-th largest value: the part's first slice sets it (the thread
  *   maxima of all warps are binned by key; the only barriers inside a part), a histogram of the candidates
  *   raises it as the part streams. What is kept is the float4 GROUP that holds a candidate (four values and the
- *   id of the first), placed by one ballot and two stores into the warp's own list. Temperature and top-p rows
- *   also sum expf((x - warp maximum) * inv_t) per warp and slice.
+ *   id of the first): the lanes that hold any place them into the warp's own list themselves, one pass per
+ *   slice, the places counted in shared memory. Temperature and top-p rows also sum
+ *   expf((x - warp maximum) * inv_t) per warp and slice.
  *
  *   Before any of this a row's share may pass the soft cap tanhf(x / c) * c and the mask of allowed columns,
  *   in place in the stage (head.c:145-159; only launches that carry one pay for it).
@@ -33,8 +34,13 @@
  *   (top-k beyond 256, wide nuclei) are worked on a private copy of the row in global scratch (the multi-pass
  *   path, ROW_SLOW_PATH). finish_rows_kernel<false> carries all of that; finish_rows_kernel<true> carries greedy
  *   and top-k alone and is launched instead when the caller vouched for such rows (F_FAST_ONLY); with
- *   F_GREEDY_ONLY thread blocks that stream whole rows write the tokens themselves and no finishing kernel runs.
+ *   F_GREEDY_ONLY, and with F_INLINE_TOPK (whole rows per thread block, greedy and top-k rows), the stream kernel
+ *   writes the tokens itself and no finishing kernel runs.
  *   Histories of more than kRowIds ids are counted per row by row_ids_kernel ahead of all this.
+ *
+ *   The stream kernel is a template over what a launch can meet (kinds of rows vouched for, penalties at all,
+ *   plain input, short histories), chosen by the host at the launch: an instantiation carries no code for the
+ *   rest, and no call to an out-of-line function is left inside its slice loop.
  *
  * Semantics follow geistlib's CPU sampler:
  *   mode dispatch ............ src/archs/transformer/forward/head.c:172-183
